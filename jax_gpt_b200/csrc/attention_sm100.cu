@@ -1,0 +1,702 @@
+// Flash attention for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+//
+// Forward: one CTA per (128-query block, head, batch). Warp 0 streams K/V tiles with TMA,
+// warp 1 issues S = Q K^T and O_j = P V into TMEM, warps 2..5 own one query row per thread:
+// they read S from TMEM, do the online softmax without any cross-thread traffic, hand P back
+// through 128B-swizzled shared memory and keep the running output in registers. Two CTAs fit
+// on an SM (112 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the
+// other's MMAs.
+//
+// Backward: one CTA per (128-key block, kv head, batch) looping over the query blocks that
+// see it. It works on the TRANSPOSED score tile S^T = K Q^T so that each thread owns a key
+// row; P^T and dS^T go to shared memory once and serve three MMAs each through K-major and
+// MN-major descriptors (dV += P^T dO, dK += dS^T Q, dQ = dS K) with no transposes in memory.
+// dK/dV accumulate in TMEM across the whole loop; dQ tiles leave through fp32 reductions.
+//
+// Replaces the dense (B,H,T,S) score materialisation of the reference
+// (jax_gpt/models/gpt2/model.py:167-176, jax_gpt/models/qwen35/gqa.py:103-119) and applies
+// the causal rule q_pos >= k_pos on true positions.
+#include "attention_sm100.cuh"
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "tma_host.h"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct FwdArgs {
+  int B, T, H, Hkv;
+  float scale_log2;
+  int causal;
+  __nv_bfloat16* out;
+  int64_t ldo;
+  float* lse;
+  int* status;
+};
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kTile = 128 * D * 2;      // bytes of a 128 x D bf16 tile
+  static constexpr int kPBytes = 128 * 128 * 2;
+  static constexpr int kStages = 2;
+  static constexpr int kOffK = kTile;
+  static constexpr int kOffP = kTile + kStages * 2 * kTile;
+  static constexpr int kOffBar = kOffP + kPBytes;
+  static constexpr int kSmem = kOffBar + 256;
+  static constexpr int kTmemCols = 256;
+};
+
+struct FwdBars {
+  uint64_t q_full, kv_full[2], kv_empty[2], s_full, p_ready, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Writes 32 consecutive bf16 values of row `r`, columns [c0, c0+32) of a 128 x 128 tile laid
+// out as two K-major 128B-swizzled halves of 64 columns (the layout TMA would produce).
+__device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int r, int c0, const uint32_t (&pk)[16]) {
+  uint8_t* base = tile + (c0 >> 6) * 16384 + r * 128;
+  const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int phys = (chunk0 + i) ^ (r & 7);
+    *reinterpret_cast<uint4*>(base + phys * 16) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int col0, int row0) {
+#pragma unroll
+  for (int h = 0; h < D / 64; ++h) tma_load_2d(dst + h * 16384, m, bar, col0 + h * 64, row0);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, (D == 64) ? 2 : 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ FwdArgs a) {
+  using C = FwdCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_status(a.status, kBadArgument, 1, 0, 0);
+    return;
+  }
+  FwdBars* bars = reinterpret_cast<FwdBars*>(smem + C::kOffBar);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_blk = gridDim.x - 1 - blockIdx.x;  // longest rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hkv = h / (a.H / a.Hkv);
+  const int n_kv_all = (a.T + 127) / 128;
+  const int n_kv = a.causal ? min(q_blk + 1, n_kv_all) : n_kv_all;
+  const int row0 = b * a.T + q_blk * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->o_full, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  uint8_t* sQ = smem;
+  uint8_t* sP = smem + C::kOffP;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&bars->q_full, C::kTile);
+      load_tile<D>(sQ, &tq, &bars->q_full, h * D, row0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->kv_empty[s], ph ^ 1, abort_flag)) {
+          report_status(a.status, kWaitEmptyTimeout, 100, blockIdx.x, j);
+          break;
+        }
+        uint8_t* sK = smem + C::kOffK + s * 2 * C::kTile;
+        mbar_arrive_expect_tx(&bars->kv_full[s], 2 * C::kTile);
+        load_tile<D>(sK, &tk, &bars->kv_full[s], hkv * D, b * a.T + j * 128);
+        load_tile<D>(sK + C::kTile, &tv, &bars->kv_full[s], hkv * D, b * a.T + j * 128);
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc_s = make_idesc(128, 128, 0, 0, 1);
+    constexpr uint32_t idesc_o = make_idesc(128, D, 0, 1, 1);
+    bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+    if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 101, blockIdx.x, 0);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&bars->kv_full[s], ph, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 102, blockIdx.x, j);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t aQ = smem_u32(sQ);
+      const uint32_t aK = smem_u32(smem + C::kOffK + s * 2 * C::kTile);
+      const uint32_t aV = aK + C::kTile;
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), idesc_s, kk > 0);
+        }
+        tc_commit(&bars->s_full);
+      }
+      __syncwarp();
+      if (!mbar_wait(&bars->p_ready, j & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 103, blockIdx.x, j);
+        break;
+      }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t aP = smem_u32(sP);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem + 128, make_smem_desc(aP + off, 16, 1024), make_smem_desc(aV + kk * 2048, 16384, 1024),
+                    idesc_o, kk > 0);
+        }
+        tc_commit(&bars->o_full);
+        tc_commit(&bars->kv_empty[s]);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // query row inside the block == TMEM lane
+    const int qpos = q_blk * 128 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(&bars->s_full, j & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 104, blockIdx.x, j);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool need_mask = (a.causal && j == q_blk) || ((j + 1) * 128 > a.T);
+      const int kv0 = j * 128;
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]) * a.scale_log2;
+          if (need_mask) {
+            const int kvpos = kv0 + c * 32 + i;
+            if (kvpos >= a.T || (a.causal && kvpos > qpos)) s = -INFINITY;
+          }
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float mref = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = exp2f(m - mref);  // m == -inf -> 0
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float s0 = __uint_as_float(v[i]) * a.scale_log2, s1 = __uint_as_float(v[i + 1]) * a.scale_log2;
+          if (need_mask) {
+            const int kvpos = kv0 + c * 32 + i;
+            if (kvpos >= a.T || (a.causal && kvpos > qpos)) s0 = -INFINITY;
+            if (kvpos + 1 >= a.T || (a.causal && kvpos + 1 > qpos)) s1 = -INFINITY;
+          }
+          const float p0 = exp2f(s0 - mref), p1 = exp2f(s1 - mref);
+          rs += p0 + p1;
+          pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        store_row_chunk_sw128(sP, r, c * 32, pk);
+      }
+      l = l * alpha + rs;
+      m = mx;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready);
+      if (!mbar_wait(&bars->o_full, j & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 105, blockIdx.x, j);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + 128 + c * 32 + lane_off, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+    }
+    if (ok && qpos < a.T) {
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = a.out + static_cast<int64_t>(b * a.T + qpos) * a.ldo + h * D;
+#pragma unroll
+      for (int i = 0; i < D; i += 8) {
+        uint4 pk = make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
+                              pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv));
+        *reinterpret_cast<uint4*>(orow + i) = pk;
+      }
+      if (a.lse != nullptr) a.lse[(static_cast<int64_t>(b) * a.H + h) * a.T + qpos] = m + log2f(l);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+// ------------------------------------ backward ------------------------------------------
+struct BwdArgs {
+  int B, T, H, Hkv;
+  float scale, scale_log2;
+  int causal;
+  const float* lse;
+  const float* delta;
+  float* dq_accum;  // [B*T, H*D] fp32
+  __nv_bfloat16* dk;
+  int64_t lddk;
+  __nv_bfloat16* dv;
+  int64_t lddv;
+  int* status;
+};
+
+template <int D>
+struct BwdCfg {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kTile;
+  static constexpr int kOffRing = 2 * kTile;                      // stages of {Q_i, dO_i}
+  static constexpr int kOffPT = kOffRing + kStages * 2 * kTile;   // P^T  128 x 128 bf16
+  static constexpr int kOffDST = kOffPT + 32768;                  // dS^T 128 x 128 bf16
+  static constexpr int kOffStats = kOffDST + 32768;               // lse / delta, 2 x 2 x 128 fp32
+  static constexpr int kOffBar = kOffStats + 2048;
+  static constexpr int kSmem = kOffBar + 256;
+  static constexpr int kTmemCols = 512;  // S^T|dQ [0,128), dP^T [128,256), dV [256,256+D), dK [384,384+D)
+};
+
+struct BwdBars {
+  uint64_t kv_full, qdo_full[2], qdo_empty[2], st_full, p_ready, dq_full, dq_read, stats_ready;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                const __grid_constant__ BwdArgs a) {
+  using C = BwdCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_status(a.status, kBadArgument, 2, 0, 0);
+    return;
+  }
+  BwdBars* bars = reinterpret_cast<BwdBars*>(smem + C::kOffBar);
+  volatile int* abort_flag = &bars->abort_flag;
+  float* stats = reinterpret_cast<float*>(smem + C::kOffStats);  // [buf][0: lse, 1: delta][128]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x;  // key block
+  const int hkv = blockIdx.y, b = blockIdx.z;
+  const int group = a.H / a.Hkv;
+  const int n_q = (a.T + 127) / 128;
+  const int i0 = a.causal ? jb : 0;
+  const int nqi = n_q - i0;
+  const int n_iters = group * nqi;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->qdo_full[s], 1);
+      mbar_init(&bars->qdo_empty[s], 1);
+    }
+    mbar_init(&bars->st_full, 1);
+    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->dq_read, 128);
+    mbar_init(&bars->stats_ready, 128);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const int kv_row0 = b * a.T + jb * 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&bars->kv_full, 2 * C::kTile);
+      load_tile<D>(smem + C::kOffK, &tk, &bars->kv_full, hkv * D, kv_row0);
+      load_tile<D>(smem + C::kOffV, &tv, &bars->kv_full, hkv * D, kv_row0);
+      for (int it = 0; it < n_iters; ++it) {
+        const int s = it % C::kStages;
+        const uint32_t ph = (it / C::kStages) & 1;
+        if (!mbar_wait(&bars->qdo_empty[s], ph ^ 1, abort_flag)) {
+          report_status(a.status, kWaitEmptyTimeout, 200, blockIdx.x, it);
+          break;
+        }
+        const int hq = hkv * group + it / nqi;
+        const int qrow0 = b * a.T + (i0 + it % nqi) * 128;
+        uint8_t* st = smem + C::kOffRing + s * 2 * C::kTile;
+        mbar_arrive_expect_tx(&bars->qdo_full[s], 2 * C::kTile);
+        load_tile<D>(st, &tq, &bars->qdo_full[s], hq * D, qrow0);
+        load_tile<D>(st + C::kTile, &tdo, &bars->qdo_full[s], hq * D, qrow0);
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc_st = make_idesc(128, 128, 0, 0, 1);  // K-major x K-major
+    constexpr uint32_t idesc_kn = make_idesc(128, D, 0, 1, 1);    // A K-major, B MN-major
+    constexpr uint32_t idesc_nn = make_idesc(128, D, 1, 1, 1);    // A MN-major, B MN-major
+    bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
+    if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 201, blockIdx.x, 0);
+    const uint32_t aK = smem_u32(smem + C::kOffK), aV = smem_u32(smem + C::kOffV);
+    const uint32_t aPT = smem_u32(smem + C::kOffPT), aDST = smem_u32(smem + C::kOffDST);
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const int s = it % C::kStages;
+      const uint32_t ph = (it / C::kStages) & 1;
+      if (!mbar_wait(&bars->qdo_full[s], ph, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 202, blockIdx.x, it);
+        break;
+      }
+      if (it > 0 && !mbar_wait(&bars->dq_read, (it - 1) & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 203, blockIdx.x, it);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t aQ = smem_u32(smem + C::kOffRing + s * 2 * C::kTile);
+      const uint32_t aDO = aQ + C::kTile;
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024), idesc_st, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem + 128, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + off, 16, 1024), idesc_st,
+                    kk > 0);
+        }
+        tc_commit(&bars->st_full);
+      }
+      __syncwarp();
+      if (!mbar_wait(&bars->p_ready, it & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 204, blockIdx.x, it);
+        break;
+      }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // contraction over the 128 query rows
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem + 256, make_smem_desc(aPT + off, 16, 1024), make_smem_desc(aDO + kk * 2048, 16384, 1024),
+                    idesc_kn, (it > 0 || kk > 0));
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem + 384, make_smem_desc(aDST + off, 16, 1024), make_smem_desc(aQ + kk * 2048, 16384, 1024),
+                    idesc_kn, (it > 0 || kk > 0));
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // contraction over the 128 key rows: dQ = dS K
+          umma_bf16(tmem, make_smem_desc(aDST + kk * 2048, 16384, 1024), make_smem_desc(aK + kk * 2048, 16384, 1024),
+                    idesc_nn, kk > 0);
+        }
+        tc_commit(&bars->dq_full);
+        tc_commit(&bars->qdo_empty[s]);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;  // key row inside the block (and query row when reading dQ)
+    const int tid = threadIdx.x - 64;
+    const int kvpos = jb * 128 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_iters; ++it) {
+      const int hq = hkv * group + it / nqi;
+      const int iq = i0 + it % nqi;
+      const int q0 = iq * 128;
+      float* st_lse = stats + (it & 1) * 256;
+      float* st_del = st_lse + 128;
+      {
+        const int qp = q0 + tid;
+        const int64_t si = (static_cast<int64_t>(b) * a.H + hq) * a.T + qp;
+        st_lse[tid] = (qp < a.T) ? a.lse[si] : 0.f;
+        st_del[tid] = (qp < a.T) ? a.delta[si] : 0.f;
+      }
+      // bounded rendezvous of the 128 compute threads on the per-query statistics
+      mbar_arrive(&bars->stats_ready);
+      if (!mbar_wait(&bars->stats_ready, it & 1, abort_flag) || !mbar_wait(&bars->st_full, it & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 205, blockIdx.x, it);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool need_mask = (a.causal && iq == jb) || ((iq + 1) * 128 > a.T) || ((jb + 1) * 128 > a.T);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tmem + c * 32 + lane_off, sv);
+        tmem_ld_32x32(tmem + 128 + c * 32 + lane_off, dv);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int qi = c * 32 + i + e;
+            bool valid = true;
+            if (need_mask) {
+              const int qp = q0 + qi;
+              valid = !(qp >= a.T || kvpos >= a.T || (a.causal && qp < kvpos));
+            }
+            const float pe = valid ? exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - st_lse[qi]) : 0.f;
+            p[e] = pe;
+            ds[e] = valid ? pe * (__uint_as_float(dv[i + e]) - st_del[qi]) * a.scale : 0.f;
+          }
+          pp[i >> 1] = pack_bf16x2(p[0], p[1]);
+          dd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+        }
+        store_row_chunk_sw128(smem + C::kOffPT, r, c * 32, pp);
+        store_row_chunk_sw128(smem + C::kOffDST, r, c * 32, dd);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready);
+      if (!mbar_wait(&bars->dq_full, it & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 206, blockIdx.x, it);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      {
+        const int qp = q0 + r;
+        float* dq = a.dq_accum + (static_cast<int64_t>(b) * a.T + qp) * (static_cast<int64_t>(a.H) * D) + hq * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+          tmem_ld_wait();
+          if (qp < a.T) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq + c * 32 + i),
+                           "f"(__uint_as_float(v[i])), "f"(__uint_as_float(v[i + 1])), "f"(__uint_as_float(v[i + 2])),
+                           "f"(__uint_as_float(v[i + 3]))
+                           : "memory");
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->dq_read);
+    }
+    if (ok && n_iters > 0) {
+      // The last dq_full commit also covered every dV / dK accumulation.
+      tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* base = which == 0 ? a.dv : a.dk;
+        const int64_t ld = which == 0 ? a.lddv : a.lddk;
+        const uint32_t col = which == 0 ? 256 : 384;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + col + c * 32 + lane_off, v);
+          tmem_ld_wait();
+          if (kvpos < a.T) {
+            __nv_bfloat16* dst = base + static_cast<int64_t>(b * a.T + kvpos) * ld + hkv * D + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 pk = make_uint4(pack_bf16x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                                    pack_bf16x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                                    pack_bf16x2(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                                    pack_bf16x2(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+              *reinterpret_cast<uint4*>(dst + i) = pk;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (row, head).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo,
+                                  const __nv_bfloat16* __restrict__ dout, int64_t lddo, float* __restrict__ delta,
+                                  int B, int T, int H, int D) {
+  const int64_t gw = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= static_cast<int64_t>(B) * T * H) return;
+  const int h = static_cast<int>(gw % H);
+  const int64_t row = gw / H;
+  const __nv_bfloat16* po = o + row * ldo + h * D;
+  const __nv_bfloat16* pd = dout + row * lddo + h * D;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + d));
+    float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + d));
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) {
+    const int64_t bidx = row / T, t = row % T;
+    delta[(bidx * H + h) * T + t] = s;
+  }
+}
+
+__global__ void cast_rows_kernel(const float* __restrict__ src, int64_t lds, __nv_bfloat16* __restrict__ dst,
+                                 int64_t ldd, int M, int N) {
+  const int n4 = N / 4;
+  const int64_t total = static_cast<int64_t>(M) * n4;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / n4;
+    const int c = static_cast<int>(i % n4) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(src + r * lds + c);
+    uint2 pk = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    *reinterpret_cast<uint2*>(dst + r * ldd + c) = pk;
+  }
+}
+
+cudaError_t make_map(CUtensorMap* m, const __nv_bfloat16* p, int64_t ld, int rows, int cols) {
+  return encode_tma_2d(m, p, 2, cols, rows, ld * 2, 64, 128);
+}
+
+template <int D>
+cudaError_t fwd_launch(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* out, int64_t ldo, float* lse,
+                       int* status, cudaStream_t stream) {
+  using C = FwdCfg<D>;
+  CUtensorMap tq, tk, tv;
+  const int rows = s.B * s.T;
+  cudaError_t e;
+  if ((e = make_map(&tq, t.q, t.ldq, rows, s.H * D)) != cudaSuccess) return e;
+  if ((e = make_map(&tk, t.k, t.ldk, rows, s.Hkv * D)) != cudaSuccess) return e;
+  if ((e = make_map(&tv, t.v, t.ldv, rows, s.Hkv * D)) != cudaSuccess) return e;
+  auto kernel = attn_fwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem)) != cudaSuccess)
+      return e;
+    configured = true;
+  }
+  FwdArgs a{s.B, s.T, s.H, s.Hkv, s.scale * kLog2e, s.causal, out, ldo, lse, status};
+  dim3 grid((s.T + 127) / 128, s.H, s.B);
+  kernel<<<grid, kThreads, C::kSmem, stream>>>(tq, tk, tv, a);
+  return cudaGetLastError();
+}
+
+template <int D>
+cudaError_t bwd_launch(const AttnTensors& t, const AttnShape& s, const __nv_bfloat16* out, int64_t ldo,
+                       const __nv_bfloat16* dout, int64_t lddo, const float* lse, float* delta, float* dq_accum,
+                       __nv_bfloat16* dk, int64_t lddk, __nv_bfloat16* dv, int64_t lddv, int* status,
+                       cudaStream_t stream) {
+  using C = BwdCfg<D>;
+  CUtensorMap tq, tk, tv, tdo;
+  const int rows = s.B * s.T;
+  cudaError_t e;
+  if ((e = make_map(&tq, t.q, t.ldq, rows, s.H * D)) != cudaSuccess) return e;
+  if ((e = make_map(&tk, t.k, t.ldk, rows, s.Hkv * D)) != cudaSuccess) return e;
+  if ((e = make_map(&tv, t.v, t.ldv, rows, s.Hkv * D)) != cudaSuccess) return e;
+  if ((e = make_map(&tdo, dout, lddo, rows, s.H * D)) != cudaSuccess) return e;
+  {
+    const int64_t warps = static_cast<int64_t>(rows) * s.H;
+    const int blocks = static_cast<int>((warps * 32 + 255) / 256);
+    attn_delta_kernel<<<blocks, 256, 0, stream>>>(out, ldo, dout, lddo, delta, s.B, s.T, s.H, D);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  }
+  auto kernel = attn_bwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem)) != cudaSuccess)
+      return e;
+    configured = true;
+  }
+  BwdArgs a{s.B, s.T, s.H, s.Hkv, s.scale, s.scale * kLog2e, s.causal, lse, delta, dq_accum, dk, lddk, dv, lddv, status};
+  dim3 grid((s.T + 127) / 128, s.Hkv, s.B);
+  kernel<<<grid, kThreads, C::kSmem, stream>>>(tq, tk, tv, tdo, a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_attn_fwd(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* out, int64_t ldo, float* lse,
+                            int* status, cudaStream_t stream) {
+  if (s.H % s.Hkv != 0) return cudaErrorInvalidValue;
+  if (s.D == 64) return fwd_launch<64>(t, s, out, ldo, lse, status, stream);
+  if (s.D == 128) return fwd_launch<128>(t, s, out, ldo, lse, status, stream);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_attn_bwd(const AttnTensors& t, const AttnShape& s, const __nv_bfloat16* out, int64_t ldo,
+                            const __nv_bfloat16* dout, int64_t lddo, const float* lse, float* delta, float* dq_accum,
+                            __nv_bfloat16* dk, int64_t lddk, __nv_bfloat16* dv, int64_t lddv, int* status,
+                            cudaStream_t stream) {
+  if (s.H % s.Hkv != 0) return cudaErrorInvalidValue;
+  if (s.D == 64)
+    return bwd_launch<64>(t, s, out, ldo, dout, lddo, lse, delta, dq_accum, dk, lddk, dv, lddv, status, stream);
+  if (s.D == 128)
+    return bwd_launch<128>(t, s, out, ldo, dout, lddo, lse, delta, dq_accum, dk, lddk, dv, lddv, status, stream);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_cast_rows_f32_bf16(const float* src, int64_t lds, __nv_bfloat16* dst, int64_t ldd, int M, int N,
+                                      cudaStream_t stream) {
+  if (N % 4 != 0) return cudaErrorInvalidValue;
+  const int64_t total = static_cast<int64_t>(M) * (N / 4);
+  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  cast_rows_kernel<<<grid, 256, 0, stream>>>(src, lds, dst, ldd, M, N);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

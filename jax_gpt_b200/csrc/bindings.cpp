@@ -1,0 +1,330 @@
+// torch bindings for the sm_100a kernels: tensors in, raw pointers + current stream out.
+// Registered as torch.ops.b200.* ; no computation happens in this file.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include "attention_sm100.cuh"
+#include "elementwise.cuh"
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using at::Tensor;
+using b200::GemmArgs;
+
+#define B200_CHECK_CUDA(expr)                                                              \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    TORCH_CHECK(_e == cudaSuccess, "b200 kernel launch failed: ", cudaGetErrorString(_e)); \
+  } while (0)
+
+const __nv_bfloat16* bf16_ptr(const Tensor& t) { return reinterpret_cast<const __nv_bfloat16*>(t.data_ptr()); }
+__nv_bfloat16* bf16_mut(Tensor& t) { return reinterpret_cast<__nv_bfloat16*>(t.data_ptr()); }
+const __nv_bfloat16* bf16_opt(const c10::optional<Tensor>& t) {
+  return t.has_value() ? reinterpret_cast<const __nv_bfloat16*>(t->data_ptr()) : nullptr;
+}
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_bf16_2d(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1, name,
+              " must be a 2-D bf16 CUDA tensor with unit inner stride");
+  TORCH_CHECK(t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name,
+              " must have a 16-byte aligned base and row stride");
+}
+
+// One status buffer per device: 4 int32 words written by kernels whose bounded waits expire.
+Tensor status_tensor(int device) {
+  static std::vector<Tensor> per_device(64);
+  if (!per_device[device].defined()) {
+    per_device[device] = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  }
+  return per_device[device];
+}
+int* status_ptr(const Tensor& like) { return status_tensor(like.get_device()).data_ptr<int>(); }
+
+Tensor status(int64_t device) { return status_tensor(static_cast<int>(device)); }
+
+// out[M,N] = epilogue(alpha * A @ B^T ...). a: [M,K] (or [K,M] if a_mn_major); b: [N,K] (or [K,N]).
+void gemm(const Tensor& a, bool a_mn_major, const Tensor& b, bool b_mn_major, Tensor out,
+          const c10::optional<Tensor>& bias, const c10::optional<Tensor>& residual, const c10::optional<Tensor>& aux,
+          int64_t epilogue, int64_t out_mode, double alpha, int64_t split_k) {
+  c10::cuda::CUDAGuard guard(a.device());
+  check_bf16_2d(a, "a");
+  check_bf16_2d(b, "b");
+  const int M = static_cast<int>(a_mn_major ? a.size(1) : a.size(0));
+  const int K = static_cast<int>(a_mn_major ? a.size(0) : a.size(1));
+  const int N = static_cast<int>(b_mn_major ? b.size(1) : b.size(0));
+  const int Kb = static_cast<int>(b_mn_major ? b.size(0) : b.size(1));
+  TORCH_CHECK(K == Kb, "gemm: contraction sizes differ: ", K, " vs ", Kb);
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1,
+              "gemm: out must be [M,N] with unit inner stride");
+  GemmArgs g{};
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.out = out.data_ptr();
+  g.ldo = out.stride(0);
+  g.out_mode = static_cast<int>(out_mode);
+  if (g.out_mode == b200::kOutBf16) {
+    TORCH_CHECK(out.scalar_type() == at::kBFloat16, "gemm: out must be bf16");
+  } else {
+    TORCH_CHECK(out.scalar_type() == at::kFloat, "gemm: out must be fp32 for this output mode");
+  }
+  g.bias = bf16_opt(bias);
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->numel() == N && bias->scalar_type() == at::kBFloat16, "gemm: bad bias");
+  }
+  g.residual = bf16_opt(residual);
+  g.ldr = residual.has_value() ? residual->stride(0) : 0;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->size(0) == M && residual->size(1) == N,
+                "gemm: bad residual");
+  }
+  g.epilogue = static_cast<int>(epilogue);
+  if (g.epilogue == b200::kEpiGelu) {
+    TORCH_CHECK(aux.has_value() && aux->scalar_type() == at::kBFloat16 && aux->size(0) == M && aux->size(1) == N,
+                "gemm: GELU epilogue needs an [M,N] bf16 aux output");
+    g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux->data_ptr());
+    g.ldaux = aux->stride(0);
+  } else if (g.epilogue == b200::kEpiGeluGrad) {
+    TORCH_CHECK(aux.has_value() && aux->scalar_type() == at::kBFloat16 && aux->size(0) == M && aux->size(1) == N,
+                "gemm: GELU-grad epilogue needs the [M,N] bf16 pre-activation");
+    g.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux->data_ptr());
+    g.ldaux = aux->stride(0);
+  }
+  g.alpha = static_cast<float>(alpha);
+  g.split_k = static_cast<int>(split_k);
+  g.status = status_ptr(a);
+  B200_CHECK_CUDA(b200::launch_gemm_bf16(bf16_ptr(a), a.stride(0), a_mn_major ? 1 : 0, bf16_ptr(b), b.stride(0),
+                                         b_mn_major ? 1 : 0, g, cur_stream()));
+}
+
+// All-gather -> GEMM over peer-mapped activation shards (pointers as int64), and GEMM ->
+// reduce-scatter into peer-mapped fp32 buffers. Shapes: each shard [rows_per_src, K] bf16.
+void gemm_gathered_a(std::vector<int64_t> a_ptrs, int64_t rows_per_src, int64_t first_src, int64_t K, int64_t lda,
+                     const Tensor& b, bool b_mn_major, Tensor out, const c10::optional<Tensor>& bias) {
+  c10::cuda::CUDAGuard guard(b.device());
+  check_bf16_2d(b, "b");
+  const int n_src = static_cast<int>(a_ptrs.size());
+  TORCH_CHECK(n_src >= 1 && n_src <= b200::kMaxPeers, "gemm_gathered_a: 1..8 sources");
+  const int N = static_cast<int>(b_mn_major ? b.size(1) : b.size(0));
+  GemmArgs g{};
+  g.M = static_cast<int>(rows_per_src * n_src);
+  g.N = N;
+  g.K = static_cast<int>(K);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == g.M && out.size(1) == N, "gemm_gathered_a: bad out");
+  g.out = out.data_ptr();
+  g.ldo = out.stride(0);
+  g.out_mode = b200::kOutBf16;
+  g.bias = bf16_opt(bias);
+  g.alpha = 1.f;
+  g.split_k = 1;
+  g.status = status_ptr(b);
+  const __nv_bfloat16* srcs[b200::kMaxPeers];
+  for (int i = 0; i < n_src; ++i) srcs[i] = reinterpret_cast<const __nv_bfloat16*>(a_ptrs[i]);
+  B200_CHECK_CUDA(b200::launch_gemm_bf16_gathered_a(srcs, n_src, static_cast<int>(rows_per_src),
+                                                    static_cast<int>(first_src), lda, bf16_ptr(b), b.stride(0),
+                                                    b_mn_major ? 1 : 0, g, cur_stream()));
+}
+
+void gemm_reduce_scatter(const Tensor& a, const Tensor& b, bool b_mn_major, std::vector<int64_t> out_ptrs,
+                         int64_t rows_per_peer, int64_t ldo) {
+  c10::cuda::CUDAGuard guard(a.device());
+  check_bf16_2d(a, "a");
+  check_bf16_2d(b, "b");
+  const int n = static_cast<int>(out_ptrs.size());
+  TORCH_CHECK(n >= 1 && n <= b200::kMaxPeers, "gemm_reduce_scatter: 1..8 peers");
+  GemmArgs g{};
+  g.M = static_cast<int>(a.size(0));
+  g.K = static_cast<int>(a.size(1));
+  g.N = static_cast<int>(b_mn_major ? b.size(1) : b.size(0));
+  TORCH_CHECK(rows_per_peer * n == g.M, "gemm_reduce_scatter: rows_per_peer * peers must equal M");
+  g.out = nullptr;
+  g.ldo = ldo;
+  g.out_mode = b200::kOutBf16PeerRed;
+  g.n_peers = n;
+  g.rows_per_peer = static_cast<int>(rows_per_peer);
+  for (int i = 0; i < n; ++i) g.peer_out[i] = reinterpret_cast<float*>(out_ptrs[i]);
+  g.alpha = 1.f;
+  g.split_k = 1;
+  g.status = status_ptr(a);
+  B200_CHECK_CUDA(b200::launch_gemm_bf16(bf16_ptr(a), a.stride(0), 0, bf16_ptr(b), b.stride(0), b_mn_major ? 1 : 0, g,
+                                         cur_stream()));
+}
+
+void norm_fwd(int64_t mode, const Tensor& x, const Tensor& gamma, const c10::optional<Tensor>& beta, Tensor y,
+              c10::optional<Tensor> mean, c10::optional<Tensor> rstd, double eps) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.scalar_type() == at::kBFloat16, "norm_fwd: contiguous bf16");
+  const int D = static_cast<int>(x.size(-1));
+  const int M = static_cast<int>(x.numel() / D);
+  B200_CHECK_CUDA(b200::launch_norm_fwd(static_cast<int>(mode), bf16_ptr(x), bf16_ptr(gamma), bf16_opt(beta),
+                                        bf16_mut(y), mean.has_value() ? mean->data_ptr<float>() : nullptr,
+                                        rstd.has_value() ? rstd->data_ptr<float>() : nullptr, M, D,
+                                        static_cast<float>(eps), cur_stream()));
+}
+
+void norm_bwd(int64_t mode, const Tensor& dy, const Tensor& x, const Tensor& gamma, const c10::optional<Tensor>& mean,
+              const Tensor& rstd, const c10::optional<Tensor>& dres, Tensor dx, Tensor dgamma,
+              c10::optional<Tensor> dbeta) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous(), "norm_bwd: contiguous tensors");
+  TORCH_CHECK(dgamma.scalar_type() == at::kFloat, "norm_bwd: dgamma must be fp32");
+  const int D = static_cast<int>(x.size(-1));
+  const int M = static_cast<int>(x.numel() / D);
+  B200_CHECK_CUDA(b200::launch_norm_bwd(static_cast<int>(mode), bf16_ptr(dy), bf16_ptr(x), bf16_ptr(gamma),
+                                        mean.has_value() ? mean->data_ptr<float>() : nullptr, rstd.data_ptr<float>(),
+                                        bf16_opt(dres), bf16_mut(dx), dgamma.data_ptr<float>(),
+                                        dbeta.has_value() ? dbeta->data_ptr<float>() : nullptr, M, D, cur_stream()));
+}
+
+void embed_fwd(const Tensor& idx, const Tensor& wte, const c10::optional<Tensor>& wpe, Tensor out, int64_t T,
+               int64_t pos0) {
+  c10::cuda::CUDAGuard guard(idx.device());
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous(), "embed_fwd: int32 contiguous indices");
+  const int D = static_cast<int>(wte.size(1));
+  B200_CHECK_CUDA(b200::launch_embed_fwd(idx.data_ptr<int>(), bf16_ptr(wte), bf16_opt(wpe), bf16_mut(out),
+                                         static_cast<int>(idx.numel()), static_cast<int>(T), D,
+                                         static_cast<int>(pos0), cur_stream()));
+}
+
+void embed_bwd(const Tensor& idx, const Tensor& dout, Tensor dwte, c10::optional<Tensor> dwpe, int64_t T,
+               int64_t pos0) {
+  c10::cuda::CUDAGuard guard(idx.device());
+  TORCH_CHECK(dwte.scalar_type() == at::kFloat, "embed_bwd: fp32 gradient buffers");
+  const int D = static_cast<int>(dwte.size(1));
+  B200_CHECK_CUDA(b200::launch_embed_bwd(idx.data_ptr<int>(), bf16_ptr(dout), dwte.data_ptr<float>(),
+                                         dwpe.has_value() ? dwpe->data_ptr<float>() : nullptr,
+                                         static_cast<int>(idx.numel()), static_cast<int>(T), D,
+                                         static_cast<int>(pos0), cur_stream()));
+}
+
+void ce_fwd_bwd(Tensor logits, const Tensor& targets, Tensor loss, int64_t V, double scale, bool write_grad) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.scalar_type() == at::kBFloat16, "ce: bf16 logits");
+  TORCH_CHECK(targets.scalar_type() == at::kInt && loss.scalar_type() == at::kFloat, "ce: int32 targets, fp32 loss");
+  B200_CHECK_CUDA(b200::launch_ce_fwd_bwd(bf16_mut(logits), targets.data_ptr<int>(), loss.data_ptr<float>(),
+                                          static_cast<int>(logits.size(0)), static_cast<int>(V),
+                                          static_cast<int>(logits.stride(0)), static_cast<float>(scale),
+                                          write_grad ? 1 : 0, cur_stream()));
+}
+
+void bias_grad(const Tensor& dy, Tensor dbias) {
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(dy.is_contiguous() && dy.dim() == 2 && dbias.scalar_type() == at::kFloat, "bias_grad: bad arguments");
+  B200_CHECK_CUDA(b200::launch_bias_grad(bf16_ptr(dy), dbias.data_ptr<float>(), static_cast<int>(dy.size(0)),
+                                         static_cast<int>(dy.size(1)), cur_stream()));
+}
+
+void sumsq(const Tensor& g, Tensor out) {
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.is_contiguous() && g.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat, "sumsq: fp32");
+  B200_CHECK_CUDA(b200::launch_sumsq(g.data_ptr<float>(), g.numel(), out.data_ptr<float>(), cur_stream()));
+}
+
+void adamw(Tensor p, Tensor g, Tensor m, Tensor v, c10::optional<Tensor> p_bf16, const Tensor& hp,
+           const c10::optional<Tensor>& gnorm_sq, double beta1, double beta2, double eps, double wd, double clip,
+           bool zero_grad) {
+  c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous");
+  TORCH_CHECK(p.scalar_type() == at::kFloat && g.scalar_type() == at::kFloat, "adamw: fp32 master and grad");
+  B200_CHECK_CUDA(b200::launch_adamw(
+      p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+      p_bf16.has_value() ? reinterpret_cast<__nv_bfloat16*>(p_bf16->data_ptr()) : nullptr, p.numel(),
+      hp.data_ptr<float>(), gnorm_sq.has_value() ? gnorm_sq->data_ptr<float>() : nullptr, static_cast<float>(beta1),
+      static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd), static_cast<float>(clip),
+      zero_grad ? 1 : 0, cur_stream()));
+}
+
+// q/k/v: 2-D bf16 views [B*T, H*D] (possibly column slices of one fused buffer).
+void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Tensor lse, int64_t B, int64_t T,
+              int64_t H, int64_t Hkv, int64_t D, double scale, bool causal) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16_2d(q, "q");
+  check_bf16_2d(k, "k");
+  check_bf16_2d(v, "v");
+  check_bf16_2d(out, "out");
+  b200::AttnTensors t{bf16_ptr(q), bf16_ptr(k), bf16_ptr(v), q.stride(0), k.stride(0), v.stride(0)};
+  b200::AttnShape s{static_cast<int>(B), static_cast<int>(T), static_cast<int>(H), static_cast<int>(Hkv),
+                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0};
+  B200_CHECK_CUDA(b200::launch_attn_fwd(t, s, bf16_mut(out), out.stride(0), lse.data_ptr<float>(), status_ptr(q),
+                                        cur_stream()));
+}
+
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& dout,
+              const Tensor& lse, Tensor delta, Tensor dq_accum, Tensor dk, Tensor dv, int64_t B, int64_t T, int64_t H,
+              int64_t Hkv, int64_t D, double scale, bool causal) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16_2d(q, "q");
+  check_bf16_2d(k, "k");
+  check_bf16_2d(v, "v");
+  check_bf16_2d(out, "out");
+  check_bf16_2d(dout, "dout");
+  check_bf16_2d(dk, "dk");
+  check_bf16_2d(dv, "dv");
+  TORCH_CHECK(dq_accum.scalar_type() == at::kFloat && dq_accum.is_contiguous(), "attn_bwd: dq_accum fp32 contiguous");
+  b200::AttnTensors t{bf16_ptr(q), bf16_ptr(k), bf16_ptr(v), q.stride(0), k.stride(0), v.stride(0)};
+  b200::AttnShape s{static_cast<int>(B), static_cast<int>(T), static_cast<int>(H), static_cast<int>(Hkv),
+                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0};
+  B200_CHECK_CUDA(b200::launch_attn_bwd(t, s, bf16_ptr(out), out.stride(0), bf16_ptr(dout), dout.stride(0),
+                                        lse.data_ptr<float>(), delta.data_ptr<float>(), dq_accum.data_ptr<float>(),
+                                        bf16_mut(dk), dk.stride(0), bf16_mut(dv), dv.stride(0), status_ptr(q),
+                                        cur_stream()));
+}
+
+void cast_rows(const Tensor& src, Tensor dst) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.dim() == 2 && dst.dim() == 2 && src.stride(1) == 1 && dst.stride(1) == 1, "cast_rows: 2-D");
+  TORCH_CHECK(src.scalar_type() == at::kFloat && dst.scalar_type() == at::kBFloat16, "cast_rows: fp32 -> bf16");
+  B200_CHECK_CUDA(b200::launch_cast_rows_f32_bf16(src.data_ptr<float>(), src.stride(0), bf16_mut(dst), dst.stride(0),
+                                                  static_cast<int>(src.size(0)), static_cast<int>(src.size(1)),
+                                                  cur_stream()));
+}
+
+}  // namespace
+
+#include "bindings_extra.inc"
+
+TORCH_LIBRARY(b200, m) {
+  m.def("status(int device) -> Tensor", &status);
+  m.def(
+      "gemm(Tensor a, bool a_mn_major, Tensor b, bool b_mn_major, Tensor(a!) out, Tensor? bias, Tensor? residual, "
+      "Tensor? aux, int epilogue, int out_mode, float alpha, int split_k) -> ()",
+      &gemm);
+  m.def(
+      "gemm_gathered_a(int[] a_ptrs, int rows_per_src, int first_src, int K, int lda, Tensor b, bool b_mn_major, "
+      "Tensor(a!) out, Tensor? bias) -> ()",
+      &gemm_gathered_a);
+  m.def("gemm_reduce_scatter(Tensor a, Tensor b, bool b_mn_major, int[] out_ptrs, int rows_per_peer, int ldo) -> ()",
+        &gemm_reduce_scatter);
+  m.def(
+      "norm_fwd(int mode, Tensor x, Tensor gamma, Tensor? beta, Tensor(a!) y, Tensor(b!)? mean, Tensor(c!)? rstd, "
+      "float eps) -> ()",
+      &norm_fwd);
+  m.def(
+      "norm_bwd(int mode, Tensor dy, Tensor x, Tensor gamma, Tensor? mean, Tensor rstd, Tensor? dres, Tensor(a!) dx, "
+      "Tensor(b!) dgamma, Tensor(c!)? dbeta) -> ()",
+      &norm_bwd);
+  m.def("embed_fwd(Tensor idx, Tensor wte, Tensor? wpe, Tensor(a!) out, int T, int pos0) -> ()", &embed_fwd);
+  m.def("embed_bwd(Tensor idx, Tensor dout, Tensor(a!) dwte, Tensor(b!)? dwpe, int T, int pos0) -> ()", &embed_bwd);
+  m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor(b!) loss, int V, float scale, bool write_grad) -> ()",
+        &ce_fwd_bwd);
+  m.def("bias_grad(Tensor dy, Tensor(a!) dbias) -> ()", &bias_grad);
+  m.def("sumsq(Tensor g, Tensor(a!) out) -> ()", &sumsq);
+  m.def(
+      "adamw(Tensor(a!) p, Tensor(b!) g, Tensor(c!) m, Tensor(d!) v, Tensor(e!)? p_bf16, Tensor hp, Tensor? gnorm_sq, "
+      "float beta1, float beta2, float eps, float wd, float clip, bool zero_grad) -> ()",
+      &adamw);
+  m.def(
+      "attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, int B, int T, int H, int Hkv, int D, "
+      "float scale, bool causal) -> ()",
+      &attn_fwd);
+  m.def(
+      "attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor dout, Tensor lse, Tensor(a!) delta, Tensor(b!) "
+      "dq_accum, Tensor(c!) dk, Tensor(d!) dv, int B, int T, int H, int Hkv, int D, float scale, bool causal) -> ()",
+      &attn_bwd);
+  m.def("cast_rows(Tensor src, Tensor(a!) dst) -> ()", &cast_rows);
+  b200_register_extra(m);
+}

@@ -1,0 +1,97 @@
+"""Causal / full softmax attention: tcgen05 flash kernels on CUDA, dense fp32 reference elsewhere.
+
+The reference materialises (B,H,T,S) scores (jax_gpt/models/gpt2/model.py:167-176,
+jax_gpt/models/qwen35/gqa.py:103-119); the kernels tile the same math with an online softmax.
+Tensors are [B, T, H, D]; q/k/v may be column slices of one fused projection output.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import _ext
+
+
+def attention_ref(q, k, v, causal: bool = True, scale: Optional[float] = None, q_pos0: int = 0):
+    """fp32 dense attention; q [B,T,H,D], k/v [B,S,Hkv,D]; query i sits at position q_pos0 + i."""
+    B, T, H, D = q.shape
+    S, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, dim=1)
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    if causal:
+        qp = torch.arange(T, device=q.device)[:, None] + q_pos0
+        kp = torch.arange(S, device=q.device)[None, :]
+        s = s.masked_fill(kp > qp, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return (p @ vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def _as2d(t):
+    B, T, H, D = t.shape
+    assert t.stride(3) == 1 and t.stride(2) == D and t.stride(0) == T * t.stride(1), "unsupported attention layout"
+    return t.as_strided((B * T, H * D), (t.stride(1), 1))
+
+
+def attn_fwd(q, k, v, causal=True, scale=None, out=None, lse=None):
+    """Raw CUDA forward. Returns (out [B,T,H,D] bf16, lse [B,H,T] fp32 in log2 units)."""
+    B, T, H, D = q.shape
+    Hkv = k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty(B, T, H, D, device=q.device, dtype=torch.bfloat16)
+    if lse is None:
+        lse = torch.empty(B, H, T, device=q.device, dtype=torch.float32)
+    _ext.ops().attn_fwd(_as2d(q), _as2d(k), _as2d(v), _as2d(out), lse, B, T, H, Hkv, D, scale, causal)
+    return out, lse
+
+
+def attn_bwd(q, k, v, out, dout, lse, causal=True, scale=None, dq=None, dk=None, dv=None, dq_accum=None, delta=None):
+    """Raw CUDA backward. Returns (dq, dk, dv) in bf16 with the layouts of q/k/v."""
+    B, T, H, D = q.shape
+    Hkv = k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if dq_accum is None:
+        dq_accum = torch.zeros(B * T, H * D, device=q.device, dtype=torch.float32)
+    if delta is None:
+        delta = torch.empty(B, H, T, device=q.device, dtype=torch.float32)
+    if dq is None:
+        dq = torch.empty(B, T, H, D, device=q.device, dtype=torch.bfloat16)
+    if dk is None:
+        dk = torch.empty(B, T, Hkv, D, device=q.device, dtype=torch.bfloat16)
+    if dv is None:
+        dv = torch.empty(B, T, Hkv, D, device=q.device, dtype=torch.bfloat16)
+    _ext.ops().attn_bwd(_as2d(q), _as2d(k), _as2d(v), _as2d(out), _as2d(dout), lse, delta, dq_accum, _as2d(dk),
+                        _as2d(dv), B, T, H, Hkv, D, scale, causal)
+    _ext.ops().cast_rows(dq_accum, _as2d(dq))
+    return dq, dk, dv
+
+
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        out, lse = attn_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = attn_bwd(q, k, v, out, dout.contiguous(), lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def supports_cuda_kernel(q, k) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[1] == k.shape[1])
+
+
+def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
+    """Softmax attention over [B,T,H,D] tensors (GQA when k/v have fewer heads)."""
+    if supports_cuda_kernel(q, k):
+        return _AttnFn.apply(q, k, v, causal, scale)
+    return attention_ref(q, k, v, causal, scale)
