@@ -1,0 +1,275 @@
+// Communication fused into compute over NVLink peer memory.
+//
+// sharded_adamw_kernel is the FSDP / ZeRO optimizer step as ONE cooperative kernel per rank:
+//
+//   flag barrier (all ranks' gradients are final)
+//   A: reduce-scatter  - this rank sums its 1/W slice of every rank's fp32 gradient buffer with
+//      plain peer loads (or one multimem.ld_reduce through the NVSwitch when a multicast
+//      alias is given), keeps the reduced slice locally and accumulates sum(g^2)
+//   exchange of the W partial sums of squares through the control blocks (same summation
+//      order on every rank, so every rank applies the same clip coefficient)
+//   B: clip -> Adam -> decoupled weight decay -> lr on the local fp32 master shard, then
+//      all-gather - the updated bf16 values are pushed straight into every rank's compute
+//      buffer (peer stores, or one multimem.st)
+//   flag barrier (every rank's pushes have landed; nobody reads gradients any more)
+//
+// Every cross-rank wait is bounded; on expiry the kernel records kWaitFlagTimeout, skips
+// the remaining work, still passes every grid-wide sync and returns normally.
+//
+// The optimizer math is the chain of jax_gpt/trainer/optimizer.py:48-63; the reference
+// leaves gradient reduction to XLA (jax_gpt/trainer/train_step.py:63-67) and has no FSDP
+// (jax_gpt/trainer/sharding.py:58-69 declares the axis only).
+#include "comm_kernels.cuh"
+
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200 {
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_f32(float* p, float v) {
+  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc)
+               : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st_b128(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// Bounded wait until *flag >= expected (system scope). Returns false on expiry.
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int expected, uint64_t budget_ns) {
+  if (ld_acquire_sys(flag) >= expected) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if (ld_acquire_sys(flag) >= expected) return true;
+    if (globaltimer_ns() - t0 > budget_ns) return false;
+    __nanosleep(64);
+  }
+}
+
+// All-to-all flag barrier run by the first `world` threads of ONE block. Thread p tells rank p
+// "I reached `epoch` on `slot`" and waits for rank p to say the same. Returns false on expiry.
+__device__ bool flag_barrier(CommCtrl* const* peer_ctrl, int world, int rank, int slot, int epoch,
+                             uint64_t budget_ns, int* status) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int p = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(&peer_ctrl[p]->flags[slot][rank], epoch);
+    if (!wait_flag_ge(&peer_ctrl[rank]->flags[slot][p], epoch, budget_ns)) {
+      report_status(status, kWaitFlagTimeout, slot, p, epoch);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__device__ __forceinline__ float block_sum(float v) {
+  __shared__ float red[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float s = 0.f;
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  }
+  return s;  // valid in thread 0
+}
+
+__global__ void __launch_bounds__(512, 2) sharded_adamw_kernel(const __grid_constant__ ShardedAdamWArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  CommCtrl* my = a.peer_ctrl[a.rank];
+  const int epoch = my->epoch + 1;
+  const int W = a.world;
+  const int64_t S = a.n_total / W;  // shard length
+  const int64_t base = S * a.rank;
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) {
+      my->sq_local = 0.f;
+      my->abort_flag = 0;
+    }
+    if (!flag_barrier(a.peer_ctrl, W, a.rank, 0, epoch, a.wait_budget_ns, a.status) && threadIdx.x == 0)
+      my->abort_flag = 1;
+  }
+  __threadfence();
+  grid.sync();
+  bool alive = (*reinterpret_cast<volatile int*>(&my->abort_flag) == 0);
+
+  // ---- A: reduce-scatter of this rank's slice + partial sum of squares ----
+  float sq = 0.f;
+  if (alive) {
+    float* mine = a.peer_grad[a.rank] + base;
+    for (int64_t i = tid * 4; i < S; i += nthreads * 4) {
+      float4 acc;
+      if (a.mc_grad != nullptr) {
+        acc = multimem_ld_reduce_f32x4(a.mc_grad + base + i);
+      } else {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int p = 0; p < kCommMaxRanks; ++p) {
+          if (p < W) {
+            const int src = (a.rank + p) % W;  // start local, spread the peers across ranks
+            const float4 g = __ldcg(reinterpret_cast<const float4*>(a.peer_grad[src] + base + i));
+            acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+          }
+        }
+      }
+      *reinterpret_cast<float4*>(mine + i) = acc;
+      sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
+  }
+  sq = block_sum(sq);
+  if (threadIdx.x == 0 && alive) atomicAdd(&my->sq_local, sq);
+  __threadfence();
+  grid.sync();
+
+  // ---- exchange of the partial norms ----
+  if (blockIdx.x == 0) {
+    if (alive && threadIdx.x < W)
+      st_relaxed_sys_f32(&a.peer_ctrl[threadIdx.x]->norm_slots[a.rank], *reinterpret_cast<volatile float*>(&my->sq_local));
+    const bool ok = flag_barrier(a.peer_ctrl, W, a.rank, 1, epoch, a.wait_budget_ns, a.status);
+    if (threadIdx.x == 0) {
+      if (!ok) my->abort_flag = 1;
+      float tot = 0.f;
+      for (int p = 0; p < W; ++p) tot += *reinterpret_cast<volatile float*>(&my->norm_slots[p]);
+      my->sq_total = tot;
+    }
+  }
+  __threadfence();
+  grid.sync();
+  alive = (*reinterpret_cast<volatile int*>(&my->abort_flag) == 0);
+
+  // ---- B: AdamW on the shard, push bf16 parameters to every rank ----
+  if (alive) {
+    const float lr = a.hp[0], bc1 = a.hp[1], bc2 = a.hp[2], gscale = a.hp[3];
+    float coef = gscale;
+    if (a.clip > 0.f) {
+      const float norm = sqrtf(*reinterpret_cast<volatile float*>(&my->sq_total)) * gscale;
+      coef *= fminf(1.f, a.clip / (norm + 1e-6f));
+    }
+    const float* gsh = a.peer_grad[a.rank] + base;
+    for (int64_t i = tid * 8; i < S; i += nthreads * 8) {
+      float g[8], p[8], m[8], v[8];
+      *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(gsh + i);
+      *reinterpret_cast<float4*>(g + 4) = *reinterpret_cast<const float4*>(gsh + i + 4);
+      *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(a.master + i);
+      *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(a.master + i + 4);
+      *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(a.m + i);
+      *reinterpret_cast<float4*>(m + 4) = *reinterpret_cast<const float4*>(a.m + i + 4);
+      *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(a.v + i);
+      *reinterpret_cast<float4*>(v + 4) = *reinterpret_cast<const float4*>(a.v + i + 4);
+      const float wd = (base + i < a.n_decay) ? a.wd : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gi = g[j] * coef;
+        m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gi;
+        v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gi * gi;
+        const float u = (m[j] / bc1) / (sqrtf(v[j] / bc2) + a.eps) + wd * p[j];
+        p[j] -= lr * u;
+      }
+      *reinterpret_cast<float4*>(a.master + i) = *reinterpret_cast<float4*>(p);
+      *reinterpret_cast<float4*>(a.master + i + 4) = *reinterpret_cast<float4*>(p + 4);
+      *reinterpret_cast<float4*>(a.m + i) = *reinterpret_cast<float4*>(m);
+      *reinterpret_cast<float4*>(a.m + i + 4) = *reinterpret_cast<float4*>(m + 4);
+      *reinterpret_cast<float4*>(a.v + i) = *reinterpret_cast<float4*>(v);
+      *reinterpret_cast<float4*>(a.v + i + 4) = *reinterpret_cast<float4*>(v + 4);
+      const uint4 pk = make_uint4(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]), pack_bf16x2(p[4], p[5]),
+                                  pack_bf16x2(p[6], p[7]));
+      if (a.mc_param != nullptr) {
+        multimem_st_b128(a.mc_param + base + i, pk);
+      } else {
+#pragma unroll
+        for (int q = 0; q < kCommMaxRanks; ++q) {
+          if (q < W) {
+            const int dst = (a.rank + q) % W;
+            *reinterpret_cast<uint4*>(a.peer_param[dst] + base + i) = pk;
+          }
+        }
+      }
+    }
+  }
+  __threadfence_system();
+  grid.sync();
+  if (blockIdx.x == 0) {
+    flag_barrier(a.peer_ctrl, W, a.rank, 2, epoch, a.wait_budget_ns, a.status);
+    if (threadIdx.x == 0) my->epoch = epoch;
+  }
+}
+
+__global__ void comm_barrier_kernel(CommCtrl* const* peer_ctrl_dev, int world, int rank, uint64_t budget_ns,
+                                    int* status) {
+  __shared__ CommCtrl* peers[kCommMaxRanks];
+  if (threadIdx.x < world) peers[threadIdx.x] = peer_ctrl_dev[threadIdx.x];
+  __syncthreads();
+  CommCtrl* my = peers[rank];
+  const int epoch = my->bar_epoch + 1;
+  flag_barrier(peers, world, rank, 3, epoch, budget_ns, status);
+  if (threadIdx.x == 0) my->bar_epoch = epoch;
+}
+
+__global__ void wait_flag_kernel(const int* flag, int expected, uint64_t budget_ns, int* status) {
+  if (threadIdx.x == 0 && !wait_flag_ge(flag, expected, budget_ns))
+    report_status(status, kWaitFlagTimeout, 99, expected, 0);
+}
+
+}  // namespace
+
+cudaError_t launch_sharded_adamw(const ShardedAdamWArgs& args, cudaStream_t stream) {
+  if (args.world < 1 || args.world > kCommMaxRanks || args.n_total % (static_cast<int64_t>(args.world) * 8) != 0)
+    return cudaErrorInvalidValue;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int per_sm = 0;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sharded_adamw_kernel, 512, 0);
+  if (e != cudaSuccess) return e;
+  if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+  const int grid = sms * (per_sm > 2 ? 2 : per_sm);
+  ShardedAdamWArgs a = args;
+  void* params[] = {&a};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(sharded_adamw_kernel), dim3(grid), dim3(512), params, 0,
+                                     stream);
+}
+
+cudaError_t launch_comm_barrier(CommCtrl* const* peer_ctrl_dev, int world, int rank, uint64_t wait_budget_ns,
+                                int* status, cudaStream_t stream) {
+  comm_barrier_kernel<<<1, 32, 0, stream>>>(peer_ctrl_dev, world, rank, wait_budget_ns, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_flag(const int* flag, int expected, uint64_t budget_ns, int* status, cudaStream_t stream) {
+  wait_flag_kernel<<<1, 32, 0, stream>>>(flag, expected, budget_ns, status);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -17,6 +17,17 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver call and needs a current context on the calling thread.
+// Threads that have only used the runtime lazily (e.g. an autograd worker) may not have one
+// yet; a no-op runtime call binds the primary context.
+void ensure_context() {
+  thread_local bool ready = false;
+  if (!ready) {
+    cudaFree(nullptr);
+    ready = true;
+  }
+}
+
 CUtensorMapDataType dtype_for(int elem_bytes) {
   return elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                          : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
@@ -28,6 +39,7 @@ cudaError_t encode_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, ui
                           uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
   auto fn = get_encode();
   if (fn == nullptr) return cudaErrorNotSupported;
+  ensure_context();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_stride_bytes & 15) != 0) return cudaErrorMisalignedAddress;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};
@@ -44,6 +56,7 @@ cudaError_t encode_tma_3d(CUtensorMap* map, const void* base, int elem_bytes, ui
                           uint32_t box_mid, uint32_t box_outer) {
   auto fn = get_encode();
   if (fn == nullptr) return cudaErrorNotSupported;
+  ensure_context();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (mid_stride_bytes & 15) != 0 || (outer_stride_bytes & 15) != 0)
     return cudaErrorMisalignedAddress;
   cuuint64_t dims[3] = {inner, mid, outer};
