@@ -168,16 +168,20 @@ void norm_fwd(int64_t mode, const Tensor& x, const Tensor& gamma, const c10::opt
 
 void norm_bwd(int64_t mode, const Tensor& dy, const Tensor& x, const Tensor& gamma, const c10::optional<Tensor>& mean,
               const Tensor& rstd, const c10::optional<Tensor>& dres, Tensor dx, Tensor dgamma,
-              c10::optional<Tensor> dbeta) {
+              c10::optional<Tensor> dbeta, Tensor scratch) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous(), "norm_bwd: contiguous tensors");
   TORCH_CHECK(dgamma.scalar_type() == at::kFloat, "norm_bwd: dgamma must be fp32");
   const int D = static_cast<int>(x.size(-1));
+  TORCH_CHECK(scratch.scalar_type() == at::kFloat && scratch.is_contiguous() &&
+                  scratch.numel() >= b200::norm_bwd_scratch_floats(D),
+              "norm_bwd: scratch must hold ", b200::norm_bwd_scratch_floats(D), " floats");
   const int M = static_cast<int>(x.numel() / D);
   B200_CHECK_CUDA(b200::launch_norm_bwd(static_cast<int>(mode), bf16_ptr(dy), bf16_ptr(x), bf16_ptr(gamma),
                                         mean.has_value() ? mean->data_ptr<float>() : nullptr, rstd.data_ptr<float>(),
                                         bf16_opt(dres), bf16_mut(dx), dgamma.data_ptr<float>(),
-                                        dbeta.has_value() ? dbeta->data_ptr<float>() : nullptr, M, D, cur_stream()));
+                                        dbeta.has_value() ? dbeta->data_ptr<float>() : nullptr,
+                                        scratch.data_ptr<float>(), M, D, cur_stream()));
 }
 
 void embed_fwd(const Tensor& idx, const Tensor& wte, const c10::optional<Tensor>& wpe, Tensor out, int64_t T,
@@ -305,7 +309,7 @@ TORCH_LIBRARY(b200, m) {
       &norm_fwd);
   m.def(
       "norm_bwd(int mode, Tensor dy, Tensor x, Tensor gamma, Tensor? mean, Tensor rstd, Tensor? dres, Tensor(a!) dx, "
-      "Tensor(b!) dgamma, Tensor(c!)? dbeta) -> ()",
+      "Tensor(b!) dgamma, Tensor(c!)? dbeta, Tensor(d!) scratch) -> ()",
       &norm_bwd);
   m.def("embed_fwd(Tensor idx, Tensor wte, Tensor? wpe, Tensor(a!) out, int T, int pos0) -> ()", &embed_fwd);
   m.def("embed_bwd(Tensor idx, Tensor dout, Tensor(a!) dwte, Tensor(b!)? dwpe, int T, int pos0) -> ()", &embed_bwd);
@@ -326,5 +330,6 @@ TORCH_LIBRARY(b200, m) {
       "dq_accum, Tensor(c!) dk, Tensor(d!) dv, int B, int T, int H, int Hkv, int D, float scale, bool causal) -> ()",
       &attn_bwd);
   m.def("cast_rows(Tensor src, Tensor(a!) dst) -> ()", &cast_rows);
+  m.def("norm_bwd_scratch_floats(int D) -> int", [](int64_t D) { return b200::norm_bwd_scratch_floats(static_cast<int>(D)); });
   b200_register_extra(m);
 }

@@ -134,8 +134,7 @@ template <int NV, int WPR, int MODE>
 __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
-                                __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                int M, int D) {
+                                __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int M, int D) {
   constexpr int ROWS = 4 / WPR > 0 ? 4 / WPR : 1;
   __shared__ float scratch[ROWS * WPR + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -199,16 +198,43 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
       }
     }
   }
+  // One partial row per (block, row slot): plain stores, reduced by norm_bwd_reduce_kernel.
+  float* part = partials + static_cast<int64_t>(blockIdx.x * ROWS + row_in_block) * 2 * D;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int col = (i * WPR * 32 + warp_in_row * 32 + lane) * 8;
     if (col < D) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(dgamma + col + j, dg_acc[i][j]);
-        if (MODE == 0 && dbeta != nullptr) atomicAdd(dbeta + col + j, db_acc[i][j]);
+      *reinterpret_cast<float4*>(part + col) = make_float4(dg_acc[i][0], dg_acc[i][1], dg_acc[i][2], dg_acc[i][3]);
+      *reinterpret_cast<float4*>(part + col + 4) = make_float4(dg_acc[i][4], dg_acc[i][5], dg_acc[i][6], dg_acc[i][7]);
+      if (MODE == 0) {
+        *reinterpret_cast<float4*>(part + D + col) = make_float4(db_acc[i][0], db_acc[i][1], db_acc[i][2], db_acc[i][3]);
+        *reinterpret_cast<float4*>(part + D + col + 4) =
+            make_float4(db_acc[i][4], db_acc[i][5], db_acc[i][6], db_acc[i][7]);
       }
     }
+  }
+}
+
+// dgamma[c] += sum_r partials[r][0][c]; dbeta[c] += sum_r partials[r][1][c]. Block (32, 32):
+// threadIdx.x walks columns (coalesced), threadIdx.y strides over the partial rows.
+__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partials, int n_rows, int D, int with_beta,
+                                       float* __restrict__ dgamma, float* __restrict__ dbeta) {
+  __shared__ float red[32][33];
+  const int width = with_beta ? 2 * D : D;
+  const int c = blockIdx.x * 32 + threadIdx.x;  // column in the concatenated [dgamma | dbeta] row
+  float s = 0.f;
+  if (c < width) {
+    const int off = (c < D) ? c : (D + (c - D));
+    for (int r = threadIdx.y; r < n_rows; r += 32) s += partials[static_cast<int64_t>(r) * 2 * D + off];
+  }
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < width) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) t += red[k][threadIdx.x];
+    if (c < D) dgamma[c] += t;
+    else if (dbeta != nullptr) dbeta[c - D] += t;
   }
 }
 
@@ -236,15 +262,20 @@ cudaError_t norm_fwd_dispatch(const __nv_bfloat16* x, const __nv_bfloat16* g, co
 template <int MODE>
 cudaError_t norm_bwd_dispatch(const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* g,
                               const float* mean, const float* rstd, const __nv_bfloat16* dres, __nv_bfloat16* dx,
-                              float* dgamma, float* dbeta, int M, int D, cudaStream_t st) {
+                              float* dgamma, float* dbeta, float* partials, int M, int D, cudaStream_t st) {
   if (D % 8 != 0 || D > 8192) return cudaErrorInvalidValue;
 #define LAUNCH(NV, WPR)                                                                                    \
   {                                                                                                        \
     constexpr int ROWS = 4 / WPR > 0 ? 4 / WPR : 1;                                                        \
     int groups = (M + ROWS - 1) / ROWS;                                                                    \
-    int grid = groups < 148 * 8 ? groups : 148 * 8;                                                        \
+    int grid = groups < kNormBwdMaxBlocks ? groups : kNormBwdMaxBlocks;                                    \
     norm_bwd_kernel<NV, WPR, MODE><<<grid, ROWS * WPR * 32, 0, st>>>(dy, x, g, mean, rstd, dres, dx,       \
-                                                                    dgamma, dbeta, M, D);                  \
+                                                                    partials, M, D);                       \
+    cudaError_t e_ = cudaGetLastError();                                                                   \
+    if (e_ != cudaSuccess) return e_;                                                                      \
+    const int width_ = (MODE == 0) ? 2 * D : D;                                                            \
+    norm_bwd_reduce_kernel<<<(width_ + 31) / 32, dim3(32, 32), 0, st>>>(partials, grid * ROWS, D,          \
+                                                                       MODE == 0 ? 1 : 0, dgamma, dbeta); \
     return cudaGetLastError();                                                                             \
   }
   if (D <= 256) LAUNCH(1, 1)
@@ -435,16 +466,38 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ g, float
     const float norm = sqrtf(*gnorm_sq) * gscale;
     coef *= fminf(1.f, clip / (norm + 1e-6f));
   }
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const float gi = g[i] * coef;
-    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
-    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
-    m[i] = mi;
-    v[i] = vi;
-    float pi = p[i];
+  auto update = [&](float gi, float& mi, float& vi, float& pi) {
+    gi *= coef;
+    mi = beta1 * mi + (1.f - beta1) * gi;
+    vi = beta2 * vi + (1.f - beta2) * gi * gi;
     const float u = (mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * pi;
     pi -= lr * u;
+  };
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nth = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
+                   (p_bf16 == nullptr || (reinterpret_cast<uintptr_t>(p_bf16) & 7) == 0);
+  const int64_t n4 = vec ? n / 4 : 0;
+  for (int64_t i = tid; i < n4; i += nth) {
+    float4 gv = reinterpret_cast<float4*>(g)[i], mv = reinterpret_cast<float4*>(m)[i],
+           vv = reinterpret_cast<float4*>(v)[i], pv = reinterpret_cast<float4*>(p)[i];
+    update(gv.x, mv.x, vv.x, pv.x);
+    update(gv.y, mv.y, vv.y, pv.y);
+    update(gv.z, mv.z, vv.z, pv.z);
+    update(gv.w, mv.w, vv.w, pv.w);
+    reinterpret_cast<float4*>(m)[i] = mv;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    reinterpret_cast<float4*>(p)[i] = pv;
+    if (p_bf16 != nullptr)
+      reinterpret_cast<uint2*>(p_bf16)[i] = make_uint2(pack_bf16x2(pv.x, pv.y), pack_bf16x2(pv.z, pv.w));
+    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int64_t i = n4 * 4 + tid; i < n; i += nth) {
+    float mi = m[i], vi = v[i], pi = p[i];
+    update(g[i], mi, vi, pi);
+    m[i] = mi;
+    v[i] = vi;
     p[i] = pi;
     if (p_bf16 != nullptr) p_bf16[i] = __float2bfloat16(pi);
     if (zero_grad) g[i] = 0.f;
@@ -469,11 +522,11 @@ cudaError_t launch_norm_fwd(int mode, const __nv_bfloat16* x, const __nv_bfloat1
 
 cudaError_t launch_norm_bwd(int mode, const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* gamma,
                             const float* mean, const float* rstd, const __nv_bfloat16* dres, __nv_bfloat16* dx,
-                            float* dgamma, float* dbeta, int M, int D, cudaStream_t st) {
+                            float* dgamma, float* dbeta, float* partials, int M, int D, cudaStream_t st) {
   if (M <= 0) return cudaSuccess;
-  if (mode == 0) return norm_bwd_dispatch<0>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, M, D, st);
-  if (mode == 1) return norm_bwd_dispatch<1>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, M, D, st);
-  return norm_bwd_dispatch<2>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, M, D, st);
+  if (mode == 0) return norm_bwd_dispatch<0>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partials, M, D, st);
+  if (mode == 1) return norm_bwd_dispatch<1>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partials, M, D, st);
+  return norm_bwd_dispatch<2>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partials, M, D, st);
 }
 
 cudaError_t launch_embed_fwd(const int32_t* idx, const __nv_bfloat16* wte, const __nv_bfloat16* wpe,

@@ -9,10 +9,13 @@ namespace b200 {
 // mode 0: LayerNorm(gamma, beta); 1: RMSNorm * w; 2: RMSNorm * (1 + w). D % 8 == 0, D <= 8192.
 cudaError_t launch_norm_fwd(int mode, const __nv_bfloat16* x, const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
                             __nv_bfloat16* y, float* mean, float* rstd, int M, int D, float eps, cudaStream_t st);
-// dx = norm_bwd(dy) (+ dres); dgamma/dbeta are ACCUMULATED (fp32 atomics).
+// dx = norm_bwd(dy) (+ dres); dgamma/dbeta are ACCUMULATED. `partials` is scratch of
+// norm_bwd_scratch_floats(D) floats: per-block partial sums, reduced by a second kernel.
+constexpr int kNormBwdMaxBlocks = 296;
+inline int64_t norm_bwd_scratch_floats(int D) { return static_cast<int64_t>(kNormBwdMaxBlocks) * 4 * 2 * D; }
 cudaError_t launch_norm_bwd(int mode, const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* gamma,
                             const float* mean, const float* rstd, const __nv_bfloat16* dres, __nv_bfloat16* dx,
-                            float* dgamma, float* dbeta, int M, int D, cudaStream_t st);
+                            float* dgamma, float* dbeta, float* partials, int M, int D, cudaStream_t st);
 cudaError_t launch_embed_fwd(const int32_t* idx, const __nv_bfloat16* wte, const __nv_bfloat16* wpe,
                              __nv_bfloat16* out, int n_tok, int T, int D, int pos0, cudaStream_t st);
 cudaError_t launch_embed_bwd(const int32_t* idx, const __nv_bfloat16* dout, float* dwte, float* dwpe, int n_tok,

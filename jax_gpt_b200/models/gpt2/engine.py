@@ -47,7 +47,7 @@ class FlatParams:
     """Flat master / compute / gradient / moment buffers with named views."""
 
     def __init__(self, cfg: GPTConfig, device, seed: int = 0, init: Optional[Dict[str, torch.Tensor]] = None,
-                 shard: Optional[tuple] = None):
+                 alloc_grad=None, alloc_compute=None):
         shapes = param_shapes(cfg)
         self.names = PARAM_ORDER_DECAY + PARAM_ORDER_NO_DECAY
         self.offsets = {}
@@ -62,8 +62,11 @@ class FlatParams:
         # the flat size is padded so that it splits evenly across up to 8 ranks in 16-byte units
         self.total = (self.total + 511) // 512 * 512
         self.master = torch.zeros(self.total, device=device, dtype=torch.float32)
-        self.compute = torch.zeros(self.total, device=device, dtype=torch.bfloat16)
-        self.grad = torch.zeros(self.total, device=device, dtype=torch.float32)
+        # gradient and compute buffers may come from a peer-visible (symmetric) allocator
+        self.compute = (alloc_compute(self.total) if alloc_compute is not None
+                        else torch.zeros(self.total, device=device, dtype=torch.bfloat16))
+        self.grad = (alloc_grad(self.total) if alloc_grad is not None
+                     else torch.zeros(self.total, device=device, dtype=torch.float32))
         src = init if init is not None else init_params(cfg, seed, "cpu", torch.float32)
         for n in self.names:
             o, numel, shape = self.offsets[n]
@@ -93,11 +96,19 @@ class GPT2TrainEngine:
         _ext.load()
         self.hyper = dict(lr=lr, min_lr=min_lr, warmup=warmup_steps, decay=lr_decay_steps, wd=weight_decay,
                           b1=beta1, b2=beta2, clip=grad_clip)
-        self.flat = FlatParams(cfg, self.device, seed, init)
-        self.m = torch.zeros_like(self.flat.master)
-        self.v = torch.zeros_like(self.flat.master)
-        self.step_count = 0
         self.dist_optimizer = dist_optimizer
+        self.dp_world = 1
+        if dist_optimizer is not None:
+            self.flat = FlatParams(cfg, self.device, seed, init, getattr(dist_optimizer, "alloc_grad", None),
+                                   getattr(dist_optimizer, "alloc_compute", None))
+            dist_optimizer.attach(self)
+            self.dp_world = dist_optimizer.world
+            self.m = self.v = None  # moments live in the optimizer's shards
+        else:
+            self.flat = FlatParams(cfg, self.device, seed, init)
+            self.m = torch.zeros_like(self.flat.master)
+            self.v = torch.zeros_like(self.flat.master)
+        self.step_count = 0
         self.p = self.flat.tree(self.flat.compute)   # bf16 compute views
         self.g = self.flat.tree(self.flat.grad)      # fp32 gradient views
         self._alloc()
@@ -258,7 +269,7 @@ class GPT2TrainEngine:
         self._hp_host[0] = lr
         self._hp_host[1] = 1.0 - h["b1"] ** t
         self._hp_host[2] = 1.0 - h["b2"] ** t
-        self._hp_host[3] = 1.0 / n_micro
+        self._hp_host[3] = 1.0 / (n_micro * self.dp_world)
         self.hp.copy_(self._hp_host, non_blocking=True)
         return lr
 
@@ -287,11 +298,13 @@ class GPT2TrainEngine:
             return
         self._side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self._side):
-            saved = (self.flat.master.clone(), self.m.clone(), self.v.clone())
             self._fwd_bwd()
-            self.optimizer_step()
-            self.flat.master.copy_(saved[0]); self.m.copy_(saved[1]); self.v.copy_(saved[2])
-            self.flat.compute.copy_(self.flat.master)
+            if self.dist_optimizer is None:
+                # single GPU: also exercise the optimizer kernels, then restore the state
+                saved = (self.flat.master.clone(), self.m.clone(), self.v.clone())
+                self.optimizer_step()
+                self.flat.master.copy_(saved[0]); self.m.copy_(saved[1]); self.v.copy_(saved[2])
+                self.flat.compute.copy_(self.flat.master)
             self.flat.grad.zero_()
             self.loss_sum.zero_()
         torch.cuda.current_stream().wait_stream(self._side)
@@ -318,7 +331,8 @@ class GPT2TrainEngine:
         self.last_loss.copy_(self.loss_sum)
         self.last_loss.mul_(1.0 / n)
         self.loss_sum.zero_()
-        return {"loss": self.last_loss, "grad_norm_sq": self.gnorm_sq, "lr": lr, "grad_scale": 1.0 / n}
+        gsq = self.gnorm_sq if self.dist_optimizer is None else self.dist_optimizer.grad_norm_sq()
+        return {"loss": self.last_loss, "grad_norm_sq": gsq, "lr": lr, "grad_scale": 1.0 / (n * self.dp_world)}
 
     def train_step(self, tokens: Optional[torch.Tensor] = None, targets: Optional[torch.Tensor] = None):
         """One optimizer step on one micro-batch. ``tokens``/``targets`` [B,T] int32 (device or
@@ -339,6 +353,9 @@ class GPT2TrainEngine:
         return self.flat.tree(self.flat.master)
 
     def opt_state(self) -> Dict[str, Dict[str, torch.Tensor]]:
+        if self.m is None:  # sharded optimizer: moments are exposed as the flat local shards
+            d = self.dist_optimizer
+            return {"count": self.step_count, "mu": {"__shard__": d.m}, "nu": {"__shard__": d.v}}
         return {"count": self.step_count, "mu": self.flat.tree(self.m), "nu": self.flat.tree(self.v)}
 
     def load(self, params: Dict[str, torch.Tensor], opt_state=None, step: Optional[int] = None):

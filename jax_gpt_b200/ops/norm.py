@@ -40,11 +40,28 @@ def norm_fwd(mode, x, gamma, beta, eps, y=None, mean=None, rstd=None):
     return y, mean, rstd
 
 
-def norm_bwd(mode, dy, x, gamma, mean, rstd, dgamma, dbeta, dres=None, dx=None):
-    """Raw CUDA backward; ACCUMULATES into fp32 ``dgamma`` / ``dbeta``; adds ``dres`` to dx."""
+_SCRATCH = {}
+
+
+def bwd_scratch(device, D: int) -> torch.Tensor:
+    """Per-device scratch for the partial dgamma/dbeta sums of the backward kernel."""
+    n = 296 * 4 * 2 * D
+    key = (torch.device(device).index, n)
+    t = _SCRATCH.get(key)
+    if t is None:
+        t = torch.empty(n, device=device, dtype=torch.float32)
+        _SCRATCH[key] = t
+    return t
+
+
+def norm_bwd(mode, dy, x, gamma, mean, rstd, dgamma, dbeta, dres=None, dx=None, scratch=None):
+    """Raw CUDA backward; ACCUMULATES into fp32 ``dgamma`` / ``dbeta``; adds ``dres`` to dx.
+    ``scratch`` (see :func:`bwd_scratch`) holds per-block partial sums between the two kernels."""
     if dx is None:
         dx = torch.empty_like(x)
-    _ext.ops().norm_bwd(mode, dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta)
+    if scratch is None:
+        scratch = bwd_scratch(x.device, x.shape[-1])
+    _ext.ops().norm_bwd(mode, dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch)
     return dx
 
 

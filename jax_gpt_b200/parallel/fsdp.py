@@ -1,0 +1,145 @@
+"""Sharded optimizer (ZeRO / FSDP style) fused with its collectives.
+
+``FusedShardedAdamW`` replaces "reduce-scatter gradients (NCCL) -> AdamW on the shard ->
+all-gather parameters (NCCL)" by ONE kernel per rank that reads every peer's gradient slice
+over NVLink, clips, updates its fp32 master shard and pushes the new bf16 values into every
+peer's compute buffer (csrc/comm_kernels.cu). ``NcclShardedAdamW`` is the library baseline
+with the same math. ``sharded_adamw_reference`` restates the protocol with ordinary
+collectives so the host-side sharding logic is testable on CPU (gloo) ranks.
+
+The reference only declares an ``fsdp`` mesh axis (jax_gpt/trainer/sharding.py:58-69); its
+optimizer chain is jax_gpt/trainer/optimizer.py:48-63.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _ext
+from ..comm.symm import Communicator, shard_range
+from ..ops import misc
+
+
+def sharded_adamw_reference(group, grad: torch.Tensor, master_shard: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
+                            compute: torch.Tensor, hp, n_decay: int, beta1, beta2, eps, wd, clip):
+    """Same result as the fused kernel using reduce_scatter / all_reduce / all_gather.
+    ``grad`` is the full local fp32 gradient, ``compute`` the full compute-dtype parameter copy."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    n = grad.numel()
+    lo, hi = shard_range(n, world, rank)
+    red = torch.empty(hi - lo, dtype=grad.dtype, device=grad.device)
+    if grad.is_cuda:
+        dist.reduce_scatter_tensor(red, grad, group=group)
+    else:  # gloo has no reduce_scatter: all-reduce a copy and slice
+        full = grad.clone()
+        dist.all_reduce(full, group=group)
+        red.copy_(full[lo:hi])
+    sq = (red.double() ** 2).sum().float().reshape(1)
+    dist.all_reduce(sq, group=group)
+    lr, bc1, bc2, gscale = [float(x) for x in hp]
+    coef = gscale
+    if clip > 0:
+        coef *= min(1.0, clip / (float(sq) ** 0.5 * gscale + 1e-6))
+    gi = red * coef
+    m.mul_(beta1).add_(gi, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(gi, gi, value=1 - beta2)
+    idx = torch.arange(lo, hi, device=grad.device)
+    wdv = torch.where(idx < n_decay, torch.tensor(wd, device=grad.device), torch.tensor(0.0, device=grad.device))
+    u = (m / bc1) / ((v / bc2).sqrt() + eps) + wdv * master_shard
+    master_shard.sub_(lr * u)
+    pieces = [torch.empty(hi - lo, dtype=compute.dtype, device=compute.device) for _ in range(world)]
+    dist.all_gather(pieces, master_shard.to(compute.dtype), group=group)
+    compute.copy_(torch.cat(pieces))
+    return sq
+
+
+class _ShardedBase:
+    """Owns this rank's fp32 master / moment shards of an engine's flat parameter vector."""
+
+    def __init__(self, group=None, device=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = device
+        self.master = self.m = self.v = None
+
+    def _make_shards(self, engine):
+        n = engine.flat.total
+        assert n % (self.world * 8) == 0
+        lo, hi = shard_range(n, self.world, self.rank)
+        self.lo, self.hi = lo, hi
+        self.master = engine.flat.master[lo:hi].clone()
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+
+    def gather_master(self, engine):
+        """Refreshes the engine's full fp32 master copy from the shards (checkpointing path)."""
+        dist.all_gather_into_tensor(engine.flat.master, self.master, group=self.group)
+
+
+class FusedShardedAdamW(_ShardedBase):
+    """One-kernel reduce-scatter + AdamW + all-gather over NVLink peer memory."""
+
+    def __init__(self, group=None, device=None, use_multimem: bool = False, wait_seconds: float = 20.0):
+        super().__init__(group, device)
+        self.comm = Communicator(self.group, device, wait_seconds)
+        self.use_multimem = use_multimem
+        self.grad_buf = self.param_buf = None
+
+    # allocation hook used by the engine so that gradients and bf16 weights are peer-visible
+    def alloc_grad(self, numel: int):
+        self.grad_buf = self.comm.alloc(numel, torch.float32)
+        return self.grad_buf.tensor
+
+    def alloc_compute(self, numel: int):
+        self.param_buf = self.comm.alloc(numel, torch.bfloat16)
+        return self.param_buf.tensor
+
+    def attach(self, engine):
+        self._make_shards(engine)
+        self.n_total, self.n_decay = engine.flat.total, engine.flat.n_decay
+
+    def step(self, engine):
+        h = engine.hyper
+        mc_g = self.grad_buf.multicast_ptr if self.use_multimem else 0
+        mc_p = self.param_buf.multicast_ptr if self.use_multimem else 0
+        _ext.ops().sharded_adamw(self.world, self.rank, self.n_total, self.n_decay, self.grad_buf.peer_ptrs,
+                                 self.param_buf.peer_ptrs, self.comm.ctrl.peer_ptrs, mc_g, mc_p, self.master, self.m,
+                                 self.v, engine.hp, h["b1"], h["b2"], 1e-8, h["wd"], h["clip"], self.comm.wait_seconds)
+        engine.flat.grad.zero_()
+
+    def grad_norm_sq(self) -> torch.Tensor:
+        """Device scalar: global sum of squared gradients of the last step (before scaling)."""
+        # CommCtrl layout: flags 8*8 int32, norm_slots 8 fp32, epoch, bar_epoch, sq_local, sq_total
+        return self.comm.ctrl.tensor.view(torch.float32)[8 * 8 + 8 + 3:8 * 8 + 8 + 4]
+
+
+class NcclShardedAdamW(_ShardedBase):
+    """Baseline: NCCL reduce-scatter, the fused single-GPU AdamW kernel on the shard, NCCL all-gather."""
+
+    def attach(self, engine):
+        self._make_shards(engine)
+        self.n_total, self.n_decay = engine.flat.total, engine.flat.n_decay
+        self.red = torch.empty_like(self.master)
+        self.sq = torch.zeros(1, device=self.master.device)
+        self.shard_bf16 = torch.empty(self.master.numel(), device=self.master.device, dtype=torch.bfloat16)
+
+    def step(self, engine):
+        h = engine.hyper
+        dist.reduce_scatter_tensor(self.red, engine.flat.grad, group=self.group)
+        self.sq.zero_()
+        misc.sumsq(self.red, self.sq)
+        dist.all_reduce(self.sq, group=self.group)
+        nd = min(max(self.n_decay - self.lo, 0), self.hi - self.lo)
+        for a, b, wd in ((0, nd, h["wd"]), (nd, self.hi - self.lo, 0.0)):
+            if b > a:
+                misc.adamw(self.master[a:b], self.red[a:b], self.m[a:b], self.v[a:b], engine.hp, self.sq,
+                           beta1=h["b1"], beta2=h["b2"], eps=1e-8, wd=wd, clip=h["clip"],
+                           p_bf16=self.shard_bf16[a:b], zero_grad=False)
+        dist.all_gather_into_tensor(engine.flat.compute, self.shard_bf16, group=self.group)
+        engine.flat.grad.zero_()
+
+    def grad_norm_sq(self):
+        return self.sq

@@ -1,0 +1,110 @@
+"""Worker run under torchrun by the multi-GPU tests (one process per GPU, NCCL)."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def small_cfg():
+    from jax_gpt_b200.models.gpt2 import GPTConfig
+    return GPTConfig(d_model=128, d_head=64, d_ff=512, d_context=256, n_head=2, n_kv_head=2, n_layers=2, vocab_size=1003)
+
+
+def batch(rank, step, cfg, device):
+    g = torch.Generator().manual_seed(1000 * step + rank)
+    tok = torch.randint(0, cfg.vocab_size, (2, 257), generator=g, dtype=torch.int32)
+    return tok[:, :-1].contiguous().to(device), tok[:, 1:].contiguous().to(device)
+
+
+def run_fsdp(rank, world, device, use_multimem):
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.gpt2.engine import GPT2TrainEngine
+    from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW, NcclShardedAdamW
+    cfg = small_cfg()
+    kw = dict(lr=1e-3, warmup_steps=0, lr_decay_steps=1000, use_cuda_graph=False, seed=5)
+    fused = GPT2TrainEngine(cfg, 2, 256, device=device,
+                            dist_optimizer=FusedShardedAdamW(device=device, use_multimem=use_multimem, wait_seconds=5.0), **kw)
+    nccl = GPT2TrainEngine(cfg, 2, 256, device=device, dist_optimizer=NcclShardedAdamW(device=device), **kw)
+    single = GPT2TrainEngine(cfg, 2, 256, device=device, **kw)
+    res = {}
+    for step in range(3):
+        x, y = batch(rank, step, cfg, device)
+        of = fused.train_step(x, y)
+        on = nccl.train_step(x, y)
+        for r in range(world):  # the single-GPU engine sees every rank's batch as a micro-batch
+            xs, ys = batch(r, step, cfg, device)
+            single.micro_step(xs, ys)
+        single.apply_gradients()
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        res[f"step{step}_fused_vs_nccl"] = rel(fused.flat.compute, nccl.flat.compute)
+        res[f"step{step}_fused_vs_single"] = rel(fused.flat.compute, single.flat.compute)
+        res[f"step{step}_gnorm_rel"] = abs(float(of["grad_norm_sq"]) - float(on["grad_norm_sq"])) / float(on["grad_norm_sq"])
+    # identical weights on every rank
+    mine = fused.flat.compute.float().sum().reshape(1).clone()
+    lst = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(lst, mine)
+    res["rank_checksum_spread"] = float(max(lst).item() - min(lst).item())
+    dist.barrier()
+    return res
+
+
+def run_tp(rank, world, device):
+    """all-gather -> GEMM and GEMM -> reduce-scatter against their unfused definitions."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.parallel.tensor_parallel import TPContext
+    torch.manual_seed(7)
+    ctx = TPContext(device=device, wait_seconds=5.0)
+    rows, K, N = 256, 512, 384
+    x_local = torch.randn(rows, K, device=device).to(torch.bfloat16) * (rank + 1)
+    w = (torch.randn(K, N, device=device, generator=torch.Generator(device=device).manual_seed(11)) * 0.05).to(torch.bfloat16)
+    y = ctx.all_gather_matmul(x_local, w)
+    parts = [torch.empty_like(x_local) for _ in range(world)]
+    dist.all_gather(parts, x_local)
+    ref = (torch.cat(parts).float() @ w.float())
+    res = {"ag_gemm": rel(y, ref)}
+    # row-parallel: each rank holds a K-slice; result rows are scattered
+    xr = torch.randn(rows * world, K, device=device, generator=torch.Generator(device=device).manual_seed(100 + rank)).to(torch.bfloat16)
+    z = ctx.matmul_reduce_scatter(xr, w)
+    full = xr.float() @ w.float()
+    dist.all_reduce(full)
+    res["gemm_rs"] = rel(z, full[rank * rows:(rank + 1) * rows])
+    torch.cuda.synchronize()
+    _ext.check_status(device)
+    dist.barrier()
+    return res
+
+
+def main():
+    what = sys.argv[1]
+    out_path = sys.argv[2]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    if what == "fsdp":
+        res = run_fsdp(rank, world, device, False)
+    elif what == "fsdp_multimem":
+        res = run_fsdp(rank, world, device, True)
+    elif what == "tp":
+        res = run_tp(rank, world, device)
+    else:
+        raise SystemExit(f"unknown test {what}")
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(res, f)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
