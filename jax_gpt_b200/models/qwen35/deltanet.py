@@ -1,0 +1,152 @@
+"""Gated DeltaNet (jax_gpt/models/qwen35/deltanet.py:26-443).
+
+Per head the layer maintains a state S (dk x dv) with the gated delta rule
+
+    S <- exp(g) S;   S <- S + k (beta (v - S^T k))^T;   o = S^T q
+
+where beta = sigmoid(b), g = -exp(A_log) softplus(a + dt_bias), q and k are L2-normalised
+(q scaled by dk^-1/2) after a causal depthwise conv (width 4) + SiLU over the concatenated
+q|k|v channels, and the output passes a gated RMSNorm ``w * rmsnorm(o) * silu(z)``.
+
+``deltanet_prefill`` evaluates the same recurrence chunk-parallel: inside a chunk the
+dependence of the corrected values on earlier tokens is a unit lower-triangular system, solved
+here with one triangular solve per chunk (the reference unrolls a forward substitution,
+jax_gpt/models/qwen35/deltanet.py:325-329); between chunks only S is carried, in fp32
+(the reference carries it in the activation dtype, jax_gpt/models/qwen35/deltanet.py:344-345).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .fp8 import matmul_maybe_fp8
+
+
+def _l2_norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def _gated_rms_norm(x: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    xf, zf = x.float(), z.float()
+    y = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps)
+    return (weight.float() * y * F.silu(zf)).to(x.dtype)
+
+
+def causal_conv1d_update(x_new: torch.Tensor, conv_state: torch.Tensor, weight: torch.Tensor):
+    """x_new (B, C), conv_state (B, C, K) of raw inputs, newest last. Returns (silu(conv), new_state)."""
+    state = torch.cat([conv_state[:, :, 1:], x_new[:, :, None].to(conv_state.dtype)], dim=-1)
+    y = (state.float() * weight.float()[None]).sum(-1)
+    return F.silu(y).to(x_new.dtype), state
+
+
+def causal_conv1d_prefill(x: torch.Tensor, weight: torch.Tensor):
+    """x (B, T, C); depthwise causal FIR of width K then SiLU. Final state = last K raw inputs."""
+    B, T, C = x.shape
+    K = weight.shape[-1]
+    xc = F.pad(x.transpose(1, 2).float(), (K - 1, 0))
+    y = F.conv1d(xc, weight.float()[:, None, :], groups=C)
+    state = xc[:, :, -K:] if T >= 1 else xc
+    return F.silu(y).transpose(1, 2).to(x.dtype), state.to(x.dtype)
+
+
+def _project(x, params, n_qk, n_v, dk, dv):
+    mixed = matmul_maybe_fp8(x, params["in_proj_qkv"])
+    z = matmul_maybe_fp8(x, params["in_proj_z"])
+    b = matmul_maybe_fp8(x, params["in_proj_b"])
+    a = matmul_maybe_fp8(x, params["in_proj_a"])
+    return mixed, z, b, a
+
+
+def _gates(b, a, params):
+    beta = torch.sigmoid(b.float())
+    g = -torch.exp(params["A_log"].float()) * F.softplus(a.float() + params["dt_bias"].float())
+    return beta, g
+
+
+def gated_delta_step(q, k, v, beta, g, state):
+    """One token. q,k (B,H,dk) already normalised; v (B,H,dv); beta,g (B,H); state (B,H,dk,dv) fp32."""
+    state = state * torch.exp(g)[..., None, None]
+    kv = torch.einsum("bhkv,bhk->bhv", state, k)
+    delta = (v - kv) * beta[..., None]
+    state = state + torch.einsum("bhk,bhv->bhkv", k, delta)
+    return torch.einsum("bhkv,bhk->bhv", state, q), state
+
+
+def deltanet_recurrent_step(x, params, state, conv_state, n_qk: int, n_v: int, dk: int, dv: int):
+    """Decode: x (B,1,D) -> (out (B,1,D), new_state (B,Hv,dk,dv), new_conv_state (B,conv_dim,K))."""
+    B = x.shape[0]
+    key_dim, rep = n_qk * dk, n_v // n_qk
+    mixed, z, b, a = _project(x, params, n_qk, n_v, dk, dv)
+    mixed, new_conv = causal_conv1d_update(mixed[:, 0], conv_state, params["conv_weight"])
+    q = mixed[:, :key_dim].reshape(B, n_qk, dk).float()
+    k = mixed[:, key_dim:2 * key_dim].reshape(B, n_qk, dk).float()
+    v = mixed[:, 2 * key_dim:].reshape(B, n_v, dv).float()
+    beta, g = _gates(b[:, 0], a[:, 0], params)
+    q = (_l2_norm(q) * dk ** -0.5).repeat_interleave(rep, dim=1)
+    k = _l2_norm(k).repeat_interleave(rep, dim=1)
+    o, new_state = gated_delta_step(q, k, v, beta, g, state.float())
+    o = _gated_rms_norm(o.reshape(B * n_v, dv), z[:, 0].reshape(B * n_v, dv), params["norm_weight"])
+    y = matmul_maybe_fp8(o.reshape(B, n_v * dv).to(x.dtype), params["out_proj"])
+    return y[:, None, :], new_state.to(state.dtype), new_conv
+
+
+def chunk_gated_delta_rule(q, k, v, beta, g, chunk_size: int, initial_state=None):
+    """Chunk-parallel gated delta rule in fp32.
+    q,k (B,H,T,dk) normalised; v (B,H,T,dv); beta,g (B,H,T). Returns (o (B,H,T,dv), final state)."""
+    B, H, T, dk = q.shape
+    dv = v.shape[-1]
+    C = chunk_size
+    pad = (-T) % C
+    if pad:
+        q, k, v = [F.pad(t, (0, 0, 0, pad)) for t in (q, k, v)]
+        beta, g = F.pad(beta, (0, pad)), F.pad(g, (0, pad))
+    N = (T + pad) // C
+    q, k, v = [t.reshape(B, H, N, C, -1) for t in (q, k, v)]
+    beta, g = beta.reshape(B, H, N, C), g.reshape(B, H, N, C)
+    G = g.cumsum(-1)                                              # cumulative log-decay inside the chunk
+    decay = torch.exp((G[..., :, None] - G[..., None, :]).tril())  # exp(G_i - G_j), j <= i
+    strict = torch.ones(C, C, device=q.device, dtype=torch.bool).tril(-1)
+    causal = torch.ones(C, C, device=q.device, dtype=torch.bool).tril(0)
+    kb = k * beta[..., None]
+    A = (kb @ k.transpose(-1, -2)) * decay
+    A = A.masked_fill(~strict, 0.0)
+    eye = torch.eye(C, device=q.device, dtype=q.dtype)
+    # (I + A) X = rhs  for the corrected values and the decayed keys
+    rhs = torch.cat([v * beta[..., None], kb * torch.exp(G)[..., None]], dim=-1)
+    sol = torch.linalg.solve_triangular(eye + A, rhs, upper=False, unitriangular=True)
+    v_eff, k_cum = sol[..., :dv], sol[..., dv:]
+    S = initial_state.float() if initial_state is not None else q.new_zeros(B, H, dk, dv)
+    outs = []
+    for n in range(N):
+        qn, kn = q[:, :, n], k[:, :, n]
+        Gn = G[:, :, n]
+        intra = (qn @ kn.transpose(-1, -2)) * decay[:, :, n]
+        intra = intra.masked_fill(~causal, 0.0)
+        v_new = v_eff[:, :, n] - k_cum[:, :, n] @ S
+        o = (qn * torch.exp(Gn)[..., None]) @ S + intra @ v_new
+        outs.append(o)
+        g_end = Gn[..., -1]
+        S = S * torch.exp(g_end)[..., None, None] + (kn * torch.exp(g_end[..., None] - Gn)[..., None]).transpose(-1, -2) @ v_new
+    o = torch.stack(outs, dim=2).reshape(B, H, N * C, dv)[:, :, :T]
+    return o, S
+
+
+def deltanet_prefill(x, params, n_qk: int, n_v: int, dk: int, dv: int, conv_kernel: int, chunk_size: int = 256,
+                     initial_state=None):
+    """Prefill: x (B,T,D) -> (out (B,T,D), final_state (B,Hv,dk,dv) fp32, final_conv_state (B,conv_dim,K))."""
+    B, T, _ = x.shape
+    key_dim, rep = n_qk * dk, n_v // n_qk
+    mixed, z, b, a = _project(x, params, n_qk, n_v, dk, dv)
+    mixed, conv_state = causal_conv1d_prefill(mixed, params["conv_weight"])
+    q = mixed[..., :key_dim].reshape(B, T, n_qk, dk).float()
+    k = mixed[..., key_dim:2 * key_dim].reshape(B, T, n_qk, dk).float()
+    v = mixed[..., 2 * key_dim:].reshape(B, T, n_v, dv).float()
+    beta, g = _gates(b, a, params)                                   # (B,T,Hv)
+    q = (_l2_norm(q) * dk ** -0.5).repeat_interleave(rep, dim=2)
+    k = _l2_norm(k).repeat_interleave(rep, dim=2)
+    o, S = chunk_gated_delta_rule(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), beta.transpose(1, 2),
+                                  g.transpose(1, 2), chunk_size, initial_state)
+    o = o.transpose(1, 2)                                            # (B,T,Hv,dv)
+    o = _gated_rms_norm(o.reshape(B * T * n_v, dv), z.reshape(B * T * n_v, dv), params["norm_weight"])
+    y = matmul_maybe_fp8(o.reshape(B, T, n_v * dv).to(x.dtype), params["out_proj"])
+    return y, S, conv_state

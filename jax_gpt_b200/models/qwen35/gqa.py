@@ -1,0 +1,41 @@
+"""Gated grouped-query attention (jax_gpt/models/qwen35/gqa.py:20-130): a 2x-wide q projection
+split per head into query and output gate, per-head RMSNorm(1+w) on q and k, partial half-split
+RoPE, causal softmax attention, ``out * sigmoid(gate)``, output projection. The cached path
+attends over the filled prefix only (the reference spans the whole zero-padded buffer and masks)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ...ops import attention as attn_ops
+from .fp8 import matmul_maybe_fp8
+from .primitives import apply_rotary_emb, rms_norm
+
+
+def gqa_attention(x, params, n_q_heads: int, n_kv_heads: int, head_dim: int, rope_freqs, rope_dim: int,
+                  cache_k: Optional[torch.Tensor] = None, cache_v: Optional[torch.Tensor] = None,
+                  cache_pos: Optional[int] = None):
+    """x (B,T,D) -> (out (B,T,D), new_k, new_v). Caches are (B, Hkv, max_len, dh), updated in place."""
+    B, T, _ = x.shape
+    qg = matmul_maybe_fp8(x, params["q_proj"]).reshape(B, T, n_q_heads, 2 * head_dim)
+    q, gate = qg[..., :head_dim], qg[..., head_dim:]
+    k = matmul_maybe_fp8(x, params["k_proj"]).reshape(B, T, n_kv_heads, head_dim)
+    v = matmul_maybe_fp8(x, params["v_proj"]).reshape(B, T, n_kv_heads, head_dim)
+    q = rms_norm(q.contiguous(), params["q_norm"])
+    k = rms_norm(k.contiguous(), params["k_norm"])
+    pos = int(cache_pos) if cache_pos is not None else 0
+    fr = rope_freqs[pos:pos + T]
+    q = apply_rotary_emb(q, fr, rope_dim)
+    k = apply_rotary_emb(k, fr, rope_dim)
+    if cache_k is not None:
+        cache_k[:, :, pos:pos + T] = k.permute(0, 2, 1, 3).to(cache_k.dtype)
+        cache_v[:, :, pos:pos + T] = v.permute(0, 2, 1, 3).to(cache_v.dtype)
+        kk = cache_k[:, :, :pos + T].permute(0, 2, 1, 3).to(q.dtype)
+        vv = cache_v[:, :, :pos + T].permute(0, 2, 1, 3).to(q.dtype)
+        out = attn_ops.attention_ref(q, kk, vv, causal=True, q_pos0=pos)
+    else:
+        out = attn_ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), causal=True)
+    out = out * torch.sigmoid(gate.float()).to(out.dtype)
+    y = matmul_maybe_fp8(out.reshape(B, T, n_q_heads * head_dim), params["o_proj"])
+    return y, cache_k, cache_v
