@@ -95,3 +95,14 @@ def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
     if supports_cuda_kernel(q, k):
         return _AttnFn.apply(q, k, v, causal, scale)
     return attention_ref(q, k, v, causal, scale)
+
+
+def mla_attention(q, k, v, scale: float):
+    """Causal attention with different q/k and v head widths (MLA prefill: 192 / 128).
+    q,k (B,T,H,dqk); v (B,T,H,dv)."""
+    B, T, H, dqk = q.shape
+    qf, kf, vf = [t.float().permute(0, 2, 1, 3) for t in (q, k, v)]
+    s = (qf @ kf.transpose(-1, -2)) * scale
+    mask = torch.ones(T, T, dtype=torch.bool, device=q.device).tril()
+    p = torch.softmax(s.masked_fill(~mask, float("-inf")), dim=-1)
+    return (p @ vf).permute(0, 2, 1, 3).to(q.dtype)
