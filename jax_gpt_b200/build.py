@@ -73,13 +73,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
     for p in ce.include_paths():
         inc += ["-isystem", p]
     inc += ["-isystem", os.path.join(_cuda_home(), "include"), "-isystem", sysconfig.get_paths()["include"]]
-    bsrc = os.path.join(CSRC, "bindings.cpp")
-    bobj = os.path.join(OBJ, "bindings.o")
-    objs.append(bobj)
     abi = int(getattr(torch._C, "_GLIBCXX_USE_CXX11_ABI", True))
-    if force or _stale(bsrc, bobj, hdr_m):
-        jobs.append(["g++", "-O2", "-std=c++17", "-fPIC", "-I", CSRC, *inc, f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
-                     "-DTORCH_EXTENSION_NAME=_C", "-c", bsrc, "-o", bobj])
+    for f in sorted(f for f in os.listdir(CSRC) if f.endswith(".cpp")):
+        bsrc = os.path.join(CSRC, f)
+        bobj = os.path.join(OBJ, f[:-4] + ".o")
+        objs.append(bobj)
+        if force or _stale(bsrc, bobj, hdr_m):
+            jobs.append(["g++", "-O2", "-std=c++17", "-fPIC", "-I", CSRC, *inc, f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+                         "-DTORCH_EXTENSION_NAME=_C", "-c", bsrc, "-o", bobj])
     if jobs:
         if verbose:
             print(f"[b200 build] compiling {len(jobs)} translation unit(s)", file=sys.stderr)
@@ -88,7 +89,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     if jobs or not os.path.exists(LIB):
         torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
         cmd = ["g++", "-shared", "-o", LIB, *objs, f"-L{torch_lib}", "-lc10", "-lc10_cuda", "-ltorch_cpu",
-               "-ltorch_cuda", "-ltorch", f"-L{os.path.join(_cuda_home(), 'lib64')}", "-lcudart",
+               "-ltorch_cuda", "-ltorch", f"-L{os.path.join(_cuda_home(), 'lib64')}", "-lcudart", "-lpthread",
                f"-Wl,-rpath,{torch_lib}"]
         _run(cmd)
         if verbose:

@@ -291,6 +291,8 @@ void cast_rows(const Tensor& src, Tensor dst) {
 
 #include "bindings_extra.inc"
 
+void b200_register_runtime(torch::Library& m);
+
 TORCH_LIBRARY(b200, m) {
   m.def("status(int device) -> Tensor", &status);
   m.def(
@@ -332,4 +334,5 @@ TORCH_LIBRARY(b200, m) {
   m.def("cast_rows(Tensor src, Tensor(a!) dst) -> ()", &cast_rows);
   m.def("norm_bwd_scratch_floats(int D) -> int", [](int64_t D) { return b200::norm_bwd_scratch_floats(static_cast<int>(D)); });
   b200_register_extra(m);
+  b200_register_runtime(m);
 }
