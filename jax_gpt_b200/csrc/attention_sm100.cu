@@ -27,7 +27,7 @@ namespace b200 {
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 softmax warps
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct FwdArgs {
@@ -47,13 +47,14 @@ struct FwdCfg {
   static constexpr int kStages = 2;
   static constexpr int kOffK = kTile;
   static constexpr int kOffP = kTile + kStages * 2 * kTile;
-  static constexpr int kOffBar = kOffP + kPBytes;
-  static constexpr int kSmem = kOffBar + 256;
+  static constexpr int kOffXchg = kOffP + kPBytes;  // bf16 [2][128] running-max exchange
+  static constexpr int kOffBar = kOffXchg + 512;
+  static constexpr int kSmem = kOffBar + 128;       // D = 64: 115328 B, two CTAs per SM
   static constexpr int kTmemCols = 256;
 };
 
 struct FwdBars {
-  uint64_t q_full, kv_full[2], kv_empty[2], s_full, p_ready, o_full;
+  uint64_t q_full, kv_full[2], kv_empty[2], s_full, p_ready, o_full, x_ready;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -103,8 +104,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_init(&bars->kv_empty[s], 1);
     }
     mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->p_ready, 256);
     mbar_init(&bars->o_full, 1);
+    mbar_init(&bars->x_ready, 256);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -180,14 +182,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       __syncwarp();
     }
   } else {
+    // Eight softmax warps: warps w and w+4 share a TMEM lane quarter (the same 32 query rows)
+    // and split the 128 score columns and the D output columns in halves. The two threads of a
+    // row agree on the running maximum through a bf16 value in shared memory (any common
+    // reference works for the online softmax as long as both use the same one).
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = q * 32 + lane;  // query row inside the block == TMEM lane
     const int qpos = q_blk * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    __nv_bfloat16* xchg = reinterpret_cast<__nv_bfloat16*>(smem + C::kOffXchg);  // [2][128]
+    constexpr int DH = D / 2;
     float m = -INFINITY, l = 0.f;
-    float o[D];
+    float o[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait(&bars->s_full, j & 1, abort_flag)) {
@@ -197,12 +206,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       tc_fence_after();
       const bool need_mask = (a.causal && j == q_blk) || ((j + 1) * 128 > a.T);
-      const int kv0 = j * 128;
-      float mx = m;
+      const int kv0 = j * 128 + half * 64;
+      float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+        tmem_ld_32x32(tmem + half * 64 + c * 32 + lane_off, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -214,13 +223,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           mx = fmaxf(mx, s);
         }
       }
+      const __nv_bfloat16 mine = __float2bfloat16(mx);
+      xchg[half * 128 + r] = mine;
+      mbar_arrive(&bars->x_ready);
+      if (!mbar_wait(&bars->x_ready, j & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 106, blockIdx.x, j);
+        ok = false;
+        break;
+      }
+      const float other = __bfloat162float(xchg[(half ^ 1) * 128 + r]);
+      mx = fmaxf(fmaxf(__bfloat162float(mine), other), m);
       const float mref = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = exp2f(m - mref);  // m == -inf -> 0
       float rs = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+        tmem_ld_32x32(tmem + half * 64 + c * 32 + lane_off, v);
         tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
@@ -235,7 +254,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           rs += p0 + p1;
           pk[i >> 1] = pack_bf16x2(p0, p1);
         }
-        store_row_chunk_sw128(sP, r, c * 32, pk);
+        store_row_chunk_sw128(sP, r, half * 64 + c * 32, pk);
       }
       l = l * alpha + rs;
       m = mx;
@@ -249,25 +268,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DH / 32; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem + 128 + c * 32 + lane_off, v);
+        tmem_ld_32x32(tmem + 128 + half * DH + c * 32 + lane_off, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
       }
       tc_fence_before();
     }
+    if (ok) {
+      // total row sum = sum of the two halves; the P tile is free after the last o_full
+      float* lsum = reinterpret_cast<float*>(sP);
+      lsum[half * 128 + r] = l;
+      mbar_arrive(&bars->x_ready);
+      if (!mbar_wait(&bars->x_ready, n_kv & 1, abort_flag)) ok = false;
+      if (ok) l += lsum[(half ^ 1) * 128 + r];
+    }
     if (ok && qpos < a.T) {
       const float inv = (l > 0.f) ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = a.out + static_cast<int64_t>(b * a.T + qpos) * a.ldo + h * D;
+      __nv_bfloat16* orow = a.out + static_cast<int64_t>(b * a.T + qpos) * a.ldo + h * D + half * DH;
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
+      for (int i = 0; i < DH; i += 8) {
         uint4 pk = make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
                               pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv));
         *reinterpret_cast<uint4*>(orow + i) = pk;
       }
-      if (a.lse != nullptr) a.lse[(static_cast<int64_t>(b) * a.H + h) * a.T + qpos] = m + log2f(l);
+      if (a.lse != nullptr && half == 0) a.lse[(static_cast<int64_t>(b) * a.H + h) * a.T + qpos] = m + log2f(l);
     }
   }
 
@@ -306,7 +333,7 @@ struct BwdCfg {
   static constexpr int kOffStats = kOffDST + 32768;               // lse / delta, 2 x 2 x 128 fp32
   static constexpr int kOffBar = kOffStats + 2048;
   static constexpr int kSmem = kOffBar + 256;
-  static constexpr int kTmemCols = 512;  // S^T|dQ [0,128), dP^T [128,256), dV [256,256+D), dK [384,384+D)
+  static constexpr int kTmemCols = 512;  // S^T [0,128), dP^T [128,256), dV [256,256+D), dK [384,384+D), dQ [448,512) or on S^T
 };
 
 struct BwdBars {
@@ -315,12 +342,18 @@ struct BwdBars {
   int abort_flag;
 };
 
+constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 compute warps (two per TMEM lane quarter)
+
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                 const __grid_constant__ BwdArgs a) {
   using C = BwdCfg<D>;
+  // D == 64 leaves room for a private dQ accumulator, so the next score tile can be issued
+  // while this one's dQ is still being drained; D == 128 re-uses the score columns for dQ.
+  constexpr bool kAliasDq = (D != 64);
+  constexpr uint32_t kColDq = kAliasDq ? 0u : 448u;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) report_status(a.status, kBadArgument, 2, 0, 0);
@@ -345,10 +378,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_init(&bars->qdo_empty[s], 1);
     }
     mbar_init(&bars->st_full, 1);
-    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->p_ready, 256);
     mbar_init(&bars->dq_full, 1);
-    mbar_init(&bars->dq_read, 128);
-    mbar_init(&bars->stats_ready, 128);
+    mbar_init(&bars->dq_read, 256);
+    mbar_init(&bars->stats_ready, 256);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -390,16 +423,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 201, blockIdx.x, 0);
     const uint32_t aK = smem_u32(smem + C::kOffK), aV = smem_u32(smem + C::kOffV);
     const uint32_t aPT = smem_u32(smem + C::kOffPT), aDST = smem_u32(smem + C::kOffDST);
-    for (int it = 0; it < n_iters && ok; ++it) {
+    // S^T = K Q^T and dP^T = V dO^T of iteration `it` (its Q / dO stage must have landed).
+    auto issue_scores = [&](int it) -> bool {
       const int s = it % C::kStages;
       const uint32_t ph = (it / C::kStages) & 1;
       if (!mbar_wait(&bars->qdo_full[s], ph, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitFullTimeout, 202, blockIdx.x, it);
-        break;
-      }
-      if (it > 0 && !mbar_wait(&bars->dq_read, (it - 1) & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 203, blockIdx.x, it);
-        break;
+        return false;
       }
       tc_fence_after();
       const uint32_t aQ = smem_u32(smem + C::kOffRing + s * 2 * C::kTile);
@@ -419,11 +449,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tc_commit(&bars->st_full);
       }
       __syncwarp();
+      return true;
+    };
+    if (ok && n_iters > 0) ok = issue_scores(0);
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const int s = it % C::kStages;
       if (!mbar_wait(&bars->p_ready, it & 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitAttnTimeout, 204, blockIdx.x, it);
         break;
       }
       tc_fence_after();
+      const uint32_t aQ = smem_u32(smem + C::kOffRing + s * 2 * C::kTile);
+      const uint32_t aDO = aQ + C::kTile;
       if (lane == 0) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {  // contraction over the 128 query rows
@@ -439,18 +476,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {  // contraction over the 128 key rows: dQ = dS K
-          umma_bf16(tmem, make_smem_desc(aDST + kk * 2048, 16384, 1024), make_smem_desc(aK + kk * 2048, 16384, 1024),
-                    idesc_nn, kk > 0);
+          umma_bf16(tmem + kColDq, make_smem_desc(aDST + kk * 2048, 16384, 1024),
+                    make_smem_desc(aK + kk * 2048, 16384, 1024), idesc_nn, kk > 0);
         }
         tc_commit(&bars->dq_full);
         tc_commit(&bars->qdo_empty[s]);
       }
       __syncwarp();
+      if (it + 1 < n_iters) {
+        if (kAliasDq && !mbar_wait(&bars->dq_read, it & 1, abort_flag)) {
+          if (lane == 0) report_status(a.status, kWaitAttnTimeout, 203, blockIdx.x, it);
+          break;
+        }
+        // P^T / dS^T of `it` are only re-written after the compute warps have seen dq_full(it),
+        // i.e. after the MMAs above have finished reading them.
+        ok = issue_scores(it + 1);
+      }
     }
   } else {
     const int q4 = warp & 3;
-    const int r = q4 * 32 + lane;  // key row inside the block (and query row when reading dQ)
-    const int tid = threadIdx.x - 64;
+    const int half = (warp - 2) >> 2;    // which 64 score columns (and which half of D) this thread owns
+    const int r = q4 * 32 + lane;        // key row inside the block (and query row when reading dQ)
+    const int tid = threadIdx.x - 64;    // 0..255
     const int kvpos = jb * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
     bool ok = true;
@@ -461,12 +508,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       float* st_lse = stats + (it & 1) * 256;
       float* st_del = st_lse + 128;
       {
-        const int qp = q0 + tid;
+        const int qi = tid & 127;
+        const int qp = q0 + qi;
         const int64_t si = (static_cast<int64_t>(b) * a.H + hq) * a.T + qp;
-        st_lse[tid] = (qp < a.T) ? a.lse[si] : 0.f;
-        st_del[tid] = (qp < a.T) ? a.delta[si] : 0.f;
+        if (tid < 128) st_lse[qi] = (qp < a.T) ? a.lse[si] : 0.f;
+        else st_del[qi] = (qp < a.T) ? a.delta[si] : 0.f;
       }
-      // bounded rendezvous of the 128 compute threads on the per-query statistics
+      // bounded rendezvous of the 256 compute threads on the per-query statistics
       mbar_arrive(&bars->stats_ready);
       if (!mbar_wait(&bars->stats_ready, it & 1, abort_flag) || !mbar_wait(&bars->st_full, it & 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitAttnTimeout, 205, blockIdx.x, it);
@@ -476,7 +524,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_after();
       const bool need_mask = (a.causal && iq == jb) || ((iq + 1) * 128 > a.T) || ((jb + 1) * 128 > a.T);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(tmem + c * 32 + lane_off, sv);
         tmem_ld_32x32(tmem + 128 + c * 32 + lane_off, dv);
@@ -516,9 +565,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const int qp = q0 + r;
         float* dq = a.dq_accum + (static_cast<int64_t>(b) * a.T + qp) * (static_cast<int64_t>(a.H) * D) + hq * D;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int c = half * (D / 64) + cc;
           uint32_t v[32];
-          tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+          tmem_ld_32x32(tmem + kColDq + c * 32 + lane_off, v);
           tmem_ld_wait();
           if (qp < a.T) {
 #pragma unroll
@@ -542,7 +592,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const int64_t ld = which == 0 ? a.lddv : a.lddk;
         const uint32_t col = which == 0 ? 256 : 384;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int c = half * (D / 64) + cc;
           uint32_t v[32];
           tmem_ld_32x32(tmem + col + c * 32 + lane_off, v);
           tmem_ld_wait();
@@ -664,7 +715,7 @@ cudaError_t bwd_launch(const AttnTensors& t, const AttnShape& s, const __nv_bflo
   }
   BwdArgs a{s.B, s.T, s.H, s.Hkv, s.scale, s.scale * kLog2e, s.causal, lse, delta, dq_accum, dk, lddk, dv, lddv, status};
   dim3 grid((s.T + 127) / 128, s.Hkv, s.B);
-  kernel<<<grid, kThreads, C::kSmem, stream>>>(tq, tk, tv, tdo, a);
+  kernel<<<grid, kBwdThreads, C::kSmem, stream>>>(tq, tk, tv, tdo, a);
   return cudaGetLastError();
 }
 

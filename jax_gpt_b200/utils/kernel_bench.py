@@ -1,0 +1,133 @@
+"""Per-kernel micro-benchmarks with CUDA-event timing and roofline fractions.
+
+    python -m jax_gpt_b200.utils.kernel_bench --op gemm --M 8192 --N 8192 --K 8192
+    python -m jax_gpt_b200.utils.kernel_bench --op attn_fwd --B 16 --T 1024 --H 12 --D 64
+    python -m jax_gpt_b200.utils.kernel_bench --op attn_bwd | norm_fwd | norm_bwd | adamw | ce
+
+Each run does ``--warmup`` untimed launches, then times ``--iters`` launches with CUDA events on
+the launching stream (synchronised on both sides) and prints one JSON line with the achieved
+rate and its fraction of the measured peak (cuBLAS bf16 burst for FLOP-bound kernels, the copy
+bandwidth for byte-bound ones). Working sets are sized above the 126 MB L2 by default where the
+op is bandwidth-bound. The same commands are the ones run under ``ncu`` for profiles.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import roofline as R
+
+
+def _time(fn, warmup, iters):
+    for _ in range(warmup):
+        fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def main(argv=None):
+    from .. import _ext
+    from ..ops import attention as A
+    from ..ops import gemm as G
+    from ..ops import misc, norm
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", required=True)
+    ap.add_argument("--M", type=int, default=8192)
+    ap.add_argument("--N", type=int, default=8192)
+    ap.add_argument("--K", type=int, default=8192)
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--B", type=int, default=16)
+    ap.add_argument("--T", type=int, default=1024)
+    ap.add_argument("--H", type=int, default=12)
+    ap.add_argument("--D", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    peaks = R.load_peaks()
+    flops = bytes_ = 0.0
+    if args.op == "gemm":
+        M, N, K = args.M, args.N, args.K
+        a = torch.randn((K, M) if args.a_mn else (M, K), device=dev).to(torch.bfloat16)
+        b = torch.randn((K, N) if args.b_mn else (N, K), device=dev).to(torch.bfloat16)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        fn = lambda: G.gemm(a, b, a_mn_major=args.a_mn, b_mn_major=args.b_mn, out=out)
+        flops, bytes_ = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+    elif args.op in ("attn_fwd", "attn_bwd"):
+        B, T, H, D = args.B, args.T, args.H, args.D
+        qkv = torch.randn(B, T, 3 * H * D, device=dev).to(torch.bfloat16)
+        q, k, v = [qkv[..., i * H * D:(i + 1) * H * D].unflatten(-1, (H, D)) for i in range(3)]
+        out, lse = A.attn_fwd(q, k, v)
+        base = 4.0 * B * H * T * T * D / 2
+        if args.op == "attn_fwd":
+            fn = lambda: A.attn_fwd(q, k, v, out=out, lse=lse)
+            flops = base
+        else:
+            dout = torch.randn_like(out)
+            dqkv = torch.empty_like(qkv)
+            dq, dk, dv = [dqkv[..., i * H * D:(i + 1) * H * D].unflatten(-1, (H, D)) for i in range(3)]
+            acc = torch.zeros(B * T, H * D, device=dev)
+            delta = torch.empty(B, H, T, device=dev)
+
+            def fn():
+                acc.zero_()
+                A.attn_bwd(q, k, v, out, dout, lse, dq=dq, dk=dk, dv=dv, dq_accum=acc, delta=delta)
+            flops = 2.5 * base
+        bytes_ = 2.0 * 4 * B * T * H * D
+    elif args.op in ("norm_fwd", "norm_bwd"):
+        M, D = args.M, args.N if args.N <= 8192 else 768
+        x = torch.randn(M, D, device=dev).to(torch.bfloat16)
+        g = torch.ones(D, device=dev, dtype=torch.bfloat16)
+        bta = torch.zeros(D, device=dev, dtype=torch.bfloat16)
+        y, mean, rstd = norm.norm_fwd(norm.LAYERNORM, x, g, bta, 1e-5)
+        if args.op == "norm_fwd":
+            fn = lambda: norm.norm_fwd(norm.LAYERNORM, x, g, bta, 1e-5, y=y, mean=mean, rstd=rstd)
+            bytes_ = 2.0 * 2 * M * D
+        else:
+            dy = torch.randn_like(x)
+            dx = torch.empty_like(x)
+            dg = torch.zeros(D, device=dev)
+            db = torch.zeros(D, device=dev)
+            fn = lambda: norm.norm_bwd(norm.LAYERNORM, dy, x, g, mean, rstd, dg, db, dx=dx)
+            bytes_ = 2.0 * 3 * M * D
+    elif args.op == "adamw":
+        n = args.M * args.N
+        p, g, m, v = [torch.randn(n, device=dev) for _ in range(4)]
+        v.abs_()
+        pb = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        hp = torch.tensor([1e-3, 0.1, 0.05, 1.0], device=dev)
+        fn = lambda: misc.adamw(p, g, m, v, hp, None, wd=0.1, p_bf16=pb)
+        bytes_ = n * (16.0 + 18.0)
+    elif args.op == "ce":
+        M, V = args.M, args.N
+        logits = torch.randn(M, (V + 63) // 64 * 64, device=dev).to(torch.bfloat16)
+        tg = torch.randint(0, V, (M,), device=dev, dtype=torch.int32)
+        loss = torch.empty(M, device=dev)
+        fn = lambda: misc.cross_entropy_fwd_bwd(logits, tg, V, 1.0 / M, loss=loss)
+        bytes_ = 2.0 * 2 * M * V
+    else:
+        raise SystemExit(f"unknown op {args.op}")
+    ms = _time(fn, args.warmup, args.iters)
+    _ext.check_status(dev)
+    res = {"op": args.op, "ms": ms, "args": {k: v for k, v in vars(args).items() if k not in ("op",)}}
+    if flops:
+        res["tflops"] = flops / ms / 1e9
+        res["frac_of_measured_bf16_peak"] = res["tflops"] / peaks["bf16_tflops"]
+    if bytes_:
+        res["gbs"] = bytes_ / ms / 1e6
+        res["frac_of_measured_hbm"] = res["gbs"] / peaks["hbm_gbs"]
+    res["denominators"] = peaks["source"]
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()
