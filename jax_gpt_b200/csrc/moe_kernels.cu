@@ -1,0 +1,496 @@
+// Expert-parallel MoE forward as ONE cooperative kernel per rank.
+//
+//   1. every rank publishes its per-expert pair counts to all peers (tiny all-gather through peer
+//      stores + a flag barrier); from the full count table each CTA derives, in shared memory,
+//      where its rows go in every destination's receive buffer and how many rows each local
+//      expert receives - no host round trip, no separate exchange kernel;
+//   2. dispatch: one warp per (token, expert) pair copies the token row straight into the
+//      destination rank's expert-sorted receive buffer over NVLink, with its source id and
+//      routing weight, then bumps that expert's arrival counter on the destination;
+//   3. grouped GEMM 1 (tcgen05, TMA, TMEM): for each local expert, as soon as its rows have
+//      arrived, [gate | up] = X_e [W_gate_e | W_up_e] with SiLU(gate) * up in the epilogue;
+//   4. grouped GEMM 2: Y_e = act_e W_down_e; the epilogue multiplies each row by its routing
+//      weight and adds it into the OWNER rank's fp32 output row with vectorised red.add over
+//      NVLink - combine and top-k reduction happen in flight, nothing is sent back as rows.
+//
+// A static tile order (expert by expert, GEMM 1 tiles before GEMM 2 tiles) makes every
+// dependency point backwards, so the persistent CTAs cannot deadlock; every wait (arrival
+// counters of remote ranks, per-m-tile readiness of `act`, mbarriers) is bounded and reports
+// through the status word. No TMA multicast; remote data is pushed into local memory first and
+// read with ordinary TMA tile loads.
+//
+// Replaces the replicated-token expert parallelism of the reference (every rank computes all
+// rows, one psum; jax_gpt/models/qwen35/moe.py:117-222) and its three ragged_dot calls
+// (jax_gpt/models/qwen35/moe.py:83-87).
+#include "moe_kernels.cuh"
+
+#include <cooperative_groups.h>
+
+#include "comm_device.cuh"
+#include "common.cuh"
+#include "tma_host.h"
+
+namespace cg = cooperative_groups;
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 192;
+
+struct MoeTables {
+  int send_off[kMoeMaxExperts];      // first row of MY pairs for global expert e in its destination buffer
+  int rows[kMoeMaxLocalExperts];     // rows received per local expert
+  int base[kMoeMaxLocalExperts];     // first row of the local expert in this rank's receive buffer
+  int tile0[kMoeMaxLocalExperts + 1];  // first tile index of the local expert (GEMM1 tiles, then GEMM2 tiles)
+  int mt0[kMoeMaxLocalExperts + 1];    // first m-tile index of the local expert
+  int overflow;                      // some rank would receive more rows than cap_rows
+};
+
+struct MoeBars {
+  uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(MoeTables) + sizeof(MoeBars) + 64;
+
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until *p (cumulative counter) has reached `target` (wrap-safe signed difference).
+template <bool kSystem>
+__device__ __forceinline__ bool wait_counter_ge(const unsigned* p, unsigned target, uint64_t budget_ns,
+                                                volatile int* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    const unsigned v = kSystem ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p);
+    if (static_cast<int>(v - target) >= 0) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > budget_ns) {
+      *abort_flag = 1;
+      return false;
+    }
+    __nanosleep(32);
+  }
+}
+
+__global__ void moe_prepare_kernel(const int* __restrict__ idx, int n_pairs, int* __restrict__ counts,
+                                   int* __restrict__ pos) {
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += gridDim.x * blockDim.x)
+    pos[p] = atomicAdd(&counts[idx[p]], 1);
+}
+
+// Fills the shared-memory tables from the all-gathered count matrix counts[src][e].
+__device__ void build_tables(const EpMoeArgs& a, const int* counts_all, MoeTables* tb) {
+  const int W = a.world, EL = a.e_local, ET = W * EL;
+  if (threadIdx.x == 0) tb->overflow = 0;
+  __syncthreads();
+  for (int e = threadIdx.x; e < ET; e += blockDim.x) {
+    const int dst = e / EL, el = e % EL;
+    int off = 0;
+    for (int e2 = dst * EL; e2 < dst * EL + el; ++e2)   // experts placed before e on the destination
+      for (int s = 0; s < W; ++s) off += __ldcg(counts_all + s * ET + e2);
+    for (int s = 0; s < a.rank; ++s) off += __ldcg(counts_all + s * ET + e);  // sources placed before this rank
+    tb->send_off[e] = off;
+    if (el == EL - 1) {
+      int tot = off;
+      for (int s = a.rank; s < W; ++s) tot += __ldcg(counts_all + s * ET + e);
+      if (tot > a.cap_rows) tb->overflow = 1;
+    }
+  }
+  for (int el = threadIdx.x; el < EL; el += blockDim.x) {
+    int n = 0;
+    for (int s = 0; s < W; ++s) n += __ldcg(counts_all + s * ET + a.rank * EL + el);
+    tb->rows[el] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int n1 = a.inter / 128, n2 = a.d_model / BN;
+    int b = 0, t = 0, m = 0;
+    for (int el = 0; el < EL; ++el) {
+      tb->base[el] = b;
+      tb->tile0[el] = t;
+      tb->mt0[el] = m;
+      const int mt = (tb->rows[el] + BM - 1) / BM;
+      b += tb->rows[el];
+      t += mt * (n1 + n2);
+      m += mt;
+    }
+    tb->tile0[EL] = t;
+    tb->mt0[EL] = m;
+  }
+  __syncthreads();
+}
+
+struct TileInfo {
+  int el, m, n, phase;  // phase 0: GEMM1 (gate|up), 1: GEMM2 (down)
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const EpMoeArgs& a, const MoeTables* tb, int t) {
+  const int n1 = a.inter / 128, n2 = a.d_model / BN;
+  int el = 0;
+  while (t >= tb->tile0[el + 1]) ++el;
+  const int mt = (tb->rows[el] + BM - 1) / BM;
+  int r = t - tb->tile0[el];
+  TileInfo ti;
+  ti.el = el;
+  if (r < mt * n1) {
+    ti.phase = 0;
+    ti.m = r % mt;
+    ti.n = r / mt;
+  } else {
+    r -= mt * n1;
+    ti.phase = 1;
+    ti.m = r % mt;
+    ti.n = r / mt;
+  }
+  return ti;
+}
+
+}  // namespace
+
+namespace {
+
+__global__ void __launch_bounds__(kThreads, 1)
+ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_constant__ CUtensorMap t_act,
+                      const __grid_constant__ CUtensorMap t_gate, const __grid_constant__ CUtensorMap t_up,
+                      const __grid_constant__ CUtensorMap t_down, const __grid_constant__ EpMoeArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  MoeTables* tb = reinterpret_cast<MoeTables*>(smem + kStages * kStageBytes);
+  MoeBars* bars = reinterpret_cast<MoeBars*>(reinterpret_cast<uint8_t*>(tb) + ((sizeof(MoeTables) + 15) & ~size_t(15)));
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int W = a.world, EL = a.e_local, ET = W * EL, D = a.d_model, I = a.inter;
+  CommCtrl* my = a.peer_ctrl[a.rank];
+  const int epoch = my->epoch + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 4);
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  // ---- 1. publish this rank's counts, wait for everybody's ----
+  {
+    const int max_mt = a.cap_rows / BM + EL;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < max_mt; i += gridDim.x * blockDim.x) a.act_ready[i] = 0;
+  }
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) my->abort_flag = 0;
+    for (int i = threadIdx.x; i < ET; i += blockDim.x) {
+      const int c = a.my_counts[i];
+      for (int p = 0; p < W; ++p) a.peer_counts[p][a.rank * ET + i] = c;
+    }
+    const bool ok = flag_barrier(a.peer_ctrl, W, a.rank, 4, epoch, a.wait_budget_ns, a.status);
+    if (!ok && threadIdx.x == 0) my->abort_flag = 1;
+  }
+  __threadfence();
+  grid.sync();
+  bool alive = (*reinterpret_cast<volatile int*>(&my->abort_flag) == 0);
+  build_tables(a, a.peer_counts[a.rank], tb);
+  if (tb->overflow) {
+    if (alive && blockIdx.x == 0 && threadIdx.x == 0) report_status(a.status, kBadArgument, 40, a.cap_rows, 0);
+    alive = false;
+  }
+
+  // ---- 2. dispatch: one warp per (token, expert) pair ----
+  if (alive) {
+    const int n_pairs = a.tokens * a.top_k;
+    for (int p = blockIdx.x * (kThreads / 32) + warp; p < n_pairs; p += gridDim.x * (kThreads / 32)) {
+      const int e = a.idx[p];
+      const int dst = e / EL, el = e - dst * EL;
+      const int slot = tb->send_off[e] + a.pos[p];
+      const int tok = p / a.top_k;
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<int64_t>(tok) * D);
+      uint4* out = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
+      for (int i = lane; i < D / 8; i += 32) out[i] = src[i];
+      if (lane == 0) {
+        a.peer_recv_meta[dst][slot] = (a.rank << 24) | tok;
+        a.peer_recv_w[dst][slot] = a.w[p];
+        a.slot_out[p] = slot;
+      }
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_system();
+        red_release_sys_add_u32(a.peer_arrive[dst] + el, 1u);
+      }
+    }
+  }
+
+  // ---- 3./4. grouped GEMMs over the local experts ----
+  const int num_tiles = alive ? tb->tile0[EL] : 0;
+  const int n1 = I / 128;
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int ready_el = -1;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileInfo ti = decode_tile(a, tb, t);
+        if (ti.phase == 0) {
+          if (ti.el != ready_el) {
+            const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(tb->rows[ti.el]);
+            if (!wait_counter_ge<true>(a.peer_arrive[a.rank] + ti.el, target, a.wait_budget_ns, abort_flag)) {
+              report_status(a.status, kWaitFlagTimeout, 41, ti.el, t);
+              break;
+            }
+            ready_el = ti.el;
+          }
+        } else {
+          const unsigned* ready = reinterpret_cast<const unsigned*>(a.act_ready) + tb->mt0[ti.el] + ti.m;
+          if (!wait_counter_ge<false>(ready, 4u * n1, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 42, ti.el, t);
+            break;
+          }
+        }
+        fence_proxy_async_global();
+        const int row0 = tb->base[ti.el] + ti.m * BM;
+        const int nkb = (ti.phase == 0 ? D : I) / BK;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag)) {
+            report_status(a.status, kWaitEmptyTimeout, 43, blockIdx.x, t);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_arrive_expect_tx(&bars->full[stage], kStageBytes);
+          if (ti.phase == 0) {
+            tma_load_2d(sa, &t_recv, &bars->full[stage], kb * BK, row0);
+            const int ky = ti.el * D + kb * BK;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              tma_load_2d(sb + i * 8192, &t_gate, &bars->full[stage], ti.n * 128 + 64 * i, ky);
+              tma_load_2d(sb + (2 + i) * 8192, &t_up, &bars->full[stage], ti.n * 128 + 64 * i, ky);
+            }
+          } else {
+            tma_load_2d(sa, &t_act, &bars->full[stage], kb * BK, row0);
+            const int ky = ti.el * I + kb * BK;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tma_load_2d(sb + i * 8192, &t_down, &bars->full[stage], ti.n * BN + 64 * i, ky);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        for (int s = 0; s < kStages; ++s) {
+          const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&bars->full[s], armed)) {
+            if (globaltimer_ns() - t0 > 2000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc = make_idesc(BM, BN, 0, 1, 1);
+    int stage = 0, iter = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+      const TileInfo ti = decode_tile(a, tb, t);
+      const int acc = iter & 1;
+      if (!mbar_wait(&bars->tmem_empty[acc], ((iter >> 1) & 1) ^ 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemEmptyTimeout, 44, blockIdx.x, t);
+        break;
+      }
+      tc_fence_after();
+      const int nkb = (ti.phase == 0 ? D : I) / BK;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+          if (lane == 0) report_status(a.status, kWaitFullTimeout, 45, blockIdx.x, t);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16(tmem_base + acc * BN, make_smem_desc(sa + k * 32, 16, 1024),
+                      make_smem_desc(sb + k * 2048, 8192, 1024), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&bars->empty[stage]);
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok && lane == 0) tc_commit(&bars->tmem_full[acc]);
+      __syncwarp();
+    }
+  } else {
+    const int q = warp & 3;
+    int iter = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++iter) {
+      const TileInfo ti = decode_tile(a, tb, t);
+      const int acc = iter & 1;
+      if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 46, blockIdx.x, t);
+        break;
+      }
+      tc_fence_after();
+      const int r = ti.m * BM + q * 32 + lane;            // row within the expert
+      const bool row_ok = r < tb->rows[ti.el];
+      const int64_t row = tb->base[ti.el] + r;            // row in the receive buffer
+      const uint32_t tacc = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (ti.phase == 0) {
+        __nv_bfloat16* dst = a.act + row * I + ti.n * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(tacc + c * 32, g);
+          tmem_ld_32x32(tacc + 128 + c * 32, u);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
+                const float h0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(u[j + 2 * e]);
+                const float h1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(u[j + 2 * e + 1]);
+                pk[e] = pack_bf16x2(h0, h1);
+              }
+              *reinterpret_cast<uint4*>(dst + c * 32 + j) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
+        }
+      } else {
+        float wgt = 0.f;
+        float* dst = nullptr;
+        if (row_ok) {
+          wgt = a.peer_recv_w[a.rank][row];
+          const int meta = a.peer_recv_meta[a.rank][row];
+          dst = a.peer_out[meta >> 24] + static_cast<int64_t>(meta & 0xFFFFFF) * D + ti.n * BN;
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tacc + c * 32, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 32 + j),
+                           "f"(__uint_as_float(v[j]) * wgt), "f"(__uint_as_float(v[j + 1]) * wgt),
+                           "f"(__uint_as_float(v[j + 2]) * wgt), "f"(__uint_as_float(v[j + 3]) * wgt)
+                           : "memory");
+          }
+        }
+      }
+      tc_fence_before();
+      if (ti.phase == 0) {
+        __threadfence();
+        fence_proxy_async_global();
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars->tmem_empty[acc]);
+        if (ti.phase == 0) atomicAdd(a.act_ready + tb->mt0[ti.el] + ti.m, 1);
+      }
+    }
+  }
+
+  // ---- 5. every rank's contributions have landed before anybody returns ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+  __threadfence_system();
+  grid.sync();
+  if (blockIdx.x == 0) {
+    flag_barrier(a.peer_ctrl, W, a.rank, 5, epoch, a.wait_budget_ns, a.status);
+    if (alive) {
+      for (int el = threadIdx.x; el < EL; el += blockDim.x) {
+        a.arrive_target[el] += static_cast<unsigned>(tb->rows[el]);
+        a.rows_out[el] = tb->rows[el];
+      }
+    }
+    if (threadIdx.x == 0) my->epoch = epoch;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_moe_prepare(const int* idx, int n_pairs, int n_experts, int* counts, int* pos, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * n_experts, st);
+  if (e != cudaSuccess) return e;
+  const int grid = (n_pairs + 255) / 256 < 1184 ? (n_pairs + 255) / 256 : 1184;
+  moe_prepare_kernel<<<grid > 0 ? grid : 1, 256, 0, st>>>(idx, n_pairs, counts, pos);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_moe_forward(const EpMoeArgs& args, const __nv_bfloat16* gate, const __nv_bfloat16* up,
+                                  const __nv_bfloat16* down, cudaStream_t st) {
+  const EpMoeArgs& a = args;
+  if (a.world < 1 || a.world > kCommMaxRanks || a.e_local < 1 || a.e_local > kMoeMaxLocalExperts ||
+      a.world * a.e_local > kMoeMaxExperts || a.d_model % 256 != 0 || a.inter % 128 != 0 || a.cap_rows % BM != 0 ||
+      a.tokens >= (1 << 24))
+    return cudaErrorInvalidValue;
+  CUtensorMap t_recv, t_act, t_gate, t_up, t_down;
+  cudaError_t e;
+  if ((e = encode_tma_2d(&t_recv, a.peer_recv_x[a.rank], 2, a.d_model, a.cap_rows, a.d_model * 2ull, 64, BM)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&t_act, a.act, 2, a.inter, a.cap_rows, a.inter * 2ull, 64, BM)) != cudaSuccess) return e;
+  const uint64_t gate_rows = static_cast<uint64_t>(a.e_local) * a.d_model, down_rows = static_cast<uint64_t>(a.e_local) * a.inter;
+  if ((e = encode_tma_2d(&t_gate, gate, 2, a.inter, gate_rows, a.inter * 2ull, 64, 64)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&t_up, up, 2, a.inter, gate_rows, a.inter * 2ull, 64, 64)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&t_down, down, 2, a.d_model, down_rows, a.d_model * 2ull, 64, 64)) != cudaSuccess) return e;
+  static bool configured = false;
+  if (!configured) {
+    if ((e = cudaFuncSetAttribute(ep_moe_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)) != cudaSuccess)
+      return e;
+    configured = true;
+  }
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  EpMoeArgs args_copy = args;
+  void* params[] = {&t_recv, &t_act, &t_gate, &t_up, &t_down, &args_copy};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ep_moe_forward_kernel), dim3(sms), dim3(kThreads), params,
+                                     kSmemBytes, st);
+}
+
+}  // namespace b200

@@ -1,0 +1,56 @@
+// Expert-parallel MoE: token dispatch, grouped SwiGLU GEMMs and weighted combine in one kernel
+// per rank (see moe_kernels.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "comm_kernels.cuh"
+
+namespace b200 {
+
+constexpr int kMoeMaxLocalExperts = 64;
+constexpr int kMoeMaxExperts = 512;
+
+struct EpMoeArgs {
+  int world, rank;
+  int tokens;    // tokens owned by this rank
+  int top_k;
+  int d_model;   // multiple of 256
+  int inter;     // expert intermediate size, multiple of 128
+  int e_local;   // experts per rank; global expert e lives on rank e / e_local
+  int cap_rows;  // rows the receive buffers of every rank can hold
+  // local inputs
+  const __nv_bfloat16* x;  // [tokens, d_model]
+  const int* idx;          // [tokens * top_k] global expert id of each (token, choice) pair
+  const float* w;          // [tokens * top_k] routing weight of the pair
+  const int* pos;          // [tokens * top_k] index of the pair among this rank's pairs for that expert
+  const int* my_counts;    // [world * e_local] pairs per global expert from this rank
+  // symmetric (peer-visible) buffers, one pointer per rank
+  __nv_bfloat16* peer_recv_x[kCommMaxRanks];  // [cap_rows, d_model] rows sorted by local expert, then by source rank
+  int* peer_recv_meta[kCommMaxRanks];         // [cap_rows] (source rank << 24) | source token
+  float* peer_recv_w[kCommMaxRanks];          // [cap_rows] routing weight of the row
+  int* peer_counts[kCommMaxRanks];            // [world][world * e_local] every rank's my_counts
+  unsigned* peer_arrive[kCommMaxRanks];       // [e_local] rows delivered so far, cumulative over launches
+  float* peer_out[kCommMaxRanks];             // [tokens of that rank, d_model] fp32 combine target (zeroed by owner)
+  CommCtrl* peer_ctrl[kCommMaxRanks];
+  // local scratch / state
+  __nv_bfloat16* act;       // [cap_rows, inter] SwiGLU output
+  unsigned* arrive_target;  // [e_local] arrivals expected once this launch's rows are in (cumulative)
+  int* act_ready;           // [cap_rows / 128 + e_local] per m-tile count of finished GEMM1 epilogue warps
+  int* slot_out;            // [tokens * top_k] row of each pair in its destination's receive buffer
+  int* rows_out;            // [e_local] rows received per local expert (for the caller / backward)
+  uint64_t wait_budget_ns;
+  int* status;
+};
+
+// counts[e] = number of pairs routed to global expert e; pos[p] = rank of pair p within its expert.
+cudaError_t launch_moe_prepare(const int* idx, int n_pairs, int n_experts, int* counts, int* pos, cudaStream_t st);
+
+// gate/up: [e_local, d_model, inter] bf16 (in,out); down: [e_local, inter, d_model]. The kernel reads the
+// receive buffer and `act` of THIS rank through TMA (pointers args.peer_recv_x[rank], args.act).
+cudaError_t launch_ep_moe_forward(const EpMoeArgs& args, const __nv_bfloat16* gate, const __nv_bfloat16* up,
+                                  const __nv_bfloat16* down, cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,88 @@
+"""Expert-parallel MoE layers.
+
+``FusedEPMoE`` runs the routed experts of one MoE layer across the ranks of a group with the
+single-kernel dispatch -> grouped SwiGLU GEMM -> weighted combine of csrc/moe_kernels.cu:
+token rows are pushed into the owning rank's expert-sorted buffer over NVLink, the tcgen05
+grouped GEMMs start per expert as its rows arrive, and the down-projection epilogue adds the
+weighted result straight into the token owner's output row. ``NcclEPMoE`` is the library
+baseline with the same math: ``all_to_all_single`` dispatch, per-expert GEMMs, ``all_to_all_single``
+combine (jax_gpt_b200/models/qwen35/moe.py:expert_forward_ep).
+
+The reference's expert parallelism replicates the tokens and sums full outputs with one psum
+(jax_gpt/models/qwen35/moe.py:117-222).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _ext
+from ..comm.symm import Communicator
+
+
+class FusedEPMoE:
+    """Buffers and launch logic of the fused expert-parallel forward for a fixed problem size.
+
+    ``tokens``: tokens owned by every rank; ``n_experts``: global expert count (experts
+    ``[r * E/W, (r+1) * E/W)`` live on rank r); ``cap_factor``: receive-buffer rows as a multiple
+    of the balanced load ``tokens * top_k`` (the worst case is ``world``).
+    """
+
+    def __init__(self, comm: Communicator, tokens: int, d_model: int, inter: int, n_experts: int, top_k: int,
+                 cap_factor: Optional[float] = None):
+        self.comm = comm
+        W = comm.world
+        assert n_experts % W == 0 and d_model % 256 == 0 and inter % 128 == 0
+        self.tokens, self.D, self.I, self.E, self.k = tokens, d_model, inter, n_experts, top_k
+        self.e_local = n_experts // W
+        cap_factor = float(W) if cap_factor is None else cap_factor
+        self.cap_rows = (int(tokens * top_k * cap_factor) + 127) // 128 * 128
+        dev = comm.device
+        self.recv_x = comm.alloc(self.cap_rows * d_model, torch.bfloat16, zero=True)
+        self.recv_meta = comm.alloc(self.cap_rows, torch.int32)
+        self.recv_w = comm.alloc(self.cap_rows, torch.float32)
+        self.counts_all = comm.alloc(W * n_experts, torch.int32)
+        self.arrive = comm.alloc(max(self.e_local, 32), torch.int32)
+        self.out_acc = comm.alloc(tokens * d_model, torch.float32)
+        self.act = torch.zeros(self.cap_rows, inter, device=dev, dtype=torch.bfloat16)
+        self.arrive_target = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
+        self.act_ready = torch.zeros(self.cap_rows // 128 + self.e_local, device=dev, dtype=torch.int32)
+        self.slot_out = torch.zeros(tokens * top_k, device=dev, dtype=torch.int32)
+        self.rows_out = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
+        self.my_counts = torch.zeros(n_experts, device=dev, dtype=torch.int32)
+        self.pos = torch.zeros(tokens * top_k, device=dev, dtype=torch.int32)
+        dist.barrier(comm.group)
+
+    def forward(self, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, params: dict,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x (tokens, D) bf16; weights / idx (tokens, k); params hold this rank's experts stacked:
+        gate_proj / up_proj (E_local, D, I), down_proj (E_local, I, D). Returns (tokens, D) fp32."""
+        ops = _ext.ops()
+        c = self.comm
+        idx32 = idx.to(torch.int32).contiguous().view(-1)
+        w32 = weights.to(torch.float32).contiguous().view(-1)
+        ops.moe_prepare(idx32, self.my_counts, self.pos)
+        self.out_acc.tensor.zero_()
+        ops.ep_moe_forward(c.world, c.rank, self.k, self.e_local, self.cap_rows, x.contiguous(), idx32, w32, self.pos,
+                           self.my_counts, self.recv_x.peer_ptrs, self.recv_meta.peer_ptrs, self.recv_w.peer_ptrs,
+                           self.counts_all.peer_ptrs, self.arrive.peer_ptrs, self.out_acc.peer_ptrs, c.ctrl.peer_ptrs,
+                           self.act, self.arrive_target, self.act_ready, self.slot_out, self.rows_out,
+                           params["gate_proj"], params["up_proj"], params["down_proj"], c.wait_seconds)
+        res = self.out_acc.tensor.view(self.tokens, self.D)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+
+class NcclEPMoE:
+    """Baseline: NCCL all-to-all dispatch and combine around per-expert GEMMs."""
+
+    def __init__(self, group, n_experts: int):
+        self.group, self.E = group, n_experts
+
+    def forward(self, x, weights, idx, params):
+        from ..models.qwen35.moe import expert_forward_ep
+        return expert_forward_ep(x, weights, idx, params, self.group, self.E)

@@ -84,6 +84,44 @@ def run_tp(rank, world, device):
     return res
 
 
+def run_ep(rank, world, device):
+    """Fused expert-parallel MoE forward vs a dense evaluation with all experts and vs the NCCL path."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.comm.symm import Communicator
+    from jax_gpt_b200.models.qwen35.moe import expert_forward_single
+    from jax_gpt_b200.parallel.expert_parallel import FusedEPMoE, NcclEPMoE
+    tokens, D, I, E, k = 384, 512, 256, 16, 4
+    g = torch.Generator(device=device).manual_seed(3)  # same weights on every rank
+    full = {"gate_proj": (torch.randn(E, D, I, device=device, generator=g) * 0.05).to(torch.bfloat16),
+            "up_proj": (torch.randn(E, D, I, device=device, generator=g) * 0.05).to(torch.bfloat16),
+            "down_proj": (torch.randn(E, I, D, device=device, generator=g) * 0.05).to(torch.bfloat16)}
+    el = E // world
+    local = {n: t[rank * el:(rank + 1) * el].contiguous() for n, t in full.items()}
+    comm = Communicator(device=device, wait_seconds=5.0)
+    fused = FusedEPMoE(comm, tokens, D, I, E, k)
+    nccl = NcclEPMoE(dist.group.WORLD, E)
+    res = {}
+    for step, mode in enumerate(["uniform", "skewed", "uniform"]):
+        gs = torch.Generator(device=device).manual_seed(100 * step + rank)
+        x = torch.randn(tokens, D, device=device, generator=gs).to(torch.bfloat16)
+        logits = torch.randn(tokens, E, device=device, generator=gs)
+        if mode == "skewed":
+            logits[:, :3] += 6.0     # almost everything goes to three experts of rank 0; several experts stay empty
+            logits[:, 5] = -1e9
+        w, idx = torch.softmax(logits, -1).topk(k, dim=-1)
+        w = w / w.sum(-1, keepdim=True)
+        out = fused.forward(x, w, idx, local).clone()
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        ref = expert_forward_single(x.float(), w, idx, {n: t.float() for n, t in full.items()})
+        base = nccl.forward(x, w, idx, local)
+        res[f"{mode}{step}_fused_vs_dense"] = rel(out, ref)
+        res[f"{mode}{step}_nccl_vs_dense"] = rel(base, ref)
+        dist.barrier()
+    res["rows_last"] = fused.rows_out.tolist()
+    return res
+
+
 def main():
     what = sys.argv[1]
     out_path = sys.argv[2]
@@ -98,6 +136,8 @@ def main():
         res = run_fsdp(rank, world, device, True)
     elif what == "tp":
         res = run_tp(rank, world, device)
+    elif what == "ep":
+        res = run_ep(rank, world, device)
     else:
         raise SystemExit(f"unknown test {what}")
     if rank == 0:

@@ -41,6 +41,13 @@ def test_tp_fused_gemms_two_gpus(tmp_path):
     assert res["ag_gemm"] < 1e-2 and res["gemm_rs"] < 1e-2, res
 
 
+def test_fused_ep_moe_two_gpus(tmp_path):
+    res = _run("ep", tmp_path, port=29613)
+    for k, v in res.items():
+        if k.endswith("_vs_dense"):
+            assert v < 2e-2, res
+
+
 def test_bounded_wait_reports_timeout(cuda_device):
     """A flag that nothing sets: the kernel gives up after its budget, records the status
     and returns; the context stays usable."""
