@@ -1,0 +1,44 @@
+// Launchers of the routing, rotary, quantisation and Gated-DeltaNet decode kernels (seq_kernels.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// MoE router on fp32 logits [M, E] (E <= 512, E % 32 == 0).
+//  mode 0: softmax over all experts, top-k, renormalise to sum 1 (Qwen3.5).
+//  mode 1: sigmoid scores; selection on score + bias; groups ranked by the sum of their top-2;
+//          top-k over the kept groups; weights = unbiased scores / their sum * scale (DeepSeek-V3).
+// Outputs: weights [M, k] fp32, ids [M, k] int32, and (optional) counts [E] += pairs per expert.
+cudaError_t launch_router(int mode, const float* logits, const float* bias, int M, int E, int k, int n_group,
+                          int topk_group, float scale, float* weights, int* ids, int* counts, cudaStream_t st);
+
+// x [rows, H, dh] bf16 -> y: per-head RMSNorm over dh (weight w, (1 + w) when one_plus), then
+// half-split rotary on the first rope_dim features with the (cos, sin) table [n_pos, rope_dim/2, 2];
+// row r uses position pos0 + (r % T). norm_w may be nullptr (rotary only).
+cudaError_t launch_rmsnorm_rope(const __nv_bfloat16* x, const __nv_bfloat16* norm_w, const float* freqs,
+                                __nv_bfloat16* y, int rows, int T, int H, int dh, int rope_dim, int pos0, float eps,
+                                int one_plus, cudaStream_t st);
+
+// Block-scaled FP8 e4m3 quantisation. Activations: one fp32 scale per 1 x 128 block along K
+// (x [M, K] bf16 -> q [M, K] fp8, scales [M, K/128]); weights: one scale per 128 x 128 block
+// (w [R, C] bf16 -> q [R, C], scales [R/128, C/128]). scale = amax / 448, optionally rounded up to
+// a power of two; q = x / scale.
+cudaError_t launch_fp8_quant_1x128(const __nv_bfloat16* x, uint8_t* q, float* scales, int M, int K, int pow2,
+                                   cudaStream_t st);
+cudaError_t launch_fp8_quant_128x128(const __nv_bfloat16* w, uint8_t* q, float* scales, int R, int C, int pow2,
+                                     cudaStream_t st);
+
+// One decode step of a Gated-DeltaNet layer for B sequences, fused: conv-window update + depthwise
+// conv + SiLU, gates, L2-normalised q/k, state decay + delta-rule update, read-out, gated RMSNorm.
+//  mixed [B, 2*Kd + Vd] bf16 (projected q|k|v before the conv), z [B, Vd], bproj / aproj [B, Hv] bf16,
+//  conv_state [B, C, Kc] fp32 (updated in place), conv_w [C, Kc], A_log / dt_bias [Hv], norm_w [dv],
+//  state [B, Hv, dk, dv] fp32 (updated in place), out [B, Vd] bf16.
+cudaError_t launch_gdn_decode_step(const __nv_bfloat16* mixed, const __nv_bfloat16* z, const __nv_bfloat16* bproj,
+                                   const __nv_bfloat16* aproj, float* conv_state, const __nv_bfloat16* conv_w,
+                                   const __nv_bfloat16* A_log, const __nv_bfloat16* dt_bias,
+                                   const __nv_bfloat16* norm_w, float* state, __nv_bfloat16* out, int B, int Hqk, int Hv,
+                                   int dk, int dv, int Kc, float eps, cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,85 @@
+"""Fused per-head RMSNorm + partial rotary embedding, and the block-scaled FP8 quantisers.
+
+PyTorch references: ``rms_norm`` / ``apply_rotary_emb`` of models/qwen35/primitives.py (the
+semantics of jax_gpt/models/qwen35/primitives.py:29-32,79-109) and the explicit block
+quantisers below.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _ext
+
+FP8_MAX = 448.0
+
+
+def rmsnorm_rope_ref(x, norm_w, freqs, rope_dim: int, pos0: int = 0, eps: float = 1e-6, one_plus: bool = True):
+    """x (B,T,H,dh); freqs (n_pos, rope_dim/2, 2)."""
+    from ..models.qwen35.primitives import apply_rotary_emb
+    xf = x.float()
+    if norm_w is not None:
+        xf = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * ((1.0 + norm_w.float()) if one_plus else norm_w.float())
+    if rope_dim:
+        xf = apply_rotary_emb(xf, freqs[pos0:pos0 + x.shape[1]], rope_dim)
+    return xf.to(x.dtype)
+
+
+def rmsnorm_rope(x, norm_w, freqs, rope_dim: int, pos0: int = 0, eps: float = 1e-6, one_plus: bool = True):
+    B, T, H, dh = x.shape
+    per = dh // 32 if dh % 32 == 0 else 0
+    ok = (x.is_cuda and x.dtype == torch.bfloat16 and per and dh <= 256 and
+          (rope_dim == 0 or ((rope_dim // 2) % per == 0)))
+    if not ok:
+        return rmsnorm_rope_ref(x, norm_w, freqs, rope_dim, pos0, eps, one_plus)
+    xc = x.contiguous().view(B * T, H, dh)
+    y = torch.empty_like(xc)
+    _ext.ops().rmsnorm_rope(xc, norm_w, freqs.contiguous() if freqs is not None else None, y, T, rope_dim, pos0, eps, one_plus)
+    return y.view(B, T, H, dh)
+
+
+def _pow2_ceil(s):
+    return torch.exp2(torch.ceil(torch.log2(s)))
+
+
+def fp8_quant_1x128_ref(x, pow2: bool = False):
+    M, K = x.shape
+    xb = x.float().view(M, K // 128, 128)
+    sc = xb.abs().amax(-1).clamp_min(1e-12) / FP8_MAX
+    if pow2:
+        sc = _pow2_ceil(sc)
+    q = (xb / sc[..., None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).view(M, K)
+    return q, sc
+
+
+def fp8_quant_128x128_ref(w, pow2: bool = False):
+    R, C = w.shape
+    wb = w.float().view(R // 128, 128, C // 128, 128)
+    sc = wb.abs().amax(dim=(1, 3)).clamp_min(1e-12) / FP8_MAX
+    if pow2:
+        sc = _pow2_ceil(sc)
+    q = (wb / sc[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).view(R, C)
+    return q, sc
+
+
+def fp8_quant_1x128(x, pow2: bool = False):
+    """x (M,K) bf16 -> (q (M,K) e4m3, scales (M,K/128) fp32) with x ~= q * scale per 1x128 block."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16):
+        return fp8_quant_1x128_ref(x, pow2)
+    M, K = x.shape
+    q = torch.empty(M, K, device=x.device, dtype=torch.float8_e4m3fn)
+    sc = torch.empty(M, K // 128, device=x.device, dtype=torch.float32)
+    _ext.ops().fp8_quant(x.contiguous(), q, sc, False, pow2)
+    return q, sc
+
+
+def fp8_quant_128x128(w, pow2: bool = False):
+    """w (R,C) bf16 -> (q (R,C) e4m3, scales (R/128,C/128) fp32), one scale per 128x128 block."""
+    if not (w.is_cuda and w.dtype == torch.bfloat16):
+        return fp8_quant_128x128_ref(w, pow2)
+    R, C = w.shape
+    q = torch.empty(R, C, device=w.device, dtype=torch.float8_e4m3fn)
+    sc = torch.empty(R // 128, C // 128, device=w.device, dtype=torch.float32)
+    _ext.ops().fp8_quant(w.contiguous(), q, sc, True, pow2)
+    return q, sc

@@ -6,7 +6,27 @@ from __future__ import annotations
 import torch
 
 
+def _cuda_ok(logits, k, n_group=1):
+    E = logits.shape[-1]
+    return logits.is_cuda and E % 32 == 0 and E <= 512 and k <= 32 and (n_group <= 1 or (32 % n_group == 0 and E % n_group == 0))
+
+
+def router_cuda(mode: int, logits, bias, k, n_group=1, topk_group=1, scale=1.0, counts=None):
+    """Fused router kernel: (weights fp32 [M,k], ids int32 [M,k]); adds pair counts into ``counts`` when given."""
+    from .. import _ext
+    lf = logits.float().contiguous()
+    M = lf.shape[0]
+    w = torch.empty(M, k, device=lf.device, dtype=torch.float32)
+    ids = torch.empty(M, k, device=lf.device, dtype=torch.int32)
+    _ext.ops().router(mode, lf, None if bias is None else bias.float().contiguous(), k, n_group, topk_group, scale, w,
+                      ids, counts)
+    return w, ids
+
+
 def softmax_topk_router(logits: torch.Tensor, k: int):
+    if _cuda_ok(logits, k):
+        w, ids = router_cuda(0, logits, None, k)
+        return w, ids.long()
     probs = torch.softmax(logits.float(), dim=-1)
     w, idx = probs.topk(k, dim=-1)
     return w / w.sum(-1, keepdim=True), idx
@@ -15,6 +35,9 @@ def softmax_topk_router(logits: torch.Tensor, k: int):
 def deepseek_router_from_logits(logits: torch.Tensor, bias: torch.Tensor, k: int, n_group: int, topk_group: int,
                                 scale: float, norm_topk: bool = True):
     M, E = logits.shape
+    if _cuda_ok(logits, k, n_group) and norm_topk:
+        w, ids = router_cuda(1, logits, bias, k, n_group, topk_group, scale)
+        return w, ids.long()
     s = torch.sigmoid(logits.float())
     choice = s + bias.float()
     group_scores = choice.view(M, n_group, E // n_group).topk(2, dim=-1)[0].sum(-1)

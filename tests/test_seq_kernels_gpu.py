@@ -1,0 +1,103 @@
+"""Router, RMSNorm+RoPE, FP8 quantisation and Gated-DeltaNet decode kernels vs PyTorch references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("E,k", [(512, 10), (64, 2), (256, 8)])
+def test_softmax_router(cuda_device, E, k):
+    from jax_gpt_b200.ops import router as R
+    torch.manual_seed(0)
+    logits = torch.randn(777, E, device=cuda_device)
+    counts = torch.zeros(E, device=cuda_device, dtype=torch.int32)
+    w, ids = R.router_cuda(0, logits, None, k, counts=counts)
+    probs = torch.softmax(logits, -1)
+    rw, ri = probs.topk(k, -1)
+    rw = rw / rw.sum(-1, keepdim=True)
+    assert torch.equal(ids.long(), ri) and torch.allclose(w, rw, atol=1e-5)
+    assert torch.equal(counts.long(), torch.bincount(ri.reshape(-1), minlength=E))
+
+
+@pytest.mark.parametrize("E,k,G,kg", [(256, 8, 8, 4), (64, 6, 8, 3), (128, 4, 4, 2)])
+def test_deepseek_router(cuda_device, E, k, G, kg):
+    from jax_gpt_b200.ops import router as R
+    torch.manual_seed(1)
+    logits = torch.randn(500, E, device=cuda_device) * 2
+    bias = torch.randn(E, device=cuda_device) * 0.1
+    w, ids = R.router_cuda(1, logits, bias, k, G, kg, 2.5)
+    rw, ri = R.deepseek_router_from_logits(logits.cpu(), bias.cpu(), k, G, kg, 2.5)
+    # same expert set per token (order may differ) and the same weight per expert
+    a = torch.zeros(500, E).scatter_(1, ids.long().cpu(), w.cpu())
+    b = torch.zeros(500, E).scatter_(1, ri, rw)
+    assert torch.allclose(a, b, atol=1e-5)
+
+
+@pytest.mark.parametrize("dh,rope,norm", [(256, 64, True), (128, 32, True), (64, 64, False), (32, 8, True)])
+def test_rmsnorm_rope(cuda_device, dh, rope, norm):
+    from jax_gpt_b200.models.qwen35.primitives import precompute_rope_freqs
+    from jax_gpt_b200.ops import rope as RP
+    torch.manual_seed(2)
+    B, T, H = 2, 37, 3
+    x = torch.randn(B, T, H, dh, device=cuda_device).to(torch.bfloat16)
+    w = (torch.randn(dh, device=cuda_device) * 0.2).to(torch.bfloat16) if norm else None
+    fr = precompute_rope_freqs(rope, 64, 10000.0, device=cuda_device)
+    y = RP.rmsnorm_rope(x, w, fr, rope, pos0=5)
+    ref = RP.rmsnorm_rope_ref(x, w, fr, rope, pos0=5)
+    assert _rel(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("pow2", [False, True])
+def test_fp8_block_quant(cuda_device, pow2):
+    from jax_gpt_b200.ops import rope as RP
+    torch.manual_seed(3)
+    x = (torch.randn(300, 512, device=cuda_device) * torch.rand(300, 1, device=cuda_device) * 5).to(torch.bfloat16)
+    q, sc = RP.fp8_quant_1x128(x, pow2)
+    rq, rsc = RP.fp8_quant_1x128_ref(x, pow2)
+    assert torch.allclose(sc, rsc, rtol=1e-6)
+    deq = q.float().view(300, 4, 128) * sc[..., None]
+    assert ((deq.view(300, 512) - x.float()).abs().max() / x.float().abs().max()) < 0.07
+    assert (q.float() - rq.float()).abs().max() <= 32  # at most one e4m3 step apart near the top of the range
+    w = torch.randn(256, 384, device=cuda_device).to(torch.bfloat16)
+    qw, sw = RP.fp8_quant_128x128(w, pow2)
+    _, rsw = RP.fp8_quant_128x128_ref(w, pow2)
+    assert torch.allclose(sw, rsw, rtol=1e-6)
+    deq = (qw.float().view(2, 128, 3, 128) * sw[:, None, :, None]).view(256, 384)
+    assert _rel(deq, w) < 0.05
+    if pow2:
+        assert torch.equal(torch.exp2(torch.round(torch.log2(sw))), sw)
+
+
+def test_gdn_decode_step(cuda_device):
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.qwen35 import deltanet as DN
+    torch.manual_seed(4)
+    B, Hqk, Hv, dk, dv, Kc = 3, 2, 4, 128, 128, 4
+    Kd, Vd = Hqk * dk, Hv * dv
+    C = 2 * Kd + Vd
+    bf = lambda *s: (torch.randn(*s, device=cuda_device)).to(torch.bfloat16)
+    mixed, z, bp, ap = bf(B, C), bf(B, Vd), bf(B, Hv), bf(B, Hv)
+    conv_w = (torch.randn(C, Kc, device=cuda_device) * 0.5).to(torch.bfloat16)
+    A_log = torch.log(torch.rand(Hv, device=cuda_device) * 4 + 0.1).to(torch.bfloat16)
+    dt_bias = torch.ones(Hv, device=cuda_device, dtype=torch.bfloat16)
+    norm_w = (torch.randn(dv, device=cuda_device) * 0.3 + 1).to(torch.bfloat16)
+    conv_state = torch.randn(B, C, Kc, device=cuda_device)
+    state = torch.randn(B, Hv, dk, dv, device=cuda_device) * 0.1
+    # reference (fp32 torch)
+    cs_ref, st_ref = conv_state.clone(), state.clone()
+    mx, cs_ref = DN.causal_conv1d_update(mixed.float(), cs_ref, conv_w.float())
+    q = DN._l2_norm(mx[:, :Kd].reshape(B, Hqk, dk)) * dk ** -0.5
+    k = DN._l2_norm(mx[:, Kd:2 * Kd].reshape(B, Hqk, dk))
+    v = mx[:, 2 * Kd:].reshape(B, Hv, dv)
+    beta, g = DN._gates(bp.float(), ap.float(), {"A_log": A_log.float(), "dt_bias": dt_bias.float()})
+    o, st_ref = DN.gated_delta_step(q.repeat_interleave(Hv // Hqk, 1), k.repeat_interleave(Hv // Hqk, 1), v, beta, g, st_ref)
+    o = DN._gated_rms_norm(o.reshape(B * Hv, dv), z.float().reshape(B * Hv, dv), norm_w.float()).reshape(B, Vd)
+    out = torch.empty(B, Vd, device=cuda_device, dtype=torch.bfloat16)
+    _ext.ops().gdn_decode_step(mixed, z, bp, ap, conv_state, conv_w, A_log, dt_bias, norm_w, state, out, Hqk, Hv, dk, dv, 1e-6)
+    assert _rel(out, o) < 1e-2
+    assert _rel(state, st_ref) < 1e-4 and _rel(conv_state, cs_ref) < 1e-6
