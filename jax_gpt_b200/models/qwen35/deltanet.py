@@ -77,6 +77,18 @@ def deltanet_recurrent_step(x, params, state, conv_state, n_qk: int, n_v: int, d
     B = x.shape[0]
     key_dim, rep = n_qk * dk, n_v // n_qk
     mixed, z, b, a = _project(x, params, n_qk, n_v, dk, dv)
+    if (x.is_cuda and x.dtype == torch.bfloat16 and state.dtype == torch.float32 and conv_state.dtype == torch.float32
+            and max(dk, dv) <= 256 and not isinstance(params["out_proj"], dict)):
+        # fused CUDA step: conv window update, gates, delta rule, gated RMSNorm; states updated in place
+        from ... import _ext
+        out = torch.empty(B, n_v * dv, device=x.device, dtype=torch.bfloat16)
+        state_c, conv_c = state.contiguous(), conv_state.contiguous()
+        bf = lambda t: t.to(torch.bfloat16).contiguous()
+        _ext.ops().gdn_decode_step(mixed[:, 0].contiguous(), z[:, 0].contiguous(), b[:, 0].contiguous(),
+                                   a[:, 0].contiguous(), conv_c, bf(params["conv_weight"]), bf(params["A_log"]),
+                                   bf(params["dt_bias"]), bf(params["norm_weight"]), state_c, out, n_qk, n_v, dk, dv, 1e-6)
+        y = matmul_maybe_fp8(out, params["out_proj"])
+        return y[:, None, :], state_c, conv_c
     mixed, new_conv = causal_conv1d_update(mixed[:, 0], conv_state, params["conv_weight"])
     q = mixed[:, :key_dim].reshape(B, n_qk, dk).float()
     k = mixed[:, key_dim:2 * key_dim].reshape(B, n_qk, dk).float()

@@ -22,12 +22,18 @@ def gqa_attention(x, params, n_q_heads: int, n_kv_heads: int, head_dim: int, rop
     q, gate = qg[..., :head_dim], qg[..., head_dim:]
     k = matmul_maybe_fp8(x, params["k_proj"]).reshape(B, T, n_kv_heads, head_dim)
     v = matmul_maybe_fp8(x, params["v_proj"]).reshape(B, T, n_kv_heads, head_dim)
-    q = rms_norm(q.contiguous(), params["q_norm"])
-    k = rms_norm(k.contiguous(), params["k_norm"])
     pos = int(cache_pos) if cache_pos is not None else 0
-    fr = rope_freqs[pos:pos + T]
-    q = apply_rotary_emb(q, fr, rope_dim)
-    k = apply_rotary_emb(k, fr, rope_dim)
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        # per-head RMSNorm(1 + w) and partial rotary in one kernel
+        from ...ops.rope import rmsnorm_rope
+        q = rmsnorm_rope(q, params["q_norm"], rope_freqs, rope_dim, pos)
+        k = rmsnorm_rope(k, params["k_norm"], rope_freqs, rope_dim, pos)
+    else:
+        q = rms_norm(q.contiguous(), params["q_norm"])
+        k = rms_norm(k.contiguous(), params["k_norm"])
+        fr = rope_freqs[pos:pos + T]
+        q = apply_rotary_emb(q, fr, rope_dim)
+        k = apply_rotary_emb(k, fr, rope_dim)
     if cache_k is not None:
         cache_k[:, :, pos:pos + T] = k.permute(0, 2, 1, 3).to(cache_k.dtype)
         cache_v[:, :, pos:pos + T] = v.permute(0, 2, 1, 3).to(cache_v.dtype)

@@ -1,0 +1,104 @@
+"""Pipeline schedule and failure detection on CPU (gloo) ranks."""
+import os
+import tempfile
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from jax_gpt_b200.parallel.pipeline import one_f_one_b_order, split_layers
+
+
+def test_schedule_shapes():
+    assert [list(r) for r in split_layers(10, 4)] == [[0, 1, 2], [3, 4, 5], [6, 7], [8, 9]]
+    for S, M in [(4, 8), (2, 3), (3, 1)]:
+        for s in range(S):
+            order = one_f_one_b_order(s, S, M)
+            assert [i for k, i in order if k == "F"] == list(range(M)) and [i for k, i in order if k == "B"] == list(range(M))
+            done = set()
+            live = 0
+            for k, i in order:      # a backward never precedes its forward; at most S - s in flight
+                if k == "F":
+                    done.add(i); live += 1
+                else:
+                    assert i in done; live -= 1
+                assert live <= S - s
+    assert one_f_one_b_order(0, 4, 8)[:4] == [("F", 0), ("F", 1), ("F", 2), ("F", 3)]
+
+
+def _pp_worker(rank, world, path):
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world)
+    from jax_gpt_b200.parallel.pipeline import PipelineStage
+    torch.manual_seed(0)
+    D, n_layers, n_micro, B = 16, 4, 4, 3
+    Ws = [torch.randn(D, D) * 0.3 for _ in range(n_layers)]     # same weights on every rank
+    xs = [torch.randn(B, D) for _ in range(n_micro)]
+    ys = [torch.randn(B, D) for _ in range(n_micro)]
+    mine = split_layers(n_layers, world)[rank]
+    params = [Ws[i].clone().requires_grad_(True) for i in mine]
+
+    def fwd(inp, i):
+        x, tgt = (inp, None)
+        if rank == world - 1:
+            x, tgt = inp if world > 1 else (inp[0], inp[1])
+        for w in params:
+            x = torch.tanh(x @ w)
+        return ((x - tgt) ** 2).mean() if tgt is not None else x
+
+    stage = PipelineStage(fwd, params, (B, D), torch.float32)
+    inputs = xs if rank == 0 else (ys if rank == world - 1 else [None] * n_micro)
+    loss = stage.run(inputs)
+    # single-process reference
+    ref_params = [w.clone().requires_grad_(True) for w in Ws]
+    tot = 0
+    for x, y in zip(xs, ys):
+        h = x
+        for w in ref_params:
+            h = torch.tanh(h @ w)
+        tot = tot + ((h - y) ** 2).mean() / n_micro
+    tot.backward()
+    for j, i in enumerate(mine):
+        assert torch.allclose(params[j].grad, ref_params[i].grad, atol=1e-6), (rank, i)
+    if rank == world - 1:
+        assert abs(float(loss) - float(tot)) < 1e-6
+    dist.destroy_process_group()
+
+
+def test_pipeline_1f1b_matches_single_process():
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_pp_worker, args=(2, os.path.join(d, "rdv")), nprocs=2, join=True)
+
+
+def _wd_worker(rank, world, path, result_path):
+    from jax_gpt_b200.utils.watchdog import PeerFailure, Watchdog
+    store = dist.FileStore(path, world)
+    wd = Watchdog(store, rank, world, interval=0.1, timeout=1.0).start()
+    if rank == 1:
+        time.sleep(0.5)
+        os._exit(0)          # this rank dies between steps, without saying goodbye
+    t0 = time.time()
+    seen = None
+    while time.time() - t0 < 10:
+        try:
+            wd.check()
+        except PeerFailure as e:
+            seen = e.dead
+            break
+        time.sleep(0.05)
+    with open(f"{result_path}.{rank}", "w") as f:
+        f.write(repr(seen))
+    wd.stop()
+
+
+def test_watchdog_detects_a_dead_rank():
+    with tempfile.TemporaryDirectory() as d:
+        ctx = mp.spawn(_wd_worker, args=(3, os.path.join(d, "store"), os.path.join(d, "res")), nprocs=3, join=False)
+        t0 = time.time()
+        while time.time() - t0 < 30 and not all(os.path.exists(os.path.join(d, f"res.{r}")) for r in (0, 2)):
+            time.sleep(0.1)
+        for r in (0, 2):
+            assert open(os.path.join(d, f"res.{r}")).read() == "[1]"
+        for p in ctx.processes:
+            p.join(timeout=5)
