@@ -83,3 +83,38 @@ def fp8_quant_128x128(w, pow2: bool = False):
     sc = torch.empty(R // 128, C // 128, device=w.device, dtype=torch.float32)
     _ext.ops().fp8_quant(w.contiguous(), q, sc, True, pow2)
     return q, sc
+
+
+def fp8_gemm_ref(a_q, a_s, b_q, b_s):
+    """fp32 reference of the block-scaled product: de-quantise both operands, multiply."""
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    a = a_q.float().view(M, K // 128, 128) * a_s[..., None]
+    bs = b_s.repeat_interleave(128, dim=0)[:N]
+    b = b_q.float().view(N, K // 128, 128) * bs[..., None]
+    return a.view(M, K) @ b.view(N, K).t()
+
+
+def fp8_gemm(a_q, a_s, b_q, b_s, out_dtype=torch.bfloat16):
+    """a_q [M,K] e4m3 with 1x128 scales, b_q [N,K] e4m3 with 128x128 scales -> [M,N]."""
+    if not a_q.is_cuda:
+        return fp8_gemm_ref(a_q, a_s, b_q, b_s).to(out_dtype)
+    out = torch.empty(a_q.shape[0], b_q.shape[0], device=a_q.device, dtype=out_dtype)
+    _ext.ops().gemm_fp8(a_q, a_s, b_q, b_s, out)
+    return out
+
+
+class Fp8Linear:
+    """y = x @ W with W (in, out) held as block-scaled FP8: the weight is quantised once
+    (transposed to [out, in] so K is contiguous), activations are quantised per call."""
+
+    def __init__(self, w: torch.Tensor, pow2: bool = False):
+        self.in_features, self.out_features = w.shape
+        self.w_q, self.w_s = fp8_quant_128x128(w.t().contiguous().to(torch.bfloat16), pow2)
+        self.pow2 = pow2
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1]).to(torch.bfloat16).contiguous()
+        xq, xs = fp8_quant_1x128(x2, self.pow2)
+        return fp8_gemm(xq, xs, self.w_q, self.w_s).reshape(*shp[:-1], self.out_features)

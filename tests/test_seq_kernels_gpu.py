@@ -101,3 +101,21 @@ def test_gdn_decode_step(cuda_device):
     _ext.ops().gdn_decode_step(mixed, z, bp, ap, conv_state, conv_w, A_log, dt_bias, norm_w, state, out, Hqk, Hv, dk, dv, 1e-6)
     assert _rel(out, o) < 1e-2
     assert _rel(state, st_ref) < 1e-4 and _rel(conv_state, cs_ref) < 1e-6
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 256, 512), (1024, 2048, 7168), (4096, 4096, 2048)])
+def test_fp8_blockscaled_gemm(cuda_device, M, N, K):
+    from jax_gpt_b200.ops import rope as RP
+    torch.manual_seed(5)
+    x = (torch.randn(M, K, device=cuda_device) * (torch.rand(M, 1, device=cuda_device) * 3 + 0.1)).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=cuda_device) * 0.05).to(torch.bfloat16)
+    xq, xs = RP.fp8_quant_1x128(x)
+    wq, ws = RP.fp8_quant_128x128(w) if N % 128 == 0 else RP.fp8_quant_128x128_ref(torch.nn.functional.pad(w, (0, 0, 0, (-N) % 128)))
+    if N % 128:
+        wq = wq[:N].contiguous()
+    out = RP.fp8_gemm(xq, xs, wq, ws)
+    ref = RP.fp8_gemm_ref(xq, xs, wq, ws)
+    assert _rel(out, ref) < 1e-2                      # kernel vs exact arithmetic on the same quantised operands
+    assert _rel(out, x.float() @ w.float().t()) < 6e-2   # and the quantisation error itself stays small
+    lin = RP.Fp8Linear(w.t().contiguous())
+    assert _rel(lin(x), x.float() @ w.float().t()) < 6e-2
