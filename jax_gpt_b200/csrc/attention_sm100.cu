@@ -40,17 +40,20 @@ struct FwdArgs {
   int* status;
 };
 
-template <int D>
+// D: width of q and k heads; DV: width of v heads (MLA prefill uses 192 / 128).
+template <int D, int DV>
 struct FwdCfg {
-  static constexpr int kTile = 128 * D * 2;      // bytes of a 128 x D bf16 tile
+  static constexpr int kQTile = 128 * D * 2;     // bytes of a 128 x D bf16 tile (Q and K)
+  static constexpr int kVTile = 128 * DV * 2;
+  static constexpr int kStageBytes = kQTile + kVTile;
   static constexpr int kPBytes = 128 * 128 * 2;
-  static constexpr int kStages = 2;
-  static constexpr int kOffK = kTile;
-  static constexpr int kOffP = kTile + kStages * 2 * kTile;
+  static constexpr int kStages = (D + DV <= 256) ? 2 : 1;
+  static constexpr int kOffK = kQTile;
+  static constexpr int kOffP = kQTile + kStages * kStageBytes;
   static constexpr int kOffXchg = kOffP + kPBytes;  // bf16 [2][128] running-max exchange
   static constexpr int kOffBar = kOffXchg + 512;
   static constexpr int kSmem = kOffBar + 128;       // D = 64: 115328 B, two CTAs per SM
-  static constexpr int kTmemCols = 256;
+  static constexpr int kTmemCols = (128 + DV <= 256) ? 256 : 512;  // S [0,128), O [128, 128+DV)
 };
 
 struct FwdBars {
@@ -77,11 +80,11 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, ui
   for (int h = 0; h < D / 64; ++h) tma_load_2d(dst + h * 16384, m, bar, col0 + h * 64, row0);
 }
 
-template <int D>
+template <int D, int DV>
 __global__ void __launch_bounds__(kThreads, (D == 64) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ FwdArgs a) {
-  using C = FwdCfg<D>;
+  using C = FwdCfg<D, DV>;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) report_status(a.status, kBadArgument, 1, 0, 0);
@@ -123,37 +126,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(&bars->q_full, C::kTile);
+      mbar_arrive_expect_tx(&bars->q_full, C::kQTile);
       load_tile<D>(sQ, &tq, &bars->q_full, h * D, row0);
       for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int s = j % C::kStages;
+        const uint32_t ph = (j / C::kStages) & 1;
         if (!mbar_wait(&bars->kv_empty[s], ph ^ 1, abort_flag)) {
           report_status(a.status, kWaitEmptyTimeout, 100, blockIdx.x, j);
           break;
         }
-        uint8_t* sK = smem + C::kOffK + s * 2 * C::kTile;
-        mbar_arrive_expect_tx(&bars->kv_full[s], 2 * C::kTile);
+        uint8_t* sK = smem + C::kOffK + s * C::kStageBytes;
+        mbar_arrive_expect_tx(&bars->kv_full[s], C::kStageBytes);
         load_tile<D>(sK, &tk, &bars->kv_full[s], hkv * D, b * a.T + j * 128);
-        load_tile<D>(sK + C::kTile, &tv, &bars->kv_full[s], hkv * D, b * a.T + j * 128);
+        load_tile<DV>(sK + C::kQTile, &tv, &bars->kv_full[s], hkv * DV, b * a.T + j * 128);
       }
     }
   } else if (warp == 1) {
     constexpr uint32_t idesc_s = make_idesc(128, 128, 0, 0, 1);
-    constexpr uint32_t idesc_o = make_idesc(128, D, 0, 1, 1);
+    constexpr uint32_t idesc_o = make_idesc(128, DV, 0, 1, 1);
     bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
     if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 101, blockIdx.x, 0);
     for (int j = 0; j < n_kv && ok; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
+      const int s = j % C::kStages;
+      const uint32_t ph = (j / C::kStages) & 1;
       if (!mbar_wait(&bars->kv_full[s], ph, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitFullTimeout, 102, blockIdx.x, j);
         break;
       }
       tc_fence_after();
       const uint32_t aQ = smem_u32(sQ);
-      const uint32_t aK = smem_u32(smem + C::kOffK + s * 2 * C::kTile);
-      const uint32_t aV = aK + C::kTile;
+      const uint32_t aK = smem_u32(smem + C::kOffK + s * C::kStageBytes);
+      const uint32_t aV = aK + C::kQTile;
       if (lane == 0) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -192,7 +195,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int qpos = q_blk * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     __nv_bfloat16* xchg = reinterpret_cast<__nv_bfloat16*>(smem + C::kOffXchg);  // [2][128]
-    constexpr int DH = D / 2;
+    constexpr int DH = DV / 2;
     float m = -INFINITY, l = 0.f;
     float o[DH];
 #pragma unroll
@@ -287,7 +290,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
     if (ok && qpos < a.T) {
       const float inv = (l > 0.f) ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = a.out + static_cast<int64_t>(b * a.T + qpos) * a.ldo + h * D + half * DH;
+      __nv_bfloat16* orow = a.out + static_cast<int64_t>(b * a.T + qpos) * a.ldo + h * DV + half * DH;
 #pragma unroll
       for (int i = 0; i < DH; i += 8) {
         uint4 pk = make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
@@ -664,17 +667,17 @@ cudaError_t make_map(CUtensorMap* m, const __nv_bfloat16* p, int64_t ld, int row
   return encode_tma_2d(m, p, 2, cols, rows, ld * 2, 64, 128);
 }
 
-template <int D>
+template <int D, int DV>
 cudaError_t fwd_launch(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* out, int64_t ldo, float* lse,
                        int* status, cudaStream_t stream) {
-  using C = FwdCfg<D>;
+  using C = FwdCfg<D, DV>;
   CUtensorMap tq, tk, tv;
   const int rows = s.B * s.T;
   cudaError_t e;
   if ((e = make_map(&tq, t.q, t.ldq, rows, s.H * D)) != cudaSuccess) return e;
   if ((e = make_map(&tk, t.k, t.ldk, rows, s.Hkv * D)) != cudaSuccess) return e;
-  if ((e = make_map(&tv, t.v, t.ldv, rows, s.Hkv * D)) != cudaSuccess) return e;
-  auto kernel = attn_fwd_kernel<D>;
+  if ((e = make_map(&tv, t.v, t.ldv, rows, s.Hkv * DV)) != cudaSuccess) return e;
+  auto kernel = attn_fwd_kernel<D, DV>;
   static bool configured = false;
   if (!configured) {
     if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem)) != cudaSuccess)
@@ -724,8 +727,11 @@ cudaError_t bwd_launch(const AttnTensors& t, const AttnShape& s, const __nv_bflo
 cudaError_t launch_attn_fwd(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* out, int64_t ldo, float* lse,
                             int* status, cudaStream_t stream) {
   if (s.H % s.Hkv != 0) return cudaErrorInvalidValue;
-  if (s.D == 64) return fwd_launch<64>(t, s, out, ldo, lse, status, stream);
-  if (s.D == 128) return fwd_launch<128>(t, s, out, ldo, lse, status, stream);
+  const int dv = s.Dv > 0 ? s.Dv : s.D;
+  if (s.D == 64 && dv == 64) return fwd_launch<64, 64>(t, s, out, ldo, lse, status, stream);
+  if (s.D == 128 && dv == 128) return fwd_launch<128, 128>(t, s, out, ldo, lse, status, stream);
+  if (s.D == 256 && dv == 256) return fwd_launch<256, 256>(t, s, out, ldo, lse, status, stream);
+  if (s.D == 192 && dv == 128) return fwd_launch<192, 128>(t, s, out, ldo, lse, status, stream);
   return cudaErrorInvalidValue;
 }
 

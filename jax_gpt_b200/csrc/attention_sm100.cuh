@@ -16,9 +16,10 @@ struct AttnTensors {
 };
 
 struct AttnShape {
-  int B, T, H, Hkv, D;  // D in {64, 128}; H % Hkv == 0
+  int B, T, H, Hkv, D;  // forward: D in {64, 128, 256} or (D, Dv) = (192, 128); backward: D in {64, 128}
   float scale;          // softmax scale (1/sqrt(D) by default)
   int causal;
+  int Dv;               // v head width when it differs from D (forward only: 192/128 for MLA); 0 = D
 };
 
 // out [B*T, ldo] bf16 with head h at columns [h*D, +D); lse [B, H, T] fp32 holds

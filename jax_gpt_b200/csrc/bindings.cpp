@@ -244,7 +244,7 @@ void adamw(Tensor p, Tensor g, Tensor m, Tensor v, c10::optional<Tensor> p_bf16,
 
 // q/k/v: 2-D bf16 views [B*T, H*D] (possibly column slices of one fused buffer).
 void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Tensor lse, int64_t B, int64_t T,
-              int64_t H, int64_t Hkv, int64_t D, double scale, bool causal) {
+              int64_t H, int64_t Hkv, int64_t D, double scale, bool causal, int64_t Dv) {
   c10::cuda::CUDAGuard guard(q.device());
   check_bf16_2d(q, "q");
   check_bf16_2d(k, "k");
@@ -252,7 +252,7 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Ten
   check_bf16_2d(out, "out");
   b200::AttnTensors t{bf16_ptr(q), bf16_ptr(k), bf16_ptr(v), q.stride(0), k.stride(0), v.stride(0)};
   b200::AttnShape s{static_cast<int>(B), static_cast<int>(T), static_cast<int>(H), static_cast<int>(Hkv),
-                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0};
+                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0, static_cast<int>(Dv)};
   B200_CHECK_CUDA(b200::launch_attn_fwd(t, s, bf16_mut(out), out.stride(0), lse.data_ptr<float>(), status_ptr(q),
                                         cur_stream()));
 }
@@ -271,7 +271,7 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   TORCH_CHECK(dq_accum.scalar_type() == at::kFloat && dq_accum.is_contiguous(), "attn_bwd: dq_accum fp32 contiguous");
   b200::AttnTensors t{bf16_ptr(q), bf16_ptr(k), bf16_ptr(v), q.stride(0), k.stride(0), v.stride(0)};
   b200::AttnShape s{static_cast<int>(B), static_cast<int>(T), static_cast<int>(H), static_cast<int>(Hkv),
-                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0};
+                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0, 0};
   B200_CHECK_CUDA(b200::launch_attn_bwd(t, s, bf16_ptr(out), out.stride(0), bf16_ptr(dout), dout.stride(0),
                                         lse.data_ptr<float>(), delta.data_ptr<float>(), dq_accum.data_ptr<float>(),
                                         bf16_mut(dk), dk.stride(0), bf16_mut(dv), dv.stride(0), status_ptr(q),
@@ -325,7 +325,7 @@ TORCH_LIBRARY(b200, m) {
       &adamw);
   m.def(
       "attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, int B, int T, int H, int Hkv, int D, "
-      "float scale, bool causal) -> ()",
+      "float scale, bool causal, int Dv) -> ()",
       &attn_fwd);
   m.def(
       "attn_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor dout, Tensor lse, Tensor(a!) delta, Tensor(b!) "

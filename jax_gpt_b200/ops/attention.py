@@ -40,13 +40,13 @@ def _as2d(t):
 def attn_fwd(q, k, v, causal=True, scale=None, out=None, lse=None):
     """Raw CUDA forward. Returns (out [B,T,H,D] bf16, lse [B,H,T] fp32 in log2 units)."""
     B, T, H, D = q.shape
-    Hkv = k.shape[2]
+    Hkv, Dv = k.shape[2], v.shape[3]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if out is None:
-        out = torch.empty(B, T, H, D, device=q.device, dtype=torch.bfloat16)
+        out = torch.empty(B, T, H, Dv, device=q.device, dtype=torch.bfloat16)
     if lse is None:
         lse = torch.empty(B, H, T, device=q.device, dtype=torch.float32)
-    _ext.ops().attn_fwd(_as2d(q), _as2d(k), _as2d(v), _as2d(out), lse, B, T, H, Hkv, D, scale, causal)
+    _ext.ops().attn_fwd(_as2d(q), _as2d(k), _as2d(v), _as2d(out), lse, B, T, H, Hkv, D, scale, causal, Dv)
     return out, lse
 
 
@@ -90,16 +90,29 @@ def supports_cuda_kernel(q, k) -> bool:
     return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[1] == k.shape[1])
 
 
+def supports_cuda_forward(q, k, v) -> bool:
+    d, dv = q.shape[-1], v.shape[-1]
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[1] == k.shape[1] and
+            ((d == dv and d in (64, 128, 256)) or (d == 192 and dv == 128)))
+
+
 def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
-    """Softmax attention over [B,T,H,D] tensors (GQA when k/v have fewer heads)."""
-    if supports_cuda_kernel(q, k):
+    """Softmax attention over [B,T,H,D] tensors (GQA when k/v have fewer heads). Head widths
+    64 / 128 run forward and backward on the tcgen05 kernels; 256 and the MLA shape (192 / 128)
+    run the forward kernel when no gradient is needed."""
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if supports_cuda_kernel(q, k) and v.shape[-1] == q.shape[-1]:
         return _AttnFn.apply(q, k, v, causal, scale)
+    if supports_cuda_forward(q, k, v) and not needs_grad:
+        return attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale)[0]
     return attention_ref(q, k, v, causal, scale)
 
 
 def mla_attention(q, k, v, scale: float):
     """Causal attention with different q/k and v head widths (MLA prefill: 192 / 128).
     q,k (B,T,H,dqk); v (B,T,H,dv)."""
+    if supports_cuda_forward(q, k, v) and not (torch.is_grad_enabled() and q.requires_grad):
+        return attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), True, scale)[0]
     B, T, H, dqk = q.shape
     qf, kf, vf = [t.float().permute(0, 2, 1, 3) for t in (q, k, v)]
     s = (qf @ kf.transpose(-1, -2)) * scale

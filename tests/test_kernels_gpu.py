@@ -183,3 +183,21 @@ def test_attention_fused_qkv_views(cuda_device):
     out, _ = A.attn_fwd(q, k, v, causal=True)
     ref = A.attention_ref(q, k, v, causal=True)
     assert _rel_err(out, ref) < 2e-2
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D,Dv", [(1, 256, 4, 1, 256, 256), (2, 384, 4, 4, 192, 128), (1, 200, 2, 2, 192, 128)])
+def test_attention_forward_wide_heads(cuda_device, B, T, H, Hkv, D, Dv):
+    """Forward-only kernels: gated attention with 256-wide heads and the MLA prefill shape 192 / 128."""
+    from jax_gpt_b200.ops import attention as A
+    torch.manual_seed(8)
+    q = torch.randn(B, T, H, D, device=cuda_device).to(torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, device=cuda_device).to(torch.bfloat16)
+    v = torch.randn(B, T, Hkv, Dv, device=cuda_device).to(torch.bfloat16)
+    with torch.no_grad():
+        out = A.attention(q, k, v, causal=True, scale=D ** -0.5) if D == Dv else A.mla_attention(q, k, v, D ** -0.5)
+    kk = k.float().repeat_interleave(H // Hkv, 2)
+    vv = v.float().repeat_interleave(H // Hkv, 2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), kk) * D ** -0.5
+    s = s.masked_fill(~torch.ones(T, T, dtype=torch.bool, device=cuda_device).tril(), float("-inf"))
+    ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), vv)
+    assert out.shape == (B, T, H, Dv) and _rel_err(out, ref) < 2e-2

@@ -1,0 +1,62 @@
+"""Qwen3.5 and DeepSeek-V3 models in bf16 on a B200 (CUDA kernels engaged) vs fp32 CPU math."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _to(tree, device, dtype):
+    if isinstance(tree, dict):
+        return {k: _to(v, device, dtype) for k, v in tree.items()}
+    return tree.to(device=device, dtype=dtype if tree.is_floating_point() else tree.dtype)
+
+
+def test_qwen35_forward_and_decode_on_gpu(cuda_device):
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.qwen35 import Qwen35Config, forward, init_cache, init_params
+    cfg = Qwen35Config(d_model=256, vocab_size=512, n_layers=4, max_position_embeddings=256, gqa_n_q_heads=4,
+                       gqa_n_kv_heads=2, gqa_head_dim=64, delta_n_qk_heads=2, delta_n_v_heads=4, delta_qk_head_dim=64,
+                       delta_v_head_dim=64, delta_chunk_size=16, n_routed_experts=32, n_experts_per_token=4,
+                       moe_intermediate_size=128, shared_expert_intermediate_size=128)
+    p32 = init_params(cfg, 0)
+    # non-trivial norm weights so the fused norm + rotary kernel is exercised
+    p32["groups"]["gqa_layer"]["attn"]["q_norm"] = torch.randn_like(p32["groups"]["gqa_layer"]["attn"]["q_norm"]) * 0.1
+    tok = torch.randint(0, cfg.vocab_size, (2, 33))
+    with torch.no_grad():
+        ref, _ = forward(p32, tok, cfg)
+        pg = _to(p32, cuda_device, torch.bfloat16)
+        out, _ = forward(pg, tok.to(cuda_device), cfg)
+        assert (out.float().cpu() - ref).abs().max() < 0.15 and torch.isfinite(out).all()
+        # prefill + decode steps with fp32 states: the fused DeltaNet decode kernel runs here
+        cache = init_cache(cfg, 2, 64, dtype=torch.float32, device=cuda_device)
+        cache.gqa_k, cache.gqa_v = cache.gqa_k.to(torch.bfloat16), cache.gqa_v.to(torch.bfloat16)
+        l1, cache = forward(pg, tok[:, :30].to(cuda_device), cfg, cache=cache)
+        steps = [l1]
+        for t in range(30, 33):
+            lt, cache = forward(pg, tok[:, t:t + 1].to(cuda_device), cfg, cache=cache, is_decode=True)
+            steps.append(lt)
+        got = torch.cat(steps, 1).float().cpu()
+        assert (got - ref).abs().max() < 0.2
+        assert (got[:, -1].argmax(-1) == ref[:, -1].argmax(-1)).float().mean() >= 0.5
+    _ext.check_status(cuda_device)
+
+
+def test_deepseek_v3_forward_on_gpu(cuda_device):
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.deepseek_v3 import DeepSeekV3Config, forward, init_params, make_cache
+    cfg = DeepSeekV3Config(d_model=256, vocab_size=512, n_layers=2, first_k_dense=1, dense_intermediate_size=512,
+                           max_position_embeddings=512, n_heads=4, q_lora_rank=128, kv_lora_rank=128,
+                           qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=32,
+                           n_experts_per_token=4, n_group=4, topk_group=2, moe_intermediate_size=128, page_size=64)
+    p32 = init_params(cfg, 0)
+    tok = torch.randint(0, cfg.vocab_size, (2, 160))
+    with torch.no_grad():
+        ref = forward(p32, tok, cfg)
+        pg = _to(p32, cuda_device, torch.bfloat16)
+        out = forward(pg, tok.to(cuda_device), cfg)          # MLA prefill on the 192 / 128 kernel
+        assert (out.float().cpu() - ref).abs().max() < 0.15
+        cache = make_cache(cfg, 16, 2, 8, torch.bfloat16, cuda_device)
+        l1 = forward(pg, tok[:, :158].to(cuda_device), cfg, cache, [0, 1])
+        l2 = forward(pg, tok[:, 158:159].to(cuda_device), cfg, cache, [0, 1], is_decode=True)
+        assert (l2[:, 0].float().cpu() - ref[:, 158]).abs().max() < 0.2
+    _ext.check_status(cuda_device)
