@@ -129,6 +129,31 @@ void gemm_gathered_a(std::vector<int64_t> a_ptrs, int64_t rows_per_src, int64_t 
                                                     b_mn_major ? 1 : 0, g, cur_stream()));
 }
 
+// x [M,K] @ W [K,N] where W is row-sharded over the ranks: shard_ptrs[s] -> [K / n, N] bf16.
+void gemm_sharded_b(const Tensor& a, std::vector<int64_t> shard_ptrs, int64_t first_src, int64_t N, Tensor out,
+                    const c10::optional<Tensor>& bias) {
+  c10::cuda::CUDAGuard guard(a.device());
+  check_bf16_2d(a, "a");
+  const int n = static_cast<int>(shard_ptrs.size());
+  TORCH_CHECK(n >= 1 && n <= b200::kMaxPeers, "gemm_sharded_b: 1..8 shards");
+  GemmArgs g{};
+  g.M = static_cast<int>(a.size(0));
+  g.K = static_cast<int>(a.size(1));
+  g.N = static_cast<int>(N);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == g.M && out.size(1) == N, "gemm_sharded_b: bad out");
+  g.out = out.data_ptr();
+  g.ldo = out.stride(0);
+  g.out_mode = b200::kOutBf16;
+  g.bias = bf16_opt(bias);
+  g.alpha = 1.f;
+  g.split_k = 1;
+  g.status = status_ptr(a);
+  const __nv_bfloat16* srcs[b200::kMaxPeers];
+  for (int i = 0; i < n; ++i) srcs[i] = reinterpret_cast<const __nv_bfloat16*>(shard_ptrs[i]);
+  B200_CHECK_CUDA(b200::launch_gemm_bf16_sharded_b(bf16_ptr(a), a.stride(0), srcs, n, static_cast<int>(first_src), N, g,
+                                                   cur_stream()));
+}
+
 void gemm_reduce_scatter(const Tensor& a, const Tensor& b, bool b_mn_major, std::vector<int64_t> out_ptrs,
                          int64_t rows_per_peer, int64_t ldo) {
   c10::cuda::CUDAGuard guard(a.device());
@@ -303,6 +328,8 @@ TORCH_LIBRARY(b200, m) {
       "gemm_gathered_a(int[] a_ptrs, int rows_per_src, int first_src, int K, int lda, Tensor b, bool b_mn_major, "
       "Tensor(a!) out, Tensor? bias) -> ()",
       &gemm_gathered_a);
+  m.def("gemm_sharded_b(Tensor a, int[] shard_ptrs, int first_src, int N, Tensor(a!) out, Tensor? bias) -> ()",
+        &gemm_sharded_b);
   m.def("gemm_reduce_scatter(Tensor a, Tensor b, bool b_mn_major, int[] out_ptrs, int rows_per_peer, int ldo) -> ()",
         &gemm_reduce_scatter);
   m.def(

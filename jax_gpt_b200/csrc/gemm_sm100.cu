@@ -35,6 +35,11 @@ struct GatherInfo {
   int n_src;           // number of A sources (1 = plain GEMM)
   int blocks_per_src;  // M-blocks per source
   int first_src;       // source visited first
+  // B (an MN-major weight [K, N]) split by rows across b_n_src sources of b_kb_per_src K-blocks
+  // each (FSDP parameter shards): K-blocks are visited starting with source b_first_src.
+  int b_n_src;
+  int b_kb_per_src;
+  int b_first_src;
 };
 
 template <int BN>
@@ -58,7 +63,7 @@ struct Barriers {
 
 template <int BN, int A_MAJOR, int B_MAJOR>
 __global__ void __launch_bounds__(kNumThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ CUtensorMap tma_b,
+gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ TmaSet tma_b,
                  const __grid_constant__ GemmArgs args, const __grid_constant__ GatherInfo gi) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -115,7 +120,7 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ C
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tma_b);
+      tma_prefetch_desc(&tma_b.m[0]);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -137,7 +142,11 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ C
           uint8_t* sa = smem + stage * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
           mbar_arrive_expect_tx(&bars->full[stage], C::kStageBytes);
-          const int k0 = kb * BK;
+          // with row-sharded B the K-blocks are rotated so that the local shard is consumed first
+          const int kbe = (gi.b_n_src > 1) ? (kb + gi.b_first_src * gi.b_kb_per_src) % total_kb : kb;
+          const int k0 = kbe * BK;
+          const CUtensorMap* tbp = &tma_b.m[(gi.b_n_src > 1) ? kbe / gi.b_kb_per_src : 0];
+          const int kb_row = (gi.b_n_src > 1) ? (kbe % gi.b_kb_per_src) * BK : k0;
           if (A_MAJOR == 0) {
             tma_load_2d(sa, ta, &bars->full[stage], k0, m0);
           } else {
@@ -145,10 +154,10 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ C
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, ta, &bars->full[stage], m0 + 64 * i, k0);
           }
           if (B_MAJOR == 0) {
-            tma_load_2d(sb, &tma_b, &bars->full[stage], k0, n0);
+            tma_load_2d(sb, tbp, &bars->full[stage], k0, n0);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tma_b, &bars->full[stage], n0 + 64 * i, k0);
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, tbp, &bars->full[stage], n0 + 64 * i, kb_row);
           }
           if (++stage == C::kStages) {
             stage = 0;
@@ -388,7 +397,7 @@ _Pragma("unroll") for (int j = 0; j < 32; ++j)
 }
 
 template <int BN, int A_MAJOR, int B_MAJOR>
-cudaError_t launch_variant(const TmaSet& ta, const CUtensorMap& tb, const GemmArgs& args, const GatherInfo& gi,
+cudaError_t launch_variant(const TmaSet& ta, const TmaSet& tb, const GemmArgs& args, const GatherInfo& gi,
                            cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kernel = gemm_bf16_kernel<BN, A_MAJOR, B_MAJOR>;
@@ -415,7 +424,8 @@ cudaError_t make_operand_map(CUtensorMap* map, const __nv_bfloat16* p, int64_t l
 
 cudaError_t launch_common(const __nv_bfloat16* const* a_src, int n_src, int rows_per_src, int first_src, int64_t lda,
                           int a_major, const __nv_bfloat16* B, int64_t ldb, int b_major, const GemmArgs& args_in,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const __nv_bfloat16* const* b_src = nullptr, int b_n_src = 1,
+                          int b_first_src = 0) {
   GemmArgs args = args_in;
   if (args.M <= 0 || args.N <= 0 || args.K <= 0) return cudaErrorInvalidValue;
   if (n_src < 1 || n_src > kMaxPeers) return cudaErrorInvalidValue;
@@ -435,10 +445,22 @@ cudaError_t launch_common(const __nv_bfloat16* const* a_src, int n_src, int rows
     if (e != cudaSuccess) return e;
   }
   for (int s = n_src; s < kMaxPeers; ++s) ta.m[s] = ta.m[0];
-  CUtensorMap tb;
-  cudaError_t e = make_operand_map(&tb, B, ldb, b_major, args.N, args.K, BN);
-  if (e != cudaSuccess) return e;
-  GatherInfo gi{n_src, n_src > 1 ? rows_per_src / BM : 0, first_src};
+  TmaSet tb;
+  cudaError_t e;
+  int b_kb_per_src = 0;
+  if (b_n_src > 1) {
+    // row-sharded MN-major B: source s holds rows [s * K / b_n_src, (s + 1) * K / b_n_src)
+    if (b_major != 1 || b_n_src > kMaxPeers || args.K % (b_n_src * BK) != 0 || args.split_k > 1) return cudaErrorInvalidValue;
+    const int k_per = args.K / b_n_src;
+    b_kb_per_src = k_per / BK;
+    for (int s = 0; s < b_n_src; ++s)
+      if ((e = make_operand_map(&tb.m[s], b_src[s], ldb, 1, args.N, k_per, BN)) != cudaSuccess) return e;
+    for (int s = b_n_src; s < kMaxPeers; ++s) tb.m[s] = tb.m[0];
+  } else {
+    if ((e = make_operand_map(&tb.m[0], B, ldb, b_major, args.N, args.K, BN)) != cudaSuccess) return e;
+    for (int s = 1; s < kMaxPeers; ++s) tb.m[s] = tb.m[0];
+  }
+  GatherInfo gi{n_src, n_src > 1 ? rows_per_src / BM : 0, first_src, b_n_src, b_kb_per_src, b_first_src};
 
 #define B200_GEMM_CASE(bn, am, bm) \
   if (BN == bn && a_major == am && b_major == bm) return launch_variant<bn, am, bm>(ta, tb, args, gi, stream);
@@ -471,6 +493,13 @@ cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, int64_t lda, int a_major, c
                              int b_major, const GemmArgs& args, cudaStream_t stream) {
   const __nv_bfloat16* srcs[1] = {A};
   return launch_common(srcs, 1, 0, 0, lda, a_major, B, ldb, b_major, args, stream);
+}
+
+cudaError_t launch_gemm_bf16_sharded_b(const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* const* b_src,
+                                       int b_n_src, int b_first_src, int64_t ldb, const GemmArgs& args,
+                                       cudaStream_t stream) {
+  const __nv_bfloat16* srcs[1] = {A};
+  return launch_common(srcs, 1, 0, 0, lda, 0, nullptr, ldb, 1, args, stream, b_src, b_n_src, b_first_src);
 }
 
 cudaError_t launch_gemm_bf16_gathered_a(const __nv_bfloat16* const* a_src, int n_src, int rows_per_src,

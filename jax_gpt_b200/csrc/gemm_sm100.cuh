@@ -59,6 +59,13 @@ cudaError_t launch_gemm_bf16_gathered_a(const __nv_bfloat16* const* a_src, int n
                                         int first_src, int64_t lda, const __nv_bfloat16* B, int64_t ldb, int b_major,
                                         const GemmArgs& args, cudaStream_t stream);
 
+// Parameter all-gather fused into the consuming GEMM (FSDP): the weight W [K, N] (MN-major B) is
+// split by rows over `b_n_src` ranks; shard s lives at b_src[s] (peer-mapped for remote ranks) and
+// is read tile by tile with non-multicast TMA as the K loop reaches it, the local shard first.
+cudaError_t launch_gemm_bf16_sharded_b(const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* const* b_src,
+                                       int b_n_src, int b_first_src, int64_t ldb, const GemmArgs& args,
+                                       cudaStream_t stream);
+
 int gemm_sm_count();
 
 }  // namespace b200

@@ -143,3 +143,36 @@ class NcclShardedAdamW(_ShardedBase):
 
     def grad_norm_sq(self):
         return self.sq
+
+
+class ShardedWeight:
+    """A weight W (K, N) kept row-sharded across the ranks (FSDP), consumed WITHOUT materialising it:
+    ``matmul(x)`` runs the tcgen05 GEMM whose TMA producer reads each K-block of W from the shard
+    (local or peer-mapped over NVLink) that owns it, the local rows first, so the parameter
+    all-gather is fused into the first GEMM that needs the parameter."""
+
+    def __init__(self, comm: Communicator, w_full_or_shard: torch.Tensor, is_shard: bool = False):
+        self.comm = comm
+        W = comm.world
+        if is_shard:
+            shard = w_full_or_shard
+            self.K, self.N = shard.shape[0] * W, shard.shape[1]
+        else:
+            self.K, self.N = w_full_or_shard.shape
+            assert self.K % (W * 64) == 0, "rows per rank must be a multiple of the 64-row K block"
+            kp = self.K // W
+            shard = w_full_or_shard[comm.rank * kp:(comm.rank + 1) * kp]
+        self.buf = comm.alloc(shard.numel(), torch.bfloat16)
+        self.shard = self.buf.tensor.view(shard.shape)
+        self.shard.copy_(shard)
+        comm.barrier()
+
+    def matmul(self, x: torch.Tensor, bias=None) -> torch.Tensor:
+        x2 = x.reshape(-1, self.K)
+        out = torch.empty(x2.shape[0], self.N, device=x.device, dtype=torch.bfloat16)
+        _ext.ops().gemm_sharded_b(x2, self.buf.peer_ptrs, self.comm.rank, self.N, out, bias)
+        return out.reshape(*x.shape[:-1], self.N)
+
+    def sync(self):
+        """Call after the shards were updated (optimizer step) and before the next matmul."""
+        self.comm.barrier()

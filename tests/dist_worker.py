@@ -84,6 +84,27 @@ def run_tp(rank, world, device):
     return res
 
 
+def run_fsdp_ag(rank, world, device):
+    """Row-sharded weight consumed through peer TMA loads vs all-gather + GEMM."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.comm.symm import Communicator
+    from jax_gpt_b200.parallel.fsdp import ShardedWeight
+    comm = Communicator(device=device, wait_seconds=5.0)
+    res = {}
+    for (M, K, N) in [(512, 1024, 768), (300, 512, 264)]:
+        g = torch.Generator(device=device).manual_seed(21)
+        w = (torch.randn(K, N, device=device, generator=g) * 0.05).to(torch.bfloat16)
+        x = torch.randn(M, K, device=device, generator=torch.Generator(device=device).manual_seed(rank)).to(torch.bfloat16)
+        sw = ShardedWeight(comm, w)
+        y = sw.matmul(x)
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        res[f"ag_gemm_{M}x{K}x{N}"] = rel(y, x.float() @ w.float())
+        comm.barrier()
+    dist.barrier()
+    return res
+
+
 def run_ep(rank, world, device):
     """Fused expert-parallel MoE forward vs a dense evaluation with all experts and vs the NCCL path."""
     from jax_gpt_b200 import _ext
@@ -136,6 +157,8 @@ def main():
         res = run_fsdp(rank, world, device, True)
     elif what == "tp":
         res = run_tp(rank, world, device)
+    elif what == "fsdp_ag":
+        res = run_fsdp_ag(rank, world, device)
     elif what == "ep":
         res = run_ep(rank, world, device)
     else:

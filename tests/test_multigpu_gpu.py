@@ -41,6 +41,11 @@ def test_tp_fused_gemms_two_gpus(tmp_path):
     assert res["ag_gemm"] < 1e-2 and res["gemm_rs"] < 1e-2, res
 
 
+def test_fsdp_all_gather_fused_into_gemm_two_gpus(tmp_path):
+    res = _run("fsdp_ag", tmp_path, port=29614)
+    assert all(v < 1e-2 for v in res.values()), res
+
+
 def test_fused_ep_moe_two_gpus(tmp_path):
     res = _run("ep", tmp_path, port=29613)
     for k, v in res.items():
