@@ -56,7 +56,8 @@ struct MoeBars {
   int abort_flag;
 };
 
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(MoeTables) + sizeof(MoeBars) + 64;
+constexpr int kStageBufBytes = 4 * 32 * 33 * 4;  // per-epilogue-warp transposition buffers
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(MoeTables) + sizeof(MoeBars) + 64 + kStageBufBytes;
 
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
@@ -178,6 +179,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   MoeTables* tb = reinterpret_cast<MoeTables*>(smem + kStages * kStageBytes);
   MoeBars* bars = reinterpret_cast<MoeBars*>(reinterpret_cast<uint8_t*>(tb) + ((sizeof(MoeTables) + 15) & ~size_t(15)));
   volatile int* abort_flag = &bars->abort_flag;
+  float* stage_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + ((sizeof(MoeBars) + 15) & ~size_t(15)));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int W = a.world, EL = a.e_local, ET = W * EL, D = a.d_model, I = a.inter;
   CommCtrl* my = a.peer_ctrl[a.rank];
@@ -397,6 +399,9 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
           }
         }
       } else {
+        // Weighted combine. Each lane owns one row of the tile, but a row-per-lane reduction would
+        // put 32 scattered 16-byte pieces on NVLink per instruction; the chunk is transposed through
+        // shared memory so that eight lanes cover 128 contiguous bytes of one destination row.
         float wgt = 0.f;
         float* dst = nullptr;
         if (row_ok) {
@@ -404,19 +409,28 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
           const int meta = a.peer_recv_meta[a.rank][row];
           dst = a.peer_out[meta >> 24] + static_cast<int64_t>(meta & 0xFFFFFF) * D + ti.n * BN;
         }
+        float* stg = stage_buf + (warp - 2) * (32 * 33);
+        const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(tacc + c * 32, v);
           tmem_ld_wait();
-          if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 32 + j),
-                           "f"(__uint_as_float(v[j]) * wgt), "f"(__uint_as_float(v[j + 1]) * wgt),
-                           "f"(__uint_as_float(v[j + 2]) * wgt), "f"(__uint_as_float(v[j + 3]) * wgt)
+          for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __uint_as_float(v[j]) * wgt;
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 32; rr += 4) {
+            const int r2 = rr + (lane >> 3), c2 = (lane & 7) * 4;
+            const unsigned long long db = __shfl_sync(0xffffffffu, dst_bits, r2);
+            if (db != 0ull) {
+              float* d2 = reinterpret_cast<float*>(db) + c * 32 + c2;
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d2), "f"(stg[r2 * 33 + c2]),
+                           "f"(stg[r2 * 33 + c2 + 1]), "f"(stg[r2 * 33 + c2 + 2]), "f"(stg[r2 * 33 + c2 + 3])
                            : "memory");
+            }
           }
+          __syncwarp();
         }
       }
       tc_fence_before();
