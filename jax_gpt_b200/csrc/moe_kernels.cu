@@ -99,21 +99,27 @@ __global__ void moe_prepare_kernel(const int* __restrict__ idx, int n_pairs, int
 }
 
 // Fills the shared-memory tables from the all-gathered count matrix counts[src][e].
-__device__ void build_tables(const EpMoeArgs& a, const int* counts_all, MoeTables* tb) {
+__device__ void build_tables(const EpMoeArgs& a, const int* counts_all, MoeTables* tb, bool backward = false) {
   const int W = a.world, EL = a.e_local, ET = W * EL;
   if (threadIdx.x == 0) tb->overflow = 0;
   __syncthreads();
   for (int e = threadIdx.x; e < ET; e += blockDim.x) {
     const int dst = e / EL, el = e % EL;
+    // every expert's region starts on a 64-row boundary (ragged-K weight gradients read whole
+    // 64-row blocks; the padding rows are kept zero)
     int off = 0;
-    for (int e2 = dst * EL; e2 < dst * EL + el; ++e2)   // experts placed before e on the destination
-      for (int s = 0; s < W; ++s) off += __ldcg(counts_all + s * ET + e2);
-    for (int s = 0; s < a.rank; ++s) off += __ldcg(counts_all + s * ET + e);  // sources placed before this rank
-    tb->send_off[e] = off;
+    for (int e2 = dst * EL; e2 < dst * EL + el; ++e2) {  // experts placed before e on the destination
+      int n2 = 0;
+      for (int s = 0; s < W; ++s) n2 += __ldcg(counts_all + s * ET + e2);
+      off += (n2 + 63) & ~63;
+    }
+    int before = 0;
+    for (int s = 0; s < a.rank; ++s) before += __ldcg(counts_all + s * ET + e);  // sources placed before this rank
+    tb->send_off[e] = off + before;
     if (el == EL - 1) {
-      int tot = off;
+      int tot = before;
       for (int s = a.rank; s < W; ++s) tot += __ldcg(counts_all + s * ET + e);
-      if (tot > a.cap_rows) tb->overflow = 1;
+      if (off + ((tot + 63) & ~63) > a.cap_rows) tb->overflow = 1;
     }
   }
   for (int el = threadIdx.x; el < EL; el += blockDim.x) {
@@ -130,8 +136,13 @@ __device__ void build_tables(const EpMoeArgs& a, const int* counts_all, MoeTable
       tb->tile0[el] = t;
       tb->mt0[el] = m;
       const int mt = (tb->rows[el] + BM - 1) / BM;
-      b += tb->rows[el];
-      t += mt * (n1 + n2);
+      b += (tb->rows[el] + 63) & ~63;
+      if (!backward) {
+        t += mt * (n1 + n2);
+      } else if (mt > 0) {
+        // dAct tiles, dX tiles, dW_down tiles, dW_gate|up tiles
+        t += mt * (a.inter / BN) + mt * n2 + (a.inter / BM) * n2 + (a.d_model / BM) * (2 * a.inter / BN);
+      }
       m += mt;
     }
     tb->tile0[EL] = t;
@@ -241,7 +252,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       uint4* out = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
       for (int i = lane; i < D / 8; i += 32) out[i] = src[i];
       if (lane == 0) {
-        a.peer_recv_meta[dst][slot] = (a.rank << 24) | tok;
+        a.peer_recv_meta[dst][slot] = (a.rank << 24) | p;  // source rank and (token, choice) pair
         a.peer_recv_w[dst][slot] = a.w[p];
         a.slot_out[p] = slot;
       }
@@ -373,6 +384,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       tc_fence_after();
       const int r = ti.m * BM + q * 32 + lane;            // row within the expert
       const bool row_ok = r < tb->rows[ti.el];
+      const bool pad_row = !row_ok && r < ((tb->rows[ti.el] + 63) & ~63);  // padding rows are written as zeros
       const int64_t row = tb->base[ti.el] + r;            // row in the receive buffer
       const uint32_t tacc = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       if (ti.phase == 0) {
@@ -383,18 +395,25 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
           tmem_ld_32x32(tacc + c * 32, g);
           tmem_ld_32x32(tacc + 128 + c * 32, u);
           tmem_ld_wait();
-          if (row_ok) {
+          if (row_ok || pad_row) {
+            const float keep = row_ok ? 1.f : 0.f;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
-              uint32_t pk[4];
+              uint32_t pk[4], pg[4], pu[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
-                const float h0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(u[j + 2 * e]);
-                const float h1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(u[j + 2 * e + 1]);
-                pk[e] = pack_bf16x2(h0, h1);
+                const float g0 = __uint_as_float(g[j + 2 * e]) * keep, g1 = __uint_as_float(g[j + 2 * e + 1]) * keep;
+                const float u0 = __uint_as_float(u[j + 2 * e]) * keep, u1 = __uint_as_float(u[j + 2 * e + 1]) * keep;
+                pk[e] = pack_bf16x2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                pg[e] = pack_bf16x2(g0, g1);
+                pu[e] = pack_bf16x2(u0, u1);
               }
               *reinterpret_cast<uint4*>(dst + c * 32 + j) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              if (a.gu != nullptr) {  // pre-activations kept for the backward pass: [row, gate | up]
+                __nv_bfloat16* gp = a.gu + row * (2 * I) + ti.n * 128 + c * 32 + j;
+                *reinterpret_cast<uint4*>(gp) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                *reinterpret_cast<uint4*>(gp + I) = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+              }
             }
           }
         }
@@ -407,7 +426,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
         if (row_ok) {
           wgt = a.peer_recv_w[a.rank][row];
           const int meta = a.peer_recv_meta[a.rank][row];
-          dst = a.peer_out[meta >> 24] + static_cast<int64_t>(meta & 0xFFFFFF) * D + ti.n * BN;
+          dst = a.peer_out[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN;
         }
         float* stg = stage_buf + (warp - 2) * (32 * 33);
         const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
@@ -467,6 +486,432 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Backward. Tile order per local expert (rows > 0):
+//   Q0  dAct = dYw W_down^T  (+ SwiGLU backward -> dGU, <dAct, act> per row)      mt x I/256 tiles
+//   Q1  dX   = dGU [W_gate | W_up]^T, pushed to the token owners                     mt x D/256
+//   Q2  dW_down += act^T dYw          (ragged K = the expert's rows, 64-row blocks)  I/128 x D/256
+//   Q3  dW_gate | dW_up += X^T dGU    (ragged K)                                     D/128 x 2I/256
+// Q1 waits for the Q0 tiles of its m-tile, Q3 for all Q0 tiles of its expert; both dependencies
+// point backwards in the static order.
+struct BwdTile {
+  int el, phase, m, n;
+};
+
+__device__ __forceinline__ BwdTile decode_bwd_tile(const EpMoeArgs& a, const MoeTables* tb, int t) {
+  int el = 0;
+  while (t >= tb->tile0[el + 1]) ++el;
+  const int mt = (tb->rows[el] + BM - 1) / BM;
+  const int c0 = mt * (a.inter / BN), c1 = mt * (a.d_model / BN), c2 = (a.inter / BM) * (a.d_model / BN);
+  int r = t - tb->tile0[el];
+  BwdTile ti;
+  ti.el = el;
+  if (r < c0) {
+    ti.phase = 0; ti.m = r % mt; ti.n = r / mt;
+  } else if (r < c0 + c1) {
+    r -= c0; ti.phase = 1; ti.m = r % mt; ti.n = r / mt;
+  } else if (r < c0 + c1 + c2) {
+    r -= c0 + c1; ti.phase = 2; ti.m = r % (a.inter / BM); ti.n = r / (a.inter / BM);
+  } else {
+    r -= c0 + c1 + c2; ti.phase = 3; ti.m = r % (a.d_model / BM); ti.n = r / (a.d_model / BM);
+  }
+  return ti;
+}
+
+struct BwdMaps {
+  CUtensorMap dy_k, dgu_k, down_k, gate_k, up_k;  // K-major views: box {64, 128} for activations, {64, 256} for weights
+  CUtensorMap act_mn, dy_mn, x_mn, dgu_mn;        // MN-major views of the row buffers: box {64, 64}
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant__ EpMoeArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  MoeTables* tb = reinterpret_cast<MoeTables*>(smem + kStages * kStageBytes);
+  MoeBars* bars = reinterpret_cast<MoeBars*>(reinterpret_cast<uint8_t*>(tb) + ((sizeof(MoeTables) + 15) & ~size_t(15)));
+  volatile int* abort_flag = &bars->abort_flag;
+  float* stage_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + ((sizeof(MoeBars) + 15) & ~size_t(15)));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int W = a.world, EL = a.e_local, ET = W * EL, D = a.d_model, I = a.inter;
+  CommCtrl* my = a.peer_ctrl[a.rank];
+  const int epoch = my->epoch + 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 4);
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gthreads = gridDim.x * blockDim.x;
+
+  // ---- 1. counts exchange (same protocol as forward), zero the per-launch counters ----
+  {
+    const int max_mt = a.cap_rows / BM + EL;
+    for (int i = gtid; i < max_mt; i += gthreads) a.gu_ready[i] = 0;
+    for (int i = gtid; i < EL; i += gthreads) a.expert_done[i] = 0;
+    for (int i = gtid; i < a.cap_rows; i += gthreads) a.dw_rows[i] = 0.f;
+  }
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) my->abort_flag = 0;
+    for (int i = threadIdx.x; i < ET; i += blockDim.x) {
+      const int c = a.my_counts[i];
+      for (int p = 0; p < W; ++p) a.peer_counts[p][a.rank * ET + i] = c;
+    }
+    const bool ok = flag_barrier(a.peer_ctrl, W, a.rank, 4, epoch, a.wait_budget_ns, a.status);
+    if (!ok && threadIdx.x == 0) my->abort_flag = 1;
+  }
+  __threadfence();
+  grid.sync();
+  bool alive = (*reinterpret_cast<volatile int*>(&my->abort_flag) == 0);
+  build_tables(a, a.peer_counts[a.rank], tb, /*backward=*/true);
+  if (tb->overflow) {
+    if (alive && blockIdx.x == 0 && threadIdx.x == 0) report_status(a.status, kBadArgument, 50, a.cap_rows, 0);
+    alive = false;
+  }
+
+  // ---- 2. keep the padding rows of the receive buffers zero (nobody else writes them) ----
+  if (alive) {
+    const int vec_per_row = D / 8;
+    for (int el = 0; el < EL; ++el) {
+      const int r0 = tb->base[el] + tb->rows[el], r1 = tb->base[el] + ((tb->rows[el] + 63) & ~63);
+      const int64_t n = static_cast<int64_t>(r1 - r0) * vec_per_row;
+      uint4* px = reinterpret_cast<uint4*>(a.peer_recv_x[a.rank] + static_cast<int64_t>(r0) * D);
+      uint4* py = reinterpret_cast<uint4*>(a.peer_recv_dy[a.rank] + static_cast<int64_t>(r0) * D);
+      for (int64_t i = gtid; i < n; i += gthreads) {
+        px[i] = make_uint4(0, 0, 0, 0);
+        py[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  // ---- 3. dispatch the routing-weighted dout rows to the slots the forward pass used (the x rows, the
+  //         routing metadata, act and the pre-activations are still in place from the forward launch) ----
+  if (alive) {
+    const int n_pairs = a.tokens * a.top_k;
+    for (int p = blockIdx.x * (kThreads / 32) + warp; p < n_pairs; p += gridDim.x * (kThreads / 32)) {
+      const int e = a.idx[p];
+      const int dst = e / EL, el = e - dst * EL;
+      const int slot = tb->send_off[e] + a.pos[p];
+      const int tok = p / a.top_k;
+      const float wp = a.w[p];
+      const uint4* sy = reinterpret_cast<const uint4*>(a.dout + static_cast<int64_t>(tok) * D);
+      uint4* oy = reinterpret_cast<uint4*>(a.peer_recv_dy[dst] + static_cast<int64_t>(slot) * D);
+      for (int i = lane; i < D / 8; i += 32) {
+        const uint4 v = sy[i];
+        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+        oy[i] = make_uint4(pack_bf16x2(f0.x * wp, f0.y * wp), pack_bf16x2(f1.x * wp, f1.y * wp),
+                           pack_bf16x2(f2.x * wp, f2.y * wp), pack_bf16x2(f3.x * wp, f3.y * wp));
+      }
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_system();
+        red_release_sys_add_u32(a.peer_arrive[dst] + el, 1u);
+      }
+    }
+  }
+  __threadfence();  // the zeroed padding rows are visible before any tile reads them
+  grid.sync();
+
+  const int num_tiles = alive ? tb->tile0[EL] : 0;
+  const unsigned q0_per_mtile = 4u * (I / BN);
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int ready_el = -1;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const BwdTile ti = decode_bwd_tile(a, tb, t);
+        const int rows = tb->rows[ti.el], base = tb->base[ti.el];
+        const int mt = (rows + BM - 1) / BM;
+        if (ti.el != ready_el) {
+          const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(rows);
+          if (!wait_counter_ge<true>(a.peer_arrive[a.rank] + ti.el, target, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 51, ti.el, t);
+            break;
+          }
+          ready_el = ti.el;
+        }
+        if (ti.phase == 1) {
+          const unsigned* ready = reinterpret_cast<const unsigned*>(a.gu_ready) + tb->mt0[ti.el] + ti.m;
+          if (!wait_counter_ge<false>(ready, q0_per_mtile, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 52, ti.el, t);
+            break;
+          }
+        } else if (ti.phase == 3) {
+          const unsigned* done = reinterpret_cast<const unsigned*>(a.expert_done) + ti.el;
+          if (!wait_counter_ge<false>(done, q0_per_mtile * mt, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 53, ti.el, t);
+            break;
+          }
+        }
+        fence_proxy_async_global();
+        const int nkb = ti.phase == 0 ? D / BK : (ti.phase == 1 ? 2 * I / BK : ((rows + 63) & ~63) / BK);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag)) {
+            report_status(a.status, kWaitEmptyTimeout, 54, blockIdx.x, t);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          uint64_t* fb = &bars->full[stage];
+          mbar_arrive_expect_tx(fb, kStageBytes);
+          if (ti.phase == 0) {
+            tma_load_2d(sa, &tm.dy_k, fb, kb * BK, base + ti.m * BM);
+            tma_load_2d(sb, &tm.down_k, fb, kb * BK, ti.el * I + ti.n * BN);
+          } else if (ti.phase == 1) {
+            tma_load_2d(sa, &tm.dgu_k, fb, kb * BK, base + ti.m * BM);
+            const int kh = I / BK;
+            tma_load_2d(sb, kb < kh ? &tm.gate_k : &tm.up_k, fb, (kb % kh) * BK, ti.el * D + ti.n * BN);
+          } else {
+            const CUtensorMap* ma = ti.phase == 2 ? &tm.act_mn : &tm.x_mn;
+            const CUtensorMap* mb = ti.phase == 2 ? &tm.dy_mn : &tm.dgu_mn;
+            const int ky = base + kb * BK;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) tma_load_2d(sa + i * 8192, ma, fb, ti.m * BM + 64 * i, ky);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tma_load_2d(sb + i * 8192, mb, fb, ti.n * BN + 64 * i, ky);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        for (int s = 0; s < kStages; ++s) {
+          const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&bars->full[s], armed)) {
+            if (globaltimer_ns() - t0 > 2000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc_kk = make_idesc(BM, BN, 0, 0, 1);
+    constexpr uint32_t idesc_nn = make_idesc(BM, BN, 1, 1, 1);
+    int stage = 0, iter = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+      const BwdTile ti = decode_bwd_tile(a, tb, t);
+      const int acc = iter & 1;
+      if (!mbar_wait(&bars->tmem_empty[acc], ((iter >> 1) & 1) ^ 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemEmptyTimeout, 55, blockIdx.x, t);
+        break;
+      }
+      tc_fence_after();
+      const int rows = tb->rows[ti.el];
+      const int nkb = ti.phase == 0 ? D / BK : (ti.phase == 1 ? 2 * I / BK : ((rows + 63) & ~63) / BK);
+      const bool mn = ti.phase >= 2;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+          if (lane == 0) report_status(a.status, kWaitFullTimeout, 56, blockIdx.x, t);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = mn ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bd = mn ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(tmem_base + acc * BN, ad, bd, mn ? idesc_nn : idesc_kk, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&bars->empty[stage]);
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok && lane == 0) tc_commit(&bars->tmem_full[acc]);
+      __syncwarp();
+    }
+  } else {
+    const int q = warp & 3;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    float* stg = stage_buf + (warp - 2) * (32 * 33);
+    int iter = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++iter) {
+      const BwdTile ti = decode_bwd_tile(a, tb, t);
+      const int acc = iter & 1;
+      if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 57, blockIdx.x, t);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + acc * BN + lane_off;
+      const int rows = tb->rows[ti.el], base = tb->base[ti.el];
+      if (ti.phase == 0) {
+        // dAct tile -> SwiGLU backward. act = silu(g) * u is recomputed from the saved pre-activations.
+        const int r = ti.m * BM + q * 32 + lane;
+        const bool row_ok = r < rows;
+        const bool pad_row = !row_ok && r < ((rows + 63) & ~63);
+        const int64_t row = base + r;
+        float dwp = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tacc + c * 32, v);
+          tmem_ld_wait();
+          const int col = ti.n * BN + c * 32;
+          if (row_ok) {
+            const __nv_bfloat16* gp = a.gu + row * (2 * I) + col;
+            __nv_bfloat16* op = a.dgu + row * (2 * I) + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const uint4 gr = *reinterpret_cast<const uint4*>(gp + j);
+              const uint4 ur = *reinterpret_cast<const uint4*>(gp + I + j);
+              const uint32_t gw[4] = {gr.x, gr.y, gr.z, gr.w}, uw[4] = {ur.x, ur.y, ur.z, ur.w};
+              uint32_t og[4], ou[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 g2 = unpack_bf16x2(gw[e]), u2 = unpack_bf16x2(uw[e]);
+                const float d0 = __uint_as_float(v[j + 2 * e]), d1 = __uint_as_float(v[j + 2 * e + 1]);
+                const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+                const float l0 = g2.x * s0, l1 = g2.y * s1;  // silu
+                dwp += d0 * l0 * u2.x + d1 * l1 * u2.y;
+                ou[e] = pack_bf16x2(d0 * l0, d1 * l1);
+                og[e] = pack_bf16x2(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+              }
+              *reinterpret_cast<uint4*>(op + j) = make_uint4(og[0], og[1], og[2], og[3]);
+              *reinterpret_cast<uint4*>(op + I + j) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+            }
+          } else if (pad_row) {
+            __nv_bfloat16* op = a.dgu + row * (2 * I) + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              *reinterpret_cast<uint4*>(op + j) = make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4*>(op + I + j) = make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+        if (row_ok) atomicAdd(a.dw_rows + row, dwp);
+      } else if (ti.phase == 1) {
+        // dX rows go to the token owners with coalesced fp32 reductions (see the forward combine)
+        const int r = ti.m * BM + q * 32 + lane;
+        float* dst = nullptr;
+        if (r < rows) {
+          const int meta = a.peer_recv_meta[a.rank][base + r];
+          dst = a.peer_dx[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN;
+        }
+        const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tacc + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __uint_as_float(v[j]);
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 32; rr += 4) {
+            const int r2 = rr + (lane >> 3), c2 = (lane & 7) * 4;
+            const unsigned long long db = __shfl_sync(0xffffffffu, dst_bits, r2);
+            if (db != 0ull) {
+              float* d2 = reinterpret_cast<float*>(db) + c * 32 + c2;
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d2), "f"(stg[r2 * 33 + c2]),
+                           "f"(stg[r2 * 33 + c2 + 1]), "f"(stg[r2 * 33 + c2 + 2]), "f"(stg[r2 * 33 + c2 + 3])
+                           : "memory");
+            }
+          }
+          __syncwarp();
+        }
+      } else {
+        // weight-gradient tiles: every row of the tile is a real weight row; accumulate in fp32
+        const int r = ti.m * BM + q * 32 + lane;
+        float* dst;
+        if (ti.phase == 2) {
+          dst = a.d_down + (static_cast<int64_t>(ti.el) * I + r) * D + ti.n * BN;
+        } else {
+          const int col0 = ti.n * BN;
+          dst = (col0 < I ? a.d_gate : a.d_up) + (static_cast<int64_t>(ti.el) * D + r) * I + (col0 < I ? col0 : col0 - I);
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tacc + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 32 + j),
+                         "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])),
+                         "f"(__uint_as_float(v[j + 3]))
+                         : "memory");
+        }
+      }
+      tc_fence_before();
+      if (ti.phase == 0) {
+        __threadfence();
+        fence_proxy_async_global();
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars->tmem_empty[acc]);
+        if (ti.phase == 0) {
+          atomicAdd(a.gu_ready + tb->mt0[ti.el] + ti.m, 1);
+          atomicAdd(a.expert_done + ti.el, 1);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+  __threadfence();
+  grid.sync();
+  // ---- routing-weight gradients back to the pair owners: dw = <dAct_weighted, act> / w ----
+  if (alive) {
+    const int total = tb->base[EL - 1] + tb->rows[EL - 1];
+    for (int row = gtid; row < total; row += gthreads) {
+      int el = 0;
+      while (el + 1 < EL && row >= tb->base[el + 1]) ++el;
+      if (row - tb->base[el] < tb->rows[el]) {
+        const int meta = a.peer_recv_meta[a.rank][row];
+        const float wv = a.peer_recv_w[a.rank][row];
+        a.peer_dw[meta >> 24][meta & 0xFFFFFF] = (wv != 0.f) ? __ldcg(a.dw_rows + row) / wv : 0.f;
+      }
+    }
+  }
+  __threadfence_system();
+  grid.sync();
+  if (blockIdx.x == 0) {
+    flag_barrier(a.peer_ctrl, W, a.rank, 5, epoch, a.wait_budget_ns, a.status);
+    if (alive) {
+      for (int el = threadIdx.x; el < EL; el += blockDim.x) {
+        a.arrive_target[el] += static_cast<unsigned>(tb->rows[el]);
+        a.rows_out[el] = tb->rows[el];
+      }
+    }
+    if (threadIdx.x == 0) my->epoch = epoch;
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_moe_prepare(const int* idx, int n_pairs, int n_experts, int* counts, int* pos, cudaStream_t st) {
@@ -482,7 +927,7 @@ cudaError_t launch_ep_moe_forward(const EpMoeArgs& args, const __nv_bfloat16* ga
   const EpMoeArgs& a = args;
   if (a.world < 1 || a.world > kCommMaxRanks || a.e_local < 1 || a.e_local > kMoeMaxLocalExperts ||
       a.world * a.e_local > kMoeMaxExperts || a.d_model % 256 != 0 || a.inter % 128 != 0 || a.cap_rows % BM != 0 ||
-      a.tokens >= (1 << 24))
+      static_cast<int64_t>(a.tokens) * a.top_k >= (1 << 24))
     return cudaErrorInvalidValue;
   CUtensorMap t_recv, t_act, t_gate, t_up, t_down;
   cudaError_t e;
@@ -504,6 +949,40 @@ cudaError_t launch_ep_moe_forward(const EpMoeArgs& args, const __nv_bfloat16* ga
   EpMoeArgs args_copy = args;
   void* params[] = {&t_recv, &t_act, &t_gate, &t_up, &t_down, &args_copy};
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ep_moe_forward_kernel), dim3(sms), dim3(kThreads), params,
+                                     kSmemBytes, st);
+}
+
+cudaError_t launch_ep_moe_backward(const EpMoeArgs& args, const __nv_bfloat16* gate, const __nv_bfloat16* up,
+                                   const __nv_bfloat16* down, cudaStream_t st) {
+  const EpMoeArgs& a = args;
+  if (a.world < 1 || a.world > kCommMaxRanks || a.e_local < 1 || a.e_local > kMoeMaxLocalExperts ||
+      a.world * a.e_local > kMoeMaxExperts || a.d_model % 256 != 0 || a.inter % 256 != 0 || a.cap_rows % BM != 0 ||
+      static_cast<int64_t>(a.tokens) * a.top_k >= (1 << 24) || a.gu == nullptr || a.dgu == nullptr)
+    return cudaErrorInvalidValue;
+  BwdMaps tm;
+  cudaError_t e;
+  const uint64_t cap = a.cap_rows, D = a.d_model, I = a.inter, EL = a.e_local;
+  if ((e = encode_tma_2d(&tm.dy_k, a.peer_recv_dy[a.rank], 2, D, cap, D * 2, 64, BM)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.dgu_k, a.dgu, 2, 2 * I, cap, 2 * I * 2, 64, BM)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.down_k, down, 2, D, EL * I, D * 2, 64, BN)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.gate_k, gate, 2, I, EL * D, I * 2, 64, BN)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.up_k, up, 2, I, EL * D, I * 2, 64, BN)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.act_mn, a.act, 2, I, cap, I * 2, 64, 64)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.dy_mn, a.peer_recv_dy[a.rank], 2, D, cap, D * 2, 64, 64)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.x_mn, a.peer_recv_x[a.rank], 2, D, cap, D * 2, 64, 64)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tm.dgu_mn, a.dgu, 2, 2 * I, cap, 2 * I * 2, 64, 64)) != cudaSuccess) return e;
+  static bool configured = false;
+  if (!configured) {
+    if ((e = cudaFuncSetAttribute(ep_moe_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)) != cudaSuccess)
+      return e;
+    configured = true;
+  }
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  EpMoeArgs args_copy = args;
+  void* params[] = {&tm, &args_copy};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ep_moe_backward_kernel), dim3(sms), dim3(kThreads), params,
                                      kSmemBytes, st);
 }
 

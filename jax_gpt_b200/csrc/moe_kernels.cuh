@@ -37,10 +37,23 @@ struct EpMoeArgs {
   CommCtrl* peer_ctrl[kCommMaxRanks];
   // local scratch / state
   __nv_bfloat16* act;       // [cap_rows, inter] SwiGLU output
+  __nv_bfloat16* gu;        // [cap_rows, 2 * inter] gate | up pre-activations saved for backward, or nullptr
   unsigned* arrive_target;  // [e_local] arrivals expected once this launch's rows are in (cumulative)
   int* act_ready;           // [cap_rows / 128 + e_local] per m-tile count of finished GEMM1 epilogue warps
   int* slot_out;            // [tokens * top_k] row of each pair in its destination's receive buffer
   int* rows_out;            // [e_local] rows received per local expert (for the caller / backward)
+  // ---- backward only ----
+  const __nv_bfloat16* dout;                   // [tokens, d_model] gradient of the routed output
+  __nv_bfloat16* peer_recv_dy[kCommMaxRanks];  // [cap_rows, d_model] routing-weighted output-gradient rows
+  float* peer_dx[kCommMaxRanks];               // [tokens of that rank, d_model] fp32 input-gradient target (zeroed by owner)
+  float* peer_dw[kCommMaxRanks];               // [tokens * top_k of that rank] gradient of the routing weights
+  __nv_bfloat16* dgu;                          // [cap_rows, 2 * inter] gradient of gate | up
+  float* dw_rows;                              // [cap_rows] <dAct, act> per received row
+  int* gu_ready;                               // [cap_rows / 128 + e_local] per m-tile count of finished dAct epilogue warps
+  int* expert_done;                            // [e_local] same, per expert
+  float* d_gate;                               // [e_local, d_model, inter] fp32, accumulated
+  float* d_up;                                 // [e_local, d_model, inter]
+  float* d_down;                               // [e_local, inter, d_model]
   uint64_t wait_budget_ns;
   int* status;
 };
@@ -52,5 +65,13 @@ cudaError_t launch_moe_prepare(const int* idx, int n_pairs, int n_experts, int* 
 // receive buffer and `act` of THIS rank through TMA (pointers args.peer_recv_x[rank], args.act).
 cudaError_t launch_ep_moe_forward(const EpMoeArgs& args, const __nv_bfloat16* gate, const __nv_bfloat16* up,
                                   const __nv_bfloat16* down, cudaStream_t st);
+
+// Backward of the LAST forward launch: dispatches the w * dout rows to the slots that launch used (x rows,
+// routing metadata, act and pre-activations stay in place), computes the expert-side gradients
+// (dAct with the SwiGLU backward, dX pushed to the token owners, the three weight gradients with
+// ragged K, the routing-weight gradients) in one cooperative kernel. Needs `act` and `gu` of the
+// forward call with the same routing.
+cudaError_t launch_ep_moe_backward(const EpMoeArgs& args, const __nv_bfloat16* gate, const __nv_bfloat16* up,
+                                   const __nv_bfloat16* down, cudaStream_t st);
 
 }  // namespace b200

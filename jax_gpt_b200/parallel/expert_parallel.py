@@ -31,14 +31,16 @@ class FusedEPMoE:
     """
 
     def __init__(self, comm: Communicator, tokens: int, d_model: int, inter: int, n_experts: int, top_k: int,
-                 cap_factor: Optional[float] = None):
+                 cap_factor: Optional[float] = None, training: bool = False):
         self.comm = comm
         W = comm.world
         assert n_experts % W == 0 and d_model % 256 == 0 and inter % 128 == 0
         self.tokens, self.D, self.I, self.E, self.k = tokens, d_model, inter, n_experts, top_k
         self.e_local = n_experts // W
         cap_factor = float(W) if cap_factor is None else cap_factor
-        self.cap_rows = (int(tokens * top_k * cap_factor) + 127) // 128 * 128
+        # every expert's region is padded to a multiple of 64 rows
+        self.cap_rows = (int(tokens * top_k * cap_factor) + 64 * self.e_local + 127) // 128 * 128
+        self.training = training
         dev = comm.device
         self.recv_x = comm.alloc(self.cap_rows * d_model, torch.bfloat16, zero=True)
         self.recv_meta = comm.alloc(self.cap_rows, torch.int32)
@@ -53,7 +55,39 @@ class FusedEPMoE:
         self.rows_out = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
         self.my_counts = torch.zeros(n_experts, device=dev, dtype=torch.int32)
         self.pos = torch.zeros(tokens * top_k, device=dev, dtype=torch.int32)
+        if training:
+            self.gu = torch.zeros(self.cap_rows, 2 * inter, device=dev, dtype=torch.bfloat16)
+            self.dgu = torch.zeros(self.cap_rows, 2 * inter, device=dev, dtype=torch.bfloat16)
+            self.recv_dy = comm.alloc(self.cap_rows * d_model, torch.bfloat16, zero=True)
+            self.dx_acc = comm.alloc(tokens * d_model, torch.float32)
+            self.dw_out = comm.alloc(tokens * top_k, torch.float32)
+            self.dw_rows = torch.zeros(self.cap_rows, device=dev, dtype=torch.float32)
+            self.gu_ready = torch.zeros(self.cap_rows // 128 + self.e_local, device=dev, dtype=torch.int32)
+            self.expert_done = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
+        else:
+            self.gu = None
         dist.barrier(comm.group)
+
+    def backward(self, x, dout, weights, idx, params, grads):
+        """Gradients of the LAST ``forward`` call (same x, routing and params): the dispatched x rows,
+        their slots, the activations and the pre-activations of that launch are reused in place, only the
+        routing-weighted ``dout`` rows travel. ``grads`` holds fp32 ``gate_proj`` / ``up_proj`` /
+        ``down_proj`` buffers that are ACCUMULATED into. Returns (dx (tokens, D) fp32, dweights (tokens, k) fp32)."""
+        assert self.training, "construct FusedEPMoE(training=True) to keep what backward needs"
+        ops = _ext.ops()
+        c = self.comm
+        idx32 = idx.to(torch.int32).contiguous().view(-1)
+        w32 = weights.to(torch.float32).contiguous().view(-1)
+        self.dx_acc.tensor.zero_()   # my_counts / pos are the forward launch's: the slots must not change
+        ops.ep_moe_backward(c.world, c.rank, self.k, self.e_local, self.cap_rows, x.contiguous(), dout.contiguous(),
+                            idx32, w32, self.pos, self.my_counts, self.recv_x.peer_ptrs, self.recv_dy.peer_ptrs,
+                            self.recv_meta.peer_ptrs, self.recv_w.peer_ptrs, self.counts_all.peer_ptrs,
+                            self.arrive.peer_ptrs, self.dx_acc.peer_ptrs, self.dw_out.peer_ptrs, c.ctrl.peer_ptrs,
+                            self.act, self.gu, self.dgu, self.dw_rows, self.arrive_target, self.gu_ready,
+                            self.expert_done, self.slot_out, self.rows_out, params["gate_proj"], params["up_proj"],
+                            params["down_proj"], grads["gate_proj"], grads["up_proj"], grads["down_proj"],
+                            c.wait_seconds)
+        return self.dx_acc.tensor.view(self.tokens, self.D), self.dw_out.tensor.view(self.tokens, self.k)
 
     def forward(self, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, params: dict,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -69,7 +103,7 @@ class FusedEPMoE:
                            self.my_counts, self.recv_x.peer_ptrs, self.recv_meta.peer_ptrs, self.recv_w.peer_ptrs,
                            self.counts_all.peer_ptrs, self.arrive.peer_ptrs, self.out_acc.peer_ptrs, c.ctrl.peer_ptrs,
                            self.act, self.arrive_target, self.act_ready, self.slot_out, self.rows_out,
-                           params["gate_proj"], params["up_proj"], params["down_proj"], c.wait_seconds)
+                           params["gate_proj"], params["up_proj"], params["down_proj"], c.wait_seconds, self.gu)
         res = self.out_acc.tensor.view(self.tokens, self.D)
         if out is not None:
             out.copy_(res)

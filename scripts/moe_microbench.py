@@ -65,6 +65,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--skip-baseline", action="store_true")
     ap.add_argument("--check", action="store_true", help="compare fused and baseline outputs")
+    ap.add_argument("--backward", action="store_true", help="also time the fused backward kernel")
     args = ap.parse_args(argv)
     rank, world, device = init_distributed()
     assert world > 1, "run under torchrun with at least 2 processes"
@@ -78,12 +79,20 @@ def main(argv=None):
     logits = make_logits(T, E, args.router, device, gen)
     w, idx = deepseek_router_from_logits(logits, torch.zeros(E, device=device), k, args.n_group, args.topk_group, 2.5)
     comm = Communicator(device=device, wait_seconds=20.0)
-    fused = FusedEPMoE(comm, T, D, I, E, k)
+    fused = FusedEPMoE(comm, T, D, I, E, k, training=args.backward)
     ms_fused = timed(lambda: fused.forward(x, w, idx, local), args.warmup, args.iters, device)
     _ext.check_status(device)
     rows = fused.rows_out.sum().item()
     res = {"world": world, "tokens_per_rank": T, "router": args.router, "d_model": D, "inter": I, "experts": E,
            "top_k": k, "dtype": "bf16", "fused_fwd_ms": ms_fused, "rows_this_rank": rows}
+    if args.backward:
+        dout = torch.randn(T, D, device=device, generator=gen).to(torch.bfloat16)
+        grads = {n: torch.zeros_like(t, dtype=torch.float32) for n, t in local.items()}
+        fused.forward(x, w, idx, local)
+        ms_bwd = timed(lambda: fused.backward(x, dout, w, idx, local, grads), args.warmup, args.iters, device)
+        _ext.check_status(device)
+        res["fused_bwd_ms"] = ms_bwd
+        res["bwd_tflops_this_rank"] = 2.0 * rows * 6 * D * I / ms_bwd / 1e9
     if not args.skip_baseline:
         base = NcclEPMoE(dist.group.WORLD, E)
         res["nccl_fwd_ms"] = timed(lambda: base.forward(x, w, idx, local), 1, max(1, args.iters // 2), device)

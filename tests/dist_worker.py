@@ -143,6 +143,54 @@ def run_ep(rank, world, device):
     return res
 
 
+def run_ep_bwd(rank, world, device):
+    """Fused expert-parallel MoE backward vs autograd of the dense evaluation with all experts."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.comm.symm import Communicator
+    from jax_gpt_b200.models.qwen35.moe import expert_forward_single
+    from jax_gpt_b200.parallel.expert_parallel import FusedEPMoE
+    tokens, D, I, E, k = 384, 512, 256, 16, 4
+    g = torch.Generator(device=device).manual_seed(3)
+    full = {"gate_proj": (torch.randn(E, D, I, device=device, generator=g) * 0.05).to(torch.bfloat16),
+            "up_proj": (torch.randn(E, D, I, device=device, generator=g) * 0.05).to(torch.bfloat16),
+            "down_proj": (torch.randn(E, I, D, device=device, generator=g) * 0.05).to(torch.bfloat16)}
+    el = E // world
+    local = {n: t[rank * el:(rank + 1) * el].contiguous() for n, t in full.items()}
+    comm = Communicator(device=device, wait_seconds=5.0)
+    fused = FusedEPMoE(comm, tokens, D, I, E, k, training=True)
+    res = {}
+    for step, mode in enumerate(["uniform", "skewed", "uniform"]):
+        gs = torch.Generator(device=device).manual_seed(100 * step + rank)
+        x = torch.randn(tokens, D, device=device, generator=gs).to(torch.bfloat16)
+        dout = torch.randn(tokens, D, device=device, generator=gs).to(torch.bfloat16)
+        logits = torch.randn(tokens, E, device=device, generator=gs)
+        if mode == "skewed":
+            logits[:, :3] += 6.0
+            logits[:, 5] = -1e9
+        w, idx = torch.softmax(logits, -1).topk(k, dim=-1)
+        w = w / w.sum(-1, keepdim=True)
+        grads = {n: torch.zeros_like(t, dtype=torch.float32) for n, t in local.items()}
+        out = fused.forward(x, w, idx, local).clone()
+        dx, dw = fused.backward(x, dout, w, idx, local, grads)
+        dx, dw = dx.clone(), dw.clone()
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        xr = x.float().requires_grad_(True)
+        wr = w.float().requires_grad_(True)
+        pr = {n: t.float().requires_grad_(True) for n, t in full.items()}
+        ref = expert_forward_single(xr, wr, idx, pr)
+        (ref * dout.float()).sum().backward()
+        res[f"{mode}{step}_out"] = rel(out, ref.detach())
+        res[f"{mode}{step}_dx"] = rel(dx, xr.grad)
+        res[f"{mode}{step}_dw"] = rel(dw, wr.grad)
+        for n in full:
+            gfull = pr[n].grad.clone()
+            dist.all_reduce(gfull)
+            res[f"{mode}{step}_d{n}"] = rel(grads[n], gfull[rank * el:(rank + 1) * el])
+        dist.barrier()
+    return res
+
+
 def main():
     what = sys.argv[1]
     out_path = sys.argv[2]
@@ -161,6 +209,8 @@ def main():
         res = run_fsdp_ag(rank, world, device)
     elif what == "ep":
         res = run_ep(rank, world, device)
+    elif what == "ep_bwd":
+        res = run_ep_bwd(rank, world, device)
     else:
         raise SystemExit(f"unknown test {what}")
     if rank == 0:

@@ -53,6 +53,12 @@ def test_fused_ep_moe_two_gpus(tmp_path):
             assert v < 2e-2, res
 
 
+def test_fused_ep_moe_backward_two_gpus(tmp_path):
+    res = _run("ep_bwd", tmp_path, port=29615)
+    for k, v in res.items():
+        assert v < 3e-2, res
+
+
 def test_bounded_wait_reports_timeout(cuda_device):
     """A flag that nothing sets: the kernel gives up after its budget, records the status
     and returns; the context stays usable."""
