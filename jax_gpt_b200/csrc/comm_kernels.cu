@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(512, 2) sharded_adamw_kernel(const __grid_cons
 
   if (blockIdx.x == 0) {
     if (threadIdx.x == 0) {
-      my->sq_local = 0.f;
+      my->sq_local = a.extra_sq != nullptr ? __ldcg(a.extra_sq) : 0.f;
       my->abort_flag = 0;
     }
     if (!flag_barrier(a.peer_ctrl, W, a.rank, 0, epoch, a.wait_budget_ns, a.status) && threadIdx.x == 0)

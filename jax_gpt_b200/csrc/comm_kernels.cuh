@@ -38,6 +38,8 @@ struct ShardedAdamWArgs {
   float beta1, beta2, eps, wd, clip;
   uint64_t wait_budget_ns;   // bound of every cross-rank wait
   int* status;
+  const float* extra_sq;     // optional: this rank's sum of squared gradients of parameters that are NOT in
+                             // the flat vector (expert-parallel weights); joins the global clipping norm
 };
 
 // Gradient reduce-scatter + global-norm clip + AdamW on the local shard + all-gather of the

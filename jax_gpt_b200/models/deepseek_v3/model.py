@@ -107,7 +107,7 @@ def moe_ffn(x: torch.Tensor, mp, c: DeepSeekV3Config, ep=None) -> torch.Tensor:
         w, idx = route_tokens(xf, mp["gate_weight"], mp["e_score_correction_bias"], c)
     with scope("moe_experts"):
         if ep is not None:
-            routed = ep.forward(xf, w, idx, mp)
+            routed = ep.forward(xf, w, idx, mp).to(x.dtype)
         else:
             from ..qwen35.moe import expert_forward_single
             routed = expert_forward_single(xf, w, idx, mp)

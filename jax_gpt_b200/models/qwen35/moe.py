@@ -98,11 +98,17 @@ def shared_expert_forward(x: torch.Tensor, params) -> torch.Tensor:
 
 def moe_layer(x: torch.Tensor, params, n_experts_per_token: int, n_devices: int = 1, axis_name: str = "tp",
               mesh=None, group=None, n_experts: Optional[int] = None) -> torch.Tensor:
-    """x (B,T,D) -> (B,T,D). With ``group`` (a process group) the routed experts run expert-parallel."""
+    """x (B,T,D) -> (B,T,D). With ``group`` the routed experts run expert-parallel: a process group
+    selects the all-to-all library path, a callable ``group(x, weights, idx, params, grads)`` (the fused
+    kernel runtime of parallel/expert_parallel.py) the one-kernel path; ``params`` then hold only this
+    rank's experts and, when training, their fp32 gradient buffers under ``<name>@grad``."""
     B, T, D = x.shape
     xf = x.reshape(B * T, D)
     w, idx = moe_routing(xf, params["gate_weight"], n_experts_per_token)
-    if group is not None:
+    if callable(group):
+        grads = {n: params.get(n + "@grad") for n in ("gate_proj", "up_proj", "down_proj")}
+        routed = group(xf, w, idx, params, grads).to(x.dtype)
+    elif group is not None:
         routed = expert_forward_ep(xf, w, idx, params, group, n_experts)
     else:
         routed = expert_forward_single(xf, w, idx, params)

@@ -86,6 +86,60 @@ class _AttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+def attn_bwd_chunked(q, k, v, out, dout, lse, causal=True, scale=None, chunk: int = 1024):
+    """Gradients from the forward kernel's (out, lse) with the probabilities recomputed one query
+    chunk at a time (library matmuls; memory O(chunk * T) per head group). Covers the head widths
+    that have a forward kernel but no backward kernel: 256 and the MLA shape 192 / 128.
+    q (B,T,H,D), k (B,T,Hkv,D), v (B,T,Hkv,Dv); lse (B,H,T) is the log2-sum-exp of scale*log2(e)*scores."""
+    B, T, H, D = q.shape
+    Hkv, Dv = k.shape[2], v.shape[3]
+    g = H // Hkv
+    scale = float(scale) if scale is not None else D ** -0.5
+    c2 = scale * 1.4426950408889634
+    dq = torch.empty_like(q)
+    dk = torch.zeros(B, T, Hkv, D, device=q.device, dtype=torch.float32)
+    dv = torch.zeros(B, T, Hkv, Dv, device=q.device, dtype=torch.float32)
+    delta = (out.float() * dout.float()).sum(-1)          # (B,T,H)
+    for b in range(B):
+        for hk in range(Hkv):
+            hs = slice(hk * g, (hk + 1) * g)
+            for q0 in range(0, T, chunk):
+                q1 = min(T, q0 + chunk)
+                kv1 = q1 if causal else T
+                kk, vv = k[b, :kv1, hk], v[b, :kv1, hk]                         # (kv1, D), (kv1, Dv)
+                qs = q[b, q0:q1, hs].permute(1, 0, 2)                           # (g, c, D)
+                do = dout[b, q0:q1, hs].permute(1, 0, 2)                        # (g, c, Dv)
+                s2 = torch.matmul(qs, kk.t()).float() * c2                      # (g, c, kv1)
+                p = torch.exp2(s2 - lse[b, hs, q0:q1, None])
+                if causal:
+                    qi = torch.arange(q0, q1, device=q.device)[:, None]
+                    p = p.masked_fill(torch.arange(kv1, device=q.device)[None, :] > qi, 0.0)
+                dp = torch.matmul(do, vv.t()).float()
+                ds = (p * (dp - delta[b, q0:q1, hs].t()[:, :, None]) * scale).to(q.dtype)
+                pb = p.to(q.dtype)
+                dq[b, q0:q1, hs] = torch.matmul(ds, kk).permute(1, 0, 2)
+                dk[b, :kv1, hk] += torch.matmul(ds.reshape(-1, kv1).t(), qs.reshape(-1, D)).float()
+                dv[b, :kv1, hk] += torch.matmul(pb.reshape(-1, kv1).t(), do.reshape(-1, Dv)).float()
+    return dq, dk.to(k.dtype), dv.to(v.dtype)
+
+
+class _AttnFwdKernelFn(torch.autograd.Function):
+    """Forward on the tcgen05 kernel, backward by chunked recomputation (head widths without a backward kernel)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        out, lse = attn_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = attn_bwd_chunked(q, k, v, out, dout.contiguous(), lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
 def supports_cuda_kernel(q, k) -> bool:
     return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and q.shape[1] == k.shape[1])
 
@@ -99,11 +153,13 @@ def supports_cuda_forward(q, k, v) -> bool:
 def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
     """Softmax attention over [B,T,H,D] tensors (GQA when k/v have fewer heads). Head widths
     64 / 128 run forward and backward on the tcgen05 kernels; 256 and the MLA shape (192 / 128)
-    run the forward kernel when no gradient is needed."""
+    run the forward kernel, and their gradients come from a chunked recomputation."""
     needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
     if supports_cuda_kernel(q, k) and v.shape[-1] == q.shape[-1]:
         return _AttnFn.apply(q, k, v, causal, scale)
-    if supports_cuda_forward(q, k, v) and not needs_grad:
+    if supports_cuda_forward(q, k, v):
+        if needs_grad:
+            return _AttnFwdKernelFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale)
         return attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale)[0]
     return attention_ref(q, k, v, causal, scale)
 
@@ -111,7 +167,9 @@ def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
 def mla_attention(q, k, v, scale: float):
     """Causal attention with different q/k and v head widths (MLA prefill: 192 / 128).
     q,k (B,T,H,dqk); v (B,T,H,dv)."""
-    if supports_cuda_forward(q, k, v) and not (torch.is_grad_enabled() and q.requires_grad):
+    if supports_cuda_forward(q, k, v):
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+            return _AttnFwdKernelFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), True, scale)
         return attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), True, scale)[0]
     B, T, H, dqk = q.shape
     qf, kf, vf = [t.float().permute(0, 2, 1, 3) for t in (q, k, v)]

@@ -51,6 +51,35 @@ def cross_entropy_fwd_bwd(logits, targets, vocab: int, scale: float, write_grad:
     return loss
 
 
+class _CrossEntropyMeanFn(torch.autograd.Function):
+    """Mean token cross-entropy on the fused kernel: one pass produces the per-row losses and overwrites
+    the logits with ``(softmax - onehot) / n_valid``; the backward hands that buffer on."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, vocab):
+        n_valid = (targets >= 0).sum().clamp_min(1).float()
+        rows = cross_entropy_fwd_bwd(logits, targets, vocab, 1.0, True)
+        ctx.save_for_backward(logits, n_valid)
+        return rows.sum() / n_valid
+
+    @staticmethod
+    def backward(ctx, g):
+        dlogits, n_valid = ctx.saved_tensors
+        return dlogits.mul_((g / n_valid).to(dlogits.dtype)), None, None
+
+
+def cross_entropy_mean(logits, targets, vocab=None):
+    """Mean cross-entropy over rows with target >= 0. logits (M, V') with V' >= vocab (padding columns
+    ignored). CUDA bf16 logits are CONSUMED (overwritten with their gradient)."""
+    vocab = logits.shape[-1] if vocab is None else vocab
+    logits = logits.reshape(-1, logits.shape[-1])
+    targets = targets.reshape(-1)
+    if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1:
+        return _CrossEntropyMeanFn.apply(logits, targets.to(torch.int32).contiguous(), vocab)
+    rows = cross_entropy_ref(logits, targets, vocab)
+    return rows.sum() / (targets >= 0).sum().clamp_min(1)
+
+
 def bias_grad(dy, out=None):
     """Column sums of a [M,N] bf16 matrix, accumulated into an fp32 vector."""
     if not dy.is_cuda:

@@ -23,9 +23,16 @@ def router_cuda(mode: int, logits, bias, k, n_group=1, topk_group=1, scale=1.0, 
     return w, ids
 
 
+def _needs_grad(t):
+    return torch.is_grad_enabled() and t.requires_grad
+
+
 def softmax_topk_router(logits: torch.Tensor, k: int):
     if _cuda_ok(logits, k):
-        w, ids = router_cuda(0, logits, None, k)
+        w, ids = router_cuda(0, logits.detach(), None, k)
+        if _needs_grad(logits):  # the kernel picks the experts; the weights are re-derived differentiably
+            w = torch.softmax(logits.float(), dim=-1).gather(1, ids.long())
+            w = w / w.sum(-1, keepdim=True)
         return w, ids.long()
     probs = torch.softmax(logits.float(), dim=-1)
     w, idx = probs.topk(k, dim=-1)
@@ -36,7 +43,10 @@ def deepseek_router_from_logits(logits: torch.Tensor, bias: torch.Tensor, k: int
                                 scale: float, norm_topk: bool = True):
     M, E = logits.shape
     if _cuda_ok(logits, k, n_group) and norm_topk:
-        w, ids = router_cuda(1, logits, bias, k, n_group, topk_group, scale)
+        w, ids = router_cuda(1, logits.detach(), bias, k, n_group, topk_group, scale)
+        if _needs_grad(logits):
+            w = torch.sigmoid(logits.float()).gather(1, ids.long())
+            w = w / (w.sum(-1, keepdim=True) + 1e-20) * scale
         return w, ids.long()
     s = torch.sigmoid(logits.float())
     choice = s + bias.float()

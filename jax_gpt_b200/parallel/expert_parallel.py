@@ -41,6 +41,7 @@ class FusedEPMoE:
         # every expert's region is padded to a multiple of 64 rows
         self.cap_rows = (int(tokens * top_k * cap_factor) + 64 * self.e_local + 127) // 128 * 128
         self.training = training
+        self.launch_token = 0    # identifies the forward launch whose state sits in the buffers
         dev = comm.device
         self.recv_x = comm.alloc(self.cap_rows * d_model, torch.bfloat16, zero=True)
         self.recv_meta = comm.alloc(self.cap_rows, torch.int32)
@@ -98,6 +99,7 @@ class FusedEPMoE:
         idx32 = idx.to(torch.int32).contiguous().view(-1)
         w32 = weights.to(torch.float32).contiguous().view(-1)
         ops.moe_prepare(idx32, self.my_counts, self.pos)
+        self.launch_token += 1
         self.out_acc.tensor.zero_()
         ops.ep_moe_forward(c.world, c.rank, self.k, self.e_local, self.cap_rows, x.contiguous(), idx32, w32, self.pos,
                            self.my_counts, self.recv_x.peer_ptrs, self.recv_meta.peer_ptrs, self.recv_w.peer_ptrs,
@@ -109,6 +111,77 @@ class FusedEPMoE:
             out.copy_(res)
             return out
         return res
+
+
+class _FusedEPMoEFn(torch.autograd.Function):
+    """Autograd node around one ``FusedEPMoE`` layer. Expert weights stay outside autograd: their fp32
+    gradients are accumulated by the backward kernel straight into ``grads`` (main-grad convention)."""
+
+    @staticmethod
+    def forward(ctx, x, weights, idx, layer, params, grads):
+        out = layer.forward(x, weights, idx, params)
+        ctx.layer, ctx.params, ctx.grads = layer, params, grads
+        ctx.token = layer.launch_token
+        ctx.save_for_backward(x, weights, idx)
+        return out.to(x.dtype)   # a copy: the symmetric accumulation buffer is reused by the next launch
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, weights, idx = ctx.saved_tensors
+        layer = ctx.layer
+        if layer.launch_token != ctx.token:
+            # another MoE layer used the buffers since: recompute this layer's dispatch and activations
+            layer.forward(x, weights, idx, ctx.params)
+        dx, dw = layer.backward(x, dout.to(torch.bfloat16), weights, idx, ctx.params, ctx.grads)
+        return dx.to(x.dtype), dw.to(weights.dtype), None, None, None, None
+
+
+def fused_ep_moe(layer: "FusedEPMoE", x, weights, idx, params, grads):
+    """Differentiable routed-expert sum. x (tokens, D) bf16; weights (tokens, k) fp32 (may require grad);
+    ``params`` / ``grads``: this rank's stacked expert weights (bf16) and their fp32 gradient buffers."""
+    return _FusedEPMoEFn.apply(x, weights, idx, layer, params, grads)
+
+
+class EPMoERuntime:
+    """What the model code calls for the routed experts of an expert-parallel layer: the fused kernels
+    of one ``FusedEPMoE`` buffer set shared by all layers of the same shape. With gradient buffers in
+    the layer's parameter dict (``<name>@grad``) and autograd on, the call is differentiable."""
+
+    def __init__(self, layer: FusedEPMoE):
+        self.layer = layer
+
+    def __call__(self, x, weights, idx, params, grads=None):
+        if grads is None:
+            grads = {n: params.get(n + "@grad") for n in ("gate_proj", "up_proj", "down_proj")}
+        train = torch.is_grad_enabled() and grads.get("gate_proj") is not None and self.layer.training
+        if train:
+            return fused_ep_moe(self.layer, x, weights, idx, params, grads)
+        return self.layer.forward(x, weights, idx, params).to(x.dtype)
+
+    def forward(self, x, weights, idx, params):
+        return self(x, weights, idx, params)
+
+
+def shard_experts(params: dict, rank: int, world: int, names=("gate_proj", "up_proj", "down_proj"), _path=()) -> dict:
+    """Copy of a parameter tree in which the stacked routed-expert weights (expert axis third from last)
+    keep only the experts ``[rank * E / world, (rank + 1) * E / world)`` of this rank."""
+    out = {}
+    for k, v in params.items():
+        if isinstance(v, dict):
+            out[k] = shard_experts(v, rank, world, names, _path + (k,))
+        elif k in names and v.dim() >= 3 and "mlp" not in _path:
+            E = v.shape[-3]
+            assert E % world == 0
+            el = E // world
+            out[k] = v.narrow(v.dim() - 3, rank * el, el).contiguous()
+        else:
+            out[k] = v
+    return out
+
+
+def is_expert_leaf(path, t, names=("gate_proj", "up_proj", "down_proj")) -> bool:
+    """Predicate for ``TreeTrainEngine(local=...)``: the stacked routed-expert weights."""
+    return path[-1] in names and t.dim() >= 3 and "shared" not in path[-1] and "mlp" not in path
 
 
 class NcclEPMoE:

@@ -101,13 +101,16 @@ class FusedShardedAdamW(_ShardedBase):
         self._make_shards(engine)
         self.n_total, self.n_decay = engine.flat.total, engine.flat.n_decay
 
-    def step(self, engine):
+    def step(self, engine, extra_sq=None):
+        """``extra_sq``: device scalar with this rank's sum of squared gradients of parameters kept
+        outside the flat vector (expert-parallel weights); it joins the global clipping norm."""
         h = engine.hyper
         mc_g = self.grad_buf.multicast_ptr if self.use_multimem else 0
         mc_p = self.param_buf.multicast_ptr if self.use_multimem else 0
         _ext.ops().sharded_adamw(self.world, self.rank, self.n_total, self.n_decay, self.grad_buf.peer_ptrs,
                                  self.param_buf.peer_ptrs, self.comm.ctrl.peer_ptrs, mc_g, mc_p, self.master, self.m,
-                                 self.v, engine.hp, h["b1"], h["b2"], 1e-8, h["wd"], h["clip"], self.comm.wait_seconds)
+                                 self.v, engine.hp, h["b1"], h["b2"], 1e-8, h["wd"], h["clip"], self.comm.wait_seconds,
+                                 extra_sq)
         engine.flat.grad.zero_()
 
     def grad_norm_sq(self) -> torch.Tensor:
@@ -126,11 +129,13 @@ class NcclShardedAdamW(_ShardedBase):
         self.sq = torch.zeros(1, device=self.master.device)
         self.shard_bf16 = torch.empty(self.master.numel(), device=self.master.device, dtype=torch.bfloat16)
 
-    def step(self, engine):
+    def step(self, engine, extra_sq=None):
         h = engine.hyper
         dist.reduce_scatter_tensor(self.red, engine.flat.grad, group=self.group)
         self.sq.zero_()
         misc.sumsq(self.red, self.sq)
+        if extra_sq is not None:
+            self.sq += extra_sq
         dist.all_reduce(self.sq, group=self.group)
         nd = min(max(self.n_decay - self.lo, 0), self.hi - self.lo)
         for a, b, wd in ((0, nd, h["wd"]), (nd, self.hi - self.lo, 0.0)):

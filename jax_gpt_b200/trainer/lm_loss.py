@@ -1,0 +1,28 @@
+"""Next-token losses of the function-style model families, in the form ``TreeTrainEngine`` expects
+(``loss_fn(tree, tokens, targets)``). The reference has no training path for these models (its
+trainer only knows GPT-2, jax_gpt/trainer/train_step.py:34-84); the loss is the same mean token
+cross-entropy."""
+from __future__ import annotations
+
+import torch
+
+from ..ops.misc import cross_entropy_mean
+
+
+def qwen35_loss_fn(config, ep=None):
+    """``ep``: None (all experts local), a process group (all-to-all path) or an ``EPMoERuntime``."""
+    from ..models.qwen35.model import forward
+
+    def loss_fn(tree, tokens, targets):
+        logits, _ = forward(tree, tokens, config, ep_group=ep)
+        return cross_entropy_mean(logits, targets, config.vocab_size)
+    return loss_fn
+
+
+def deepseek_v3_loss_fn(config, ep=None):
+    from ..models.deepseek_v3.model import forward
+
+    def loss_fn(tree, tokens, targets):
+        logits = forward(tree, tokens, config, ep=ep)
+        return cross_entropy_mean(logits, targets, config.vocab_size)
+    return loss_fn

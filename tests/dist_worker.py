@@ -191,6 +191,51 @@ def run_ep_bwd(rank, world, device):
     return res
 
 
+def run_moe_train(rank, world, device):
+    """Qwen3.5-style training with expert parallelism (fused MoE forward/backward kernels) and the fused
+    sharded optimizer for the dense weights, against one process that holds all experts and sees every
+    rank's batch as micro-batches."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.qwen35.config import Qwen35Config
+    from jax_gpt_b200.models.qwen35.model import init_params
+    from jax_gpt_b200.parallel.expert_parallel import EPMoERuntime, FusedEPMoE, is_expert_leaf, shard_experts
+    from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW
+    from jax_gpt_b200.trainer.lm_loss import qwen35_loss_fn
+    from jax_gpt_b200.trainer.tree_engine import TreeTrainEngine
+    cfg = Qwen35Config(d_model=256, vocab_size=512, n_layers=4, max_position_embeddings=128, gqa_n_q_heads=4,
+                       gqa_n_kv_heads=2, gqa_head_dim=64, delta_n_qk_heads=2, delta_n_v_heads=4, delta_qk_head_dim=32,
+                       delta_v_head_dim=32, delta_chunk_size=16, n_routed_experts=8, n_experts_per_token=2,
+                       moe_intermediate_size=256, shared_expert_intermediate_size=256)
+    B, T = 2, 64
+    full = init_params(cfg, 0, torch.float32)
+    hyper = dict(lr=2e-3, min_lr=2e-3, warmup_steps=0, grad_clip=1.0)
+    opt = FusedShardedAdamW(device=device, wait_seconds=10.0)
+    layer = FusedEPMoE(opt.comm, B * T, cfg.d_model, cfg.moe_intermediate_size, cfg.n_routed_experts,
+                       cfg.n_experts_per_token, training=True)
+    ep = EPMoERuntime(layer)
+    eng = TreeTrainEngine(shard_experts(full, rank, world), qwen35_loss_fn(cfg, ep), device=device, local=is_expert_leaf,
+                          dist_optimizer=opt, **hyper)
+    ref = TreeTrainEngine(full, qwen35_loss_fn(cfg, None), device=device, **hyper)
+    res = {"ep_loss": [], "ref_loss": []}
+    for step in range(4):
+        g = torch.Generator().manual_seed(1000)   # the same batch every step: the loss must fall
+        tok_all = torch.randint(0, cfg.vocab_size, (world, B, T + 1), generator=g).to(device)
+        mine = tok_all[rank]
+        out = eng.train_step(mine[:, :-1].contiguous(), mine[:, 1:].contiguous())
+        loss = out["loss"].clone()
+        dist.all_reduce(loss)
+        for r in range(world):
+            ref.micro_step(tok_all[r][:, :-1].contiguous(), tok_all[r][:, 1:].contiguous())
+        rout = ref.apply_gradients()
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        res["ep_loss"].append(loss.item() / world)
+        res["ref_loss"].append(rout["loss"].item())
+        res.setdefault("gnorm_ep", []).append(out["grad_norm_sq"].item() ** 0.5 / world)
+        res.setdefault("gnorm_ref", []).append(rout["grad_norm_sq"].item() ** 0.5 / world)
+    return res
+
+
 def main():
     what = sys.argv[1]
     out_path = sys.argv[2]
@@ -211,6 +256,8 @@ def main():
         res = run_ep(rank, world, device)
     elif what == "ep_bwd":
         res = run_ep_bwd(rank, world, device)
+    elif what == "moe_train":
+        res = run_moe_train(rank, world, device)
     else:
         raise SystemExit(f"unknown test {what}")
     if rank == 0:

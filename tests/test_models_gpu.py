@@ -68,3 +68,52 @@ def test_deepseek_v3_forward_on_gpu(cuda_device):
         l2 = forward(pg, tok[:, 158:159].to(cuda_device), cfg, cache, [0, 1], is_decode=True)
         assert _close(l2[:, 0], ref[:, 158])
     _ext.check_status(cuda_device)
+
+
+def _lm_batch(vocab, B, T, device, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    tok = torch.randint(0, vocab, (B, T + 1), generator=g).to(device)
+    return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+
+
+def test_qwen35_bf16_training_steps_on_gpu(cuda_device):
+    """bf16 training through the CUDA ops (tcgen05 linears fwd/dgrad/wgrad, fused norm, attention forward
+    kernel + chunked backward at head width 256, fused cross-entropy, AdamW kernel): loss starts at ln(V)
+    and decreases on a repeated batch."""
+    import math
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.qwen35.config import Qwen35Config
+    from jax_gpt_b200.models.qwen35.model import init_params
+    from jax_gpt_b200.trainer.lm_loss import qwen35_loss_fn
+    from jax_gpt_b200.trainer.tree_engine import TreeTrainEngine
+    cfg = Qwen35Config(d_model=256, vocab_size=1024, n_layers=4, max_position_embeddings=256, gqa_n_q_heads=2,
+                       gqa_n_kv_heads=1, gqa_head_dim=256, delta_n_qk_heads=2, delta_n_v_heads=4, delta_qk_head_dim=64,
+                       delta_v_head_dim=64, delta_chunk_size=32, n_routed_experts=8, n_experts_per_token=2,
+                       moe_intermediate_size=128, shared_expert_intermediate_size=128)
+    eng = TreeTrainEngine(init_params(cfg, 0, torch.float32), qwen35_loss_fn(cfg), device=cuda_device, lr=2e-3,
+                          min_lr=2e-3, warmup_steps=0)
+    tokens, targets = _lm_batch(cfg.vocab_size, 2, 128, cuda_device)
+    losses = [float(eng.train_step(tokens, targets)["loss"]) for _ in range(8)]
+    _ext.check_status(cuda_device)
+    assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5, losses
+    assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_deepseek_v3_bf16_training_steps_on_gpu(cuda_device):
+    """Same for the MLA + group-limited MoE family (attention shape 192 / 128)."""
+    import math
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
+    from jax_gpt_b200.models.deepseek_v3.model import init_params
+    from jax_gpt_b200.trainer.lm_loss import deepseek_v3_loss_fn
+    from jax_gpt_b200.trainer.tree_engine import TreeTrainEngine
+    cfg = DeepSeekV3Config.tiny().replace(d_model=256, vocab_size=1024, n_heads=4, qk_nope_head_dim=128,
+                                          qk_rope_head_dim=64, v_head_dim=128, q_lora_rank=128, kv_lora_rank=128,
+                                          moe_intermediate_size=128, dense_intermediate_size=512)
+    eng = TreeTrainEngine(init_params(cfg, 0, torch.float32), deepseek_v3_loss_fn(cfg), device=cuda_device, lr=2e-3,
+                          min_lr=2e-3, warmup_steps=0)
+    tokens, targets = _lm_batch(cfg.vocab_size, 2, 128, cuda_device)
+    losses = [float(eng.train_step(tokens, targets)["loss"]) for _ in range(8)]
+    _ext.check_status(cuda_device)
+    assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5, losses
+    assert losses[-1] < losses[0] - 0.5, losses

@@ -59,6 +59,17 @@ def test_fused_ep_moe_backward_two_gpus(tmp_path):
         assert v < 3e-2, res
 
 
+def test_qwen35_expert_parallel_training_matches_single_process(tmp_path):
+    res = _run("moe_train", tmp_path, port=29616)
+    assert res["ep_loss"][0] > 5.5                      # ln(512) = 6.24 at random init
+    assert res["ref_loss"][-1] < res["ref_loss"][0], res
+    assert res["ep_loss"][-1] < res["ep_loss"][0], res
+    for a, b in zip(res["ep_loss"], res["ref_loss"]):
+        assert abs(a - b) < 0.05 * b, res
+    for a, b in zip(res["gnorm_ep"], res["gnorm_ref"]):
+        assert abs(a - b) < 0.1 * b + 1e-3, res
+
+
 def test_bounded_wait_reports_timeout(cuda_device):
     """A flag that nothing sets: the kernel gives up after its budget, records the status
     and returns; the context stays usable."""
