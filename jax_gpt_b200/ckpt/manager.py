@@ -38,6 +38,20 @@ def _unflatten(flat):
     return out
 
 
+def save_tree(path: str, tree: dict) -> None:
+    """Writes a nested tensor dict as ONE safetensors file with '.'-joined keys (written to ``.tmp`` and renamed)."""
+    from safetensors.torch import save_file
+    flat = {k: v.detach().to("cpu").contiguous() for k, v in flatten(tree).items()}
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    save_file(flat, path + ".tmp")
+    os.replace(path + ".tmp", path)
+
+
+def load_tree(path: str, device="cpu") -> dict:
+    from safetensors.torch import load_file
+    return _unflatten(load_file(path, device=str(device)))
+
+
 def _model_params(model):
     if hasattr(model, "params"):
         return model.params() if callable(model.params) else model.params

@@ -3,6 +3,12 @@
 
     python scripts/train.py --preset gpt2 --synthetic --max_steps=50 --micro_batch_size=16 --seq_len=1024
     torchrun --nproc-per-node 8 --master-addr 127.0.0.1 scripts/train.py --preset gpt2 --synthetic ...
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 scripts/train.py --preset qwen35-mini --synthetic ...
+    python scripts/train.py --preset deepseek-v3-tiny --synthetic --max_steps=20 --micro_batch_size=2 --seq_len=64
+
+``--preset qwen35-<tiny|mini|mid|ns>`` / ``deepseek-v3-<tiny|train8>`` train the MoE families: experts
+are sharded over the ranks (fused dispatch / grouped GEMM / combine kernels, forward and backward),
+dense weights go through the fused sharded optimizer.
 
 Every TrainConfig field is a ``--name=value`` flag. Flow: process group -> model -> optimizer and
 state (fused engine on CUDA; sharded fused AdamW across ranks) -> resume from the latest
@@ -19,6 +25,81 @@ from utils import get_tokenizer, gpt_config, init_distributed  # noqa: F401  (al
 import torch
 
 
+def moe_config(preset: str):
+    """(family, config) of a ``qwen35-*`` / ``deepseek-v3-*`` preset."""
+    if preset.startswith("qwen35-"):
+        from utils import qwen_config
+        return "qwen35", qwen_config(preset.split("-", 1)[1])
+    from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
+    name = preset.split("-", 2)[2]
+    return "deepseek_v3", {"tiny": DeepSeekV3Config.tiny, "train8": DeepSeekV3Config.eight_layer,
+                           "full": DeepSeekV3Config.full}[name]()
+
+
+def train_moe(args, tc, rank, world, device):
+    """Loop for the function-style MoE models on ``TreeTrainEngine``."""
+    import os
+
+    from jax_gpt_b200.data.pipeline import DataPipeline
+    from jax_gpt_b200.data.tokenize import write_synthetic
+    from jax_gpt_b200.trainer import MetricsLogger
+    from jax_gpt_b200.trainer.lm_loss import deepseek_v3_loss_fn, qwen35_loss_fn
+    from jax_gpt_b200.trainer.tree_engine import TreeTrainEngine
+    family, cfg = moe_config(args.preset)
+    if family == "qwen35":
+        from jax_gpt_b200.models.qwen35.model import init_params
+        make_loss = qwen35_loss_fn
+    else:
+        from jax_gpt_b200.models.deepseek_v3.model import init_params
+        make_loss = deepseek_v3_loss_fn
+    if args.synthetic and rank == 0 and not os.path.exists(os.path.join(tc.local_data_path, "train.bin")):
+        write_synthetic(tc.local_data_path, args.synthetic_tokens, cfg.vocab_size, tc.seed)
+    if world > 1:
+        torch.distributed.barrier()
+    params = init_params(cfg, tc.seed, torch.float32)
+    ep = dist_opt = local = None
+    on_gpu = device.type == "cuda"
+    if world > 1 and on_gpu:
+        from jax_gpt_b200.parallel.expert_parallel import EPMoERuntime, FusedEPMoE, is_expert_leaf, shard_experts
+        from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW, NcclShardedAdamW
+        dist_opt = NcclShardedAdamW(device=device) if args.nccl_optimizer else FusedShardedAdamW(device=device)
+        if not args.nccl_optimizer and cfg.d_model % 256 == 0 and cfg.moe_intermediate_size % 256 == 0:
+            layer = FusedEPMoE(dist_opt.comm, tc.micro_batch_size * tc.seq_len, cfg.d_model, cfg.moe_intermediate_size,
+                               cfg.n_routed_experts, cfg.n_experts_per_token, training=True)
+            ep, local = EPMoERuntime(layer), is_expert_leaf
+            params = shard_experts(params, rank, world)
+    eng = TreeTrainEngine(params, make_loss(cfg, ep), device=device, local=local,
+                          compute_dtype=torch.bfloat16 if on_gpu else torch.float32, lr=tc.learning_rate,
+                          min_lr=tc.min_lr, warmup_steps=tc.warmup_steps, lr_decay_steps=tc.lr_decay_steps,
+                          weight_decay=tc.weight_decay, beta1=tc.beta1, beta2=tc.beta2, grad_clip=tc.grad_clip,
+                          dist_optimizer=dist_opt)
+    del params
+    data = DataPipeline(tc, "train")
+    logger = MetricsLogger(tc, cfg, jsonl_path=args.jsonl if rank == 0 else "")
+    tokens_per_step = tc.micro_batch_size * tc.seq_len * tc.grad_accum_steps * world
+    if rank == 0:
+        print(f"{args.preset}: {eng.n_params() / 1e6:.1f}M parameters on this rank, expert parallel: {ep is not None}")
+    out, since = {}, 0
+    while eng.step_count < tc.max_steps:
+        for _ in range(tc.grad_accum_steps):
+            x, y = data.get_batch()
+            eng.micro_step(x.to(device, non_blocking=True), y.to(device, non_blocking=True))
+        out = eng.apply_gradients()
+        since += tokens_per_step
+        if eng.step_count % tc.log_interval == 0:
+            logger.log(eng.step_count, {"loss": out["loss"], "grad_norm": out["grad_norm_sq"].sqrt() * out["grad_scale"],
+                                        "lr": out["lr"]}, since)
+            since = 0
+    if rank == 0 and out:
+        print(f"done: step {eng.step_count} loss {float(out['loss']):.4f}")
+    if tc.checkpoint_dir and tc.save_interval > 0 and rank == 0 and dist_opt is None:
+        from jax_gpt_b200.ckpt.manager import save_tree
+        save_tree(os.path.join(tc.checkpoint_dir, f"{args.preset}_step{eng.step_count}.safetensors"), eng.master_tree())
+    data.close()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
 def main(argv=None):
     from jax_gpt_b200.data.pipeline import DataPipeline
     from jax_gpt_b200.data.tokenize import write_synthetic
@@ -28,7 +109,8 @@ def main(argv=None):
     from jax_gpt_b200.trainer.checkpointing import CheckpointManager
 
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--preset", default="gpt2", help="gpt2 | gpt2-medium | gpt2-large | gpt2-xl | gpt2-tiny")
+    ap.add_argument("--preset", default="gpt2", help="gpt2 | gpt2-medium | gpt2-large | gpt2-xl | gpt2-tiny | qwen35-<tiny|mini|mid|ns> | "
+                    "deepseek-v3-<tiny|train8>")
     ap.add_argument("--synthetic", action="store_true", help="train on uniform-random token ids written to local_data_path")
     ap.add_argument("--synthetic_tokens", type=int, default=8_000_000)
     ap.add_argument("--nccl_optimizer", action="store_true", help="multi-GPU: NCCL reduce-scatter/all-gather baseline")
@@ -39,6 +121,8 @@ def main(argv=None):
         ap.error(f"unknown arguments: {rest}")
 
     rank, world, device = init_distributed()
+    if args.preset.startswith(("qwen35-", "deepseek-v3-")):
+        return train_moe(args, tc.replace(dp=world), rank, world, device)
     cfg = gpt_config(args.preset)
     tc = tc.replace(dp=world)
     if args.synthetic and rank == 0:
