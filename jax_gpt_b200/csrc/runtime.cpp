@@ -280,10 +280,101 @@ class AsyncWriter {
   std::thread worker_;
 };
 
+// ------------------------------------------------------------------------------------------------
+// Block-table manager of the paged KV cache: a free list of pages, the page list and token count of
+// every sequence, and host mirrors (pinned when CUDA is present) of the block table and the length
+// vector that the cache uploads with one asynchronous copy when they change.
+class PageTable {
+ public:
+  PageTable(int64_t n_pages, int64_t page_size, int64_t max_seqs, int64_t max_pages, bool pin)
+      : page_size_(page_size), max_pages_(max_pages), owned_(max_seqs, 0) {
+    TORCH_CHECK(n_pages > 0 && page_size > 0 && max_seqs > 0 && max_pages > 0, "page table: bad sizes");
+    auto opt = at::TensorOptions().dtype(at::kInt).pinned_memory(pin);
+    table_ = at::full({max_seqs, max_pages}, -1, opt);
+    lens_ = at::zeros({max_seqs}, opt);
+    free_.reserve(n_pages);
+    for (int64_t p = n_pages - 1; p >= 0; --p) free_.push_back(static_cast<int32_t>(p));
+  }
+  // Makes sequence `seq` own enough pages for `new_len` tokens; returns how many pages were added.
+  int64_t reserve(int64_t seq, int64_t new_len) {
+    std::lock_guard<std::mutex> l(mu_);
+    check_seq(seq);
+    const int64_t need = (new_len + page_size_ - 1) / page_size_;
+    TORCH_CHECK(need <= max_pages_, "paged cache: sequence ", seq, " needs ", need, " pages, the block table has ",
+                max_pages_, " columns");
+    const int64_t have = owned_[seq];
+    if (need <= have) return 0;
+    TORCH_CHECK(need - have <= static_cast<int64_t>(free_.size()), "paged cache exhausted: want ", need - have,
+                " pages, ", free_.size(), " free");
+    int32_t* row = table_.data_ptr<int32_t>() + seq * max_pages_;
+    for (int64_t i = have; i < need; ++i) {
+      row[i] = free_.back();
+      free_.pop_back();
+    }
+    owned_[seq] = need;
+    ++version_;
+    return need - have;
+  }
+  void advance(const std::vector<int64_t>& seqs, int64_t n) {
+    std::lock_guard<std::mutex> l(mu_);
+    int32_t* lens = lens_.data_ptr<int32_t>();
+    for (int64_t s : seqs) {
+      check_seq(s);
+      TORCH_CHECK((lens[s] + n + page_size_ - 1) / page_size_ <= owned_[s], "paged cache: advance past the reserved pages");
+      lens[s] += static_cast<int32_t>(n);
+    }
+    ++version_;
+  }
+  void release(int64_t seq) {
+    std::lock_guard<std::mutex> l(mu_);
+    check_seq(seq);
+    int32_t* row = table_.data_ptr<int32_t>() + seq * max_pages_;
+    for (int64_t i = owned_[seq] - 1; i >= 0; --i) {
+      free_.push_back(row[i]);
+      row[i] = -1;
+    }
+    owned_[seq] = 0;
+    lens_.data_ptr<int32_t>()[seq] = 0;
+    ++version_;
+  }
+  int64_t length(int64_t seq) {
+    std::lock_guard<std::mutex> l(mu_);
+    check_seq(seq);
+    return lens_.data_ptr<int32_t>()[seq];
+  }
+  int64_t n_free() {
+    std::lock_guard<std::mutex> l(mu_);
+    return static_cast<int64_t>(free_.size());
+  }
+  int64_t version() {
+    std::lock_guard<std::mutex> l(mu_);
+    return version_;
+  }
+  Tensor table() { return table_; }
+  Tensor lens() { return lens_; }
+
+ private:
+  void check_seq(int64_t s) const { TORCH_CHECK(s >= 0 && s < static_cast<int64_t>(owned_.size()), "paged cache: bad sequence id ", s); }
+  int64_t page_size_, max_pages_;
+  std::vector<int64_t> owned_;
+  std::vector<int32_t> free_;
+  Tensor table_, lens_;
+  int64_t version_ = 0;
+  std::mutex mu_;
+};
+
 std::mutex g_mu;
 std::unordered_map<int64_t, std::unique_ptr<TokenLoader>> g_loaders;
 std::unordered_map<int64_t, std::unique_ptr<AsyncWriter>> g_writers;
+std::unordered_map<int64_t, std::unique_ptr<PageTable>> g_tables;
 int64_t g_next = 1;
+
+PageTable* page_table(int64_t h) {
+  std::lock_guard<std::mutex> l(g_mu);
+  auto it = g_tables.find(h);
+  TORCH_CHECK(it != g_tables.end(), "unknown page-table handle ", h);
+  return it->second.get();
+}
 
 TokenLoader* loader(int64_t h) {
   std::lock_guard<std::mutex> l(g_mu);
@@ -341,6 +432,33 @@ void b200_register_runtime(torch::Library& m) {
   m.def("writer_wait(int handle, float timeout_s) -> bool", [](int64_t h, double t) { return writer(h)->wait(t); });
   m.def("writer_pending(int handle) -> int", [](int64_t h) { return writer(h)->pending(); });
   m.def("writer_last_error(int handle) -> str", [](int64_t h) { return writer(h)->last_error(); });
+  m.def("pagetable_create(int n_pages, int page_size, int max_seqs, int max_pages, bool pin) -> int",
+        [](int64_t n, int64_t ps, int64_t ms, int64_t mp, bool pin) {
+          auto p = std::make_unique<PageTable>(n, ps, ms, mp, pin);
+          std::lock_guard<std::mutex> l(g_mu);
+          g_tables[g_next] = std::move(p);
+          return g_next++;
+        });
+  m.def("pagetable_reserve(int handle, int[] seqs, int[] new_lens) -> int",
+        [](int64_t h, std::vector<int64_t> seqs, std::vector<int64_t> lens) {
+          TORCH_CHECK(seqs.size() == lens.size(), "pagetable_reserve: one length per sequence");
+          int64_t added = 0;
+          for (size_t i = 0; i < seqs.size(); ++i) added += page_table(h)->reserve(seqs[i], lens[i]);
+          return added;
+        });
+  m.def("pagetable_advance(int handle, int[] seqs, int n) -> ()",
+        [](int64_t h, std::vector<int64_t> seqs, int64_t n) { page_table(h)->advance(seqs, n); });
+  m.def("pagetable_release(int handle, int seq) -> ()", [](int64_t h, int64_t s) { page_table(h)->release(s); });
+  m.def("pagetable_length(int handle, int seq) -> int", [](int64_t h, int64_t s) { return page_table(h)->length(s); });
+  m.def("pagetable_n_free(int handle) -> int", [](int64_t h) { return page_table(h)->n_free(); });
+  m.def("pagetable_version(int handle) -> int", [](int64_t h) { return page_table(h)->version(); });
+  m.def("pagetable_tensors(int handle) -> (Tensor, Tensor)", [](int64_t h) {
+    return std::make_tuple(page_table(h)->table(), page_table(h)->lens());
+  });
+  m.def("pagetable_close(int handle) -> ()", [](int64_t h) {
+    std::lock_guard<std::mutex> l(g_mu);
+    g_tables.erase(h);
+  });
   m.def("writer_close(int handle) -> ()", [](int64_t h) {
     std::unique_ptr<AsyncWriter> p;
     {

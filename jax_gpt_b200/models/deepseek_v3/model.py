@@ -146,25 +146,58 @@ def mla_prefill(x, ap, c: DeepSeekV3Config, rope, pos0: int = 0):
 
 
 def mla_decode_absorbed(x, ap, c: DeepSeekV3Config, rope, cache: PagedCache, layer: int, seq_ids: List[int]):
-    """One new token per sequence over the paged latent cache (weights absorbed).
-    x (B,1,D). The new token's latent must already be in the cache (not yet committed)."""
+    """One new token per sequence over the paged latent cache (weights absorbed). x (B,1,D).
+    The new token's latent is appended to the cache here (lengths are committed once per model step)."""
+    from ...ops.mla_decode import mla_paged_decode
     B = x.shape[0]
     H, dn, dr, dv, kvr = c.n_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim, c.kv_lora_rank
-    outs = []
     wkv = ap["kv_b_proj"].reshape(kvr, H, dn + dv)
     w_uk, w_uv = wkv[..., :dn], wkv[..., dn:]          # (kvr,H,dn), (kvr,H,dv)
-    for b, sid in enumerate(seq_ids):
-        pos = cache.length(sid)
-        q_nope, q_rope, c_new, k_new = mla_project(x[b:b + 1], ap, c, rope, pos)
-        cache.append(layer, [sid], torch.cat([c_new, k_new], dim=-1))
-        lat = cache.gather(layer, sid, pos + 1).float()    # (S, kvr+dr)
-        q_lat = torch.einsum("hd,khd->hk", q_nope[0, 0].float(), w_uk.float())       # (H,kvr)
-        s = (q_lat @ lat[:, :kvr].t() + q_rope[0, 0].float() @ lat[:, kvr:].t()) * c.softmax_scale
-        p = torch.softmax(s, dim=-1)
-        o_lat = p @ lat[:, :kvr]                                                        # (H,kvr)
-        o = torch.einsum("hk,khd->hd", o_lat, w_uv.float()).reshape(1, 1, H * dv).to(x.dtype)
-        outs.append(linear(o, ap["o_proj"]))
-    return torch.cat(outs, dim=0)
+    lens = [cache.length(s) for s in seq_ids]
+    if len(set(lens)) == 1:
+        q_nope, q_rope, c_new, k_new = mla_project(x, ap, c, rope, lens[0])
+    else:  # ragged batch: every sequence has its own rotary position
+        parts = [mla_project(x[b:b + 1], ap, c, rope, lens[b]) for b in range(B)]
+        q_nope, q_rope, c_new, k_new = [torch.cat([p[i] for p in parts], dim=0) for i in range(4)]
+    cache.append(layer, seq_ids, torch.cat([c_new, k_new], dim=-1))
+    # absorb W_uk into the query: (B,H,dn) x (kvr,H,dn) -> (B,H,kvr)
+    q_lat = torch.einsum("bhd,khd->bhk", q_nope[:, 0], w_uk.to(q_nope.dtype))
+    q_full = torch.cat([q_lat, q_rope[:, 0]], dim=-1).contiguous()
+    if _decode_kernel_ok(q_full, cache, kvr):
+        # the kernel reads the lengths from the device: they must count the token appended above
+        o_lat = _decode_with_pending_token(q_full, cache, layer, seq_ids, c.softmax_scale)
+    else:
+        outs = []
+        for b, sid in enumerate(seq_ids):
+            lat = cache.gather(layer, sid, lens[b] + 1).float()
+            s = (q_full[b].float() @ lat.t()) * c.softmax_scale
+            outs.append(torch.softmax(s, dim=-1) @ lat[:, :kvr])
+        o_lat = torch.stack(outs).to(x.dtype)
+    o = torch.einsum("bhk,khd->bhd", o_lat, w_uv.to(o_lat.dtype)).reshape(B, 1, H * dv)
+    return linear(o, ap["o_proj"])
+
+
+def _decode_kernel_ok(q_full, cache, kvr) -> bool:
+    from ...ops.mla_decode import supports_cuda
+    return supports_cuda(q_full, cache, kvr)
+
+
+def _decode_with_pending_token(q_full, cache, layer, seq_ids, scale):
+    from ...ops.mla_decode import mla_paged_decode
+    ids = cache.seq_id_tensor(seq_ids).long()
+    cache.seq_lens[ids] += 1          # count the appended, not yet committed token for this launch
+    try:
+        return mla_paged_decode(q_full, cache, layer, seq_ids, scale, n_splits=_splits_for(cache, seq_ids, q_full))
+    finally:
+        cache.seq_lens[ids] -= 1
+
+
+def _splits_for(cache, seq_ids, q_full) -> int:
+    B, H, _ = q_full.shape
+    sms = torch.cuda.get_device_properties(q_full.device).multi_processor_count
+    ctas = B * ((H + 31) // 32)
+    longest = max(cache.length(s) for s in seq_ids) + 1
+    return max(1, min(sms // max(ctas, 1), (longest + 127) // 128, 32))
 
 
 # ------------------------------------------------------------------------------------------------

@@ -117,3 +117,28 @@ def test_deepseek_v3_bf16_training_steps_on_gpu(cuda_device):
     _ext.check_status(cuda_device)
     assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5, losses
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_deepseek_v3_paged_decode_kernel_matches_prefill(cuda_device):
+    """Decode steps through the paged-MLA tcgen05 kernel (latent 512 + 64, 64-token pages) reproduce the
+    logits of a full prefill over the same tokens."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
+    from jax_gpt_b200.models.deepseek_v3.model import forward, init_params, make_cache
+    c = DeepSeekV3Config.tiny().replace(d_model=256, vocab_size=512, n_heads=16, qk_nope_head_dim=128,
+                                        qk_rope_head_dim=64, v_head_dim=128, q_lora_rank=128, kv_lora_rank=512,
+                                        moe_intermediate_size=128, dense_intermediate_size=512, page_size=64,
+                                        max_position_embeddings=512)
+    p = _to(init_params(c, 1), cuda_device, torch.bfloat16)
+    tok = torch.randint(0, c.vocab_size, (3, 140), generator=torch.Generator().manual_seed(2)).to(cuda_device)
+    with torch.no_grad():
+        full = forward(p, tok, c)
+        cache = make_cache(c, 16, 4, 4, torch.bfloat16, cuda_device)
+        outs = [forward(p, tok[:, :130], c, cache, [2, 0, 1])]
+        for t in range(130, 140):
+            outs.append(forward(p, tok[:, t:t + 1], c, cache, [2, 0, 1], is_decode=True))
+    torch.cuda.synchronize()
+    _ext.check_status(cuda_device)
+    got = torch.cat(outs, 1)
+    assert cache.length(0) == 140
+    assert _close(got[:, 130:], full[:, 130:]), ((got - full).abs().max().item())

@@ -119,3 +119,35 @@ def test_fp8_blockscaled_gemm(cuda_device, M, N, K):
     assert _rel(out, x.float() @ w.float().t()) < 6e-2   # and the quantisation error itself stays small
     lin = RP.Fp8Linear(w.t().contiguous())
     assert _rel(lin(x), x.float() @ w.float().t()) < 6e-2
+
+
+@pytest.mark.parametrize("heads,n_splits", [(16, 1), (16, 0), (128, 3), (40, 0)])
+def test_mla_paged_decode_and_paged_write(cuda_device, heads, n_splits):
+    """Ragged batch over the paged latent cache: the tcgen05 decode kernel vs fp32 math on the gathered
+    pages; the rows get into their pages through the paged write kernel."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.cache.paged import PagedCache
+    from jax_gpt_b200.ops.mla_decode import mla_paged_decode, mla_paged_decode_ref
+    lens = [1, 63, 64, 65, 128, 200, 1000, 2309]
+    B = len(lens)
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    cache = PagedCache(2, 576, n_pages=80, page_size=64, max_seqs=16, max_pages_per_seq=40, device=cuda_device)
+    ids = [3, 0, 7, 1, 12, 5, 9, 2]
+    # interleave the appends so that the page lists are not contiguous
+    for chunk in range(3):
+        for b, sid in enumerate(ids):
+            n = lens[b] // 3 if chunk < 2 else lens[b] - 2 * (lens[b] // 3)
+            if n:
+                rows = torch.randn(1, n, 576, device=cuda_device, generator=g).to(torch.bfloat16)
+                cache.append(1, [sid], rows, commit=True)
+    assert [cache.length(s) for s in ids] == lens
+    q = (torch.randn(B, heads, 576, device=cuda_device, generator=g) * 0.3).to(torch.bfloat16)
+    scale = 192 ** -0.5
+    out = mla_paged_decode(q, cache, 1, ids, scale, n_splits=n_splits)
+    torch.cuda.synchronize()
+    _ext.check_status(cuda_device)
+    ref = mla_paged_decode_ref(q, cache, 1, ids, scale, 512)
+    err = (out.float() - ref.float()).abs().max().item()
+    assert err < 3e-2, err
+    rel = ((out.float() - ref.float()).norm() / ref.float().norm()).item()
+    assert rel < 1.5e-2, rel
