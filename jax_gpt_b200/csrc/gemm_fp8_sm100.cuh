@@ -1,5 +1,6 @@
 // Launcher of the block-scaled FP8 GEMM (gemm_fp8_sm100.cu).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -10,5 +11,11 @@ namespace b200 {
 cudaError_t launch_gemm_fp8_blockscaled(const uint8_t* a_q, const float* a_scales, const uint8_t* b_q,
                                         const float* b_scales, void* out, int64_t ldo, int out_f32, int M, int N, int K,
                                         int* status, cudaStream_t stream);
+
+// Hardware block-scaled variant (gemm_mxfp8_sm100.cu): the scales are UE8M0 exponent bytes in the packed
+// 512-byte-chunk layout described there ([ceil(rows/128), K/128, 512]); out bf16 [M, ldo].
+cudaError_t launch_gemm_mxfp8(const uint8_t* a_q, const uint8_t* sfa_packed, const uint8_t* b_q,
+                              const uint8_t* sfb_packed, __nv_bfloat16* out, int64_t ldo, int M, int N, int K, int* status,
+                              cudaStream_t stream);
 
 }  // namespace b200

@@ -105,6 +105,36 @@ def fp8_gemm(a_q, a_s, b_q, b_s, out_dtype=torch.bfloat16):
     return out
 
 
+def pack_scales_ue8m0(scales: torch.Tensor, rows: int, per_row: bool) -> torch.Tensor:
+    """Power-of-two fp32 block scales -> the packed UE8M0 layout the hardware-scaled GEMM reads:
+    ``[ceil(rows/128), K/128, 512]`` bytes, byte ``(r % 32) * 16 + (r / 32) * 4 + j`` of a chunk being the
+    exponent of row r for the j-th 32-wide K block of the slab (all four j equal here).
+    ``per_row``: scales are (rows, K/128) (1x128 activation scales); else (ceil(rows/128), K/128)
+    (128x128 weight scales)."""
+    e = (torch.log2(scales.float()).round() + 127).clamp(0, 254).to(torch.uint8)
+    KS = e.shape[1]
+    MB = (rows + 127) // 128
+    if per_row:
+        pad = torch.full((MB * 128, KS), 127, dtype=torch.uint8, device=e.device)
+        pad[:rows] = e
+        t = pad.view(MB, 4, 32, KS).permute(0, 3, 2, 1)                  # (MB, KS, lane, group)
+        return t.unsqueeze(-1).expand(MB, KS, 32, 4, 4).reshape(MB, KS, 512).contiguous()
+    return e[:MB, :, None].expand(MB, KS, 512).contiguous()
+
+
+def mxfp8_gemm(a_q, a_s, b_q, b_s):
+    """Same product as ``fp8_gemm`` for POWER-OF-TWO scales, with the scaling done by the tensor core
+    (tcgen05 block-scaled MMA). a_s (M, K/128), b_s (ceil(N/128), K/128) fp32 powers of two. Returns bf16."""
+    if not a_q.is_cuda:
+        return fp8_gemm_ref(a_q, a_s, b_q, b_s).to(torch.bfloat16)
+    M, N = a_q.shape[0], b_q.shape[0]
+    sfa = pack_scales_ue8m0(a_s, M, True)
+    sfb = pack_scales_ue8m0(b_s, N, False)
+    out = torch.empty(M, N, device=a_q.device, dtype=torch.bfloat16)
+    _ext.ops().gemm_mxfp8(a_q, sfa, b_q, sfb, out)
+    return out
+
+
 class Fp8Linear:
     """y = x @ W with W (in, out) held as block-scaled FP8: the weight is quantised once
     (transposed to [out, in] so K is contiguous), activations are quantised per call."""

@@ -3,6 +3,7 @@
     python -m jax_gpt_b200.utils.kernel_bench --op gemm --M 8192 --N 8192 --K 8192
     python -m jax_gpt_b200.utils.kernel_bench --op attn_fwd --B 16 --T 1024 --H 12 --D 64
     python -m jax_gpt_b200.utils.kernel_bench --op attn_bwd | norm_fwd | norm_bwd | adamw | ce
+    python -m jax_gpt_b200.utils.kernel_bench --op mla_decode --B 32 --T 2304 --H 16
 
 Each run does ``--warmup`` untimed launches, then times ``--iters`` launches with CUDA events on
 the launching stream (synchronised on both sides) and prints one JSON line with the achieved
@@ -49,6 +50,7 @@ def main(argv=None):
     ap.add_argument("--T", type=int, default=1024)
     ap.add_argument("--H", type=int, default=12)
     ap.add_argument("--D", type=int, default=64)
+    ap.add_argument("--splits", type=int, default=0, help="mla_decode: KV splits per sequence (0 = fill the SMs)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args(argv)
@@ -114,6 +116,38 @@ def main(argv=None):
         loss = torch.empty(M, device=dev)
         fn = lambda: misc.cross_entropy_fwd_bwd(logits, tg, V, 1.0 / M, loss=loss)
         bytes_ = 2.0 * 2 * M * V
+    elif args.op == "gemm_mxfp8":
+        from ..ops import rope as Q
+        M, N, K = args.M, args.N, args.K
+        xq, xs = Q.fp8_quant_1x128(torch.randn(M, K, device=dev).to(torch.bfloat16), pow2=True)
+        wq, ws = Q.fp8_quant_128x128(torch.randn(N, K, device=dev).to(torch.bfloat16), pow2=True)
+        sfa, sfb = Q.pack_scales_ue8m0(xs, M, True), Q.pack_scales_ue8m0(ws, N, False)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        fn = lambda: _ext.ops().gemm_mxfp8(xq, sfa, wq, sfb, out)
+        flops, bytes_ = 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
+    elif args.op == "mla_decode":
+        # --B sequences of --T cached tokens each, --H heads (16 = DeepSeek-V3 with 8-way head sharding)
+        from ..cache.paged import PagedCache
+        from ..ops.mla_decode import mla_paged_decode
+        B, T, H = args.B, args.T, args.H
+        pages = (T + 63) // 64
+        cache = PagedCache(1, 576, n_pages=B * pages, page_size=64, max_seqs=B, max_pages_per_seq=pages, device=dev)
+        cache.pool.normal_()
+        ids = list(range(B))
+        cache._tab.reserve(ids, [T] * B)
+        cache.commit(ids, T)
+        q = (torch.randn(B, H, 576, device=dev) * 0.3).to(torch.bfloat16)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        ns = args.splits or max(1, min(sms // (B * ((H + 31) // 32)), (T + 127) // 128, 32))
+        part_out = torch.empty(B * ns * H * 512, device=dev)
+        part_lse = torch.empty(B * ns * H, device=dev)
+        out = torch.empty(B, H, 512, device=dev, dtype=torch.bfloat16)
+        idt = cache.seq_id_tensor(ids)
+        pool0 = cache.pool[0]
+        fn = lambda: _ext.ops().mla_paged_decode(q, pool0, cache.block_table, cache.seq_lens, idt, 192 ** -0.5, ns,
+                                                 part_out, part_lse, out)
+        bytes_ = 2.0 * B * T * 576
+        flops = 2.0 * B * H * T * (576 + 512)
     else:
         raise SystemExit(f"unknown op {args.op}")
     ms = _time(fn, args.warmup, args.iters)

@@ -151,3 +151,23 @@ def test_mla_paged_decode_and_paged_write(cuda_device, heads, n_splits):
     assert err < 3e-2, err
     rel = ((out.float() - ref.float()).norm() / ref.float().norm()).item()
     assert rel < 1.5e-2, rel
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 512, 1024), (256, 384, 512), (1024, 2048, 7168)])
+def test_mxfp8_gemm_hardware_block_scales(cuda_device, M, N, K):
+    """tcgen05 block-scaled MMA (UE8M0 scales in TMEM) vs the de-quantised fp32 product."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.ops import rope as Q
+    torch.manual_seed(3)
+    x = (torch.randn(M, K, device=cuda_device) * torch.rand(M, 1, device=cuda_device) * 4).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=cuda_device) * 0.05).to(torch.bfloat16)
+    wp = torch.zeros((N + 127) // 128 * 128, K, device=cuda_device, dtype=torch.bfloat16)
+    wp[:N] = w
+    xq, xs = Q.fp8_quant_1x128(x, pow2=True)
+    wq, ws = Q.fp8_quant_128x128(wp, pow2=True)
+    out = Q.mxfp8_gemm(xq, xs, wq[:N].contiguous(), ws)
+    torch.cuda.synchronize()
+    _ext.check_status(cuda_device)
+    ref = Q.fp8_gemm_ref(xq, xs, wq[:N], ws)
+    assert _rel(out, ref) < 5e-3, _rel(out, ref)
+    assert _rel(out, x.float() @ w.float().t()) < 6e-2
