@@ -50,47 +50,6 @@ struct MxArgs {
   int* status;
 };
 
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-
-// Un-swizzled K-major descriptor of a 32-row x 16-byte block stored contiguously (8-row core matrices 128 B apart).
-__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>(128 >> 4) << 32;  // stride between 8-row groups
-  d |= 1ull << 46;
-  return d;
-}
-
-__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-// kind::mxf8f6f4 instruction descriptor: e4m3 x e4m3, UE8M0 scales, K-major operands.
-__host__ __device__ constexpr uint32_t make_idesc_mx(int M, int N, int sf_id) {
-  return (static_cast<uint32_t>(sf_id) << 4)        // B scale id: byte of the 32-bit scale column
-         | (static_cast<uint32_t>(N >> 3) << 17)    //
-         | (1u << 23)                               // scale format UE8M0
-         | (static_cast<uint32_t>(M >> 4) << 24)    //
-         | (static_cast<uint32_t>(sf_id) << 29);    // A scale id
-}
-
-__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
-      "}\n" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
-      : "memory");
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ CUtensorMap tb,
                   const __grid_constant__ MxArgs a) {

@@ -1,0 +1,141 @@
+// Pieces shared by the expert-parallel MoE kernels (moe_kernels.cu, moe_fp8_kernels.cu): the
+// shared-memory routing tables built from the all-gathered pair counts, the static tile order,
+// bounded counter waits and the release/acquire helpers of the arrival protocol.
+#pragma once
+#include "common.cuh"
+#include "moe_kernels.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kMoeBM = 128, kMoeBN = 256;
+
+struct MoeTables {
+  int send_off[kMoeMaxExperts];      // first row of MY pairs for global expert e in its destination buffer
+  int rows[kMoeMaxLocalExperts];     // rows received per local expert
+  int base[kMoeMaxLocalExperts];     // first row of the local expert in this rank's receive buffer
+  int tile0[kMoeMaxLocalExperts + 1];  // first tile index of the local expert (GEMM1 tiles, then GEMM2 tiles)
+  int mt0[kMoeMaxLocalExperts + 1];    // first m-tile index of the local expert
+  int overflow;                      // some rank would receive more rows than cap_rows
+};
+
+
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until *p (cumulative counter) has reached `target` (wrap-safe signed difference).
+template <bool kSystem>
+__device__ __forceinline__ bool wait_counter_ge(const unsigned* p, unsigned target, uint64_t budget_ns,
+                                                volatile int* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    const unsigned v = kSystem ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p);
+    if (static_cast<int>(v - target) >= 0) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > budget_ns) {
+      *abort_flag = 1;
+      return false;
+    }
+    __nanosleep(32);
+  }
+}
+
+
+// Fills the shared-memory tables from the all-gathered count matrix counts[src][e].
+template <class Args>
+__device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb, bool backward = false, int pad = 64) {
+  const int W = a.world, EL = a.e_local, ET = W * EL;
+  if (threadIdx.x == 0) tb->overflow = 0;
+  __syncthreads();
+  for (int e = threadIdx.x; e < ET; e += blockDim.x) {
+    const int dst = e / EL, el = e % EL;
+    // every expert's region starts on a 64-row boundary (ragged-K weight gradients read whole
+    // 64-row blocks; the padding rows are kept zero)
+    int off = 0;
+    for (int e2 = dst * EL; e2 < dst * EL + el; ++e2) {  // experts placed before e on the destination
+      int n2 = 0;
+      for (int s = 0; s < W; ++s) n2 += __ldcg(counts_all + s * ET + e2);
+      off += (n2 + pad - 1) / pad * pad;
+    }
+    int before = 0;
+    for (int s = 0; s < a.rank; ++s) before += __ldcg(counts_all + s * ET + e);  // sources placed before this rank
+    tb->send_off[e] = off + before;
+    if (el == EL - 1) {
+      int tot = before;
+      for (int s = a.rank; s < W; ++s) tot += __ldcg(counts_all + s * ET + e);
+      if (off + (tot + pad - 1) / pad * pad > a.cap_rows) tb->overflow = 1;
+    }
+  }
+  for (int el = threadIdx.x; el < EL; el += blockDim.x) {
+    int n = 0;
+    for (int s = 0; s < W; ++s) n += __ldcg(counts_all + s * ET + a.rank * EL + el);
+    tb->rows[el] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
+    int b = 0, t = 0, m = 0;
+    for (int el = 0; el < EL; ++el) {
+      tb->base[el] = b;
+      tb->tile0[el] = t;
+      tb->mt0[el] = m;
+      const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
+      b += (tb->rows[el] + pad - 1) / pad * pad;
+      if (!backward) {
+        t += mt * (n1 + n2);
+      } else if (mt > 0) {
+        // dAct tiles, dX tiles, dW_down tiles, dW_gate|up tiles
+        t += mt * (a.inter / kMoeBN) + mt * n2 + (a.inter / kMoeBM) * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
+      }
+      m += mt;
+    }
+    tb->tile0[EL] = t;
+    tb->mt0[EL] = m;
+  }
+  __syncthreads();
+}
+
+struct TileInfo {
+  int el, m, n, phase;  // phase 0: GEMM1 (gate|up), 1: GEMM2 (down)
+};
+
+template <class Args>
+__device__ __forceinline__ TileInfo decode_tile(const Args& a, const MoeTables* tb, int t) {
+  const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
+  int el = 0;
+  while (t >= tb->tile0[el + 1]) ++el;
+  const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
+  int r = t - tb->tile0[el];
+  TileInfo ti;
+  ti.el = el;
+  if (r < mt * n1) {
+    ti.phase = 0;
+    ti.m = r % mt;
+    ti.n = r / mt;
+  } else {
+    r -= mt * n1;
+    ti.phase = 1;
+    ti.m = r % mt;
+    ti.n = r / mt;
+  }
+  return ti;
+}
+
+
+}  // namespace
+
+}  // namespace b200

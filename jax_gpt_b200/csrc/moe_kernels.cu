@@ -28,6 +28,7 @@
 
 #include "comm_device.cuh"
 #include "common.cuh"
+#include "moe_common.cuh"
 #include "tma_host.h"
 
 namespace cg = cooperative_groups;
@@ -41,15 +42,6 @@ constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 192;
 
-struct MoeTables {
-  int send_off[kMoeMaxExperts];      // first row of MY pairs for global expert e in its destination buffer
-  int rows[kMoeMaxLocalExperts];     // rows received per local expert
-  int base[kMoeMaxLocalExperts];     // first row of the local expert in this rank's receive buffer
-  int tile0[kMoeMaxLocalExperts + 1];  // first tile index of the local expert (GEMM1 tiles, then GEMM2 tiles)
-  int mt0[kMoeMaxLocalExperts + 1];    // first m-tile index of the local expert
-  int overflow;                      // some rank would receive more rows than cap_rows
-};
-
 struct MoeBars {
   uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
@@ -59,121 +51,10 @@ struct MoeBars {
 constexpr int kStageBufBytes = 4 * 32 * 33 * 4;  // per-epilogue-warp transposition buffers
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(MoeTables) + sizeof(MoeBars) + 64 + kStageBufBytes;
 
-__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
-
-__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_sys_add_u32(unsigned* p, unsigned v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Bounded wait until *p (cumulative counter) has reached `target` (wrap-safe signed difference).
-template <bool kSystem>
-__device__ __forceinline__ bool wait_counter_ge(const unsigned* p, unsigned target, uint64_t budget_ns,
-                                                volatile int* abort_flag) {
-  const uint64_t t0 = globaltimer_ns();
-  while (true) {
-    const unsigned v = kSystem ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p);
-    if (static_cast<int>(v - target) >= 0) return true;
-    if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > budget_ns) {
-      *abort_flag = 1;
-      return false;
-    }
-    __nanosleep(32);
-  }
-}
-
 __global__ void moe_prepare_kernel(const int* __restrict__ idx, int n_pairs, int* __restrict__ counts,
                                    int* __restrict__ pos) {
   for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += gridDim.x * blockDim.x)
     pos[p] = atomicAdd(&counts[idx[p]], 1);
-}
-
-// Fills the shared-memory tables from the all-gathered count matrix counts[src][e].
-__device__ void build_tables(const EpMoeArgs& a, const int* counts_all, MoeTables* tb, bool backward = false) {
-  const int W = a.world, EL = a.e_local, ET = W * EL;
-  if (threadIdx.x == 0) tb->overflow = 0;
-  __syncthreads();
-  for (int e = threadIdx.x; e < ET; e += blockDim.x) {
-    const int dst = e / EL, el = e % EL;
-    // every expert's region starts on a 64-row boundary (ragged-K weight gradients read whole
-    // 64-row blocks; the padding rows are kept zero)
-    int off = 0;
-    for (int e2 = dst * EL; e2 < dst * EL + el; ++e2) {  // experts placed before e on the destination
-      int n2 = 0;
-      for (int s = 0; s < W; ++s) n2 += __ldcg(counts_all + s * ET + e2);
-      off += (n2 + 63) & ~63;
-    }
-    int before = 0;
-    for (int s = 0; s < a.rank; ++s) before += __ldcg(counts_all + s * ET + e);  // sources placed before this rank
-    tb->send_off[e] = off + before;
-    if (el == EL - 1) {
-      int tot = before;
-      for (int s = a.rank; s < W; ++s) tot += __ldcg(counts_all + s * ET + e);
-      if (off + ((tot + 63) & ~63) > a.cap_rows) tb->overflow = 1;
-    }
-  }
-  for (int el = threadIdx.x; el < EL; el += blockDim.x) {
-    int n = 0;
-    for (int s = 0; s < W; ++s) n += __ldcg(counts_all + s * ET + a.rank * EL + el);
-    tb->rows[el] = n;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int n1 = a.inter / 128, n2 = a.d_model / BN;
-    int b = 0, t = 0, m = 0;
-    for (int el = 0; el < EL; ++el) {
-      tb->base[el] = b;
-      tb->tile0[el] = t;
-      tb->mt0[el] = m;
-      const int mt = (tb->rows[el] + BM - 1) / BM;
-      b += (tb->rows[el] + 63) & ~63;
-      if (!backward) {
-        t += mt * (n1 + n2);
-      } else if (mt > 0) {
-        // dAct tiles, dX tiles, dW_down tiles, dW_gate|up tiles
-        t += mt * (a.inter / BN) + mt * n2 + (a.inter / BM) * n2 + (a.d_model / BM) * (2 * a.inter / BN);
-      }
-      m += mt;
-    }
-    tb->tile0[EL] = t;
-    tb->mt0[EL] = m;
-  }
-  __syncthreads();
-}
-
-struct TileInfo {
-  int el, m, n, phase;  // phase 0: GEMM1 (gate|up), 1: GEMM2 (down)
-};
-
-__device__ __forceinline__ TileInfo decode_tile(const EpMoeArgs& a, const MoeTables* tb, int t) {
-  const int n1 = a.inter / 128, n2 = a.d_model / BN;
-  int el = 0;
-  while (t >= tb->tile0[el + 1]) ++el;
-  const int mt = (tb->rows[el] + BM - 1) / BM;
-  int r = t - tb->tile0[el];
-  TileInfo ti;
-  ti.el = el;
-  if (r < mt * n1) {
-    ti.phase = 0;
-    ti.m = r % mt;
-    ti.n = r / mt;
-  } else {
-    r -= mt * n1;
-    ti.phase = 1;
-    ti.m = r % mt;
-    ti.n = r / mt;
-  }
-  return ti;
 }
 
 }  // namespace

@@ -74,4 +74,47 @@ cudaError_t launch_ep_moe_forward(const EpMoeArgs& args, const __nv_bfloat16* ga
 cudaError_t launch_ep_moe_backward(const EpMoeArgs& args, const __nv_bfloat16* gate, const __nv_bfloat16* up,
                                    const __nv_bfloat16* down, cudaStream_t st);
 
+// ------------------------------------------------------------------------------------------------
+// FP8 forward (moe_fp8_kernels.cu): token rows are quantised to e4m3 with power-of-two 1 x 128 scales
+// once, pushed as bytes (half the NVLink traffic of bf16) together with their UE8M0 scale bytes, the
+// grouped GEMMs run on the block-scaled tensor-core path (scales in TMEM), and the SwiGLU epilogue
+// re-quantises the activation for the down projection. Weights are quantised ahead of time with
+// power-of-two 128 x 128 scales and stored K-major:
+//   gate_q / up_q [E_local, I, D] bytes, down_q [E_local, D, I] bytes,
+//   sfb1 [E_local, I/128, D/128, 512]: packed scale chunk of GEMM 1's B tile (rows 0-63 gate, 64-127 up),
+//   sfb2 [E_local, D/128, I/128, 512]: packed scale chunks of down_q.
+// Packed chunk layout: byte (r % 32) * 16 + (r / 32) * 4 + j = exponent of row r, K block j.
+struct EpMoeFp8Args {
+  int world, rank;
+  int tokens, top_k, d_model, inter, e_local, cap_rows;  // expert regions are padded to 128 rows
+  const __nv_bfloat16* x;
+  const int* idx;
+  const float* w;
+  const int* pos;
+  const int* my_counts;
+  uint8_t* xq;                              // [tokens, d_model] local staging of the quantised rows
+  uint8_t* xe;                              // [tokens, d_model / 128] their scale exponents
+  uint8_t* peer_recv_q[kCommMaxRanks];      // [cap_rows, d_model]
+  uint8_t* peer_recv_sf[kCommMaxRanks];     // [cap_rows / 128, d_model / 128, 512]
+  int* peer_recv_meta[kCommMaxRanks];
+  float* peer_recv_w[kCommMaxRanks];
+  int* peer_counts[kCommMaxRanks];
+  unsigned* peer_arrive[kCommMaxRanks];
+  float* peer_out[kCommMaxRanks];
+  CommCtrl* peer_ctrl[kCommMaxRanks];
+  uint8_t* act_q;                           // [cap_rows, inter]
+  uint8_t* act_sf;                          // [cap_rows / 128, inter / 128, 512]
+  const uint8_t* sfb1;
+  const uint8_t* sfb2;
+  unsigned* arrive_target;
+  int* act_ready;
+  int* slot_out;
+  int* rows_out;
+  uint64_t wait_budget_ns;
+  int* status;
+};
+
+cudaError_t launch_ep_moe_forward_fp8(const EpMoeFp8Args& args, const uint8_t* gate_q, const uint8_t* up_q,
+                                      const uint8_t* down_q, cudaStream_t st);
+
 }  // namespace b200

@@ -113,6 +113,111 @@ class FusedEPMoE:
         return res
 
 
+def quantize_expert_weights_fp8(params: dict) -> dict:
+    """Stacked bf16 expert weights (gate_proj / up_proj (E, D, I), down_proj (E, I, D)) -> what the FP8
+    kernel reads: K-major e4m3 bytes with power-of-two 128 x 128 block scales, and the packed UE8M0
+    scale chunks (csrc/moe_kernels.cuh: EpMoeFp8Args)."""
+    from ..ops.rope import fp8_quant_128x128
+    gate, up, down = params["gate_proj"], params["up_proj"], params["down_proj"]
+    E, D, I = gate.shape
+    dev = gate.device
+
+    def q(w):  # (E, K, N) -> bytes (E, N, K), exponents (E, N/128, K/128)
+        qs, es = [], []
+        for e in range(w.shape[0]):
+            qe, se = fp8_quant_128x128(w[e].t().contiguous().to(torch.bfloat16), pow2=True)
+            qs.append(qe.view(torch.uint8))
+            es.append((torch.log2(se.float()).round() + 127).clamp(1, 254).to(torch.uint8))
+        return torch.stack(qs), torch.stack(es)
+
+    gq, ge = q(gate)
+    uq, ue = q(up)
+    dq, de = q(down)
+    # GEMM 1 chunk: rows 0-63 of the B tile are gate rows, 64-127 up rows -> 32-row groups (gate, gate, up, up)
+    grp = torch.stack([ge, ge, ue, ue], dim=-1)                                   # (E, I/128, D/128, 4)
+    sfb1 = grp[:, :, :, None, :, None].expand(E, I // 128, D // 128, 32, 4, 4).reshape(E, I // 128, D // 128, 512)
+    sfb2 = de[:, :, :, None].expand(E, D // 128, I // 128, 512)
+    return {"gate_q": gq.contiguous(), "up_q": uq.contiguous(), "down_q": dq.contiguous(),
+            "sfb1": sfb1.contiguous(), "sfb2": sfb2.contiguous(), "gate_e": ge, "up_e": ue, "down_e": de}
+
+
+def fp8_moe_reference(x, weights, idx, qw_full: dict) -> torch.Tensor:
+    """fp32 restatement of the FP8 kernel's arithmetic with ALL experts local: 1 x 128 power-of-two
+    activation quantisation, de-quantised block-scaled weights, SwiGLU, re-quantised activation."""
+    from ..ops.rope import fp8_quant_1x128_ref
+
+    def deq(qb, eb):  # (N, K) bytes + (N/128, K/128) exponents -> fp32 (N, K)
+        sc = torch.exp2(eb.float() - 127).repeat_interleave(128, 0).repeat_interleave(128, 1)
+        return qb.view(torch.float8_e4m3fn).float() * sc
+
+    def qdq(t):
+        qv, sc = fp8_quant_1x128_ref(t, pow2=True)
+        return (qv.float().view(t.shape[0], -1, 128) * sc[..., None]).view(t.shape)
+
+    xq = qdq(x.float())
+    out = torch.zeros(x.shape[0], x.shape[1], dtype=torch.float32, device=x.device)
+    for e in idx.unique().tolist():
+        tok, slot = (idx == e).nonzero(as_tuple=True)
+        g = xq[tok] @ deq(qw_full["gate_q"][e], qw_full["gate_e"][e]).t()
+        u = xq[tok] @ deq(qw_full["up_q"][e], qw_full["up_e"][e]).t()
+        act = qdq(torch.nn.functional.silu(g) * u)
+        y = act @ deq(qw_full["down_q"][e], qw_full["down_e"][e]).t()
+        out.index_add_(0, tok, y * weights[tok, slot][:, None].float())
+    return out
+
+
+class FusedEPMoEFp8:
+    """FP8 forward of the fused expert-parallel layer: e4m3 rows with power-of-two 1 x 128 scales on the
+    wire and in the grouped GEMMs (tensor-core block scaling), weights pre-quantised with
+    ``quantize_expert_weights_fp8``. Same constructor arguments as ``FusedEPMoE``."""
+
+    def __init__(self, comm: Communicator, tokens: int, d_model: int, inter: int, n_experts: int, top_k: int,
+                 cap_factor: Optional[float] = None):
+        self.comm = comm
+        W = comm.world
+        assert n_experts % W == 0 and d_model % 256 == 0 and inter % 128 == 0
+        self.tokens, self.D, self.I, self.E, self.k = tokens, d_model, inter, n_experts, top_k
+        self.e_local = n_experts // W
+        cap_factor = float(W) if cap_factor is None else cap_factor
+        self.cap_rows = (int(tokens * top_k * cap_factor) + 128 * self.e_local + 127) // 128 * 128
+        dev = comm.device
+        u8 = torch.uint8
+        self.recv_q = comm.alloc(self.cap_rows * d_model, u8, zero=True)
+        self.recv_sf = comm.alloc((self.cap_rows // 128) * (d_model // 128) * 512, u8, zero=True)
+        self.recv_meta = comm.alloc(self.cap_rows, torch.int32)
+        self.recv_w = comm.alloc(self.cap_rows, torch.float32)
+        self.counts_all = comm.alloc(W * n_experts, torch.int32)
+        self.arrive = comm.alloc(max(self.e_local, 32), torch.int32)
+        self.out_acc = comm.alloc(tokens * d_model, torch.float32)
+        self.xq = torch.zeros(tokens, d_model, device=dev, dtype=u8)
+        self.xe = torch.zeros(tokens, d_model // 128, device=dev, dtype=u8)
+        self.act_q = torch.zeros(self.cap_rows, inter, device=dev, dtype=u8)
+        self.act_sf = torch.full(((self.cap_rows // 128) * (inter // 128) * 512,), 127, device=dev, dtype=u8)
+        self.arrive_target = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
+        self.act_ready = torch.zeros(self.cap_rows // 128 + self.e_local, device=dev, dtype=torch.int32)
+        self.slot_out = torch.zeros(tokens * top_k, device=dev, dtype=torch.int32)
+        self.rows_out = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
+        self.my_counts = torch.zeros(n_experts, device=dev, dtype=torch.int32)
+        self.pos = torch.zeros(tokens * top_k, device=dev, dtype=torch.int32)
+        dist.barrier(comm.group)
+
+    def forward(self, x, weights, idx, qw: dict) -> torch.Tensor:
+        """x (tokens, D) bf16; ``qw``: this rank's experts from ``quantize_expert_weights_fp8``. Returns fp32."""
+        ops = _ext.ops()
+        c = self.comm
+        idx32 = idx.to(torch.int32).contiguous().view(-1)
+        w32 = weights.to(torch.float32).contiguous().view(-1)
+        ops.moe_prepare(idx32, self.my_counts, self.pos)
+        self.out_acc.tensor.zero_()
+        ops.ep_moe_forward_fp8(c.world, c.rank, self.k, self.e_local, self.cap_rows, x.contiguous(), idx32, w32, self.pos,
+                               self.my_counts, self.xq, self.xe, self.recv_q.peer_ptrs, self.recv_sf.peer_ptrs,
+                               self.recv_meta.peer_ptrs, self.recv_w.peer_ptrs, self.counts_all.peer_ptrs,
+                               self.arrive.peer_ptrs, self.out_acc.peer_ptrs, c.ctrl.peer_ptrs, self.act_q, self.act_sf,
+                               self.arrive_target, self.act_ready, self.slot_out, self.rows_out, qw["gate_q"],
+                               qw["up_q"], qw["down_q"], qw["sfb1"], qw["sfb2"], c.wait_seconds)
+        return self.out_acc.tensor.view(self.tokens, self.D)
+
+
 class _FusedEPMoEFn(torch.autograd.Function):
     """Autograd node around one ``FusedEPMoE`` layer. Expert weights stay outside autograd: their fp32
     gradients are accumulated by the backward kernel straight into ``grads`` (main-grad convention)."""

@@ -66,6 +66,7 @@ def main(argv=None):
     ap.add_argument("--skip-baseline", action="store_true")
     ap.add_argument("--check", action="store_true", help="compare fused and baseline outputs")
     ap.add_argument("--backward", action="store_true", help="also time the fused backward kernel")
+    ap.add_argument("--fp8", action="store_true", help="also time the FP8 (block-scaled tensor-core) fused forward")
     args = ap.parse_args(argv)
     rank, world, device = init_distributed()
     assert world > 1, "run under torchrun with at least 2 processes"
@@ -93,6 +94,18 @@ def main(argv=None):
         _ext.check_status(device)
         res["fused_bwd_ms"] = ms_bwd
         res["bwd_tflops_this_rank"] = 2.0 * rows * 6 * D * I / ms_bwd / 1e9
+    if args.fp8:
+        from jax_gpt_b200.parallel.expert_parallel import FusedEPMoEFp8, quantize_expert_weights_fp8
+        qw = quantize_expert_weights_fp8(local)
+        f8 = FusedEPMoEFp8(comm, T, D, I, E, k)
+        ms8 = timed(lambda: f8.forward(x, w, idx, qw), args.warmup, args.iters, device)
+        _ext.check_status(device)
+        res["fused_fp8_fwd_ms"] = ms8
+        res["fp8_tflops_this_rank"] = 2.0 * rows * 3 * D * I / ms8 / 1e9
+        if args.check:
+            a8 = f8.forward(x, w, idx, qw).float().clone()
+            b16 = fused.forward(x, w, idx, local).float()
+            res["fp8_vs_bf16_rel"] = ((a8 - b16).norm() / b16.norm()).item()
     if not args.skip_baseline:
         base = NcclEPMoE(dist.group.WORLD, E)
         res["nccl_fwd_ms"] = timed(lambda: base.forward(x, w, idx, local), 1, max(1, args.iters // 2), device)

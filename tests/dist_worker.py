@@ -191,6 +191,43 @@ def run_ep_bwd(rank, world, device):
     return res
 
 
+def run_ep_fp8(rank, world, device):
+    """FP8 fused expert-parallel forward vs the fp32 restatement of its quantised arithmetic and vs bf16 math."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.comm.symm import Communicator
+    from jax_gpt_b200.models.qwen35.moe import expert_forward_single
+    from jax_gpt_b200.parallel.expert_parallel import FusedEPMoEFp8, fp8_moe_reference, quantize_expert_weights_fp8
+    tokens, D, I, E, k = 384, 512, 256, 16, 4
+    g = torch.Generator(device=device).manual_seed(3)
+    full = {"gate_proj": (torch.randn(E, D, I, device=device, generator=g) * 0.05).to(torch.bfloat16),
+            "up_proj": (torch.randn(E, D, I, device=device, generator=g) * 0.05).to(torch.bfloat16),
+            "down_proj": (torch.randn(E, I, D, device=device, generator=g) * 0.05).to(torch.bfloat16)}
+    el = E // world
+    qw_full = quantize_expert_weights_fp8(full)
+    qw = {n: t[rank * el:(rank + 1) * el].contiguous() for n, t in qw_full.items()}
+    comm = Communicator(device=device, wait_seconds=5.0)
+    fused = FusedEPMoEFp8(comm, tokens, D, I, E, k)
+    res = {}
+    for step, mode in enumerate(["uniform", "skewed", "uniform"]):
+        gs = torch.Generator(device=device).manual_seed(100 * step + rank)
+        x = (torch.randn(tokens, D, device=device, generator=gs) * (1 + 3 * torch.rand(tokens, 1, device=device, generator=gs))).to(torch.bfloat16)
+        logits = torch.randn(tokens, E, device=device, generator=gs)
+        if mode == "skewed":
+            logits[:, :3] += 6.0
+            logits[:, 5] = -1e9
+        w, idx = torch.softmax(logits, -1).topk(k, dim=-1)
+        w = w / w.sum(-1, keepdim=True)
+        out = fused.forward(x, w, idx, qw).clone()
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        ref_q = fp8_moe_reference(x, w, idx, qw_full)
+        ref = expert_forward_single(x.float(), w, idx, {n: t.float() for n, t in full.items()})
+        res[f"{mode}{step}_fused_vs_quantised_ref"] = rel(out, ref_q)
+        res[f"{mode}{step}_fused_vs_bf16_math"] = rel(out, ref)
+        dist.barrier()
+    return res
+
+
 def run_moe_train(rank, world, device):
     """Qwen3.5-style training with expert parallelism (fused MoE forward/backward kernels) and the fused
     sharded optimizer for the dense weights, against one process that holds all experts and sees every
@@ -256,6 +293,8 @@ def main():
         res = run_ep(rank, world, device)
     elif what == "ep_bwd":
         res = run_ep_bwd(rank, world, device)
+    elif what == "ep_fp8":
+        res = run_ep_fp8(rank, world, device)
     elif what == "moe_train":
         res = run_moe_train(rank, world, device)
     else:

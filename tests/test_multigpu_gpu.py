@@ -59,6 +59,15 @@ def test_fused_ep_moe_backward_two_gpus(tmp_path):
         assert v < 3e-2, res
 
 
+def test_fused_ep_moe_fp8_two_gpus(tmp_path):
+    res = _run("ep_fp8", tmp_path, port=29617)
+    for k, v in res.items():
+        if k.endswith("_vs_quantised_ref"):
+            assert v < 2e-2, res
+        if k.endswith("_vs_bf16_math"):
+            assert v < 1e-1, res
+
+
 def test_qwen35_expert_parallel_training_matches_single_process(tmp_path):
     res = _run("moe_train", tmp_path, port=29616)
     assert res["ep_loss"][0] > 5.5                      # ln(512) = 6.24 at random init
