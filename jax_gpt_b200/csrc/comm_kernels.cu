@@ -171,6 +171,110 @@ __global__ void __launch_bounds__(512, 2) sharded_adamw_kernel(const __grid_cons
   }
 }
 
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(256, 1) vocab_parallel_ce_kernel(const __grid_constant__ VocabCeArgs a) {
+  cg::grid_group grid = cg::this_grid();
+  CommCtrl* my = a.peer_ctrl[a.rank];
+  const int epoch = my->epoch + 1;
+  const int W = a.world;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gwarp = blockIdx.x * (blockDim.x >> 5) + warp, gwarps = gridDim.x * (blockDim.x >> 5);
+  const int64_t buf = static_cast<int64_t>(epoch & 1) * W * a.M * 4;
+  const int nvec = a.v_local / 8;  // 16-byte vectors; the tail is read element-wise
+
+  // ---- phase 1: statistics of this shard, pushed to every rank ----
+  for (int row = gwarp; row < a.M; row += gwarps) {
+    const __nv_bfloat16* lp = a.logits + static_cast<int64_t>(row) * a.ldl;
+    const uint4* lv = reinterpret_cast<const uint4*>(lp);
+    float mx = -INFINITY;
+    for (int i = lane; i < nvec; i += 32) {
+      const uint4 u = lv[i];
+      const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+      mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(f0.x, f0.y), fmaxf(f1.x, f1.y)), fmaxf(fmaxf(f2.x, f2.y), fmaxf(f3.x, f3.y))));
+    }
+    for (int i = nvec * 8 + lane; i < a.v_local; i += 32) mx = fmaxf(mx, __bfloat162float(lp[i]));
+    mx = warp_max(mx);
+    float se = 0.f;
+    for (int i = lane; i < nvec; i += 32) {
+      const uint4 u = lv[i];
+      const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+      se += __expf(f0.x - mx) + __expf(f0.y - mx) + __expf(f1.x - mx) + __expf(f1.y - mx) + __expf(f2.x - mx) +
+            __expf(f2.y - mx) + __expf(f3.x - mx) + __expf(f3.y - mx);
+    }
+    for (int i = nvec * 8 + lane; i < a.v_local; i += 32) se += __expf(__bfloat162float(lp[i]) - mx);
+    se = warp_sum(se);
+    const int tg = a.targets[row] - a.v0;
+    const float tl = (tg >= 0 && tg < a.v_local) ? __bfloat162float(lp[tg]) : 0.f;
+    if (lane < W) {
+      float4* dst = reinterpret_cast<float4*>(a.peer_stats[lane] + buf + (static_cast<int64_t>(a.rank) * a.M + row) * 4);
+      *dst = make_float4(mx, se, tl, 0.f);
+    }
+  }
+  __threadfence_system();
+  grid.sync();
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) my->abort_flag = 0;
+    __syncthreads();
+    const bool ok = flag_barrier(a.peer_ctrl, W, a.rank, 6, epoch, a.wait_budget_ns, a.status);
+    if (!ok && threadIdx.x == 0) my->abort_flag = 1;
+    if (threadIdx.x == 0) my->epoch = epoch;
+  }
+  __threadfence();
+  grid.sync();
+  if (*reinterpret_cast<volatile int*>(&my->abort_flag) != 0) return;
+
+  // ---- phase 2: global loss; this shard's gradient in place ----
+  const float* st = a.peer_stats[a.rank] + buf;
+  for (int row = gwarp; row < a.M; row += gwarps) {
+    float gm = -INFINITY;
+    for (int r = 0; r < W; ++r) gm = fmaxf(gm, __ldcg(st + (static_cast<int64_t>(r) * a.M + row) * 4));
+    float gs = 0.f, tl = 0.f;
+    for (int r = 0; r < W; ++r) {
+      const float4 s4 = __ldcg(reinterpret_cast<const float4*>(st + (static_cast<int64_t>(r) * a.M + row) * 4));
+      gs += s4.y * __expf(s4.x - gm);
+      tl += s4.z;
+    }
+    const int target = a.targets[row];
+    const bool valid = target >= 0;
+    if (lane == 0) a.loss[row] = valid ? (__logf(gs) + gm - tl) : 0.f;
+    if (!a.write_grad) continue;
+    const float inv = valid ? a.scale / gs : 0.f;
+    const int tg = target - a.v0;
+    __nv_bfloat16* lp = a.logits + static_cast<int64_t>(row) * a.ldl;
+    uint4* lv = reinterpret_cast<uint4*>(lp);
+    for (int i = lane; i < nvec; i += 32) {
+      const uint4 u = lv[i];
+      const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(in[e]);
+        const int c = i * 8 + 2 * e;
+        float p0 = __expf(f.x - gm) * inv, p1 = __expf(f.y - gm) * inv;
+        if (valid && c == tg) p0 -= a.scale;
+        if (valid && c + 1 == tg) p1 -= a.scale;
+        o[e] = pack_bf16x2(p0, p1);
+      }
+      lv[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    for (int i = nvec * 8 + lane; i < a.v_local; i += 32) {
+      float p = __expf(__bfloat162float(lp[i]) - gm) * inv;
+      if (valid && i == tg) p -= a.scale;
+      lp[i] = __float2bfloat16(p);
+    }
+  }
+}
+
 __global__ void comm_barrier_kernel(CommCtrl* const* peer_ctrl_dev, int world, int rank, uint64_t budget_ns,
                                     int* status) {
   __shared__ CommCtrl* peers[kCommMaxRanks];
@@ -204,6 +308,19 @@ cudaError_t launch_sharded_adamw(const ShardedAdamWArgs& args, cudaStream_t stre
   void* params[] = {&a};
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(sharded_adamw_kernel), dim3(grid), dim3(512), params, 0,
                                      stream);
+}
+
+cudaError_t launch_vocab_parallel_ce(const VocabCeArgs& args, cudaStream_t stream) {
+  if (args.world < 1 || args.world > kCommMaxRanks || args.M < 1 || args.v_local < 1 || args.ldl % 8 != 0)
+    return cudaErrorInvalidValue;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int want = (args.M + 7) / 8;
+  VocabCeArgs a = args;
+  void* params[] = {&a};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(vocab_parallel_ce_kernel), dim3(want < sms ? want : sms),
+                                     dim3(256), params, 0, stream);
 }
 
 cudaError_t launch_comm_barrier(CommCtrl* const* peer_ctrl_dev, int world, int rank, uint64_t wait_budget_ns,

@@ -55,4 +55,25 @@ cudaError_t launch_comm_barrier(CommCtrl* const* peer_ctrl, int world, int rank,
 // that nothing sets makes the kernel record kWaitFlagTimeout in `status` and return.
 cudaError_t launch_wait_flag(const int* flag, int expected, uint64_t budget_ns, int* status, cudaStream_t stream);
 
+// Vocabulary-parallel cross-entropy: every rank holds the logits of its vocabulary shard only,
+// [M, ldl] bf16 with columns [0, v_local) valid = global ids [v0, v0 + v_local). One cooperative kernel:
+// per-row (max, sum-exp, target logit) of the shard, pushed to every peer's statistics buffer over
+// NVLink, a flag barrier, then the global loss and, in place, this shard's gradient
+// scale * (softmax - onehot). The full (M, V) logits are never gathered.
+struct VocabCeArgs {
+  int world, rank;
+  int M, v_local, v0;
+  int64_t ldl;
+  __nv_bfloat16* logits;                   // this rank's shard; overwritten with its gradient when write_grad
+  const int* targets;                      // [M] global ids; < 0 = ignored row (loss 0, zero gradient)
+  float* peer_stats[kCommMaxRanks];        // every rank's buffer [2][world][M][4] fp32 (double-buffered by launch parity)
+  CommCtrl* peer_ctrl[kCommMaxRanks];
+  float* loss;                             // [M] per-row loss (identical on every rank)
+  float scale;
+  int write_grad;
+  uint64_t wait_budget_ns;
+  int* status;
+};
+cudaError_t launch_vocab_parallel_ce(const VocabCeArgs& args, cudaStream_t stream);
+
 }  // namespace b200

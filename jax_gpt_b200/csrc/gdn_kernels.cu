@@ -1,0 +1,361 @@
+// Gated-DeltaNet prefill kernels for sm_100a: the causal depthwise conv + SiLU, and the
+// inter-chunk scan of the chunked gated delta rule on tcgen05 tensor cores.
+//
+// The chunked algorithm splits every head's sequence into chunks of 64 tokens. What does not depend
+// on the running state S (cumulative decays, the unit-lower-triangular solve giving the corrected
+// values v_eff and the decayed keys k_cum, the masked intra-chunk scores) is computed for all chunks
+// at once with batched library calls. What does depend on it is a strictly sequential recurrence,
+//     v_new = v_eff - k_cum S
+//     o     = (q * exp(G)) S + intra v_new
+//     S     = exp(g_end) S + (k * exp(g_end - G))^T v_new
+// which the reference runs as a `lax.scan` over chunks (jax_gpt/models/qwen35/deltanet.py:300-360).
+// Here one CTA per (batch, head) walks the chunks with S resident on chip: fp32 in the registers of
+// 128 threads (one row of the 128 x 128 state each), a bf16 copy in shared memory as tensor-core
+// operand. Per chunk three MMAs:
+//   1. D[128 x 128] = [k_cum ; q exp(G)] S      (the two 64-row operands stacked to M = 128)
+//   2. D[64:128]   += [0 ; intra] v_new         (A tile with a zero upper half)
+//   3. P[128 x 128] = (k exp(g_end - G))^T v_new
+// with v_new produced between 1 and 2 by the threads that own rows 0..63 of D. TMA double-buffers
+// the per-chunk operand tiles.
+#include "seq_kernels.cuh"
+
+#include "common.cuh"
+#include "tma_host.h"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kC = 64, kDk = 128, kDv = 128;
+constexpr int kStages = 2;
+constexpr int kA1Bytes = 128 * kDk * 2;      // 32 KB  [k_cum ; qg], two 64-column K blocks of 16 KB
+constexpr int kA2Bytes = 128 * kC * 2;       // 16 KB  [0 ; intra]
+constexpr int kKdBytes = kC * kDk * 2;       // 16 KB  k_dec, two 64-column blocks of 8 KB
+constexpr int kStageBytes = kA1Bytes + kA2Bytes + kKdBytes;   // 64 KB
+constexpr int kSbBytes = kDk * kDv * 2;      // 32 KB  S as bf16, two 64-column blocks of 16 KB
+constexpr int kVnBytes = kC * kDv * 2;       // 16 KB  v_new, two 64-column blocks of 8 KB
+constexpr int kThreads = 192;
+constexpr int kSmem = 1024 + kStages * kStageBytes + kSbBytes + kVnBytes + 256;
+
+struct ScanBars {
+  uint64_t full[kStages], empty[kStages], d_full, vn_ready, p_full, s_ready;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct ScanArgs {
+  int n_chunks;
+  const __nv_bfloat16* veff;   // [BH, N, 64, dv]
+  const float* e;              // [BH, N]
+  const float* s0;             // [BH, dk, dv] or nullptr
+  __nv_bfloat16* o;            // [BH, N, 64, dv]
+  float* s_out;                // [BH, dk, dv]
+  int* status;
+};
+
+// byte offset of (row r, column c) in a bf16 tile made of 64-column blocks with 128-byte swizzled rows
+__device__ __forceinline__ uint32_t swz(int r, int c, int block_bytes) {
+  return (c >> 6) * block_bytes + r * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4) + (c & 7) * 2;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gdn_scan_kernel(const __grid_constant__ CUtensorMap t_kq, const __grid_constant__ CUtensorMap t_intra,
+                const __grid_constant__ CUtensorMap t_kdec, const __grid_constant__ ScanArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sb = smem + kStages * kStageBytes;
+  uint8_t* vn = sb + kSbBytes;
+  ScanBars* bars = reinterpret_cast<ScanBars*>(vn + kVnBytes);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x;
+  const int N = a.n_chunks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->d_full, 1);
+    mbar_init(&bars->vn_ready, 128);
+    mbar_init(&bars->p_full, 1);
+    mbar_init(&bars->s_ready, 128);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  // the upper half of every [0 ; intra] tile stays zero for the whole kernel
+  for (int i = threadIdx.x; i < kStages * (kA2Bytes / 2) / 16; i += kThreads) {
+    const int s = i / ((kA2Bytes / 2) / 16), j = i % ((kA2Bytes / 2) / 16);
+    reinterpret_cast<uint4*>(smem + s * kStageBytes + kA1Bytes)[j] = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int n = 0; n < N; ++n, ++issued) {
+        const int st = n & 1;
+        if (n >= kStages && !mbar_wait(&bars->empty[st], ((n >> 1) - 1) & 1, abort_flag)) {
+          report_status(a.status, kWaitEmptyTimeout, 100, bh, n);
+          ok = false;
+          break;
+        }
+        uint8_t* base = smem + st * kStageBytes;
+        const int chunk = bh * N + n;
+        mbar_arrive_expect_tx(&bars->full[st], kA1Bytes + kA2Bytes / 2 + kKdBytes);
+        tma_load_2d(base, &t_kq, &bars->full[st], 0, chunk * 128);
+        tma_load_2d(base + 16384, &t_kq, &bars->full[st], 64, chunk * 128);
+        tma_load_2d(base + kA1Bytes + kA2Bytes / 2, &t_intra, &bars->full[st], 0, chunk * 64);
+        tma_load_2d(base + kA1Bytes + kA2Bytes, &t_kdec, &bars->full[st], 0, chunk * 64);
+        tma_load_2d(base + kA1Bytes + kA2Bytes + 8192, &t_kdec, &bars->full[st], 64, chunk * 64);
+      }
+      if (!ok || *abort_flag) {
+        // leave no bulk copy in flight: wait (bounded) for the last fill of each stage to land
+        const uint64_t tw = globaltimer_ns();
+        for (int s = 0; s < kStages; ++s) {
+          const int uses = (issued + 1 - s) / 2;
+          if (uses > 0)
+            while (!mbar_try_wait(&bars->full[s], (uses - 1) & 1) && globaltimer_ns() - tw < 2000000ull) {
+            }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc_kn = make_idesc(128, 128, 0, 1, 1);   // A K-major, B MN-major
+    constexpr uint32_t idesc_nn = make_idesc(128, 128, 1, 1, 1);   // both MN-major
+    const uint32_t a_sb = smem_u32(sb), a_vn = smem_u32(vn);
+    for (int n = 0; n < N; ++n) {
+      const int st = n & 1;
+      const uint32_t a1 = smem_u32(smem + st * kStageBytes), a2 = a1 + kA1Bytes, kd = a2 + kA2Bytes;
+      if (!mbar_wait(&bars->s_ready, n & 1, abort_flag) || !mbar_wait(&bars->full[st], (n >> 1) & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 101, bh, n);
+        break;
+      }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)   // K = dk = 128: block k / 4, 32 bytes per step
+          umma_bf16(tmem, make_smem_desc(a1 + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(a_sb + k * 2048, 16384, 1024), idesc_kn, k > 0 ? 1u : 0u);
+        tc_commit(&bars->d_full);
+      }
+      __syncwarp();
+      if (!mbar_wait(&bars->vn_ready, n & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 102, bh, n);
+        break;
+      }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // K = 64 tokens
+          umma_bf16(tmem, make_smem_desc(a2 + k * 32, 16, 1024), make_smem_desc(a_vn + k * 2048, 8192, 1024), idesc_kn, 1u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tmem + 128, make_smem_desc(kd + k * 2048, 8192, 1024), make_smem_desc(a_vn + k * 2048, 8192, 1024),
+                    idesc_nn, k > 0 ? 1u : 0u);
+        tc_commit(&bars->empty[st]);
+        tc_commit(&bars->p_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;                     // row of D / P / S owned by this thread
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    float S[kDv];
+    if (a.s0 != nullptr) {
+      const float4* sp = reinterpret_cast<const float4*>(a.s0 + (static_cast<int64_t>(bh) * kDk + r) * kDv);
+#pragma unroll
+      for (int j = 0; j < kDv / 4; ++j) {
+        const float4 f = sp[j];
+        S[4 * j] = f.x; S[4 * j + 1] = f.y; S[4 * j + 2] = f.z; S[4 * j + 3] = f.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kDv; ++j) S[j] = 0.f;
+    }
+    bool ok = true;
+    for (int n = 0; n <= N; ++n) {
+      // ---- publish S (bf16) for the next chunk's first product ----
+      if (n < N) {
+#pragma unroll
+        for (int c = 0; c < kDv; c += 8)
+          *reinterpret_cast<uint4*>(sb + swz(r, c, 16384)) =
+              make_uint4(pack_bf16x2(S[c], S[c + 1]), pack_bf16x2(S[c + 2], S[c + 3]), pack_bf16x2(S[c + 4], S[c + 5]),
+                         pack_bf16x2(S[c + 6], S[c + 7]));
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->s_ready);
+      } else {
+        break;
+      }
+      const int64_t chunk = static_cast<int64_t>(bh) * N + n;
+      // rows 0..63 own a token of the chunk: fetch its corrected value early
+      uint4 ve[16];
+      if (r < kC) {
+        const uint4* vp = reinterpret_cast<const uint4*>(a.veff + (chunk * kC + r) * kDv);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) ve[j] = __ldg(vp + j);
+      }
+      const float e = a.e[chunk];
+      if (ok && !mbar_wait(&bars->d_full, n & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 103, bh, n);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok && r < kC) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            const uint4 u = ve[c * 4 + (j >> 3)];
+            const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+            *reinterpret_cast<uint4*>(vn + swz(r, c * 32 + j, 8192)) = make_uint4(
+                pack_bf16x2(f0.x - __uint_as_float(v[j]), f0.y - __uint_as_float(v[j + 1])),
+                pack_bf16x2(f1.x - __uint_as_float(v[j + 2]), f1.y - __uint_as_float(v[j + 3])),
+                pack_bf16x2(f2.x - __uint_as_float(v[j + 4]), f2.y - __uint_as_float(v[j + 5])),
+                pack_bf16x2(f3.x - __uint_as_float(v[j + 6]), f3.y - __uint_as_float(v[j + 7])));
+          }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(&bars->vn_ready);
+      if (ok && !mbar_wait(&bars->p_full, n & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 104, bh, n);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) continue;
+      tc_fence_after();
+      if (r >= kC) {   // rows 64..127 of D are the chunk's outputs
+        uint4* op = reinterpret_cast<uint4*>(a.o + (chunk * kC + (r - kC)) * kDv);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + c * 32 + lane_off, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8)
+            op[c * 4 + (j >> 3)] = make_uint4(pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
+                                               pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
+                                               pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])),
+                                               pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + 128 + c * 32 + lane_off, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) S[c * 32 + j] = S[c * 32 + j] * e + __uint_as_float(v[j]);
+      }
+      tc_fence_before();
+    }
+    if (ok) {
+      float4* sp = reinterpret_cast<float4*>(a.s_out + (static_cast<int64_t>(bh) * kDk + r) * kDv);
+#pragma unroll
+      for (int j = 0; j < kDv / 4; ++j) sp[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// y[b, t, c] = silu(sum_j w[c, j] x[b, t - (K-1) + j, c]); state[b, c, :] = the last K raw inputs (zero padded).
+template <int K>
+__global__ void gdn_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                     __nv_bfloat16* __restrict__ y, float* __restrict__ state, int T, int C) {
+  const int b = blockIdx.z, t = blockIdx.y;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float wv[8][K];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) wv[i][j] = __bfloat162float(w[(c0 + i) * K + j]);
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    const int tt = t - (K - 1) + j;
+    if (tt < 0) continue;
+    const uint4 u = *reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(b) * T + tt) * C + c0);
+    const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(in[e]);
+      acc[2 * e] += wv[2 * e][j] * f.x;
+      acc[2 * e + 1] += wv[2 * e + 1][j] * f.y;
+    }
+    if (state != nullptr && t == T - 1) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(in[e]);
+        state[(static_cast<int64_t>(b) * C + c0 + 2 * e) * K + j] = f.x;
+        state[(static_cast<int64_t>(b) * C + c0 + 2 * e + 1) * K + j] = f.y;
+      }
+    }
+  }
+  if (state != nullptr && t == T - 1) {
+    for (int j = 0; j < K; ++j)
+      if (t - (K - 1) + j < 0)
+        for (int i = 0; i < 8; ++i) state[(static_cast<int64_t>(b) * C + c0 + i) * K + j] = 0.f;
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float a0 = acc[2 * e], a1 = acc[2 * e + 1];
+    o[e] = pack_bf16x2(a0 / (1.f + __expf(-a0)), a1 / (1.f + __expf(-a1)));
+  }
+  *reinterpret_cast<uint4*>(y + (static_cast<int64_t>(b) * T + t) * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+}  // namespace
+
+cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
+                            const __nv_bfloat16* veff, const float* e, const float* s0, __nv_bfloat16* o, float* s_out,
+                            int bh, int n_chunks, int* status, cudaStream_t stream) {
+  if (bh < 1 || n_chunks < 1) return cudaErrorInvalidValue;
+  CUtensorMap t_kq, t_intra, t_kdec;
+  cudaError_t err;
+  const uint64_t chunks = static_cast<uint64_t>(bh) * n_chunks;
+  if ((err = encode_tma_2d(&t_kq, kq, 2, kDk, chunks * 128, kDk * 2ull, 64, 128)) != cudaSuccess) return err;
+  if ((err = encode_tma_2d(&t_intra, intra, 2, kC, chunks * kC, kC * 2ull, 64, 64)) != cudaSuccess) return err;
+  if ((err = encode_tma_2d(&t_kdec, kdec, 2, kDk, chunks * kC, kDk * 2ull, 64, 64)) != cudaSuccess) return err;
+  static bool configured = false;
+  if (!configured) {
+    if ((err = cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return err;
+    configured = true;
+  }
+  ScanArgs args{n_chunks, veff, e, s0, o, s_out, status};
+  gdn_scan_kernel<<<bh, kThreads, kSmem, stream>>>(t_kq, t_intra, t_kdec, args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, float* state, int B,
+                                 int T, int C, int K, cudaStream_t stream) {
+  if (K != 4 || C % 8 != 0 || B < 1 || T < 1) return cudaErrorInvalidValue;
+  const int threads = 128;
+  const dim3 grid((C / 8 + threads - 1) / threads, T, B);
+  gdn_conv_silu_kernel<4><<<grid, threads, 0, stream>>>(x, w, y, state, T, C);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

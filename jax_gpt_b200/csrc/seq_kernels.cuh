@@ -41,4 +41,19 @@ cudaError_t launch_gdn_decode_step(const __nv_bfloat16* mixed, const __nv_bfloat
                                    const __nv_bfloat16* norm_w, float* state, __nv_bfloat16* out, int B, int Hqk, int Hv,
                                    int dk, int dv, int Kc, float eps, cudaStream_t st);
 
+// Inter-chunk scan of the chunked gated delta rule (gdn_kernels.cu); head widths dk = dv = 128, chunks of 64.
+//   kq    [BH, N, 128, 128] bf16: rows 0-63 k_cum, rows 64-127 q * exp(G) of every chunk
+//   intra [BH, N, 64, 64]   bf16: causal-masked (q k^T * decay)
+//   kdec  [BH, N, 64, 128]  bf16: k * exp(g_end - G)
+//   veff  [BH, N, 64, 128]  bf16: corrected values;  e [BH, N] fp32: exp(g_end);  s0: initial state or nullptr
+// Writes o [BH, N, 64, 128] bf16 and the final state s_out [BH, 128, 128] fp32.
+cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
+                            const __nv_bfloat16* veff, const float* e, const float* s0, __nv_bfloat16* o, float* s_out,
+                            int bh, int n_chunks, int* status, cudaStream_t stream);
+
+// Causal depthwise conv (width 4) + SiLU over x [B, T, C] bf16 with w [C, 4]; `state` (optional) [B, C, 4] fp32
+// receives the last four raw inputs of every channel.
+cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, float* state, int B,
+                                 int T, int C, int K, cudaStream_t stream);
+
 }  // namespace b200

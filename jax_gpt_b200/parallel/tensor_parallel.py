@@ -82,3 +82,68 @@ def matmul_reduce_scatter_nccl(x, w, group=None):
     out = torch.empty(x.shape[0] // world, w.shape[1], device=x.device, dtype=torch.float32)
     dist.reduce_scatter_tensor(out, part, group=group)
     return out.to(torch.bfloat16)
+
+
+# ---- vocabulary-parallel cross-entropy --------------------------------------------------------
+def vocab_parallel_ce_reference(logits_local: torch.Tensor, targets: torch.Tensor, v0: int, group=None):
+    """Per-row loss and the local-shard gradient ``softmax - onehot`` with library collectives
+    (all_reduce of max / sum-exp / target logit). Works on CPU (gloo) ranks: the host-side protocol."""
+    lf = logits_local.float()
+    m = lf.max(dim=-1).values
+    dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
+    e = torch.exp(lf - m[:, None])
+    s = e.sum(-1)
+    dist.all_reduce(s, group=group)
+    tg = targets.long() - v0
+    mine = (tg >= 0) & (tg < lf.shape[1])
+    tl = torch.where(mine, lf.gather(1, tg.clamp(0, lf.shape[1] - 1)[:, None])[:, 0], torch.zeros_like(m))
+    dist.all_reduce(tl, group=group)
+    valid = targets >= 0
+    loss = torch.where(valid, torch.log(s) + m - tl, torch.zeros_like(m))
+    grad = e / s[:, None]
+    grad[mine, tg[mine]] -= 1.0
+    grad = grad * valid[:, None]
+    return loss, grad
+
+
+class _VocabParallelCEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits_local, targets, vp):
+        M = logits_local.shape[0]
+        loss = torch.empty(M, device=logits_local.device, dtype=torch.float32)
+        n_valid = (targets >= 0).sum().clamp_min(1).float()
+        c = vp.comm
+        _ext.ops().vocab_parallel_ce(c.world, c.rank, logits_local, targets, vp.v_local, vp.v0, vp.stats(M).peer_ptrs,
+                                     c.ctrl.peer_ptrs, loss, 1.0, True, c.wait_seconds)
+        ctx.save_for_backward(logits_local, n_valid)
+        return loss.sum() / n_valid
+
+    @staticmethod
+    def backward(ctx, g):
+        dlogits, n_valid = ctx.saved_tensors
+        return dlogits.mul_((g / n_valid).to(dlogits.dtype)), None, None
+
+
+class VocabParallelCE:
+    """Mean token cross-entropy over logits whose vocabulary axis is sharded across the ranks of ``comm``
+    (rank r holds columns ``[r * v_local, (r + 1) * v_local)``): ONE kernel computes the shard statistics,
+    exchanges them through peer memory, and turns the shard into its gradient in place - the (M, V)
+    logits are never gathered (the reference all-gathers them implicitly through GSPMD when it evaluates
+    ``optax.softmax_cross_entropy_with_integer_labels``, jax_gpt/trainer/train_step.py:24-31)."""
+
+    def __init__(self, comm: Communicator, vocab_size: int):
+        assert vocab_size % comm.world == 0
+        self.comm = comm
+        self.v_local = vocab_size // comm.world
+        self.v0 = comm.rank * self.v_local
+        self._stats = {}
+
+    def stats(self, M: int):
+        if M not in self._stats:
+            self._stats[M] = self.comm.alloc(2 * self.comm.world * M * 4, torch.float32)
+        return self._stats[M]
+
+    def __call__(self, logits_local: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """logits_local (M, >= v_local) bf16, CONSUMED (overwritten with its gradient); targets (M,) global ids."""
+        logits_local = logits_local.reshape(-1, logits_local.shape[-1])
+        return _VocabParallelCEFn.apply(logits_local, targets.reshape(-1).to(torch.int32).contiguous(), self)

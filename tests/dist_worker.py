@@ -228,6 +228,39 @@ def run_ep_fp8(rank, world, device):
     return res
 
 
+def run_vocab_ce(rank, world, device):
+    """Vocabulary-parallel cross-entropy (one kernel, statistics exchanged over peer memory) vs the full softmax."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.comm.symm import Communicator
+    from jax_gpt_b200.parallel.tensor_parallel import VocabParallelCE, vocab_parallel_ce_reference
+    M, V, D = 777, 50304, 256
+    g = torch.Generator(device=device).manual_seed(11)
+    h = torch.randn(M, D, device=device, generator=g).to(torch.bfloat16)
+    w = (torch.randn(D, V, device=device, generator=g) * 0.2).to(torch.bfloat16)
+    targets = torch.randint(0, V, (M,), device=device, generator=g)
+    targets[5] = -1
+    comm = Communicator(device=device, wait_seconds=5.0)
+    vp = VocabParallelCE(comm, V)
+    res = {}
+    for step in range(3):
+        w_local = w[:, vp.v0:vp.v0 + vp.v_local].contiguous().requires_grad_(True)
+        logits_local = (h @ w_local)
+        keep = logits_local.detach().clone()
+        loss = vp(logits_local, targets)
+        loss.backward()
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        wf = w.float().requires_grad_(True)
+        full = torch.nn.functional.cross_entropy(h.float() @ wf, targets.long(), ignore_index=-1)
+        full.backward()
+        res[f"loss_err{step}"] = abs(loss.item() - full.item()) / full.item()
+        res[f"dw_rel{step}"] = rel(w_local.grad, wf.grad[:, vp.v0:vp.v0 + vp.v_local])
+        l2, g2 = vocab_parallel_ce_reference(keep, targets, vp.v0)
+        res[f"ref_loss_err{step}"] = abs((l2.sum() / (targets >= 0).sum()).item() - full.item()) / full.item()
+        dist.barrier()
+    return res
+
+
 def run_moe_train(rank, world, device):
     """Qwen3.5-style training with expert parallelism (fused MoE forward/backward kernels) and the fused
     sharded optimizer for the dense weights, against one process that holds all experts and sees every
@@ -293,6 +326,8 @@ def main():
         res = run_ep(rank, world, device)
     elif what == "ep_bwd":
         res = run_ep_bwd(rank, world, device)
+    elif what == "vocab_ce":
+        res = run_vocab_ce(rank, world, device)
     elif what == "ep_fp8":
         res = run_ep_fp8(rank, world, device)
     elif what == "moe_train":

@@ -59,6 +59,12 @@ def test_fused_ep_moe_backward_two_gpus(tmp_path):
         assert v < 3e-2, res
 
 
+def test_vocab_parallel_cross_entropy_two_gpus(tmp_path):
+    res = _run("vocab_ce", tmp_path, port=29618)
+    for k, v in res.items():
+        assert v < (2e-2 if k.startswith("dw") else 3e-3), res
+
+
 def test_fused_ep_moe_fp8_two_gpus(tmp_path):
     res = _run("ep_fp8", tmp_path, port=29617)
     for k, v in res.items():

@@ -102,3 +102,26 @@ def test_watchdog_detects_a_dead_rank():
             assert open(os.path.join(d, f"res.{r}")).read() == "[1]"
         for p in ctx.processes:
             p.join(timeout=5)
+
+
+def _vce_worker(rank, world, path):
+    from jax_gpt_b200.parallel.tensor_parallel import vocab_parallel_ce_reference
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(0)
+    M, V = 33, 64
+    logits = torch.randn(M, V, generator=g) * 3
+    targets = torch.randint(0, V, (M,), generator=g)
+    targets[4] = -1
+    vl = V // world
+    loss, grad = vocab_parallel_ce_reference(logits[:, rank * vl:(rank + 1) * vl].clone(), targets, rank * vl)
+    lf = logits.clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, targets, ignore_index=-1, reduction="none")
+    ref.sum().backward()
+    assert torch.allclose(loss, ref, atol=1e-5)
+    assert torch.allclose(grad, lf.grad[:, rank * vl:(rank + 1) * vl], atol=1e-5)
+    dist.destroy_process_group()
+
+
+def test_vocab_parallel_cross_entropy_protocol_on_cpu_ranks():
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_vce_worker, args=(2, os.path.join(d, "rdv")), nprocs=2, join=True)
