@@ -43,6 +43,13 @@ def causal_conv1d_prefill(x: torch.Tensor, weight: torch.Tensor):
     """x (B, T, C); depthwise causal FIR of width K then SiLU. Final state = last K raw inputs."""
     B, T, C = x.shape
     K = weight.shape[-1]
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    if x.is_cuda and x.dtype == torch.bfloat16 and K == 4 and C % 8 == 0 and not needs_grad:
+        from ... import _ext
+        y = torch.empty_like(x, memory_format=torch.contiguous_format)
+        state = torch.empty(B, C, K, device=x.device, dtype=torch.float32)
+        _ext.ops().gdn_conv_silu(x.contiguous(), weight.to(torch.bfloat16).contiguous(), y, state)
+        return y, state.to(x.dtype)
     xc = F.pad(x.transpose(1, 2).float(), (K - 1, 0))
     y = F.conv1d(xc, weight.float()[:, None, :], groups=C)
     state = xc[:, :, -K:] if T >= 1 else xc
@@ -127,6 +134,22 @@ def chunk_gated_delta_rule(q, k, v, beta, g, chunk_size: int, initial_state=None
     rhs = torch.cat([v * beta[..., None], kb * torch.exp(G)[..., None]], dim=-1)
     sol = torch.linalg.solve_triangular(eye + A, rhs, upper=False, unitriangular=True)
     v_eff, k_cum = sol[..., :dv], sol[..., dv:]
+    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, beta, g))
+    if q.is_cuda and dk == 128 and dv == 128 and C == 64 and not needs_grad:
+        # the sequential part runs as ONE kernel per (batch, head) with the state on chip (csrc/gdn_kernels.cu)
+        from ... import _ext
+        bf = torch.bfloat16
+        g_end = G[..., -1]
+        kq = torch.cat([k_cum, q * torch.exp(G)[..., None]], dim=-2).to(bf).reshape(B * H, N, 2 * C, dk).contiguous()
+        intra = ((q @ k.transpose(-1, -2)) * decay).masked_fill(~causal, 0.0).to(bf).reshape(B * H, N, C, C).contiguous()
+        kdec = (k * torch.exp(g_end[..., None] - G)[..., None]).to(bf).reshape(B * H, N, C, dk).contiguous()
+        veff = v_eff.to(bf).reshape(B * H, N, C, dv).contiguous()
+        e = torch.exp(g_end).float().reshape(B * H, N).contiguous()
+        s0 = initial_state.float().reshape(B * H, dk, dv).contiguous() if initial_state is not None else None
+        o = torch.empty(B * H, N, C, dv, device=q.device, dtype=bf)
+        s_out = torch.empty(B * H, dk, dv, device=q.device, dtype=torch.float32)
+        _ext.ops().gdn_scan(kq, intra, kdec, veff, e, s0, o, s_out)
+        return o.reshape(B, H, N * C, dv)[:, :, :T].float(), s_out.reshape(B, H, dk, dv)
     S = initial_state.float() if initial_state is not None else q.new_zeros(B, H, dk, dv)
     outs = []
     for n in range(N):

@@ -171,3 +171,47 @@ def test_mxfp8_gemm_hardware_block_scales(cuda_device, M, N, K):
     ref = Q.fp8_gemm_ref(xq, xs, wq[:N], ws)
     assert _rel(out, ref) < 5e-3, _rel(out, ref)
     assert _rel(out, x.float() @ w.float().t()) < 6e-2
+
+
+def test_gdn_conv_silu_kernel(cuda_device):
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    torch.manual_seed(0)
+    B, T, C = 2, 70, 1024
+    x = torch.randn(B, T, C, device=cuda_device).to(torch.bfloat16)
+    w = (torch.randn(C, 4, device=cuda_device) * 0.5).to(torch.bfloat16)
+    with torch.no_grad():
+        y, st = D.causal_conv1d_prefill(x, w)
+        y_ref, st_ref = D.causal_conv1d_prefill(x.float().cpu(), w.float().cpu())
+    assert _rel(y.cpu(), y_ref) < 1e-2
+    assert torch.equal(st.float().cpu(), st_ref)
+    with torch.no_grad():
+        _, st1 = D.causal_conv1d_prefill(x[:, :2].contiguous(), w)      # shorter than the window: zero padded
+    assert torch.equal(st1.float().cpu(), D.causal_conv1d_prefill(x[:, :2].float().cpu(), w.float().cpu())[1])
+
+
+@pytest.mark.parametrize("T,with_state", [(64, False), (200, False), (1024, True)])
+def test_gdn_chunk_scan_kernel(cuda_device, T, with_state):
+    """Chunked gated delta rule with the tcgen05 inter-chunk scan vs the token-by-token recurrence in fp32."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    torch.manual_seed(1)
+    B, H, dk, dv = 2, 3, 128, 128
+    q = D._l2_norm(torch.randn(B, H, T, dk)) * dk ** -0.5
+    k = D._l2_norm(torch.randn(B, H, T, dk))
+    v = torch.randn(B, H, T, dv)
+    beta = torch.sigmoid(torch.randn(B, H, T))
+    g = -torch.rand(B, H, T) * 0.2
+    s0 = torch.randn(B, H, dk, dv) * 0.1 if with_state else None
+    S = s0.clone() if with_state else torch.zeros(B, H, dk, dv)
+    outs = []
+    for t in range(T):
+        o, S = D.gated_delta_step(q[:, :, t], k[:, :, t], v[:, :, t], beta[:, :, t], g[:, :, t], S)
+        outs.append(o)
+    ref = torch.stack(outs, dim=2)
+    dev = lambda t: None if t is None else t.to(cuda_device)
+    with torch.no_grad():
+        o_k, S_k = D.chunk_gated_delta_rule(dev(q), dev(k), dev(v), dev(beta), dev(g), 64, dev(s0))
+    torch.cuda.synchronize()
+    _ext.check_status(cuda_device)
+    assert _rel(o_k.cpu(), ref) < 2e-2, _rel(o_k.cpu(), ref)
+    assert _rel(S_k.cpu(), S) < 2e-2, _rel(S_k.cpu(), S)
