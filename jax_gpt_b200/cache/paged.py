@@ -8,8 +8,8 @@ the 576-wide latent (compressed KV + rotary key); for gated-attention layers it 
 the 2 KV heads.
 
 Bookkeeping (free list, page lists, lengths) lives in the native ``PageTable`` of
-csrc/runtime.cpp, which owns pinned host mirrors of the block table and the length vector; the
-cache uploads them with one asynchronous copy when they changed. Without the library the same
+csrc/runtime.cpp, which owns host mirrors of the block table and the length vector; the cache
+uploads them when they changed (the upload snapshots the pageable mirrors at call time). Without the library the same
 bookkeeping runs in ``PageAllocator`` (Python). On CUDA, new rows are scattered into their pages
 by the ``paged_kv_write`` kernel and read by the paged decode kernel (csrc/mla_decode_sm100.cu).
 """

@@ -31,7 +31,7 @@ def rmsnorm_rope(x, norm_w, freqs, rope_dim: int, pos0: int = 0, eps: float = 1e
     per = dh // 32 if dh % 32 == 0 else 0
     ok = (x.is_cuda and x.dtype == torch.bfloat16 and per and dh <= 256 and
           (rope_dim == 0 or ((rope_dim // 2) % per == 0)))
-    if not ok or (torch.is_grad_enabled() and (x.requires_grad or norm_w.requires_grad)):
+    if not ok or (torch.is_grad_enabled() and (x.requires_grad or (norm_w is not None and norm_w.requires_grad))):
         # gradients come from the PyTorch restatement of the same math
         return rmsnorm_rope_ref(x, norm_w, freqs, rope_dim, pos0, eps, one_plus)
     xc = x.contiguous().view(B * T, H, dh)
