@@ -20,8 +20,8 @@ struct MlaDecodeArgs {
   const int* seq_lens;            // [max_seqs] tokens to attend over (the new token included)
   const int* seq_ids;             // [batch] row of block_table / seq_lens for every batch slot
   float scale_log2;               // softmax scale * log2(e)
-  float* part_out;                // [batch, n_splits, heads, 512] normalised partial outputs
-  float* part_lse;                // [batch, n_splits, heads] log2-sum-exp of each split (-inf when empty)
+  float* part_out;                // [batch, 2 * n_splits, heads, 512] normalised partials (two softmax groups per split)
+  float* part_lse;                // [batch, 2 * n_splits, heads] log2-sum-exp of each partial (-inf when empty)
   int* status;
 };
 

@@ -195,7 +195,7 @@ def _decode_with_pending_token(q_full, cache, layer, seq_ids, scale):
 def _splits_for(cache, seq_ids, q_full) -> int:
     B, H, _ = q_full.shape
     sms = torch.cuda.get_device_properties(q_full.device).multi_processor_count
-    ctas = B * ((H + 31) // 32)
+    ctas = B * (1 if H <= 16 else (H + 31) // 32)
     longest = max(cache.length(s) for s in seq_ids) + 1
     return max(1, min(sms // max(ctas, 1), (longest + 127) // 128, 32))
 

@@ -38,11 +38,11 @@ def mla_paged_decode(q_lat, cache, layer: int, seq_ids, scale: float, latent: in
     dev = q_lat.device
     if n_splits <= 0:
         sms = _SM_COUNT.setdefault(dev.index, torch.cuda.get_device_properties(dev).multi_processor_count)
-        ctas = B * ((H + 31) // 32)
+        ctas = B * (1 if H <= 16 else (H + 31) // 32)
         longest = max(cache.length(s) for s in seq_ids)
-        n_splits = max(1, min(sms // max(ctas, 1), (longest + 127) // 128, 32))
-    part_out = torch.empty(B * n_splits * H * 512, device=dev, dtype=torch.float32)
-    part_lse = torch.empty(B * n_splits * H, device=dev, dtype=torch.float32)
+        n_splits = max(1, min(sms // max(ctas, 1), (longest + 127) // 128, 32))   # at least two tiles per CTA
+    part_out = torch.empty(2 * B * n_splits * H * 512, device=dev, dtype=torch.float32)   # two softmax groups per split
+    part_lse = torch.empty(2 * B * n_splits * H, device=dev, dtype=torch.float32)
     out = torch.empty(B, H, 512, device=dev, dtype=torch.bfloat16)
     _ext.ops().mla_paged_decode(q_lat.contiguous(), cache.pool[layer], cache.block_table, cache.seq_lens,
                                 cache.seq_id_tensor(seq_ids), scale, n_splits, part_out, part_lse, out)

@@ -51,6 +51,7 @@ def main(argv=None):
     ap.add_argument("--H", type=int, default=12)
     ap.add_argument("--D", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0, help="mla_decode: KV splits per sequence (0 = fill the SMs)")
+    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays (excludes host launch overhead)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args(argv)
@@ -138,9 +139,9 @@ def main(argv=None):
         cache.commit(ids, T)
         q = (torch.randn(B, H, 576, device=dev) * 0.3).to(torch.bfloat16)
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        ns = args.splits or max(1, min(sms // (B * ((H + 31) // 32)), (T + 127) // 128, 32))
-        part_out = torch.empty(B * ns * H * 512, device=dev)
-        part_lse = torch.empty(B * ns * H, device=dev)
+        ns = args.splits or max(1, min(sms // (B * (1 if H <= 16 else (H + 31) // 32)), (T + 127) // 128, 32))
+        part_out = torch.empty(2 * B * ns * H * 512, device=dev)
+        part_lse = torch.empty(2 * B * ns * H, device=dev)
         out = torch.empty(B, H, 512, device=dev, dtype=torch.bfloat16)
         idt = cache.seq_id_tensor(ids)
         pool0 = cache.pool[0]
@@ -150,7 +151,18 @@ def main(argv=None):
         flops = 2.0 * B * H * T * (576 + 512)
     else:
         raise SystemExit(f"unknown op {args.op}")
-    ms = _time(fn, args.warmup, args.iters)
+    if args.graph:
+        # launch-bound ops: replay `--iters` launches from one CUDA graph so that host time is excluded
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(args.iters):
+                fn()
+        inner = args.iters
+        ms = _time(graph.replay, args.warmup, 3) / inner
+    else:
+        ms = _time(fn, args.warmup, args.iters)
     _ext.check_status(dev)
     res = {"op": args.op, "ms": ms, "args": {k: v for k, v in vars(args).items() if k not in ("op",)}}
     if flops:
