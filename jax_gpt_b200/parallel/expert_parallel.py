@@ -267,6 +267,44 @@ class EPMoERuntime:
         return self(x, weights, idx, params)
 
 
+class EPMoEInferenceRuntime:
+    """Expert-parallel dispatcher for inference: one fused-kernel buffer set per token count (a prefill
+    shape and a decode shape), bf16 or FP8. With ``fp8`` the layer's parameter dict must hold the
+    pre-quantised weights of ``quantize_expert_weights_fp8`` (``gate_q`` ... ``sfb2``)."""
+
+    def __init__(self, comm: Communicator, d_model: int, inter: int, n_experts: int, top_k: int, fp8: bool = False,
+                 cap_factor: Optional[float] = None):
+        self.comm, self.shape, self.fp8, self.cap_factor = comm, (d_model, inter, n_experts, top_k), fp8, cap_factor
+        self._layers = {}
+
+    def _layer(self, tokens: int):
+        if tokens not in self._layers:
+            cls = FusedEPMoEFp8 if self.fp8 else FusedEPMoE
+            self._layers[tokens] = cls(self.comm, tokens, *self.shape, cap_factor=self.cap_factor)
+        return self._layers[tokens]
+
+    def forward(self, x, weights, idx, params):
+        layer = self._layer(x.shape[0])
+        if self.fp8:
+            return layer.forward(x, weights, idx, params).to(x.dtype)
+        return layer.forward(x, weights, idx, params).to(x.dtype)
+
+    __call__ = forward
+
+
+def quantize_stacked_experts_fp8(moe_params: dict) -> dict:
+    """``moe_params``: a MoE parameter dict whose expert weights carry a leading layer axis
+    ((L, E, D, I) / (L, E, I, D)). Returns a copy in which they are replaced by the stacked FP8 tensors
+    (``gate_q`` ... ``sfb2`` with the same leading axis); the other entries are kept."""
+    L = moe_params["gate_proj"].shape[0]
+    per = [quantize_expert_weights_fp8({n: moe_params[n][l] for n in ("gate_proj", "up_proj", "down_proj")})
+           for l in range(L)]
+    out = {k: v for k, v in moe_params.items() if k not in ("gate_proj", "up_proj", "down_proj")}
+    for k in ("gate_q", "up_q", "down_q", "sfb1", "sfb2"):
+        out[k] = torch.stack([p[k] for p in per])
+    return out
+
+
 def shard_experts(params: dict, rank: int, world: int, names=("gate_proj", "up_proj", "down_proj"), _path=()) -> dict:
     """Copy of a parameter tree in which the stacked routed-expert weights (expert axis third from last)
     keep only the experts ``[rank * E / world, (rank + 1) * E / world)`` of this rank."""

@@ -23,7 +23,7 @@ from utils import init_distributed, qwen_config
 
 import torch
 
-SCENARIOS = {"8k1k": (8192, 1024), "1k1k": (1024, 1024), "1k8k": (1024, 8192), "tiny": (32, 8)}
+SCENARIOS = {"8k1k": (8192, 1024), "1k1k": (1024, 1024), "1k8k": (1024, 8192), "2k256": (2048, 256), "tiny": (32, 8)}
 
 
 class _Timer:
@@ -76,20 +76,50 @@ def make_runner(args, device):
     from jax_gpt_b200.models.qwen35.sharding import tree_map
     cfg = {"tiny": DeepSeekV3Config.tiny, "8l": DeepSeekV3Config.eight_layer, "full": DeepSeekV3Config.full}[args.config]()
     if args.n_layers:
-        cfg = cfg.replace(n_layers=args.n_layers, first_k_dense=min(cfg.first_k_dense, args.n_layers))
-    params = tree_map(lambda t: t.to(device), init_params(cfg, 0, dtype=dtype))
+        cfg = cfg.replace(n_layers=args.n_layers, first_k_dense=min(cfg.first_k_dense, max(args.n_layers - 1, 0)))
+    if args.experts:
+        cfg = cfg.replace(n_routed_experts=args.experts)
+    params = init_params(cfg, 0, dtype=dtype)
+    ep = None
+    import torch.distributed as dist
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if world > 1 and device.type == "cuda" and cfg.n_moe_layers > 0:
+        # data-parallel attention (every rank serves its own sequences), expert-parallel MoE over all ranks
+        from jax_gpt_b200.comm.symm import Communicator
+        from jax_gpt_b200.parallel.expert_parallel import (EPMoEInferenceRuntime, quantize_stacked_experts_fp8,
+                                                           shard_experts)
+        params = shard_experts(params, dist.get_rank(), world)
+        params = tree_map(lambda t: t.to(device), params)
+        if args.fp8:
+            params["moe_layers"]["moe"] = quantize_stacked_experts_fp8(params["moe_layers"]["moe"])
+        ep = EPMoEInferenceRuntime(Communicator(device=device, wait_seconds=30.0), cfg.d_model, cfg.moe_intermediate_size,
+                                   cfg.n_routed_experts, cfg.n_experts_per_token, fp8=args.fp8)
+    else:
+        params = tree_map(lambda t: t.to(device), params)
     plen, dlen = SCENARIOS[args.scenario]
 
     def prefill(B):
         per = (plen + dlen + cfg.page_size - 1) // cfg.page_size
         cache = make_cache(cfg, B * per, B, per, dtype, device)
         tok = torch.randint(0, cfg.vocab_size, (B, plen), device=device)
-        logits = forward(params, tok, cfg, cache, list(range(B)))
+        logits = forward(params, tok, cfg, cache, list(range(B)), ep=ep)
         return logits[:, -1].argmax(-1), cache
+
+    engines = {}
 
     def decode(state):
         nxt, cache = state
-        logits = forward(params, nxt[:, None], cfg, cache, list(range(nxt.shape[0])), is_decode=True)
+        B = nxt.shape[0]
+        if args.engine and device.type == "cuda" and cfg.kv_lora_rank == 512 and cfg.qk_rope_head_dim == 64:
+            # graph-captured token step (one replay per token); the engine is built once per cache
+            from jax_gpt_b200.models.deepseek_v3.decode_engine import DeepSeekV3DecodeEngine
+            eng = engines.get(id(cache))
+            if eng is None:
+                engines.clear()
+                eng = engines[id(cache)] = DeepSeekV3DecodeEngine(params, cfg, cache, list(range(B)), ep=ep,
+                                                                  use_cuda_graph=not args.no_graph, max_len=plen + dlen)
+            return eng.step(nxt).clone(), cache
+        logits = forward(params, nxt[:, None], cfg, cache, list(range(B)), is_decode=True, ep=ep)
         return logits[:, -1].argmax(-1), cache
     return prefill, decode, cfg
 
@@ -130,6 +160,9 @@ def main(argv=None):
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--fp8", action="store_true")
     ap.add_argument("--n-layers", type=int, default=0)
+    ap.add_argument("--experts", type=int, default=0, help="deepseek_v3: override the routed expert count")
+    ap.add_argument("--engine", action="store_true", help="deepseek_v3: decode through the CUDA-graph decode engine")
+    ap.add_argument("--no-graph", action="store_true", help="with --engine: run the engine's step eagerly")
     ap.add_argument("--prefill-reps", type=int, default=5)
     ap.add_argument("--decode-steps", type=int, default=20)
     ap.add_argument("--out", default="")
@@ -147,6 +180,7 @@ def main(argv=None):
         for _ in range(args.prefill_reps):
             state, ms = timer.run(lambda: prefill(B))
             pre.append(_max_over_ranks(ms, device))
+        state = decode(state)   # untimed: first decode step (buffer set-up, graph capture)
         dec = []
         from jax_gpt_b200.utils.profiling import profiler_trace
         with profiler_trace(args.profile_dir):
@@ -155,12 +189,13 @@ def main(argv=None):
                 dec.append(_max_over_ranks(ms, device))
     dec_sorted = sorted(dec)
     res = {
-        "model": args.model, "config": args.config, "scenario": args.scenario, "batch": B, "world": world,
+        "model": args.model, "config": args.config, "scenario": args.scenario, "batch_per_rank": B,
+        "global_batch": B * world if args.model == "deepseek_v3" else B, "world": world, "fp8_moe": bool(args.fp8),
         "prefill_len": plen, "prefill_ms_mean": statistics.mean(pre),
-        "prefill_toks_per_sec": B * plen / (statistics.mean(pre) / 1e3),
+        "prefill_toks_per_sec": B * plen * (world if args.model == "deepseek_v3" else 1) / (statistics.mean(pre) / 1e3),
         "decode_ms_mean": statistics.mean(dec), "decode_ms_p50": statistics.median(dec),
         "decode_ms_p99": dec_sorted[min(len(dec) - 1, int(0.99 * len(dec)))],
-        "decode_toks_per_sec": B / (statistics.mean(dec) / 1e3), "dtype": args.dtype, "timing": "cuda events, max over ranks",
+        "decode_toks_per_sec": B * (world if args.model == "deepseek_v3" else 1) / (statistics.mean(dec) / 1e3), "dtype": args.dtype, "timing": "cuda events, max over ranks",
     }
     if rank == 0:
         print(json.dumps(res, indent=1))

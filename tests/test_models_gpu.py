@@ -142,3 +142,32 @@ def test_deepseek_v3_paged_decode_kernel_matches_prefill(cuda_device):
     got = torch.cat(outs, 1)
     assert cache.length(0) == 140
     assert _close(got[:, 130:], full[:, 130:]), ((got - full).abs().max().item())
+
+
+def test_deepseek_v3_decode_engine_matches_eager_decode(cuda_device):
+    """The device-side token step of the decode engine (positions, write slots and lengths read from device
+    memory; eager here, graph capture needs the expert-parallel dispatcher) reproduces the eager decode path."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
+    from jax_gpt_b200.models.deepseek_v3.decode_engine import DeepSeekV3DecodeEngine
+    from jax_gpt_b200.models.deepseek_v3.model import forward, init_params, make_cache
+    c = DeepSeekV3Config.tiny().replace(d_model=256, vocab_size=512, n_heads=16, qk_nope_head_dim=128,
+                                        qk_rope_head_dim=64, v_head_dim=128, q_lora_rank=128, kv_lora_rank=512,
+                                        moe_intermediate_size=128, dense_intermediate_size=512, page_size=64,
+                                        max_position_embeddings=512)
+    p = _to(init_params(c, 1), cuda_device, torch.bfloat16)
+    tok = torch.randint(0, c.vocab_size, (3, 70), generator=torch.Generator().manual_seed(2)).to(cuda_device)
+    ids = [2, 0, 1]
+    with torch.no_grad():
+        cache_a = make_cache(c, 16, 4, 4, torch.bfloat16, cuda_device)
+        cache_b = make_cache(c, 16, 4, 4, torch.bfloat16, cuda_device)
+        la = forward(p, tok[:, :64], c, cache_a, ids)
+        forward(p, tok[:, :64], c, cache_b, ids)
+        eng = DeepSeekV3DecodeEngine(p, c, cache_b, ids, ep=None)
+        for t in range(64, 70):
+            la = forward(p, tok[:, t:t + 1], c, cache_a, ids, is_decode=True)
+            eng.step(tok[:, t])
+            assert _close(eng.logits, la[:, 0]), (t, (eng.logits - la[:, 0]).abs().max().item())
+    torch.cuda.synchronize()
+    _ext.check_status(cuda_device)
+    assert cache_b.length(0) == 70 and int(cache_b.seq_lens[0]) == 70
