@@ -126,6 +126,20 @@ def main(argv=None):
         out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         fn = lambda: _ext.ops().gemm_mxfp8(xq, sfa, wq, sfb, out)
         flops, bytes_ = 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
+    elif args.op == "gdn_scan":
+        # --B (batch x heads) sequences of --T tokens: the inter-chunk scan of the gated delta rule
+        BH, N = args.B, args.T // 64
+        bf = torch.bfloat16
+        kq = (torch.randn(BH, N, 128, 128, device=dev) * 0.05).to(bf)
+        intra = (torch.randn(BH, N, 64, 64, device=dev) * 0.05).to(bf)
+        kdec = (torch.randn(BH, N, 64, 128, device=dev) * 0.05).to(bf)
+        veff = torch.randn(BH, N, 64, 128, device=dev).to(bf)
+        e = torch.full((BH, N), 0.9, device=dev)
+        o = torch.empty(BH, N, 64, 128, device=dev, dtype=bf)
+        s_out = torch.empty(BH, 128, 128, device=dev)
+        fn = lambda: _ext.ops().gdn_scan(kq, intra, kdec, veff, e, None, o, s_out)
+        bytes_ = 2.0 * BH * N * (128 * 128 + 64 * 64 + 64 * 128 * 3)
+        flops = 2.0 * BH * N * (128 * 128 * 128 + 64 * 64 * 128 + 128 * 64 * 128)
     elif args.op == "mla_decode":
         # --B sequences of --T cached tokens each, --H heads (16 = DeepSeek-V3 with 8-way head sharding)
         from ..cache.paged import PagedCache

@@ -69,7 +69,14 @@ def main(argv=None):
     ap.add_argument("--fp8", action="store_true", help="also time the FP8 (block-scaled tensor-core) fused forward")
     args = ap.parse_args(argv)
     rank, world, device = init_distributed()
-    assert world > 1, "run under torchrun with at least 2 processes"
+    if world == 1:
+        # one rank holding all experts: the same kernels with every "peer" being this GPU (the only form in
+        # which the fused kernel can be profiled: a profiler is never wrapped around a multi-rank command)
+        import os
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+        args.skip_baseline = True
     E, D, I, k, T = args.experts, args.d_model, args.inter, args.top_k, args.tokens
     el = E // world
     gen = torch.Generator(device=device).manual_seed(11 + rank)
