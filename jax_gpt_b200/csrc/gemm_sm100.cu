@@ -2,7 +2,7 @@
 //
 //   warp 0      : TMA producer  (cp.async.bulk.tensor tiles -> 128B-swizzled shared memory)
 //   warp 1      : MMA issuer    (one lane issues tcgen05.mma, accumulators live in TMEM)
-//   warps 2..5  : epilogue      (tcgen05.ld -> registers -> fused bias / GELU / residual ->
+//   warps 2..9  : epilogue      (tcgen05.ld -> registers -> fused bias / GELU / residual ->
 //                                global, or fp32 atomics into local or peer buffers)
 //
 // The tile is 128 x BN x 64 with a multi-stage shared-memory ring and two TMEM
@@ -25,7 +25,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kNumThreads = 192;
+constexpr int kNumThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 
 struct TmaSet {
   CUtensorMap m[kMaxPeers];
@@ -89,7 +89,7 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ T
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->tmem_full[a], 1);
-      mbar_init(&bars->tmem_empty[a], 4);
+      mbar_init(&bars->tmem_empty[a], 8);
     }
     bars->abort_flag = 0;
     fence_mbar_init();
@@ -109,12 +109,19 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ T
   auto decode_tile = [&](int t, int& m_blk, int& n_blk, int& ks) {
     ks = t % split_k;
     int mn = t / split_k;
-    int mi = mn % m_blocks;
-    n_blk = mn / m_blocks;
     if (gi.n_src > 1) {
-      mi = (mi + gi.first_src * gi.blocks_per_src) % m_blocks;
+      int mi = mn % m_blocks;
+      n_blk = mn / m_blocks;
+      m_blk = (mi + gi.first_src * gi.blocks_per_src) % m_blocks;
+      return;
     }
-    m_blk = mi;
+    // bands of 16 m-blocks: one wave of CTAs then touches ~16 x 9 tiles instead of a whole column of A
+    constexpr int kBand = 16;
+    const int per_band = kBand * n_blocks;
+    const int band = mn / per_band, r = mn - band * per_band;
+    const int rows = min(kBand, m_blocks - band * kBand);
+    m_blk = band * kBand + r % rows;
+    n_blk = r / rows;
   };
 
   if (warp == 0) {
@@ -231,6 +238,7 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ T
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp converts and stores
     int iter = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
@@ -250,7 +258,7 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ T
       // Empty K range (possible only for trailing splits): nothing was accumulated.
       const bool has_k = ks * kb_per_split < total_kb;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= args.N) break;  // uniform across the warp
         uint32_t v[32];
