@@ -11,7 +11,7 @@ cudaError_t launch_norm_fwd(int mode, const __nv_bfloat16* x, const __nv_bfloat1
                             __nv_bfloat16* y, float* mean, float* rstd, int M, int D, float eps, cudaStream_t st);
 // dx = norm_bwd(dy) (+ dres); dgamma/dbeta are ACCUMULATED. `partials` is scratch of
 // norm_bwd_scratch_floats(D) floats: per-block partial sums, reduced by a second kernel.
-constexpr int kNormBwdMaxBlocks = 296;
+constexpr int kNormBwdMaxBlocks = 592;   // four 128-thread blocks per SM: the row loop is latency-bound below that
 inline int64_t norm_bwd_scratch_floats(int D) { return static_cast<int64_t>(kNormBwdMaxBlocks) * 4 * 2 * D; }
 cudaError_t launch_norm_bwd(int mode, const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* gamma,
                             const float* mean, const float* rstd, const __nv_bfloat16* dres, __nv_bfloat16* dx,

@@ -10,7 +10,7 @@
 
 namespace b200 {
 
-constexpr int kMoeMaxLocalExperts = 256;
+constexpr int kMoeMaxLocalExperts = 512;
 constexpr int kMoeMaxExperts = 512;
 
 struct EpMoeArgs {

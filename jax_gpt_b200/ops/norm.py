@@ -45,7 +45,7 @@ _SCRATCH = {}
 
 def bwd_scratch(device, D: int) -> torch.Tensor:
     """Per-device scratch for the partial dgamma/dbeta sums of the backward kernel."""
-    n = 296 * 4 * 2 * D
+    n = int(_ext.ops().norm_bwd_scratch_floats(D))   # per-block partial rows; the library knows its grid cap
     key = (torch.device(device).index, n)
     t = _SCRATCH.get(key)
     if t is None:

@@ -283,11 +283,10 @@ class EPMoEInferenceRuntime:
             self._layers[tokens] = cls(self.comm, tokens, *self.shape, cap_factor=self.cap_factor)
         return self._layers[tokens]
 
-    def forward(self, x, weights, idx, params):
-        layer = self._layer(x.shape[0])
-        if self.fp8:
-            return layer.forward(x, weights, idx, params).to(x.dtype)
-        return layer.forward(x, weights, idx, params).to(x.dtype)
+    def forward(self, x, weights, idx, params, grads=None):
+        """``grads`` is accepted (and ignored) so that the object also fits the callable form
+        ``group(x, weights, idx, params, grads)`` of models/qwen35/moe.py:moe_layer."""
+        return self._layer(x.shape[0]).forward(x.contiguous(), weights, idx, params).to(x.dtype)
 
     __call__ = forward
 

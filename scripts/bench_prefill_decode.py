@@ -58,18 +58,35 @@ def make_runner(args, device):
         cfg = qwen_config(args.config)
         if args.n_layers:
             cfg = cfg.replace(n_layers=args.n_layers)
-        params = tree_map(lambda t: t.to(device), init_params(cfg, 0, dtype=dtype, fp8=args.fp8))
+        params = init_params(cfg, 0, dtype=dtype, fp8=args.fp8)
+        ep = None
+        if device.type == "cuda" and not args.fp8 and cfg.d_model % 256 == 0 and cfg.moe_intermediate_size % 128 == 0:
+            # routed experts through the fused dispatch / grouped-GEMM / combine kernel, expert-parallel over the
+            # ranks (with one rank: one kernel per MoE layer instead of a launch per expert)
+            import os
+            import torch.distributed as dist
+            from jax_gpt_b200.comm.symm import Communicator
+            from jax_gpt_b200.parallel.expert_parallel import EPMoEInferenceRuntime, shard_experts
+            if not dist.is_initialized():
+                os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+                os.environ.setdefault("MASTER_PORT", "29534")
+                dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+            if dist.get_world_size() > 1:
+                params = shard_experts(params, dist.get_rank(), dist.get_world_size())
+            ep = EPMoEInferenceRuntime(Communicator(device=device, wait_seconds=30.0), cfg.d_model,
+                                       cfg.moe_intermediate_size, cfg.n_routed_experts, cfg.n_experts_per_token)
+        params = tree_map(lambda t: t.to(device), params)
         plen, dlen = SCENARIOS[args.scenario]
 
         def prefill(B):
             tok = torch.randint(0, cfg.vocab_size, (B, plen), device=device)
             cache = init_cache(cfg, B, plen + dlen, dtype=dtype, device=device)
-            logits, cache = forward(params, tok, cfg, cache=cache)
+            logits, cache = forward(params, tok, cfg, cache=cache, ep_group=ep)
             return logits[:, -1].argmax(-1), cache
 
         def decode(state):
             nxt, cache = state
-            logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True)
+            logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True, ep_group=ep)
             return logits[:, -1].argmax(-1), cache
         return prefill, decode, cfg
     from jax_gpt_b200.models.deepseek_v3 import DeepSeekV3Config, forward, init_params, make_cache
