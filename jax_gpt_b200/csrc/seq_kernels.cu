@@ -198,6 +198,88 @@ __global__ void rmsnorm_rope_kernel(const __nv_bfloat16* __restrict__ x, const _
     if (j < per) yp[j] = __float2bfloat16(v[j]);
 }
 
+// Backward of rmsnorm_rope_kernel: persistent blocks, one warp per (row, head) item; the weight gradient is
+// accumulated per lane over the block's items, reduced through shared memory and flushed once per block.
+__global__ void rmsnorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                        const __nv_bfloat16* __restrict__ norm_w, const float* __restrict__ freqs,
+                                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows, int T, int H,
+                                        int dh, int rope_dim, int pos0, float eps, int one_plus) {
+  __shared__ float red[8][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = dh / 32;
+  const int64_t items = static_cast<int64_t>(rows) * H;
+  float dw_acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int64_t gw = blockIdx.x * 8 + warp; gw < items; gw += static_cast<int64_t>(gridDim.x) * 8) {
+    const int64_t row = gw / H;
+    const __nv_bfloat16* xp = x + gw * dh + lane * per;
+    const __nv_bfloat16* gp = dy + gw * dh + lane * per;
+    float xv[8], dv[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      xv[j] = (j < per) ? __bfloat162float(xp[j]) : 0.f;
+      dv[j] = (j < per) ? __bfloat162float(gp[j]) : 0.f;
+      ss += xv[j] * xv[j];
+    }
+    if (rope_dim > 0) {   // transpose of the rotation
+      const int half = rope_dim / 2;
+      const int dl = half / per;
+      const int pos = pos0 + static_cast<int>(row % T);
+      const float* fr = freqs + static_cast<int64_t>(pos) * half * 2;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < per) {
+          const int i = lane * per + j;
+          const float lo = __shfl_sync(0xffffffffu, dv[j], (lane + 32 - dl) & 31);
+          const float hi = __shfl_sync(0xffffffffu, dv[j], (lane + dl) & 31);
+          if (i < half) {
+            dv[j] = dv[j] * fr[i * 2] + hi * fr[i * 2 + 1];
+          } else if (i < rope_dim) {
+            dv[j] = dv[j] * fr[(i - half) * 2] - lo * fr[(i - half) * 2 + 1];
+          }
+        }
+      }
+    }
+    if (norm_w != nullptr) {
+      const float r = rsqrtf(warp_sum_f(ss) / dh + eps);
+      float dot = 0.f;
+      float dxh[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < per) {
+          const float w = __bfloat162float(norm_w[lane * per + j]);
+          const float xh = xv[j] * r;
+          dw_acc[j] += dv[j] * xh;
+          dxh[j] = dv[j] * (one_plus ? 1.f + w : w);
+          dot += dxh[j] * xh;
+          xv[j] = xh;
+        } else {
+          dxh[j] = 0.f;
+        }
+      }
+      dot = warp_sum_f(dot) / dh;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dv[j] = r * (dxh[j] - xv[j] * dot);
+    }
+    __nv_bfloat16* op = dx + gw * dh + lane * per;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < per) op[j] = __float2bfloat16(dv[j]);
+  }
+  if (norm_w != nullptr && dw != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < per) red[warp][lane * per + j] = dw_acc[j];
+    __syncthreads();
+    for (int i = threadIdx.x; i < dh; i += blockDim.x) {
+      float t = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < 8; ++w8) t += red[w8][i];
+      atomicAdd(dw + i, t);
+    }
+  }
+}
+
 __device__ __forceinline__ float pow2_ceil(float s) {
   // smallest power of two >= s (s > 0)
   int e;
@@ -382,6 +464,20 @@ cudaError_t launch_rmsnorm_rope(const __nv_bfloat16* x, const __nv_bfloat16* nor
   if (warps <= 0) return cudaSuccess;
   rmsnorm_rope_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(x, norm_w, freqs, y, rows, T, H, dh, rope_dim,
                                                                        pos0, eps, one_plus);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm_rope_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, const __nv_bfloat16* norm_w,
+                                    const float* freqs, __nv_bfloat16* dx, float* dw, int rows, int T, int H, int dh,
+                                    int rope_dim, int pos0, float eps, int one_plus, cudaStream_t st) {
+  if (dh % 32 != 0 || dh > 256) return cudaErrorInvalidValue;
+  const int per = dh / 32;
+  if (rope_dim > 0 && (rope_dim % 2 != 0 || (rope_dim / 2) % per != 0 || rope_dim > dh)) return cudaErrorInvalidValue;
+  const int64_t warps = static_cast<int64_t>(rows) * H;
+  if (warps <= 0) return cudaSuccess;
+  const int64_t want = (warps + 7) / 8;
+  rmsnorm_rope_bwd_kernel<<<static_cast<int>(want < 1184 ? want : 1184), 256, 0, st>>>(
+      x, dy, norm_w, freqs, dx, dw, rows, T, H, dh, rope_dim, pos0, eps, one_plus);
   return cudaGetLastError();
 }
 

@@ -41,6 +41,11 @@ cudaError_t launch_gdn_decode_step(const __nv_bfloat16* mixed, const __nv_bfloat
                                    const __nv_bfloat16* norm_w, float* state, __nv_bfloat16* out, int B, int Hqk, int Hv,
                                    int dk, int dv, int Kc, float eps, cudaStream_t st);
 
+// Backward of launch_rmsnorm_rope: dx [rows, H, dh] bf16; dw [dh] fp32 is ACCUMULATED into (may be nullptr).
+cudaError_t launch_rmsnorm_rope_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, const __nv_bfloat16* norm_w,
+                                    const float* freqs, __nv_bfloat16* dx, float* dw, int rows, int T, int H, int dh,
+                                    int rope_dim, int pos0, float eps, int one_plus, cudaStream_t st);
+
 // Inter-chunk scan of the chunked gated delta rule (gdn_kernels.cu); head widths dk = dv = 128, chunks of 64.
 //   kq    [BH, N, 128, 128] bf16: rows 0-63 k_cum, rows 64-127 q * exp(G) of every chunk
 //   intra [BH, N, 64, 64]   bf16: causal-masked (q k^T * decay)

@@ -26,14 +26,40 @@ def rmsnorm_rope_ref(x, norm_w, freqs, rope_dim: int, pos0: int = 0, eps: float 
     return xf.to(x.dtype)
 
 
+class _RmsnormRopeFn(torch.autograd.Function):
+    """Forward and backward on the fused kernels (per-head RMSNorm with (1 + w) or w gain, partial half-split rotary)."""
+
+    @staticmethod
+    def forward(ctx, x, norm_w, freqs, rope_dim, pos0, eps, one_plus):
+        B, T, H, dh = x.shape
+        xc = x.contiguous().view(B * T, H, dh)
+        y = torch.empty_like(xc)
+        fr = freqs.contiguous() if freqs is not None else None
+        _ext.ops().rmsnorm_rope(xc, norm_w, fr, y, T, rope_dim, pos0, eps, one_plus)
+        ctx.save_for_backward(xc, norm_w, fr)
+        ctx.meta = (B, T, H, dh, rope_dim, pos0, eps, one_plus)
+        return y.view(B, T, H, dh)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, norm_w, fr = ctx.saved_tensors
+        B, T, H, dh, rope_dim, pos0, eps, one_plus = ctx.meta
+        dyc = dy.contiguous().view(B * T, H, dh)
+        dx = torch.empty_like(xc)
+        dw = torch.zeros(dh, device=xc.device, dtype=torch.float32) if norm_w is not None else None
+        _ext.ops().rmsnorm_rope_bwd(xc, dyc, norm_w, fr, dx, dw, T, rope_dim, pos0, eps, one_plus)
+        return dx.view(B, T, H, dh), (dw.to(norm_w.dtype) if dw is not None else None), None, None, None, None, None
+
+
 def rmsnorm_rope(x, norm_w, freqs, rope_dim: int, pos0: int = 0, eps: float = 1e-6, one_plus: bool = True):
     B, T, H, dh = x.shape
     per = dh // 32 if dh % 32 == 0 else 0
     ok = (x.is_cuda and x.dtype == torch.bfloat16 and per and dh <= 256 and
           (rope_dim == 0 or ((rope_dim // 2) % per == 0)))
-    if not ok or (torch.is_grad_enabled() and (x.requires_grad or (norm_w is not None and norm_w.requires_grad))):
-        # gradients come from the PyTorch restatement of the same math
+    if not ok or (norm_w is not None and norm_w.dtype != torch.bfloat16):
         return rmsnorm_rope_ref(x, norm_w, freqs, rope_dim, pos0, eps, one_plus)
+    if torch.is_grad_enabled() and (x.requires_grad or (norm_w is not None and norm_w.requires_grad)):
+        return _RmsnormRopeFn.apply(x, norm_w, freqs, rope_dim, pos0, eps, one_plus)
     xc = x.contiguous().view(B * T, H, dh)
     y = torch.empty_like(xc)
     _ext.ops().rmsnorm_rope(xc, norm_w, freqs.contiguous() if freqs is not None else None, y, T, rope_dim, pos0, eps, one_plus)

@@ -50,6 +50,17 @@ def test_rmsnorm_rope(cuda_device, dh, rope, norm):
     y = RP.rmsnorm_rope(x, w, fr, rope, pos0=5)
     ref = RP.rmsnorm_rope_ref(x, w, fr, rope, pos0=5)
     assert _rel(y, ref) < 1e-2
+    # backward kernel vs autograd of the fp32 restatement
+    xg = x.clone().requires_grad_(True)
+    wg = w.clone().requires_grad_(True) if norm else None
+    dy = torch.randn_like(x)
+    RP.rmsnorm_rope(xg, wg, fr, rope, pos0=5).backward(dy)
+    xr = x.float().requires_grad_(True)
+    wr = w.float().requires_grad_(True) if norm else None
+    RP.rmsnorm_rope_ref(xr, wr, fr, rope, pos0=5).backward(dy.float())
+    assert _rel(xg.grad, xr.grad) < 1.5e-2
+    if norm:
+        assert _rel(wg.grad, wr.grad) < 1.5e-2
 
 
 @pytest.mark.parametrize("pow2", [False, True])
