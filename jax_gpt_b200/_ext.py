@@ -13,11 +13,13 @@ import torch
 
 _LOCK = threading.Lock()
 _LOADED = False
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_C.so")
+DEBUG = os.environ.get("B200_DEBUG", "") not in ("", "0")   # range-checked build of the same kernels
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_C_debug.so" if DEBUG else "_C.so")
 
 STATUS_NAMES = {
     0: "ok", 1: "wait_full_timeout", 2: "wait_empty_timeout", 3: "wait_tmem_full_timeout",
     4: "wait_tmem_empty_timeout", 5: "wait_flag_timeout", 6: "bad_argument", 7: "wait_attn_timeout",
+    8: "bounds_violation",
 }
 
 
@@ -37,7 +39,7 @@ def load(build_if_missing: bool = True) -> None:
             if not build_if_missing:
                 raise RuntimeError(f"{LIB_PATH} is missing; run `python -m jax_gpt_b200.build`")
             from . import build as _build
-            _build.build()
+            _build.build(debug=DEBUG)
         torch.ops.load_library(LIB_PATH)
         _LOADED = True
 

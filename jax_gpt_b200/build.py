@@ -51,11 +51,16 @@ def _run(cmd: list[str]) -> None:
         raise RuntimeError("build step failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
 
 
-def build(verbose: bool = False, force: bool = False) -> str:
-    """Builds ``_C.so`` if needed and returns its path."""
+def build(verbose: bool = False, force: bool = False, debug: bool = False) -> str:
+    """Builds ``_C.so`` if needed and returns its path. ``debug`` builds ``_C_debug.so`` instead: the same
+    sources with ``-DB200_DEBUG`` (data-dependent indices are range-checked, violations land in the status
+    word and the access is skipped); load it with ``B200_DEBUG=1`` in the environment."""
     import torch
     from torch.utils import cpp_extension as ce
 
+    OBJ = os.path.join(HERE, "build", "debug") if debug else globals()["OBJ"]
+    LIB = os.path.join(HERE, "_C_debug.so") if debug else globals()["LIB"]
+    NVCC_FLAGS = globals()["NVCC_FLAGS"] + (["-DB200_DEBUG"] if debug else [])
     os.makedirs(OBJ, exist_ok=True)
     hdr_m = _newest_header_mtime()
     nvcc = os.path.join(_cuda_home(), "bin", "nvcc")
@@ -98,4 +103,4 @@ def build(verbose: bool = False, force: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(verbose=True, force="--force" in sys.argv))
+    print(build(verbose=True, force="--force" in sys.argv, debug="--debug" in sys.argv))

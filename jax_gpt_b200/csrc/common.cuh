@@ -23,6 +23,7 @@ enum StatusCode : int {
   kWaitFlagTimeout = 5,      // cross-rank flag wait ran out of time
   kBadArgument = 6,
   kWaitAttnTimeout = 7,
+  kBoundsViolation = 8,      // debug build: an index into a global buffer was out of range (access skipped)
 };
 
 __device__ __forceinline__ void report_status(int* status, int code, int a = 0, int b = 0, int c = 0) {
@@ -33,6 +34,19 @@ __device__ __forceinline__ void report_status(int* status, int code, int a = 0, 
     status[3] = c;
   }
 }
+
+// Debug build (-DB200_DEBUG, `python -m jax_gpt_b200.build --debug`): data-dependent indices into global
+// buffers (routing slots, page ids, source ranks) are checked before use; a violation records
+// (tag, index, limit) in the status word and the caller skips the access. Compiled out otherwise.
+#ifdef B200_DEBUG
+__device__ __forceinline__ bool bounds_ok(int64_t idx, int64_t limit, int* status, int tag) {
+  if (idx >= 0 && idx < limit) return true;
+  report_status(status, kBoundsViolation, tag, static_cast<int>(idx), static_cast<int>(limit));
+  return false;
+}
+#else
+__device__ __forceinline__ bool bounds_ok(int64_t, int64_t, int*, int) { return true; }
+#endif
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;

@@ -177,7 +177,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap t_pool, const __grid_const
         }
         const int t = t0 + it;
         const int page = t < a.max_pages ? bt[t] : -1;
-        if (page < 0) {  // a sequence longer than its page list: give up cleanly
+        if (page < 0 || !bounds_ok(page, a.n_pages, a.status, 221)) {  // a sequence longer than its page list: give up cleanly
           report_status(a.status, kBadArgument, 71, b, t);
           *abort_flag = 1;
           ok = false;
@@ -446,7 +446,9 @@ cudaError_t launch_mla_paged_decode(const __nv_bfloat16* q, const __nv_bfloat16*
   if ((e = encode_tma_2d(&t_q, q, 2, kMlaWidth, static_cast<uint64_t>(args.batch) * args.heads, kMlaWidth * 2ull, 64,
                          hpc)) != cudaSuccess)
     return e;
-  e = hpc == 16 ? launch_decode_t<16>(t_pool, t_q, args, stream) : launch_decode_t<32>(t_pool, t_q, args, stream);
+  MlaDecodeArgs a2 = args;
+  a2.n_pages = n_pages;
+  e = hpc == 16 ? launch_decode_t<16>(t_pool, t_q, a2, stream) : launch_decode_t<32>(t_pool, t_q, a2, stream);
   if (e != cudaSuccess) return e;
   mla_merge_kernel<<<args.batch * args.heads, kMlaLatent / 4, 0, stream>>>(args.part_out, args.part_lse, out, args.heads,
                                                                           2 * args.n_splits);

@@ -16,6 +16,7 @@ struct MlaDecodeArgs {
   int batch, heads;               // sequences in this step, query heads per sequence
   int max_pages;                  // columns of the block table
   int n_splits;                   // KV splits per sequence (grid.x)
+  int n_pages;                    // pages in the pool (filled in by the launcher)
   const int* block_table;         // [max_seqs, max_pages] page ids
   const int* seq_lens;            // [max_seqs] tokens to attend over (the new token included)
   const int* seq_ids;             // [batch] row of block_table / seq_lens for every batch slot

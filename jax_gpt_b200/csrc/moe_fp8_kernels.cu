@@ -159,6 +159,7 @@ ep_moe_forward_fp8_kernel(const __grid_constant__ Fp8Maps tm, const __grid_const
       const int e = a.idx[p];
       const int dst = e / EL, el = e - dst * EL;
       const int slot = tb->send_off[e] + a.pos[p];
+      if (!bounds_ok(e, ET, a.status, 211) || !bounds_ok(slot, a.cap_rows, a.status, 212)) continue;
       const int tok = p / a.top_k;
       const uint4* src = reinterpret_cast<const uint4*>(a.xq + static_cast<int64_t>(tok) * D);
       uint4* out = reinterpret_cast<uint4*>(a.peer_recv_q[dst] + static_cast<int64_t>(slot) * D);
@@ -386,7 +387,8 @@ ep_moe_forward_fp8_kernel(const __grid_constant__ Fp8Maps tm, const __grid_const
         if (row_ok) {
           wgt = a.peer_recv_w[a.rank][row];
           const int meta = a.peer_recv_meta[a.rank][row];
-          dst = a.peer_out[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN + half * 128;
+          if (bounds_ok(meta >> 24, W, a.status, 213) && bounds_ok(meta & 0xFFFFFF, a.tokens * a.top_k, a.status, 214))
+            dst = a.peer_out[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN + half * 128;
         }
         const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
 #pragma unroll

@@ -128,6 +128,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       const int e = a.idx[p];
       const int dst = e / EL, el = e - dst * EL;
       const int slot = tb->send_off[e] + a.pos[p];
+      if (!bounds_ok(e, ET, a.status, 201) || !bounds_ok(slot, a.cap_rows, a.status, 202)) continue;
       const int tok = p / a.top_k;
       const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<int64_t>(tok) * D);
       uint4* out = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
@@ -307,7 +308,8 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
         if (row_ok) {
           wgt = a.peer_recv_w[a.rank][row];
           const int meta = a.peer_recv_meta[a.rank][row];
-          dst = a.peer_out[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN;
+          if (bounds_ok(meta >> 24, W, a.status, 203) && bounds_ok(meta & 0xFFFFFF, a.tokens * a.top_k, a.status, 204))
+            dst = a.peer_out[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN;
         }
         float* stg = stage_buf + (warp - 2) * (32 * 33);
         const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
@@ -695,7 +697,8 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
         float* dst = nullptr;
         if (r < rows) {
           const int meta = a.peer_recv_meta[a.rank][base + r];
-          dst = a.peer_dx[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN;
+          if (bounds_ok(meta >> 24, W, a.status, 205) && bounds_ok(meta & 0xFFFFFF, a.tokens * a.top_k, a.status, 206))
+            dst = a.peer_dx[meta >> 24] + static_cast<int64_t>((meta & 0xFFFFFF) / a.top_k) * D + ti.n * BN;
         }
         const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
 #pragma unroll 1
@@ -775,6 +778,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       if (row - tb->base[el] < tb->rows[el]) {
         const int meta = a.peer_recv_meta[a.rank][row];
         const float wv = a.peer_recv_w[a.rank][row];
+        if (!bounds_ok(meta >> 24, W, a.status, 207) || !bounds_ok(meta & 0xFFFFFF, a.tokens * a.top_k, a.status, 208)) continue;
         a.peer_dw[meta >> 24][meta & 0xFFFFFF] = (wv != 0.f) ? __ldcg(a.dw_rows + row) / wv : 0.f;
       }
     }
