@@ -350,12 +350,18 @@ class GPT2TrainEngine:
 
     # -- parameter access (reference tree) -------------------------------------------------------
     def params(self) -> Dict[str, torch.Tensor]:
+        """fp32 master parameters as the reference tree. With a sharded optimizer this is a collective call
+        (the shards are gathered first): every rank must make it."""
+        if self.dist_optimizer is not None:
+            self.dist_optimizer.gather_master(self)
         return self.flat.tree(self.flat.master)
 
     def opt_state(self) -> Dict[str, Dict[str, torch.Tensor]]:
-        if self.m is None:  # sharded optimizer: moments are exposed as the flat local shards
-            d = self.dist_optimizer
-            return {"count": self.step_count, "mu": {"__shard__": d.m}, "nu": {"__shard__": d.v}}
+        """Adam moments as trees shaped like the parameters. Collective with a sharded optimizer; the result
+        does not depend on the number of ranks."""
+        if self.m is None:
+            m, v = self.dist_optimizer.gather_moments(self)
+            return {"count": self.step_count, "mu": self.flat.tree(m), "nu": self.flat.tree(v)}
         return {"count": self.step_count, "mu": self.flat.tree(self.m), "nu": self.flat.tree(self.v)}
 
     def load(self, params: Dict[str, torch.Tensor], opt_state=None, step: Optional[int] = None):
@@ -363,7 +369,17 @@ class GPT2TrainEngine:
             for n, t in params.items():
                 self.flat.view(self.flat.master, n).copy_(t)
             self.flat.compute.copy_(self.flat.master)
-            if opt_state is not None:
+            if self.dist_optimizer is not None:
+                # sharded optimizer: assemble full-length moments, then keep this rank's slices
+                m = v = None
+                if opt_state is not None:
+                    m, v = torch.zeros_like(self.flat.master), torch.zeros_like(self.flat.master)
+                    for n, t in opt_state["mu"].items():
+                        self.flat.view(m, n).copy_(t)
+                    for n, t in opt_state["nu"].items():
+                        self.flat.view(v, n).copy_(t)
+                self.dist_optimizer.scatter_state(self, m, v)
+            elif opt_state is not None:
                 for n, t in opt_state["mu"].items():
                     self.flat.view(self.m, n).copy_(t)
                 for n, t in opt_state["nu"].items():

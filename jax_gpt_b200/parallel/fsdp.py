@@ -75,8 +75,25 @@ class _ShardedBase:
         self.v = torch.zeros_like(self.master)
 
     def gather_master(self, engine):
-        """Refreshes the engine's full fp32 master copy from the shards (checkpointing path)."""
+        """Refreshes the engine's full fp32 master copy from the shards (checkpointing path). Collective."""
         dist.all_gather_into_tensor(engine.flat.master, self.master, group=self.group)
+
+    def gather_moments(self, engine):
+        """Full-length Adam moments (m, v) assembled from every rank's shard. Collective; the result is
+        independent of the number of ranks, so a checkpoint can be resumed at another sharding degree."""
+        m = torch.empty_like(engine.flat.master)
+        v = torch.empty_like(engine.flat.master)
+        dist.all_gather_into_tensor(m, self.m, group=self.group)
+        dist.all_gather_into_tensor(v, self.v, group=self.group)
+        return m, v
+
+    def scatter_state(self, engine, m_full=None, v_full=None):
+        """Re-slices this rank's shards from full-length buffers (after a checkpoint was loaded into the engine)."""
+        self.master.copy_(engine.flat.master[self.lo:self.hi])
+        if m_full is not None:
+            self.m.copy_(m_full[self.lo:self.hi])
+        if v_full is not None:
+            self.v.copy_(v_full[self.lo:self.hi])
 
 
 class FusedShardedAdamW(_ShardedBase):

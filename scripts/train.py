@@ -163,8 +163,15 @@ def main(argv=None):
         if tc.eval_interval > 0 and state.step % tc.eval_interval == 0:
             losses = [float(eval_step(model, val_data.get_batch(), engine=state.engine)) for _ in range(tc.eval_steps)]
             logger.log_val(state.step, sum(losses) / len(losses))
-        if ckpt.should_save(state.step) and rank == 0 and dist_opt is None:
-            ckpt.save(state.step, state, data_state=train_data.state())
+        if ckpt.should_save(state.step):
+            if dist_opt is not None:
+                # the sharded optimizer assembles master weights and moments collectively (every rank calls);
+                # the saved tree does not depend on the number of ranks
+                state.engine.params()
+                st = state.engine.opt_state()
+                state.opt_state.mu, state.opt_state.nu = st["mu"], st["nu"]
+            if rank == 0:
+                ckpt.save(state.step, state, data_state=train_data.state())
     ckpt.wait_until_finished()
     if rank == 0 and metrics:
         print(f"done: step {state.step} loss {float(metrics['loss']):.4f}")

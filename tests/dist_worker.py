@@ -49,6 +49,23 @@ def run_fsdp(rank, world, device, use_multimem):
         res[f"step{step}_fused_vs_nccl"] = rel(fused.flat.compute, nccl.flat.compute)
         res[f"step{step}_fused_vs_single"] = rel(fused.flat.compute, single.flat.compute)
         res[f"step{step}_gnorm_rel"] = abs(float(of["grad_norm_sq"]) - float(on["grad_norm_sq"])) / float(on["grad_norm_sq"])
+    # checkpoint state of the sharded optimizer: gathered trees match the single-GPU engine, and a fresh
+    # sharded engine loaded from them continues identically
+    p_tree = {k: v.clone() for k, v in fused.params().items()}
+    st = fused.opt_state()
+    st = {"count": st["count"], "mu": {k: v.clone() for k, v in st["mu"].items()}, "nu": {k: v.clone() for k, v in st["nu"].items()}}
+    ss = single.opt_state()
+    res["ckpt_mu_vs_single"] = max(rel(st["mu"][k], ss["mu"][k]) for k in list(ss["mu"])[:6])
+    res["ckpt_nu_vs_single"] = max(rel(st["nu"][k], ss["nu"][k]) for k in list(ss["nu"])[:6])
+    fused2 = GPT2TrainEngine(cfg, 2, 256, device=device,
+                             dist_optimizer=FusedShardedAdamW(device=device, use_multimem=use_multimem, wait_seconds=5.0), **kw)
+    fused2.load(p_tree, st, fused.step_count)
+    x, y = batch(rank, 7, cfg, device)
+    fused.train_step(x, y)
+    fused2.train_step(x, y)
+    torch.cuda.synchronize()
+    _ext.check_status(device)
+    res["ckpt_resume_fused_vs_nccl"] = rel(fused2.flat.compute, fused.flat.compute)
     # identical weights on every rank
     mine = fused.flat.compute.float().sum().reshape(1).clone()
     lst = [torch.zeros_like(mine) for _ in range(world)]

@@ -33,6 +33,8 @@ def test_fused_sharded_adamw_two_gpus(tmp_path):
             assert v < 5e-3, res
         if k.endswith("gnorm_rel"):
             assert v < 1e-2, res
+        if k.startswith("ckpt_"):
+            assert v < 5e-3, res
     assert res["rank_checksum_spread"] == 0.0, res
 
 
