@@ -245,6 +245,52 @@ def run_ep_fp8(rank, world, device):
     return res
 
 
+def run_tp_attention(rank, world, device):
+    """MLA and gated attention with heads split over the ranks and tokens sharded between layers (fused
+    all-gather -> GEMM in, GEMM -> reduce-scatter out) vs the single-GPU layers."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
+    from jax_gpt_b200.models.deepseek_v3.model import _attn_params, mla_prefill
+    from jax_gpt_b200.models.qwen35.gqa import gqa_attention
+    from jax_gpt_b200.models.qwen35.primitives import precompute_rope_freqs
+    from jax_gpt_b200.parallel.tensor_parallel import TPContext
+    from jax_gpt_b200.parallel.tp_attention import gqa_attention_tp, mla_prefill_tp, shard_gqa_params, shard_mla_params
+    ctx = TPContext(device=device, wait_seconds=5.0)
+    g = torch.Generator().manual_seed(5)
+    bf = torch.bfloat16
+    res = {}
+    # ---- MLA ----
+    c = DeepSeekV3Config.tiny().replace(d_model=512, n_heads=8, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                                        q_lora_rank=256, kv_lora_rank=512, max_position_embeddings=512)
+    n = lambda *s: (torch.randn(*s, generator=g) * 0.05).to(device=device, dtype=bf)
+    ones = lambda *s: torch.ones(*s, device=device, dtype=bf)
+    ap = _attn_params(c, (), n, ones)
+    B, T = 2, 256
+    x = torch.randn(B, T, c.d_model, generator=g).to(device=device, dtype=bf)
+    rope = precompute_rope_freqs(c.qk_rope_head_dim, 512, c.rope_theta, device=device)
+    with torch.no_grad():
+        ref, _ = mla_prefill(x, ap, c, rope)
+        rows = B * T // world
+        xl = x.reshape(B * T, -1)[rank * rows:(rank + 1) * rows].contiguous()
+        out = mla_prefill_tp(ctx, xl, shard_mla_params(ap, c, rank, world), c, rope, B, T)
+    res["mla_tp"] = rel(out, ref.reshape(B * T, -1)[rank * rows:(rank + 1) * rows])
+    # ---- gated attention ----
+    D, Hq, Hkv, dh = 512, 8, 2, 128
+    gp = {"q_proj": n(D, 2 * Hq * dh), "k_proj": n(D, Hkv * dh), "v_proj": n(D, Hkv * dh), "o_proj": n(Hq * dh, D),
+          "q_norm": torch.zeros(dh, device=device, dtype=bf), "k_norm": torch.zeros(dh, device=device, dtype=bf)}
+    x2 = torch.randn(B, T, D, generator=g).to(device=device, dtype=bf)
+    fr = precompute_rope_freqs(32, 512, 1e7, device=device)
+    with torch.no_grad():
+        ref2, _, _ = gqa_attention(x2, gp, Hq, Hkv, dh, fr, 32)
+        xl2 = x2.reshape(B * T, -1)[rank * rows:(rank + 1) * rows].contiguous()
+        out2 = gqa_attention_tp(ctx, xl2, shard_gqa_params(gp, Hq, Hkv, dh, rank, world), Hkv, dh, fr, 32, B, T)
+    res["gqa_tp"] = rel(out2, ref2.reshape(B * T, -1)[rank * rows:(rank + 1) * rows])
+    torch.cuda.synchronize()
+    _ext.check_status(device)
+    dist.barrier()
+    return res
+
+
 def run_vocab_ce(rank, world, device):
     """Vocabulary-parallel cross-entropy (one kernel, statistics exchanged over peer memory) vs the full softmax."""
     from jax_gpt_b200 import _ext
@@ -343,6 +389,8 @@ def main():
         res = run_ep(rank, world, device)
     elif what == "ep_bwd":
         res = run_ep_bwd(rank, world, device)
+    elif what == "tp_attention":
+        res = run_tp_attention(rank, world, device)
     elif what == "vocab_ce":
         res = run_vocab_ce(rank, world, device)
     elif what == "ep_fp8":

@@ -61,6 +61,11 @@ def test_fused_ep_moe_backward_two_gpus(tmp_path):
         assert v < 3e-2, res
 
 
+def test_tensor_parallel_attention_layers_two_gpus(tmp_path):
+    res = _run("tp_attention", tmp_path, port=29619)
+    assert res["mla_tp"] < 2e-2 and res["gqa_tp"] < 2e-2, res
+
+
 def test_vocab_parallel_cross_entropy_two_gpus(tmp_path):
     res = _run("vocab_ce", tmp_path, port=29618)
     for k, v in res.items():
