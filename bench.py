@@ -97,6 +97,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=16)
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--overlap", action="store_true", help="several GPUs: reduce-scatter each layer's gradients during backward")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -121,7 +122,8 @@ def main():
 
     cfg = GPTConfig.from_model_type(args.model)
     B, T = args.micro_batch, args.seq_len
-    tc = TrainConfig(micro_batch_size=B, seq_len=T, dp=world, cuda_graph=not args.no_graph)
+    tc = TrainConfig(micro_batch_size=B, seq_len=T, dp=world, cuda_graph=not args.no_graph,
+                     overlap_grad_reduce=args.overlap)
     model = GPT(cfg, seed=0)
     dist_opt = None
     if world > 1:
@@ -197,7 +199,9 @@ def main():
                        "global_batch": B * world, "seq_len": T, "parallelism": f"dp{world}" if world > 1 else "1gpu",
                        "optimizer": "AdamW + global-norm clip, fp32 master weights, inside the timed step",
                        "l2": "per-step working set (~7 GB of activations and logits) exceeds the 126 MB L2; no flush",
-                       "cuda_graph": not args.no_graph},
+                       "cuda_graph": not args.no_graph,
+                       "grad_reduce": ("per-layer reduce-scatter kernels on a side stream during backward" if world > 1 and args.overlap
+                                       else ("inside the fused optimizer kernel after backward" if world > 1 else "none (1 GPU)"))},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": 2 * B * T * 4, "d2h_bytes_per_step": 4,

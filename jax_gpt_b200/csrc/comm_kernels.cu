@@ -76,7 +76,9 @@ __global__ void __launch_bounds__(512, 2) sharded_adamw_kernel(const __grid_cons
     float* mine = a.peer_grad[a.rank] + base;
     for (int64_t i = tid * 4; i < S; i += nthreads * 4) {
       float4 acc;
-      if (a.mc_grad != nullptr) {
+      if (a.pre_reduced) {
+        acc = *reinterpret_cast<const float4*>(mine + i);
+      } else if (a.mc_grad != nullptr) {
         acc = multimem_ld_reduce_f32x4(a.mc_grad + base + i);
       } else {
         acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(512, 2) sharded_adamw_kernel(const __grid_cons
           }
         }
       }
-      *reinterpret_cast<float4*>(mine + i) = acc;
+      if (!a.pre_reduced) *reinterpret_cast<float4*>(mine + i) = acc;
       sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
     }
   }
@@ -275,6 +277,44 @@ __global__ void __launch_bounds__(256, 1) vocab_parallel_ce_kernel(const __grid_
   }
 }
 
+__global__ void __launch_bounds__(256) rs_bucket_kernel(const __grid_constant__ RsBucketArgs a) {
+  __shared__ int ok_s;
+  const int epoch = *a.epoch;
+  const int W = a.world;
+  if (threadIdx.x == 0) ok_s = 1;
+  if (blockIdx.x == 0 && threadIdx.x < W) {
+    __threadfence_system();
+    st_release_sys(a.peer_flags[threadIdx.x] + a.bucket * kCommMaxRanks + a.rank, epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x < W) {
+    if (!wait_flag_ge(a.peer_flags[a.rank] + a.bucket * kCommMaxRanks + threadIdx.x, epoch, a.wait_budget_ns)) {
+      report_status(a.status, kWaitFlagTimeout, 110, a.bucket, threadIdx.x);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const int64_t tid = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) * 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * 4;
+  float* mine = a.peer_grad[a.rank];
+  for (int r = 0; r < a.n_ranges; ++r) {
+    const int64_t start = a.ranges[2 * r], len = a.ranges[2 * r + 1];
+    for (int64_t i = tid; i < len; i += stride) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < kCommMaxRanks; ++p) {
+        if (p < W) {
+          const int src = (a.rank + p) % W;
+          const float4 g = __ldcg(reinterpret_cast<const float4*>(a.peer_grad[src] + start + i));
+          acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+        }
+      }
+      *reinterpret_cast<float4*>(mine + start + i) = acc;
+    }
+  }
+}
+
 __global__ void comm_barrier_kernel(CommCtrl* const* peer_ctrl_dev, int world, int rank, uint64_t budget_ns,
                                     int* status) {
   __shared__ CommCtrl* peers[kCommMaxRanks];
@@ -308,6 +348,12 @@ cudaError_t launch_sharded_adamw(const ShardedAdamWArgs& args, cudaStream_t stre
   void* params[] = {&a};
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(sharded_adamw_kernel), dim3(grid), dim3(512), params, 0,
                                      stream);
+}
+
+cudaError_t launch_rs_bucket(const RsBucketArgs& args, int blocks, cudaStream_t stream) {
+  if (args.world < 1 || args.world > kCommMaxRanks || args.n_ranges < 0 || blocks < 1) return cudaErrorInvalidValue;
+  rs_bucket_kernel<<<blocks, 256, 0, stream>>>(args);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_vocab_parallel_ce(const VocabCeArgs& args, cudaStream_t stream) {

@@ -40,7 +40,25 @@ struct ShardedAdamWArgs {
   int* status;
   const float* extra_sq;     // optional: this rank's sum of squared gradients of parameters that are NOT in
                              // the flat vector (expert-parallel weights); joins the global clipping norm
+  int pre_reduced;           // 1: this rank's shard of its gradient buffer already holds the sum over ranks
+                             // (bucket kernels below ran during backward): skip the peer loads
 };
+
+// Reduce-scatter of ONE gradient bucket, launched on a side stream while backward still runs: publishes
+// "my gradients of this bucket are final" to every peer, waits (bounded) for the peers' flags, then sums the
+// peers' values of the listed ranges (this rank's shard of the bucket) into this rank's own buffer.
+struct RsBucketArgs {
+  int world, rank;
+  float* peer_grad[kCommMaxRanks];   // every rank's full fp32 gradient buffer
+  int* peer_flags[kCommMaxRanks];    // every rank's flag table [n_buckets][kCommMaxRanks]
+  const int64_t* ranges;             // [n_ranges][2] (start, length) in elements, multiples of 4, inside this rank's shard
+  int n_ranges;
+  int bucket;
+  const int* epoch;                  // device scalar: the training step; flags carry it
+  uint64_t wait_budget_ns;
+  int* status;
+};
+cudaError_t launch_rs_bucket(const RsBucketArgs& args, int blocks, cudaStream_t stream);
 
 // Gradient reduce-scatter + global-norm clip + AdamW on the local shard + all-gather of the
 // updated bf16 parameters, one cooperative launch. Leaves every rank's gradient buffer

@@ -88,7 +88,8 @@ class GPT2TrainEngine:
     def __init__(self, cfg: GPTConfig, batch: int, seq: int, *, device=None, seed: int = 0, lr: float = 6e-4,
                  min_lr: float = 6e-5, warmup_steps: int = 2000, lr_decay_steps: int = 600000,
                  weight_decay: float = 0.1, beta1: float = 0.9, beta2: float = 0.95, grad_clip: float = 1.0,
-                 init: Optional[Dict[str, torch.Tensor]] = None, use_cuda_graph: bool = True, dist_optimizer=None):
+                 init: Optional[Dict[str, torch.Tensor]] = None, use_cuda_graph: bool = True, dist_optimizer=None,
+                 overlap_grad_reduce: bool = False):
         assert cfg.n_head == cfg.n_kv_head and cfg.d_head in (64, 128)
         assert cfg.d_model % 8 == 0 and seq <= cfg.d_context
         self.cfg, self.B, self.T = cfg, batch, seq
@@ -98,11 +99,31 @@ class GPT2TrainEngine:
                           b1=beta1, b2=beta2, clip=grad_clip)
         self.dist_optimizer = dist_optimizer
         self.dp_world = 1
+        self._overlap = False
+        self._overlap_now = False
+        self._pre_reduced = False
         if dist_optimizer is not None:
             self.flat = FlatParams(cfg, self.device, seed, init, getattr(dist_optimizer, "alloc_grad", None),
                                    getattr(dist_optimizer, "alloc_compute", None))
             dist_optimizer.attach(self)
             self.dp_world = dist_optimizer.world
+            self._overlap = bool(overlap_grad_reduce) and hasattr(dist_optimizer, "setup_buckets") and self.dp_world > 1
+            if self._overlap:
+                # one bucket per transformer layer (its slice of every stacked parameter), completed in reverse
+                # layer order by backward, then one bucket with everything else (embeddings, final norm)
+                L = cfg.n_layers
+                layer_b = [[] for _ in range(L)]
+                rest = []
+                for n in self.flat.names:
+                    o, numel, shape = self.flat.offsets[n]
+                    if n.startswith("h."):
+                        per = numel // L
+                        for l in range(L):
+                            layer_b[l].append((o + l * per, per))
+                    else:
+                        rest.append((o, numel))
+                dist_optimizer.setup_buckets(layer_b + [rest])
+                self._rs_stream = torch.cuda.Stream(device=self.device)
             self.m = self.v = None  # moments live in the optimizer's shards
         else:
             self.flat = FlatParams(cfg, self.device, seed, init)
@@ -244,14 +265,30 @@ class GPT2TrainEngine:
                           self.ln1_rstd[l], g["h.ln_1.layer_norm.scale"][l], g["h.ln_1.layer_norm.bias"][l], dres=dx,
                           dx=dx_other)
             dx, dx_other = dx_other, dx
+            if self._overlap_now:
+                self._reduce_bucket_async(l)
         misc.embed_bwd(self.tokens, dx.view(self.B, self.T, d), g["wte.embedding"], g["wpe.embedding"], 0)
+        if self._overlap_now:
+            self.dist_optimizer.reduce_bucket(L)          # embeddings / final norm: nothing left to overlap with
+            torch.cuda.current_stream().wait_stream(self._rs_stream)
+
+    def _reduce_bucket_async(self, b: int):
+        """Reduce-scatter of layer ``b``'s gradients on the side stream, behind the kernels that produced them."""
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self._rs_stream):
+            self._rs_stream.wait_event(ev)
+            self.dist_optimizer.reduce_bucket(b)
 
     def optimizer_step(self):
         """clip -> Adam -> decoupled decay (kernels only) -> lr; also refreshes bf16 weights, zeroes grads."""
         h = self.hyper
         fl = self.flat
         if self.dist_optimizer is not None:
-            self.dist_optimizer.step(self)
+            if self._pre_reduced:
+                self.dist_optimizer.step(self, pre_reduced=True)
+            else:
+                self.dist_optimizer.step(self)
             return
         self.gnorm_sq.zero_()
         misc.sumsq(fl.grad, self.gnorm_sq)
@@ -277,6 +314,16 @@ class GPT2TrainEngine:
         self.forward(True, True)
         self.backward()
         self.loss_sum.add_(self.loss)
+
+    def _fwd_bwd_reduce(self):
+        """Forward + backward of the step's ONLY micro-batch with the gradient reduce-scatter of every layer
+        launched on a side stream as soon as that layer's backward is enqueued."""
+        self.dist_optimizer.epoch_t.add_(1)
+        self._overlap_now = True
+        try:
+            self._fwd_bwd()
+        finally:
+            self._overlap_now = False
 
     def _run(self, name: str, fn):
         """Runs ``fn`` eagerly, or through a CUDA graph captured on first use."""
@@ -305,6 +352,10 @@ class GPT2TrainEngine:
                 self.optimizer_step()
                 self.flat.master.copy_(saved[0]); self.m.copy_(saved[1]); self.v.copy_(saved[2])
                 self.flat.compute.copy_(self.flat.master)
+            if self._overlap:
+                # first launch of the bucket kernel outside any capture (epoch 0: no flag to wait for)
+                for b in range(self.cfg.n_layers + 1):
+                    self.dist_optimizer.reduce_bucket(b)
             self.flat.grad.zero_()
             self.loss_sum.zero_()
         torch.cuda.current_stream().wait_stream(self._side)
@@ -324,7 +375,8 @@ class GPT2TrainEngine:
     def apply_gradients(self):
         """Optimizer step over the accumulated gradients (mean over the micro-batches seen)."""
         lr = self._set_hyper(max(1, self._micro))
-        self._run("opt", self.optimizer_step)
+        self._run("opt_pre" if self._pre_reduced else "opt", self.optimizer_step)
+        self._pre_reduced = False
         self.step_count += 1
         n = max(1, self._micro)
         self._micro = 0
@@ -338,6 +390,17 @@ class GPT2TrainEngine:
         """One optimizer step on one micro-batch. ``tokens``/``targets`` [B,T] int32 (device or
         pinned host); when omitted the static input buffers are re-used. Returns device scalars
         ``loss`` and ``grad_norm_sq`` (no host sync) plus the learning rate used."""
+        if self._overlap and self._micro == 0:
+            # a step of one micro-batch: its gradients are final layer by layer, so their reduce-scatter
+            # overlaps the rest of backward
+            if tokens is not None:
+                self.tokens.copy_(tokens, non_blocking=True)
+                self.targets.copy_(targets.reshape(-1), non_blocking=True)
+            self._warm_up()
+            self._run("fwd_bwd_reduce", self._fwd_bwd_reduce)
+            self._micro += 1
+            self._pre_reduced = True
+            return self.apply_gradients()
         self.micro_step(tokens, targets)
         return self.apply_gradients()
 

@@ -118,16 +118,42 @@ class FusedShardedAdamW(_ShardedBase):
         self._make_shards(engine)
         self.n_total, self.n_decay = engine.flat.total, engine.flat.n_decay
 
-    def step(self, engine, extra_sq=None):
+    # ---- gradient reduce-scatter overlapped with backward ------------------------------------------
+    def setup_buckets(self, buckets, blocks: int = 16):
+        """``buckets``: list (in the order backward completes them) of lists of (offset, length) element ranges
+        of the flat gradient vector. Each bucket's part inside this rank's shard is reduced by one small
+        kernel on a side stream as soon as backward has produced it (``reduce_bucket``)."""
+        dev = self.comm.device
+        self._bucket_ranges = []
+        for ranges in buckets:
+            mine = []
+            for off, n in ranges:
+                a, b = max(off, self.lo), min(off + n, self.hi)
+                if b > a:
+                    assert a % 4 == 0 and (b - a) % 4 == 0
+                    mine.append((a, b - a))
+            self._bucket_ranges.append(torch.tensor(mine, dtype=torch.int64, device=dev).reshape(-1, 2))
+        self._bucket_flags = self.comm.alloc(len(buckets) * 8, torch.int32)
+        self.epoch_t = torch.zeros(1, device=dev, dtype=torch.int32)
+        self._bucket_blocks = blocks
+        dist.barrier(self.group)
+
+    def reduce_bucket(self, b: int):
+        """Launch on the CURRENT stream (the caller puts it on a side stream behind the producing kernels)."""
+        _ext.ops().rs_bucket(self.world, self.rank, self.grad_buf.peer_ptrs, self._bucket_flags.peer_ptrs,
+                             self._bucket_ranges[b], b, self.epoch_t, self._bucket_blocks, self.comm.wait_seconds)
+
+    def step(self, engine, extra_sq=None, pre_reduced: bool = False):
         """``extra_sq``: device scalar with this rank's sum of squared gradients of parameters kept
-        outside the flat vector (expert-parallel weights); it joins the global clipping norm."""
+        outside the flat vector (expert-parallel weights); it joins the global clipping norm.
+        ``pre_reduced``: every bucket was already reduce-scattered during backward."""
         h = engine.hyper
         mc_g = self.grad_buf.multicast_ptr if self.use_multimem else 0
         mc_p = self.param_buf.multicast_ptr if self.use_multimem else 0
         _ext.ops().sharded_adamw(self.world, self.rank, self.n_total, self.n_decay, self.grad_buf.peer_ptrs,
                                  self.param_buf.peer_ptrs, self.comm.ctrl.peer_ptrs, mc_g, mc_p, self.master, self.m,
                                  self.v, engine.hp, h["b1"], h["b2"], 1e-8, h["wd"], h["clip"], self.comm.wait_seconds,
-                                 extra_sq)
+                                 extra_sq, pre_reduced)
         engine.flat.grad.zero_()
 
     def grad_norm_sq(self) -> torch.Tensor:

@@ -54,6 +54,7 @@ class TrainConfig:
     hardware: str = "b200"
     # runtime
     cuda_graph: bool = True
+    overlap_grad_reduce: bool = False  # several GPUs: reduce-scatter each layer's gradients during backward
     seed: int = 0
 
     def replace(self, **kw) -> "TrainConfig":

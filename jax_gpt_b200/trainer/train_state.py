@@ -32,7 +32,8 @@ def create_train_state(model, tx, *, train_config=None, device=None, dist_optimi
                               min_lr=c.min_lr, warmup_steps=c.warmup_steps, lr_decay_steps=c.lr_decay_steps,
                               weight_decay=c.weight_decay, beta1=c.beta1, beta2=c.beta2, grad_clip=c.grad_clip,
                               init={k: v.detach().cpu() for k, v in model.params.items()},
-                              use_cuda_graph=c.cuda_graph, dist_optimizer=dist_optimizer)
+                              use_cuda_graph=c.cuda_graph, dist_optimizer=dist_optimizer,
+                              overlap_grad_reduce=getattr(c, "overlap_grad_reduce", False))
         model.params = eng.params()
         from .optimizer import AdamWState
         st = eng.opt_state()

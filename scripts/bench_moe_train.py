@@ -56,6 +56,17 @@ def main(argv=None):
         cfg = cfg.replace(vocab_size=args.vocab)
     params = init_params(cfg, 0, torch.bfloat16)
     ep = dist_opt = local = None
+    if world == 1 and device.type == "cuda" and cfg.n_routed_experts <= 512:
+        # one GPU: the same fused expert kernels with all experts local (one launch per MoE layer and direction)
+        import os
+        from jax_gpt_b200.comm.symm import Communicator
+        from jax_gpt_b200.parallel.expert_parallel import EPMoERuntime, FusedEPMoE, is_expert_leaf
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29535")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+        layer = FusedEPMoE(Communicator(device=device), args.batch * args.seq, cfg.d_model, cfg.moe_intermediate_size,
+                           cfg.n_routed_experts, cfg.n_experts_per_token, training=True)
+        ep, local = EPMoERuntime(layer), is_expert_leaf
     if world > 1:
         from jax_gpt_b200.parallel.expert_parallel import EPMoERuntime, FusedEPMoE, is_expert_leaf, shard_experts
         from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW

@@ -34,12 +34,21 @@ def run_fsdp(rank, world, device, use_multimem):
     fused = GPT2TrainEngine(cfg, 2, 256, device=device,
                             dist_optimizer=FusedShardedAdamW(device=device, use_multimem=use_multimem, wait_seconds=5.0), **kw)
     nccl = GPT2TrainEngine(cfg, 2, 256, device=device, dist_optimizer=NcclShardedAdamW(device=device), **kw)
+    # the same fused optimizer with every layer's gradient reduce-scatter launched during backward; once eager,
+    # once through CUDA graphs (side-stream fork / join inside the capture)
+    overlap = GPT2TrainEngine(cfg, 2, 256, device=device, overlap_grad_reduce=True,
+                              dist_optimizer=FusedShardedAdamW(device=device, wait_seconds=5.0), **kw)
+    kwg = dict(kw, use_cuda_graph=True)
+    overlap_g = GPT2TrainEngine(cfg, 2, 256, device=device, overlap_grad_reduce=True,
+                                dist_optimizer=FusedShardedAdamW(device=device, wait_seconds=5.0), **kwg)
     single = GPT2TrainEngine(cfg, 2, 256, device=device, **kw)
     res = {}
     for step in range(3):
         x, y = batch(rank, step, cfg, device)
         of = fused.train_step(x, y)
         on = nccl.train_step(x, y)
+        overlap.train_step(x, y)
+        overlap_g.train_step(x, y)
         for r in range(world):  # the single-GPU engine sees every rank's batch as a micro-batch
             xs, ys = batch(r, step, cfg, device)
             single.micro_step(xs, ys)
@@ -48,6 +57,8 @@ def run_fsdp(rank, world, device, use_multimem):
         _ext.check_status(device)
         res[f"step{step}_fused_vs_nccl"] = rel(fused.flat.compute, nccl.flat.compute)
         res[f"step{step}_fused_vs_single"] = rel(fused.flat.compute, single.flat.compute)
+        res[f"step{step}_overlap_fused_vs_nccl"] = rel(overlap.flat.compute, fused.flat.compute)
+        res[f"step{step}_overlapgraph_fused_vs_nccl"] = rel(overlap_g.flat.compute, fused.flat.compute)
         res[f"step{step}_gnorm_rel"] = abs(float(of["grad_norm_sq"]) - float(on["grad_norm_sq"])) / float(on["grad_norm_sq"])
     # checkpoint state of the sharded optimizer: gathered trees match the single-GPU engine, and a fresh
     # sharded engine loaded from them continues identically
