@@ -50,6 +50,8 @@ struct ScanArgs {
   const float* s0;             // [BH, dk, dv] or nullptr
   __nv_bfloat16* o;            // [BH, N, 64, dv]
   float* s_out;                // [BH, dk, dv]
+  __nv_bfloat16* s_save;       // optional [BH, N, dk, dv]: the state every chunk STARTS from (for the backward scan)
+  __nv_bfloat16* vn_save;      // optional [BH, N, 64, dv]: v_new of every chunk
   int* status;
 };
 
@@ -187,11 +189,16 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap t_kq, const __grid_constant_
     for (int n = 0; n <= N; ++n) {
       // ---- publish S (bf16) for the next chunk's first product ----
       if (n < N) {
+        uint4* ssave = a.s_save != nullptr
+                           ? reinterpret_cast<uint4*>(a.s_save + ((static_cast<int64_t>(bh) * N + n) * kDk + r) * kDv)
+                           : nullptr;
 #pragma unroll
-        for (int c = 0; c < kDv; c += 8)
-          *reinterpret_cast<uint4*>(sb + swz(r, c, 16384)) =
-              make_uint4(pack_bf16x2(S[c], S[c + 1]), pack_bf16x2(S[c + 2], S[c + 3]), pack_bf16x2(S[c + 4], S[c + 5]),
-                         pack_bf16x2(S[c + 6], S[c + 7]));
+        for (int c = 0; c < kDv; c += 8) {
+          const uint4 pk = make_uint4(pack_bf16x2(S[c], S[c + 1]), pack_bf16x2(S[c + 2], S[c + 3]),
+                                      pack_bf16x2(S[c + 4], S[c + 5]), pack_bf16x2(S[c + 6], S[c + 7]));
+          *reinterpret_cast<uint4*>(sb + swz(r, c, 16384)) = pk;
+          if (ssave != nullptr) ssave[c >> 3] = pk;
+        }
         fence_proxy_async_smem();
         mbar_arrive(&bars->s_ready);
       } else {
@@ -222,11 +229,14 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap t_kq, const __grid_constant_
           for (int j = 0; j < 32; j += 8) {
             const uint4 u = ve[c * 4 + (j >> 3)];
             const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-            *reinterpret_cast<uint4*>(vn + swz(r, c * 32 + j, 8192)) = make_uint4(
+            const uint4 pk = make_uint4(
                 pack_bf16x2(f0.x - __uint_as_float(v[j]), f0.y - __uint_as_float(v[j + 1])),
                 pack_bf16x2(f1.x - __uint_as_float(v[j + 2]), f1.y - __uint_as_float(v[j + 3])),
                 pack_bf16x2(f2.x - __uint_as_float(v[j + 4]), f2.y - __uint_as_float(v[j + 5])),
                 pack_bf16x2(f3.x - __uint_as_float(v[j + 6]), f3.y - __uint_as_float(v[j + 7])));
+            *reinterpret_cast<uint4*>(vn + swz(r, c * 32 + j, 8192)) = pk;
+            if (a.vn_save != nullptr)
+              reinterpret_cast<uint4*>(a.vn_save + (chunk * kC + r) * kDv)[c * 4 + (j >> 3)] = pk;
           }
         }
         tc_fence_before();
@@ -331,7 +341,8 @@ __global__ void gdn_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, const 
 
 cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
                             const __nv_bfloat16* veff, const float* e, const float* s0, __nv_bfloat16* o, float* s_out,
-                            int bh, int n_chunks, int* status, cudaStream_t stream) {
+                            __nv_bfloat16* s_save, __nv_bfloat16* vn_save, int bh, int n_chunks, int* status,
+                            cudaStream_t stream) {
   if (bh < 1 || n_chunks < 1) return cudaErrorInvalidValue;
   CUtensorMap t_kq, t_intra, t_kdec;
   cudaError_t err;
@@ -344,7 +355,7 @@ cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra,
     if ((err = cudaFuncSetAttribute(gdn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem)) != cudaSuccess) return err;
     configured = true;
   }
-  ScanArgs args{n_chunks, veff, e, s0, o, s_out, status};
+  ScanArgs args{n_chunks, veff, e, s0, o, s_out, s_save, vn_save, status};
   gdn_scan_kernel<<<bh, kThreads, kSmem, stream>>>(t_kq, t_intra, t_kdec, args);
   return cudaGetLastError();
 }
@@ -355,6 +366,347 @@ cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w,
   const int threads = 128;
   const dim3 grid((C / 8 + threads - 1) / threads, T, B);
   gdn_conv_silu_kernel<4><<<grid, threads, 0, stream>>>(x, w, y, state, T, C);
+  return cudaGetLastError();
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Backward of the inter-chunk scan: one CTA per (batch, head) walks the chunks in REVERSE with the state
+// gradient dS (128 x 128 fp32) in the registers of 128 threads and a bf16 copy in shared memory. With
+// S = the state the chunk started from, Vn = its v_new (both saved by the forward kernel) and
+// W = -dVn:
+//   phase 1   T1 = [kdec ; 0] dS + [intra^T ; 0] dO            -> dVn (rows 0..63) = d v_eff
+//   phase 2   T2 = [dO ; W] S^T      rows 0..63 d(q exp G), rows 64..127 d k_cum
+//             T3 = [dO ; W] Vn^T     rows 0..63 d intra
+//             T4 = [Vn ; 0] dS^T     rows 0..63 d kdec
+//             T5 = (q exp G)^T dO + k_cum^T W                  -> dS <- e dS + T5,  d e = <dS, S>
+// 64-row operands are stacked in pairs (or padded with a zero half) to fill M = 128.
+namespace {
+
+constexpr int kBwdThreads = 192;
+constexpr int kTileKq = 0;                         // [k_cum ; qg]   128 x dk, 32 KB
+constexpr int kTileKd = kTileKq + 32768;           // [kdec ; 0]     128 x dk, 32 KB
+constexpr int kTileIn = kTileKd + 32768;           // intra | zeros  64 x 128, 16 KB (two 64-column blocks of 8 KB)
+constexpr int kTileDw = kTileIn + 16384;           // [dO ; W]       128 x dv, 32 KB
+constexpr int kTileS = kTileDw + 32768;            // S              dk x dv, 32 KB
+constexpr int kTileVn = kTileS + 32768;            // [Vn ; 0]       128 x dv, 32 KB
+constexpr int kTileDs = kTileVn + 32768;           // dS (bf16)      dk x dv, 32 KB
+constexpr int kBwdTiles = kTileDs + 32768;         // 208 KB
+constexpr int kBwdSmem = 1024 + kBwdTiles + 256;
+constexpr int kBwdLoadBytes = 32768 + 16384 + 8192 + 16384 + 32768 + 16384;   // TMA bytes per chunk
+
+struct BwdBars {
+  uint64_t full, inputs_free, t1_full, w_ready, t2_full, ds_ready;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwdArgs {
+  int n_chunks;
+  const float* e;
+  const float* ds_final;
+  __nv_bfloat16* d_kq;
+  __nv_bfloat16* d_intra;
+  __nv_bfloat16* d_kdec;
+  __nv_bfloat16* d_veff;
+  float* d_e;
+  float* ds0;
+  int* status;
+};
+
+struct BwdMaps {
+  CUtensorMap kq, intra, kdec, d_o, s, vn;
+};
+
+__device__ __forceinline__ uint4 pack8(const uint32_t* v, float sign) {
+  return make_uint4(pack_bf16x2(sign * __uint_as_float(v[0]), sign * __uint_as_float(v[1])),
+                    pack_bf16x2(sign * __uint_as_float(v[2]), sign * __uint_as_float(v[3])),
+                    pack_bf16x2(sign * __uint_as_float(v[4]), sign * __uint_as_float(v[5])),
+                    pack_bf16x2(sign * __uint_as_float(v[6]), sign * __uint_as_float(v[7])));
+}
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+gdn_scan_bwd_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant__ BwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  BwdBars* bars = reinterpret_cast<BwdBars*>(smem + kBwdTiles);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x;
+  const int N = a.n_chunks;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->full, 1);
+    mbar_init(&bars->inputs_free, 1);
+    mbar_init(&bars->t1_full, 1);
+    mbar_init(&bars->w_ready, 128);
+    mbar_init(&bars->t2_full, 1);
+    mbar_init(&bars->ds_ready, 128);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  // zero halves that stay zero: rows 64..127 of [kdec ; 0] and [Vn ; 0], the second column block of the intra tile
+  for (int i = threadIdx.x; i < 512; i += kBwdThreads) {   // 8 KB = 512 x 16 B per zero region
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    reinterpret_cast<uint4*>(smem + kTileKd + 8192)[i] = z;            // block 0, rows 64..127
+    reinterpret_cast<uint4*>(smem + kTileKd + 16384 + 8192)[i] = z;    // block 1, rows 64..127
+    reinterpret_cast<uint4*>(smem + kTileVn + 8192)[i] = z;
+    reinterpret_cast<uint4*>(smem + kTileVn + 16384 + 8192)[i] = z;
+    reinterpret_cast<uint4*>(smem + kTileIn + 8192)[i] = z;            // second 64-column block
+  }
+  fence_proxy_async_smem();
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  constexpr uint32_t kT1 = 0, kT2 = 128, kT3 = 256, kT4 = 320;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int n = N - 1; n >= 0; --n, ++it) {
+        // the previous chunk's products are done with the tiles (inputs_free) AND its epilogue has finished
+        // reading S for d e (it then publishes dS for this chunk: ds_ready)
+        if (it > 0 && (!mbar_wait(&bars->inputs_free, (it - 1) & 1, abort_flag) ||
+                       !mbar_wait(&bars->ds_ready, it & 1, abort_flag))) {
+          report_status(a.status, kWaitEmptyTimeout, 120, bh, n);
+          break;
+        }
+        const int chunk = bh * N + n;
+        mbar_arrive_expect_tx(&bars->full, kBwdLoadBytes);
+        tma_load_2d(smem + kTileKq, &tm.kq, &bars->full, 0, chunk * 128);
+        tma_load_2d(smem + kTileKq + 16384, &tm.kq, &bars->full, 64, chunk * 128);
+        tma_load_2d(smem + kTileKd, &tm.kdec, &bars->full, 0, chunk * 64);
+        tma_load_2d(smem + kTileKd + 16384, &tm.kdec, &bars->full, 64, chunk * 64);
+        tma_load_2d(smem + kTileIn, &tm.intra, &bars->full, 0, chunk * 64);
+        tma_load_2d(smem + kTileDw, &tm.d_o, &bars->full, 0, chunk * 64);
+        tma_load_2d(smem + kTileDw + 16384, &tm.d_o, &bars->full, 64, chunk * 64);
+        tma_load_2d(smem + kTileS, &tm.s, &bars->full, 0, chunk * 128);
+        tma_load_2d(smem + kTileS + 16384, &tm.s, &bars->full, 64, chunk * 128);
+        tma_load_2d(smem + kTileVn, &tm.vn, &bars->full, 0, chunk * 64);
+        tma_load_2d(smem + kTileVn + 16384, &tm.vn, &bars->full, 64, chunk * 64);
+      }
+      if (*abort_flag && it > 0) {
+        const uint64_t tw = globaltimer_ns();
+        while (!mbar_try_wait(&bars->full, (it - 1) & 1) && globaltimer_ns() - tw < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t i_kn = make_idesc(128, 128, 0, 1, 1);   // A K-major, B MN-major
+    constexpr uint32_t i_nn = make_idesc(128, 128, 1, 1, 1);   // both MN-major
+    constexpr uint32_t i_kk = make_idesc(128, 128, 0, 0, 1);   // both K-major
+    constexpr uint32_t i_kk64 = make_idesc(128, 64, 0, 0, 1);
+    const uint32_t b0 = smem_u32(smem);
+    const uint32_t kq = b0 + kTileKq, kd = b0 + kTileKd, in = b0 + kTileIn, dw = b0 + kTileDw, ss = b0 + kTileS,
+                   vn = b0 + kTileVn, ds = b0 + kTileDs;
+    int it = 0;
+    for (int n = N - 1; n >= 0; --n, ++it) {
+      if (!mbar_wait(&bars->ds_ready, it & 1, abort_flag) || !mbar_wait(&bars->full, it & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 121, bh, n);
+        break;
+      }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)   // T1 = [kdec ; 0] dS      (K = dk)
+          umma_bf16(tmem + kT1, make_smem_desc(kd + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(ds + k * 2048, 16384, 1024), i_kn, k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // T1 += [intra^T ; 0] dO  (K = 64 tokens)
+          umma_bf16(tmem + kT1, make_smem_desc(in + k * 2048, 8192, 1024), make_smem_desc(dw + k * 2048, 16384, 1024),
+                    i_nn, 1u);
+        tc_commit(&bars->t1_full);
+      }
+      __syncwarp();
+      if (!mbar_wait(&bars->w_ready, it & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 122, bh, n);
+        break;
+      }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {   // K = dv
+          const uint64_t a_dw = make_smem_desc(dw + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          umma_bf16(tmem + kT2, a_dw, make_smem_desc(ss + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), i_kk, k > 0 ? 1u : 0u);
+          umma_bf16(tmem + kT3, a_dw, make_smem_desc(vn + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), i_kk64, k > 0 ? 1u : 0u);
+          umma_bf16(tmem + kT4, make_smem_desc(vn + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                    make_smem_desc(ds + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024), i_kk, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // T5 = qg^T dO   (qg = rows 64..127 of the kq tile, K = tokens)
+          umma_bf16(tmem + kT1, make_smem_desc(kq + 8192 + k * 2048, 16384, 1024), make_smem_desc(dw + k * 2048, 16384, 1024),
+                    i_nn, k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // T5 += k_cum^T W (W = rows 64..127 of the [dO ; W] tile)
+          umma_bf16(tmem + kT1, make_smem_desc(kq + k * 2048, 16384, 1024),
+                    make_smem_desc(dw + 8192 + k * 2048, 16384, 1024), i_nn, 1u);
+        tc_commit(&bars->inputs_free);
+        tc_commit(&bars->t2_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    uint8_t* t_ds = smem + kTileDs;
+    float dS[kDv];
+    if (a.ds_final != nullptr) {
+      const float4* sp = reinterpret_cast<const float4*>(a.ds_final + (static_cast<int64_t>(bh) * kDk + r) * kDv);
+#pragma unroll
+      for (int j = 0; j < kDv / 4; ++j) {
+        const float4 f = sp[j];
+        dS[4 * j] = f.x; dS[4 * j + 1] = f.y; dS[4 * j + 2] = f.z; dS[4 * j + 3] = f.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kDv; ++j) dS[j] = 0.f;
+    }
+    bool ok = true;
+    int it = 0;
+    for (int n = N - 1; n >= -1; --n, ++it) {
+      // ---- publish dS (bf16) for the chunk's products ----
+#pragma unroll
+      for (int c = 0; c < kDv; c += 8)
+        *reinterpret_cast<uint4*>(t_ds + swz(r, c, 16384)) =
+            make_uint4(pack_bf16x2(dS[c], dS[c + 1]), pack_bf16x2(dS[c + 2], dS[c + 3]), pack_bf16x2(dS[c + 4], dS[c + 5]),
+                       pack_bf16x2(dS[c + 6], dS[c + 7]));
+      fence_proxy_async_smem();
+      if (n < 0) break;
+      mbar_arrive(&bars->ds_ready);
+      const int64_t chunk = static_cast<int64_t>(bh) * N + n;
+      const float e = a.e[chunk];
+      if (ok && !mbar_wait(&bars->t1_full, it & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 123, bh, n);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok && r < kC) {
+        tc_fence_after();
+        uint4* dve = reinterpret_cast<uint4*>(a.d_veff + (chunk * kC + r) * kDv);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + kT1 + c * 32 + lane_off, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            dve[c * 4 + (j >> 3)] = pack8(v + j, 1.f);
+            *reinterpret_cast<uint4*>(smem + kTileDw + swz(64 + r, c * 32 + j, 16384)) = pack8(v + j, -1.f);
+          }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(&bars->w_ready);
+      if (ok && !mbar_wait(&bars->t2_full, it & 1, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 124, bh, n);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) continue;
+      tc_fence_after();
+      // T2: rows 0..63 -> d qg (stored at rows 64..127 of d_kq), rows 64..127 -> d k_cum (rows 0..63)
+      {
+        uint4* dst = reinterpret_cast<uint4*>(a.d_kq + (chunk * 128 + (r < kC ? r + kC : r - kC)) * kDk);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + kT2 + c * 32 + lane_off, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) dst[c * 4 + (j >> 3)] = pack8(v + j, 1.f);
+        }
+      }
+      if (r < kC) {
+        uint4* di = reinterpret_cast<uint4*>(a.d_intra + (chunk * kC + r) * kC);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + kT3 + c * 32 + lane_off, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) di[c * 4 + (j >> 3)] = pack8(v + j, 1.f);
+        }
+        uint4* dk = reinterpret_cast<uint4*>(a.d_kdec + (chunk * kC + r) * kDk);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + kT4 + c * 32 + lane_off, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) dk[c * 4 + (j >> 3)] = pack8(v + j, 1.f);
+        }
+      }
+      // d e = <dS, S> with the dS that entered the chunk; then dS <- e dS + T5
+      float de = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + kT1 + c * 32 + lane_off, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          const uint4 sv = *reinterpret_cast<const uint4*>(smem + kTileS + swz(r, c * 32 + j, 16384));
+          const float2 s0 = unpack_bf16x2(sv.x), s1 = unpack_bf16x2(sv.y), s2 = unpack_bf16x2(sv.z), s3 = unpack_bf16x2(sv.w);
+          const float sf[8] = {s0.x, s0.y, s1.x, s1.y, s2.x, s2.y, s3.x, s3.y};
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int col = c * 32 + j + t;
+            de += dS[col] * sf[t];
+            dS[col] = dS[col] * e + __uint_as_float(v[j + t]);
+          }
+        }
+      }
+      tc_fence_before();
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) de += __shfl_xor_sync(0xffffffffu, de, o);
+      if (lane == 0) atomicAdd(a.d_e + chunk, de);
+    }
+    if (ok) {
+      float4* sp = reinterpret_cast<float4*>(a.ds0 + (static_cast<int64_t>(bh) * kDk + r) * kDv);
+#pragma unroll
+      for (int j = 0; j < kDv / 4; ++j) sp[j] = make_float4(dS[4 * j], dS[4 * j + 1], dS[4 * j + 2], dS[4 * j + 3]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_gdn_scan_bwd(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
+                                const __nv_bfloat16* s_save, const __nv_bfloat16* vn_save, const float* e,
+                                const __nv_bfloat16* d_o, const float* ds_final, __nv_bfloat16* d_kq,
+                                __nv_bfloat16* d_intra, __nv_bfloat16* d_kdec, __nv_bfloat16* d_veff, float* d_e, float* ds0,
+                                int bh, int n_chunks, int* status, cudaStream_t stream) {
+  if (bh < 1 || n_chunks < 1) return cudaErrorInvalidValue;
+  BwdMaps tm;
+  cudaError_t err;
+  const uint64_t chunks = static_cast<uint64_t>(bh) * n_chunks;
+  if ((err = encode_tma_2d(&tm.kq, kq, 2, kDk, chunks * 128, kDk * 2ull, 64, 128)) != cudaSuccess) return err;
+  if ((err = encode_tma_2d(&tm.intra, intra, 2, kC, chunks * kC, kC * 2ull, 64, 64)) != cudaSuccess) return err;
+  if ((err = encode_tma_2d(&tm.kdec, kdec, 2, kDk, chunks * kC, kDk * 2ull, 64, 64)) != cudaSuccess) return err;
+  if ((err = encode_tma_2d(&tm.d_o, d_o, 2, kDv, chunks * kC, kDv * 2ull, 64, 64)) != cudaSuccess) return err;
+  if ((err = encode_tma_2d(&tm.s, s_save, 2, kDv, chunks * kDk, kDv * 2ull, 64, 128)) != cudaSuccess) return err;
+  if ((err = encode_tma_2d(&tm.vn, vn_save, 2, kDv, chunks * kC, kDv * 2ull, 64, 64)) != cudaSuccess) return err;
+  static bool configured = false;
+  if (!configured) {
+    if ((err = cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem)) != cudaSuccess)
+      return err;
+    configured = true;
+  }
+  BwdArgs args{n_chunks, e, ds_final, d_kq, d_intra, d_kdec, d_veff, d_e, ds0, status};
+  gdn_scan_bwd_kernel<<<bh, kBwdThreads, kBwdSmem, stream>>>(tm, args);
   return cudaGetLastError();
 }
 

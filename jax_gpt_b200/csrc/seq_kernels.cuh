@@ -51,10 +51,22 @@ cudaError_t launch_rmsnorm_rope_bwd(const __nv_bfloat16* x, const __nv_bfloat16*
 //   intra [BH, N, 64, 64]   bf16: causal-masked (q k^T * decay)
 //   kdec  [BH, N, 64, 128]  bf16: k * exp(g_end - G)
 //   veff  [BH, N, 64, 128]  bf16: corrected values;  e [BH, N] fp32: exp(g_end);  s0: initial state or nullptr
-// Writes o [BH, N, 64, 128] bf16 and the final state s_out [BH, 128, 128] fp32.
+// Writes o [BH, N, 64, 128] bf16 and the final state s_out [BH, 128, 128] fp32; with s_save / vn_save (optional,
+// [BH, N, 128, 128] / [BH, N, 64, 128] bf16) also the state every chunk starts from and its v_new, which the
+// backward scan consumes.
 cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
                             const __nv_bfloat16* veff, const float* e, const float* s0, __nv_bfloat16* o, float* s_out,
-                            int bh, int n_chunks, int* status, cudaStream_t stream);
+                            __nv_bfloat16* s_save, __nv_bfloat16* vn_save, int bh, int n_chunks, int* status,
+                            cudaStream_t stream);
+
+// Backward of the scan (reverse over chunks, dS resident on chip). dO [BH, N, 64, 128] bf16; ds_final optional
+// [BH, 128, 128] fp32. Writes d_kq [BH, N, 128, 128] (rows 0-63 d k_cum, 64-127 d q*exp(G)), d_intra, d_kdec,
+// d_veff (bf16, shaped like the inputs), ACCUMULATES d_e [BH, N] fp32 (zero it first), writes ds0 [BH, 128, 128] fp32.
+cudaError_t launch_gdn_scan_bwd(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
+                                const __nv_bfloat16* s_save, const __nv_bfloat16* vn_save, const float* e,
+                                const __nv_bfloat16* d_o, const float* ds_final, __nv_bfloat16* d_kq,
+                                __nv_bfloat16* d_intra, __nv_bfloat16* d_kdec, __nv_bfloat16* d_veff, float* d_e, float* ds0,
+                                int bh, int n_chunks, int* status, cudaStream_t stream);
 
 // Causal depthwise conv (width 4) + SiLU over x [B, T, C] bf16 with w [C, 4]; `state` (optional) [B, C, 4] fp32
 // receives the last four raw inputs of every channel.

@@ -109,6 +109,48 @@ def deltanet_recurrent_step(x, params, state, conv_state, n_qk: int, n_v: int, d
     return y[:, None, :], new_state.to(state.dtype), new_conv
 
 
+class _GdnScanFn(torch.autograd.Function):
+    """Inter-chunk scan of the gated delta rule on the tcgen05 kernels. Inputs per (batch*head, chunk):
+    kq (128, dk) = [k_cum ; q exp(G)], intra (64, 64), kdec (64, dk), veff (64, dv) in bf16, e fp32, optional
+    initial state. Returns (o (BH, N, 64, dv) bf16, final state fp32)."""
+
+    @staticmethod
+    def forward(ctx, kq, intra, kdec, veff, e, s0):
+        from ... import _ext
+        kq, intra, kdec, veff, e = [t.contiguous() for t in (kq, intra, kdec, veff, e)]
+        BH, N = kq.shape[0], kq.shape[1]
+        dev = kq.device
+        o = torch.empty(BH, N, 64, 128, device=dev, dtype=torch.bfloat16)
+        s_out = torch.empty(BH, 128, 128, device=dev, dtype=torch.float32)
+        needs = any(ctx.needs_input_grad)
+        s_save = torch.empty(BH, N, 128, 128, device=dev, dtype=torch.bfloat16) if needs else None
+        vn_save = torch.empty(BH, N, 64, 128, device=dev, dtype=torch.bfloat16) if needs else None
+        s0c = s0.contiguous() if s0 is not None else None
+        _ext.ops().gdn_scan(kq, intra, kdec, veff, e, s0c, o, s_out, s_save, vn_save)
+        if needs:
+            ctx.save_for_backward(kq, intra, kdec, e, s_save, vn_save)
+            ctx.has_s0 = s0 is not None
+        return o, s_out
+
+    @staticmethod
+    def backward(ctx, d_o, d_s_out):
+        from ... import _ext
+        kq, intra, kdec, e, s_save, vn_save = ctx.saved_tensors
+        BH, N = kq.shape[0], kq.shape[1]
+        dev = kq.device
+        bf = torch.bfloat16
+        d_kq = torch.empty_like(kq)
+        d_intra = torch.empty_like(intra)
+        d_kdec = torch.empty_like(kdec)
+        d_veff = torch.empty(BH, N, 64, 128, device=dev, dtype=bf)
+        d_e = torch.zeros(BH, N, device=dev, dtype=torch.float32)
+        ds0 = torch.empty(BH, 128, 128, device=dev, dtype=torch.float32)
+        dsf = d_s_out.float().contiguous() if d_s_out is not None else None
+        _ext.ops().gdn_scan_bwd(kq, intra, kdec, s_save, vn_save, e, d_o.to(bf).contiguous(), dsf, d_kq, d_intra, d_kdec,
+                                d_veff, d_e, ds0)
+        return d_kq, d_intra, d_kdec, d_veff, d_e, (ds0 if ctx.has_s0 else None)
+
+
 def chunk_gated_delta_rule(q, k, v, beta, g, chunk_size: int, initial_state=None):
     """Chunk-parallel gated delta rule in fp32.
     q,k (B,H,T,dk) normalised; v (B,H,T,dv); beta,g (B,H,T). Returns (o (B,H,T,dv), final state)."""
@@ -134,21 +176,18 @@ def chunk_gated_delta_rule(q, k, v, beta, g, chunk_size: int, initial_state=None
     rhs = torch.cat([v * beta[..., None], kb * torch.exp(G)[..., None]], dim=-1)
     sol = torch.linalg.solve_triangular(eye + A, rhs, upper=False, unitriangular=True)
     v_eff, k_cum = sol[..., :dv], sol[..., dv:]
-    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, beta, g))
-    if q.is_cuda and dk == 128 and dv == 128 and C == 64 and not needs_grad:
-        # the sequential part runs as ONE kernel per (batch, head) with the state on chip (csrc/gdn_kernels.cu)
-        from ... import _ext
+    if q.is_cuda and dk == 128 and dv == 128 and C == 64:
+        # the sequential part runs as ONE kernel per (batch, head) with the state on chip, forward and
+        # backward (csrc/gdn_kernels.cu); the batched algebra around it stays differentiable PyTorch
         bf = torch.bfloat16
         g_end = G[..., -1]
-        kq = torch.cat([k_cum, q * torch.exp(G)[..., None]], dim=-2).to(bf).reshape(B * H, N, 2 * C, dk).contiguous()
-        intra = ((q @ k.transpose(-1, -2)) * decay).masked_fill(~causal, 0.0).to(bf).reshape(B * H, N, C, C).contiguous()
-        kdec = (k * torch.exp(g_end[..., None] - G)[..., None]).to(bf).reshape(B * H, N, C, dk).contiguous()
-        veff = v_eff.to(bf).reshape(B * H, N, C, dv).contiguous()
-        e = torch.exp(g_end).float().reshape(B * H, N).contiguous()
-        s0 = initial_state.float().reshape(B * H, dk, dv).contiguous() if initial_state is not None else None
-        o = torch.empty(B * H, N, C, dv, device=q.device, dtype=bf)
-        s_out = torch.empty(B * H, dk, dv, device=q.device, dtype=torch.float32)
-        _ext.ops().gdn_scan(kq, intra, kdec, veff, e, s0, o, s_out)
+        kq = torch.cat([k_cum, q * torch.exp(G)[..., None]], dim=-2).to(bf).reshape(B * H, N, 2 * C, dk)
+        intra = ((q @ k.transpose(-1, -2)) * decay).masked_fill(~causal, 0.0).to(bf).reshape(B * H, N, C, C)
+        kdec = (k * torch.exp(g_end[..., None] - G)[..., None]).to(bf).reshape(B * H, N, C, dk)
+        veff = v_eff.to(bf).reshape(B * H, N, C, dv)
+        e = torch.exp(g_end).float().reshape(B * H, N)
+        s0 = initial_state.float().reshape(B * H, dk, dv) if initial_state is not None else None
+        o, s_out = _GdnScanFn.apply(kq, intra, kdec, veff, e, s0)
         return o.reshape(B, H, N * C, dv)[:, :, :T].float(), s_out.reshape(B, H, dk, dv)
     S = initial_state.float() if initial_state is not None else q.new_zeros(B, H, dk, dv)
     outs = []

@@ -226,3 +226,36 @@ def test_gdn_chunk_scan_kernel(cuda_device, T, with_state):
     _ext.check_status(cuda_device)
     assert _rel(o_k.cpu(), ref) < 2e-2, _rel(o_k.cpu(), ref)
     assert _rel(S_k.cpu(), S) < 2e-2, _rel(S_k.cpu(), S)
+
+
+@pytest.mark.parametrize("T,with_state", [(128, False), (300, True)])
+def test_gdn_chunk_scan_backward_kernel(cuda_device, T, with_state):
+    """Gradients through the tcgen05 forward + backward scan kernels vs autograd of the fp32 PyTorch chunk loop."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    torch.manual_seed(4)
+    B, H, dk, dv = 1, 2, 128, 128
+    q0 = D._l2_norm(torch.randn(B, H, T, dk)) * dk ** -0.5
+    k0 = D._l2_norm(torch.randn(B, H, T, dk))
+    v0 = torch.randn(B, H, T, dv)
+    b0 = torch.sigmoid(torch.randn(B, H, T))
+    g0 = -torch.rand(B, H, T) * 0.2
+    s0 = torch.randn(B, H, dk, dv) * 0.1 if with_state else None
+    wo, ws = torch.randn(B, H, T, dv), torch.randn(B, H, dk, dv) * 0.1
+
+    def run(device):
+        leaves = [t.clone().to(device).requires_grad_(True) for t in (q0, k0, v0, b0, g0)]
+        st = s0.clone().to(device).requires_grad_(True) if with_state else None
+        o, S = D.chunk_gated_delta_rule(*leaves, 64, st)
+        ((o * wo.to(device)).sum() + (S * ws.to(device)).sum()).backward()
+        grads = [t.grad.float().cpu() for t in leaves] + ([st.grad.float().cpu()] if with_state else [])
+        return o.detach().float().cpu(), grads
+
+    o_ref, g_ref = run("cpu")
+    o_k, g_k = run(cuda_device)
+    torch.cuda.synchronize()
+    _ext.check_status(cuda_device)
+    assert _rel(o_k, o_ref) < 2e-2
+    names = ["q", "k", "v", "beta", "g"] + (["s0"] if with_state else [])
+    for n, a, b in zip(names, g_k, g_ref):
+        assert _rel(a, b) < 4e-2, (n, _rel(a, b))
