@@ -59,6 +59,18 @@ def train_moe(args, tc, rank, world, device):
     params = init_params(cfg, tc.seed, torch.float32)
     ep = dist_opt = local = None
     on_gpu = device.type == "cuda"
+    fusable = cfg.d_model % 256 == 0 and cfg.moe_intermediate_size % 256 == 0 and cfg.n_routed_experts <= 512
+    if world == 1 and on_gpu and fusable:
+        # one GPU: the fused expert kernels with all experts local (one launch per MoE layer and direction)
+        import torch.distributed as dist
+        from jax_gpt_b200.comm.symm import Communicator
+        from jax_gpt_b200.parallel.expert_parallel import EPMoERuntime, FusedEPMoE, is_expert_leaf
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29536")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+        layer = FusedEPMoE(Communicator(device=device), tc.micro_batch_size * tc.seq_len, cfg.d_model,
+                           cfg.moe_intermediate_size, cfg.n_routed_experts, cfg.n_experts_per_token, training=True)
+        ep, local = EPMoERuntime(layer), is_expert_leaf
     if world > 1 and on_gpu:
         from jax_gpt_b200.parallel.expert_parallel import EPMoERuntime, FusedEPMoE, is_expert_leaf, shard_experts
         from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW, NcclShardedAdamW
@@ -96,7 +108,7 @@ def train_moe(args, tc, rank, world, device):
         from jax_gpt_b200.ckpt.manager import save_tree
         save_tree(os.path.join(tc.checkpoint_dir, f"{args.preset}_step{eng.step_count}.safetensors"), eng.master_tree())
     data.close()
-    if world > 1:
+    if torch.distributed.is_initialized():
         torch.distributed.destroy_process_group()
 
 
