@@ -269,7 +269,7 @@ class GPT2TrainEngine:
                 self._reduce_bucket_async(l)
         misc.embed_bwd(self.tokens, dx.view(self.B, self.T, d), g["wte.embedding"], g["wpe.embedding"], 0)
         if self._overlap_now:
-            self.dist_optimizer.reduce_bucket(L)          # embeddings / final norm: nothing left to overlap with
+            self.dist_optimizer.reduce_bucket(L, blocks=1184)   # embeddings / final norm: nothing left to overlap with
             torch.cuda.current_stream().wait_stream(self._rs_stream)
 
     def _reduce_bucket_async(self, b: int):

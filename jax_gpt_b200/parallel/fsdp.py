@@ -119,7 +119,7 @@ class FusedShardedAdamW(_ShardedBase):
         self.n_total, self.n_decay = engine.flat.total, engine.flat.n_decay
 
     # ---- gradient reduce-scatter overlapped with backward ------------------------------------------
-    def setup_buckets(self, buckets, blocks: int = 16):
+    def setup_buckets(self, buckets, blocks: int = 74):
         """``buckets``: list (in the order backward completes them) of lists of (offset, length) element ranges
         of the flat gradient vector. Each bucket's part inside this rank's shard is reduced by one small
         kernel on a side stream as soon as backward has produced it (``reduce_bucket``)."""
@@ -138,10 +138,11 @@ class FusedShardedAdamW(_ShardedBase):
         self._bucket_blocks = blocks
         dist.barrier(self.group)
 
-    def reduce_bucket(self, b: int):
-        """Launch on the CURRENT stream (the caller puts it on a side stream behind the producing kernels)."""
+    def reduce_bucket(self, b: int, blocks: Optional[int] = None):
+        """Launch on the CURRENT stream (the caller puts it on a side stream behind the producing kernels).
+        ``blocks``: CTAs of 256 threads; few for a kernel that shares the GPU with backward, many for one that runs alone."""
         _ext.ops().rs_bucket(self.world, self.rank, self.grad_buf.peer_ptrs, self._bucket_flags.peer_ptrs,
-                             self._bucket_ranges[b], b, self.epoch_t, self._bucket_blocks, self.comm.wait_seconds)
+                             self._bucket_ranges[b], b, self.epoch_t, blocks or self._bucket_blocks, self.comm.wait_seconds)
 
     def step(self, engine, extra_sq=None, pre_reduced: bool = False):
         """``extra_sq``: device scalar with this rank's sum of squared gradients of parameters kept
