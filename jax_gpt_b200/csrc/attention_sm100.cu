@@ -624,28 +624,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (row, head).
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per token row, 16-byte loads, the D / 8 lanes
+// that cover one head reduce among themselves.
+template <int D>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int64_t ldo,
                                   const __nv_bfloat16* __restrict__ dout, int64_t lddo, float* __restrict__ delta,
-                                  int B, int T, int H, int D) {
-  const int64_t gw = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+                                  int B, int T, int H) {
+  constexpr int kLanesPerHead = D / 8;   // 8 (D = 64) or 16 (D = 128): divides 32
+  const int64_t row = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (gw >= static_cast<int64_t>(B) * T * H) return;
-  const int h = static_cast<int>(gw % H);
-  const int64_t row = gw / H;
-  const __nv_bfloat16* po = o + row * ldo + h * D;
-  const __nv_bfloat16* pd = dout + row * lddo + h * D;
-  float s = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + d));
-    float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + d));
-    s += x.x * y.x + x.y * y.y;
-  }
+  if (row >= static_cast<int64_t>(B) * T) return;
+  const uint4* po = reinterpret_cast<const uint4*>(o + row * ldo);
+  const uint4* pd = reinterpret_cast<const uint4*>(dout + row * lddo);
+  const int nvec = H * kLanesPerHead;
+  const int64_t bidx = row / T, t = row % T;
+  for (int i0 = 0; i0 < nvec; i0 += 32) {
+    const int i = i0 + lane;
+    float s = 0.f;
+    if (i < nvec) {
+      const uint4 x = po[i], y = pd[i];
+      const float2 x0 = unpack_bf16x2(x.x), x1 = unpack_bf16x2(x.y), x2 = unpack_bf16x2(x.z), x3 = unpack_bf16x2(x.w);
+      const float2 y0 = unpack_bf16x2(y.x), y1 = unpack_bf16x2(y.y), y2 = unpack_bf16x2(y.z), y3 = unpack_bf16x2(y.w);
+      s = x0.x * y0.x + x0.y * y0.y + x1.x * y1.x + x1.y * y1.y + x2.x * y2.x + x2.y * y2.y + x3.x * y3.x + x3.y * y3.y;
+    }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
-    const int64_t bidx = row / T, t = row % T;
-    delta[(bidx * H + h) * T + t] = s;
+    for (int off = kLanesPerHead / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (i < nvec && (lane % kLanesPerHead) == 0) delta[(bidx * H + i / kLanesPerHead) * T + t] = s;
   }
 }
 
@@ -704,9 +708,9 @@ cudaError_t bwd_launch(const AttnTensors& t, const AttnShape& s, const __nv_bflo
   if ((e = make_map(&tv, t.v, t.ldv, rows, s.Hkv * D)) != cudaSuccess) return e;
   if ((e = make_map(&tdo, dout, lddo, rows, s.H * D)) != cudaSuccess) return e;
   {
-    const int64_t warps = static_cast<int64_t>(rows) * s.H;
+    const int64_t warps = static_cast<int64_t>(rows);
     const int blocks = static_cast<int>((warps * 32 + 255) / 256);
-    attn_delta_kernel<<<blocks, 256, 0, stream>>>(out, ldo, dout, lddo, delta, s.B, s.T, s.H, D);
+    attn_delta_kernel<D><<<blocks, 256, 0, stream>>>(out, ldo, dout, lddo, delta, s.B, s.T, s.H);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
   auto kernel = attn_bwd_kernel<D>;

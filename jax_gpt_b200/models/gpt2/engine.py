@@ -102,6 +102,7 @@ class GPT2TrainEngine:
         self._overlap = False
         self._overlap_now = False
         self._pre_reduced = False
+        self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         if dist_optimizer is not None:
             self.flat = FlatParams(cfg, self.device, seed, init, getattr(dist_optimizer, "alloc_grad", None),
                                    getattr(dist_optimizer, "alloc_compute", None))
@@ -223,23 +224,40 @@ class GPT2TrainEngine:
         cfg, p, g = self.cfg, self.p, self.g
         L, d = cfg.n_layers, cfg.d_model
         M = self.B * self.T
-        split = max(1, min(8, M // 4096))
+        sms = self._sm_count
+
+        def split_for(out_rows: int, out_cols: int) -> int:
+            """Split-K factor of a weight-gradient GEMM (K = tokens): the number of (tile, split) work items should
+            fill whole waves of the persistent kernel's CTAs; every split keeps at least 1024 tokens."""
+            tiles = ((out_rows + 127) // 128) * ((out_cols + 255) // 256)
+            best, best_eff = 1, 0.0
+            lo = max(1, min(4, M // 4096))
+            for sp in range(lo, max(lo, min(16, M // 1024)) + 1):
+                items = tiles * sp
+                eff = items / (-(-items // sms) * sms)
+                if eff > best_eff + 0.02:
+                    best, best_eff = sp, eff
+            return best
+
+        f = cfg.d_ff
+        sp_lm, sp_proj2, sp_fc = split_for(cfg.vocab_size, d), split_for(f, d), split_for(d, f)
+        sp_proj, sp_attn = split_for(d, d), split_for(d, 3 * d)
         dlog = self.logits[:, :cfg.vocab_size]
         # lm head (tied): dlnf = dlogits @ wte ; dwte += dlogits^T @ lnf
         G.gemm(dlog, p["wte.embedding"], b_mn_major=True, out=self.dtmp)
         G.gemm(dlog, self.lnf, a_mn_major=True, b_mn_major=True, out=g["wte.embedding"], out_mode=G.OUT_F32_ATOMIC,
-               split_k=split)
+               split_k=sp_lm)
         dx, dx_other = self.dx_a, self.dx_b
         norm.norm_bwd(norm.LAYERNORM, self.dtmp, self.x[L], p["ln_f.layer_norm.scale"], self.lnf_mean, self.lnf_rstd,
                       g["ln_f.layer_norm.scale"], g["ln_f.layer_norm.bias"], dx=dx)
         for l in reversed(range(L)):
             # MLP: x[l+1] = fc_act @ W2 + b2 + xmid
             G.gemm(self.fc_act[l], dx, a_mn_major=True, b_mn_major=True, out=g["h.mlp.c_proj.kernel"][l],
-                   out_mode=G.OUT_F32_ATOMIC, split_k=split)
+                   out_mode=G.OUT_F32_ATOMIC, split_k=sp_proj2)
             misc.bias_grad(dx, g["h.mlp.c_proj.bias"][l])
             G.gemm(dx, p["h.mlp.c_proj.kernel"][l], aux=self.fc_pre[l], epilogue=G.EPI_GELU_GRAD, out=self.dfc)
             G.gemm(self.ln2[l], self.dfc, a_mn_major=True, b_mn_major=True, out=g["h.mlp.c_fc.kernel"][l],
-                   out_mode=G.OUT_F32_ATOMIC, split_k=split)
+                   out_mode=G.OUT_F32_ATOMIC, split_k=sp_fc)
             misc.bias_grad(self.dfc, g["h.mlp.c_fc.bias"][l])
             G.gemm(self.dfc, p["h.mlp.c_fc.kernel"][l], out=self.dtmp)
             norm.norm_bwd(norm.LAYERNORM, self.dtmp, self.xmid[l], p["h.ln_2.layer_norm.scale"][l], self.ln2_mean[l],
@@ -248,7 +266,7 @@ class GPT2TrainEngine:
             dx, dx_other = dx_other, dx  # dx = gradient w.r.t. xmid
             # attention: xmid = att @ Wo + bo + x[l]
             G.gemm(self.att[l], dx, a_mn_major=True, b_mn_major=True, out=g["h.attn.c_proj.kernel"][l],
-                   out_mode=G.OUT_F32_ATOMIC, split_k=split)
+                   out_mode=G.OUT_F32_ATOMIC, split_k=sp_proj)
             misc.bias_grad(dx, g["h.attn.c_proj.bias"][l])
             G.gemm(dx, p["h.attn.c_proj.kernel"][l], out=self.dtmp)
             self.dq_acc.zero_()
@@ -258,7 +276,7 @@ class GPT2TrainEngine:
                               dq=self._heads(self.dqkv, 0), dk=self._heads(self.dqkv, 1), dv=self._heads(self.dqkv, 2),
                               dq_accum=self.dq_acc, delta=self.delta)
             G.gemm(self.ln1[l], self.dqkv, a_mn_major=True, b_mn_major=True, out=g["h.attn.c_attn.kernel"][l],
-                   out_mode=G.OUT_F32_ATOMIC, split_k=split)
+                   out_mode=G.OUT_F32_ATOMIC, split_k=sp_attn)
             misc.bias_grad(self.dqkv, g["h.attn.c_attn.bias"][l])
             G.gemm(self.dqkv, p["h.attn.c_attn.kernel"][l], out=self.dtmp)
             norm.norm_bwd(norm.LAYERNORM, self.dtmp, self.x[l], p["h.ln_1.layer_norm.scale"][l], self.ln1_mean[l],
