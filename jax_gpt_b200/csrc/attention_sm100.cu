@@ -218,7 +218,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * a.scale_log2;
+          float s = __uint_as_float(v[i]);   // the (positive) softmax scale is applied to the maximum once, below
           if (need_mask) {
             const int kvpos = kv0 + c * 32 + i;
             if (kvpos >= a.T || (a.causal && kvpos > qpos)) s = -INFINITY;
@@ -226,6 +226,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           mx = fmaxf(mx, s);
         }
       }
+      mx *= a.scale_log2;
       const __nv_bfloat16 mine = __float2bfloat16(mx);
       xchg[half * 128 + r] = mine;
       mbar_arrive(&bars->x_ready);
@@ -247,13 +248,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(v[i]) * a.scale_log2, s1 = __uint_as_float(v[i + 1]) * a.scale_log2;
+          float s0 = fmaf(__uint_as_float(v[i]), a.scale_log2, -mref), s1 = fmaf(__uint_as_float(v[i + 1]), a.scale_log2, -mref);
           if (need_mask) {
             const int kvpos = kv0 + c * 32 + i;
             if (kvpos >= a.T || (a.causal && kvpos > qpos)) s0 = -INFINITY;
             if (kvpos + 1 >= a.T || (a.causal && kvpos + 1 > qpos)) s1 = -INFINITY;
           }
-          const float p0 = exp2f(s0 - mref), p1 = exp2f(s1 - mref);
+          const float p0 = exp2f(s0), p1 = exp2f(s1);
           rs += p0 + p1;
           pk[i >> 1] = pack_bf16x2(p0, p1);
         }
@@ -535,22 +536,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tmem_ld_wait();
         uint32_t pp[16], dd[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p[2], ds[2];
+        for (int i = 0; i < 32; i += 4) {
+          // per-query statistics of four consecutive columns with one 16-byte shared-memory load each
+          const float4 l4 = *reinterpret_cast<const float4*>(&st_lse[c * 32 + i]);
+          const float4 d4 = *reinterpret_cast<const float4*>(&st_del[c * 32 + i]);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, de[4] = {d4.x, d4.y, d4.z, d4.w};
+          float p[4], ds[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
+          for (int e = 0; e < 4; ++e) {
             const int qi = c * 32 + i + e;
             bool valid = true;
             if (need_mask) {
               const int qp = q0 + qi;
               valid = !(qp >= a.T || kvpos >= a.T || (a.causal && qp < kvpos));
             }
-            const float pe = valid ? exp2f(__uint_as_float(sv[i + e]) * a.scale_log2 - st_lse[qi]) : 0.f;
+            const float pe = valid ? exp2f(fmaf(__uint_as_float(sv[i + e]), a.scale_log2, -ls[e])) : 0.f;
             p[e] = pe;
-            ds[e] = valid ? pe * (__uint_as_float(dv[i + e]) - st_del[qi]) * a.scale : 0.f;
+            ds[e] = valid ? (pe * a.scale) * (__uint_as_float(dv[i + e]) - de[e]) : 0.f;
           }
           pp[i >> 1] = pack_bf16x2(p[0], p[1]);
+          pp[(i >> 1) + 1] = pack_bf16x2(p[2], p[3]);
           dd[i >> 1] = pack_bf16x2(ds[0], ds[1]);
+          dd[(i >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
         }
         store_row_chunk_sw128(smem + C::kOffPT, r, c * 32, pp);
         store_row_chunk_sw128(smem + C::kOffDST, r, c * 32, dd);
