@@ -505,21 +505,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int kvpos = jb * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
     bool ok = true;
+    // Per-query statistics (lse, delta) of iteration `jt` go to the shared buffer jt & 1. They are staged one
+    // iteration ahead (right after the element-wise part of the previous iteration), so their global-load
+    // latency is off the critical path; a thread only stages jt + 1 after it has seen stats_ready(jt), i.e.
+    // after every thread has finished reading buffer (jt - 1) & 1.
+    auto stage_stats = [&](int jt) {
+      const int hq_j = hkv * group + jt / nqi;
+      const int q0_j = (i0 + jt % nqi) * 128;
+      float* dst = stats + (jt & 1) * 256;
+      const int qi = tid & 127;
+      const int qp = q0_j + qi;
+      const int64_t si = (static_cast<int64_t>(b) * a.H + hq_j) * a.T + qp;
+      if (tid < 128) dst[qi] = (qp < a.T) ? a.lse[si] : 0.f;
+      else dst[128 + qi] = (qp < a.T) ? a.delta[si] : 0.f;
+      mbar_arrive(&bars->stats_ready);
+    };
+    if (n_iters > 0) stage_stats(0);
     for (int it = 0; it < n_iters; ++it) {
       const int hq = hkv * group + it / nqi;
       const int iq = i0 + it % nqi;
       const int q0 = iq * 128;
       float* st_lse = stats + (it & 1) * 256;
       float* st_del = st_lse + 128;
-      {
-        const int qi = tid & 127;
-        const int qp = q0 + qi;
-        const int64_t si = (static_cast<int64_t>(b) * a.H + hq) * a.T + qp;
-        if (tid < 128) st_lse[qi] = (qp < a.T) ? a.lse[si] : 0.f;
-        else st_del[qi] = (qp < a.T) ? a.delta[si] : 0.f;
-      }
       // bounded rendezvous of the 256 compute threads on the per-query statistics
-      mbar_arrive(&bars->stats_ready);
       if (!mbar_wait(&bars->stats_ready, it & 1, abort_flag) || !mbar_wait(&bars->st_full, it & 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitAttnTimeout, 205, blockIdx.x, it);
         ok = false;
@@ -565,6 +573,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars->p_ready);
+      if (it + 1 < n_iters) stage_stats(it + 1);
       if (!mbar_wait(&bars->dq_full, it & 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitAttnTimeout, 206, blockIdx.x, it);
         ok = false;
