@@ -360,6 +360,13 @@ TORCH_LIBRARY(b200, m) {
       &attn_bwd);
   m.def("cast_rows(Tensor src, Tensor(a!) dst) -> ()", &cast_rows);
   m.def("norm_bwd_scratch_floats(int D) -> int", [](int64_t D) { return b200::norm_bwd_scratch_floats(static_cast<int>(D)); });
+  m.def("gemm_uses_pair(int M, int N, int split_k) -> bool", [](int64_t M, int64_t N, int64_t split_k) {
+    b200::GemmArgs a{};
+    a.M = static_cast<int>(M);
+    a.N = static_cast<int>(N);
+    a.split_k = static_cast<int>(split_k);
+    return b200::gemm_pair_wanted(a);
+  });
   b200_register_extra(m);
   b200_register_runtime(m);
 }

@@ -17,6 +17,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include "tma_host.h"
 
 namespace b200 {
@@ -265,130 +266,7 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ T
         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
         tmem_ld_wait();
         if (!row_ok || !has_k) continue;
-        float f[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * args.alpha;
-        const bool full = (col0 + 32 <= args.N);
-        if (args.bias != nullptr && ks == 0) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (full || col0 + j < args.N) f[j] += __bfloat162float(args.bias[col0 + j]);
-        }
-        if (args.epilogue == kEpiGelu) {
-          __nv_bfloat16* aux = args.aux_out + static_cast<int64_t>(row) * args.ldaux + col0;
-          if (full && (args.ldaux & 7) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 pk = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
-                                    pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
-              *reinterpret_cast<uint4*>(aux + j) = pk;
-            }
-          } else {
-            {
-_Pragma("unroll") for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) aux[j] = __float2bfloat16(f[j]);
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = gelu_tanh(__bfloat162float(__float2bfloat16(f[j])));
-        } else if (args.epilogue == kEpiGeluGrad) {
-          const __nv_bfloat16* aux = args.aux_in + static_cast<int64_t>(row) * args.ldaux + col0;
-          if (full && (args.ldaux & 7) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 pk = *reinterpret_cast<const uint4*>(aux + j);
-              float2 a0 = unpack_bf16x2(pk.x), a1 = unpack_bf16x2(pk.y), a2 = unpack_bf16x2(pk.z),
-                     a3 = unpack_bf16x2(pk.w);
-              f[j] *= gelu_tanh_grad(a0.x);
-              f[j + 1] *= gelu_tanh_grad(a0.y);
-              f[j + 2] *= gelu_tanh_grad(a1.x);
-              f[j + 3] *= gelu_tanh_grad(a1.y);
-              f[j + 4] *= gelu_tanh_grad(a2.x);
-              f[j + 5] *= gelu_tanh_grad(a2.y);
-              f[j + 6] *= gelu_tanh_grad(a3.x);
-              f[j + 7] *= gelu_tanh_grad(a3.y);
-            }
-          } else {
-            {
-_Pragma("unroll") for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) f[j] *= gelu_tanh_grad(__bfloat162float(aux[j]));
-            }
-          }
-        }
-        if (args.residual != nullptr && ks == 0) {
-          const __nv_bfloat16* res = args.residual + static_cast<int64_t>(row) * args.ldr + col0;
-          if (full && (args.ldr & 7) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 pk = *reinterpret_cast<const uint4*>(res + j);
-              float2 a0 = unpack_bf16x2(pk.x), a1 = unpack_bf16x2(pk.y), a2 = unpack_bf16x2(pk.z),
-                     a3 = unpack_bf16x2(pk.w);
-              f[j] += a0.x;
-              f[j + 1] += a0.y;
-              f[j + 2] += a1.x;
-              f[j + 3] += a1.y;
-              f[j + 4] += a2.x;
-              f[j + 5] += a2.y;
-              f[j + 6] += a3.x;
-              f[j + 7] += a3.y;
-            }
-          } else {
-            {
-_Pragma("unroll") for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) f[j] += __bfloat162float(res[j]);
-            }
-          }
-        }
-        if (args.out_mode == kOutBf16) {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(args.out) + static_cast<int64_t>(row) * args.ldo + col0;
-          if (full && (args.ldo & 7) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 pk = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
-                                    pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
-              *reinterpret_cast<uint4*>(o + j) = pk;
-            }
-          } else {
-            {
-_Pragma("unroll") for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) o[j] = __float2bfloat16(f[j]);
-            }
-          }
-        } else if (args.out_mode == kOutF32) {
-          float* o = static_cast<float*>(args.out) + static_cast<int64_t>(row) * args.ldo + col0;
-          if (full && (args.ldo & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-          } else {
-            {
-_Pragma("unroll") for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) o[j] = f[j];
-            }
-          }
-        } else {
-          float* o;
-          if (args.out_mode == kOutBf16PeerRed) {
-            const int peer = row / args.rows_per_peer;
-            o = args.peer_out[peer] + static_cast<int64_t>(row - peer * args.rows_per_peer) * args.ldo + col0;
-          } else {
-            o = static_cast<float*>(args.out) + static_cast<int64_t>(row) * args.ldo + col0;
-          }
-          if (full && (args.ldo & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              // vectorised fp32 reduction; also valid on peer-mapped (NVLink) addresses
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(f[j]), "f"(f[j + 1]),
-                           "f"(f[j + 2]), "f"(f[j + 3])
-                           : "memory");
-            }
-          } else {
-            {
-_Pragma("unroll") for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) atomicAdd(o + j, f[j]);
-            }
-          }
-        }
+        gemm_epilogue_chunk(args, v, row, col0, ks);
       }
       tc_fence_before();
       __syncwarp();
@@ -499,6 +377,7 @@ int gemm_sm_count() {
 
 cudaError_t launch_gemm_bf16(const __nv_bfloat16* A, int64_t lda, int a_major, const __nv_bfloat16* B, int64_t ldb,
                              int b_major, const GemmArgs& args, cudaStream_t stream) {
+  if (gemm_pair_wanted(args)) return launch_gemm_bf16_pair(A, lda, a_major, B, ldb, b_major, args, stream);
   const __nv_bfloat16* srcs[1] = {A};
   return launch_common(srcs, 1, 0, 0, lda, a_major, B, ldb, b_major, args, stream);
 }

@@ -66,6 +66,13 @@ cudaError_t launch_gemm_bf16_sharded_b(const __nv_bfloat16* A, int64_t lda, cons
                                        int b_n_src, int b_first_src, int64_t ldb, const GemmArgs& args,
                                        cudaStream_t stream);
 
+// CTA-pair variant (gemm_pair_sm100.cu): 256 x 256 tiles computed by two CTAs of a cluster with
+// tcgen05.mma.cta_group::2. launch_gemm_bf16 forwards to it when gemm_pair_wanted() says so
+// (environment B200_GEMM_PAIR: 0 never, 1 whenever M, N >= 256, unset: when the 256 x 256 tiles occupy at least 3/4 of the CTA pairs).
+cudaError_t launch_gemm_bf16_pair(const __nv_bfloat16* A, int64_t lda, int a_major, const __nv_bfloat16* B, int64_t ldb,
+                                  int b_major, const GemmArgs& args, cudaStream_t stream);
+bool gemm_pair_wanted(const GemmArgs& args);
+
 int gemm_sm_count();
 
 }  // namespace b200

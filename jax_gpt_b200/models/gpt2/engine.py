@@ -228,13 +228,20 @@ class GPT2TrainEngine:
 
         def split_for(out_rows: int, out_cols: int) -> int:
             """Split-K factor of a weight-gradient GEMM (K = tokens): the number of (tile, split) work items should
-            fill whole waves of the persistent kernel's CTAs; every split keeps at least 1024 tokens."""
-            tiles = ((out_rows + 127) // 128) * ((out_cols + 255) // 256)
+            fill whole waves of the persistent kernel's CTAs (128 x 256 tiles on every SM) or CTA pairs (256 x 256
+            tiles on every two SMs, whichever the launcher picks for that count); every split keeps at least
+            1024 tokens."""
+            tiles1 = ((out_rows + 127) // 128) * ((out_cols + 255) // 256)
+            tiles2 = ((out_rows + 255) // 256) * ((out_cols + 255) // 256)
+            uses_pair = _ext.ops().gemm_uses_pair
             best, best_eff = 1, 0.0
             lo = max(1, min(4, M // 4096))
             for sp in range(lo, max(lo, min(16, M // 1024)) + 1):
-                items = tiles * sp
-                eff = items / (-(-items // sms) * sms)
+                if uses_pair(out_rows, out_cols, sp):
+                    items, units = tiles2 * sp, sms // 2
+                else:
+                    items, units = tiles1 * sp, sms
+                eff = items / (-(-items // units) * units)
                 if eff > best_eff + 0.02:
                     best, best_eff = sp, eff
             return best
