@@ -41,7 +41,8 @@ constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BNH * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * BN;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kEpiBytes = 8 * kEpiStageBytesPerWarp;  // store staging of the eight epilogue warps
+constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
 constexpr int kNumThreads = 320;
 constexpr int kBand = 8;   // 256-row blocks per band of the tile order
 
@@ -119,7 +120,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                       const __grid_constant__ GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + kStages * kStageBytes);
+  uint8_t* epi_stage = smem + kStages * kStageBytes;
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(epi_stage + kEpiBytes);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -296,20 +298,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         break;
       }
       tc_fence_after();
-      const int row = m_blk * 2 * BM + static_cast<int>(rank) * BM + q * 32 + lane;
-      const bool row_ok = row < args.M;
-      const int n0 = n_blk * BN;
       const bool has_k = ks * kb_per_split < total_kb;
-#pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= args.N) break;  // uniform across the warp
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
-        tmem_ld_wait();
-        if (!row_ok || !has_k) continue;
-        gemm_epilogue_chunk(args, v, row, col0, ks);
-      }
+      gemm_epilogue_columns(args, tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16),
+                            epi_stage + (warp - 2) * kEpiStageBytesPerWarp,
+                            m_blk * 2 * BM + static_cast<int>(rank) * BM + q * 32, n_blk * BN, half * (BN / 2),
+                            (half + 1) * (BN / 2), lane, ks, has_k);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(empty_leader + acc * 8);

@@ -50,7 +50,8 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiBytes = 8 * kEpiStageBytesPerWarp;  // store staging of the eight epilogue warps
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct Barriers {
@@ -70,7 +71,8 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ T
   extern __shared__ uint8_t smem_raw[];
   // 128B swizzle needs the tile bases on 1024-byte boundaries.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::kStages * C::kStageBytes);
+  uint8_t* epi_stage = smem + C::kStages * C::kStageBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(epi_stage + C::kEpiBytes);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -253,21 +255,11 @@ gemm_bf16_kernel(const __grid_constant__ TmaSet tma_a, const __grid_constant__ T
         break;
       }
       tc_fence_after();
-      const int row = m_blk * BM + q * 32 + lane;
-      const bool row_ok = row < args.M;
-      const int n0 = n_blk * BN;
       // Empty K range (possible only for trailing splits): nothing was accumulated.
       const bool has_k = ks * kb_per_split < total_kb;
-#pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= args.N) break;  // uniform across the warp
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
-        tmem_ld_wait();
-        if (!row_ok || !has_k) continue;
-        gemm_epilogue_chunk(args, v, row, col0, ks);
-      }
+      gemm_epilogue_columns(args, tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16),
+                            epi_stage + (warp - 2) * kEpiStageBytesPerWarp, m_blk * BM + q * 32, n_blk * BN,
+                            half * (BN / 2), (half + 1) * (BN / 2), lane, ks, has_k);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
