@@ -131,7 +131,8 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
 // rows a block visits and flushed once with fp32 atomics. `dres` (optional) is added to dx,
 // which folds the residual-branch gradient into the same pass.
 template <int NV, int WPR, int MODE>
-__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__((4 / WPR > 0 ? 4 / WPR : 1) * WPR * 32, NV <= 3 ? 4 : 1)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
                                 __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int M, int D) {
@@ -153,12 +154,15 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
     const float mean = (MODE == 0) ? mean_in[rr] : 0.f;
     const float rstd = rstd_in[rr];
     float xh[NV][8], dg[NV][8];
+    uint4 res_raw[NV];  // the residual-branch gradient is fetched with the other operands, not after the row sums
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int col = (i * WPR * 32 + warp_in_row * 32 + lane) * 8;
+      res_raw[i] = make_uint4(0u, 0u, 0u, 0u);
       if (col < D && active) {
         float xv[8], dv[8], g[8];
+        if (dres != nullptr) res_raw[i] = *reinterpret_cast<const uint4*>(dres + static_cast<int64_t>(rr) * D + col);
         load8(x + static_cast<int64_t>(rr) * D + col, xv);
         load8(dy + static_cast<int64_t>(rr) * D + col, dv);
         load8(gamma + col, g);
@@ -188,10 +192,9 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] = rstd * (dg[i][j] - s1 - xh[i][j] * s2);
           if (dres != nullptr) {
-            float r[8];
-            load8(dres + static_cast<int64_t>(row) * D + col, r);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] += r[j];
+            const float2 a = unpack_bf16x2(res_raw[i].x), b = unpack_bf16x2(res_raw[i].y),
+                         c = unpack_bf16x2(res_raw[i].z), d = unpack_bf16x2(res_raw[i].w);
+            o[0] += a.x; o[1] += a.y; o[2] += b.x; o[3] += b.y; o[4] += c.x; o[5] += c.y; o[6] += d.x; o[7] += d.y;
           }
           store8(dx + static_cast<int64_t>(row) * D + col, o);
         }
@@ -216,16 +219,20 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
 }
 
 // dgamma[c] += sum_r partials[r][0][c]; dbeta[c] += sum_r partials[r][1][c]. Block (32, 32):
-// threadIdx.x walks columns (coalesced), threadIdx.y strides over the partial rows.
+// threadIdx.x walks columns (coalesced), threadIdx.y strides over the partial rows of the block's
+// slice (blockIdx.y of gridDim.y slices; the slices meet in one fp32 atomic per column).
+constexpr int kNormReduceSlices = 8;
 __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partials, int n_rows, int D, int with_beta,
                                        float* __restrict__ dgamma, float* __restrict__ dbeta) {
   __shared__ float red[32][33];
   const int width = with_beta ? 2 * D : D;
   const int c = blockIdx.x * 32 + threadIdx.x;  // column in the concatenated [dgamma | dbeta] row
+  const int per = (n_rows + gridDim.y - 1) / gridDim.y;
+  const int r0 = blockIdx.y * per, r1 = min(n_rows, r0 + per);
   float s = 0.f;
   if (c < width) {
-    const int off = (c < D) ? c : (D + (c - D));
-    for (int r = threadIdx.y; r < n_rows; r += 32) s += partials[static_cast<int64_t>(r) * 2 * D + off];
+#pragma unroll 4
+    for (int r = r0 + threadIdx.y; r < r1; r += 32) s += partials[static_cast<int64_t>(r) * 2 * D + c];
   }
   red[threadIdx.y][threadIdx.x] = s;
   __syncthreads();
@@ -233,8 +240,8 @@ __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partials, int n
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < 32; ++k) t += red[k][threadIdx.x];
-    if (c < D) dgamma[c] += t;
-    else if (dbeta != nullptr) dbeta[c - D] += t;
+    if (c < D) atomicAdd(dgamma + c, t);
+    else if (dbeta != nullptr) atomicAdd(dbeta + (c - D), t);
   }
 }
 
@@ -274,7 +281,7 @@ cudaError_t norm_bwd_dispatch(const __nv_bfloat16* dy, const __nv_bfloat16* x, c
     cudaError_t e_ = cudaGetLastError();                                                                   \
     if (e_ != cudaSuccess) return e_;                                                                      \
     const int width_ = (MODE == 0) ? 2 * D : D;                                                            \
-    norm_bwd_reduce_kernel<<<(width_ + 31) / 32, dim3(32, 32), 0, st>>>(partials, grid * ROWS, D,          \
+    norm_bwd_reduce_kernel<<<dim3((width_ + 31) / 32, kNormReduceSlices), dim3(32, 32), 0, st>>>(partials, grid * ROWS, D, \
                                                                        MODE == 0 ? 1 : 0, dgamma, dbeta); \
     return cudaGetLastError();                                                                             \
   }

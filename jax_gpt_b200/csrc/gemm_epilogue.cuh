@@ -298,6 +298,46 @@ __device__ __forceinline__ void gemm_epilogue_group64(const GemmArgs& args, uint
   stage_store(static_cast<__nv_bfloat16*>(args.out), args.ldo);
 }
 
+// fp32 outputs (plain store or reduction into a local buffer), 32 rows x 32 columns per call: the same staging
+// tile holds 128-byte rows of four-float chunks, so that every store / red.add instruction covers four whole lines.
+__device__ __forceinline__ bool gemm_epilogue_staged_f32_ok(const GemmArgs& args, int col0, int ks) {
+  if (args.out_mode != kOutF32 && args.out_mode != kOutF32Atomic) return false;
+  if (col0 + 32 > args.N || (args.ldo & 3) != 0 || args.epilogue != kEpiNone) return false;
+  if (ks == 0 && (args.bias != nullptr || args.residual != nullptr)) return false;
+  return true;
+}
+__device__ __forceinline__ void gemm_epilogue_group32_f32(const GemmArgs& args, uint32_t tmem_addr, uint8_t* stage,
+                                                          int row0, int col0, int lane) {
+  const int tr = lane >> 3, tc = lane & 7;
+  auto chunk_ptr = [&](int r, int c) { return reinterpret_cast<float4*>(stage + r * 128 + ((c ^ (r & 7)) << 4)); };
+  uint32_t v[32];
+  tmem_ld_32x32(tmem_addr, v);
+  tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *chunk_ptr(lane, c) = make_float4(__uint_as_float(v[4 * c]) * args.alpha, __uint_as_float(v[4 * c + 1]) * args.alpha,
+                                      __uint_as_float(v[4 * c + 2]) * args.alpha,
+                                      __uint_as_float(v[4 * c + 3]) * args.alpha);
+  __syncwarp();
+  float* out = static_cast<float*>(args.out);
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + tr;
+    if (row0 + r < args.M) {
+      const float4 val = *chunk_ptr(r, tc);
+      float* o = out + static_cast<int64_t>(row0 + r) * args.ldo + col0 + tc * 4;
+      if (args.out_mode == kOutF32) {
+        *reinterpret_cast<float4*>(o) = val;
+      } else {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(val.x), "f"(val.y), "f"(val.z),
+                     "f"(val.w)
+                     : "memory");
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // The columns [col_begin, col_end) of one accumulator (multiples of 64 within the tile) for one epilogue warp:
 // staged 64-column groups where possible, 32-column chunks otherwise.
 //   tmem_acc: TMEM address of the accumulator's column 0 in the warp's lane quarter; n0: the tile's first column
@@ -317,6 +357,10 @@ __device__ __forceinline__ void gemm_epilogue_columns(const GemmArgs& args, uint
 #pragma unroll 1
     for (int h = 0; h < 2; ++h) {
       if (col0 + h * 32 >= args.N) break;
+      if (gemm_epilogue_staged_f32_ok(args, col0 + h * 32, ks)) {
+        gemm_epilogue_group32_f32(args, tmem_acc + cc + h * 32, stage, row0, col0 + h * 32, lane);
+        continue;
+      }
       uint32_t v[32];
       tmem_ld_32x32(tmem_acc + cc + h * 32, v);
       tmem_ld_wait();
