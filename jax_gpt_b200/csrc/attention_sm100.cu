@@ -93,8 +93,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   FwdBars* bars = reinterpret_cast<FwdBars*>(smem + C::kOffBar);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_blk = gridDim.x - 1 - blockIdx.x;  // longest rows first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // The query block is the slowest grid dimension and runs backwards: with a causal mask the CTAs with the most
+  // key tiles are dispatched first over all heads and sequences, the short ones fill the tail of the launch.
+  const int q_blk = gridDim.z - 1 - blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int hkv = h / (a.H / a.Hkv);
   const int n_kv_all = (a.T + 127) / 128;
   const int n_kv = a.causal ? min(q_blk + 1, n_kv_all) : n_kv_all;
@@ -132,7 +134,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const int s = j % C::kStages;
         const uint32_t ph = (j / C::kStages) & 1;
         if (!mbar_wait(&bars->kv_empty[s], ph ^ 1, abort_flag)) {
-          report_status(a.status, kWaitEmptyTimeout, 100, blockIdx.x, j);
+          report_status(a.status, kWaitEmptyTimeout, 100, blockIdx.z, j);
           break;
         }
         uint8_t* sK = smem + C::kOffK + s * C::kStageBytes;
@@ -145,12 +147,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     constexpr uint32_t idesc_s = make_idesc(128, 128, 0, 0, 1);
     constexpr uint32_t idesc_o = make_idesc(128, DV, 0, 1, 1);
     bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
-    if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 101, blockIdx.x, 0);
+    if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 101, blockIdx.z, 0);
     for (int j = 0; j < n_kv && ok; ++j) {
       const int s = j % C::kStages;
       const uint32_t ph = (j / C::kStages) & 1;
       if (!mbar_wait(&bars->kv_full[s], ph, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitFullTimeout, 102, blockIdx.x, j);
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 102, blockIdx.z, j);
         break;
       }
       tc_fence_after();
@@ -167,7 +169,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       __syncwarp();
       if (!mbar_wait(&bars->p_ready, j & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 103, blockIdx.x, j);
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 103, blockIdx.z, j);
         break;
       }
       tc_fence_after();
@@ -203,7 +205,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait(&bars->s_full, j & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 104, blockIdx.x, j);
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 104, blockIdx.z, j);
         ok = false;
         break;
       }
@@ -231,7 +233,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       xchg[half * 128 + r] = mine;
       mbar_arrive(&bars->x_ready);
       if (!mbar_wait(&bars->x_ready, j & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 106, blockIdx.x, j);
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 106, blockIdx.z, j);
         ok = false;
         break;
       }
@@ -266,7 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(&bars->p_ready);
       if (!mbar_wait(&bars->o_full, j & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 105, blockIdx.x, j);
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 105, blockIdx.z, j);
         ok = false;
         break;
       }
@@ -367,8 +369,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   volatile int* abort_flag = &bars->abort_flag;
   float* stats = reinterpret_cast<float*>(smem + C::kOffStats);  // [buf][0: lse, 1: delta][128]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jb = blockIdx.x;  // key block
-  const int hkv = blockIdx.y, b = blockIdx.z;
+  const int jb = blockIdx.z;  // key block, slowest grid dimension: block 0 (seen by every query block) goes first
+  const int hkv = blockIdx.x, b = blockIdx.y;
   const int group = a.H / a.Hkv;
   const int n_q = (a.T + 127) / 128;
   const int i0 = a.causal ? jb : 0;
@@ -408,7 +410,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const int s = it % C::kStages;
         const uint32_t ph = (it / C::kStages) & 1;
         if (!mbar_wait(&bars->qdo_empty[s], ph ^ 1, abort_flag)) {
-          report_status(a.status, kWaitEmptyTimeout, 200, blockIdx.x, it);
+          report_status(a.status, kWaitEmptyTimeout, 200, blockIdx.z, it);
           break;
         }
         const int hq = hkv * group + it / nqi;
@@ -424,7 +426,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     constexpr uint32_t idesc_kn = make_idesc(128, D, 0, 1, 1);    // A K-major, B MN-major
     constexpr uint32_t idesc_nn = make_idesc(128, D, 1, 1, 1);    // A MN-major, B MN-major
     bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
-    if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 201, blockIdx.x, 0);
+    if (!ok && lane == 0) report_status(a.status, kWaitFullTimeout, 201, blockIdx.z, 0);
     const uint32_t aK = smem_u32(smem + C::kOffK), aV = smem_u32(smem + C::kOffV);
     const uint32_t aPT = smem_u32(smem + C::kOffPT), aDST = smem_u32(smem + C::kOffDST);
     // S^T = K Q^T and dP^T = V dO^T of iteration `it` (its Q / dO stage must have landed).
@@ -432,7 +434,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const int s = it % C::kStages;
       const uint32_t ph = (it / C::kStages) & 1;
       if (!mbar_wait(&bars->qdo_full[s], ph, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitFullTimeout, 202, blockIdx.x, it);
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 202, blockIdx.z, it);
         return false;
       }
       tc_fence_after();
@@ -459,7 +461,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     for (int it = 0; it < n_iters && ok; ++it) {
       const int s = it % C::kStages;
       if (!mbar_wait(&bars->p_ready, it & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 204, blockIdx.x, it);
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 204, blockIdx.z, it);
         break;
       }
       tc_fence_after();
@@ -489,7 +491,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       __syncwarp();
       if (it + 1 < n_iters) {
         if (kAliasDq && !mbar_wait(&bars->dq_read, it & 1, abort_flag)) {
-          if (lane == 0) report_status(a.status, kWaitAttnTimeout, 203, blockIdx.x, it);
+          if (lane == 0) report_status(a.status, kWaitAttnTimeout, 203, blockIdx.z, it);
           break;
         }
         // P^T / dS^T of `it` are only re-written after the compute warps have seen dq_full(it),
@@ -529,7 +531,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       float* st_del = st_lse + 128;
       // bounded rendezvous of the 256 compute threads on the per-query statistics
       if (!mbar_wait(&bars->stats_ready, it & 1, abort_flag) || !mbar_wait(&bars->st_full, it & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 205, blockIdx.x, it);
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 205, blockIdx.z, it);
         ok = false;
         break;
       }
@@ -575,7 +577,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_arrive(&bars->p_ready);
       if (it + 1 < n_iters) stage_stats(it + 1);
       if (!mbar_wait(&bars->dq_full, it & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 206, blockIdx.x, it);
+        if (lane == 0) report_status(a.status, kWaitAttnTimeout, 206, blockIdx.z, it);
         ok = false;
         break;
       }
@@ -705,7 +707,7 @@ cudaError_t fwd_launch(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* 
     configured = true;
   }
   FwdArgs a{s.B, s.T, s.H, s.Hkv, s.scale * kLog2e, s.causal, out, ldo, lse, status};
-  dim3 grid((s.T + 127) / 128, s.H, s.B);
+  dim3 grid(s.H, s.B, (s.T + 127) / 128);
   kernel<<<grid, kThreads, C::kSmem, stream>>>(tq, tk, tv, a);
   return cudaGetLastError();
 }
@@ -737,7 +739,7 @@ cudaError_t bwd_launch(const AttnTensors& t, const AttnShape& s, const __nv_bflo
     configured = true;
   }
   BwdArgs a{s.B, s.T, s.H, s.Hkv, s.scale, s.scale * kLog2e, s.causal, lse, delta, dq_accum, dk, lddk, dv, lddv, status};
-  dim3 grid((s.T + 127) / 128, s.Hkv, s.B);
+  dim3 grid(s.Hkv, s.B, (s.T + 127) / 128);
   kernel<<<grid, kBwdThreads, C::kSmem, stream>>>(tq, tk, tv, tdo, a);
   return cudaGetLastError();
 }
