@@ -337,6 +337,102 @@ __global__ void gdn_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, const 
   *reinterpret_cast<uint4*>(y + (static_cast<int64_t>(b) * T + t) * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+
+// Backward of the depthwise causal FIR + SiLU above. One thread owns eight channels and a strip of kStrip time
+// steps: it walks the strip (plus K-1 steps past its end, for the taps that reach back into it) with the last K
+// inputs and the last K pre-activation gradients in registers, so x and dy are read once and dx written once.
+//   pre[t] = sum_j w[j] x[t-(K-1)+j];  dpre[t] = dy[t] * sigmoid(pre) * (1 + pre * (1 - sigmoid(pre)))
+//   dx[t]  = sum_j w[j] dpre[t+(K-1)-j];  dw[j] += sum_t dpre[t] x[t-(K-1)+j]   (fp32 atomics, one per strip)
+template <int K, int kStrip>
+__global__ void gdn_conv_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                         const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx,
+                                         float* __restrict__ dw, int T, int C) {
+  const int b = blockIdx.z;
+  const int t0 = blockIdx.y * kStrip;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= C || t0 >= T) return;
+  const int t1 = min(T, t0 + kStrip);
+  float wv[8][K], dwa[8][K], xw[8][K], dp[8][K];  // xw / dp: sliding windows, newest in slot K-1
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      wv[i][j] = __bfloat162float(w[(c0 + i) * K + j]);
+      dwa[i][j] = 0.f;
+      xw[i][j] = 0.f;
+      dp[i][j] = 0.f;
+    }
+  auto load8 = [&](const __nv_bfloat16* base, int t, float (&f)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(base + (static_cast<int64_t>(b) * T + t) * C + c0);
+    const float2 a = unpack_bf16x2(u.x), bb = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = bb.x; f[3] = bb.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+  };
+  // inputs before the strip (zeros before the sequence start)
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) {
+    const int tt = t0 - (K - 1) + j;
+    if (tt >= 0) {
+      float f[8];
+      load8(x, tt, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xw[i][j + 1] = f[i];
+    }
+  }
+  const int t_end = min(T, t1 + K - 1);
+  for (int t = t0; t < t1 + K - 1; ++t) {
+    // shift the windows; positions past the end of the sequence contribute zero gradients
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < K - 1; ++j) {
+        xw[i][j] = xw[i][j + 1];
+        dp[i][j] = dp[i][j + 1];
+      }
+    if (t < t_end) {
+      float xv[8], dv[8];
+      load8(x, t, xv);
+      load8(dy, t, dv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        xw[i][K - 1] = xv[i];
+        float pre = 0.f;
+#pragma unroll
+        for (int j = 0; j < K; ++j) pre = fmaf(wv[i][j], xw[i][j], pre);
+        const float sg = 1.f / (1.f + __expf(-pre));
+        const float g = dv[i] * sg * fmaf(pre, 1.f - sg, 1.f);
+        dp[i][K - 1] = g;
+        if (t < t1) {
+#pragma unroll
+          for (int j = 0; j < K; ++j) dwa[i][j] = fmaf(g, xw[i][j], dwa[i][j]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        xw[i][K - 1] = 0.f;
+        dp[i][K - 1] = 0.f;
+      }
+    }
+    const int to = t - (K - 1);  // dx[to] = sum_j w[j] dpre[to + K-1 - j] = sum_j w[j] dp[K-1-j]
+    if (to >= t0) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < K; ++j) acc = fmaf(wv[i][j], dp[i][K - 1 - j], acc);
+        o[i] = acc;
+      }
+      *reinterpret_cast<uint4*>(dx + (static_cast<int64_t>(b) * T + to) * C + c0) =
+          make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) atomicAdd(dw + (c0 + i) * K + j, dwa[i][j]);
+}
+
 }  // namespace
 
 cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
@@ -366,6 +462,16 @@ cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w,
   const int threads = 128;
   const dim3 grid((C / 8 + threads - 1) / threads, T, B);
   gdn_conv_silu_kernel<4><<<grid, threads, 0, stream>>>(x, w, y, state, T, C);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gdn_conv_silu_bwd(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* dy,
+                                     __nv_bfloat16* dx, float* dw, int B, int T, int C, int K, cudaStream_t stream) {
+  if (K != 4 || C % 8 != 0 || B < 1 || T < 1) return cudaErrorInvalidValue;
+  constexpr int kStrip = 32;
+  const int threads = 128;
+  const dim3 grid((C / 8 + threads - 1) / threads, (T + kStrip - 1) / kStrip, B);
+  gdn_conv_silu_bwd_kernel<4, kStrip><<<grid, threads, 0, stream>>>(x, w, dy, dx, dw, T, C);
   return cudaGetLastError();
 }
 

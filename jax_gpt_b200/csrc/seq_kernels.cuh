@@ -72,5 +72,8 @@ cudaError_t launch_gdn_scan_bwd(const __nv_bfloat16* kq, const __nv_bfloat16* in
 // receives the last four raw inputs of every channel.
 cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, float* state, int B,
                                  int T, int C, int K, cudaStream_t stream);
+// Backward of the same op: dx [B, T, C] bf16 is written, dw [C, K] fp32 is ACCUMULATED (atomics).
+cudaError_t launch_gdn_conv_silu_bwd(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* dy,
+                                     __nv_bfloat16* dx, float* dw, int B, int T, int C, int K, cudaStream_t stream);
 
 }  // namespace b200

@@ -39,17 +39,41 @@ def causal_conv1d_update(x_new: torch.Tensor, conv_state: torch.Tensor, weight: 
     return F.silu(y).to(x_new.dtype), state
 
 
+class _ConvSiluFn(torch.autograd.Function):
+    """Depthwise causal FIR (width 4) + SiLU on the CUDA kernels, forward and backward; also returns the final
+    conv state (the last K raw inputs), which carries no gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        from ... import _ext
+        B, T, C = x.shape
+        xc = x.contiguous()
+        wb = weight.to(torch.bfloat16).contiguous()
+        y = torch.empty_like(xc)
+        state = torch.empty(B, C, weight.shape[-1], device=x.device, dtype=torch.float32)
+        _ext.ops().gdn_conv_silu(xc, wb, y, state)
+        ctx.save_for_backward(xc, wb)
+        ctx.w_dtype = weight.dtype
+        state = state.to(x.dtype)
+        ctx.mark_non_differentiable(state)
+        return y, state
+
+    @staticmethod
+    def backward(ctx, dy, _dstate):
+        from ... import _ext
+        xc, wb = ctx.saved_tensors
+        dx = torch.empty_like(xc)
+        dw = torch.zeros(wb.shape, device=xc.device, dtype=torch.float32)
+        _ext.ops().gdn_conv_silu_bwd(xc, wb, dy.to(torch.bfloat16).contiguous(), dx, dw)
+        return dx, dw.to(ctx.w_dtype)
+
+
 def causal_conv1d_prefill(x: torch.Tensor, weight: torch.Tensor):
     """x (B, T, C); depthwise causal FIR of width K then SiLU. Final state = last K raw inputs."""
     B, T, C = x.shape
     K = weight.shape[-1]
-    needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
-    if x.is_cuda and x.dtype == torch.bfloat16 and K == 4 and C % 8 == 0 and not needs_grad:
-        from ... import _ext
-        y = torch.empty_like(x, memory_format=torch.contiguous_format)
-        state = torch.empty(B, C, K, device=x.device, dtype=torch.float32)
-        _ext.ops().gdn_conv_silu(x.contiguous(), weight.to(torch.bfloat16).contiguous(), y, state)
-        return y, state.to(x.dtype)
+    if x.is_cuda and x.dtype == torch.bfloat16 and K == 4 and C % 8 == 0:
+        return _ConvSiluFn.apply(x, weight)
     xc = F.pad(x.transpose(1, 2).float(), (K - 1, 0))
     y = F.conv1d(xc, weight.float()[:, None, :], groups=C)
     state = xc[:, :, -K:] if T >= 1 else xc

@@ -54,6 +54,41 @@ def test_gemm_epilogues(cuda_device):
     assert _rel_err(acc, ref) < 1e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 3072, 256), (4000, 3080, 192), (8192, 768, 320)])
+def test_gemm_pair_kernel_epilogues(cuda_device, M, N, K):
+    """Shapes whose 256 x 256 tiles fill the GPU, so the CTA-pair kernel (cta_group::2) runs: every fused
+    epilogue, ragged M (rows past the end of a pair tile) and an N that is not a multiple of the 64-column
+    staging group, against the fp32 reference."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.ops import gemm as G
+    assert _ext.ops().gemm_uses_pair(M, N, 1) or N < 1024
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device=cuda_device).to(torch.bfloat16)
+    w = (torch.randn(K, N, device=cuda_device) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device=cuda_device).to(torch.bfloat16)
+    res = torch.randn(M, N, device=cuda_device).to(torch.bfloat16)
+    out = G.gemm(a, w, b_mn_major=True, bias=bias, residual=res)
+    assert _rel_err(out, G.gemm_ref(a, w, b_mn_major=True, bias=bias, residual=res)) < 1e-2
+    aux = torch.empty(M, N, device=cuda_device, dtype=torch.bfloat16)
+    aux_ref = torch.empty_like(aux)
+    out = G.gemm(a, w, b_mn_major=True, bias=bias, aux=aux, epilogue=G.EPI_GELU)
+    ref = G.gemm_ref(a, w, b_mn_major=True, bias=bias, aux=aux_ref, epilogue=G.EPI_GELU)
+    assert _rel_err(aux, aux_ref) < 1e-2 and _rel_err(out, ref) < 1e-2
+    out = G.gemm(a, w, b_mn_major=True, aux=aux_ref, epilogue=G.EPI_GELU_GRAD)
+    assert _rel_err(out, G.gemm_ref(a, w, b_mn_major=True, aux=aux_ref, epilogue=G.EPI_GELU_GRAD)) < 1e-2
+    # K-major B (the dgrad layout) and fp32 output
+    wt = w.t().contiguous()
+    out32 = G.gemm(a, wt, out_mode=G.OUT_F32)
+    assert _rel_err(out32, a.float() @ w.float()) < 1e-2
+    # weight-gradient layout with split-K accumulation: [K, N] += a^T @ dy, twice
+    dy = torch.randn(M, N, device=cuda_device).to(torch.bfloat16)
+    a2 = torch.randn(M, 1024, device=cuda_device).to(torch.bfloat16)
+    big = torch.zeros(N, 1024, device=cuda_device)
+    G.gemm(dy, a2, a_mn_major=True, b_mn_major=True, out=big, out_mode=G.OUT_F32_ATOMIC, split_k=4)
+    G.gemm(dy, a2, a_mn_major=True, b_mn_major=True, out=big, out_mode=G.OUT_F32_ATOMIC, split_k=1)
+    assert _rel_err(big, 2 * (dy.float().t() @ a2.float())) < 1e-3
+
+
 def test_linear_autograd(cuda_device):
     from jax_gpt_b200.ops.gemm import linear
     torch.manual_seed(2)

@@ -200,6 +200,26 @@ def test_gdn_conv_silu_kernel(cuda_device):
     assert torch.equal(st1.float().cpu(), D.causal_conv1d_prefill(x[:, :2].float().cpu(), w.float().cpu())[1])
 
 
+@pytest.mark.parametrize("B,T,C", [(2, 70, 1024), (1, 33, 256), (1, 257, 2048)])
+def test_gdn_conv_silu_backward_kernel(cuda_device, B, T, C):
+    """dx and dw of the depthwise causal FIR + SiLU kernel against autograd of the fp32 library path (strips of 32
+    steps: T = 70 / 33 / 257 cover a ragged last strip and taps that cross strip boundaries)."""
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    torch.manual_seed(4)
+    x = torch.randn(B, T, C, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(C, 4, device=cuda_device) * 0.5).requires_grad_()          # fp32 master weight
+    dy = torch.randn(B, T, C, device=cuda_device).to(torch.bfloat16)
+    y, _ = D.causal_conv1d_prefill(x, w)
+    y.backward(dy)
+    xr = x.detach().float().cpu().requires_grad_()
+    wr = w.detach().to(torch.bfloat16).float().cpu().requires_grad_()
+    yr, _ = D.causal_conv1d_prefill(xr, wr)
+    yr.backward(dy.float().cpu())
+    assert w.grad.dtype == torch.float32
+    assert _rel(x.grad.float().cpu(), xr.grad) < 1e-2
+    assert _rel(w.grad.cpu(), wr.grad) < 1e-2
+
+
 @pytest.mark.parametrize("T,with_state", [(64, False), (200, False), (1024, True)])
 def test_gdn_chunk_scan_kernel(cuda_device, T, with_state):
     """Chunked gated delta rule with the tcgen05 inter-chunk scan vs the token-by-token recurrence in fp32."""
