@@ -240,7 +240,9 @@ def forward(params, tokens, config: DeepSeekV3Config, cache: Optional[PagedCache
         cache.commit(seq_ids, T)
     with scope("output_head"):
         x = rms_norm(x, params["final_norm"], c.rms_norm_eps)
-        return linear(x, params["lm_head"])
+        from ...ops.fp8_linear import fp8_training
+        with fp8_training(False):          # the head stays in bf16 also when the layers train in FP8
+            return linear(x, params["lm_head"])
 
 
 def make_cache(config: DeepSeekV3Config, n_pages: int, max_seqs: int, max_pages_per_seq: int, dtype=torch.bfloat16,

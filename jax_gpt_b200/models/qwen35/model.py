@@ -102,7 +102,9 @@ def forward(params, tokens, config: Qwen35Config, cache: Optional[HybridCache] =
         new_conv.append(conv)
     with scope("output_head"):
         x = rms_norm(x, params["final_norm"], c.rms_norm_eps)
-        logits = matmul_maybe_fp8(x, params["lm_head"])
+        from ...ops.fp8_linear import fp8_training
+        with fp8_training(False):          # the head stays in bf16 also when the layers train in FP8
+            logits = matmul_maybe_fp8(x, params["lm_head"])
     new_cache = None
     if cache is not None:
         new_cache = HybridCache(torch.stack(new_M).to(cache.delta_M.dtype),

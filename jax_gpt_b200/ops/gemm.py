@@ -105,7 +105,11 @@ class _LinearFn(torch.autograd.Function):
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x @ w + bias`` with ``w`` of shape (in, out). CUDA bf16 tensors run on the tcgen05 GEMM."""
+    """``x @ w + bias`` with ``w`` of shape (in, out). CUDA bf16 tensors run on the tcgen05 GEMM; inside
+    ``ops.fp8_linear.fp8_training()`` eligible layers run their three GEMMs in block-scaled FP8."""
+    from . import fp8_linear as F8
+    if F8.fp8_enabled() and F8.fp8_eligible(x, w):
+        return F8.fp8_linear(x, w, bias)
     if x.is_cuda and x.dtype == torch.bfloat16:
         return _LinearFn.apply(x, w, bias)
     y = x @ w

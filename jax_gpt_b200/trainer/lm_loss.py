@@ -6,23 +6,29 @@ from __future__ import annotations
 
 import torch
 
+from ..ops.fp8_linear import fp8_training
 from ..ops.misc import cross_entropy_mean
 
 
-def qwen35_loss_fn(config, ep=None):
-    """``ep``: None (all experts local), a process group (all-to-all path) or an ``EPMoERuntime``."""
+def qwen35_loss_fn(config, ep=None, fp8: bool = False):
+    """``ep``: None (all experts local), a process group (all-to-all path) or an ``EPMoERuntime``.
+    ``fp8``: run the dense projections (forward, input and weight gradients) as block-scaled FP8 GEMMs."""
     from ..models.qwen35.model import forward
 
     def loss_fn(tree, tokens, targets):
-        logits, _ = forward(tree, tokens, config, ep_group=ep)
+        with fp8_training(fp8):
+            logits, _ = forward(tree, tokens, config, ep_group=ep)
         return cross_entropy_mean(logits, targets, config.vocab_size)
     return loss_fn
 
 
-def deepseek_v3_loss_fn(config, ep=None):
+def deepseek_v3_loss_fn(config, ep=None, fp8: bool = False):
+    """``fp8``: the DeepSeek-V3 recipe for the dense projections (1x128 activation / 128x128 weight blocks in
+    forward, dgrad and wgrad); the routed experts keep their own kernels."""
     from ..models.deepseek_v3.model import forward
 
     def loss_fn(tree, tokens, targets):
-        logits = forward(tree, tokens, config, ep=ep)
+        with fp8_training(fp8):
+            logits = forward(tree, tokens, config, ep=ep)
         return cross_entropy_mean(logits, targets, config.vocab_size)
     return loss_fn

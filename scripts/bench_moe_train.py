@@ -36,6 +36,7 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=1, help="sequences per rank")
     ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (0 = the family's)")
+    ap.add_argument("--fp8", action="store_true", help="dense projections in block-scaled FP8 (forward, dgrad, wgrad)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args(argv)
@@ -75,7 +76,7 @@ def main(argv=None):
                            cfg.n_routed_experts, cfg.n_experts_per_token, training=True)
         ep, local = EPMoERuntime(layer), is_expert_leaf
         params = shard_experts(params, rank, world)
-    eng = TreeTrainEngine(params, make_loss(cfg, ep), device=device, local=local, lr=1e-4, min_lr=1e-4, warmup_steps=0,
+    eng = TreeTrainEngine(params, make_loss(cfg, ep, fp8=args.fp8), device=device, local=local, lr=1e-4, min_lr=1e-4, warmup_steps=0,
                           dist_optimizer=dist_opt)
     del params
     g = torch.Generator().manual_seed(1 + rank)
@@ -97,7 +98,7 @@ def main(argv=None):
     res = {"model": args.model, "layers": args.layers, "experts": args.experts, "seq_len": args.seq,
            "global_batch": args.batch * world, "n_gpus": world, "params_this_rank_M": eng.n_params() / 1e6,
            "ms_per_step": ms, "tokens_per_s": args.batch * args.seq * world / (ms / 1e3), "loss": float(out["loss"]),
-           "dtype": "bf16", "expert_parallel": ep is not None, "peak_mem_GB": torch.cuda.max_memory_allocated() / 2 ** 30}
+           "dtype": "bf16 + fp8 dense GEMMs" if args.fp8 else "bf16", "expert_parallel": ep is not None, "peak_mem_GB": torch.cuda.max_memory_allocated() / 2 ** 30}
     if rank == 0:
         print(json.dumps(res))
     if world > 1:

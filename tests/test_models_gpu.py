@@ -119,6 +119,31 @@ def test_deepseek_v3_bf16_training_steps_on_gpu(cuda_device):
     assert losses[-1] < losses[0] - 0.5, losses
 
 
+def test_deepseek_v3_fp8_training_steps_on_gpu(cuda_device):
+    """The same run with the dense projections in block-scaled FP8 (forward, dgrad and wgrad on the
+    hardware-scaled GEMM): starts at ln(vocab), learns, and ends close to the bf16 run."""
+    import math
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
+    from jax_gpt_b200.models.deepseek_v3.model import init_params
+    from jax_gpt_b200.trainer.lm_loss import deepseek_v3_loss_fn
+    from jax_gpt_b200.trainer.tree_engine import TreeTrainEngine
+    cfg = DeepSeekV3Config.tiny().replace(d_model=256, vocab_size=1024, n_heads=4, qk_nope_head_dim=128,
+                                          qk_rope_head_dim=64, v_head_dim=128, q_lora_rank=128, kv_lora_rank=128,
+                                          moe_intermediate_size=128, dense_intermediate_size=512)
+    tokens, targets = _lm_batch(cfg.vocab_size, 2, 128, cuda_device)
+    finals = {}
+    for fp8 in (False, True):
+        eng = TreeTrainEngine(init_params(cfg, 0, torch.float32), deepseek_v3_loss_fn(cfg, fp8=fp8), device=cuda_device,
+                              lr=2e-3, min_lr=2e-3, warmup_steps=0)
+        losses = [float(eng.train_step(tokens, targets)["loss"]) for _ in range(8)]
+        _ext.check_status(cuda_device)
+        assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5, losses
+        assert losses[-1] < losses[0] - 0.5, losses
+        finals[fp8] = losses[-1]
+    assert abs(finals[True] - finals[False]) < 0.3, finals
+
+
 def test_deepseek_v3_paged_decode_kernel_matches_prefill(cuda_device):
     """Decode steps through the paged-MLA tcgen05 kernel (latent 512 + 64, 64-token pages) reproduce the
     logits of a full prefill over the same tokens."""
