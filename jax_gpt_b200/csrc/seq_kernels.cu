@@ -314,6 +314,90 @@ __global__ void fp8_quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint
   if (lane == 0) scales[row * kb + blk] = sc;
 }
 
+// Block-scaled e4m3 quantisation for the hardware-scaled GEMM, one CTA (256 threads) per 128 x 128 tile of x
+// [R, C] bf16, optionally TRANSPOSING: the output is q [R, C] (contraction along C) or q^T [C, R] (contraction
+// along R) with one power-of-two scale per 1 x 128 block of an output row (kBlock = false) or per 128 x 128 tile
+// (kBlock = true). The scales are written twice: as fp32 ([rows, Kc/128] or [rows/128, Kc/128]) and as exponent
+// bytes in the packed layout the GEMM copies into tensor memory: [rows/128, Kc/128, 512] bytes, the word at byte
+// (r % 32) * 16 + ((r % 128) / 32) * 4 of a chunk holding the exponent of output row r four times.
+// The tile passes through shared memory, so both the reads of x and the writes of q move whole lines also
+// when transposing (the weight-gradient operands of an FP8 layer are x^T and dy^T).
+template <bool kTranspose, bool kBlock>
+__global__ void __launch_bounds__(256)
+fp8_quant_mx_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scales,
+                    uint8_t* __restrict__ sf_packed, int R, int C) {
+  constexpr int kLd = 136;  // padded row of the staged tile, in elements (272 bytes: keeps 16-byte alignment)
+  __shared__ __align__(16) __nv_bfloat16 tile[128 * kLd];
+  __shared__ float red[8];
+  const int cb = C / 128;
+  const int tr = blockIdx.x / cb, tc = blockIdx.x % cb;
+  const int r0 = tr * 128, c0 = tc * 128;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = it * 256 + threadIdx.x;
+    const int row = idx >> 4, cv = idx & 15;
+    const uint4 v = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(r0 + row) * C + c0 + cv * 8);
+    *reinterpret_cast<uint4*>(tile + row * kLd + cv * 8) = v;
+  }
+  __syncthreads();
+  const int line = threadIdx.x >> 1, half = threadIdx.x & 1;  // output row inside the tile, which 64 of its elements
+  float f[64];
+  float amax = 0.f;
+  if (!kTranspose) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 v = *reinterpret_cast<const uint4*>(tile + line * kLd + half * 64 + i * 8);
+      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+      f[8 * i] = a.x; f[8 * i + 1] = a.y; f[8 * i + 2] = b.x; f[8 * i + 3] = b.y;
+      f[8 * i + 4] = c.x; f[8 * i + 5] = c.y; f[8 * i + 6] = d.x; f[8 * i + 7] = d.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) f[i] = __bfloat162float(tile[(half * 64 + i) * kLd + line]);
+  }
+#pragma unroll
+  for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(f[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // the two halves of a line sit in adjacent lanes
+  if (kBlock) {
+    amax = warp_max_f(amax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  }
+  const float sc = pow2_ceil(fmaxf(amax, 1e-12f) / 448.f);
+  const float inv = 1.f / sc;
+  // output geometry: row of q this line becomes, and the 128-wide block along the contraction dimension
+  const int out_row = kTranspose ? (c0 + line) : (r0 + line);
+  const int kblk = kTranspose ? tr : tc;
+  const int64_t ldq = kTranspose ? R : C;
+  const int n_kblk = static_cast<int>(ldq / 128);
+  uint8_t* qp = q + static_cast<int64_t>(out_row) * ldq + kblk * 128 + half * 64;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float* g = f + i * 16 + j * 4;
+      w[j] = to_e4m3(g[0] * inv) | (to_e4m3(g[1] * inv) << 8) | (to_e4m3(g[2] * inv) << 16) |
+             (static_cast<uint32_t>(to_e4m3(g[3] * inv)) << 24);
+    }
+    *reinterpret_cast<uint4*>(qp + i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  if (half == 0) {
+    int e;
+    frexpf(sc, &e);                                   // sc = 0.5 * 2^e exactly
+    const uint32_t byte = static_cast<uint32_t>(min(254, max(0, e - 1 + 127)));
+    uint8_t* chunk = sf_packed + (static_cast<int64_t>(out_row >> 7) * n_kblk + kblk) * 512;
+    *reinterpret_cast<uint32_t*>(chunk + (out_row & 31) * 16 + ((out_row & 127) >> 5) * 4) = byte * 0x01010101u;
+    if (scales != nullptr) {
+      if (!kBlock) scales[static_cast<int64_t>(out_row) * n_kblk + kblk] = sc;
+      else if (line == 0) scales[static_cast<int64_t>(out_row >> 7) * n_kblk + kblk] = sc;
+    }
+  }
+}
+
 // One block of 256 threads per 128 x 128 tile.
 __global__ void fp8_quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ q,
                                          float* __restrict__ scales, int R, int C, int pow2) {
@@ -494,6 +578,20 @@ cudaError_t launch_fp8_quant_128x128(const __nv_bfloat16* w, uint8_t* q, float* 
                                      cudaStream_t st) {
   if (R % 128 != 0 || C % 128 != 0) return cudaErrorInvalidValue;
   fp8_quant_128x128_kernel<<<(R / 128) * (C / 128), 256, 0, st>>>(w, q, scales, R, C, pow2);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fp8_quant_mx(const __nv_bfloat16* x, uint8_t* q, float* scales, uint8_t* sf_packed, int R, int C,
+                                int transpose, int block, cudaStream_t st) {
+  if (R % 128 != 0 || C % 128 != 0 || R <= 0 || C <= 0) return cudaErrorInvalidValue;
+  const int grid = (R / 128) * (C / 128);
+  if (transpose) {
+    if (block) fp8_quant_mx_kernel<true, true><<<grid, 256, 0, st>>>(x, q, scales, sf_packed, R, C);
+    else fp8_quant_mx_kernel<true, false><<<grid, 256, 0, st>>>(x, q, scales, sf_packed, R, C);
+  } else {
+    if (block) fp8_quant_mx_kernel<false, true><<<grid, 256, 0, st>>>(x, q, scales, sf_packed, R, C);
+    else fp8_quant_mx_kernel<false, false><<<grid, 256, 0, st>>>(x, q, scales, sf_packed, R, C);
+  }
   return cudaGetLastError();
 }
 

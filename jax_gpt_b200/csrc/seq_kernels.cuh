@@ -30,6 +30,13 @@ cudaError_t launch_fp8_quant_1x128(const __nv_bfloat16* x, uint8_t* q, float* sc
 cudaError_t launch_fp8_quant_128x128(const __nv_bfloat16* w, uint8_t* q, float* scales, int R, int C, int pow2,
                                      cudaStream_t st);
 
+// Quantisation for the hardware-scaled GEMM in one pass: x [R, C] bf16 (R, C multiples of 128) -> q [R, C], or with
+// `transpose` q^T [C, R]; power-of-two scales per 1 x 128 block of an output row (`block` = 0) or per 128 x 128
+// tile (`block` = 1), written as fp32 (`scales`, may be null) and as packed exponent bytes
+// [rows/128, contraction/128, 512] (`sf_packed`, the operand layout of launch_gemm_mxfp8).
+cudaError_t launch_fp8_quant_mx(const __nv_bfloat16* x, uint8_t* q, float* scales, uint8_t* sf_packed, int R, int C,
+                                int transpose, int block, cudaStream_t st);
+
 // One decode step of a Gated-DeltaNet layer for B sequences, fused: conv-window update + depthwise
 // conv + SiLU, gates, L2-normalised q/k, state decay + delta-rule update, read-out, gated RMSNorm.
 //  mixed [B, 2*Kd + Vd] bf16 (projected q|k|v before the conv), z [B, Vd], bproj / aproj [B, Hv] bf16,

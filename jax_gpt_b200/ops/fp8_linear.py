@@ -7,9 +7,10 @@ everything between the GEMMs stay in bf16 / fp32.
     dgrad     dx = dy @ W^T      dy [M, out]  1x128 blocks along out    W   [in, out] 128x128 blocks (same blocks)
     wgrad     dW^T = dy^T @ x    dy^T [out, M] 1x128 blocks along M     x^T [in, M]   128x128 blocks
 
-The weight is quantised once per step (its [in, out] block scales serve the forward through a transposed copy of
-the e4m3 bytes); activations and gradients are quantised per call, the weight-gradient operands after a
-transposing copy so that the token dimension is the contiguous one. The weight gradient leaves the GEMM in bf16.
+Every operand is produced by ONE kernel (csrc/seq_kernels.cu:fp8_quant_mx_kernel) that reads a 128 x 128 bf16 tile,
+optionally transposes it through shared memory (the weight-gradient operands need the token dimension
+contiguous), quantises it and writes the e4m3 bytes plus the exponent bytes in the packed layout the GEMM copies
+into tensor memory. The weight gradient leaves the GEMM in bf16.
 
 Use: ``with fp8_training(): loss = loss_fn(...)`` makes ``ops.gemm.linear`` take this path for every weight whose
 dimensions and token count are multiples of 128; other calls keep the bf16 kernel.
@@ -24,7 +25,7 @@ from typing import Optional
 
 import torch
 
-from .rope import fp8_quant_1x128, fp8_quant_128x128, mxfp8_gemm
+from .rope import fp8_gemm_ref, fp8_quant_mx, mxfp8_gemm_packed
 
 _STATE = {"on": False}
 
@@ -51,9 +52,18 @@ def fp8_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
     return tokens % 128 == 0 and tokens > 0 and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0
 
 
-def _t8(q: torch.Tensor) -> torch.Tensor:
-    """Transposed contiguous copy of an e4m3 matrix (moved as bytes)."""
-    return q.view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn)
+def _quant(x: torch.Tensor, transpose: bool, block: bool):
+    """(q, scales in the form :func:`_mm` wants on x's device): one kernel on CUDA (quantise, transpose and pack
+    the exponent bytes), the reference functions elsewhere."""
+    q, sf, sc = fp8_quant_mx(x, transpose, block)
+    return (q, sf) if x.is_cuda else (q, sc)
+
+
+def _mm(a, b):
+    """a = (q [M,K], scales 1x128), b = (q [N,K], scales 128x128) -> bf16 [M,N]."""
+    if a[0].is_cuda:
+        return mxfp8_gemm_packed(a[0], a[1], b[0], b[1])
+    return fp8_gemm_ref(a[0], a[1], b[0], b[1]).to(torch.bfloat16)
 
 
 class _Fp8LinearFn(torch.autograd.Function):
@@ -61,29 +71,27 @@ class _Fp8LinearFn(torch.autograd.Function):
     def forward(ctx, x, w, bias):
         K, N = w.shape
         x2 = x.reshape(-1, K).to(torch.bfloat16).contiguous()
-        xq, xs = fp8_quant_1x128(x2, True)
-        wq, ws = fp8_quant_128x128(w.detach().to(torch.bfloat16).contiguous(), True)     # blocks of W [in, out]
-        y = mxfp8_gemm(xq, xs, _t8(wq), ws.t().contiguous())
+        wb = w.detach().to(torch.bfloat16).contiguous()
+        y = _mm(_quant(x2, False, False), _quant(wb, True, True))            # x [M,in] x (W^T [out,in])^T
         if bias is not None:
             y = y + bias.to(y.dtype)
-        ctx.save_for_backward(x2, wq, ws)
+        ctx.save_for_backward(x2, wb)
         ctx.has_bias = bias is not None
         ctx.xshape, ctx.x_dtype, ctx.w_dtype = x.shape, x.dtype, w.dtype
         return y.to(x.dtype).reshape(*x.shape[:-1], N)
 
     @staticmethod
     def backward(ctx, dy):
-        x2, wq, ws = ctx.saved_tensors
-        N = wq.shape[1]
+        x2, wb = ctx.saved_tensors
+        N = wb.shape[1]
         dy2 = dy.reshape(-1, N).to(torch.bfloat16).contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dyq, dys = fp8_quant_1x128(dy2, True)
-            dx = mxfp8_gemm(dyq, dys, wq, ws).to(ctx.x_dtype).reshape(ctx.xshape)       # [M, out] x [in, out]^T
+            dx = _mm(_quant(dy2, False, False), _quant(wb, False, True))       # dy [M,out] x (W [in,out])^T
+            dx = dx.to(ctx.x_dtype).reshape(ctx.xshape)
         if ctx.needs_input_grad[1]:
-            dytq, dyts = fp8_quant_1x128(dy2.t().contiguous(), True)                     # [out, M]
-            xtq, xts = fp8_quant_128x128(x2.t().contiguous(), True)                      # [in, M]
-            dw = mxfp8_gemm(dytq, dyts, xtq, xts).t().to(ctx.w_dtype)                    # [out, in] -> (in, out)
+            dwt = _mm(_quant(dy2, True, False), _quant(x2, True, True))        # dy^T [out,M] x (x^T [in,M])^T
+            dw = dwt.t().to(ctx.w_dtype)                                       # [out,in] -> (in,out)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(ctx.w_dtype)
         return dx, dw, db

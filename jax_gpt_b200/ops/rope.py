@@ -161,6 +161,31 @@ def mxfp8_gemm(a_q, a_s, b_q, b_s):
     return out
 
 
+def fp8_quant_mx(x: torch.Tensor, transpose: bool = False, block: bool = False):
+    """One-pass quantisation for the hardware-scaled GEMM. x (R, C) bf16, R and C multiples of 128. Returns
+    ``(q, sf_packed, scales)``: q is x (or x^T when ``transpose``) in e4m3 with power-of-two scales per 1x128
+    block of an output row (``block=False``) or per 128x128 tile; ``sf_packed`` the exponent bytes in the
+    operand layout of :func:`mxfp8_gemm_packed`; ``scales`` the same scales in fp32."""
+    R, C = x.shape
+    rows, kc = (C, R) if transpose else (R, C)
+    if not (x.is_cuda and x.dtype == torch.bfloat16):
+        xt = (x.t() if transpose else x).contiguous()
+        q, sc = (fp8_quant_128x128_ref if block else fp8_quant_1x128_ref)(xt, True)
+        return q, pack_scales_ue8m0(sc, rows, not block), sc
+    q = torch.empty(rows, kc, device=x.device, dtype=torch.float8_e4m3fn)
+    sf = torch.empty(rows // 128, kc // 128, 512, device=x.device, dtype=torch.uint8)
+    sc = torch.empty(rows // 128 if block else rows, kc // 128, device=x.device, dtype=torch.float32)
+    _ext.ops().fp8_quant_mx(x.contiguous(), q, sc, sf, transpose, block)
+    return q, sf, sc
+
+
+def mxfp8_gemm_packed(a_q, sfa, b_q, sfb):
+    """a_q [M,K] @ b_q [N,K]^T in e4m3 with packed exponent-byte scales (see :func:`fp8_quant_mx`) -> bf16 [M,N]."""
+    out = torch.empty(a_q.shape[0], b_q.shape[0], device=a_q.device, dtype=torch.bfloat16)
+    _ext.ops().gemm_mxfp8(a_q, sfa, b_q, sfb, out)
+    return out
+
+
 class Fp8Linear:
     """y = x @ W with W (in, out) held as block-scaled FP8: the weight is quantised once
     (transposed to [out, in] so K is contiguous), activations are quantised per call."""

@@ -305,3 +305,19 @@ def test_fp8_linear_training_path_on_gpu(cuda_device):
         assert _rel(outs["gpu_fp8"][i], outs["gpu_bf16"][i]) < 6e-2, what
     assert outs["gpu_fp8"][2].shape == (K, N)
 
+
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("block", [False, True])
+def test_fp8_quant_mx_kernel_matches_reference(cuda_device, transpose, block):
+    """One-pass quantise (+ transpose) + packed exponent bytes against the reference functions: same e4m3 bytes,
+    same power-of-two scales, same packed layout."""
+    from jax_gpt_b200.ops import rope as R
+    torch.manual_seed(6)
+    x = (torch.randn(384, 256) * torch.logspace(-2, 2, 256)[None, :]).to(torch.bfloat16)
+    q, sf, sc = R.fp8_quant_mx(x.to(cuda_device), transpose, block)
+    q_ref, sf_ref, sc_ref = R.fp8_quant_mx(x, transpose, block)
+    assert q.shape == q_ref.shape == ((256, 384) if transpose else (384, 256))
+    assert torch.equal(sc.cpu(), sc_ref)
+    assert torch.equal(sf.cpu(), sf_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
