@@ -86,41 +86,46 @@ class _AttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
-def attn_bwd_chunked(q, k, v, out, dout, lse, causal=True, scale=None, chunk: int = 1024):
+def attn_bwd_chunked(q, k, v, out, dout, lse, causal=True, scale=None, chunk: Optional[int] = None):
     """Gradients from the forward kernel's (out, lse) with the probabilities recomputed one query
-    chunk at a time (library matmuls; memory O(chunk * T) per head group). Covers the head widths
-    that have a forward kernel but no backward kernel: 256 and the MLA shape 192 / 128.
+    chunk at a time, ALL heads of a sequence per step (batched library matmuls over the kv heads; a chunk is
+    sized so that its fp32 score block stays near 1 GB). Covers the head widths that have a forward kernel but
+    no backward kernel: 256 and the MLA shape 192 / 128.
     q (B,T,H,D), k (B,T,Hkv,D), v (B,T,Hkv,Dv); lse (B,H,T) is the log2-sum-exp of scale*log2(e)*scores."""
     B, T, H, D = q.shape
     Hkv, Dv = k.shape[2], v.shape[3]
     g = H // Hkv
     scale = float(scale) if scale is not None else D ** -0.5
     c2 = scale * 1.4426950408889634
+    if chunk is None:
+        chunk = max(64, min(1024, (1 << 28) // max(1, H * T) // 64 * 64))
     dq = torch.empty_like(q)
-    dk = torch.zeros(B, T, Hkv, D, device=q.device, dtype=torch.float32)
-    dv = torch.zeros(B, T, Hkv, Dv, device=q.device, dtype=torch.float32)
+    dk = torch.zeros(B, Hkv, T, D, device=q.device, dtype=torch.float32)
+    dv = torch.zeros(B, Hkv, T, Dv, device=q.device, dtype=torch.float32)
     delta = (out.float() * dout.float()).sum(-1)          # (B,T,H)
+    pos = torch.arange(T, device=q.device)
     for b in range(B):
-        for hk in range(Hkv):
-            hs = slice(hk * g, (hk + 1) * g)
-            for q0 in range(0, T, chunk):
-                q1 = min(T, q0 + chunk)
-                kv1 = q1 if causal else T
-                kk, vv = k[b, :kv1, hk], v[b, :kv1, hk]                         # (kv1, D), (kv1, Dv)
-                qs = q[b, q0:q1, hs].permute(1, 0, 2)                           # (g, c, D)
-                do = dout[b, q0:q1, hs].permute(1, 0, 2)                        # (g, c, Dv)
-                s2 = torch.matmul(qs, kk.t()).float() * c2                      # (g, c, kv1)
-                p = torch.exp2(s2 - lse[b, hs, q0:q1, None])
-                if causal:
-                    qi = torch.arange(q0, q1, device=q.device)[:, None]
-                    p = p.masked_fill(torch.arange(kv1, device=q.device)[None, :] > qi, 0.0)
-                dp = torch.matmul(do, vv.t()).float()
-                ds = (p * (dp - delta[b, q0:q1, hs].t()[:, :, None]) * scale).to(q.dtype)
-                pb = p.to(q.dtype)
-                dq[b, q0:q1, hs] = torch.matmul(ds, kk).permute(1, 0, 2)
-                dk[b, :kv1, hk] += torch.matmul(ds.reshape(-1, kv1).t(), qs.reshape(-1, D)).float()
-                dv[b, :kv1, hk] += torch.matmul(pb.reshape(-1, kv1).t(), do.reshape(-1, Dv)).float()
-    return dq, dk.to(k.dtype), dv.to(v.dtype)
+        kb, vb = k[b].permute(1, 0, 2), v[b].permute(1, 0, 2)                    # (Hkv, T, D), (Hkv, T, Dv)
+        for q0 in range(0, T, chunk):
+            q1 = min(T, q0 + chunk)
+            c = q1 - q0
+            kv1 = q1 if causal else T
+            kk, vv = kb[:, :kv1], vb[:, :kv1]
+            # rows of a kv head: its g query heads one after the other, c positions each
+            qs = q[b, q0:q1].reshape(c, Hkv, g, D).permute(1, 2, 0, 3).reshape(Hkv, g * c, D)
+            do = dout[b, q0:q1].reshape(c, Hkv, g, Dv).permute(1, 2, 0, 3).reshape(Hkv, g * c, Dv)
+            l2 = lse[b, :, q0:q1].reshape(Hkv, g * c, 1)
+            dl = delta[b, q0:q1].t().reshape(Hkv, g * c, 1)
+            p = torch.matmul(qs, kk.transpose(1, 2)).float().mul_(c2).sub_(l2).exp2_()      # (Hkv, g*c, kv1)
+            if causal:
+                p.view(Hkv, g, c, kv1).masked_fill_(pos[None, :kv1] > pos[q0:q1, None], 0.0)
+            ds = torch.matmul(do, vv.transpose(1, 2)).float().sub_(dl).mul_(p).mul_(scale).to(q.dtype)
+            pb = p.to(q.dtype)
+            del p
+            dq[b, q0:q1] = torch.matmul(ds, kk).reshape(Hkv, g, c, D).permute(2, 0, 1, 3).reshape(c, H, D)
+            dk[b, :, :kv1] += torch.matmul(ds.transpose(1, 2), qs)
+            dv[b, :, :kv1] += torch.matmul(pb.transpose(1, 2), do)
+    return dq, dk.permute(0, 2, 1, 3).to(k.dtype), dv.permute(0, 2, 1, 3).to(v.dtype)
 
 
 class _AttnFwdKernelFn(torch.autograd.Function):
