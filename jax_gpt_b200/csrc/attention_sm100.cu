@@ -685,6 +685,42 @@ __global__ void cast_rows_kernel(const float* __restrict__ src, int64_t lds, __n
   }
 }
 
+// Elementwise core of the recomputed attention backward (head widths without a tensor-core backward kernel):
+// scores and dP = dO V^T come from batched library matmuls as bf16 [rows, kv]; this pass turns them IN PLACE into
+// P = exp2(scale_log2 * s - lse) (zero above the causal diagonal) and dS = P * (dP - delta) * scale, eight columns
+// per thread. Row r holds query position q0 + r % c (c positions per head, heads one after the other).
+__global__ void attn_bwd_probs_kernel(__nv_bfloat16* __restrict__ s, __nv_bfloat16* __restrict__ dp,
+                                      const float* __restrict__ lse, const float* __restrict__ delta, int64_t rows,
+                                      int kv, int c, int q0, float scale_log2, float scale, int causal) {
+  const int vec = kv >> 3;
+  const int64_t total = rows * vec;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec;
+    const int col0 = static_cast<int>(i - r * vec) << 3;
+    const float l = lse[r], d = delta[r];
+    const int qpos = q0 + static_cast<int>(r % c);
+    uint4* sp = reinterpret_cast<uint4*>(s + r * kv + col0);
+    uint4* dpp = reinterpret_cast<uint4*>(dp + r * kv + col0);
+    const uint4 sv = *sp, dv = *dpp;
+    const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+    uint32_t po[4], dso[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = unpack_bf16x2(sw[e]), g = unpack_bf16x2(dw[e]);
+      float p0 = exp2f(fmaf(a.x, scale_log2, -l)), p1 = exp2f(fmaf(a.y, scale_log2, -l));
+      if (causal) {
+        if (col0 + 2 * e > qpos) p0 = 0.f;
+        if (col0 + 2 * e + 1 > qpos) p1 = 0.f;
+      }
+      po[e] = pack_bf16x2(p0, p1);
+      dso[e] = pack_bf16x2(p0 * (g.x - d) * scale, p1 * (g.y - d) * scale);
+    }
+    *sp = make_uint4(po[0], po[1], po[2], po[3]);
+    *dpp = make_uint4(dso[0], dso[1], dso[2], dso[3]);
+  }
+}
+
 cudaError_t make_map(CUtensorMap* m, const __nv_bfloat16* p, int64_t ld, int rows, int cols) {
   return encode_tma_2d(m, p, 2, cols, rows, ld * 2, 64, 128);
 }
@@ -775,6 +811,15 @@ cudaError_t launch_cast_rows_f32_bf16(const float* src, int64_t lds, __nv_bfloat
   const int64_t total = static_cast<int64_t>(M) * (N / 4);
   const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
   cast_rows_kernel<<<grid, 256, 0, stream>>>(src, lds, dst, ldd, M, N);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_attn_bwd_probs(__nv_bfloat16* s, __nv_bfloat16* dp, const float* lse, const float* delta,
+                                  int64_t rows, int kv, int c, int q0, float scale, int causal, cudaStream_t stream) {
+  if (kv % 8 != 0 || rows <= 0 || c <= 0) return cudaErrorInvalidValue;
+  const int64_t total = rows * (kv / 8);
+  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 32));
+  attn_bwd_probs_kernel<<<grid, 256, 0, stream>>>(s, dp, lse, delta, rows, kv, c, q0, scale * kLog2e, scale, causal);
   return cudaGetLastError();
 }
 

@@ -36,6 +36,11 @@ cudaError_t launch_attn_bwd(const AttnTensors& t, const AttnShape& s, const __nv
                             cudaStream_t stream);
 
 // dst[r, c] (bf16, row stride ldd) = src[r, c] (fp32, row stride lds), for an M x N block.
+// In-place elementwise step of the recomputed attention backward: s [rows, kv] bf16 scores -> probabilities,
+// dp [rows, kv] bf16 (dO V^T) -> dS; lse (log2 units) and delta per row; row r is query position q0 + r % c.
+cudaError_t launch_attn_bwd_probs(__nv_bfloat16* s, __nv_bfloat16* dp, const float* lse, const float* delta,
+                                  int64_t rows, int kv, int c, int q0, float scale, int causal, cudaStream_t stream);
+
 cudaError_t launch_cast_rows_f32_bf16(const float* src, int64_t lds, __nv_bfloat16* dst, int64_t ldd, int M, int N,
                                       cudaStream_t stream);
 

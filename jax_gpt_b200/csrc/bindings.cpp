@@ -303,6 +303,21 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
                                         cur_stream()));
 }
 
+void attn_bwd_probs(Tensor s, Tensor dp, const Tensor& lse, const Tensor& delta, int64_t c, int64_t q0, double scale,
+                    bool causal) {
+  c10::cuda::CUDAGuard guard(s.device());
+  TORCH_CHECK(s.is_cuda() && s.is_contiguous() && dp.is_contiguous() && s.scalar_type() == at::kBFloat16 &&
+                  dp.scalar_type() == at::kBFloat16 && s.sizes() == dp.sizes() && s.dim() >= 2,
+              "attn_bwd_probs: s, dp [..., kv] contiguous bf16 of one shape");
+  const int64_t kv = s.size(-1), rows = s.numel() / kv;
+  TORCH_CHECK(kv % 8 == 0 && lse.is_contiguous() && delta.is_contiguous() && lse.scalar_type() == at::kFloat &&
+                  delta.scalar_type() == at::kFloat && lse.numel() == rows && delta.numel() == rows,
+              "attn_bwd_probs: kv multiple of 8; lse, delta fp32 with one value per row");
+  B200_CHECK_CUDA(b200::launch_attn_bwd_probs(bf16_mut(s), bf16_mut(dp), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                                              rows, static_cast<int>(kv), static_cast<int>(c), static_cast<int>(q0),
+                                              static_cast<float>(scale), causal ? 1 : 0, cur_stream()));
+}
+
 void cast_rows(const Tensor& src, Tensor dst) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(src.dim() == 2 && dst.dim() == 2 && src.stride(1) == 1 && dst.stride(1) == 1, "cast_rows: 2-D");
@@ -359,6 +374,7 @@ TORCH_LIBRARY(b200, m) {
       "dq_accum, Tensor(c!) dk, Tensor(d!) dv, int B, int T, int H, int Hkv, int D, float scale, bool causal) -> ()",
       &attn_bwd);
   m.def("cast_rows(Tensor src, Tensor(a!) dst) -> ()", &cast_rows);
+  m.def("attn_bwd_probs(Tensor(a!) s, Tensor(b!) dp, Tensor lse, Tensor delta, int c, int q0, float scale, bool causal) -> ()", &attn_bwd_probs);
   m.def("norm_bwd_scratch_floats(int D) -> int", [](int64_t D) { return b200::norm_bwd_scratch_floats(static_cast<int>(D)); });
   m.def("gemm_uses_pair(int M, int N, int split_k) -> bool", [](int64_t M, int64_t N, int64_t split_k) {
     b200::GemmArgs a{};

@@ -88,17 +88,22 @@ class _AttnFn(torch.autograd.Function):
 
 def attn_bwd_chunked(q, k, v, out, dout, lse, causal=True, scale=None, chunk: Optional[int] = None):
     """Gradients from the forward kernel's (out, lse) with the probabilities recomputed one query
-    chunk at a time, ALL heads of a sequence per step (batched library matmuls over the kv heads; a chunk is
-    sized so that its fp32 score block stays near 1 GB). Covers the head widths that have a forward kernel but
-    no backward kernel: 256 and the MLA shape 192 / 128.
+    chunk at a time, ALL heads of a sequence per step: batched library matmuls over the kv heads for the four
+    products, and on CUDA one elementwise kernel that rewrites the bf16 scores and dO V^T in place as P and dS
+    (chunks sized to about 8 GB of those two). Covers the head widths that have a forward kernel but no
+    tensor-core backward kernel: 256 and the MLA shape 192 / 128.
     q (B,T,H,D), k (B,T,Hkv,D), v (B,T,Hkv,Dv); lse (B,H,T) is the log2-sum-exp of scale*log2(e)*scores."""
     B, T, H, D = q.shape
     Hkv, Dv = k.shape[2], v.shape[3]
     g = H // Hkv
     scale = float(scale) if scale is not None else D ** -0.5
     c2 = scale * 1.4426950408889634
+    fused = q.is_cuda and q.dtype == torch.bfloat16 and T % 8 == 0
     if chunk is None:
-        chunk = max(64, min(1024, (1 << 28) // max(1, H * T) // 64 * 64))
+        # fused path: scores and dP are kept as bf16 and rewritten in place (4 bytes per score element);
+        # library path: fp32 temporaries (about 16 bytes per element)
+        budget = (1 << 33) // 4 if fused else (1 << 28)
+        chunk = max(64, min(T, budget // max(1, H * T) // 64 * 64))
     dq = torch.empty_like(q)
     dk = torch.zeros(B, Hkv, T, D, device=q.device, dtype=torch.float32)
     dv = torch.zeros(B, Hkv, T, Dv, device=q.device, dtype=torch.float32)
@@ -116,12 +121,18 @@ def attn_bwd_chunked(q, k, v, out, dout, lse, causal=True, scale=None, chunk: Op
             do = dout[b, q0:q1].reshape(c, Hkv, g, Dv).permute(1, 2, 0, 3).reshape(Hkv, g * c, Dv)
             l2 = lse[b, :, q0:q1].reshape(Hkv, g * c, 1)
             dl = delta[b, q0:q1].t().reshape(Hkv, g * c, 1)
-            p = torch.matmul(qs, kk.transpose(1, 2)).float().mul_(c2).sub_(l2).exp2_()      # (Hkv, g*c, kv1)
-            if causal:
-                p.view(Hkv, g, c, kv1).masked_fill_(pos[None, :kv1] > pos[q0:q1, None], 0.0)
-            ds = torch.matmul(do, vv.transpose(1, 2)).float().sub_(dl).mul_(p).mul_(scale).to(q.dtype)
-            pb = p.to(q.dtype)
-            del p
+            if fused:
+                # one elementwise kernel turns (scores, dO V^T) into (P, dS) in place
+                pb = torch.matmul(qs, kk.transpose(1, 2))                                   # (Hkv, g*c, kv1) bf16
+                ds = torch.matmul(do, vv.transpose(1, 2))
+                _ext.ops().attn_bwd_probs(pb, ds, l2.contiguous(), dl.contiguous(), c, q0, scale, causal)
+            else:
+                p = torch.matmul(qs, kk.transpose(1, 2)).float().mul_(c2).sub_(l2).exp2_()  # (Hkv, g*c, kv1)
+                if causal:
+                    p.view(Hkv, g, c, kv1).masked_fill_(pos[None, :kv1] > pos[q0:q1, None], 0.0)
+                ds = torch.matmul(do, vv.transpose(1, 2)).float().sub_(dl).mul_(p).mul_(scale).to(q.dtype)
+                pb = p.to(q.dtype)
+                del p
             dq[b, q0:q1] = torch.matmul(ds, kk).reshape(Hkv, g, c, D).permute(2, 0, 1, 3).reshape(c, H, D)
             dk[b, :, :kv1] += torch.matmul(ds.transpose(1, 2), qs)
             dv[b, :, :kv1] += torch.matmul(pb.transpose(1, 2), do)

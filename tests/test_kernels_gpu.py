@@ -208,6 +208,31 @@ def test_attention_fwd_bwd(cuda_device, B, T, H, Hkv, D, causal):
     assert _rel_err(q.grad, qr.grad) < 3e-2
 
 
+@pytest.mark.parametrize("B,T,H,Hkv,D,Dv", [(2, 256, 4, 2, 256, 256), (1, 384, 4, 4, 192, 128)])
+def test_attention_wide_heads_gradients(cuda_device, B, T, H, Hkv, D, Dv):
+    """Head widths without a tensor-core backward kernel (gated attention 256, MLA 192 / 128): forward kernel,
+    gradients from the recomputation (batched matmuls + the in-place probability / dS kernel), against autograd of
+    the fp32 reference; also with a small chunk so that the key / value gradients accumulate over chunks."""
+    from jax_gpt_b200.ops import attention as A
+    torch.manual_seed(9)
+    q = torch.randn(B, T, H, D, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    k = torch.randn(B, T, Hkv, D, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    v = torch.randn(B, T, Hkv, Dv, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    dout = torch.randn(B, T, H, Dv, device=cuda_device).to(torch.bfloat16)
+    out = A.attention(q, k, v, causal=True)
+    out.backward(dout)
+    qr, kr, vr = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ref = A.attention_ref(qr, kr, vr, causal=True)
+    ref.backward(dout.float())
+    assert _rel_err(out, ref) < 2e-2
+    for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        assert _rel_err(got, want) < 3e-2
+    lse = A.attn_fwd(q.detach(), k.detach(), v.detach(), True, None)[1]
+    dq, dk, dv = A.attn_bwd_chunked(q.detach(), k.detach(), v.detach(), out.detach(), dout, lse, True, None, chunk=128)
+    for got, want in ((dq, qr.grad), (dk, kr.grad), (dv, vr.grad)):
+        assert _rel_err(got, want) < 3e-2
+
+
 def test_attention_fused_qkv_views(cuda_device):
     """q/k/v given as column slices of one [B*T, 3*H*D] projection output."""
     from jax_gpt_b200.ops import attention as A
