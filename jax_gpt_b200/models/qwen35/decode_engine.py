@@ -1,0 +1,146 @@
+"""CUDA-graph decode engine for the Qwen3.5-style hybrid model: one graph replay per generated token.
+
+The function-style decode (model.py:forward with ``is_decode=True``) rebuilds the cache object every step
+(stacking all recurrent states), passes the position as a host integer and launches a few hundred small
+kernels, so a token step is bound by the host. Here the state lives in place and everything a step needs is in
+device memory:
+
+* the Gated-DeltaNet states and conv windows are fp32 buffers updated in place by the fused decode kernel
+  (csrc/seq_kernels.cu: conv window, gates, delta rule, gated RMSNorm in one launch per layer);
+* the position is a device scalar: rotary angles are gathered with it, the new key / value row is written with
+  ``index_copy_`` and the attention of the gated-attention layers runs over the whole (fixed-size) cache with the
+  positions past it masked, so every shape is static;
+* the routed experts go through the fused dispatch / grouped GEMM / combine kernel when an expert runtime is
+  given (a launch per expert otherwise, which cannot be captured: the engine then runs eagerly);
+* embedding, all layers, the head, the arg-max and the position increment are captured in one CUDA graph the
+  first time a step runs and replayed afterwards.
+
+The reference decodes with one jitted forward per token over the same dense cache
+(jax_gpt/models/qwen35/model.py:338-396, block.py:19-137, gqa.py:60-119, deltanet.py decode step).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .block import _slice
+from .cache import HybridCache
+from .config import Qwen35Config
+from .deltanet import deltanet_recurrent_step
+from .fp8 import matmul_maybe_fp8
+from .moe import moe_layer
+from .primitives import apply_rotary_emb, precompute_rope_freqs, rms_norm
+
+
+class Qwen35DecodeEngine:
+    def __init__(self, params: dict, config: Qwen35Config, cache: HybridCache, ep=None, use_cuda_graph: bool = True):
+        """``cache`` holds the prompts (prefill done); its key / value buffers are used in place, the recurrent
+        states are copied once into fp32 buffers. ``ep``: callable expert runtime
+        (parallel/expert_parallel.py:EPMoEInferenceRuntime) or None."""
+        c = config
+        self.p, self.c, self.ep = params, c, ep
+        self.device = cache.gqa_k.device
+        self.B = cache.gqa_k.shape[1]
+        self.max_len = cache.gqa_k.shape[3]
+        self.M = cache.delta_M.float().contiguous()          # (G, nd, B, Hv, dk, dv)
+        self.conv = cache.delta_conv.float().contiguous()    # (G, nd, B, conv_dim, K)
+        self.k, self.v = cache.gqa_k, cache.gqa_v            # (G, B, Hkv, max_len, dh)
+        self.pos = int(cache.pos)
+        self.pos_t = torch.tensor([self.pos], device=self.device, dtype=torch.long)
+        self.cols = torch.arange(self.max_len, device=self.device)
+        self.rope = precompute_rope_freqs(c.gqa_rope_dim, self.max_len, c.gqa_rope_theta, device=self.device)
+        self.tokens = torch.zeros(self.B, device=self.device, dtype=torch.long)
+        self.next_tokens = torch.zeros(self.B, device=self.device, dtype=torch.long)
+        self.logits = None
+        self.use_graph = bool(use_cuda_graph) and self.device.type == "cuda" and callable(ep)
+        self._graph = None
+
+    # ---- layers (x is (B, D)) -------------------------------------------------------------------------
+    def _moe(self, x, lp):
+        c = self.c
+        h = rms_norm(x, lp["moe_norm"], c.rms_norm_eps)
+        return x + moe_layer(h[:, None, :], lp["moe"], c.n_experts_per_token, group=self.ep,
+                             n_experts=c.n_routed_experts)[:, 0]
+
+    def _delta_layer(self, x, lp, gi: int, i: int):
+        c = self.c
+        h = rms_norm(x, lp["attn_norm"], c.rms_norm_eps)
+        state, conv = self.M[gi, i], self.conv[gi, i]
+        a, new_state, new_conv = deltanet_recurrent_step(h[:, None, :], lp["attn"], state, conv, c.delta_n_qk_heads,
+                                                         c.delta_n_v_heads, c.delta_qk_head_dim, c.delta_v_head_dim)
+        if new_state.data_ptr() != state.data_ptr():         # library path returns new tensors; the kernel works in place
+            state.copy_(new_state)
+            conv.copy_(new_conv)
+        return self._moe(x + a[:, 0], lp)
+
+    def _gqa_layer(self, x, lp, gi: int):
+        c, ap = self.c, lp["attn"]
+        B, Hq, Hkv, dh = self.B, c.gqa_n_q_heads, c.gqa_n_kv_heads, c.gqa_head_dim
+        h = rms_norm(x, lp["attn_norm"], c.rms_norm_eps)
+        qg = matmul_maybe_fp8(h, ap["q_proj"]).reshape(B, 1, Hq, 2 * dh)
+        q, gate = qg[..., :dh], qg[..., dh:]
+        k = matmul_maybe_fp8(h, ap["k_proj"]).reshape(B, 1, Hkv, dh)
+        v = matmul_maybe_fp8(h, ap["v_proj"]).reshape(B, 1, Hkv, dh)
+        fr = self.rope.index_select(0, self.pos_t)                                   # (1, rope_dim/2, 2)
+        q = apply_rotary_emb(rms_norm(q.contiguous(), ap["q_norm"]), fr, c.gqa_rope_dim)
+        k = apply_rotary_emb(rms_norm(k.contiguous(), ap["k_norm"]), fr, c.gqa_rope_dim)
+        ck, cv = self.k[gi], self.v[gi]                                              # (B, Hkv, max_len, dh)
+        ck.index_copy_(2, self.pos_t, k.permute(0, 2, 1, 3).to(ck.dtype))
+        cv.index_copy_(2, self.pos_t, v.permute(0, 2, 1, 3).to(cv.dtype))
+        g = Hq // Hkv
+        qh = q.reshape(B, Hkv, g, dh).float()
+        s = torch.matmul(qh, ck.float().transpose(2, 3)) * (dh ** -0.5)               # (B, Hkv, g, max_len)
+        s = s.masked_fill(self.cols > self.pos_t, float("-inf"))
+        o = torch.matmul(torch.softmax(s, dim=-1), cv.float())                        # (B, Hkv, g, dh)
+        o = (o.reshape(B, Hq, dh) * torch.sigmoid(gate[:, 0].float())).to(x.dtype)
+        return self._moe(x + matmul_maybe_fp8(o.reshape(B, Hq * dh), ap["o_proj"]), lp)
+
+    def _token_step(self):
+        c, p = self.c, self.p
+        x = p["embed"][self.tokens]
+        for gi in range(c.n_groups):
+            gp = _slice(p["groups"], gi)
+            for i in range(c.n_delta_per_group):
+                x = self._delta_layer(x, _slice(gp["delta_layers"], i), gi, i)
+            x = self._gqa_layer(x, gp["gqa_layer"], gi)
+        logits = matmul_maybe_fp8(rms_norm(x, p["final_norm"], c.rms_norm_eps), p["lm_head"])
+        self.next_tokens.copy_(logits.argmax(-1))
+        self.pos_t.add_(1)
+        return logits
+
+    # ---- public ---------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens (B,): the last token of every sequence. Returns the greedy next tokens (B,), a device tensor
+        the next call may take directly; ``self.logits`` (B, V) are the step's logits."""
+        assert self.pos < self.max_len, "the cache is full"
+        self.tokens.copy_(tokens.reshape(-1))
+        if not self.use_graph:
+            self.logits = self._token_step()
+        elif self._graph is None:
+            # one eager step on a side stream first (kernel attributes, symmetric buffers, allocator), undone
+            # afterwards: the recurrent states and the position are restored, the rewritten cache row is the same
+            saved = (self.M.clone(), self.conv.clone(), self.pos_t.clone())
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._token_step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.M.copy_(saved[0])
+            self.conv.copy_(saved[1])
+            self.pos_t.copy_(saved[2])
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self.logits = self._token_step()
+            self._graph.replay()                      # capture does not execute; the replay is the real step
+        else:
+            self._graph.replay()
+        self.pos += 1
+        return self.next_tokens
+
+    def cache(self, dtype: Optional[torch.dtype] = None) -> HybridCache:
+        """The state as a ``HybridCache`` (to continue with the function-style forward)."""
+        dt = dtype or self.k.dtype
+        return HybridCache(self.M.to(dt), self.conv.to(dt), self.k, self.v, self.pos)

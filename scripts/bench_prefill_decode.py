@@ -84,8 +84,19 @@ def make_runner(args, device):
             logits, cache = forward(params, tok, cfg, cache=cache, ep_group=ep)
             return logits[:, -1].argmax(-1), cache
 
+        engines = {}
+
         def decode(state):
             nxt, cache = state
+            if args.engine:
+                # in-place decode engine: device-side position, one CUDA-graph replay per token
+                from jax_gpt_b200.models.qwen35.decode_engine import Qwen35DecodeEngine
+                eng = engines.get(id(cache))
+                if eng is None:
+                    engines.clear()
+                    eng = engines[id(cache)] = Qwen35DecodeEngine(params, cfg, cache, ep=ep,
+                                                                  use_cuda_graph=not args.no_graph)
+                return eng.step(nxt), cache
             logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True, ep_group=ep)
             return logits[:, -1].argmax(-1), cache
         return prefill, decode, cfg
@@ -178,7 +189,7 @@ def main(argv=None):
     ap.add_argument("--fp8", action="store_true")
     ap.add_argument("--n-layers", type=int, default=0)
     ap.add_argument("--experts", type=int, default=0, help="deepseek_v3: override the routed expert count")
-    ap.add_argument("--engine", action="store_true", help="deepseek_v3: decode through the CUDA-graph decode engine")
+    ap.add_argument("--engine", action="store_true", help="decode through the model family's CUDA-graph decode engine")
     ap.add_argument("--no-graph", action="store_true", help="with --engine: run the engine's step eagerly")
     ap.add_argument("--prefill-reps", type=int, default=5)
     ap.add_argument("--decode-steps", type=int, default=20)

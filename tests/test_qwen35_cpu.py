@@ -214,3 +214,29 @@ def test_sharding_rules(cfg, params):
         wr = torch.where(mine, w, torch.zeros_like(w))
         acc += MOE.expert_forward_single(x, wr, torch.where(mine, idx - r * e, torch.zeros_like(idx)), lpr)
     assert torch.allclose(acc, ref, atol=1e-5)
+
+
+def test_decode_engine_matches_function_style_decode(cfg, params):
+    """The in-place decode engine (device-side position, masked attention over the whole cache, states updated
+    in place) produces the logits of ``forward(..., is_decode=True)`` step after step."""
+    from jax_gpt_b200.models.qwen35.decode_engine import Qwen35DecodeEngine
+    torch.manual_seed(11)
+    B, T, steps = 2, 6, 4
+    tok = torch.randint(0, cfg.vocab_size, (B, T))
+    with torch.no_grad():
+        cache_a = init_cache(cfg, B, T + steps + 2)
+        logits, cache_a = forward(params, tok, cfg, cache=cache_a)
+        cache_b = init_cache(cfg, B, T + steps + 2)
+        _, cache_b = forward(params, tok, cfg, cache=cache_b)
+        eng = Qwen35DecodeEngine(params, cfg, cache_b, use_cuda_graph=False)
+        nxt = logits[:, -1].argmax(-1)
+        for _ in range(steps):
+            ref, cache_a = forward(params, nxt[:, None], cfg, cache=cache_a, is_decode=True)
+            got = eng.step(nxt)
+            assert torch.allclose(eng.logits, ref[:, -1], atol=2e-4, rtol=1e-4)
+            assert torch.equal(got, ref[:, -1].argmax(-1))
+            nxt = got.clone()
+        assert eng.pos == cache_a.pos == T + steps
+        back = eng.cache(torch.float32)
+        assert torch.allclose(back.delta_M, cache_a.delta_M, atol=1e-5)
+        assert torch.allclose(back.gqa_k[:, :, :, :eng.pos], cache_a.gqa_k[:, :, :, :eng.pos], atol=1e-5)
