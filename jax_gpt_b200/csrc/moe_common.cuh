@@ -61,24 +61,30 @@ __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb
   const int W = a.world, EL = a.e_local, ET = W * EL;
   if (threadIdx.x == 0) tb->overflow = 0;
   __syncthreads();
+  // Three passes, linear in the number of experts: padded totals per global expert (every expert's region starts
+  // on a `pad`-row boundary; ragged-K weight gradients read whole blocks and the padding rows are kept zero), an
+  // exclusive scan inside every destination rank's segment (one thread per destination), then the rows of the
+  // sources placed before this rank.
   for (int e = threadIdx.x; e < ET; e += blockDim.x) {
-    const int dst = e / EL, el = e % EL;
-    // every expert's region starts on a 64-row boundary (ragged-K weight gradients read whole
-    // 64-row blocks; the padding rows are kept zero)
-    int off = 0;
-    for (int e2 = dst * EL; e2 < dst * EL + el; ++e2) {  // experts placed before e on the destination
-      int n2 = 0;
-      for (int s = 0; s < W; ++s) n2 += __ldcg(counts_all + s * ET + e2);
-      off += (n2 + pad - 1) / pad * pad;
+    int n = 0;
+    for (int s = 0; s < W; ++s) n += __ldcg(counts_all + s * ET + e);
+    tb->send_off[e] = (n + pad - 1) / pad * pad;
+  }
+  __syncthreads();
+  if (threadIdx.x < W) {
+    int run = 0;
+    for (int e = threadIdx.x * EL; e < (threadIdx.x + 1) * EL; ++e) {
+      const int v = tb->send_off[e];
+      tb->send_off[e] = run;
+      run += v;
     }
+    if (run > a.cap_rows) tb->overflow = 1;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < ET; e += blockDim.x) {
     int before = 0;
-    for (int s = 0; s < a.rank; ++s) before += __ldcg(counts_all + s * ET + e);  // sources placed before this rank
-    tb->send_off[e] = off + before;
-    if (el == EL - 1) {
-      int tot = before;
-      for (int s = a.rank; s < W; ++s) tot += __ldcg(counts_all + s * ET + e);
-      if (off + (tot + pad - 1) / pad * pad > a.cap_rows) tb->overflow = 1;
-    }
+    for (int s = 0; s < a.rank; ++s) before += __ldcg(counts_all + s * ET + e);
+    tb->send_off[e] += before;
   }
   for (int el = threadIdx.x; el < EL; el += blockDim.x) {
     int n = 0;
@@ -116,8 +122,13 @@ struct TileInfo {
 template <class Args>
 __device__ __forceinline__ TileInfo decode_tile(const Args& a, const MoeTables* tb, int t) {
   const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
-  int el = 0;
-  while (t >= tb->tile0[el + 1]) ++el;
+  // first expert whose tile range ends after t (experts without rows have empty ranges): binary search
+  int el = 0, hi = a.e_local - 1;
+  while (el < hi) {
+    const int mid = (el + hi) >> 1;
+    if (tb->tile0[mid + 1] > t) hi = mid;
+    else el = mid + 1;
+  }
   const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
   int r = t - tb->tile0[el];
   TileInfo ti;

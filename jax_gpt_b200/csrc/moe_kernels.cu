@@ -383,8 +383,12 @@ struct BwdTile {
 };
 
 __device__ __forceinline__ BwdTile decode_bwd_tile(const EpMoeArgs& a, const MoeTables* tb, int t) {
-  int el = 0;
-  while (t >= tb->tile0[el + 1]) ++el;
+  int el = 0, hi = a.e_local - 1;  // first expert whose tile range ends after t
+  while (el < hi) {
+    const int mid = (el + hi) >> 1;
+    if (tb->tile0[mid + 1] > t) hi = mid;
+    else el = mid + 1;
+  }
   const int mt = (tb->rows[el] + BM - 1) / BM;
   const int c0 = mt * (a.inter / BN), c1 = mt * (a.d_model / BN), c2 = (a.inter / BM) * (a.d_model / BN);
   int r = t - tb->tile0[el];
