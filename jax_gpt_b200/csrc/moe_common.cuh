@@ -15,7 +15,13 @@ struct MoeTables {
   int send_off[kMoeMaxExperts];      // first row of MY pairs for global expert e in its destination buffer
   int rows[kMoeMaxLocalExperts];     // rows received per local expert
   int base[kMoeMaxLocalExperts];     // first row of the local expert in this rank's receive buffer
-  int tile0[kMoeMaxLocalExperts + 1];  // first tile index of the local expert (GEMM1 tiles, then GEMM2 tiles)
+  // Static tile order. Backward: tile0[el] is the first tile of local expert el. Forward: the order is cut into
+  // n_slots = EL + lag slots, slot s holding the GEMM1 (gate|up) tiles of expert s followed by the GEMM2 (down)
+  // tiles of expert s - lag; tile0[s] is the first tile of slot s. The lag keeps about two rounds of tiles
+  // between an expert's GEMM1 tiles and the GEMM2 tiles that wait for them, so that CTAs working side by side
+  // in the order do not stall on one another.
+  int tile0[2 * kMoeMaxLocalExperts + 1];
+  int lag, n_slots;
   int mt0[kMoeMaxLocalExperts + 1];    // first m-tile index of the local expert
   int overflow;                      // some rank would receive more rows than cap_rows
 };
@@ -97,7 +103,7 @@ __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb
     int b = 0, t = 0, m = 0;
     for (int el = 0; el < EL; ++el) {
       tb->base[el] = b;
-      tb->tile0[el] = t;
+      if (backward) tb->tile0[el] = t;
       tb->mt0[el] = m;
       const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
       b += (tb->rows[el] + pad - 1) / pad * pad;
@@ -109,8 +115,26 @@ __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb
       }
       m += mt;
     }
-    tb->tile0[EL] = t;
     tb->mt0[EL] = m;
+    if (backward) {
+      tb->tile0[EL] = t;
+      tb->lag = 0;
+      tb->n_slots = EL;
+    } else {
+      // lag (in experts) worth about two rounds of the grid's CTAs at the average number of tiles per expert
+      int lag = (2 * static_cast<int>(gridDim.x) * EL + (t > 0 ? t : 1) - 1) / (t > 0 ? t : 1);
+      lag = lag < 1 ? 1 : (lag > EL ? EL : lag);
+      const int n_slots = EL + lag;
+      int u = 0;
+      for (int sl = 0; sl < n_slots; ++sl) {
+        tb->tile0[sl] = u;
+        if (sl < EL) u += ((tb->rows[sl] + kMoeBM - 1) / kMoeBM) * n1;
+        if (sl >= lag) u += ((tb->rows[sl - lag] + kMoeBM - 1) / kMoeBM) * n2;
+      }
+      tb->tile0[n_slots] = u;
+      tb->lag = lag;
+      tb->n_slots = n_slots;
+    }
   }
   __syncthreads();
 }
@@ -122,23 +146,26 @@ struct TileInfo {
 template <class Args>
 __device__ __forceinline__ TileInfo decode_tile(const Args& a, const MoeTables* tb, int t) {
   const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
-  // first expert whose tile range ends after t (experts without rows have empty ranges): binary search
-  int el = 0, hi = a.e_local - 1;
-  while (el < hi) {
-    const int mid = (el + hi) >> 1;
+  // first slot whose tile range ends after t (slots without tiles have empty ranges): binary search
+  int sl = 0, hi = tb->n_slots - 1;
+  while (sl < hi) {
+    const int mid = (sl + hi) >> 1;
     if (tb->tile0[mid + 1] > t) hi = mid;
-    else el = mid + 1;
+    else sl = mid + 1;
   }
-  const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
-  int r = t - tb->tile0[el];
+  int r = t - tb->tile0[sl];
+  const int g1 = (sl < a.e_local) ? ((tb->rows[sl] + kMoeBM - 1) / kMoeBM) * n1 : 0;
   TileInfo ti;
-  ti.el = el;
-  if (r < mt * n1) {
+  if (r < g1) {
+    const int mt = (tb->rows[sl] + kMoeBM - 1) / kMoeBM;
+    ti.el = sl;
     ti.phase = 0;
     ti.m = r % mt;
     ti.n = r / mt;
   } else {
-    r -= mt * n1;
+    r -= g1;
+    ti.el = sl - tb->lag;
+    const int mt = (tb->rows[ti.el] + kMoeBM - 1) / kMoeBM;
     ti.phase = 1;
     ti.m = r % mt;
     ti.n = r / mt;

@@ -186,7 +186,7 @@ ep_moe_forward_fp8_kernel(const __grid_constant__ Fp8Maps tm, const __grid_const
   }
 
   // ---- 3./4. grouped GEMMs over the local experts ----
-  const int num_tiles = alive ? tb->tile0[EL] : 0;
+  const int num_tiles = alive ? tb->tile0[tb->n_slots] : 0;
   const int n1 = I / 128;
   if (warp == 0) {
     if (lane == 0) {

@@ -147,7 +147,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   }
 
   // ---- 3./4. grouped GEMMs over the local experts ----
-  const int num_tiles = alive ? tb->tile0[EL] : 0;
+  const int num_tiles = alive ? tb->tile0[tb->n_slots] : 0;
   const int n1 = I / 128;
   if (warp == 0) {
     if (lane == 0) {
