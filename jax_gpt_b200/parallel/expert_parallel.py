@@ -249,18 +249,25 @@ def fused_ep_moe(layer: "FusedEPMoE", x, weights, idx, params, grads):
 
 class EPMoERuntime:
     """What the model code calls for the routed experts of an expert-parallel layer: the fused kernels
-    of one ``FusedEPMoE`` buffer set shared by all layers of the same shape. With gradient buffers in
-    the layer's parameter dict (``<name>@grad``) and autograd on, the call is differentiable."""
+    of one ``FusedEPMoE`` buffer set shared by all layers of the same shape, or of several sets used in
+    rotation (pass a list): the backward of a layer reuses what its forward launch left in its set, so with as
+    many sets as the model has MoE layers no forward launch has to be repeated in the backward pass; with fewer
+    the layers whose set was reused recompute theirs. With gradient buffers in the layer's parameter dict
+    (``<name>@grad``) and autograd on, the call is differentiable."""
 
-    def __init__(self, layer: FusedEPMoE):
-        self.layer = layer
+    def __init__(self, layer):
+        self.layers = list(layer) if isinstance(layer, (list, tuple)) else [layer]
+        self.layer = self.layers[0]
+        self._next = 0
 
     def __call__(self, x, weights, idx, params, grads=None):
         if grads is None:
             grads = {n: params.get(n + "@grad") for n in ("gate_proj", "up_proj", "down_proj")}
         train = torch.is_grad_enabled() and grads.get("gate_proj") is not None and self.layer.training
         if train:
-            return fused_ep_moe(self.layer, x, weights, idx, params, grads)
+            layer = self.layers[self._next % len(self.layers)]
+            self._next += 1
+            return fused_ep_moe(layer, x, weights, idx, params, grads)
         return self.layer.forward(x, weights, idx, params).to(x.dtype)
 
     def forward(self, x, weights, idx, params):

@@ -36,6 +36,9 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=1, help="sequences per rank")
     ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (0 = the family's)")
+    ap.add_argument("--moe-buffer-sets", type=int, default=4,
+                    help="buffer sets of the fused expert kernels used in rotation (as many as MoE layers: no "
+                         "forward launch is repeated in the backward pass)")
     ap.add_argument("--fp8", action="store_true", help="dense projections in block-scaled FP8 (forward, dgrad, wgrad)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
@@ -57,6 +60,8 @@ def main(argv=None):
         cfg = cfg.replace(vocab_size=args.vocab)
     params = init_params(cfg, 0, torch.bfloat16)
     ep = dist_opt = local = None
+    n_moe = cfg.n_layers if args.model == "qwen35" else cfg.n_layers - cfg.first_k_dense
+    n_sets = max(1, min(args.moe_buffer_sets, n_moe))
     if world == 1 and device.type == "cuda" and cfg.n_routed_experts <= 512:
         # one GPU: the same fused expert kernels with all experts local (one launch per MoE layer and direction)
         import os
@@ -65,16 +70,17 @@ def main(argv=None):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29535")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
-        layer = FusedEPMoE(Communicator(device=device), args.batch * args.seq, cfg.d_model, cfg.moe_intermediate_size,
-                           cfg.n_routed_experts, cfg.n_experts_per_token, training=True)
-        ep, local = EPMoERuntime(layer), is_expert_leaf
+        comm = Communicator(device=device)
+        layers = [FusedEPMoE(comm, args.batch * args.seq, cfg.d_model, cfg.moe_intermediate_size, cfg.n_routed_experts,
+                             cfg.n_experts_per_token, training=True) for _ in range(n_sets)]
+        ep, local = EPMoERuntime(layers), is_expert_leaf
     if world > 1:
         from jax_gpt_b200.parallel.expert_parallel import EPMoERuntime, FusedEPMoE, is_expert_leaf, shard_experts
         from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW
         dist_opt = FusedShardedAdamW(device=device)
-        layer = FusedEPMoE(dist_opt.comm, args.batch * args.seq, cfg.d_model, cfg.moe_intermediate_size,
-                           cfg.n_routed_experts, cfg.n_experts_per_token, training=True)
-        ep, local = EPMoERuntime(layer), is_expert_leaf
+        layers = [FusedEPMoE(dist_opt.comm, args.batch * args.seq, cfg.d_model, cfg.moe_intermediate_size,
+                             cfg.n_routed_experts, cfg.n_experts_per_token, training=True) for _ in range(n_sets)]
+        ep, local = EPMoERuntime(layers), is_expert_leaf
         params = shard_experts(params, rank, world)
     eng = TreeTrainEngine(params, make_loss(cfg, ep, fp8=args.fp8), device=device, local=local, lr=1e-4, min_lr=1e-4, warmup_steps=0,
                           dist_optimizer=dist_opt)
