@@ -32,3 +32,16 @@ def deepseek_v3_loss_fn(config, ep=None, fp8: bool = False):
             logits = forward(tree, tokens, config, ep=ep)
         return cross_entropy_mean(logits, targets, config.vocab_size)
     return loss_fn
+
+
+def qwen35_unstack(path, tensor) -> int:
+    """Leading layer axes of the Qwen3.5 tree (``TreeTrainEngine(unstack=...)``): everything under ``groups`` is
+    stacked over the groups, the DeltaNet layers additionally over their position in the group."""
+    if path[0] != "groups":
+        return 0
+    return 2 if "delta_layers" in path else 1
+
+
+def deepseek_v3_unstack(path, tensor) -> int:
+    """Leading layer axis of the DeepSeek-V3 tree: ``dense_layers`` and ``moe_layers`` are stacked over layers."""
+    return 1 if path[0] in ("dense_layers", "moe_layers") else 0

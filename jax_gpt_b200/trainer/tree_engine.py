@@ -53,9 +53,13 @@ class TreeTrainEngine:
                  local: Optional[Callable] = None, decay: Callable = default_decay, lr: float = 3e-4,
                  min_lr: float = 3e-5, warmup_steps: int = 100, lr_decay_steps: int = 10000, weight_decay: float = 0.1,
                  beta1: float = 0.9, beta2: float = 0.95, grad_clip: float = 1.0, dist_optimizer=None,
-                 dp_world: int = 1):
+                 dp_world: int = 1, unstack: Optional[Callable] = None):
         """``params``: nested dict of tensors (any device / dtype; copied). ``loss_fn(tree, *batch)``
-        returns a scalar. ``local(path, tensor)`` marks expert-parallel leaves."""
+        returns a scalar. ``local(path, tensor)`` marks expert-parallel leaves. ``unstack(path, tensor)`` gives
+        the number of leading (layer) axes of a dense leaf that the model indexes one slice at a time: the tree then
+        holds nested lists of per-slice autograd leaves instead of one stacked leaf, so that a layer's gradient is
+        added to its own slice of the flat buffer (a stacked leaf receives one FULL-size gradient per slice from
+        the select-backward of every layer, which costs layers^2 traffic)."""
         self.device = torch.device(device) if device is not None else torch.device("cpu")
         self.loss_fn = loss_fn
         self.hyper = dict(lr=lr, min_lr=min_lr, warmup=warmup_steps, decay=lr_decay_steps, wd=weight_decay,
@@ -117,13 +121,18 @@ class TreeTrainEngine:
         # ---- the tree the model sees ----
         self.tree: dict = {}
         self._leaf_params = []
-        for p, _ in dense:
+        def make_leaves(cview, gview, depth):
+            if depth == 0:
+                leaf = cview.requires_grad_(True)
+                leaf.register_post_accumulate_grad_hook(self._make_hook(gview))
+                self._leaf_params.append(leaf)
+                return leaf
+            return [make_leaves(cview[i], gview[i], depth - 1) for i in range(cview.shape[0])]
+
+        for p, t in dense:
             o, n, shape = self.offsets[p]
-            leaf = compute[o:o + n].view(shape).requires_grad_(True)
-            gview = grad[o:o + n].view(shape)
-            leaf.register_post_accumulate_grad_hook(self._make_hook(gview))
-            self._leaf_params.append(leaf)
-            _set(self.tree, p, leaf)
+            depth = min(int(unstack(p, t)), len(shape) - 1) if unstack is not None else 0
+            _set(self.tree, p, make_leaves(compute[o:o + n].view(shape), grad[o:o + n].view(shape), max(depth, 0)))
         for p, _ in loc:
             o, n, shape = self.local_offsets[p]
             _set(self.tree, p, self.local_compute[o:o + n].view(shape))

@@ -26,7 +26,7 @@ import torch.distributed as dist
 
 def main(argv=None):
     from jax_gpt_b200 import _ext
-    from jax_gpt_b200.trainer.lm_loss import deepseek_v3_loss_fn, qwen35_loss_fn
+    from jax_gpt_b200.trainer.lm_loss import deepseek_v3_loss_fn, deepseek_v3_unstack, qwen35_loss_fn, qwen35_unstack
     from jax_gpt_b200.trainer.tree_engine import TreeTrainEngine
     from jax_gpt_b200.utils.profiling import max_over_ranks
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -49,13 +49,13 @@ def main(argv=None):
         from jax_gpt_b200.models.qwen35.model import init_params
         cfg = Qwen35Config.ns().replace(n_layers=args.layers, n_routed_experts=args.experts,
                                         max_position_embeddings=args.seq)
-        make_loss = qwen35_loss_fn
+        make_loss, unstack = qwen35_loss_fn, qwen35_unstack
     else:
         from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
         from jax_gpt_b200.models.deepseek_v3.model import init_params
         cfg = DeepSeekV3Config.full().replace(n_layers=args.layers, first_k_dense=1, n_routed_experts=args.experts,
                                               max_position_embeddings=args.seq)
-        make_loss = deepseek_v3_loss_fn
+        make_loss, unstack = deepseek_v3_loss_fn, deepseek_v3_unstack
     if args.vocab:
         cfg = cfg.replace(vocab_size=args.vocab)
     params = init_params(cfg, 0, torch.bfloat16)
@@ -83,7 +83,7 @@ def main(argv=None):
         ep, local = EPMoERuntime(layers), is_expert_leaf
         params = shard_experts(params, rank, world)
     eng = TreeTrainEngine(params, make_loss(cfg, ep, fp8=args.fp8), device=device, local=local, lr=1e-4, min_lr=1e-4, warmup_steps=0,
-                          dist_optimizer=dist_opt)
+                          dist_optimizer=dist_opt, unstack=unstack)
     del params
     g = torch.Generator().manual_seed(1 + rank)
     tok = torch.randint(0, cfg.vocab_size, (args.batch, args.seq + 1), generator=g).to(device)

@@ -43,15 +43,15 @@ def train_moe(args, tc, rank, world, device):
     from jax_gpt_b200.data.pipeline import DataPipeline
     from jax_gpt_b200.data.tokenize import write_synthetic
     from jax_gpt_b200.trainer import MetricsLogger
-    from jax_gpt_b200.trainer.lm_loss import deepseek_v3_loss_fn, qwen35_loss_fn
+    from jax_gpt_b200.trainer.lm_loss import deepseek_v3_loss_fn, deepseek_v3_unstack, qwen35_loss_fn, qwen35_unstack
     from jax_gpt_b200.trainer.tree_engine import TreeTrainEngine
     family, cfg = moe_config(args.preset)
     if family == "qwen35":
         from jax_gpt_b200.models.qwen35.model import init_params
-        make_loss = qwen35_loss_fn
+        make_loss, unstack = qwen35_loss_fn, qwen35_unstack
     else:
         from jax_gpt_b200.models.deepseek_v3.model import init_params
-        make_loss = deepseek_v3_loss_fn
+        make_loss, unstack = deepseek_v3_loss_fn, deepseek_v3_unstack
     if args.synthetic and rank == 0 and not os.path.exists(os.path.join(tc.local_data_path, "train.bin")):
         write_synthetic(tc.local_data_path, args.synthetic_tokens, cfg.vocab_size, tc.seed)
     if world > 1:
@@ -80,7 +80,7 @@ def train_moe(args, tc, rank, world, device):
                                cfg.n_routed_experts, cfg.n_experts_per_token, training=True)
             ep, local = EPMoERuntime(layer), is_expert_leaf
             params = shard_experts(params, rank, world)
-    eng = TreeTrainEngine(params, make_loss(cfg, ep), device=device, local=local,
+    eng = TreeTrainEngine(params, make_loss(cfg, ep), device=device, local=local, unstack=unstack,
                           compute_dtype=torch.bfloat16 if on_gpu else torch.float32, lr=tc.learning_rate,
                           min_lr=tc.min_lr, warmup_steps=tc.warmup_steps, lr_decay_steps=tc.lr_decay_steps,
                           weight_decay=tc.weight_decay, beta1=tc.beta1, beta2=tc.beta2, grad_clip=tc.grad_clip,

@@ -119,3 +119,36 @@ def test_chunked_attention_backward_matches_autograd(shape):
     assert torch.allclose(dq, q.grad, atol=1e-4)
     assert torch.allclose(dk, k.grad, atol=1e-4)
     assert torch.allclose(dv, v.grad, atol=1e-4)
+
+
+@pytest.mark.parametrize("family", ["qwen35", "deepseek_v3"])
+def test_unstacked_layer_leaves_train_like_stacked_leaves(family):
+    """``unstack``: per-layer autograd leaves (nested lists in the tree the model indexes) give the same
+    parameters after a few steps as one stacked leaf per parameter, and the layer slices are real leaves."""
+    from jax_gpt_b200.trainer.lm_loss import (deepseek_v3_loss_fn, deepseek_v3_unstack, qwen35_loss_fn,
+                                              qwen35_unstack)
+    if family == "qwen35":
+        from jax_gpt_b200.models.qwen35 import Qwen35Config, init_params
+        cfg = Qwen35Config.tiny()
+        params, make_loss, unstack = init_params(cfg, 0), qwen35_loss_fn, qwen35_unstack
+    else:
+        from jax_gpt_b200.models.deepseek_v3.config import DeepSeekV3Config
+        from jax_gpt_b200.models.deepseek_v3.model import init_params
+        cfg = DeepSeekV3Config.tiny()
+        params, make_loss, unstack = init_params(cfg, 0, torch.float32), deepseek_v3_loss_fn, deepseek_v3_unstack
+    tokens, targets = _batch(cfg.vocab_size)
+    engines = [TreeTrainEngine(params, make_loss(cfg), compute_dtype=torch.float32, lr=3e-3, min_lr=3e-3, warmup_steps=0,
+                               unstack=u) for u in (None, unstack)]
+    for _ in range(3):
+        losses = [float(e.train_step(tokens, targets)["loss"]) for e in engines]
+        assert abs(losses[0] - losses[1]) < 1e-4, losses
+    a, b = engines[0].master_tree(), engines[1].master_tree()
+    for (pa, ta), (pb, tb) in zip(_walk(a), _walk(b)):
+        assert pa == pb and torch.allclose(ta, tb, atol=1e-5), pa
+    key = "groups" if family == "qwen35" else "moe_layers"
+    node = engines[1].tree[key]
+    while isinstance(node, dict):
+        node = node[sorted(node.keys())[0]]
+    assert isinstance(node, list)
+    leaf = node[0][0] if isinstance(node[0], list) else node[0]
+    assert leaf.is_leaf and leaf.requires_grad
