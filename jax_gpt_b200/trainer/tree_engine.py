@@ -156,8 +156,9 @@ class TreeTrainEngine:
     @staticmethod
     def _make_hook(gview):
         def hook(param):
-            gview.add_(param.grad)   # bf16 -> fp32 accumulate
-            param.grad = None
+            if param.grad is not None:   # a function may return no gradient for the leaf (autograd still calls the hook)
+                gview.add_(param.grad)   # bf16 -> fp32 accumulate
+                param.grad = None
         return hook
 
     # ------------------------------------------------------------------------------------------
