@@ -72,3 +72,31 @@ def test_small_mlp_trains_in_fp8_like_in_fp32():
     ref, got = run(False), run(True)
     assert got[-1] < 0.5 * got[0]
     assert abs(got[-1] - ref[-1]) < 0.15 * ref[-1] + 1e-3, (ref[-1], got[-1])
+
+
+def test_fp8_quant_mx_reference_layouts():
+    """Reference side of the one-pass quantiser: the transposed form equals quantising the transposed matrix, the
+    scales are powers of two, and the packed exponent bytes sit where the tensor-core GEMM reads them
+    (byte (r % 32) * 16 + ((r % 128) // 32) * 4 + j of the chunk of row block r // 128 and 128-wide K block)."""
+    from jax_gpt_b200.ops.rope import fp8_gemm_ref, fp8_quant_mx
+    torch.manual_seed(3)
+    x = (torch.randn(256, 384) * torch.logspace(-1, 1, 384)[None, :]).to(torch.bfloat16)
+    for block in (False, True):
+        q, sf, sc = fp8_quant_mx(x, False, block)
+        qt, sft, sct = fp8_quant_mx(x, True, block)
+        q2, sf2, sc2 = fp8_quant_mx(x.t().contiguous(), False, block)
+        assert torch.equal(qt.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(sft, sf2) and torch.equal(sct, sc2)
+        assert torch.equal(torch.exp2(torch.log2(sc).round()), sc)                     # powers of two
+        assert sf.shape == (2, 3, 512) and sft.shape == (3, 2, 512) and sf.dtype == torch.uint8
+        for r, kb in ((0, 0), (37, 1), (130, 2), (255, 0)):
+            scale = sc[r // 128, kb] if block else sc[r, kb]
+            byte = int(torch.log2(scale).round()) + 127
+            off = (r % 32) * 16 + ((r % 128) // 32) * 4
+            assert sf[r // 128, kb, off:off + 4].tolist() == [byte] * 4
+    # de-quantised product stays close to the bf16 product
+    a_q, _, a_s = fp8_quant_mx(x, False, False)
+    w = (torch.randn(128, 384) * 0.1).to(torch.bfloat16)
+    b_q, _, b_s = fp8_quant_mx(w, False, True)
+    ref = x.float() @ w.float().t()
+    got = fp8_gemm_ref(a_q, a_s, b_q, b_s)
+    assert ((got - ref).norm() / ref.norm()).item() < 0.06
