@@ -333,6 +333,28 @@ def is_expert_leaf(path, t, names=("gate_proj", "up_proj", "down_proj")) -> bool
     return path[-1] in names and t.dim() >= 3 and "shared" not in path[-1] and "mlp" not in path
 
 
+def forward_tile_order(rows, n1: int, n2: int, grid: int):
+    """Host model of the static tile order of the fused forward kernels (csrc/moe_common.cuh: build_tables /
+    decode_tile), for tests and diagnostics. ``rows[e]``: rows received by local expert e; ``n1`` / ``n2``: column
+    tiles of the gate|up and of the down GEMM; ``grid``: CTAs of the launch. Returns ``(lag, tiles)`` with
+    ``tiles[t] = (expert, phase, m_tile, n_tile)``: the order is cut into ``E + lag`` slots, slot s holding the
+    GEMM1 tiles of expert s followed by the GEMM2 tiles of expert s - lag, and the lag spans about two rounds of
+    the grid at the average number of tiles per expert."""
+    E = len(rows)
+    mt = [(r + 127) // 128 for r in rows]
+    total = sum(m * (n1 + n2) for m in mt)
+    lag = (2 * grid * E + max(total, 1) - 1) // max(total, 1)
+    lag = max(1, min(E, lag))
+    tiles = []
+    for s in range(E + lag):
+        if s < E:
+            tiles += [(s, 0, r % mt[s], r // mt[s]) for r in range(mt[s] * n1)]
+        if s >= lag:
+            e = s - lag
+            tiles += [(e, 1, r % mt[e], r // mt[e]) for r in range(mt[e] * n2)]
+    return lag, tiles
+
+
 class NcclEPMoE:
     """Baseline: NCCL all-to-all dispatch and combine around per-expert GEMMs."""
 

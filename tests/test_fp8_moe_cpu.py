@@ -96,3 +96,35 @@ def test_tensor_parallel_attention_weight_shards_cover_the_heads():
           "o_proj": torch.randn(4 * 8, 32), "q_norm": torch.zeros(8), "k_norm": torch.zeros(8)}
     sp = [shard_gqa_params(gp, 4, 2, 8, r, 2) for r in range(2)]
     assert sp[0]["qkv"].shape == (32, 2 * 2 * 8 + 2 * 2 * 8) and torch.equal(torch.cat([p["o_proj"] for p in sp]), gp["o_proj"])
+
+
+def test_forward_tile_order_keeps_producers_ahead_of_consumers():
+    """Static tile order of the fused expert kernels (host model): every tile appears once, every down-projection
+    tile comes after all gate|up tiles of its rows (so a persistent CTA never waits for a later tile), and with
+    enough work the two are at least a round of CTAs apart."""
+    import random
+    from jax_gpt_b200.parallel.expert_parallel import forward_tile_order
+    rng = random.Random(0)
+    for E, grid, n1, n2 in ((8, 148, 16, 28), (64, 148, 4, 8), (512, 148, 4, 8), (512, 16, 4, 8)):
+        for fill in ("dense", "sparse", "empty"):
+            rows = [0 if fill == "empty" or (fill == "sparse" and rng.random() < 0.8) else rng.randint(1, 400)
+                    for _ in range(E)]
+            lag, tiles = forward_tile_order(rows, n1, n2, grid)
+            assert 1 <= lag <= E
+            expect = sum(((r + 127) // 128) * (n1 + n2) for r in rows)
+            assert len(tiles) == expect == len(set(tiles))
+            last_g1 = {}
+            for t, (e, phase, m, n) in enumerate(tiles):
+                assert 0 <= m < (rows[e] + 127) // 128 and 0 <= n < (n1 if phase == 0 else n2)
+                if phase == 0:
+                    last_g1[(e, m)] = t
+            gaps = [t - last_g1[(e, m)] for t, (e, phase, m, n) in enumerate(tiles) if phase == 1]
+            assert all(g > 0 for g in gaps)
+            if fill == "dense" and expect > 8 * grid:
+                first = {}
+                for t, (e, phase, m, n) in enumerate(tiles):
+                    if phase == 1:
+                        first.setdefault(e, t)
+                # except near the end of the order, an expert's first GEMM2 tile is a round of CTAs behind its GEMM1 tiles
+                early = [first[e] - max(v for (ee, _), v in last_g1.items() if ee == e) for e in first if e < E - lag]
+                assert sorted(early)[len(early) // 2] >= grid      # the lag is sized from the average expert
