@@ -144,3 +144,29 @@ class Qwen35DecodeEngine:
         """The state as a ``HybridCache`` (to continue with the function-style forward)."""
         dt = dtype or self.k.dtype
         return HybridCache(self.M.to(dt), self.conv.to(dt), self.k, self.v, self.pos)
+
+
+@torch.no_grad()
+def generate_with_engine(params, prompt_tokens, config: Qwen35Config, max_new_tokens: int,
+                         max_seq_len: Optional[int] = None, temperature: float = 1.0, top_k: Optional[int] = None,
+                         key=None, cache_dtype=None, ep=None, use_cuda_graph: bool = True):
+    """Same contract as ``model.generate`` (returns ONLY the continuation, shape (B, max_new_tokens); same
+    sampler and random stream), with the decode steps on the in-place engine: prefill through ``forward``, then
+    one engine step (a CUDA-graph replay when ``ep`` is given on a GPU) per token, sampling from its logits."""
+    from .cache import init_cache
+    from .model import _sample, forward
+    B, T = prompt_tokens.shape
+    max_seq_len = max_seq_len or (T + max_new_tokens)
+    gen = key if isinstance(key, torch.Generator) else torch.Generator().manual_seed(int(key) if key is not None else 0)
+    dtype = cache_dtype or params["embed"].dtype
+    cache = init_cache(config, B, max_seq_len, dtype=dtype, device=prompt_tokens.device)
+    logits, cache = forward(params, prompt_tokens, config, cache=cache, is_decode=False, ep_group=ep)
+    nxt = _sample(logits[:, -1], temperature, top_k, gen)
+    out = [nxt]
+    if max_new_tokens > 1:
+        eng = Qwen35DecodeEngine(params, config, cache, ep=ep, use_cuda_graph=use_cuda_graph)
+        for _ in range(max_new_tokens - 1):
+            eng.step(nxt)
+            nxt = _sample(eng.logits, temperature, top_k, gen)
+            out.append(nxt)
+    return torch.stack(out, dim=1)

@@ -240,3 +240,13 @@ def test_decode_engine_matches_function_style_decode(cfg, params):
         back = eng.cache(torch.float32)
         assert torch.allclose(back.delta_M, cache_a.delta_M, atol=1e-5)
         assert torch.allclose(back.gqa_k[:, :, :, :eng.pos], cache_a.gqa_k[:, :, :, :eng.pos], atol=1e-5)
+
+
+def test_generate_with_engine_matches_generate(cfg, params):
+    """Same continuation as ``generate`` for greedy decoding and for sampling with the same seed."""
+    from jax_gpt_b200.models.qwen35.decode_engine import generate_with_engine
+    prompt = torch.randint(0, cfg.vocab_size, (2, 5), generator=torch.Generator().manual_seed(4))
+    for kw in (dict(temperature=0.0), dict(temperature=0.9, top_k=8, key=3)):
+        a = generate(params, prompt, cfg, 6, **kw)
+        b = generate_with_engine(params, prompt, cfg, 6, **kw)
+        assert a.shape == b.shape == (2, 6) and torch.equal(a, b), kw
