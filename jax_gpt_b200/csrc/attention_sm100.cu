@@ -19,6 +19,7 @@
 #include "attention_sm100.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "tma_host.h"
@@ -31,7 +32,10 @@ constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 softmax warps
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct FwdArgs {
-  int B, T, H, Hkv;
+  int B, T, Tk, H, Hkv;     // T queries and Tk keys per sequence
+  int q_pos0;               // position of query 0 (causal rule: key position <= q_pos0 + query index)
+  int kv_rows_b, kv_rows_h; // row of key 0 of (b, hkv) in the K / V matrices = b * kv_rows_b + hkv * kv_rows_h
+  int k_col_h, v_col_h;     // first column of kv head hkv in K / V = hkv * {k,v}_col_h
   float scale_log2;
   int causal;
   __nv_bfloat16* out;
@@ -98,9 +102,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const int q_blk = gridDim.z - 1 - blockIdx.z;
   const int h = blockIdx.x, b = blockIdx.y;
   const int hkv = h / (a.H / a.Hkv);
-  const int n_kv_all = (a.T + 127) / 128;
-  const int n_kv = a.causal ? min(q_blk + 1, n_kv_all) : n_kv_all;
+  const int n_kv_all = (a.Tk + 127) / 128;
+  const int n_kv = a.causal ? min((a.q_pos0 + q_blk * 128 + 127) / 128 + 1, n_kv_all) : n_kv_all;
   const int row0 = b * a.T + q_blk * 128;
+  const int kv_row0 = b * a.kv_rows_b + hkv * a.kv_rows_h;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -139,8 +144,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         }
         uint8_t* sK = smem + C::kOffK + s * C::kStageBytes;
         mbar_arrive_expect_tx(&bars->kv_full[s], C::kStageBytes);
-        load_tile<D>(sK, &tk, &bars->kv_full[s], hkv * D, b * a.T + j * 128);
-        load_tile<DV>(sK + C::kQTile, &tv, &bars->kv_full[s], hkv * DV, b * a.T + j * 128);
+        load_tile<D>(sK, &tk, &bars->kv_full[s], hkv * a.k_col_h, kv_row0 + j * 128);
+        load_tile<DV>(sK + C::kQTile, &tv, &bars->kv_full[s], hkv * a.v_col_h, kv_row0 + j * 128);
       }
     }
   } else if (warp == 1) {
@@ -194,7 +199,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     const int r = q * 32 + lane;  // query row inside the block == TMEM lane
-    const int qpos = q_blk * 128 + r;
+    const int qi = q_blk * 128 + r;      // query index inside the sequence
+    const int qpos = a.q_pos0 + qi;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     __nv_bfloat16* xchg = reinterpret_cast<__nv_bfloat16*>(smem + C::kOffXchg);  // [2][128]
     constexpr int DH = DV / 2;
@@ -210,7 +216,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         break;
       }
       tc_fence_after();
-      const bool need_mask = (a.causal && j == q_blk) || ((j + 1) * 128 > a.T);
+      const bool need_mask = (a.causal && j * 128 + 127 > a.q_pos0 + q_blk * 128) || ((j + 1) * 128 > a.Tk);
       const int kv0 = j * 128 + half * 64;
       float mx = -INFINITY;
 #pragma unroll 1
@@ -223,7 +229,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           float s = __uint_as_float(v[i]);   // the (positive) softmax scale is applied to the maximum once, below
           if (need_mask) {
             const int kvpos = kv0 + c * 32 + i;
-            if (kvpos >= a.T || (a.causal && kvpos > qpos)) s = -INFINITY;
+            if (kvpos >= a.Tk || (a.causal && kvpos > qpos)) s = -INFINITY;
           }
           mx = fmaxf(mx, s);
         }
@@ -253,8 +259,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           float s0 = fmaf(__uint_as_float(v[i]), a.scale_log2, -mref), s1 = fmaf(__uint_as_float(v[i + 1]), a.scale_log2, -mref);
           if (need_mask) {
             const int kvpos = kv0 + c * 32 + i;
-            if (kvpos >= a.T || (a.causal && kvpos > qpos)) s0 = -INFINITY;
-            if (kvpos + 1 >= a.T || (a.causal && kvpos + 1 > qpos)) s1 = -INFINITY;
+            if (kvpos >= a.Tk || (a.causal && kvpos > qpos)) s0 = -INFINITY;
+            if (kvpos + 1 >= a.Tk || (a.causal && kvpos + 1 > qpos)) s1 = -INFINITY;
           }
           const float p0 = exp2f(s0), p1 = exp2f(s1);
           rs += p0 + p1;
@@ -291,16 +297,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       if (!mbar_wait(&bars->x_ready, n_kv & 1, abort_flag)) ok = false;
       if (ok) l += lsum[(half ^ 1) * 128 + r];
     }
-    if (ok && qpos < a.T) {
+    if (ok && qi < a.T) {
       const float inv = (l > 0.f) ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = a.out + static_cast<int64_t>(b * a.T + qpos) * a.ldo + h * DV + half * DH;
+      __nv_bfloat16* orow = a.out + static_cast<int64_t>(b * a.T + qi) * a.ldo + h * DV + half * DH;
 #pragma unroll
       for (int i = 0; i < DH; i += 8) {
         uint4 pk = make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
                               pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv));
         *reinterpret_cast<uint4*>(orow + i) = pk;
       }
-      if (a.lse != nullptr && half == 0) a.lse[(static_cast<int64_t>(b) * a.H + h) * a.T + qpos] = m + log2f(l);
+      if (a.lse != nullptr && half == 0) a.lse[(static_cast<int64_t>(b) * a.H + h) * a.T + qi] = m + log2f(l);
     }
   }
 
@@ -726,15 +732,15 @@ cudaError_t make_map(CUtensorMap* m, const __nv_bfloat16* p, int64_t ld, int row
 }
 
 template <int D, int DV>
-cudaError_t fwd_launch(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* out, int64_t ldo, float* lse,
-                       int* status, cudaStream_t stream) {
+cudaError_t fwd_launch(const AttnTensors& t, const AttnShape& s, const AttnKvLayout& kv, __nv_bfloat16* out,
+                       int64_t ldo, float* lse, int* status, cudaStream_t stream) {
   using C = FwdCfg<D, DV>;
   CUtensorMap tq, tk, tv;
   const int rows = s.B * s.T;
   cudaError_t e;
   if ((e = make_map(&tq, t.q, t.ldq, rows, s.H * D)) != cudaSuccess) return e;
-  if ((e = make_map(&tk, t.k, t.ldk, rows, s.Hkv * D)) != cudaSuccess) return e;
-  if ((e = make_map(&tv, t.v, t.ldv, rows, s.Hkv * DV)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tk, t.k, 2, kv.k_cols, kv.rows, t.ldk * 2, 64, 128)) != cudaSuccess) return e;
+  if ((e = encode_tma_2d(&tv, t.v, 2, kv.v_cols, kv.rows, t.ldv * 2, 64, 128)) != cudaSuccess) return e;
   auto kernel = attn_fwd_kernel<D, DV>;
   static bool configured = false;
   if (!configured) {
@@ -742,7 +748,8 @@ cudaError_t fwd_launch(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* 
       return e;
     configured = true;
   }
-  FwdArgs a{s.B, s.T, s.H, s.Hkv, s.scale * kLog2e, s.causal, out, ldo, lse, status};
+  FwdArgs a{s.B, s.T, kv.Tk, s.H, s.Hkv, kv.q_pos0, kv.rows_b, kv.rows_h, kv.k_col_h, kv.v_col_h,
+            s.scale * kLog2e, s.causal, out, ldo, lse, status};
   dim3 grid(s.H, s.B, (s.T + 127) / 128);
   kernel<<<grid, kThreads, C::kSmem, stream>>>(tq, tk, tv, a);
   return cudaGetLastError();
@@ -767,6 +774,15 @@ cudaError_t bwd_launch(const AttnTensors& t, const AttnShape& s, const __nv_bflo
     attn_delta_kernel<D><<<blocks, 256, 0, stream>>>(out, ldo, dout, lddo, delta, s.B, s.T, s.H);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
   }
+  if (D == 64) {
+    // pipelined half-tile kernel unless the single-stage one is asked for (B200_ATTN_BWD=1stage)
+    static const bool one_stage = [] {
+      const char* ev = getenv("B200_ATTN_BWD");
+      return ev != nullptr && ev[0] == '1';
+    }();
+    if (!one_stage)
+      return launch_attn_bwd2_d64(t, s, dout, lddo, lse, delta, dq_accum, dk, lddk, dv, lddv, status, stream);
+  }
   auto kernel = attn_bwd_kernel<D>;
   static bool configured = false;
   if (!configured) {
@@ -782,15 +798,39 @@ cudaError_t bwd_launch(const AttnTensors& t, const AttnShape& s, const __nv_bflo
 
 }  // namespace
 
-cudaError_t launch_attn_fwd(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* out, int64_t ldo, float* lse,
-                            int* status, cudaStream_t stream) {
+cudaError_t launch_attn_fwd_kv(const AttnTensors& t, const AttnShape& s, const AttnKvLayout& kv, __nv_bfloat16* out,
+                               int64_t ldo, float* lse, int* status, cudaStream_t stream) {
   if (s.H % s.Hkv != 0) return cudaErrorInvalidValue;
   const int dv = s.Dv > 0 ? s.Dv : s.D;
-  if (s.D == 64 && dv == 64) return fwd_launch<64, 64>(t, s, out, ldo, lse, status, stream);
-  if (s.D == 128 && dv == 128) return fwd_launch<128, 128>(t, s, out, ldo, lse, status, stream);
-  if (s.D == 256 && dv == 256) return fwd_launch<256, 256>(t, s, out, ldo, lse, status, stream);
-  if (s.D == 192 && dv == 128) return fwd_launch<192, 128>(t, s, out, ldo, lse, status, stream);
+  if (s.D == 64 && dv == 64) {
+    // two-tile kernel unless the single-tile one is asked for (B200_ATTN_FWD=1tile: comparisons, fallback)
+    static const bool one_tile = [] {
+      const char* e = getenv("B200_ATTN_FWD");
+      return e != nullptr && e[0] == '1';
+    }();
+    if (!one_tile) return launch_attn_fwd2_d64(t, s, kv, out, ldo, lse, status, stream);
+    return fwd_launch<64, 64>(t, s, kv, out, ldo, lse, status, stream);
+  }
+  if (s.D == 128 && dv == 128) return fwd_launch<128, 128>(t, s, kv, out, ldo, lse, status, stream);
+  if (s.D == 256 && dv == 256) return fwd_launch<256, 256>(t, s, kv, out, ldo, lse, status, stream);
+  if (s.D == 192 && dv == 128) return fwd_launch<192, 128>(t, s, kv, out, ldo, lse, status, stream);
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_attn_fwd(const AttnTensors& t, const AttnShape& s, __nv_bfloat16* out, int64_t ldo, float* lse,
+                            int* status, cudaStream_t stream) {
+  const int dv = s.Dv > 0 ? s.Dv : s.D;
+  AttnKvLayout kv;
+  kv.Tk = s.T;
+  kv.q_pos0 = 0;
+  kv.rows_b = s.T;
+  kv.rows_h = 0;
+  kv.k_col_h = s.D;
+  kv.v_col_h = dv;
+  kv.rows = static_cast<uint64_t>(s.B) * s.T;
+  kv.k_cols = static_cast<uint64_t>(s.Hkv) * s.D;
+  kv.v_cols = static_cast<uint64_t>(s.Hkv) * dv;
+  return launch_attn_fwd_kv(t, s, kv, out, ldo, lse, status, stream);
 }
 
 cudaError_t launch_attn_bwd(const AttnTensors& t, const AttnShape& s, const __nv_bfloat16* out, int64_t ldo,
@@ -803,6 +843,19 @@ cudaError_t launch_attn_bwd(const AttnTensors& t, const AttnShape& s, const __nv
   if (s.D == 128)
     return bwd_launch<128>(t, s, out, ldo, dout, lddo, lse, delta, dq_accum, dk, lddk, dv, lddv, status, stream);
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_attn_delta(const __nv_bfloat16* out, int64_t ldo, const __nv_bfloat16* dout, int64_t lddo,
+                              float* delta, int B, int T, int H, int Dv, cudaStream_t stream) {
+  const int64_t rows = static_cast<int64_t>(B) * T;
+  const int blocks = static_cast<int>((rows * 32 + 255) / 256);
+  switch (Dv) {
+    case 64: attn_delta_kernel<64><<<blocks, 256, 0, stream>>>(out, ldo, dout, lddo, delta, B, T, H); break;
+    case 128: attn_delta_kernel<128><<<blocks, 256, 0, stream>>>(out, ldo, dout, lddo, delta, B, T, H); break;
+    case 256: attn_delta_kernel<256><<<blocks, 256, 0, stream>>>(out, ldo, dout, lddo, delta, B, T, H); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
 }
 
 cudaError_t launch_cast_rows_f32_bf16(const float* src, int64_t lds, __nv_bfloat16* dst, int64_t ldd, int M, int N,

@@ -303,6 +303,98 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
                                         cur_stream()));
 }
 
+// Forward with keys / values read from a cache (B, Hkv, max_len, D) and queries at positions q_pos0 + i.
+// q, out: 2-D views [B*Tq, H*D]; kcache, vcache: 4-D bf16 with contiguous rows of D (Dv) elements.
+void attn_fwd_cached(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor out, Tensor lse, int64_t B,
+                     int64_t Tq, int64_t H, int64_t Tk, int64_t q_pos0, double scale, bool causal) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16_2d(q, "q");
+  check_bf16_2d(out, "out");
+  TORCH_CHECK(kcache.dim() == 4 && vcache.dim() == 4 && kcache.scalar_type() == at::kBFloat16 &&
+                  vcache.scalar_type() == at::kBFloat16 && kcache.is_contiguous() && vcache.is_contiguous(),
+              "attn_fwd_cached: caches must be contiguous bf16 (B, Hkv, max_len, D)");
+  const int64_t Hkv = kcache.size(1), max_len = kcache.size(2), D = kcache.size(3), Dv = vcache.size(3);
+  TORCH_CHECK(kcache.size(0) >= B && vcache.size(0) == kcache.size(0) && vcache.size(1) == Hkv &&
+                  vcache.size(2) == max_len && Tk <= max_len && q_pos0 >= 0,
+              "attn_fwd_cached: cache shape");
+  b200::AttnTensors t{bf16_ptr(q), bf16_ptr(kcache), bf16_ptr(vcache), q.stride(0), D, Dv};
+  b200::AttnShape s{static_cast<int>(B), static_cast<int>(Tq), static_cast<int>(H), static_cast<int>(Hkv),
+                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0, static_cast<int>(Dv)};
+  b200::AttnKvLayout kv;
+  kv.Tk = static_cast<int>(Tk);
+  kv.q_pos0 = static_cast<int>(q_pos0);
+  kv.rows_b = static_cast<int>(Hkv * max_len);
+  kv.rows_h = static_cast<int>(max_len);
+  kv.k_col_h = 0;
+  kv.v_col_h = 0;
+  kv.rows = static_cast<uint64_t>(kcache.size(0) * Hkv * max_len);
+  kv.k_cols = static_cast<uint64_t>(D);
+  kv.v_cols = static_cast<uint64_t>(Dv);
+  B200_CHECK_CUDA(b200::launch_attn_fwd_kv(t, s, kv, bf16_mut(out), out.stride(0), lse.data_ptr<float>(),
+                                           status_ptr(q), cur_stream()));
+}
+
+// Gradients for the wide heads: (D, Dv) = (256, 256) or (192, 128).
+void attn_bwd_wide(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& dout,
+                   const Tensor& lse, Tensor delta, Tensor dq_accum, Tensor dk, Tensor dv, int64_t B, int64_t T,
+                   int64_t H, int64_t Hkv, int64_t D, int64_t Dv, double scale, bool causal) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16_2d(q, "q");
+  check_bf16_2d(k, "k");
+  check_bf16_2d(v, "v");
+  check_bf16_2d(out, "out");
+  check_bf16_2d(dout, "dout");
+  check_bf16_2d(dk, "dk");
+  check_bf16_2d(dv, "dv");
+  TORCH_CHECK(dq_accum.scalar_type() == at::kFloat && dq_accum.is_contiguous() && dq_accum.numel() == B * T * H * D,
+              "attn_bwd_wide: dq_accum fp32 contiguous [B*T, H*D]");
+  TORCH_CHECK(delta.scalar_type() == at::kFloat && delta.numel() == B * H * T && lse.scalar_type() == at::kFloat &&
+                  lse.numel() == B * H * T,
+              "attn_bwd_wide: lse / delta fp32 [B, H, T]");
+  b200::AttnTensors t{bf16_ptr(q), bf16_ptr(k), bf16_ptr(v), q.stride(0), k.stride(0), v.stride(0)};
+  b200::AttnShape s{static_cast<int>(B), static_cast<int>(T), static_cast<int>(H), static_cast<int>(Hkv),
+                    static_cast<int>(D), static_cast<float>(scale), causal ? 1 : 0, static_cast<int>(Dv)};
+  B200_CHECK_CUDA(b200::launch_attn_delta(bf16_ptr(out), out.stride(0), bf16_ptr(dout), dout.stride(0),
+                                          delta.data_ptr<float>(), s.B, s.T, s.H, s.Dv, cur_stream()));
+  B200_CHECK_CUDA(b200::launch_attn_bwd_wide(t, s, bf16_ptr(dout), dout.stride(0), lse.data_ptr<float>(),
+                                             delta.data_ptr<float>(), dq_accum.data_ptr<float>(), bf16_mut(dk),
+                                             dk.stride(0), bf16_mut(dv), dv.stride(0), status_ptr(q), cur_stream()));
+}
+
+// One query token per sequence against a dense cache. q, out: [B, H*D]; caches (B', Hkv, max_len, D) bf16 with
+// unit inner stride; pos: optional int32 device scalar (valid keys = pos + len_add), else `len` keys.
+void attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcache, const c10::optional<Tensor>& pos,
+                 int64_t len, int64_t len_add, int64_t H, double scale, Tensor part_o, Tensor part_ml, Tensor out) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16_2d(q, "q");
+  check_bf16_2d(out, "out");
+  TORCH_CHECK(kcache.dim() == 4 && kcache.scalar_type() == at::kBFloat16 && kcache.stride(3) == 1 &&
+                  vcache.scalar_type() == at::kBFloat16 && vcache.sizes() == kcache.sizes() &&
+                  vcache.strides() == kcache.strides(),
+              "attn_decode: caches must be bf16 (B, Hkv, max_len, D) with equal strides and unit inner stride");
+  const int64_t B = q.size(0), Hkv = kcache.size(1), D = kcache.size(3);
+  TORCH_CHECK(q.size(1) == H * D && out.size(0) == B && out.size(1) == H * D && kcache.size(0) >= B,
+              "attn_decode: q / out must be [B, H*D]");
+  TORCH_CHECK(part_o.scalar_type() == at::kFloat && part_ml.scalar_type() == at::kFloat && part_o.is_contiguous() &&
+                  part_ml.is_contiguous() && part_o.dim() == 4 && part_o.size(0) >= B && part_o.size(1) == H &&
+                  part_o.size(3) == D && part_ml.numel() * D == part_o.numel() * 2,
+              "attn_decode: part_o [B, H, splits, D], part_ml [B, H, splits, 2] fp32");
+  const int n_splits = static_cast<int>(part_o.size(2));
+  const int* pp = nullptr;
+  if (pos.has_value()) {
+    TORCH_CHECK(pos->scalar_type() == at::kInt && pos->is_cuda(), "attn_decode: pos must be an int32 device tensor");
+    pp = pos->data_ptr<int>();
+  } else {
+    TORCH_CHECK(len <= kcache.size(2), "attn_decode: len exceeds the cache");
+  }
+  B200_CHECK_CUDA(b200::launch_attn_decode(bf16_ptr(q), q.stride(0), bf16_ptr(kcache), bf16_ptr(vcache),
+                                           kcache.stride(0), kcache.stride(1), kcache.stride(2), pp,
+                                           static_cast<int>(len), static_cast<int>(len_add), static_cast<int>(B),
+                                           static_cast<int>(H), static_cast<int>(Hkv), static_cast<int>(D),
+                                           static_cast<float>(scale), n_splits, part_o.data_ptr<float>(),
+                                           part_ml.data_ptr<float>(), bf16_mut(out), out.stride(0), cur_stream()));
+}
+
 void attn_bwd_probs(Tensor s, Tensor dp, const Tensor& lse, const Tensor& delta, int64_t c, int64_t q0, double scale,
                     bool causal) {
   c10::cuda::CUDAGuard guard(s.device());
@@ -374,6 +466,19 @@ TORCH_LIBRARY(b200, m) {
       "dq_accum, Tensor(c!) dk, Tensor(d!) dv, int B, int T, int H, int Hkv, int D, float scale, bool causal) -> ()",
       &attn_bwd);
   m.def("cast_rows(Tensor src, Tensor(a!) dst) -> ()", &cast_rows);
+  m.def(
+      "attn_fwd_cached(Tensor q, Tensor kcache, Tensor vcache, Tensor(a!) out, Tensor(b!) lse, int B, int Tq, int H, "
+      "int Tk, int q_pos0, float scale, bool causal) -> ()",
+      &attn_fwd_cached);
+  m.def(
+      "attn_bwd_wide(Tensor q, Tensor k, Tensor v, Tensor out, Tensor dout, Tensor lse, Tensor(a!) delta, Tensor(b!) "
+      "dq_accum, Tensor(c!) dk, Tensor(d!) dv, int B, int T, int H, int Hkv, int D, int Dv, float scale, bool causal) "
+      "-> ()",
+      &attn_bwd_wide);
+  m.def(
+      "attn_decode(Tensor q, Tensor kcache, Tensor vcache, Tensor? pos, int len, int len_add, int H, float scale, "
+      "Tensor(a!) part_o, Tensor(b!) part_ml, Tensor(c!) out) -> ()",
+      &attn_decode);
   m.def("attn_bwd_probs(Tensor(a!) s, Tensor(b!) dp, Tensor lse, Tensor delta, int c, int q0, float scale, bool causal) -> ()", &attn_bwd_probs);
   m.def("norm_bwd_scratch_floats(int D) -> int", [](int64_t D) { return b200::norm_bwd_scratch_floats(static_cast<int>(D)); });
   m.def("gemm_uses_pair(int M, int N, int split_k) -> bool", [](int64_t M, int64_t N, int64_t split_k) {

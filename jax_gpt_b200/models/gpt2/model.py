@@ -127,9 +127,12 @@ class GPT:
             # cache layout (B, H, ctx, dh); write the new rows, attend over the filled prefix
             cache_k[:, :, pos:pos + T] = k.permute(0, 2, 1, 3)
             cache_v[:, :, pos:pos + T] = v.permute(0, 2, 1, 3)
-            kk = cache_k[:, :, :pos + T].permute(0, 2, 1, 3)
-            vv = cache_v[:, :, :pos + T].permute(0, 2, 1, 3)
-            y = attn_ops.attention_ref(q, kk, vv, causal=True, q_pos0=pos)
+            if T == 1:
+                y = attn_ops.attention_decode(q[:, 0], cache_k, cache_v, kv_len=pos + 1)[:, None]
+            elif pos == 0:
+                y = attn_ops.attention(q, k, v, causal=True)
+            else:
+                y = attn_ops.attention_cached(q, cache_k, cache_v, pos + T, pos)
             new_k, new_v = cache_k, cache_v
         else:
             y = attn_ops.attention(q, k, v, causal=True)

@@ -8,8 +8,8 @@ device memory:
 * the Gated-DeltaNet states and conv windows are fp32 buffers updated in place by the fused decode kernel
   (csrc/seq_kernels.cu: conv window, gates, delta rule, gated RMSNorm in one launch per layer);
 * the position is a device scalar: rotary angles are gathered with it, the new key / value row is written with
-  ``index_copy_`` and the attention of the gated-attention layers runs over the whole (fixed-size) cache with the
-  positions past it masked, so every shape is static;
+  ``index_copy_`` and the attention of the gated-attention layers is the split-KV decode kernel
+  (csrc/attention_decode.cu), which reads the number of valid keys from that scalar, so every shape is static;
 * the routed experts go through the fused dispatch / grouped GEMM / combine kernel when an expert runtime is
   given (a launch per expert otherwise, which cannot be captured: the engine then runs eagerly);
 * embedding, all layers, the head, the arg-max and the position increment are captured in one CUDA graph the
@@ -24,6 +24,7 @@ from typing import Optional
 
 import torch
 
+from ...ops import attention as attn_ops
 from .block import _slice
 from .cache import HybridCache
 from .config import Qwen35Config
@@ -46,9 +47,17 @@ class Qwen35DecodeEngine:
         self.M = cache.delta_M.float().contiguous()          # (G, nd, B, Hv, dk, dv)
         self.conv = cache.delta_conv.float().contiguous()    # (G, nd, B, conv_dim, K)
         self.k, self.v = cache.gqa_k, cache.gqa_v            # (G, B, Hkv, max_len, dh)
+        act_dtype = params["embed"].dtype
+        if self.device.type == "cuda" and act_dtype == torch.bfloat16 and self.k.dtype != torch.bfloat16:
+            # the decode kernel streams a bf16 cache; a cache of another type is converted once and owned here
+            self.k, self.v = self.k.to(torch.bfloat16), self.v.to(torch.bfloat16)
         self.pos = int(cache.pos)
         self.pos_t = torch.tensor([self.pos], device=self.device, dtype=torch.long)
-        self.cols = torch.arange(self.max_len, device=self.device)
+        self.pos_i32 = torch.tensor([self.pos], device=self.device, dtype=torch.int32)
+        n_splits = attn_ops.decode_splits(self.B, c.gqa_n_kv_heads, self.max_len)
+        self.dec_scratch = (torch.empty(self.B, c.gqa_n_q_heads, n_splits, c.gqa_head_dim, device=self.device,
+                                        dtype=torch.float32),
+                            torch.empty(self.B, c.gqa_n_q_heads, n_splits, 2, device=self.device, dtype=torch.float32))
         self.rope = precompute_rope_freqs(c.gqa_rope_dim, self.max_len, c.gqa_rope_theta, device=self.device)
         self.tokens = torch.zeros(self.B, device=self.device, dtype=torch.long)
         self.next_tokens = torch.zeros(self.B, device=self.device, dtype=torch.long)
@@ -88,12 +97,8 @@ class Qwen35DecodeEngine:
         ck, cv = self.k[gi], self.v[gi]                                              # (B, Hkv, max_len, dh)
         ck.index_copy_(2, self.pos_t, k.permute(0, 2, 1, 3).to(ck.dtype))
         cv.index_copy_(2, self.pos_t, v.permute(0, 2, 1, 3).to(cv.dtype))
-        g = Hq // Hkv
-        qh = q.reshape(B, Hkv, g, dh).float()
-        s = torch.matmul(qh, ck.float().transpose(2, 3)) * (dh ** -0.5)               # (B, Hkv, g, max_len)
-        s = s.masked_fill(self.cols > self.pos_t, float("-inf"))
-        o = torch.matmul(torch.softmax(s, dim=-1), cv.float())                        # (B, Hkv, g, dh)
-        o = (o.reshape(B, Hq, dh) * torch.sigmoid(gate[:, 0].float())).to(x.dtype)
+        o = attn_ops.attention_decode(q.reshape(B, Hq, dh), ck, cv, pos=self.pos_i32, scratch=self.dec_scratch)
+        o = (o.float() * torch.sigmoid(gate[:, 0].float())).to(x.dtype)
         return self._moe(x + matmul_maybe_fp8(o.reshape(B, Hq * dh), ap["o_proj"]), lp)
 
     def _token_step(self):
@@ -107,6 +112,7 @@ class Qwen35DecodeEngine:
         logits = matmul_maybe_fp8(rms_norm(x, p["final_norm"], c.rms_norm_eps), p["lm_head"])
         self.next_tokens.copy_(logits.argmax(-1))
         self.pos_t.add_(1)
+        self.pos_i32.add_(1)
         return logits
 
     # ---- public ---------------------------------------------------------------------------------------
@@ -131,6 +137,7 @@ class Qwen35DecodeEngine:
             self.M.copy_(saved[0])
             self.conv.copy_(saved[1])
             self.pos_t.copy_(saved[2])
+            self.pos_i32.copy_(saved[2])
             self._graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self._graph):
                 self.logits = self._token_step()

@@ -37,9 +37,14 @@ def gqa_attention(x, params, n_q_heads: int, n_kv_heads: int, head_dim: int, rop
     if cache_k is not None:
         cache_k[:, :, pos:pos + T] = k.permute(0, 2, 1, 3).to(cache_k.dtype)
         cache_v[:, :, pos:pos + T] = v.permute(0, 2, 1, 3).to(cache_v.dtype)
-        kk = cache_k[:, :, :pos + T].permute(0, 2, 1, 3).to(q.dtype)
-        vv = cache_v[:, :, :pos + T].permute(0, 2, 1, 3).to(q.dtype)
-        out = attn_ops.attention_ref(q, kk, vv, causal=True, q_pos0=pos)
+        if T == 1:
+            # decode: one token per sequence against the filled prefix of the cache, split over the keys
+            out = attn_ops.attention_decode(q[:, 0], cache_k, cache_v, kv_len=pos + 1)[:, None]
+        elif pos == 0:
+            out = attn_ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), causal=True)
+        else:
+            # a later chunk of a prompt: the forward kernel reads the cache in place, queries at pos + i
+            out = attn_ops.attention_cached(q.contiguous(), cache_k, cache_v, pos + T, pos)
     else:
         out = attn_ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), causal=True)
     out = out * torch.sigmoid(gate.float()).to(out.dtype)

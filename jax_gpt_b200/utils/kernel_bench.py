@@ -50,6 +50,8 @@ def main(argv=None):
     ap.add_argument("--T", type=int, default=1024)
     ap.add_argument("--H", type=int, default=12)
     ap.add_argument("--D", type=int, default=64)
+    ap.add_argument("--Dv", type=int, default=0, help="attention: v head width when it differs from --D")
+    ap.add_argument("--Hkv", type=int, default=0, help="attention: kv heads (default: --H)")
     ap.add_argument("--splits", type=int, default=0, help="mla_decode: KV splits per sequence (0 = fill the SMs)")
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays (excludes host launch overhead)")
     ap.add_argument("--warmup", type=int, default=3)
@@ -67,25 +69,42 @@ def main(argv=None):
         flops, bytes_ = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
     elif args.op in ("attn_fwd", "attn_bwd"):
         B, T, H, D = args.B, args.T, args.H, args.D
-        qkv = torch.randn(B, T, 3 * H * D, device=dev).to(torch.bfloat16)
-        q, k, v = [qkv[..., i * H * D:(i + 1) * H * D].unflatten(-1, (H, D)) for i in range(3)]
+        Hkv, Dv = args.Hkv or H, args.Dv or D
+        if Hkv == H and Dv == D:
+            qkv = torch.randn(B, T, 3 * H * D, device=dev).to(torch.bfloat16)
+            q, k, v = [qkv[..., i * H * D:(i + 1) * H * D].unflatten(-1, (H, D)) for i in range(3)]
+        else:
+            q = torch.randn(B, T, H, D, device=dev).to(torch.bfloat16)
+            k = torch.randn(B, T, Hkv, D, device=dev).to(torch.bfloat16)
+            v = torch.randn(B, T, Hkv, Dv, device=dev).to(torch.bfloat16)
         out, lse = A.attn_fwd(q, k, v)
-        base = 4.0 * B * H * T * T * D / 2
+        base = 2.0 * B * H * T * T * (D + Dv) / 2          # causal: S = Q K^T and O = P V
         if args.op == "attn_fwd":
             fn = lambda: A.attn_fwd(q, k, v, out=out, lse=lse)
             flops = base
         else:
             dout = torch.randn_like(out)
-            dqkv = torch.empty_like(qkv)
-            dq, dk, dv = [dqkv[..., i * H * D:(i + 1) * H * D].unflatten(-1, (H, D)) for i in range(3)]
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
             acc = torch.zeros(B * T, H * D, device=dev)
             delta = torch.empty(B, H, T, device=dev)
 
             def fn():
                 acc.zero_()
                 A.attn_bwd(q, k, v, out, dout, lse, dq=dq, dk=dk, dv=dv, dq_accum=acc, delta=delta)
-            flops = 2.5 * base
-        bytes_ = 2.0 * 4 * B * T * H * D
+            flops = 2.0 * B * H * T * T * (3 * D + 2 * Dv) / 2  # S, dP, dV, dK, dQ
+        bytes_ = 2.0 * B * T * (2 * H * D + 2 * Hkv * D + 2 * Hkv * Dv + 2 * H * Dv)
+    elif args.op == "attn_decode":
+        B, T, H, D = args.B, args.T, args.H, args.D
+        Hkv = args.Hkv or H
+        ck = torch.randn(B, Hkv, T, D, device=dev).to(torch.bfloat16)
+        cv = torch.randn(B, Hkv, T, D, device=dev).to(torch.bfloat16)
+        q = torch.randn(B, H, D, device=dev).to(torch.bfloat16)
+        S = args.splits or A.decode_splits(B, Hkv, T)
+        scratch = (torch.empty(B, H, S, D, device=dev), torch.empty(B, H, S, 2, device=dev))
+        out = torch.empty(B, H * D, device=dev, dtype=torch.bfloat16)
+        fn = lambda: A.attention_decode(q, ck, cv, kv_len=T, scratch=scratch, out=out)
+        flops = 4.0 * B * H * T * D
+        bytes_ = 2.0 * 2 * B * Hkv * T * D
     elif args.op in ("norm_fwd", "norm_bwd"):
         M, D = args.M, args.N if args.N <= 8192 else 768
         x = torch.randn(M, D, device=dev).to(torch.bfloat16)

@@ -208,11 +208,13 @@ def test_attention_fwd_bwd(cuda_device, B, T, H, Hkv, D, causal):
     assert _rel_err(q.grad, qr.grad) < 3e-2
 
 
-@pytest.mark.parametrize("B,T,H,Hkv,D,Dv", [(2, 256, 4, 2, 256, 256), (1, 384, 4, 4, 192, 128)])
+@pytest.mark.parametrize("B,T,H,Hkv,D,Dv", [(2, 256, 4, 2, 256, 256), (1, 384, 4, 4, 192, 128),
+                                            (1, 200, 8, 1, 256, 256), (2, 330, 2, 2, 192, 128),
+                                            (1, 64, 2, 2, 256, 256), (1, 1024, 2, 1, 192, 128)])
 def test_attention_wide_heads_gradients(cuda_device, B, T, H, Hkv, D, Dv):
-    """Head widths without a tensor-core backward kernel (gated attention 256, MLA 192 / 128): forward kernel,
-    gradients from the recomputation (batched matmuls + the in-place probability / dS kernel), against autograd of
-    the fp32 reference; also with a small chunk so that the key / value gradients accumulate over chunks."""
+    """Wide heads (gated attention 256, MLA 192 / 128): forward kernel and the 64-query-tile backward kernel
+    against autograd of the fp32 reference; the library-matmul recomputation is checked against the same
+    gradients (with a small chunk, so that the key / value gradients accumulate over chunks)."""
     from jax_gpt_b200.ops import attention as A
     torch.manual_seed(9)
     q = torch.randn(B, T, H, D, device=cuda_device).to(torch.bfloat16).requires_grad_()
