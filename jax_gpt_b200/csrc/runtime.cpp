@@ -20,6 +20,7 @@
 #include <memory>
 #include <mutex>
 #include <sstream>
+#include <set>
 #include <string>
 #include <thread>
 #include <unordered_map>
@@ -215,10 +216,26 @@ class AsyncWriter {
   static void write_all(FILE* f, const void* p, size_t n, const std::string& path) {
     TORCH_CHECK(fwrite(p, 1, n, f) == n, "AsyncWriter: short write to ", path);
   }
+  // The files of one checkpoint share a directory: once a job of a directory has failed, the later jobs of that
+  // directory (above all its manifest, which marks the checkpoint complete) are dropped.
+  static std::string dir_of(const std::string& path) {
+    const size_t p = path.find_last_of('/');
+    return p == std::string::npos ? std::string(".") : path.substr(0, p);
+  }
+  struct FileCloser {
+    FILE* f;
+    std::string tmp;
+    bool keep = false;
+    ~FileCloser() {
+      if (f != nullptr) fclose(f);
+      if (!keep) remove(tmp.c_str());
+    }
+  };
   void do_job(const WriteJob& j) {
     const std::string tmp = j.path + ".tmp";
     FILE* f = fopen(tmp.c_str(), "wb");
     TORCH_CHECK(f != nullptr, "AsyncWriter: cannot open ", tmp);
+    FileCloser guard{f, tmp};   // closes the file and removes the partial ".tmp" if anything below throws
     if (!j.raw.empty()) {
       write_all(f, j.raw.data(), j.raw.size(), tmp);
     } else {
@@ -243,26 +260,33 @@ class AsyncWriter {
       for (const Tensor& t : j.tensors)
         write_all(f, t.data_ptr(), static_cast<size_t>(t.numel()) * t.element_size(), tmp);
     }
-    fflush(f);
-    fsync(fileno(f));
-    fclose(f);
+    TORCH_CHECK(fflush(f) == 0 && fsync(fileno(f)) == 0, "AsyncWriter: flush failed for ", tmp);
+    const int rc = fclose(f);
+    guard.f = nullptr;
+    TORCH_CHECK(rc == 0, "AsyncWriter: close failed for ", tmp);
     TORCH_CHECK(rename(tmp.c_str(), j.path.c_str()) == 0, "AsyncWriter: rename failed for ", j.path);
+    guard.keep = true;
   }
   void run() {
     while (true) {
       WriteJob job;
+      bool skip = false;
       {
         std::unique_lock<std::mutex> l(mu_);
         cv_.wait(l, [this] { return stop_ || !jobs_.empty(); });
         if (jobs_.empty()) return;
         job = std::move(jobs_.front());
         jobs_.pop_front();
+        skip = failed_dirs_.count(dir_of(job.path)) > 0;
       }
-      try {
-        do_job(job);
-      } catch (const std::exception& e) {
-        std::lock_guard<std::mutex> l(mu_);
-        error_ = e.what();
+      if (!skip) {
+        try {
+          do_job(job);
+        } catch (const std::exception& e) {
+          std::lock_guard<std::mutex> l(mu_);
+          if (error_.empty()) error_ = e.what();
+          failed_dirs_.insert(dir_of(job.path));
+        }
       }
       {
         std::lock_guard<std::mutex> l(mu_);
@@ -277,6 +301,7 @@ class AsyncWriter {
   int64_t pending_ = 0;
   bool stop_ = false;
   std::string error_;
+  std::set<std::string> failed_dirs_;
   std::thread worker_;
 };
 

@@ -74,13 +74,23 @@ def test_pipeline_1f1b_matches_single_process():
 def _wd_worker(rank, world, path, result_path):
     from jax_gpt_b200.utils.watchdog import PeerFailure, Watchdog
     store = dist.FileStore(path, world)
-    wd = Watchdog(store, rank, world, interval=0.1, timeout=1.0).start()
+    wd = Watchdog(store, rank, world, interval=0.1, timeout=1.0, startup_grace=60.0).start()
+    # every rank waits until it has seen the first beat of all the others (start-up skew is not a failure)
+    t0 = time.time()
+    while time.time() - t0 < 50 and len(wd.peers_seen()) < world - 1:
+        time.sleep(0.05)
+    store.set(f"ready/{rank}", "1")
+    store.wait([f"ready/{r}" for r in range(world)])
     if rank == 1:
-        time.sleep(0.5)
         os._exit(0)          # this rank dies between steps, without saying goodbye
+    if rank == 3:
+        wd.stop()            # this one finishes cleanly: not a failure
+        with open(f"{result_path}.{rank}", "w") as f:
+            f.write("done")
+        return
     t0 = time.time()
     seen = None
-    while time.time() - t0 < 10:
+    while time.time() - t0 < 20:
         try:
             wd.check()
         except PeerFailure as e:
@@ -93,15 +103,34 @@ def _wd_worker(rank, world, path, result_path):
 
 
 def test_watchdog_detects_a_dead_rank():
+    """Four ranks: 1 dies silently after everyone has seen everyone, 3 stops cleanly; 0 and 2 must report [1] only."""
     with tempfile.TemporaryDirectory() as d:
-        ctx = mp.spawn(_wd_worker, args=(3, os.path.join(d, "store"), os.path.join(d, "res")), nprocs=3, join=False)
+        ctx = mp.spawn(_wd_worker, args=(4, os.path.join(d, "store"), os.path.join(d, "res")), nprocs=4, join=False)
         t0 = time.time()
-        while time.time() - t0 < 30 and not all(os.path.exists(os.path.join(d, f"res.{r}")) for r in (0, 2)):
+        while time.time() - t0 < 90 and not all(os.path.exists(os.path.join(d, f"res.{r}")) for r in (0, 2)):
             time.sleep(0.1)
         for r in (0, 2):
             assert open(os.path.join(d, f"res.{r}")).read() == "[1]"
         for p in ctx.processes:
             p.join(timeout=5)
+
+
+def test_watchdog_start_up_skew_is_not_a_failure():
+    """A peer that has not beaten yet is covered by the start-up grace, not by the beat timeout."""
+    from jax_gpt_b200.utils.watchdog import Watchdog
+    with tempfile.TemporaryDirectory() as d:
+        store = dist.FileStore(os.path.join(d, "s"), 2)
+        wd = Watchdog(store, 0, 2, interval=0.05, timeout=0.2, startup_grace=30.0).start()
+        time.sleep(0.8)                      # four timeouts long, rank 1 still silent
+        wd.check()
+        assert wd.dead_ranks == [] and wd.peers_seen() == []
+        late = Watchdog(store, 1, 2, interval=0.05, timeout=0.2, startup_grace=30.0).start()
+        time.sleep(0.3)
+        assert wd.peers_seen() == [1]
+        late.stop()                          # clean exit
+        time.sleep(0.6)
+        wd.check()
+        wd.stop()
 
 
 def _vce_worker(rank, world, path):
