@@ -12,7 +12,14 @@ the schedule ``count``. On disk::
 
 ``save`` copies device tensors into pinned host memory and returns; a native writer thread
 (csrc/runtime.cpp) streams them to ``*.tmp`` files and renames them, then writes the manifest,
-so a directory without a manifest is an unfinished checkpoint and is ignored. Orbax's OCDBT
+so a directory without a manifest is an unfinished checkpoint and is ignored. If a file of a checkpoint
+fails to write, the writer drops the rest of that checkpoint (no manifest appears) and the error is raised
+by ``wait_until_finished``. Older checkpoints are only deleted once enough NEWER ones are complete on disk
+(at the next ``save`` and in ``wait_until_finished``), never while the newest is still in flight.
+
+With a sharded optimizer (``state.engine.dist_optimizer``) the weights and moments live as per-rank shards:
+``save`` then assembles them itself, which makes it a COLLECTIVE call that every rank must make; only rank 0
+writes. The saved tree does not depend on the number of ranks. Orbax's OCDBT
 container cannot be produced without TensorStore; the tree is the same, the container differs.
 """
 from __future__ import annotations
@@ -96,7 +103,17 @@ class CheckpointManager:
         return names, tensors
 
     def save(self, step: int, state, data_state: Optional[dict] = None) -> None:
-        """Non-blocking: returns once the tensors are staged in host memory."""
+        """Non-blocking: returns once the tensors are staged in host memory. With a sharded optimizer every rank
+        must call it (the shards are gathered collectively) and only rank 0 writes."""
+        eng = getattr(state, "engine", None)
+        if eng is not None and getattr(eng, "dist_optimizer", None) is not None:
+            # the optimizer kernels update per-rank shards: refresh the full fp32 weights and moments first
+            eng.params()
+            st = eng.opt_state()
+            state.opt_state.mu, state.opt_state.nu = st["mu"], st["nu"]
+            if getattr(eng.dist_optimizer, "rank", 0) != 0:
+                return
+        self._prune()      # complete checkpoints only; the one about to be written does not count yet
         params = _model_params(state.model)
         flat_p = flatten(params) if any(isinstance(v, dict) for v in params.values()) else dict(params)
         opt = state.opt_state
@@ -121,7 +138,7 @@ class CheckpointManager:
             save_file(dict(zip(on, ot)), os.path.join(d, "opt_state.safetensors"))
             with open(os.path.join(d, "manifest.json"), "w") as f:
                 json.dump(manifest, f)
-        self._prune(keep_extra=step)
+            self._prune()
 
     def _complete_steps(self):
         out = []
@@ -131,10 +148,9 @@ class CheckpointManager:
                     out.append(int(n))
         return sorted(out)
 
-    def _prune(self, keep_extra=None):
+    def _prune(self):
+        """Keeps the newest ``max_checkpoints_to_keep`` COMPLETE checkpoints (those with a manifest)."""
         steps = self._complete_steps()
-        if keep_extra is not None and keep_extra not in steps:
-            steps = sorted(steps + [keep_extra])
         for s in steps[:-self._keep] if self._keep > 0 else []:
             shutil.rmtree(os.path.join(self._dir, str(s)), ignore_errors=True)
 

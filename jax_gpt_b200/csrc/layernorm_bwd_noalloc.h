@@ -23,7 +23,8 @@
  *     dbeta  += sum_rows dy
  * dy, x, dres, dx are [M, D] bf16 row-major; gamma is [D] bf16; mean, rstd are [M] fp32 as
  * written by the forward kernel; dgamma, dbeta are [D] fp32. All pointers are device pointers
- * on the current device, 16-byte aligned.
+ * on the current device, 16-byte aligned. The stream must belong to the current device as well
+ * (the scratch address is looked up for the device that is current at the call).
  *
  * Things a caller has to know:
  *  - The first call on each device looks up the device address of the scratch array

@@ -207,9 +207,12 @@ class AsyncWriter {
     std::lock_guard<std::mutex> l(mu_);
     return pending_;
   }
+  // Returns the first error since the last call and clears it (later checkpoints start clean).
   std::string last_error() {
     std::lock_guard<std::mutex> l(mu_);
-    return error_;
+    std::string e;
+    e.swap(error_);
+    return e;
   }
 
  private:

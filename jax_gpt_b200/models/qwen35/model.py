@@ -78,14 +78,28 @@ def init_params(config: Qwen35Config, key=0, dtype=torch.float32, fp8: bool = Fa
 
 
 def forward(params, tokens, config: Qwen35Config, cache: Optional[HybridCache] = None, is_decode: bool = False,
-            cache_sharding=None, n_devices: int = 1, axis_name: str = "tp", mesh=None, ep_group=None):
+            cache_sharding=None, n_devices: int = 1, axis_name: str = "tp", mesh=None, ep_group=None, tp_group=None):
     """tokens (B,T) -> (logits (B,T,V), new_cache | None). ``is_decode`` selects the recurrent
     DeltaNet step (T must be 1); otherwise the chunked prefill runs (a prefill starts from an
-    empty DeltaNet state, as in the reference)."""
+    empty DeltaNet state, as in the reference).
+
+    Tensor parallel: pass the local shard from ``shard_params`` together with ``tp_group`` (or a ``mesh`` made by
+    ``make_mesh(..., group=...)``): every rank feeds the same tokens, sharded axes are recognised by their shapes,
+    and the logits come back whole on every rank, as in the reference's sharded forward
+    (jax_gpt/models/qwen35/model.py:207-331 with the specs of sharding.py). ``n_devices``, ``axis_name`` and
+    ``cache_sharding`` are accepted for signature parity: the group and the shapes carry that information here.
+    A sharded tree without a group is an error rather than a silent wrong answer."""
+    from ...parallel.tp_ops import copy_to_tp, gather_from_tp, tp_world, vocab_parallel_embedding
     c = config
     B, T = tokens.shape
+    if tp_group is None and mesh is not None:
+        tp_group = getattr(mesh, "group", None)
+    vocab_sharded = params["embed"].shape[0] < c.vocab_size
+    if (vocab_sharded or _lm_head_cols(params["lm_head"]) < c.vocab_size) and tp_world(tp_group) == 1:
+        raise ValueError("forward() got a tensor-parallel shard of the parameters but no process group: pass "
+                         "tp_group= (or mesh=make_mesh(n, group=...)) and run one process per shard")
     with scope("embedding"):
-        x = params["embed"][tokens.long()]
+        x = vocab_parallel_embedding(tokens, params["embed"], tp_group, c.vocab_size)
     pos = cache.pos if cache is not None else 0
     max_pos = (cache.gqa_k.shape[3] if cache is not None else pos + T)
     rope = precompute_rope_freqs(c.gqa_rope_dim, max(max_pos, pos + T), c.gqa_rope_theta, device=x.device)
@@ -97,19 +111,28 @@ def forward(params, tokens, config: Qwen35Config, cache: Optional[HybridCache] =
             ck, cv = cache.gqa_k[gi], cache.gqa_v[gi]
         else:
             dM = dC = ck = cv = None
-        x, M, conv, _, _ = group_forward(x, gp, dM, dC, ck, cv, pos, c, rope, is_decode, ep_group=ep_group)
+        x, M, conv, _, _ = group_forward(x, gp, dM, dC, ck, cv, pos, c, rope, is_decode, ep_group=ep_group,
+                                         tp_group=tp_group)
         new_M.append(M)
         new_conv.append(conv)
     with scope("output_head"):
         x = rms_norm(x, params["final_norm"], c.rms_norm_eps)
         from ...ops.fp8_linear import fp8_training
         with fp8_training(False):          # the head stays in bf16 also when the layers train in FP8
-            logits = matmul_maybe_fp8(x, params["lm_head"])
+            if _lm_head_cols(params["lm_head"]) < c.vocab_size:
+                # vocabulary-parallel head: local logit columns, gathered to whole logits on every rank
+                logits = gather_from_tp(matmul_maybe_fp8(copy_to_tp(x, tp_group), params["lm_head"]), tp_group, -1)
+            else:
+                logits = matmul_maybe_fp8(x, params["lm_head"])
     new_cache = None
     if cache is not None:
         new_cache = HybridCache(torch.stack(new_M).to(cache.delta_M.dtype),
                                 torch.stack(new_conv).to(cache.delta_conv.dtype), cache.gqa_k, cache.gqa_v, pos + T)
     return logits, new_cache
+
+
+def _lm_head_cols(w) -> int:
+    return w["w"].shape[-2] if isinstance(w, dict) else w.shape[-1]
 
 
 def _sample(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] = None, generator=None):

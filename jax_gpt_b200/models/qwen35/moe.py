@@ -39,6 +39,11 @@ def grouped_swiglu(xs: torch.Tensor, group_sizes, gate_proj, up_proj, down_proj,
                                        _dense(down_proj, xs.dtype))
 
 
+def _n_local_experts(params) -> int:
+    g = params["gate_proj"]
+    return (g["w"] if is_fp8_weight(g) else g).shape[0]
+
+
 def expert_forward_single(x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, params) -> torch.Tensor:
     """x (M,D); weights/idx (M,k). Returns sum_k w_k * expert_{idx_k}(x)."""
     M, D = x.shape
@@ -90,6 +95,29 @@ def expert_forward_ep(x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor,
     return out.to(x.dtype)
 
 
+def expert_forward_tp(x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, params, group, n_experts: int):
+    """Experts split over a TENSOR-parallel group whose ranks all hold the same tokens: every rank runs the
+    (token, expert) rows of its own experts and the partial outputs are summed over the group, the scheme of the
+    reference's expert parallelism (jax_gpt/models/qwen35/moe.py:117-222), without its full-size masked work."""
+    from ...parallel.tp_ops import reduce_from_tp, tp_rank, tp_world
+    world, rank = tp_world(group), tp_rank(group)
+    M, D = x.shape
+    k = idx.shape[1]
+    e_local = n_experts // world
+    flat = idx.reshape(-1) - rank * e_local
+    sel = ((flat >= 0) & (flat < e_local)).nonzero(as_tuple=True)[0]
+    eid = flat[sel]
+    order = torch.argsort(eid, stable=True)
+    sel = sel[order]
+    tok = sel // k
+    sizes = torch.bincount(eid, minlength=e_local)
+    ys = grouped_swiglu(x[tok], sizes, params["gate_proj"], params["up_proj"], params["down_proj"])
+    ys = ys * weights.reshape(-1)[sel][:, None].to(ys.dtype)
+    out = torch.zeros(M, D, dtype=torch.float32, device=x.device)
+    out = out.index_add(0, tok, ys.float())
+    return reduce_from_tp(out, group).to(x.dtype)
+
+
 def shared_expert_forward(x: torch.Tensor, params) -> torch.Tensor:
     g = matmul_maybe_fp8(x, params["shared_gate_proj"])
     u = matmul_maybe_fp8(x, params["shared_up_proj"])
@@ -97,11 +125,13 @@ def shared_expert_forward(x: torch.Tensor, params) -> torch.Tensor:
 
 
 def moe_layer(x: torch.Tensor, params, n_experts_per_token: int, n_devices: int = 1, axis_name: str = "tp",
-              mesh=None, group=None, n_experts: Optional[int] = None) -> torch.Tensor:
+              mesh=None, group=None, n_experts: Optional[int] = None, tp_group=None) -> torch.Tensor:
     """x (B,T,D) -> (B,T,D). With ``group`` the routed experts run expert-parallel: a process group
     selects the all-to-all library path, a callable ``group(x, weights, idx, params, grads)`` (the fused
     kernel runtime of parallel/expert_parallel.py) the one-kernel path; ``params`` then hold only this
-    rank's experts and, when training, their fp32 gradient buffers under ``<name>@grad``."""
+    rank's experts and, when training, their fp32 gradient buffers under ``<name>@grad``. ``tp_group``: the
+    ranks hold the SAME tokens (tensor parallelism) and, when the expert axis of ``params`` is a shard, split
+    the experts among them (partial outputs summed over the group)."""
     B, T, D = x.shape
     xf = x.reshape(B * T, D)
     w, idx = moe_routing(xf, params["gate_weight"], n_experts_per_token)
@@ -110,6 +140,10 @@ def moe_layer(x: torch.Tensor, params, n_experts_per_token: int, n_devices: int 
         routed = group(xf, w, idx, params, grads).to(x.dtype)
     elif group is not None:
         routed = expert_forward_ep(xf, w, idx, params, group, n_experts)
+    elif tp_group is not None and n_experts is not None and _n_local_experts(params) < n_experts:
+        from ...parallel.tp_ops import copy_to_tp
+        # entry of the sharded region: activations and routing weights get the SUM of the ranks' gradients
+        routed = expert_forward_tp(copy_to_tp(xf, tp_group), copy_to_tp(w, tp_group), idx, params, tp_group, n_experts)
     else:
         routed = expert_forward_single(xf, w, idx, params)
     shared = shared_expert_forward(xf, params)

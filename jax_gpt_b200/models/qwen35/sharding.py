@@ -41,16 +41,21 @@ AXIS_RULES_B = {"vocab": "tp", "experts": "tp", "q_heads": None, "q_heads_out": 
 
 @dataclass
 class Mesh:
-    """A 1-D device mesh: ``n_devices`` ranks on one axis."""
+    """A 1-D device mesh: ``n_devices`` ranks on one axis; ``group`` is the process group of that axis (None: the
+    default group when torch.distributed is initialised, else a single process)."""
     n_devices: int
     axis_name: str = "tp"
+    group: object = None
 
 
-def make_mesh(n_devices: Optional[int] = None, axis_name: str = "tp") -> Mesh:
+def make_mesh(n_devices: Optional[int] = None, axis_name: str = "tp", group=None) -> Mesh:
+    import torch.distributed as dist
+    live = dist.is_available() and dist.is_initialized()
     if n_devices is None:
-        import torch.distributed as dist
-        n_devices = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
-    return Mesh(n_devices, axis_name)
+        n_devices = dist.get_world_size(group) if live else 1
+    if group is None and live and n_devices == dist.get_world_size():
+        group = dist.group.WORLD
+    return Mesh(n_devices, axis_name, group)
 
 
 def tree_map(fn, tree):

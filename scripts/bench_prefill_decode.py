@@ -19,7 +19,7 @@ import json
 import statistics
 import time
 
-from utils import init_distributed, qwen_config
+from utils import fake_quant_w8a8, init_distributed, load_hf_dir, make_tp_dp_groups, qwen_config
 
 import torch
 
@@ -58,9 +58,23 @@ def make_runner(args, device):
         cfg = qwen_config(args.config)
         if args.n_layers:
             cfg = cfg.replace(n_layers=args.n_layers)
-        params = init_params(cfg, 0, dtype=dtype, fp8=args.fp8)
+        if args.model_dir and not args.random_weights:
+            from jax_gpt_b200.models.qwen35.weight_loader import load_from_hf_state_dict
+            params = load_from_hf_state_dict(load_hf_dir(args.model_dir), cfg, dtype=dtype)
+        else:
+            params = init_params(cfg, 0, dtype=dtype, fp8=args.fp8)
+        if args.w8a8:
+            params = fake_quant_w8a8(params)
         ep = None
-        if device.type == "cuda" and not args.fp8 and cfg.d_model % 256 == 0 and cfg.moe_intermediate_size % 128 == 0:
+        tp_group, tp_rank, _ = make_tp_dp_groups(args.tp, args.dp)
+        if args.tp > 1:
+            # tensor parallel: this rank keeps its shard (rules A: heads, experts, vocabulary; B: experts, vocabulary)
+            from jax_gpt_b200.models.qwen35.sharding import AXIS_RULES_A, AXIS_RULES_B, make_mesh, shard_cache, shard_params
+            rules = AXIS_RULES_A if args.sharding == "A" else AXIS_RULES_B
+            mesh = make_mesh(args.tp, group=tp_group)
+            params = shard_params(params, mesh, cfg, rules, rank=tp_rank)
+        elif device.type == "cuda" and not args.fp8 and cfg.d_model % 256 == 0 and cfg.moe_intermediate_size % 128 == 0 \
+                and args.dp == 1:
             # routed experts through the fused dispatch / grouped-GEMM / combine kernel, expert-parallel over the
             # ranks (with one rank: one kernel per MoE layer instead of a launch per expert)
             import os
@@ -79,9 +93,12 @@ def make_runner(args, device):
         plen, dlen = SCENARIOS[args.scenario]
 
         def prefill(B):
-            tok = torch.randint(0, cfg.vocab_size, (B, plen), device=device)
+            gen = torch.Generator(device="cpu").manual_seed(1234 + (0 if args.tp > 1 else 0))
+            tok = torch.randint(0, cfg.vocab_size, (B, plen), generator=gen).to(device)   # same tokens within a TP group
             cache = init_cache(cfg, B, plen + dlen, dtype=dtype, device=device)
-            logits, cache = forward(params, tok, cfg, cache=cache, ep_group=ep)
+            if args.tp > 1:
+                cache = shard_cache(cache, mesh, cfg, rules, rank=tp_rank)
+            logits, cache = forward(params, tok, cfg, cache=cache, ep_group=ep, tp_group=tp_group)
             return logits[:, -1].argmax(-1), cache
 
         engines = {}
@@ -97,9 +114,12 @@ def make_runner(args, device):
                     eng = engines[id(cache)] = Qwen35DecodeEngine(params, cfg, cache, ep=ep,
                                                                   use_cuda_graph=not args.no_graph)
                 return eng.step(nxt), cache
-            logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True, ep_group=ep)
+            logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True, ep_group=ep, tp_group=tp_group)
             return logits[:, -1].argmax(-1), cache
         return prefill, decode, cfg
+    if args.tp > 1 or args.dp > 1 or args.model_dir or args.w8a8:
+        raise SystemExit("--tp / --dp / --sharding / --model-dir / --w8a8 apply to --model qwen35; the DeepSeek-V3 shape "
+                         "runs data-parallel attention with expert-parallel MoE over all ranks of the launch")
     from jax_gpt_b200.models.deepseek_v3 import DeepSeekV3Config, forward, init_params, make_cache
     from jax_gpt_b200.models.qwen35.sharding import tree_map
     cfg = {"tiny": DeepSeekV3Config.tiny, "8l": DeepSeekV3Config.eight_layer, "full": DeepSeekV3Config.full}[args.config]()
@@ -184,7 +204,8 @@ def main(argv=None):
     ap.add_argument("--max-batch", type=int, default=64)
     ap.add_argument("--batch", type=int, default=0, help="fixed batch (skips the search)")
     ap.add_argument("--sharding", default="A", choices=["A", "B"])
-    ap.add_argument("--random-weights", action="store_true")
+    ap.add_argument("--random-weights", action="store_true", help="ignore --model-dir and use random weights")
+    ap.add_argument("--w8a8", action="store_true", help="per-tensor fp8 fake quantisation of the weights (reference mode)")
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--fp8", action="store_true")
     ap.add_argument("--n-layers", type=int, default=0)
@@ -192,13 +213,17 @@ def main(argv=None):
     ap.add_argument("--engine", action="store_true", help="decode through the model family's CUDA-graph decode engine")
     ap.add_argument("--no-graph", action="store_true", help="with --engine: run the engine's step eagerly")
     ap.add_argument("--prefill-reps", type=int, default=5)
-    ap.add_argument("--decode-steps", type=int, default=20)
+    ap.add_argument("--decode-steps", type=int, default=256, help="timed decode steps (capped by the scenario)")
     ap.add_argument("--out", default="")
     args = ap.parse_args(argv)
     rank, world, device = init_distributed()
     if device.type == "cpu" and args.dtype == "bfloat16":
         args.dtype = "float32"
+    if args.engine and args.tp > 1:
+        raise SystemExit("--engine (the in-place decode engine) serves unsharded or expert-parallel parameters; use the "
+                         "function-style decode with --tp")
     prefill, decode, cfg = make_runner(args, device)
+    args.decode_steps = max(1, min(args.decode_steps, SCENARIOS[args.scenario][1] - 1))
     timer = _Timer(device)
     with torch.no_grad():
         prefill(1)  # warm-up (kernel set-up, allocator)
@@ -218,12 +243,15 @@ def main(argv=None):
     dec_sorted = sorted(dec)
     res = {
         "model": args.model, "config": args.config, "scenario": args.scenario, "batch_per_rank": B,
-        "global_batch": B * world if args.model == "deepseek_v3" else B, "world": world, "fp8_moe": bool(args.fp8),
+        "global_batch": B * world if args.model == "deepseek_v3" else B * args.dp, "world": world, "fp8_moe": bool(args.fp8),
         "prefill_len": plen, "prefill_ms_mean": statistics.mean(pre),
-        "prefill_toks_per_sec": B * plen * (world if args.model == "deepseek_v3" else 1) / (statistics.mean(pre) / 1e3),
+        "prefill_toks_per_sec": B * plen * (world if args.model == "deepseek_v3" else args.dp) / (statistics.mean(pre) / 1e3),
         "decode_ms_mean": statistics.mean(dec), "decode_ms_p50": statistics.median(dec),
-        "decode_ms_p99": dec_sorted[min(len(dec) - 1, int(0.99 * len(dec)))],
-        "decode_toks_per_sec": B * (world if args.model == "deepseek_v3" else 1) / (statistics.mean(dec) / 1e3), "dtype": args.dtype, "timing": "cuda events, max over ranks",
+        "decode_ms_p99": (dec_sorted[-(-99 * len(dec) // 100) - 1] if len(dec) >= 100 else None),
+        "decode_ms_max": dec_sorted[-1], "decode_steps": len(dec), "tp": args.tp, "dp": args.dp,
+        "sharding": args.sharding if args.tp > 1 else "none",
+        "decode_toks_per_sec": B * (world if args.model == "deepseek_v3" else args.dp) / (statistics.mean(dec) / 1e3),
+        "dtype": args.dtype, "timing": "cuda events, max over ranks",
     }
     if rank == 0:
         print(json.dumps(res, indent=1))

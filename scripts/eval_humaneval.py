@@ -1,9 +1,12 @@
 """HumanEval-style evaluation of the Qwen3.5 hybrid model (scripts/eval_humaneval.py:50-818).
 
-Each data-parallel replica takes every ``world``-th problem, generates a completion with the
+The processes form ``--dp`` replicas of ``--tp`` tensor-parallel ranks (``--sharding`` picks the rule set of
+models/qwen35/sharding.py). Each replica takes every ``dp``-th problem, generates a completion with the
 KV / recurrent-state cache (prefill, then one recurrent step per token until a stop id or
 ``--max-new-tokens``), runs the problem's tests in a subprocess with a 10 s limit, writes its
 results to ``--output-dir`` and waits on a file barrier (600 s, then merges what exists).
+The prompt goes through the tokenizer's chat template when it has one (``--enable-thinking`` is passed to it),
+otherwise through the plain-text fallback below.
 Without the ``datasets`` package or network a single built-in problem is used, as in the
 reference (scripts/eval_humaneval.py:423-448).
 """
@@ -17,7 +20,7 @@ import sys
 import tempfile
 import time
 
-from utils import get_tokenizer, init_distributed, qwen_config
+from utils import get_tokenizer, init_distributed, make_tp_dp_groups, qwen_config
 
 import torch
 
@@ -64,24 +67,73 @@ def file_barrier(out_dir: str, rank: int, world: int, timeout: float = 600.0) ->
     return False
 
 
+INSTRUCTION = ("Complete the following Python function. Return only the code that continues the given prefix.\n\n"
+               "```python\n{prompt}```")
+
+
+def build_prompt(problem_prompt: str, hf_tok, enable_thinking: bool) -> str:
+    """Chat-formatted prompt as the reference builds it (scripts/eval_humaneval.py:311-360 there): the
+    tokenizer's own chat template when it has one, with ``enable_thinking`` handed through; without a template
+    (byte / GPT-2 fallback tokenizers) a ChatML-style frame with an opened or pre-closed think block."""
+    msg = [{"role": "user", "content": INSTRUCTION.format(prompt=problem_prompt)}]
+    if hf_tok is not None and getattr(hf_tok, "chat_template", None):
+        try:
+            return hf_tok.apply_chat_template(msg, tokenize=False, add_generation_prompt=True,
+                                              enable_thinking=enable_thinking)
+        except TypeError:
+            return hf_tok.apply_chat_template(msg, tokenize=False, add_generation_prompt=True)
+    think = "<think>\n" if enable_thinking else "<think>\n\n</think>\n\n"
+    return f"<|im_start|>user\n{msg[0]['content']}<|im_end|>\n<|im_start|>assistant\n{think}"
+
+
+def extract_code(text: str) -> str:
+    """The completion's code: what follows a closed think block, inside a ```python fence when there is one."""
+    if "</think>" in text:
+        text = text.split("</think>", 1)[1]
+    if "```" in text:
+        body = text.split("```", 1)[1]
+        body = body.split("\n", 1)[1] if body.startswith(("python", "py")) and "\n" in body else body
+        text = body.split("```", 1)[0]
+    return text
+
+
 @torch.no_grad()
-def generate_completion(params, cfg, prompt_ids, max_new_tokens, stop_ids, sampler_kw, device, gen, cache_dtype):
+def generate_completion(params, cfg, prompt_ids, max_new_tokens, stop_ids, sampler_kw, device, gen, cache_dtype,
+                        tp=None, use_engine=False):
+    """``tp = (group, mesh, rules, rank)`` for tensor-parallel parameters: every rank of the group runs the same
+    loop on the same tokens (the sampler is seeded alike), so they stay in lock step as in the reference
+    (scripts/eval_humaneval.py:388-408 there). ``use_engine``: decode through the in-place CUDA-graph engine."""
     from jax_gpt_b200.models.qwen35 import forward, init_cache
     from jax_gpt_b200.utils.sampling import sample
     tok = torch.tensor([prompt_ids], device=device)
     cache = init_cache(cfg, 1, len(prompt_ids) + max_new_tokens, dtype=cache_dtype, device=device)
+    tp_group = None
+    if tp is not None:
+        from jax_gpt_b200.models.qwen35.sharding import shard_cache
+        tp_group, mesh, rules, tp_rank = tp
+        cache = shard_cache(cache, mesh, cfg, rules, rank=tp_rank)
     seen = torch.zeros(1, cfg.vocab_size, device=device)
     seen[0, tok[0]] = 1.0
-    logits, cache = forward(params, tok, cfg, cache=cache)
+    logits, cache = forward(params, tok, cfg, cache=cache, tp_group=tp_group)
+    engine = None
+    if use_engine and tp is None:
+        from jax_gpt_b200.models.qwen35.decode_engine import Qwen35DecodeEngine
+        engine = Qwen35DecodeEngine(params, cfg, cache, use_cuda_graph=False)
     out = []
+    last = logits[:, -1]
     for _ in range(max_new_tokens):
-        nxt = sample(logits[:, -1], presence_mask=seen, generator=gen, **sampler_kw)
+        nxt = sample(last, presence_mask=seen, generator=gen, **sampler_kw)
         t = int(nxt)
         if t in stop_ids:
             break
         out.append(t)
         seen[0, t] = 1.0
-        logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True)
+        if engine is not None:
+            engine.step(nxt)
+            last = engine.logits
+        else:
+            logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True, tp_group=tp_group)
+            last = logits[:, -1]
     return out
 
 
@@ -104,8 +156,12 @@ def main(argv=None):
     ap.add_argument("--tokenizer", default="")
     ap.add_argument("--random-weights", action="store_true")
     ap.add_argument("--enable-thinking", action="store_true")
+    ap.add_argument("--engine", action="store_true", help="decode on the in-place engine (not with --tp)")
     args = ap.parse_args(argv)
     rank, world, device = init_distributed()
+    if args.tp * args.dp == 1 and world > 1:
+        args.dp = world                       # plain data parallelism over the launched processes
+    tp_group, tp_rank, dp_rank = make_tp_dp_groups(args.tp, args.dp)
     cfg = qwen_config(args.config)
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     if args.model_dir and not args.random_weights:
@@ -114,7 +170,15 @@ def main(argv=None):
         params = load_from_hf_state_dict(LazySafetensors(args.model_dir), cfg, dtype=dtype)
     else:
         params = init_params(cfg, 0, dtype=dtype)
+    tp = None
+    if args.tp > 1:
+        from jax_gpt_b200.models.qwen35.sharding import AXIS_RULES_A, AXIS_RULES_B, make_mesh, shard_params
+        rules = AXIS_RULES_A if args.sharding == "A" else AXIS_RULES_B
+        mesh = make_mesh(args.tp, group=tp_group)
+        params = shard_params(params, mesh, cfg, rules, rank=tp_rank)
+        tp = (tp_group, mesh, rules, tp_rank)
     params = tree_map(lambda t: t.to(device), params)
+    hf_tok = None
     if args.tokenizer:
         from transformers import AutoTokenizer
         hf_tok = AutoTokenizer.from_pretrained(args.tokenizer)
@@ -126,23 +190,26 @@ def main(argv=None):
         decode, stop_ids = bt.decode, {bt.eot % cfg.vocab_size}
     os.makedirs(args.output_dir, exist_ok=True)
     problems = load_problems(args.n_problems)
-    mine = problems[rank::world]
-    gen = torch.Generator().manual_seed(rank)
+    mine = problems[dp_rank::args.dp]
+    gen = torch.Generator().manual_seed(dp_rank)        # the ranks of a tensor-parallel group sample alike
     kw = dict(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, presence_penalty=args.presence_penalty)
     results = []
     for p in mine:
         t0 = time.time()
-        prompt = p["prompt"] if not args.enable_thinking else "<think>\n" + p["prompt"]
-        ids = generate_completion(params, cfg, encode(prompt), args.max_new_tokens, stop_ids, kw, device, gen, dtype)
-        text = decode(ids)
-        results.append({"task_id": p["task_id"], "completion": text, "passed": evaluate_completion(p, text),
-                        "n_tokens": len(ids), "seconds": time.time() - t0})
-    with open(os.path.join(args.output_dir, f"results_rank{rank}.json"), "w") as f:
-        json.dump(results, f)
+        prompt = build_prompt(p["prompt"], hf_tok, args.enable_thinking)
+        ids = generate_completion(params, cfg, encode(prompt), args.max_new_tokens, stop_ids, kw, device, gen, dtype,
+                                  tp=tp, use_engine=args.engine)
+        text = extract_code(decode(ids))
+        if tp_rank == 0:
+            results.append({"task_id": p["task_id"], "completion": text, "passed": evaluate_completion(p, text),
+                            "n_tokens": len(ids), "seconds": time.time() - t0})
+    if tp_rank == 0:
+        with open(os.path.join(args.output_dir, f"results_rank{dp_rank}.json"), "w") as f:
+            json.dump(results, f)
     complete = file_barrier(args.output_dir, rank, world)
     if rank == 0:
         merged = []
-        for r in range(world):
+        for r in range(args.dp):
             path = os.path.join(args.output_dir, f"results_rank{r}.json")
             if os.path.exists(path):
                 merged += json.load(open(path))

@@ -176,13 +176,9 @@ def main(argv=None):
             losses = [float(eval_step(model, val_data.get_batch(), engine=state.engine)) for _ in range(tc.eval_steps)]
             logger.log_val(state.step, sum(losses) / len(losses))
         if ckpt.should_save(state.step):
-            if dist_opt is not None:
-                # the sharded optimizer assembles master weights and moments collectively (every rank calls);
-                # the saved tree does not depend on the number of ranks
-                state.engine.params()
-                st = state.engine.opt_state()
-                state.opt_state.mu, state.opt_state.nu = st["mu"], st["nu"]
-            if rank == 0:
+            # with the sharded optimizer, save() gathers master weights and moments collectively: every rank
+            # calls it and rank 0 writes; the saved tree does not depend on the number of ranks
+            if dist_opt is not None or rank == 0:
                 ckpt.save(state.step, state, data_state=train_data.state())
     ckpt.wait_until_finished()
     if rank == 0 and metrics:

@@ -86,6 +86,49 @@ def run_fsdp(rank, world, device, use_multimem):
     return res
 
 
+def run_ckpt_manager(rank, world, device, tmp_dir):
+    """The trainer API with the fused sharded optimizer: a few steps, then CheckpointManager.save called on every
+    rank; the file must hold the TRAINED weights and moments (equal to a single-GPU run over the same batches)."""
+    from jax_gpt_b200.ckpt.manager import CheckpointManager
+    from jax_gpt_b200.models.gpt2.engine import GPT2TrainEngine
+    from jax_gpt_b200.models.gpt2.model import GPT
+    from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW
+    from jax_gpt_b200.trainer.config import TrainConfig
+    from jax_gpt_b200.trainer.optimizer import create_optimizer
+    from jax_gpt_b200.trainer.train_state import create_train_state
+    from jax_gpt_b200.trainer.train_step import train_step
+    cfg = small_cfg()
+    tc = TrainConfig(micro_batch_size=2, seq_len=256, learning_rate=1e-3, warmup_steps=0, lr_decay_steps=1000,
+                     checkpoint_dir=tmp_dir, max_checkpoints_to_keep=2, save_interval=1, cuda_graph=False)
+    model = GPT(cfg, rngs=5)
+    state = create_train_state(model, create_optimizer(model, tc), train_config=tc, device=device,
+                               dist_optimizer=FusedShardedAdamW(device=device, wait_seconds=5.0))
+    single = GPT2TrainEngine(cfg, 2, 256, device=device, lr=1e-3, warmup_steps=0, lr_decay_steps=1000,
+                             use_cuda_graph=False, init={k: v.detach().cpu() for k, v in GPT(cfg, rngs=5).params.items()})
+    for step in range(3):
+        state, _ = train_step(state, batch(rank, step, cfg, device))
+        for r in range(world):
+            xs, ys = batch(r, step, cfg, device)
+            single.micro_step(xs, ys)
+        single.apply_gradients()
+    mgr = CheckpointManager(tc, cfg)
+    mgr.save(3, state)                 # collective: every rank
+    res = {}
+    if rank == 0:
+        mgr.wait_until_finished()
+        from safetensors.torch import load_file
+        flat = load_file(os.path.join(tmp_dir, "3", "params.safetensors"))
+        opt = load_file(os.path.join(tmp_dir, "3", "opt_state.safetensors"))
+        sp, so = single.params(), single.opt_state()
+        keys = list(sp)[:8]
+        res["ckpt_params_vs_single"] = max(rel(flat[k].to(device), sp[k]) for k in keys)
+        res["ckpt_mu_vs_single"] = max(rel(opt["mu." + k].to(device), so["mu"][k]) for k in keys)
+        init = GPT(cfg, rngs=5).params
+        res["moved_from_init"] = min(rel(flat[k], init[k].float()) for k in keys if flat[k].dim() > 1)
+    dist.barrier()
+    return res
+
+
 def run_tp(rank, world, device):
     """all-gather -> GEMM and GEMM -> reduce-scatter against their unfused definitions."""
     from jax_gpt_b200 import _ext
@@ -392,6 +435,8 @@ def main():
         res = run_fsdp(rank, world, device, False)
     elif what == "fsdp_multimem":
         res = run_fsdp(rank, world, device, True)
+    elif what == "ckpt_manager":
+        res = run_ckpt_manager(rank, world, device, out_path + ".ckpt")
     elif what == "tp":
         res = run_tp(rank, world, device)
     elif what == "fsdp_ag":

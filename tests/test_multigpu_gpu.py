@@ -38,6 +38,23 @@ def test_fused_sharded_adamw_two_gpus(tmp_path):
     assert res["rank_checksum_spread"] == 0.0, res
 
 
+def test_fused_sharded_adamw_multimem_two_gpus(tmp_path):
+    """The NVLS variant (multimem.ld_reduce / multimem.st through the switch) against the NCCL baseline and one GPU."""
+    res = _run("fsdp_multimem", tmp_path, port=29621)
+    for k, v in res.items():
+        if k.endswith("fused_vs_nccl"):
+            assert v < 2e-3, res
+        if k.endswith("fused_vs_single"):
+            assert v < 5e-3, res
+    assert res["rank_checksum_spread"] == 0.0, res
+
+
+def test_checkpoint_manager_saves_trained_sharded_state_two_gpus(tmp_path):
+    res = _run("ckpt_manager", tmp_path, port=29622)
+    assert res["ckpt_params_vs_single"] < 5e-3 and res["ckpt_mu_vs_single"] < 5e-3, res
+    assert res["moved_from_init"] > 1e-4, res
+
+
 def test_tp_fused_gemms_two_gpus(tmp_path):
     res = _run("tp", tmp_path, port=29612)
     assert res["ag_gemm"] < 1e-2 and res["gemm_rs"] < 1e-2, res

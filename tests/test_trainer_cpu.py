@@ -132,6 +132,69 @@ def test_checkpoint_roundtrip(tmp_path):
     mgr.close()
 
 
+def test_checkpoint_failed_write_leaves_no_manifest_and_keeps_the_older_step(tmp_path):
+    """A checkpoint whose data file cannot be written must not look complete, and with keep = 1 the older,
+    complete checkpoint must survive it."""
+    tc, st = _state(seed=3, checkpoint_dir=str(tmp_path / "ck"), max_checkpoints_to_keep=1, save_interval=1)
+    st, _ = train_step(st, _batch())
+    mgr = CheckpointManager(tc, TINY)
+    if mgr._writer is None:
+        pytest.skip("native writer not built")
+    mgr.save(1, st)
+    mgr.wait_until_finished()
+    assert mgr.latest_step() == 1
+    # make params.safetensors of step 2 unwritable: its path is taken by a directory
+    os.makedirs(tmp_path / "ck" / "2" / "params.safetensors.tmp")
+    mgr.save(2, st)
+    with pytest.raises(RuntimeError, match="checkpoint write failed"):
+        mgr.wait_until_finished()
+    assert not os.path.exists(tmp_path / "ck" / "2" / "manifest.json")
+    assert mgr.latest_step() == 1 and os.path.exists(tmp_path / "ck" / "1" / "manifest.json")
+    # the writer recovers: the next checkpoint is complete and only then is step 1 pruned
+    mgr.save(3, st)
+    mgr.wait_until_finished()
+    assert mgr.latest_step() == 3 and not os.path.exists(tmp_path / "ck" / "1")
+    mgr.close()
+
+
+def test_checkpoint_save_refreshes_sharded_state_and_only_rank0_writes(tmp_path):
+    """With a sharded optimizer the manager itself gathers weights and moments (a collective on every rank)
+    instead of writing the snapshot taken when the state was created."""
+    tc, st = _state(seed=4, checkpoint_dir=str(tmp_path / "ck"), max_checkpoints_to_keep=2, save_interval=1)
+    fresh = {k: v.detach().clone() + 1.0 for k, v in st.model.params.items()}
+    calls = []
+
+    class FakeEngine:
+        def __init__(self, rank):
+            self.dist_optimizer = type("D", (), {"rank": rank})()
+
+        def params(self):
+            calls.append("params")
+            for k in st.model.params:
+                st.model.params[k].data.copy_(fresh[k])      # what gather_master does: refresh in place
+            return st.model.params
+
+        def opt_state(self):
+            calls.append("opt_state")
+            return {"count": 5, "mu": {k: torch.full_like(v, 0.25) for k, v in fresh.items()},
+                    "nu": {k: torch.full_like(v, 0.5) for k, v in fresh.items()}}
+
+    mgr = CheckpointManager(tc, TINY)
+    st.engine = FakeEngine(rank=1)
+    mgr.save(7, st)
+    mgr.wait_until_finished()
+    assert calls == ["params", "opt_state"] and mgr.latest_step() is None      # took part, wrote nothing
+    st.engine = FakeEngine(rank=0)
+    mgr.save(7, st)
+    mgr.wait_until_finished()
+    from safetensors.torch import load_file
+    flat = load_file(str(tmp_path / "ck" / "7" / "params.safetensors"))
+    opt = load_file(str(tmp_path / "ck" / "7" / "opt_state.safetensors"))
+    k = "h.attn.c_attn.kernel"
+    assert torch.equal(flat[k], fresh[k]) and float(opt["mu." + k].mean()) == 0.25 and float(opt["nu." + k].mean()) == 0.5
+    mgr.close()
+
+
 @pytest.mark.parametrize("native", [True, False])
 def test_data_pipeline(tmp_path, native):
     write_synthetic(str(tmp_path), 20000, vocab_size=1000, seed=0)
