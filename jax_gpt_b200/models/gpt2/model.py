@@ -115,13 +115,19 @@ class GPT:
                 self.params[k].copy_(v.to(self.params[k].dtype))
 
     # -- forward ------------------------------------------------------------------------------
-    def _block(self, l, x, cache_k, cache_v, pos, acts):
+    def _block(self, l, x, cache_k, cache_v, pos, acts, tp_group=None):
+        """``tp_group`` with sharded projections (trainer/sharding.py): this rank's heads and its slice of the MLP,
+        row-parallel outputs summed over the group, their biases added once after the sum."""
+        from ...parallel.tp_ops import copy_to_tp, reduce_from_tp
         p, cfg = self.params, self.config
         B, T, d = x.shape
-        H, dh = cfg.n_head, cfg.d_head
+        dh = cfg.d_head
+        dl = p["h.attn.c_attn.kernel"].shape[-1] // 3        # local width of q, k and v
+        H = dl // dh
+        tp = tp_group if dl < d else None
         h1 = norm_ops.layer_norm(x, p["h.ln_1.layer_norm.scale"][l], p["h.ln_1.layer_norm.bias"][l], 1e-5)
-        qkv = gemm_ops.linear(h1, p["h.attn.c_attn.kernel"][l], p["h.attn.c_attn.bias"][l])
-        q, k, v = [t.unflatten(-1, (H, dh)) for t in qkv.split(d, dim=-1)]
+        qkv = gemm_ops.linear(copy_to_tp(h1, tp), p["h.attn.c_attn.kernel"][l], p["h.attn.c_attn.bias"][l])
+        q, k, v = [t.unflatten(-1, (H, dh)) for t in qkv.split(dl, dim=-1)]
         new_k = new_v = None
         if cache_k is not None:
             # cache layout (B, H, ctx, dh); write the new rows, attend over the filled prefix
@@ -136,12 +142,20 @@ class GPT:
             new_k, new_v = cache_k, cache_v
         else:
             y = attn_ops.attention(q, k, v, causal=True)
-        a = gemm_ops.linear(y.reshape(B, T, d), p["h.attn.c_proj.kernel"][l], p["h.attn.c_proj.bias"][l])
+        if tp is None:
+            a = gemm_ops.linear(y.reshape(B, T, dl), p["h.attn.c_proj.kernel"][l], p["h.attn.c_proj.bias"][l])
+        else:
+            a = reduce_from_tp(gemm_ops.linear(y.reshape(B, T, dl), p["h.attn.c_proj.kernel"][l]), tp) \
+                + p["h.attn.c_proj.bias"][l]
         x = x + a
         h2 = norm_ops.layer_norm(x, p["h.ln_2.layer_norm.scale"][l], p["h.ln_2.layer_norm.bias"][l], 1e-5)
-        f = gemm_ops.linear(h2, p["h.mlp.c_fc.kernel"][l], p["h.mlp.c_fc.bias"][l])
+        mlp_tp = tp_group if p["h.mlp.c_fc.kernel"].shape[-1] < cfg.d_ff else None
+        f = gemm_ops.linear(copy_to_tp(h2, mlp_tp), p["h.mlp.c_fc.kernel"][l], p["h.mlp.c_fc.bias"][l])
         f = gemm_ops.gelu_tanh(f)
-        m = gemm_ops.linear(f, p["h.mlp.c_proj.kernel"][l], p["h.mlp.c_proj.bias"][l])
+        if mlp_tp is None:
+            m = gemm_ops.linear(f, p["h.mlp.c_proj.kernel"][l], p["h.mlp.c_proj.bias"][l])
+        else:
+            m = reduce_from_tp(gemm_ops.linear(f, p["h.mlp.c_proj.kernel"][l]), mlp_tp) + p["h.mlp.c_proj.bias"][l]
         if acts is not None:
             acts[f"block_{l}_ln1_output"] = h1
             acts[f"block_{l}_attn_output_pre_residual"] = a
@@ -156,15 +170,26 @@ class GPT:
         assert pos + T <= cfg.d_context, "sequence exceeds d_context"
         acts = {} if return_activations else None
         idx = x.long()
-        h = p["wte.embedding"][idx] + p["wpe.embedding"][pos:pos + T]
+        from ...parallel.tp_ops import copy_to_tp, gather_from_tp, tp_world, vocab_parallel_embedding
+        tp_group = getattr(mesh, "group", None) if mesh is not None else None
+        vocab_sharded = p["wte.embedding"].shape[0] < cfg.vocab_size
+        if (vocab_sharded or p["h.attn.c_attn.kernel"].shape[-1] < 3 * cfg.d_model) and tp_world(tp_group) == 1:
+            raise ValueError("the parameters are a tensor-parallel shard: pass mesh=make_mesh(config) "
+                             "(trainer/sharding.py) and run one process per shard")
+        h = vocab_parallel_embedding(idx, p["wte.embedding"], tp_group, cfg.vocab_size) + p["wpe.embedding"][pos:pos + T]
         if acts is not None:
             acts["initial_embedding"] = h
         for l in range(cfg.n_layers):
             ck = cache.key[l] if cache is not None else None
             cv = cache.value[l] if cache is not None else None
-            h, _, _ = self._block(l, h, ck, cv, pos, acts)
+            h, _, _ = self._block(l, h, ck, cv, pos, acts, tp_group)
         h = norm_ops.layer_norm(h, p["ln_f.layer_norm.scale"], p["ln_f.layer_norm.bias"], 1e-5)
-        logits = h @ p["wte.embedding"].t()
+        if vocab_sharded:
+            # tied, vocabulary-parallel head: this rank's logit columns, gathered to whole logits
+            logits = gather_from_tp(copy_to_tp(h, tp_group) @ p["wte.embedding"].t(), tp_group, -1)
+            logits = logits[..., :cfg.vocab_size]
+        else:
+            logits = h @ p["wte.embedding"].t()
         new_cache = KVCache(cache.key, cache.value, pos + T) if cache is not None else None
         if acts is not None:
             acts["final_layernorm"] = h
