@@ -23,18 +23,89 @@ BASELINE_TOKENS_PER_S = None  # the reference publishes no training throughput
 
 
 def reference_arm(args):
-    """Runs the unmodified reference from baseline/_ref through its own API. It imports jax at
-    module load; without jax in the image it cannot run, which is reported as such."""
+    """Runs the UNMODIFIED reference from baseline/_ref through its own public API: ``GPT``, ``create_optimizer``,
+    ``create_train_state`` and ``train_step`` (jax_gpt/trainer/train_step.py:34-76), the step wrapped in ``nnx.jit``
+    as that file's header prescribes, on the same model, batch shape, step and warm-up counts as the b200 arm, and
+    prints the same JSON line with ``"impl": "reference"``. The reference imports jax / flax / optax at module
+    load; where they are missing (no wheel in the offline image) it cannot run and says so."""
     here = os.path.dirname(os.path.abspath(__file__))
     sys.path.insert(0, os.path.join(here, "baseline", "_ref"))
-    try:
-        import jax  # noqa: F401
-        import jax_gpt.trainer.train_step  # noqa: F401
-    except Exception as e:  # pragma: no cover - depends on the image
-        print(json.dumps({"impl": "reference",
-                          "unavailable": f"reference needs jax/flax/optax, not installed and no wheel offline ({type(e).__name__}: {e})"}))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+
+    def unavailable(why):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
         return 0
-    print(json.dumps({"impl": "reference", "unavailable": "reference import succeeded but no runner is wired"}))
+    try:
+        import jax
+        import jax.numpy as jnp
+        import numpy as np
+        from flax import nnx
+        from jax_gpt.models.gpt2.config import GPTConfig
+        from jax_gpt.models.gpt2.model import GPT
+        from jax_gpt.trainer.config import TrainConfig
+        from jax_gpt.trainer.optimizer import create_optimizer
+        from jax_gpt.trainer.train_state import TrainState, create_train_state
+        from jax_gpt.trainer.train_step import train_step as ref_train_step
+    except Exception as e:  # pragma: no cover - depends on the image
+        return unavailable(f"reference needs jax/flax/optax, not installed and no wheel offline ({type(e).__name__}: {e})")
+    if world > 1:
+        # its train_step has no data-parallel path: batches are never placed with a dp spec and gradients are not
+        # reduced across processes (jax_gpt/trainer/sharding.py annotates tensor-parallel specs only)
+        return unavailable("the reference's train_step has no multi-process data-parallel path (no gradient reduction "
+                           "across processes); it is measured on one GPU only")
+    try:
+        if not any(d.platform == "gpu" for d in jax.devices()):
+            return unavailable(f"jax has no GPU backend here (devices: {[d.platform for d in jax.devices()]})")
+        cfg = GPTConfig.from_model_type(args.model)
+        B, T = args.micro_batch, args.seq_len
+        tc = TrainConfig(micro_batch_size=B, seq_len=T)
+        model = GPT(cfg, rngs=nnx.Rngs(0))
+        tx = create_optimizer(model, tc)
+        state = create_train_state(model, tx)
+
+        @nnx.jit
+        def step_fn(model, opt_state, x, y):
+            st, metrics = ref_train_step(TrainState(step=0, model=model, tx=tx, opt_state=opt_state), (x, y))
+            return st.opt_state, metrics
+
+        rng = np.random.default_rng(1234)
+        n = args.steps + args.warmup
+        host = [rng.integers(0, cfg.vocab_size, (B, T + 1), dtype=np.int32) for _ in range(n)]
+        dev = [(jnp.asarray(h[:, :-1]), jnp.asarray(h[:, 1:])) for h in host]
+        opt_state = state.opt_state
+        for i in range(args.warmup):
+            opt_state, m = step_fn(model, opt_state, *dev[i])
+        jax.block_until_ready(m["loss"])
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            opt_state, m = step_fn(model, opt_state, *dev[args.warmup + i])
+        jax.block_until_ready(m["loss"])
+        ms = (time.perf_counter() - t0) * 1e3
+        final_loss = float(m["loss"])
+        # end to end: host arrays in, loss read back, every step
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            h = host[args.warmup + i]
+            opt_state, m = step_fn(model, opt_state, jnp.asarray(h[:, :-1]), jnp.asarray(h[:, 1:]))
+            loss_host = float(m["loss"])
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        tokens = B * T * args.steps
+        print(json.dumps({
+            "impl": "reference", "metric": "train tokens/s/box", "value": tokens / (ms / 1e3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp32 parameters and activations (the reference never consumes its dtype field)",
+            "data": "synthetic uniform-random token ids, random-init weights",
+            "config": {"model": "GPT-2 small (12L, d768, 12 heads, ctx 1024, vocab 50257, tied embeddings)",
+                       "global_batch": B, "seq_len": T, "parallelism": "1gpu",
+                       "step": "jax_gpt.trainer.train_step under nnx.jit (XLA:GPU)", "timing": "host clock around block_until_ready"},
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": 2 * B * T * 4, "d2h_bytes_per_step": 4},
+            "final_loss": final_loss, "e2e_final_loss": loss_host}))
+    except Exception as e:  # pragma: no cover - needs a jax install to exercise
+        return unavailable(f"reference runner failed: {type(e).__name__}: {str(e)[:300]}")
     return 0
 
 

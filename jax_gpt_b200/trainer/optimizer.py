@@ -68,12 +68,24 @@ class AdamW:
                           {k: torch.zeros_like(v, dtype=torch.float32) for k, v in params.items()})
 
     @torch.no_grad()
-    def update(self, grads: Dict[str, torch.Tensor], state: AdamWState, params: Dict[str, torch.Tensor]):
-        """Applies one step IN PLACE to ``params`` and the moments; returns (grad_norm, lr)."""
+    def update(self, grads: Dict[str, torch.Tensor], state: AdamWState, params: Dict[str, torch.Tensor], mesh=None,
+               model_config=None):
+        """Applies one step IN PLACE to ``params`` and the moments; returns (grad_norm, lr). With a tensor-parallel
+        ``mesh`` the leaves are shards: the squared norms of the sharded leaves are summed over the group, those of
+        the replicated leaves counted once, so every rank clips by the same global norm as a single process."""
         sq = None
-        for g in grads.values():
+        sq_sharded = None
+        tp = mesh is not None and getattr(mesh, "group", None) is not None and mesh.size("tp") > 1
+        for k, g in grads.items():
             s = (g.float() ** 2).sum()
-            sq = s if sq is None else sq + s
+            if tp and _is_tp_sharded(k, g, model_config, mesh):
+                sq_sharded = s if sq_sharded is None else sq_sharded + s
+            else:
+                sq = s if sq is None else sq + s
+        if sq_sharded is not None:
+            import torch.distributed as dist
+            dist.all_reduce(sq_sharded, group=mesh.group)
+            sq = sq_sharded if sq is None else sq + sq_sharded
         gnorm = float(sq.sqrt())
         lr = self.schedule(state.count)
         t = state.count + 1
@@ -92,6 +104,25 @@ class AdamW:
                 p.copy_(pf)
         state.count = t
         return gnorm, lr
+
+
+def _is_tp_sharded(name: str, t: torch.Tensor, model_config, mesh) -> bool:
+    """True when leaf ``name`` is a tensor-parallel shard under the trainer's rules (trainer/sharding.py)."""
+    from .sharding import param_spec
+    if "tp" not in param_spec(name, t.dim()):
+        return False
+    if model_config is None:
+        return True
+    from .sharding import shard_gpt2_tensor
+    full_shape = _full_shape(name, model_config)
+    return full_shape is None or tuple(t.shape) != tuple(full_shape)
+
+
+def _full_shape(name: str, c):
+    L, d, f, V = c.n_layers, c.d_model, c.d_ff, c.vocab_size
+    return {"wte.embedding": (V, d), "h.attn.c_attn.kernel": (L, d, 3 * d), "h.attn.c_attn.bias": (L, 3 * d),
+            "h.attn.c_proj.kernel": (L, d, d), "h.mlp.c_fc.kernel": (L, d, f), "h.mlp.c_fc.bias": (L, f),
+            "h.mlp.c_proj.kernel": (L, f, d), "lm_head.kernel": (d, V)}.get(name)
 
 
 def create_optimizer(model, config) -> AdamW:

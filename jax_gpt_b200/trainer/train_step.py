@@ -1,6 +1,8 @@
 """train / eval steps with the reference's signatures (jax_gpt/trainer/train_step.py:34-165).
 
-``train_step(state, batch, mesh=None) -> (state, {'loss', 'grad_norm', 'lr'})``: forward,
+``train_step(state, batch, mesh=None) -> (state, {'loss', 'grad_norm', 'lr'})`` (``mesh``: a
+``trainer.sharding.DeviceMesh``; with tensor-parallel shards in the state the model runs its TP forward and the
+clipping norm is the global one): forward,
 fp32 mean softmax cross-entropy with integer labels, gradients, global norm, AdamW update,
 step + 1. ``batch`` is ``(x, y)`` of shape (B, T). With a fused engine in the state the whole
 step is a CUDA-graph replay and the returned metrics are device tensors (read them with
@@ -15,13 +17,13 @@ import torch
 from .train_state import TrainState
 
 
-def _loss_fn(model, x, y):
-    logits, _ = model(x, deterministic=False)
+def _loss_fn(model, x, y, mesh=None):
+    logits, _ = model(x, deterministic=False, mesh=mesh)
     lf = logits.float()
     return torch.nn.functional.cross_entropy(lf.reshape(-1, lf.shape[-1]), y.reshape(-1).long())
 
 
-def _autograd_grads(model, micro_batches):
+def _autograd_grads(model, micro_batches, mesh=None):
     params = model.params
     leaves = list(params.values())
     for p in leaves:
@@ -29,7 +31,7 @@ def _autograd_grads(model, micro_batches):
     total = 0.0
     sums = None
     for x, y in micro_batches:
-        loss = _loss_fn(model, x, y)
+        loss = _loss_fn(model, x, y, mesh)
         grads = torch.autograd.grad(loss, leaves, allow_unused=True)
         grads = [g if g is not None else torch.zeros_like(p) for g, p in zip(grads, leaves)]
         sums = grads if sums is None else [a + b for a, b in zip(sums, grads)]
@@ -51,8 +53,9 @@ def train_step_with_accumulation(state: TrainState, micro_batches: Sequence, mes
         state.opt_state.count = eng.step_count
         gn = out["grad_norm_sq"].sqrt() * out["grad_scale"]
         return state, {"loss": out["loss"], "grad_norm": gn, "lr": out["lr"]}
-    loss, grads = _autograd_grads(state.model, micro_batches)
-    gnorm, lr = state.tx.update(grads, state.opt_state, state.model.params)
+    loss, grads = _autograd_grads(state.model, micro_batches, mesh)
+    gnorm, lr = state.tx.update(grads, state.opt_state, state.model.params, mesh=mesh,
+                                model_config=getattr(state.model, "config", None))
     state.step += 1
     return state, {"loss": loss, "grad_norm": gnorm, "lr": lr}
 

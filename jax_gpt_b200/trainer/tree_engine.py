@@ -243,5 +243,62 @@ class TreeTrainEngine:
             _set(out, p, self.local_master[o:o + n].view(shape))
         return out
 
+    # ---- checkpoint state ------------------------------------------------------------------------
+    def dense_state(self):
+        """(master, m, v) of the dense group as nested dicts of full-size fp32 tensors keyed like the parameter
+        tree. With a sharded optimizer this gathers the shards: a COLLECTIVE call on every rank; the result does not
+        depend on the number of ranks."""
+        if self.dist_optimizer is not None:
+            self.dist_optimizer.gather_master(self)
+            m, v = self.dist_optimizer.gather_moments(self)
+        else:
+            m, v = self.m, self.v
+        out = ({}, {}, {})
+        for p, (o, n, shape) in self.offsets.items():
+            for tree, buf in zip(out, (self.flat.master, m, v)):
+                _set(tree, p, buf[o:o + n].view(shape))
+        return out
+
+    def local_state(self):
+        """(master, m, v) of this rank's expert-parallel leaves as nested dicts (empty without such leaves)."""
+        out = ({}, {}, {})
+        for p, (o, n, shape) in self.local_offsets.items():
+            for tree, buf in zip(out, (self.local_master, self.local_m, self.local_v)):
+                _set(tree, p, buf[o:o + n].view(shape))
+        return out
+
+    def load_state(self, dense=None, local=None, step: Optional[int] = None):
+        """Inverse of ``dense_state`` / ``local_state``: ``dense`` and ``local`` are (master, m, v) triples of nested
+        dicts (moments may be None). Every rank loads the full dense trees; the sharded optimizer re-slices."""
+        def get(tree, p):
+            for k in p:
+                tree = tree[k]
+            return tree
+        if dense is not None:
+            master, m, v = dense
+            full_m = torch.zeros_like(self.flat.master) if m is not None else None
+            full_v = torch.zeros_like(self.flat.master) if v is not None else None
+            for p, (o, n, shape) in self.offsets.items():
+                self.flat.master[o:o + n].copy_(get(master, p).reshape(-1).to(self.flat.master))
+                if m is not None:
+                    full_m[o:o + n].copy_(get(m, p).reshape(-1).to(full_m))
+                    full_v[o:o + n].copy_(get(v, p).reshape(-1).to(full_v))
+            self.flat.compute.copy_(self.flat.master)
+            if self.dist_optimizer is not None:
+                self.dist_optimizer.scatter_state(self, full_m, full_v)
+            elif m is not None:
+                self.m.copy_(full_m)
+                self.v.copy_(full_v)
+        if local is not None and self.local_total:
+            master, m, v = local
+            for p, (o, n, shape) in self.local_offsets.items():
+                self.local_master[o:o + n].copy_(get(master, p).reshape(-1).to(self.local_master))
+                if m is not None:
+                    self.local_m[o:o + n].copy_(get(m, p).reshape(-1).to(self.local_m))
+                    self.local_v[o:o + n].copy_(get(v, p).reshape(-1).to(self.local_v))
+            self.local_compute.copy_(self.local_master)
+        if step is not None:
+            self.step_count = int(step)
+
     def n_params(self) -> int:
         return sum(n for _, n, _ in self.offsets.values()) + sum(n for _, n, _ in self.local_offsets.values())

@@ -10,6 +10,12 @@
 are sharded over the ranks (fused dispatch / grouped GEMM / combine kernels, forward and backward),
 dense weights go through the fused sharded optimizer.
 
+``--tp=N`` (GPT-2 presets, N = number of processes) trains tensor parallel on the shards of
+``trainer/sharding.py`` through the autograd model; with several ranks a watchdog over the rendezvous store turns a
+rank that stops beating into a ``PeerFailure`` on the others before their next step. The MoE families checkpoint
+periodically too (``--save_interval``, ``--resume_from=latest``): dense state gathered to rank 0, every rank writes
+its experts, and a checkpoint restores at another expert-parallel degree (ckpt/tree_ckpt.py).
+
 Every TrainConfig field is a ``--name=value`` flag. Flow: process group -> model -> optimizer and
 state (fused engine on CUDA; sharded fused AdamW across ranks) -> resume from the latest
 checkpoint -> data pipelines positioned at the restored step -> loop with gradient
@@ -34,6 +40,18 @@ def moe_config(preset: str):
     name = preset.split("-", 2)[2]
     return "deepseek_v3", {"tiny": DeepSeekV3Config.tiny, "train8": DeepSeekV3Config.eight_layer,
                            "full": DeepSeekV3Config.full}[name]()
+
+
+def start_watchdog(rank, world):
+    """Heartbeats over the job's rendezvous store (utils/watchdog.py); None for a single process."""
+    if world <= 1 or not torch.distributed.is_initialized():
+        return None
+    from jax_gpt_b200.utils.watchdog import Watchdog
+    try:
+        store = torch.distributed.distributed_c10d._get_default_store()
+    except Exception:
+        return None
+    return Watchdog(store, rank, world, interval=2.0, timeout=120.0, startup_grace=900.0).start()
 
 
 def train_moe(args, tc, rank, world, device):
@@ -86,13 +104,26 @@ def train_moe(args, tc, rank, world, device):
                           weight_decay=tc.weight_decay, beta1=tc.beta1, beta2=tc.beta2, grad_clip=tc.grad_clip,
                           dist_optimizer=dist_opt)
     del params
+    from jax_gpt_b200.ckpt.tree_ckpt import TreeCheckpointer
+    ckpt = None
+    if tc.checkpoint_dir and tc.save_interval > 0:
+        ckpt = TreeCheckpointer(os.path.join(tc.checkpoint_dir, args.preset), tc.max_checkpoints_to_keep, rank, world,
+                                barrier=(torch.distributed.barrier if world > 1 else None))
+        if tc.resume_from:
+            man = ckpt.load(eng, None if tc.resume_from == "latest" else int(tc.resume_from))
+            if man is not None and rank == 0:
+                print(f"resumed at step {eng.step_count}")
     data = DataPipeline(tc, "train")
+    data.skip_to_step(eng.step_count, tc.grad_accum_steps)
+    wd = start_watchdog(rank, world)
     logger = MetricsLogger(tc, cfg, jsonl_path=args.jsonl if rank == 0 else "")
     tokens_per_step = tc.micro_batch_size * tc.seq_len * tc.grad_accum_steps * world
     if rank == 0:
         print(f"{args.preset}: {eng.n_params() / 1e6:.1f}M parameters on this rank, expert parallel: {ep is not None}")
     out, since = {}, 0
     while eng.step_count < tc.max_steps:
+        if wd is not None:
+            wd.check()          # a peer that stopped beating: PeerFailure here, before the next collective
         for _ in range(tc.grad_accum_steps):
             x, y = data.get_batch()
             eng.micro_step(x.to(device, non_blocking=True), y.to(device, non_blocking=True))
@@ -102,14 +133,62 @@ def train_moe(args, tc, rank, world, device):
             logger.log(eng.step_count, {"loss": out["loss"], "grad_norm": out["grad_norm_sq"].sqrt() * out["grad_scale"],
                                         "lr": out["lr"]}, since)
             since = 0
+        if ckpt is not None and eng.step_count % tc.save_interval == 0:
+            ckpt.save(eng.step_count, eng, extra={"data_state": data.state()})      # collective: every rank
     if rank == 0 and out:
         print(f"done: step {eng.step_count} loss {float(out['loss']):.4f}")
-    if tc.checkpoint_dir and tc.save_interval > 0 and rank == 0 and dist_opt is None:
-        from jax_gpt_b200.ckpt.manager import save_tree
-        save_tree(os.path.join(tc.checkpoint_dir, f"{args.preset}_step{eng.step_count}.safetensors"), eng.master_tree())
+    if ckpt is not None and eng.step_count % tc.save_interval != 0:
+        ckpt.save(eng.step_count, eng, extra={"data_state": data.state()})
+    if wd is not None:
+        wd.stop()
     data.close()
     if torch.distributed.is_initialized():
         torch.distributed.destroy_process_group()
+
+
+def train_gpt2_tp(args, tc, cfg, rank, world, device):
+    """GPT-2 tensor parallel over all processes (``--tp=N``): every rank holds its shard of the attention heads,
+    the MLP and the vocabulary (trainer/sharding.py), feeds the SAME batch, and the autograd model runs the
+    Megatron-style forward / backward of parallel/tp_ops.py. Replicated parameters see the full gradient on every
+    rank, so each rank updates its own shard with the plain optimizer and no gradient exchange."""
+    import os
+
+    from jax_gpt_b200.data.pipeline import DataPipeline
+    from jax_gpt_b200.data.tokenize import write_synthetic
+    from jax_gpt_b200.models.gpt2 import GPT
+    from jax_gpt_b200.trainer import MetricsLogger, create_optimizer, create_train_state, train_step_with_accumulation
+    from jax_gpt_b200.trainer.sharding import make_mesh, shard_train_state
+    if tc.tp != world:
+        raise SystemExit(f"--tp={tc.tp} needs {tc.tp} processes (found {world}); combine with data parallelism by "
+                         f"launching tp x dp processes is not wired into this loop")
+    if args.synthetic and rank == 0 and not os.path.exists(os.path.join(tc.local_data_path, "train.bin")):
+        write_synthetic(tc.local_data_path, args.synthetic_tokens, cfg.vocab_size, tc.seed)
+    torch.distributed.barrier()
+    mesh = make_mesh(tc)
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    model = GPT(cfg, seed=tc.seed, device=device, dtype=torch.float32)
+    state = create_train_state(model, create_optimizer(model, tc))
+    state = shard_train_state(state, mesh, cfg)
+    state.mesh = mesh
+    data = DataPipeline(tc, "train", _shard_index=0, _shard_count=1)       # the ranks of a TP group read the same windows
+    logger = MetricsLogger(tc, cfg, jsonl_path=args.jsonl if rank == 0 else "")
+    wd = start_watchdog(rank, world)
+    metrics, since = {}, 0
+    while state.step < tc.max_steps:
+        if wd is not None:
+            wd.check()
+        micro = [tuple(t.to(device) for t in data.get_batch()) for _ in range(tc.grad_accum_steps)]
+        state, metrics = train_step_with_accumulation(state, micro, mesh=mesh)
+        since += tc.micro_batch_size * tc.seq_len * tc.grad_accum_steps
+        if state.step % tc.log_interval == 0:
+            logger.log(state.step, metrics, since)
+            since = 0
+    if rank == 0 and metrics:
+        print(f"done: step {state.step} loss {float(metrics['loss']):.4f} (tensor parallel x{tc.tp}, {dtype})")
+    if wd is not None:
+        wd.stop()
+    data.close()
+    torch.distributed.destroy_process_group()
 
 
 def main(argv=None):
@@ -136,6 +215,8 @@ def main(argv=None):
     if args.preset.startswith(("qwen35-", "deepseek-v3-")):
         return train_moe(args, tc.replace(dp=world), rank, world, device)
     cfg = gpt_config(args.preset)
+    if tc.tp > 1:
+        return train_gpt2_tp(args, tc, cfg, rank, world, device)
     tc = tc.replace(dp=world)
     if args.synthetic and rank == 0:
         import os
@@ -161,11 +242,14 @@ def main(argv=None):
     train_data = DataPipeline(tc, "train")
     val_data = DataPipeline(tc, "val")
     train_data.skip_to_step(state.step, tc.grad_accum_steps)
+    wd = start_watchdog(rank, world)
     logger = MetricsLogger(tc, cfg, jsonl_path=args.jsonl if rank == 0 else "")
     tokens_per_step = tc.micro_batch_size * tc.seq_len * tc.grad_accum_steps * world
     metrics = {}
     tokens_since_log = 0
     while state.step < tc.max_steps:
+        if wd is not None:
+            wd.check()
         micro = [train_data.get_batch() for _ in range(tc.grad_accum_steps)]
         state, metrics = train_step_with_accumulation(state, micro)
         tokens_since_log += tokens_per_step
@@ -181,6 +265,8 @@ def main(argv=None):
             if dist_opt is not None or rank == 0:
                 ckpt.save(state.step, state, data_state=train_data.state())
     ckpt.wait_until_finished()
+    if wd is not None:
+        wd.stop()
     if rank == 0 and metrics:
         print(f"done: step {state.step} loss {float(metrics['loss']):.4f}")
     train_data.close()
