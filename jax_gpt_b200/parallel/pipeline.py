@@ -122,3 +122,44 @@ class PipelineStage:
                                                                       self.group)]))
         flush()
         return torch.stack(losses).mean() if losses else None
+
+
+def gpt2_stage(model, stage: int, n_stages: int, micro_batch: int, seq_len: int, group=None, device=None,
+               act_dtype: Optional[torch.dtype] = None) -> PipelineStage:
+    """The pipeline stage ``stage`` of a GPT-2 (models/gpt2/model.py): its contiguous range of blocks, plus the
+    embeddings on the first stage and the final norm, tied head and mean cross-entropy on the last. ``model`` holds
+    the full parameter dict on every rank (only the stage's layers are used and receive gradients). The last stage
+    takes ``targets`` as its micro-batch input, the first stage ``tokens``."""
+    from ..ops import norm as norm_ops
+    cfg, p = model.config, model.params
+    layers = split_layers(cfg.n_layers, n_stages)[stage]
+    first, last = stage == 0, stage == n_stages - 1
+    dtype = act_dtype or p["wte.embedding"].dtype
+
+    def fwd(inp, i):
+        x, tgt = (inp if (last and not first) else (inp, None))
+        if first:
+            tokens = x if not last else x[0]
+            tgt = None if not last else inp[1]
+            T = tokens.shape[1]
+            x = p["wte.embedding"][tokens.long()] + p["wpe.embedding"][:T]
+        for l in layers:
+            x, _, _ = model._block(l, x, None, None, 0, None)
+        if not last:
+            return x
+        h = norm_ops.layer_norm(x, p["ln_f.layer_norm.scale"], p["ln_f.layer_norm.bias"], 1e-5)
+        logits = (h @ p["wte.embedding"].t()).float()
+        return torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]), tgt.reshape(-1).long())
+
+    used = [v for k, v in p.items() if not k.startswith("h.")] + [v for k, v in p.items() if k.startswith("h.")]
+    return PipelineStage(fwd, used, (micro_batch, seq_len, cfg.d_model), dtype, group, device)
+
+
+def sync_tied_embedding_grad(model, group=None) -> None:
+    """GPT-2 ties the token embedding to the output head, so under pipeline parallelism its gradient is split between
+    the first stage (lookup) and the last stage (head). Sums it over the pipeline group (middle stages add zeros);
+    call after ``PipelineStage.run`` and before the optimizer step."""
+    w = model.params["wte.embedding"]
+    if w.grad is None:
+        w.grad = torch.zeros_like(w)
+    dist.all_reduce(w.grad, group=group)

@@ -129,6 +129,48 @@ def run_ckpt_manager(rank, world, device, tmp_dir):
     return res
 
 
+def run_pp(rank, world, device):
+    """GPT-2 in pipeline stages over NCCL point-to-point (1F1B, four micro-batches): the loss and the gradients of
+    every stage's layers against one process running the same micro-batches."""
+    from jax_gpt_b200.models.gpt2 import GPT, GPTConfig
+    from jax_gpt_b200.parallel.pipeline import gpt2_stage, split_layers
+    cfg = GPTConfig(d_model=128, d_head=64, d_ff=512, d_context=128, n_head=2, n_kv_head=2, n_layers=4, vocab_size=512)
+    B, T, n_micro = 2, 128, 4
+    model = GPT(cfg, seed=9, device=device, dtype=torch.bfloat16)
+    ref = GPT(cfg, seed=9, device=device, dtype=torch.bfloat16)
+    for m in (model, ref):
+        m.requires_grad_(True)
+    g = torch.Generator().manual_seed(3)
+    toks = [torch.randint(0, cfg.vocab_size, (B, T + 1), generator=g).to(device) for _ in range(n_micro)]
+    stage = gpt2_stage(model, rank, world, B, T, device=device)
+    inputs = [t[:, :-1] for t in toks] if rank == 0 else ([t[:, 1:] for t in toks] if rank == world - 1 else [None] * n_micro)
+    loss = stage.run(inputs)
+    torch.cuda.synchronize()
+    tot = 0.0
+    for t in toks:
+        logits, _ = ref(t[:, :-1])
+        l = torch.nn.functional.cross_entropy(logits.float().reshape(-1, cfg.vocab_size), t[:, 1:].reshape(-1)) / n_micro
+        l.backward()
+        tot += float(l)
+    mine = split_layers(cfg.n_layers, world)[rank]
+    worst = 0.0
+    for k, v in model.params.items():
+        if not k.startswith("h.") or v.grad is None:
+            continue
+        worst = max(worst, rel(v.grad[mine.start:mine.stop], ref.params[k].grad[mine.start:mine.stop]))
+    res = {"stage_grad_rel": worst}
+    t = torch.tensor([worst], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res["stage_grad_rel"] = float(t)
+    lt = torch.tensor([float(loss) if loss is not None else 0.0], device=device)
+    dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    res["loss_abs_err"] = abs(float(lt) - tot)
+    if rank == 0:
+        e = model.params["wte.embedding"].grad
+        res["first_stage_embed_grad"] = float(e.abs().sum()) if e is not None else 0.0
+    return res
+
+
 def run_tp(rank, world, device):
     """all-gather -> GEMM and GEMM -> reduce-scatter against their unfused definitions."""
     from jax_gpt_b200 import _ext
@@ -437,6 +479,8 @@ def main():
         res = run_fsdp(rank, world, device, True)
     elif what == "ckpt_manager":
         res = run_ckpt_manager(rank, world, device, out_path + ".ckpt")
+    elif what == "pp":
+        res = run_pp(rank, world, device)
     elif what == "tp":
         res = run_tp(rank, world, device)
     elif what == "fsdp_ag":

@@ -55,6 +55,12 @@ def test_checkpoint_manager_saves_trained_sharded_state_two_gpus(tmp_path):
     assert res["moved_from_init"] > 1e-4, res
 
 
+def test_pipeline_1f1b_gpt2_over_nccl_two_gpus(tmp_path):
+    """PP = 2 over NCCL p2p == one GPU: loss and the gradients of both stages' blocks."""
+    res = _run("pp", tmp_path, port=29623)
+    assert res["stage_grad_rel"] < 3e-2 and res["loss_abs_err"] < 2e-2, res
+
+
 def test_tp_fused_gemms_two_gpus(tmp_path):
     res = _run("tp", tmp_path, port=29612)
     assert res["ag_gemm"] < 1e-2 and res["gemm_rs"] < 1e-2, res

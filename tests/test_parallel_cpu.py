@@ -71,6 +71,43 @@ def test_pipeline_1f1b_matches_single_process():
         mp.spawn(_pp_worker, args=(2, os.path.join(d, "rdv")), nprocs=2, join=True)
 
 
+def _pp_gpt2_worker(rank, world, path):
+    dist.init_process_group("gloo", init_method=f"file://{path}", rank=rank, world_size=world)
+    from jax_gpt_b200.models.gpt2 import GPT, GPTConfig
+    from jax_gpt_b200.parallel.pipeline import gpt2_stage, sync_tied_embedding_grad
+    cfg = GPTConfig(d_model=32, d_head=16, d_ff=64, d_context=16, n_head=2, n_kv_head=2, n_layers=4, vocab_size=64)
+    model, ref = GPT(cfg, seed=9), GPT(cfg, seed=9)
+    for m in (model, ref):
+        m.requires_grad_(True)
+    g = torch.Generator().manual_seed(3)
+    toks = [torch.randint(0, 64, (2, 17), generator=g) for _ in range(4)]
+    stage = gpt2_stage(model, rank, world, 2, 16)
+    inputs = [t[:, :-1] for t in toks] if rank == 0 else ([t[:, 1:] for t in toks] if rank == world - 1 else [None] * 4)
+    loss = stage.run(inputs)
+    sync_tied_embedding_grad(model)
+    tot = 0.0
+    for t in toks:
+        part = torch.nn.functional.cross_entropy(ref(t[:, :-1])[0].reshape(-1, 64), t[:, 1:].reshape(-1)) / 4
+        part.backward()
+        tot += float(part.detach())
+    mine = split_layers(cfg.n_layers, world)[rank]
+    for k, v in model.params.items():
+        if k.startswith("h."):
+            assert torch.allclose(v.grad[mine.start:mine.stop], ref.params[k].grad[mine.start:mine.stop], atol=1e-6), k
+    assert torch.allclose(model.params["wte.embedding"].grad, ref.params["wte.embedding"].grad, atol=1e-6)
+    if rank == world - 1:
+        assert abs(float(loss) - tot) < 1e-5
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_pipeline_gpt2_stages_match_single_process(world):
+    """GPT-2 cut into pipeline stages (embeddings first, tied head and loss last): block gradients per stage and the
+    tied embedding gradient after its cross-stage sum equal one process."""
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_pp_gpt2_worker, args=(world, os.path.join(d, "rdv")), nprocs=world, join=True)
+
+
 def _wd_worker(rank, world, path, result_path):
     from jax_gpt_b200.utils.watchdog import PeerFailure, Watchdog
     store = dist.FileStore(path, world)
