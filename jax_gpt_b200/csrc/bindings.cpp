@@ -267,6 +267,21 @@ void adamw(Tensor p, Tensor g, Tensor m, Tensor v, c10::optional<Tensor> p_bf16,
       zero_grad ? 1 : 0, cur_stream()));
 }
 
+void adamw_bf16_state(Tensor p, Tensor g, Tensor m, Tensor v, const Tensor& hp, const c10::optional<Tensor>& gnorm_sq,
+                      double beta1, double beta2, double eps, double wd, double clip, bool zero_grad, int64_t seed) {
+  c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.numel() == g.numel() && p.numel() == m.numel() && p.numel() == v.numel(), "adamw_bf16_state: sizes differ");
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw_bf16_state: contiguous");
+  TORCH_CHECK(p.scalar_type() == at::kBFloat16 && m.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 &&
+                  g.scalar_type() == at::kFloat,
+              "adamw_bf16_state: bf16 weights and moments, fp32 gradient");
+  B200_CHECK_CUDA(b200::launch_adamw_bf16_state(
+      bf16_mut(p), g.data_ptr<float>(), bf16_mut(m), bf16_mut(v), p.numel(), hp.data_ptr<float>(),
+      gnorm_sq.has_value() ? gnorm_sq->data_ptr<float>() : nullptr, static_cast<float>(beta1), static_cast<float>(beta2),
+      static_cast<float>(eps), static_cast<float>(wd), static_cast<float>(clip), zero_grad ? 1 : 0,
+      static_cast<uint32_t>(seed), cur_stream()));
+}
+
 // q/k/v: 2-D bf16 views [B*T, H*D] (possibly column slices of one fused buffer).
 void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Tensor lse, int64_t B, int64_t T,
               int64_t H, int64_t Hkv, int64_t D, double scale, bool causal, int64_t Dv) {
@@ -466,6 +481,10 @@ TORCH_LIBRARY(b200, m) {
       "dq_accum, Tensor(c!) dk, Tensor(d!) dv, int B, int T, int H, int Hkv, int D, float scale, bool causal) -> ()",
       &attn_bwd);
   m.def("cast_rows(Tensor src, Tensor(a!) dst) -> ()", &cast_rows);
+  m.def(
+      "adamw_bf16_state(Tensor(a!) p, Tensor(b!) g, Tensor(c!) m, Tensor(d!) v, Tensor hp, Tensor? gnorm_sq, float beta1, "
+      "float beta2, float eps, float wd, float clip, bool zero_grad, int seed) -> ()",
+      &adamw_bf16_state);
   m.def(
       "attn_fwd_cached(Tensor q, Tensor kcache, Tensor vcache, Tensor(a!) out, Tensor(b!) lse, int B, int Tq, int H, "
       "int Tk, int q_pos0, float scale, bool causal) -> ()",

@@ -578,6 +578,61 @@ cudaError_t launch_sumsq(const float* g, int64_t n, float* out, cudaStream_t st)
   return cudaGetLastError();
 }
 
+// AdamW with ALL state in bf16: the weights themselves are the master copy and both moments are bf16, 6 bytes of
+// state per parameter instead of 16 (the 77 B-parameter expert banks of the MoE benchmark shapes do not fit
+// otherwise). Every bf16 store is rounded stochastically (a per-element hash of index and step supplies the lower
+// 16 bits), so updates smaller than half a bf16 ulp still move the weight in expectation instead of being lost.
+__device__ __forceinline__ uint32_t hash32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352dU;
+  x ^= x >> 15;
+  x *= 0x846ca68bU;
+  x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ uint32_t sr_bf16_bits(float x, uint32_t rnd16) {
+  uint32_t b = __float_as_uint(x);
+  if ((b & 0x7f800000u) != 0x7f800000u) b += rnd16;   // leave inf / nan alone
+  return b >> 16;
+}
+
+__global__ void adamw_bf16_state_kernel(__nv_bfloat16* __restrict__ p, float* __restrict__ g,
+                                        __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v, int64_t n,
+                                        const float* __restrict__ hp, const float* __restrict__ gnorm_sq, float beta1,
+                                        float beta2, float eps, float wd, float clip, int zero_grad, uint32_t seed) {
+  const float lr = hp[0], bc1 = hp[1], bc2 = hp[2], gscale = hp[3];
+  float coef = gscale;
+  if (gnorm_sq != nullptr && clip > 0.f) {
+    const float norm = sqrtf(*gnorm_sq) * gscale;
+    coef *= fminf(1.f, clip / (norm + 1e-6f));
+  }
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nth = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = tid; i < n; i += nth) {
+    float gi = g[i] * coef;
+    float mi = __bfloat162float(m[i]), vi = __bfloat162float(v[i]), pi = __bfloat162float(p[i]);
+    mi = beta1 * mi + (1.f - beta1) * gi;
+    vi = beta2 * vi + (1.f - beta2) * gi * gi;
+    pi -= lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * pi);
+    const uint32_t r = hash32(static_cast<uint32_t>(i) * 0x9e3779b9u + static_cast<uint32_t>(i >> 32) + seed);
+    const uint32_t r2 = hash32(r ^ 0x85ebca6bu);
+    reinterpret_cast<uint16_t*>(p)[i] = static_cast<uint16_t>(sr_bf16_bits(pi, r & 0xffffu));
+    reinterpret_cast<uint16_t*>(m)[i] = static_cast<uint16_t>(sr_bf16_bits(mi, r >> 16));
+    reinterpret_cast<uint16_t*>(v)[i] = static_cast<uint16_t>(sr_bf16_bits(vi, r2 & 0xffffu));
+    if (zero_grad) g[i] = 0.f;
+  }
+}
+
+cudaError_t launch_adamw_bf16_state(__nv_bfloat16* p, float* g, __nv_bfloat16* m, __nv_bfloat16* v, int64_t n,
+                                    const float* hp, const float* gnorm_sq, float beta1, float beta2, float eps,
+                                    float wd, float clip, int zero_grad, uint32_t seed, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  const int grid = static_cast<int>(std::min<int64_t>((n + 255) / 256, 148 * 16));
+  adamw_bf16_state_kernel<<<grid, 256, 0, st>>>(p, g, m, v, n, hp, gnorm_sq, beta1, beta2, eps, wd, clip, zero_grad,
+                                                seed);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_adamw(float* p, float* g, float* m, float* v, __nv_bfloat16* p_bf16, int64_t n, const float* hp,
                          const float* gnorm_sq, float beta1, float beta2, float eps, float wd, float clip,
                          int zero_grad, cudaStream_t st) {

@@ -24,6 +24,11 @@ cudaError_t launch_ce_fwd_bwd(__nv_bfloat16* logits, const int32_t* targets, flo
                               float scale, int write_grad, cudaStream_t st);
 cudaError_t launch_bias_grad(const __nv_bfloat16* dy, float* dbias, int M, int N, cudaStream_t st);
 cudaError_t launch_sumsq(const float* g, int64_t n, float* out, cudaStream_t st);
+// AdamW with bf16 weights (no fp32 master) and bf16 moments, stochastically rounded; `seed` should change every step.
+cudaError_t launch_adamw_bf16_state(__nv_bfloat16* p, float* g, __nv_bfloat16* m, __nv_bfloat16* v, int64_t n,
+                                    const float* hp, const float* gnorm_sq, float beta1, float beta2, float eps,
+                                    float wd, float clip, int zero_grad, uint32_t seed, cudaStream_t st);
+
 cudaError_t launch_adamw(float* p, float* g, float* m, float* v, __nv_bfloat16* p_bf16, int64_t n, const float* hp,
                          const float* gnorm_sq, float beta1, float beta2, float eps, float wd, float clip,
                          int zero_grad, cudaStream_t st);

@@ -62,11 +62,24 @@ def _attn_params(c: DeepSeekV3Config, lead, n, ones):
     }
 
 
-def init_params(config: DeepSeekV3Config, key=0, dtype=torch.float32, device="cpu") -> dict:
+def init_params(config: DeepSeekV3Config, key=0, dtype=torch.float32, device="cpu", on_device: bool = False,
+                expert_shard=None) -> dict:
+    """``on_device=True`` draws every tensor on ``device`` in ``dtype`` (no host copy); ``expert_shard=(rank, world)``
+    creates only this rank's routed experts from a stream of their own (see models/qwen35/model.py:init_params)."""
+    from ..qwen35.model import _normal
     c = config
-    g = key if isinstance(key, torch.Generator) else torch.Generator().manual_seed(int(key))
+    if on_device and torch.device(device).type != "cpu" and not isinstance(key, torch.Generator):
+        g = torch.Generator(device=device).manual_seed(int(key))
+    else:
+        g = key if isinstance(key, torch.Generator) else torch.Generator().manual_seed(int(key))
     dev = dict(device=device, dtype=dtype)
-    n = lambda *s: (torch.randn(*s, generator=g) * 0.02).to(**dev)
+    n = _normal(g, device, dtype)
+    e, n_local = n, c.n_routed_experts
+    if expert_shard is not None:
+        rank, world = expert_shard
+        assert c.n_routed_experts % world == 0
+        n_local = c.n_routed_experts // world
+        e = _normal(torch.Generator(device=g.device).manual_seed((int(g.initial_seed()) + 1) * 1000003 + rank), device, dtype)
     ones = lambda *s: torch.ones(*s, **dev)
     Ld, Lm, D = c.first_k_dense, c.n_moe_layers, c.d_model
     E, I, SI = c.n_routed_experts, c.moe_intermediate_size, c.moe_intermediate_size * c.n_shared_experts
@@ -81,7 +94,7 @@ def init_params(config: DeepSeekV3Config, key=0, dtype=torch.float32, device="cp
         p["moe_layers"] = {
             "attn_norm": ones(Lm, D), "ffn_norm": ones(Lm, D), "attn": _attn_params(c, (Lm,), n, ones),
             "moe": {"gate_weight": n(Lm, D, E), "e_score_correction_bias": torch.zeros(Lm, E, **dev),
-                    "gate_proj": n(Lm, E, D, I), "up_proj": n(Lm, E, D, I), "down_proj": n(Lm, E, I, D),
+                    "gate_proj": e(Lm, n_local, D, I), "up_proj": e(Lm, n_local, D, I), "down_proj": e(Lm, n_local, I, D),
                     "shared_gate_proj": n(Lm, D, SI), "shared_up_proj": n(Lm, D, SI), "shared_down_proj": n(Lm, SI, D)},
         }
     return p

@@ -34,31 +34,60 @@ from .primitives import precompute_rope_freqs, rms_norm
 from .quantize import quantize_params_fp8
 
 
-def _moe_params(c: Qwen35Config, lead, g, dtype, device):
+def _normal(g, device, dtype):
+    """``n(*shape)``: N(0, 0.02) of that shape. A generator that lives on the target device draws there, in the
+    target dtype (no host copy of the tree); a CPU generator draws in fp32 on the host and moves the result."""
+    if g.device.type != "cpu":
+        return lambda *s: torch.randn(*s, generator=g, device=g.device, dtype=dtype).mul_(0.02)
+    return lambda *s: (torch.randn(*s, generator=g) * 0.02).to(device=device, dtype=dtype)
+
+
+def _moe_params(c: Qwen35Config, lead, g, dtype, device, g_experts=None, n_local=None):
     D, E, I, SI = c.d_model, c.n_routed_experts, c.moe_intermediate_size, c.shared_expert_intermediate_size
-    n = lambda *s: (torch.randn(*lead, *s, generator=g) * 0.02).to(device=device, dtype=dtype)
+    nn = _normal(g, device, dtype)
+    n = lambda *s: nn(*lead, *s)
+    if n_local is not None:           # only this rank's experts, from the rank's own stream
+        ne = _normal(g_experts, device, dtype)
+        e = lambda *s: ne(*lead, *s)
+        El = n_local
+    else:
+        e, El = n, E
     return {
-        "gate_weight": n(D, E), "gate_proj": n(E, D, I), "up_proj": n(E, D, I), "down_proj": n(E, I, D),
+        "gate_weight": n(D, E), "gate_proj": e(El, D, I), "up_proj": e(El, D, I), "down_proj": e(El, I, D),
         "shared_gate_proj": n(D, SI), "shared_up_proj": n(D, SI), "shared_down_proj": n(SI, D),
         "shared_expert_gate_weight": n(D, 1),
     }
 
 
-def init_params(config: Qwen35Config, key=0, dtype=torch.float32, fp8: bool = False, device="cpu") -> dict:
-    """``key``: integer seed (or a torch.Generator)."""
+def init_params(config: Qwen35Config, key=0, dtype=torch.float32, fp8: bool = False, device="cpu",
+                on_device: bool = False, expert_shard=None) -> dict:
+    """``key``: integer seed (or a torch.Generator). ``on_device=True`` draws every tensor on ``device`` in ``dtype``
+    (nothing of the tree ever exists on the host: the 77 B-parameter benchmark shape cannot be initialised there).
+    ``expert_shard=(rank, world)`` creates only this rank's ``E / world`` routed experts, from a stream of their own
+    seeded with (key, rank); everything else is drawn identically on every rank."""
     c = config
-    g = key if isinstance(key, torch.Generator) else torch.Generator().manual_seed(int(key))
+    if on_device and torch.device(device).type != "cpu" and not isinstance(key, torch.Generator):
+        g = torch.Generator(device=device).manual_seed(int(key))
+    else:
+        g = key if isinstance(key, torch.Generator) else torch.Generator().manual_seed(int(key))
+    g_experts = n_local = None
+    if expert_shard is not None:
+        rank, world = expert_shard
+        assert c.n_routed_experts % world == 0
+        n_local = c.n_routed_experts // world
+        g_experts = torch.Generator(device=g.device).manual_seed((int(g.initial_seed()) + 1) * 1000003 + rank)
     G, nd, D = c.n_groups, c.n_delta_per_group, c.d_model
     Kd, Vd, Hv = c.delta_key_dim, c.delta_value_dim, c.delta_n_v_heads
     Hq, Hkv, dh = c.gqa_n_q_heads, c.gqa_n_kv_heads, c.gqa_head_dim
     dev = dict(device=device, dtype=dtype)
-    n = lambda *s: (torch.randn(*s, generator=g) * 0.02).to(**dev)
+    n = _normal(g, device, dtype)
     zeros = lambda *s: torch.zeros(*s, **dev)
     ones = lambda *s: torch.ones(*s, **dev)
     delta_attn = {
         "in_proj_qkv": n(G, nd, D, 2 * Kd + Vd), "in_proj_z": n(G, nd, D, Vd), "in_proj_b": n(G, nd, D, Hv),
         "in_proj_a": n(G, nd, D, Hv), "conv_weight": n(G, nd, 2 * Kd + Vd, c.delta_conv_kernel),
-        "A_log": torch.log(torch.rand(G, nd, Hv, generator=g) * 15.9 + 0.1).to(**dev), "dt_bias": ones(G, nd, Hv),
+        "A_log": torch.log(torch.rand(G, nd, Hv, generator=g, device=g.device) * 15.9 + 0.1).to(**dev),
+        "dt_bias": ones(G, nd, Hv),
         "norm_weight": ones(G, nd, c.delta_v_head_dim), "out_proj": n(G, nd, Vd, D),
     }
     gqa_attn = {
@@ -69,9 +98,9 @@ def init_params(config: Qwen35Config, key=0, dtype=torch.float32, fp8: bool = Fa
         "embed": n(c.vocab_size, D), "final_norm": zeros(D), "lm_head": n(D, c.vocab_size),
         "groups": {
             "delta_layers": {"attn_norm": zeros(G, nd, D), "moe_norm": zeros(G, nd, D), "attn": delta_attn,
-                             "moe": _moe_params(c, (G, nd), g, dtype, device)},
+                             "moe": _moe_params(c, (G, nd), g, dtype, device, g_experts, n_local)},
             "gqa_layer": {"attn_norm": zeros(G, D), "moe_norm": zeros(G, D), "attn": gqa_attn,
-                          "moe": _moe_params(c, (G,), g, dtype, device)},
+                          "moe": _moe_params(c, (G,), g, dtype, device, g_experts, n_local)},
         },
     }
     return quantize_params_fp8(params) if fp8 else params

@@ -119,6 +119,22 @@ def adamw_ref(p, g, m, v, hp, gnorm_sq, beta1, beta2, eps, wd, clip, p_bf16=None
         g.zero_()
 
 
+def adamw_bf16_state(p, g, m, v, hp, gnorm_sq=None, *, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, clip=0.0,
+                     zero_grad=True, seed=0):
+    """AdamW whose whole state is bf16: ``p`` (the weights, no fp32 master), ``m`` and ``v``; ``g`` fp32. Stores are
+    rounded stochastically on CUDA (``seed`` should change every step); the CPU path rounds to nearest."""
+    if p.is_cuda:
+        _ext.ops().adamw_bf16_state(p, g, m, v, hp, gnorm_sq, beta1, beta2, eps, wd, clip, zero_grad, int(seed) & 0x7fffffff)
+        return
+    pf, mf, vf = p.float(), m.float(), v.float()
+    adamw_ref(pf, g.clone(), mf, vf, hp, gnorm_sq, beta1, beta2, eps, wd, clip, None, zero_grad=False)
+    p.copy_(pf)
+    m.copy_(mf)
+    v.copy_(vf)
+    if zero_grad:
+        g.zero_()
+
+
 def adamw(p, g, m, v, hp, gnorm_sq=None, *, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, clip=0.0, p_bf16=None,
           zero_grad=True):
     """Fused AdamW over flat fp32 buffers; also refreshes the bf16 compute copy and zeroes the grad."""

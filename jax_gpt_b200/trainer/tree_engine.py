@@ -48,18 +48,33 @@ def default_decay(path, t) -> bool:
     return t.dim() >= 2 and "norm" not in path[-1]
 
 
+def _drop(tree: dict, path) -> None:
+    """Removes a leaf from a nested dict (its storage is freed once nothing else refers to it)."""
+    node = tree
+    for k in path[:-1]:
+        node = node[k]
+    node.pop(path[-1], None)
+
+
 class TreeTrainEngine:
     def __init__(self, params: dict, loss_fn: Callable, *, device=None, compute_dtype=torch.bfloat16,
                  local: Optional[Callable] = None, decay: Callable = default_decay, lr: float = 3e-4,
                  min_lr: float = 3e-5, warmup_steps: int = 100, lr_decay_steps: int = 10000, weight_decay: float = 0.1,
                  beta1: float = 0.9, beta2: float = 0.95, grad_clip: float = 1.0, dist_optimizer=None,
-                 dp_world: int = 1, unstack: Optional[Callable] = None):
+                 dp_world: int = 1, unstack: Optional[Callable] = None, local_state_dtype=torch.float32,
+                 consume_params: bool = False):
         """``params``: nested dict of tensors (any device / dtype; copied). ``loss_fn(tree, *batch)``
         returns a scalar. ``local(path, tensor)`` marks expert-parallel leaves. ``unstack(path, tensor)`` gives
         the number of leading (layer) axes of a dense leaf that the model indexes one slice at a time: the tree then
         holds nested lists of per-slice autograd leaves instead of one stacked leaf, so that a layer's gradient is
         added to its own slice of the flat buffer (a stacked leaf receives one FULL-size gradient per slice from
-        the select-backward of every layer, which costs layers^2 traffic)."""
+        the select-backward of every layer, which costs layers^2 traffic).
+
+        ``local_state_dtype=torch.bfloat16`` keeps the expert-parallel leaves WITHOUT an fp32 master and with bf16
+        moments (stochastically rounded AdamW, csrc/elementwise.cu): 6 bytes of state per expert parameter instead
+        of 16 plus the fp32 gradient, which is what lets the 512-expert / 48-layer benchmark shape fit eight GPUs.
+        ``consume_params=True`` frees every leaf of ``params`` as soon as it has been copied into the flat buffers
+        (the tree is emptied), so that a model initialised on the device is not held twice."""
         self.device = torch.device(device) if device is not None else torch.device("cpu")
         self.loss_fn = loss_fn
         self.hyper = dict(lr=lr, min_lr=min_lr, warmup=warmup_steps, decay=lr_decay_steps, wd=weight_decay,
@@ -92,9 +107,14 @@ class TreeTrainEngine:
         else:
             compute = torch.zeros(total, device=dev, dtype=compute_dtype)
         grad = alloc_g(total) if alloc_g is not None else torch.zeros(total, device=dev, dtype=torch.float32)
-        for p, t in dense:
+        del leaves
+        for i, (p, t) in enumerate(dense):
             o, n, _ = self.offsets[p]
             master[o:o + n].copy_(t.reshape(-1).to(torch.float32))
+            if consume_params:          # keep only the shape: the caller's tree and these lists let go of the storage
+                _drop(params, p)
+                dense[i] = (p, torch.empty(t.shape, device="meta", dtype=t.dtype))
+        del t
         compute.copy_(master)
         grad.zero_()
         self.flat = SimpleNamespace(total=total, n_decay=n_decay, master=master, compute=compute, grad=grad)
@@ -106,16 +126,24 @@ class TreeTrainEngine:
             self.local_offsets[p] = (off, t.numel(), tuple(t.shape))
             off += (t.numel() + 63) // 64 * 64
         self.local_total = off
+        self.local_lowmem = bool(off) and local_state_dtype == torch.bfloat16 and compute_dtype == torch.bfloat16
         if off:
-            self.local_master = torch.zeros(off, device=dev, dtype=torch.float32)
             self.local_compute = torch.zeros(off, device=dev, dtype=compute_dtype)
             self.local_grad = torch.zeros(off, device=dev, dtype=torch.float32)
-            self.local_m = torch.zeros(off, device=dev, dtype=torch.float32)
-            self.local_v = torch.zeros(off, device=dev, dtype=torch.float32)
-            for p, t in loc:
+            sdt = torch.bfloat16 if self.local_lowmem else torch.float32
+            self.local_m = torch.zeros(off, device=dev, dtype=sdt)
+            self.local_v = torch.zeros(off, device=dev, dtype=sdt)
+            # without an fp32 master the bf16 compute copy IS the master
+            self.local_master = self.local_compute if self.local_lowmem else torch.zeros(off, device=dev, dtype=torch.float32)
+            for i, (p, t) in enumerate(loc):
                 o, n, _ = self.local_offsets[p]
-                self.local_master[o:o + n].copy_(t.reshape(-1).to(torch.float32))
-            self.local_compute.copy_(self.local_master)
+                self.local_master[o:o + n].copy_(t.reshape(-1).to(self.local_master.dtype))
+                if consume_params:
+                    _drop(params, p)
+                    loc[i] = (p, torch.empty(t.shape, device="meta", dtype=t.dtype))
+            del t
+            if not self.local_lowmem:
+                self.local_compute.copy_(self.local_master)
         self.local_sq = torch.zeros(1, device=dev, dtype=torch.float32)
 
         # ---- the tree the model sees ----
@@ -215,7 +243,11 @@ class TreeTrainEngine:
                            p_bf16=pb(nd, fl.total), **kw)
             if cdt != torch.bfloat16:
                 fl.compute.copy_(fl.master)
-        if self.local_total:
+        if self.local_total and self.local_lowmem:
+            misc.adamw_bf16_state(self.local_compute, self.local_grad, self.local_m, self.local_v, self.hp, gsq,
+                                  beta1=h["b1"], beta2=h["b2"], eps=1e-8, wd=h["wd"], clip=h["clip"],
+                                  seed=0x9e3779b1 * (self.step_count + 1))
+        elif self.local_total:
             lb = self.local_compute if self.local_compute.dtype == torch.bfloat16 else None
             misc.adamw(self.local_master, self.local_grad, self.local_m, self.local_v, self.hp, gsq, beta1=h["b1"],
                        beta2=h["b2"], eps=1e-8, wd=h["wd"], clip=h["clip"], p_bf16=lb)
@@ -296,7 +328,8 @@ class TreeTrainEngine:
                 if m is not None:
                     self.local_m[o:o + n].copy_(get(m, p).reshape(-1).to(self.local_m))
                     self.local_v[o:o + n].copy_(get(v, p).reshape(-1).to(self.local_v))
-            self.local_compute.copy_(self.local_master)
+            if not self.local_lowmem:
+                self.local_compute.copy_(self.local_master)
         if step is not None:
             self.step_count = int(step)
 

@@ -263,3 +263,34 @@ def test_attention_forward_wide_heads(cuda_device, B, T, H, Hkv, D, Dv):
     s = s.masked_fill(~torch.ones(T, T, dtype=torch.bool, device=cuda_device).tril(), float("-inf"))
     ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), vv)
     assert out.shape == (B, T, H, Dv) and _rel_err(out, ref) < 2e-2
+
+
+def test_adamw_with_bf16_state_is_unbiased(cuda_device):
+    """AdamW whose weights and moments are bf16 (no fp32 master): every element within one bf16 ulp of the fp32
+    update, and, because the stores round stochastically, the mean error far below the half-ulp bias that
+    round-to-nearest would leave on updates smaller than an ulp."""
+    from jax_gpt_b200.ops import misc
+    torch.manual_seed(4)
+    n = 1 << 20
+    p0 = (torch.randn(n, device=cuda_device) * 0.02).to(torch.bfloat16)
+    g = torch.randn(n, device=cuda_device) * 1e-3
+    m0 = (torch.randn(n, device=cuda_device) * 1e-4).to(torch.bfloat16)
+    v0 = (torch.rand(n, device=cuda_device) * 1e-6).to(torch.bfloat16)
+    hp = torch.tensor([1e-4, 0.1, 0.05, 1.0], device=cuda_device)
+    pr, mr, vr = p0.float().cpu(), m0.float().cpu(), v0.float().cpu()
+    misc.adamw_ref(pr, g.cpu().clone(), mr, vr, hp.cpu(), None, 0.9, 0.95, 1e-8, 0.1, 0.0, None, zero_grad=False)
+    p, m, v, gg = p0.clone(), m0.clone(), v0.clone(), g.clone()
+    misc.adamw_bf16_state(p, gg, m, v, hp, None, wd=0.1, seed=123)
+    assert gg.abs().max().item() == 0
+    ulp = (p0.float().abs() * 2 ** -7).clamp_min(1e-30).cpu()
+    err = p.float().cpu() - pr
+    assert (err.abs() <= ulp * 1.01).all()
+    step = (pr - p0.float().cpu())
+    # the true update is a small fraction of an ulp for most elements, yet its mean survives the rounding
+    assert step.abs().median() < 0.5 * ulp.median()
+    assert abs(err.mean().item()) < 0.02 * step.abs().mean().item()
+    assert _rel_err(m, mr) < 1e-2 and _rel_err(v, vr) < 1e-2
+    # a different seed rounds differently
+    p2, m2, v2, g2 = p0.clone(), m0.clone(), v0.clone(), g.clone()
+    misc.adamw_bf16_state(p2, g2, m2, v2, hp, None, wd=0.1, seed=124)
+    assert not torch.equal(p, p2)
