@@ -75,6 +75,26 @@ cudaError_t launch_gdn_scan_bwd(const __nv_bfloat16* kq, const __nv_bfloat16* in
                                 __nv_bfloat16* d_intra, __nv_bfloat16* d_kdec, __nv_bfloat16* d_veff, float* d_e, float* ds0,
                                 int bh, int n_chunks, int* status, cudaStream_t stream);
 
+// State-independent part of the chunked gated delta rule (gdn_chunk_kernels.cu), chunks of 64, dk = dv = 128.
+//   mixed [B, T, (2 Hqk + Hv) * 128] bf16: q | k | v after the conv + SiLU;  b_in, a_in [B, T, Hv] bf16: gate
+//   pre-activations;  A_log, dt_bias [Hv] fp32.
+// Writes the operands of launch_gdn_scan for BH = B * Hv (value head hv reads q/k head hv / (Hv / Hqk)) and
+// N = ceil(T / 64) chunks: kq, intra, kdec, veff, e (rows at or beyond T behave as zero-padded tokens).
+cudaError_t launch_gdn_chunk_prep(const __nv_bfloat16* mixed, const __nv_bfloat16* b_in, const __nv_bfloat16* a_in,
+                                  const float* A_log, const float* dt_bias, __nv_bfloat16* kq, __nv_bfloat16* intra,
+                                  __nv_bfloat16* kdec, __nv_bfloat16* veff, float* e, int B, int T, int Hqk, int Hv,
+                                  cudaStream_t stream);
+
+// Backward of launch_gdn_chunk_prep: recomputes the forward from the same inputs. d_kq / d_intra / d_kdec / d_veff
+// bf16 and d_e fp32 are shaped like the forward outputs. Writes d_mixed [B, T, conv_dim] bf16 (every element),
+// d_b, d_a [B, T, Hv] fp32, and ACCUMULATES d_A_log, d_dt_bias [Hv] fp32 (zero them first).
+cudaError_t launch_gdn_chunk_prep_bwd(const __nv_bfloat16* mixed, const __nv_bfloat16* b_in, const __nv_bfloat16* a_in,
+                                      const float* A_log, const float* dt_bias, const __nv_bfloat16* d_kq,
+                                      const __nv_bfloat16* d_intra, const __nv_bfloat16* d_kdec,
+                                      const __nv_bfloat16* d_veff, const float* d_e, __nv_bfloat16* d_mixed, float* d_b,
+                                      float* d_a, float* d_A_log, float* d_dt_bias, int B, int T, int Hqk, int Hv,
+                                      cudaStream_t stream);
+
 // Causal depthwise conv (width 4) + SiLU over x [B, T, C] bf16 with w [C, 4]; `state` (optional) [B, C, 4] fp32
 // receives the last four raw inputs of every channel.
 cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, float* state, int B,

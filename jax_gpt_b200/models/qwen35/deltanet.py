@@ -175,6 +175,63 @@ class _GdnScanFn(torch.autograd.Function):
         return d_kq, d_intra, d_kdec, d_veff, d_e, (ds0 if ctx.has_s0 else None)
 
 
+class _GdnChunkPrepFn(torch.autograd.Function):
+    """Everything of the chunked rule that does not depend on the running state, as one CUDA kernel forward and one
+    backward (csrc/gdn_chunk_kernels.cu): gates, L2 norms of q and k, in-chunk decays, the two 64 x 64 Gram
+    matrices, and the unit-lower-triangular solve. Inputs: ``mixed`` (B, T, 2 Kd + Vd) bf16 after conv + SiLU, the
+    gate pre-activations ``b``, ``a`` (B, T, Hv) bf16, ``A_log``, ``dt_bias`` (Hv,). Outputs: the operands of
+    ``_GdnScanFn`` for chunks of 64 (head widths 128). The backward recomputes the forward from the inputs, so
+    nothing but the inputs is kept alive."""
+
+    @staticmethod
+    def forward(ctx, mixed, b, a, A_log, dt_bias, n_qk, n_v):
+        from ... import _ext
+        B, T, _ = mixed.shape
+        N = (T + 63) // 64
+        dev, bf = mixed.device, torch.bfloat16
+        mixed, b, a = mixed.contiguous(), b.to(bf).contiguous(), a.to(bf).contiguous()
+        al, dt = A_log.float().contiguous(), dt_bias.float().contiguous()
+        BH = B * n_v
+        kq = torch.empty(BH, N, 128, 128, device=dev, dtype=bf)
+        intra = torch.empty(BH, N, 64, 64, device=dev, dtype=bf)
+        kdec = torch.empty(BH, N, 64, 128, device=dev, dtype=bf)
+        veff = torch.empty(BH, N, 64, 128, device=dev, dtype=bf)
+        e = torch.empty(BH, N, device=dev, dtype=torch.float32)
+        _ext.ops().gdn_chunk_prep(mixed, b, a, al, dt, kq, intra, kdec, veff, e, n_qk, n_v)
+        ctx.save_for_backward(mixed, b, a, al, dt)
+        ctx.heads = (n_qk, n_v)
+        ctx.param_dtypes = (A_log.dtype, dt_bias.dtype)
+        return kq, intra, kdec, veff, e
+
+    @staticmethod
+    def backward(ctx, d_kq, d_intra, d_kdec, d_veff, d_e):
+        from ... import _ext
+        mixed, b, a, al, dt = ctx.saved_tensors
+        n_qk, n_v = ctx.heads
+        bf = torch.bfloat16
+        d_mixed = torch.empty_like(mixed)
+        d_b = torch.empty(b.shape, device=b.device, dtype=torch.float32)
+        d_a = torch.empty_like(d_b)
+        d_al, d_dt = torch.zeros_like(al), torch.zeros_like(dt)
+        _ext.ops().gdn_chunk_prep_bwd(mixed, b, a, al, dt, d_kq.to(bf).contiguous(), d_intra.to(bf).contiguous(),
+                                      d_kdec.to(bf).contiguous(), d_veff.to(bf).contiguous(), d_e.float().contiguous(),
+                                      d_mixed, d_b, d_a, d_al, d_dt, n_qk, n_v)
+        return (d_mixed, d_b.to(b.dtype), d_a.to(a.dtype), d_al.to(ctx.param_dtypes[0]), d_dt.to(ctx.param_dtypes[1]),
+                None, None)
+
+
+def gated_delta_prefill_cuda(mixed, b, a, A_log, dt_bias, n_qk: int, n_v: int, initial_state=None):
+    """The whole gated-delta-rule prefill on this package's kernels (no library call): ``mixed`` (B, T, conv_dim)
+    bf16 after conv + SiLU and the gate pre-activations -> (o (B, T, Hv, 128) bf16, final state (B, Hv, 128, 128)
+    fp32). Chunks of 64 whatever the configured chunk size (the result does not depend on it)."""
+    B, T, _ = mixed.shape
+    kq, intra, kdec, veff, e = _GdnChunkPrepFn.apply(mixed, b, a, A_log, dt_bias, n_qk, n_v)
+    s0 = initial_state.float().reshape(B * n_v, 128, 128) if initial_state is not None else None
+    o, s_out = _GdnScanFn.apply(kq, intra, kdec, veff, e, s0)
+    o = o.reshape(B, n_v, -1, 128)[:, :, :T].transpose(1, 2)
+    return o, s_out.reshape(B, n_v, 128, 128)
+
+
 def chunk_gated_delta_rule(q, k, v, beta, g, chunk_size: int, initial_state=None):
     """Chunk-parallel gated delta rule in fp32.
     q,k (B,H,T,dk) normalised; v (B,H,T,dv); beta,g (B,H,T). Returns (o (B,H,T,dv), final state)."""
@@ -236,6 +293,11 @@ def deltanet_prefill(x, params, n_qk: int, n_v: int, dk: int, dv: int, conv_kern
     key_dim, rep = n_qk * dk, n_v // n_qk
     mixed, z, b, a = _project(x, params, n_qk, n_v, dk, dv)
     mixed, conv_state = causal_conv1d_prefill(mixed, params["conv_weight"])
+    if mixed.is_cuda and mixed.dtype == torch.bfloat16 and dk == 128 and dv == 128 and n_v % n_qk == 0:
+        o, S = gated_delta_prefill_cuda(mixed, b, a, params["A_log"], params["dt_bias"], n_qk, n_v, initial_state)
+        o = _gated_rms_norm(o.reshape(B * T * n_v, dv), z.reshape(B * T * n_v, dv), params["norm_weight"])
+        y = matmul_maybe_fp8(o.reshape(B, T, n_v * dv).to(x.dtype), params["out_proj"])
+        return y, S, conv_state
     q = mixed[..., :key_dim].reshape(B, T, n_qk, dk).float()
     k = mixed[..., key_dim:2 * key_dim].reshape(B, T, n_qk, dk).float()
     v = mixed[..., 2 * key_dim:].reshape(B, T, n_v, dv).float()

@@ -281,6 +281,100 @@ def test_gdn_chunk_scan_backward_kernel(cuda_device, T, with_state):
         assert _rel(a, b) < 4e-2, (n, _rel(a, b))
 
 
+def _gdn_inputs(B, T, n_qk, n_v, seed):
+    g = torch.Generator().manual_seed(seed)
+    conv_dim = (2 * n_qk + n_v) * 128
+    mixed = torch.nn.functional.silu(torch.randn(B, T, conv_dim, generator=g)).to(torch.bfloat16)
+    b = torch.randn(B, T, n_v, generator=g).to(torch.bfloat16)
+    a = torch.randn(B, T, n_v, generator=g).to(torch.bfloat16)
+    A_log = torch.log(torch.rand(n_v, generator=g) * 3.9 + 0.1)
+    dt_bias = torch.ones(n_v) + 0.1 * torch.randn(n_v, generator=g)
+    return mixed, b, a, A_log, dt_bias
+
+
+def _gdn_reference(mixed, b, a, A_log, dt_bias, n_qk, n_v, s0=None):
+    """fp32 PyTorch: split q | k | v, gates, L2 norms, chunked rule (triangular solve + chunk loop)."""
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    B, T, _ = mixed.shape
+    Kd, rep = n_qk * 128, n_v // n_qk
+    q = mixed[..., :Kd].reshape(B, T, n_qk, 128).float()
+    k = mixed[..., Kd:2 * Kd].reshape(B, T, n_qk, 128).float()
+    v = mixed[..., 2 * Kd:].reshape(B, T, n_v, 128).float()
+    beta, g = D._gates(b, a, {"A_log": A_log, "dt_bias": dt_bias})
+    q = (D._l2_norm(q) * 128 ** -0.5).repeat_interleave(rep, dim=2)
+    k = D._l2_norm(k).repeat_interleave(rep, dim=2)
+    o, S = D.chunk_gated_delta_rule(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), beta.transpose(1, 2),
+                                    g.transpose(1, 2), 64, s0)
+    return o.transpose(1, 2), S
+
+
+@pytest.mark.parametrize("B,T,n_qk,n_v", [(2, 64, 1, 1), (1, 200, 2, 4), (2, 1024, 2, 2)])
+def test_gdn_chunk_prep_kernel(cuda_device, B, T, n_qk, n_v):
+    """The fused state-independent kernel (gates, L2 norms, decays, Gram matrices, triangular solve) against the
+    same quantities computed in fp32 PyTorch with ``solve_triangular``."""
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    mixed, b, a, A_log, dt_bias = _gdn_inputs(B, T, n_qk, n_v, 7)
+    dev = lambda t: t.to(cuda_device)
+    with torch.no_grad():
+        kq, intra, kdec, veff, e = D._GdnChunkPrepFn.apply(dev(mixed), dev(b), dev(a), dev(A_log), dev(dt_bias), n_qk, n_v)
+    torch.cuda.synchronize()
+    # reference, chunk by chunk on zero-padded inputs
+    C, N, pad = 64, (T + 63) // 64, (-T) % 64
+    Kd, rep = n_qk * 128, n_v // n_qk
+    F = torch.nn.functional
+    q = (D._l2_norm(mixed[..., :Kd].reshape(B, T, n_qk, 128).float()) * 128 ** -0.5).repeat_interleave(rep, 2)
+    k = D._l2_norm(mixed[..., Kd:2 * Kd].reshape(B, T, n_qk, 128).float()).repeat_interleave(rep, 2)
+    v = mixed[..., 2 * Kd:].reshape(B, T, n_v, 128).float()
+    beta, g = D._gates(b, a, {"A_log": A_log, "dt_bias": dt_bias})
+    q, k, v = [F.pad(t.transpose(1, 2), (0, 0, 0, pad)).reshape(B * n_v, N, C, 128) for t in (q, k, v)]
+    beta, g = [F.pad(t.transpose(1, 2), (0, pad)).reshape(B * n_v, N, C) for t in (beta, g)]
+    G = g.cumsum(-1)
+    decay = torch.exp((G[..., :, None] - G[..., None, :]).tril())
+    kb = k * beta[..., None]
+    A = ((kb @ k.transpose(-1, -2)) * decay).tril(-1)
+    rhs = torch.cat([v * beta[..., None], kb * torch.exp(G)[..., None]], dim=-1)
+    sol = torch.linalg.solve_triangular(torch.eye(C) + A, rhs, upper=False, unitriangular=True)
+    ref_kq = torch.cat([sol[..., 128:], q * torch.exp(G)[..., None]], dim=-2)
+    ref_intra = ((q @ k.transpose(-1, -2)) * decay).tril()
+    ref_kdec = k * torch.exp(G[..., -1:] - G)[..., None]
+    for name, got, ref in (("kq", kq, ref_kq), ("intra", intra, ref_intra), ("kdec", kdec, ref_kdec),
+                           ("veff", veff, sol[..., :128]), ("e", e, torch.exp(G[..., -1]))):
+        assert _rel(got.float().cpu(), ref) < 8e-3, (name, _rel(got.float().cpu(), ref))
+
+
+@pytest.mark.parametrize("B,T,n_qk,n_v,with_state", [(1, 128, 1, 1, False), (2, 200, 2, 4, True)])
+def test_gated_delta_prefill_cuda_gradients(cuda_device, B, T, n_qk, n_v, with_state):
+    """The whole prefill on the kernels (chunk preparation + inter-chunk scan, forward and backward) against
+    autograd of the fp32 PyTorch path: outputs, final state, and the gradients of every input and gate parameter."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    ins = _gdn_inputs(B, T, n_qk, n_v, 9)
+    torch.manual_seed(10)
+    s0 = torch.randn(B, n_v, 128, 128) * 0.1 if with_state else None
+    wo, ws = torch.randn(B, T, n_v, 128), torch.randn(B, n_v, 128, 128) * 0.1
+
+    def run(device):
+        leaves = [t.clone().float().to(device).requires_grad_(True) for t in ins]
+        st = s0.clone().to(device).requires_grad_(True) if with_state else None
+        mixed, b, a = [t.to(torch.bfloat16) for t in leaves[:3]]          # the cast carries the gradient back in fp32
+        if device == "cpu":
+            o, S = _gdn_reference(mixed, b, a, leaves[3], leaves[4], n_qk, n_v, st)
+        else:
+            o, S = D.gated_delta_prefill_cuda(mixed, b, a, leaves[3], leaves[4], n_qk, n_v, st)
+        ((o.float() * wo.to(device)).sum() + (S * ws.to(device)).sum()).backward()
+        grads = [t.grad.float().cpu() for t in leaves] + ([st.grad.float().cpu()] if with_state else [])
+        return o.detach().float().cpu(), S.detach().float().cpu(), grads
+
+    o_ref, S_ref, g_ref = run("cpu")
+    o_k, S_k, g_k = run(cuda_device)
+    torch.cuda.synchronize()
+    _ext.check_status(cuda_device)
+    assert _rel(o_k, o_ref) < 2e-2 and _rel(S_k, S_ref) < 2e-2, (_rel(o_k, o_ref), _rel(S_k, S_ref))
+    names = ["mixed", "b", "a", "A_log", "dt_bias"] + (["s0"] if with_state else [])
+    bad = [(n, _rel(x, y)) for n, x, y in zip(names, g_k, g_ref) if _rel(x, y) > 5e-2]
+    assert not bad, bad
+
+
 def test_fp8_linear_training_path_on_gpu(cuda_device):
     """Forward / dgrad / wgrad of a linear layer on the hardware block-scaled FP8 GEMM: against the same recipe
     evaluated by the CPU reference kernels (same quantisation, so only summation order and bf16 rounding differ)
