@@ -290,51 +290,72 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap t_kq, const __grid_constant_
 }
 
 // y[b, t, c] = silu(sum_j w[c, j] x[b, t - (K-1) + j, c]); state[b, c, :] = the last K raw inputs (zero padded).
-template <int K>
+// One thread owns 8 channels and a strip of kStrip consecutive tokens: the K-wide window slides through registers,
+// so every input is read once (plus K - 1 rows of overlap per strip) and the weights once per strip.
+template <int K, int kStrip>
 __global__ void gdn_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                      __nv_bfloat16* __restrict__ y, float* __restrict__ state, int T, int C) {
-  const int b = blockIdx.z, t = blockIdx.y;
+  static_assert(K == 4, "the weight rows are read as one 8-byte vector");
+  const int b = blockIdx.z, t0 = blockIdx.y * kStrip;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c0 >= C) return;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float wv[8][K];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < K; ++j) wv[i][j] = __bfloat162float(w[(c0 + i) * K + j]);
+  for (int i = 0; i < 8; ++i) {
+    const uint2 u = *reinterpret_cast<const uint2*>(w + (c0 + i) * K);
+    const float2 lo = unpack_bf16x2(u.x), hi = unpack_bf16x2(u.y);
+    wv[i][0] = lo.x; wv[i][1] = lo.y; wv[i][2] = hi.x; wv[i][3] = hi.y;
+  }
+  const __nv_bfloat16* xb = x + static_cast<int64_t>(b) * T * C + c0;
+  float win[K][8];                      // win[j] = the input row at t - (K-1) + j
 #pragma unroll
   for (int j = 0; j < K; ++j) {
-    const int tt = t - (K - 1) + j;
-    if (tt < 0) continue;
-    const uint4 u = *reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(b) * T + tt) * C + c0);
+    const int tt = t0 - K + j;          // rows t0-K .. t0-1; the loop shifts before it uses them
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if (tt >= 0 && j > 0) u = *reinterpret_cast<const uint4*>(xb + static_cast<int64_t>(tt) * C);   // row 0 is shifted out unused
     const uint32_t in[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 f = unpack_bf16x2(in[e]);
-      acc[2 * e] += wv[2 * e][j] * f.x;
-      acc[2 * e + 1] += wv[2 * e + 1][j] * f.y;
+      win[j][2 * e] = f.x;
+      win[j][2 * e + 1] = f.y;
     }
+  }
+#pragma unroll
+  for (int s = 0; s < kStrip; ++s) {
+    const int t = t0 + s;
+    if (t >= T) break;
+    const uint4 u = *reinterpret_cast<const uint4*>(xb + static_cast<int64_t>(t) * C);
+    const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j + 1 < K; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) win[j][i] = win[j + 1][i];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(in[e]);
+      win[K - 1][2 * e] = f.x;
+      win[K - 1][2 * e + 1] = f.y;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        a0 += wv[2 * e][j] * win[j][2 * e];
+        a1 += wv[2 * e + 1][j] * win[j][2 * e + 1];
+      }
+      o[e] = pack_bf16x2(a0 / (1.f + __expf(-a0)), a1 / (1.f + __expf(-a1)));
+    }
+    *reinterpret_cast<uint4*>(y + (static_cast<int64_t>(b) * T + t) * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
     if (state != nullptr && t == T - 1) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = unpack_bf16x2(in[e]);
-        state[(static_cast<int64_t>(b) * C + c0 + 2 * e) * K + j] = f.x;
-        state[(static_cast<int64_t>(b) * C + c0 + 2 * e + 1) * K + j] = f.y;
-      }
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < K; ++j) state[(static_cast<int64_t>(b) * C + c0 + i) * K + j] = win[j][i];
     }
   }
-  if (state != nullptr && t == T - 1) {
-    for (int j = 0; j < K; ++j)
-      if (t - (K - 1) + j < 0)
-        for (int i = 0; i < 8; ++i) state[(static_cast<int64_t>(b) * C + c0 + i) * K + j] = 0.f;
-  }
-  uint32_t o[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float a0 = acc[2 * e], a1 = acc[2 * e + 1];
-    o[e] = pack_bf16x2(a0 / (1.f + __expf(-a0)), a1 / (1.f + __expf(-a1)));
-  }
-  *reinterpret_cast<uint4*>(y + (static_cast<int64_t>(b) * T + t) * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 
@@ -433,6 +454,90 @@ __global__ void gdn_conv_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, co
     for (int j = 0; j < K; ++j) atomicAdd(dw + (c0 + i) * K + j, dwa[i][j]);
 }
 
+// Gated RMSNorm of the scan output fused with the head-major -> token-major transpose:
+//   y[b, t, h, :] = w * o[b, h, t, :] * rsqrt(mean(o^2) + eps) * silu(z[b, t, h, :])
+// o is [B*Hv, Tpad, 128] bf16 (the scan kernel's layout), z and y are [B, T, Hv * 128] bf16. One warp per row.
+__global__ void gdn_gated_norm_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z,
+                                      const float* __restrict__ w, __nv_bfloat16* __restrict__ y, int rows, int T,
+                                      int Tpad, int Hv, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int h = row % Hv, bt = row / Hv, t = bt % T, b = bt / T;
+  const uint2 uo = *reinterpret_cast<const uint2*>(o + ((static_cast<int64_t>(b) * Hv + h) * Tpad + t) * 128 + lane * 4);
+  const uint2 uz = *reinterpret_cast<const uint2*>(z + static_cast<int64_t>(row) * 128 + lane * 4);
+  const float4 wv = *reinterpret_cast<const float4*>(w + lane * 4);
+  const float2 o0 = unpack_bf16x2(uo.x), o1 = unpack_bf16x2(uo.y), z0 = unpack_bf16x2(uz.x), z1 = unpack_bf16x2(uz.y);
+  float ss = o0.x * o0.x + o0.y * o0.y + o1.x * o1.x + o1.y * o1.y;
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+  const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+  auto silu = [](float v) { return v / (1.f + __expf(-v)); };
+  uint2 out;
+  out.x = pack_bf16x2(wv.x * o0.x * r * silu(z0.x), wv.y * o0.y * r * silu(z0.y));
+  out.y = pack_bf16x2(wv.z * o1.x * r * silu(z1.x), wv.w * o1.y * r * silu(z1.y));
+  *reinterpret_cast<uint2*>(y + static_cast<int64_t>(row) * 128 + lane * 4) = out;
+}
+
+// Backward: with n = o r, s = silu(z):  dn = dy w s;  do = r (dn - n mean(dn n));  dz = dy w n silu'(z);
+// dw += sum_rows dy n s (per-warp partial sums over a grid-stride loop, then one atomic per column and CTA).
+__global__ void gdn_gated_norm_bwd_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z,
+                                          const float* __restrict__ w, const __nv_bfloat16* __restrict__ dy,
+                                          __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dz,
+                                          float* __restrict__ dw, int rows, int T, int Tpad, int Hv, float eps) {
+  __shared__ float s_dw[8][128];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  const float4 wv = *reinterpret_cast<const float4*>(w + lane * 4);
+  const float wl[4] = {wv.x, wv.y, wv.z, wv.w};
+  float dwa[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const int h = row % Hv, bt = row / Hv, t = bt % T, b = bt / T;
+    const int64_t o_off = ((static_cast<int64_t>(b) * Hv + h) * Tpad + t) * 128 + lane * 4;
+    const int64_t r_off = static_cast<int64_t>(row) * 128 + lane * 4;
+    const uint2 uo = *reinterpret_cast<const uint2*>(o + o_off);
+    const uint2 uz = *reinterpret_cast<const uint2*>(z + r_off);
+    const uint2 ud = *reinterpret_cast<const uint2*>(dy + r_off);
+    const float2 a0 = unpack_bf16x2(uo.x), a1 = unpack_bf16x2(uo.y), b0 = unpack_bf16x2(uz.x), b1 = unpack_bf16x2(uz.y);
+    const float2 c0 = unpack_bf16x2(ud.x), c1 = unpack_bf16x2(ud.y);
+    const float ov[4] = {a0.x, a0.y, a1.x, a1.y}, zv[4] = {b0.x, b0.y, b1.x, b1.y}, dv[4] = {c0.x, c0.y, c1.x, c1.y};
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ss += ov[i] * ov[i];
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+    const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+    float nv[4], dn[4], dzv[4], dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float sg = 1.f / (1.f + __expf(-zv[i]));
+      const float sl = zv[i] * sg;
+      nv[i] = ov[i] * r;
+      dn[i] = dv[i] * wl[i] * sl;
+      dzv[i] = dv[i] * wl[i] * nv[i] * sg * (1.f + zv[i] * (1.f - sg));
+      dwa[i] += dv[i] * nv[i] * sl;
+      dot += dn[i] * nv[i];
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+    dot *= (1.f / 128.f);
+    uint2 uo_out, uz_out;
+    uo_out.x = pack_bf16x2(r * (dn[0] - nv[0] * dot), r * (dn[1] - nv[1] * dot));
+    uo_out.y = pack_bf16x2(r * (dn[2] - nv[2] * dot), r * (dn[3] - nv[3] * dot));
+    uz_out.x = pack_bf16x2(dzv[0], dzv[1]);
+    uz_out.y = pack_bf16x2(dzv[2], dzv[3]);
+    *reinterpret_cast<uint2*>(d_o + o_off) = uo_out;
+    *reinterpret_cast<uint2*>(dz + r_off) = uz_out;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s_dw[warp][lane * 4 + i] = dwa[i];
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float acc = 0.f;
+    for (int q = 0; q < wpb; ++q) acc += s_dw[q][threadIdx.x];
+    atomicAdd(dw + threadIdx.x, acc);
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra, const __nv_bfloat16* kdec,
@@ -459,9 +564,10 @@ cudaError_t launch_gdn_scan(const __nv_bfloat16* kq, const __nv_bfloat16* intra,
 cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, float* state, int B,
                                  int T, int C, int K, cudaStream_t stream) {
   if (K != 4 || C % 8 != 0 || B < 1 || T < 1) return cudaErrorInvalidValue;
+  constexpr int kStrip = 16;
   const int threads = 128;
-  const dim3 grid((C / 8 + threads - 1) / threads, T, B);
-  gdn_conv_silu_kernel<4><<<grid, threads, 0, stream>>>(x, w, y, state, T, C);
+  const dim3 grid((C / 8 + threads - 1) / threads, (T + kStrip - 1) / kStrip, B);
+  gdn_conv_silu_kernel<4, kStrip><<<grid, threads, 0, stream>>>(x, w, y, state, T, C);
   return cudaGetLastError();
 }
 
@@ -813,6 +919,28 @@ cudaError_t launch_gdn_scan_bwd(const __nv_bfloat16* kq, const __nv_bfloat16* in
   }
   BwdArgs args{n_chunks, e, ds_final, d_kq, d_intra, d_kdec, d_veff, d_e, ds0, status};
   gdn_scan_bwd_kernel<<<bh, kBwdThreads, kBwdSmem, stream>>>(tm, args);
+  return cudaGetLastError();
+}
+
+}  // namespace b200
+
+namespace b200 {
+
+cudaError_t launch_gdn_gated_norm(const __nv_bfloat16* o, const __nv_bfloat16* z, const float* w, __nv_bfloat16* y, int B,
+                                  int T, int Tpad, int Hv, float eps, cudaStream_t stream) {
+  if (B < 1 || T < 1 || Tpad < T || Hv < 1) return cudaErrorInvalidValue;
+  const int rows = B * T * Hv;
+  gdn_gated_norm_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(o, z, w, y, rows, T, Tpad, Hv, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gdn_gated_norm_bwd(const __nv_bfloat16* o, const __nv_bfloat16* z, const float* w,
+                                      const __nv_bfloat16* dy, __nv_bfloat16* d_o, __nv_bfloat16* dz, float* dw, int B,
+                                      int T, int Tpad, int Hv, float eps, cudaStream_t stream) {
+  if (B < 1 || T < 1 || Tpad < T || Hv < 1) return cudaErrorInvalidValue;
+  const int rows = B * T * Hv;
+  const int blocks = (rows + 7) / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8;
+  gdn_gated_norm_bwd_kernel<<<blocks, 256, 0, stream>>>(o, z, w, dy, d_o, dz, dw, rows, T, Tpad, Hv, eps);
   return cudaGetLastError();
 }
 

@@ -95,6 +95,17 @@ cudaError_t launch_gdn_chunk_prep_bwd(const __nv_bfloat16* mixed, const __nv_bfl
                                       float* d_a, float* d_A_log, float* d_dt_bias, int B, int T, int Hqk, int Hv,
                                       cudaStream_t stream);
 
+// Gated RMSNorm of the scan output, fused with the head-major -> token-major transpose:
+//   y[b, t, h, :] = w * o[b, h, t, :] * rsqrt(mean(o^2) + eps) * silu(z[b, t, h, :]),   head width 128
+// o [B*Hv, Tpad, 128] bf16 (the layout launch_gdn_scan writes, Tpad >= T), z and y [B, T, Hv * 128] bf16, w [128] fp32.
+cudaError_t launch_gdn_gated_norm(const __nv_bfloat16* o, const __nv_bfloat16* z, const float* w, __nv_bfloat16* y, int B,
+                                  int T, int Tpad, int Hv, float eps, cudaStream_t stream);
+// Backward: writes d_o (rows t < T of the [B*Hv, Tpad, 128] layout; zero the padding yourself) and dz, ACCUMULATES
+// dw [128] fp32.
+cudaError_t launch_gdn_gated_norm_bwd(const __nv_bfloat16* o, const __nv_bfloat16* z, const float* w,
+                                      const __nv_bfloat16* dy, __nv_bfloat16* d_o, __nv_bfloat16* dz, float* dw, int B,
+                                      int T, int Tpad, int Hv, float eps, cudaStream_t stream);
+
 // Causal depthwise conv (width 4) + SiLU over x [B, T, C] bf16 with w [C, 4]; `state` (optional) [B, C, 4] fp32
 // receives the last four raw inputs of every channel.
 cudaError_t launch_gdn_conv_silu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, float* state, int B,

@@ -220,15 +220,45 @@ class _GdnChunkPrepFn(torch.autograd.Function):
                 None, None)
 
 
-def gated_delta_prefill_cuda(mixed, b, a, A_log, dt_bias, n_qk: int, n_v: int, initial_state=None):
+class _GdnGatedNormFn(torch.autograd.Function):
+    """``w * rmsnorm(o) * silu(z)`` on the scan kernel's head-major output ``o`` (B*Hv, N, 64, 128), written
+    token-major as (B, T, Hv * 128): the transpose, the norm and the gate in one kernel, forward and backward."""
+
+    @staticmethod
+    def forward(ctx, o, z, weight, n_v, eps):
+        from ... import _ext
+        zc = z.contiguous()
+        w = weight.float().contiguous()
+        y = torch.empty_like(zc)
+        _ext.ops().gdn_gated_norm(o, zc, w, y, n_v, eps)
+        ctx.save_for_backward(o, zc, w)
+        ctx.meta = (n_v, eps, weight.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ... import _ext
+        o, z, w = ctx.saved_tensors
+        n_v, eps, w_dtype = ctx.meta
+        T, Tpad = z.shape[1], o.shape[1] * o.shape[2]
+        d_o = torch.empty_like(o) if Tpad == T else torch.zeros_like(o)
+        dz = torch.empty_like(z)
+        dw = torch.zeros(128, device=o.device, dtype=torch.float32)
+        _ext.ops().gdn_gated_norm_bwd(o, z, w, dy.to(torch.bfloat16).contiguous(), d_o, dz, dw, n_v, eps)
+        return d_o, dz, dw.to(w_dtype), None, None
+
+
+def gated_delta_prefill_cuda(mixed, b, a, A_log, dt_bias, n_qk: int, n_v: int, initial_state=None, head_major=False):
     """The whole gated-delta-rule prefill on this package's kernels (no library call): ``mixed`` (B, T, conv_dim)
     bf16 after conv + SiLU and the gate pre-activations -> (o (B, T, Hv, 128) bf16, final state (B, Hv, 128, 128)
-    fp32). Chunks of 64 whatever the configured chunk size (the result does not depend on it)."""
+    fp32). Chunks of 64 whatever the configured chunk size (the result does not depend on it). ``head_major``
+    returns o as the scan kernel wrote it, (B*Hv, N, 64, 128) with zero-padded tail, for the fused gated norm."""
     B, T, _ = mixed.shape
     kq, intra, kdec, veff, e = _GdnChunkPrepFn.apply(mixed, b, a, A_log, dt_bias, n_qk, n_v)
     s0 = initial_state.float().reshape(B * n_v, 128, 128) if initial_state is not None else None
     o, s_out = _GdnScanFn.apply(kq, intra, kdec, veff, e, s0)
-    o = o.reshape(B, n_v, -1, 128)[:, :, :T].transpose(1, 2)
+    if not head_major:
+        o = o.reshape(B, n_v, -1, 128)[:, :, :T].transpose(1, 2)
     return o, s_out.reshape(B, n_v, 128, 128)
 
 
@@ -294,10 +324,10 @@ def deltanet_prefill(x, params, n_qk: int, n_v: int, dk: int, dv: int, conv_kern
     mixed, z, b, a = _project(x, params, n_qk, n_v, dk, dv)
     mixed, conv_state = causal_conv1d_prefill(mixed, params["conv_weight"])
     if mixed.is_cuda and mixed.dtype == torch.bfloat16 and dk == 128 and dv == 128 and n_v % n_qk == 0:
-        o, S = gated_delta_prefill_cuda(mixed, b, a, params["A_log"], params["dt_bias"], n_qk, n_v, initial_state)
-        o = _gated_rms_norm(o.reshape(B * T * n_v, dv), z.reshape(B * T * n_v, dv), params["norm_weight"])
-        y = matmul_maybe_fp8(o.reshape(B, T, n_v * dv).to(x.dtype), params["out_proj"])
-        return y, S, conv_state
+        o, S = gated_delta_prefill_cuda(mixed, b, a, params["A_log"], params["dt_bias"], n_qk, n_v, initial_state,
+                                        head_major=True)
+        o = _GdnGatedNormFn.apply(o, z, params["norm_weight"], n_v, 1e-6)
+        return matmul_maybe_fp8(o, params["out_proj"]), S, conv_state
     q = mixed[..., :key_dim].reshape(B, T, n_qk, dk).float()
     k = mixed[..., key_dim:2 * key_dim].reshape(B, T, n_qk, dk).float()
     v = mixed[..., 2 * key_dim:].reshape(B, T, n_v, dv).float()

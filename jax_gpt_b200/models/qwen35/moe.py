@@ -23,7 +23,8 @@ from .fp8 import dequantize_weight, is_fp8_weight, matmul_maybe_fp8
 def moe_routing(x: torch.Tensor, gate_weight, k: int):
     """x (M, D) -> (weights (M,k) fp32 summing to 1, expert ids (M,k) int64)."""
     from ...ops.router import softmax_topk_router
-    logits = matmul_maybe_fp8(x, gate_weight).float() if is_fp8_weight(gate_weight) else x.float() @ gate_weight.float()
+    from ...ops.gemm import linear_f32out
+    logits = matmul_maybe_fp8(x, gate_weight).float() if is_fp8_weight(gate_weight) else linear_f32out(x, gate_weight)
     return softmax_topk_router(logits, k)
 
 

@@ -74,6 +74,48 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     return out
 
 
+def _weight_grad(x2, dy2, w):
+    """dW = x^T dy on the split-K GEMM. A weight that carries a ``grad_buf`` attribute (an fp32 tensor of its shape:
+    the trainer's flat gradient buffer) gets the product ACCUMULATED there by the GEMM's own epilogue and no
+    autograd gradient, which saves the bf16 round trip and the separate accumulation pass."""
+    split = max(1, min(16, x2.shape[0] // 2048))
+    buf = getattr(w, "grad_buf", None)
+    if buf is not None and buf.dtype == torch.float32 and buf.shape == w.shape and buf.is_contiguous():
+        gemm(x2, dy2, a_mn_major=True, b_mn_major=True, out=buf, out_mode=OUT_F32_ATOMIC, split_k=split)
+        return None
+    return gemm(x2, dy2, a_mn_major=True, b_mn_major=True, out_mode=OUT_F32_ATOMIC, split_k=split).to(w.dtype)
+
+
+class _LinearF32OutFn(torch.autograd.Function):
+    """y = x @ W with bf16 operands and an fp32 result (router logits: the products are exact, the sum is fp32,
+    which is what an fp32 GEMM on the upcast operands computes)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w, b_mn_major=True, out_mode=OUT_F32)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        return y.reshape(*x.shape[:-1], w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        dx = gemm(dy2, w).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw = _weight_grad(x2, dy2, w) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def linear_f32out(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w`` as fp32, ``w`` of shape (in, out). CUDA bf16 operands with row strides the TMA accepts (both widths
+    multiples of 8) run on the tcgen05 GEMM; anything else is computed in fp32 by PyTorch."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
+            and w.shape[0] % 8 == 0 and w.is_contiguous()):
+        return _LinearF32OutFn.apply(x, w)
+    return x.float() @ w.float()
+
+
 class _LinearFn(torch.autograd.Function):
     """y = x @ W (+ b) with W stored (in,out); bf16 compute, fp32 parameter gradients."""
 
@@ -93,10 +135,7 @@ class _LinearFn(torch.autograd.Function):
         dx = gemm(dy2, w).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
-            M = x2.shape[0]
-            split = max(1, min(16, M // 2048))
-            dw = gemm(x2, dy2, a_mn_major=True, b_mn_major=True, out_mode=OUT_F32_ATOMIC, split_k=split)
-            dw = dw.to(w.dtype)
+            dw = _weight_grad(x2, dy2, w)
         db = None
         if ctx.has_bias and ctx.needs_input_grad[2]:
             from .misc import bias_grad

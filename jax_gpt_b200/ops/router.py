@@ -64,5 +64,6 @@ def deepseek_router_from_logits(logits: torch.Tensor, bias: torch.Tensor, k: int
 def deepseek_router(x: torch.Tensor, gate_weight: torch.Tensor, bias: torch.Tensor, k: int, n_group: int,
                     topk_group: int, scale: float, norm_topk: bool = True):
     """x (M,D), gate_weight (D,E) -> (weights (M,k) fp32, ids (M,k)). Logits in fp32."""
-    logits = x.float() @ gate_weight.float()
+    from .gemm import linear_f32out
+    logits = linear_f32out(x, gate_weight)
     return deepseek_router_from_logits(logits, bias, k, n_group, topk_group, scale, norm_topk)

@@ -153,6 +153,8 @@ class TreeTrainEngine:
             if depth == 0:
                 leaf = cview.requires_grad_(True)
                 leaf.register_post_accumulate_grad_hook(self._make_hook(gview))
+                if leaf.is_cuda and leaf.dim() == 2:
+                    leaf.grad_buf = gview    # ops.gemm's weight-gradient GEMM accumulates straight into the flat buffer
                 self._leaf_params.append(leaf)
                 return leaf
             return [make_leaves(cview[i], gview[i], depth - 1) for i in range(cview.shape[0])]

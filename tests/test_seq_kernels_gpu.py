@@ -375,6 +375,64 @@ def test_gated_delta_prefill_cuda_gradients(cuda_device, B, T, n_qk, n_v, with_s
     assert not bad, bad
 
 
+@pytest.mark.parametrize("B,T,Hv", [(2, 64, 2), (1, 200, 4)])
+def test_gdn_gated_norm_kernel(cuda_device, B, T, Hv):
+    """Fused transpose + RMSNorm + SiLU gate on the scan kernel's head-major layout (zero-padded to chunks of
+    64), forward and backward, against the fp32 PyTorch expression on the token-major tensor."""
+    from jax_gpt_b200.models.qwen35 import deltanet as D
+    torch.manual_seed(12)
+    N = (T + 63) // 64
+    o_tm = torch.randn(B, T, Hv, 128)                                   # token-major values
+    o_hm = torch.zeros(B, Hv, N * 64, 128)
+    o_hm[:, :, :T] = o_tm.transpose(1, 2)
+    z = torch.randn(B, T, Hv * 128)
+    w = torch.rand(128) + 0.5
+    dy = torch.randn(B, T, Hv * 128)
+    bf = torch.bfloat16
+    o_k = o_hm.to(bf).reshape(B * Hv, N, 64, 128).to(cuda_device).requires_grad_()
+    z_k = z.to(bf).to(cuda_device).requires_grad_()
+    w_k = w.to(cuda_device).requires_grad_()
+    y = D._GdnGatedNormFn.apply(o_k, z_k, w_k, Hv, 1e-6)
+    y.backward(dy.to(bf).to(cuda_device))
+    o_r = o_tm.to(bf).float().requires_grad_()
+    z_r = z.to(bf).float().requires_grad_()
+    w_r = w.clone().requires_grad_()
+    y_r = D._gated_rms_norm(o_r.reshape(-1, 128), z_r.reshape(-1, 128), w_r).reshape(B, T, Hv * 128)
+    y_r.backward(dy.to(bf).float())
+    assert _rel(y.float().cpu(), y_r) < 1e-2
+    d_o = o_k.grad.float().cpu().reshape(B, Hv, N * 64, 128)
+    assert d_o[:, :, T:].abs().max().item() == 0 if N * 64 > T else True
+    assert _rel(d_o[:, :, :T].transpose(1, 2), o_r.grad) < 1e-2
+    assert _rel(z_k.grad.float().cpu(), z_r.grad) < 1e-2
+    assert _rel(w_k.grad.cpu(), w_r.grad) < 1e-2
+
+
+def test_linear_with_fp32_output_and_gradient_buffer(cuda_device):
+    """Router-style GEMM (bf16 operands, fp32 logits) and the weight gradient accumulated by the GEMM epilogue
+    straight into an fp32 buffer attached to the weight (``grad_buf``), twice, as in gradient accumulation."""
+    from jax_gpt_b200.ops.gemm import linear, linear_f32out
+    torch.manual_seed(13)
+    M, K, N = 4096, 512, 64
+    x = torch.randn(M, K, device=cuda_device).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(K, N, device=cuda_device) * 0.05).to(torch.bfloat16).requires_grad_()
+    y = linear_f32out(x, w)
+    assert y.dtype == torch.float32
+    ref = x.detach().float() @ w.detach().float()
+    assert _rel(y, ref) < 1e-5
+    dy = torch.randn(M, N, device=cuda_device)
+    y.backward(dy)
+    assert _rel(x.grad, dy @ w.detach().float().t()) < 1e-2
+    assert _rel(w.grad, x.detach().float().t() @ dy) < 1e-2
+    # with a gradient buffer: no autograd gradient, two backward passes add up in fp32
+    w2 = w.detach().clone().requires_grad_()
+    w2.grad_buf = torch.zeros(K, N, device=cuda_device)
+    for fn in (linear, linear_f32out):
+        out = fn(x.detach(), w2)
+        out.backward(dy.to(out.dtype))
+    assert w2.grad is None
+    assert _rel(w2.grad_buf, 2 * (x.detach().float().t() @ dy)) < 1e-2
+
+
 def test_fp8_linear_training_path_on_gpu(cuda_device):
     """Forward / dgrad / wgrad of a linear layer on the hardware block-scaled FP8 GEMM: against the same recipe
     evaluated by the CPU reference kernels (same quantisation, so only summation order and bf16 rounding differ)
