@@ -92,6 +92,10 @@ class GPT2TrainEngine:
                  overlap_grad_reduce: bool = False):
         assert cfg.n_head == cfg.n_kv_head and cfg.d_head in (64, 128)
         assert cfg.d_model % 8 == 0 and seq <= cfg.d_context
+        if cfg.dropout > 0.0:
+            raise NotImplementedError("the fused engine has no dropout masks in its kernels; train with "
+                                      "GPT(..., deterministic=False) under autograd (trainer.train_step without "
+                                      "an engine) or set dropout=0.0 as the reference's training configs do")
         self.cfg, self.B, self.T = cfg, batch, seq
         self.device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
         _ext.load()

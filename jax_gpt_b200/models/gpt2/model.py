@@ -22,6 +22,7 @@ from dataclasses import dataclass
 from typing import Dict, Optional
 
 import torch
+import torch.nn.functional as F
 
 from ...ops import attention as attn_ops
 from ...ops import gemm as gemm_ops
@@ -115,7 +116,7 @@ class GPT:
                 self.params[k].copy_(v.to(self.params[k].dtype))
 
     # -- forward ------------------------------------------------------------------------------
-    def _block(self, l, x, cache_k, cache_v, pos, acts, tp_group=None):
+    def _block(self, l, x, cache_k, cache_v, pos, acts, tp_group=None, drop: float = 0.0):
         """``tp_group`` with sharded projections (trainer/sharding.py): this rank's heads and its slice of the MLP,
         row-parallel outputs summed over the group, their biases added once after the sum."""
         from ...parallel.tp_ops import copy_to_tp, reduce_from_tp
@@ -140,6 +141,11 @@ class GPT:
             else:
                 y = attn_ops.attention_cached(q, cache_k, cache_v, pos + T, pos)
             new_k, new_v = cache_k, cache_v
+        elif drop > 0.0:
+            # dropout on the attention probabilities (jax_gpt/models/gpt2/model.py:175) cannot pass through the
+            # flash kernels, which never materialise them: the stock fused attention applies it
+            y = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                               dropout_p=drop, is_causal=True).transpose(1, 2)
         else:
             y = attn_ops.attention(q, k, v, causal=True)
         if tp is None:
@@ -147,7 +153,7 @@ class GPT:
         else:
             a = reduce_from_tp(gemm_ops.linear(y.reshape(B, T, dl), p["h.attn.c_proj.kernel"][l]), tp) \
                 + p["h.attn.c_proj.bias"][l]
-        x = x + a
+        x = x + F.dropout(a, drop, training=drop > 0.0)
         h2 = norm_ops.layer_norm(x, p["h.ln_2.layer_norm.scale"][l], p["h.ln_2.layer_norm.bias"][l], 1e-5)
         mlp_tp = tp_group if p["h.mlp.c_fc.kernel"].shape[-1] < cfg.d_ff else None
         f = gemm_ops.linear(copy_to_tp(h2, mlp_tp), p["h.mlp.c_fc.kernel"][l], p["h.mlp.c_fc.bias"][l])
@@ -160,7 +166,7 @@ class GPT:
             acts[f"block_{l}_ln1_output"] = h1
             acts[f"block_{l}_attn_output_pre_residual"] = a
             acts[f"block_{l}_mlp_output_pre_residual"] = m
-        return x + m, new_k, new_v
+        return x + F.dropout(m, drop, training=drop > 0.0), new_k, new_v
 
     def __call__(self, x, *, deterministic: bool = True, cache: Optional[KVCache] = None,
                  return_activations: bool = False, mesh=None):
@@ -177,12 +183,16 @@ class GPT:
             raise ValueError("the parameters are a tensor-parallel shard: pass mesh=make_mesh(config) "
                              "(trainer/sharding.py) and run one process per shard")
         h = vocab_parallel_embedding(idx, p["wte.embedding"], tp_group, cfg.vocab_size) + p["wpe.embedding"][pos:pos + T]
+        # ``deterministic=False`` with ``config.dropout > 0``: embedding, attention-probability and residual dropout
+        # as in the reference modules (jax_gpt/models/gpt2/model.py:93-102, 132-180, 234)
+        drop = float(cfg.dropout) if (not deterministic and cache is None) else 0.0
+        h = F.dropout(h, drop, training=drop > 0.0)
         if acts is not None:
             acts["initial_embedding"] = h
         for l in range(cfg.n_layers):
             ck = cache.key[l] if cache is not None else None
             cv = cache.value[l] if cache is not None else None
-            h, _, _ = self._block(l, h, ck, cv, pos, acts, tp_group)
+            h, _, _ = self._block(l, h, ck, cv, pos, acts, tp_group, drop)
         h = norm_ops.layer_norm(h, p["ln_f.layer_norm.scale"], p["ln_f.layer_norm.bias"], 1e-5)
         if vocab_sharded:
             # tied, vocabulary-parallel head: this rank's logit columns, gathered to whole logits

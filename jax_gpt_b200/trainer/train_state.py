@@ -25,7 +25,8 @@ def create_train_state(model, tx, *, train_config=None, device=None, dist_optimi
     """``tx.init`` over the model's parameters. With ``train_config`` and a CUDA ``device`` a
     GPT-2 model is moved onto the fused engine (bf16 compute, fp32 master weights)."""
     from ..models.gpt2.model import GPT
-    if train_config is not None and device is not None and torch.device(device).type == "cuda" and isinstance(model, GPT):
+    if (train_config is not None and device is not None and torch.device(device).type == "cuda" and isinstance(model, GPT)
+            and model.config.dropout == 0.0):   # dropout > 0 trains under autograd: the engine's kernels carry no masks
         from ..models.gpt2.engine import GPT2TrainEngine
         c = train_config
         eng = GPT2TrainEngine(model.config, c.micro_batch_size, c.seq_len, device=device, lr=c.learning_rate,

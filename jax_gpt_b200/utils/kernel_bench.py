@@ -4,6 +4,7 @@
     python -m jax_gpt_b200.utils.kernel_bench --op attn_fwd --B 16 --T 1024 --H 12 --D 64
     python -m jax_gpt_b200.utils.kernel_bench --op attn_bwd | norm_fwd | norm_bwd | adamw | ce
     python -m jax_gpt_b200.utils.kernel_bench --op mla_decode --B 32 --T 2304 --H 16
+    python -m jax_gpt_b200.utils.kernel_bench --op gdn_prep_fwd | gdn_prep_bwd | gdn_prefill --B 1 --T 4096
 
 Each run does ``--warmup`` untimed launches, then times ``--iters`` launches with CUDA events on
 the launching stream (synchronised on both sides) and prints one JSON line with the achieved
@@ -159,6 +160,46 @@ def main(argv=None):
         fn = lambda: _ext.ops().gdn_scan(kq, intra, kdec, veff, e, None, o, s_out)
         bytes_ = 2.0 * BH * N * (128 * 128 + 64 * 64 + 64 * 128 * 3)
         flops = 2.0 * BH * N * (128 * 128 * 128 + 64 * 64 * 128 + 128 * 64 * 128)
+    elif args.op in ("gdn_prep_fwd", "gdn_prep_bwd", "gdn_prefill"):
+        # the Gated-DeltaNet prefill between the input and the output projection: --B sequences of --T tokens,
+        # --Hkv q/k heads and --H value heads of width 128 (defaults 16 / 32). gdn_prep_*: the chunk-preparation
+        # kernel alone; gdn_prefill: preparation + scan + gated norm, forward and backward through autograd
+        from ..models.qwen35 import deltanet as DN
+        B, T, Hv = args.B, args.T, args.H if args.H != 12 else 32
+        Hqk = args.Hkv or Hv // 2
+        N = (T + 63) // 64
+        bf = torch.bfloat16
+        mixed = torch.nn.functional.silu(torch.randn(B, T, (2 * Hqk + Hv) * 128, device=dev)).to(bf)
+        bg, ag = torch.randn(B, T, Hv, device=dev).to(bf), torch.randn(B, T, Hv, device=dev).to(bf)
+        A_log = torch.log(torch.rand(Hv, device=dev) * 15.9 + 0.1)
+        dtb = torch.ones(Hv, device=dev)
+        BH = B * Hv
+        kq = torch.empty(BH, N, 128, 128, device=dev, dtype=bf)
+        intra = torch.empty(BH, N, 64, 64, device=dev, dtype=bf)
+        kdec, veff = torch.empty(BH, N, 64, 128, device=dev, dtype=bf), torch.empty(BH, N, 64, 128, device=dev, dtype=bf)
+        e = torch.empty(BH, N, device=dev)
+        if args.op == "gdn_prep_fwd":
+            fn = lambda: _ext.ops().gdn_chunk_prep(mixed, bg, ag, A_log, dtb, kq, intra, kdec, veff, e, Hqk, Hv)
+            bytes_ = 2.0 * (mixed.numel() + kq.numel() + intra.numel() + kdec.numel() + veff.numel())
+        elif args.op == "gdn_prep_bwd":
+            _ext.ops().gdn_chunk_prep(mixed, bg, ag, A_log, dtb, kq, intra, kdec, veff, e, Hqk, Hv)
+            dm = torch.empty_like(mixed)
+            db, da = torch.empty(B, T, Hv, device=dev), torch.empty(B, T, Hv, device=dev)
+            dal, ddt = torch.zeros(Hv, device=dev), torch.zeros(Hv, device=dev)
+            fn = lambda: _ext.ops().gdn_chunk_prep_bwd(mixed, bg, ag, A_log, dtb, kq, intra, kdec, veff, e, dm, db, da,
+                                                       dal, ddt, Hqk, Hv)
+            bytes_ = 2.0 * (2 * mixed.numel() + kq.numel() + intra.numel() + kdec.numel() + veff.numel())
+        else:
+            leaves = [t.requires_grad_() for t in (mixed, bg, ag, A_log, dtb)]
+            z = torch.randn(B, T, Hv * 128, device=dev).to(bf).requires_grad_()
+            w = torch.ones(128, device=dev, requires_grad=True)
+            dy = torch.randn(B, T, Hv * 128, device=dev).to(bf)
+
+            def fn():
+                o, _ = DN.gated_delta_prefill_cuda(*leaves, Hqk, Hv, head_major=True)
+                DN._GdnGatedNormFn.apply(o, z, w, Hv, 1e-6).backward(dy)
+            flops = 0.0
+            bytes_ = 0.0
     elif args.op == "mla_decode":
         # --B sequences of --T cached tokens each, --H heads (16 = DeepSeek-V3 with 8-way head sharding)
         from ..cache.paged import PagedCache

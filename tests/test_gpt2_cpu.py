@@ -51,3 +51,40 @@ def test_loglikelihood_tokens():
         lp = torch.log_softmax(m(full[:, :-1])[0].float(), -1)[0]
         want = sum(lp[len(ctx) - 1 + i, t].item() for i, t in enumerate(cont))
         assert abs(ll - want) < 1e-4 and isinstance(greedy, bool)
+
+
+def test_dropout_is_applied_only_when_training():
+    """``config.dropout`` acts in ``deterministic=False`` passes (embedding, attention probabilities, both residual
+    branches) and never in evaluation or cached decoding; p = 0 leaves the training pass equal to evaluation."""
+    cfg = GPTConfig(d_model=64, d_head=16, d_ff=256, d_context=32, n_head=4, n_kv_head=4, n_layers=2, vocab_size=100,
+                    dropout=0.5)
+    m = GPT(cfg, seed=0)
+    x = torch.randint(0, 100, (2, 8))
+    ev1, _ = m(x, deterministic=True)
+    ev2, _ = m(x)
+    assert torch.equal(ev1, ev2)
+    torch.manual_seed(0)
+    tr1, _ = m(x, deterministic=False)
+    tr2, _ = m(x, deterministic=False)
+    assert not torch.allclose(tr1, ev1, atol=1e-3) and not torch.allclose(tr1, tr2, atol=1e-3)
+    m0 = GPT(CFG, seed=0)                      # dropout 0.0
+    a, _ = m0(x, deterministic=False)
+    b, _ = m0(x, deterministic=True)
+    assert torch.allclose(a, b, atol=1e-6)
+    # gradients flow through the dropout path
+    for p in m.params.values():
+        p.requires_grad_(True)
+    m(x, deterministic=False)[0].sum().backward()
+    assert m.params["h.attn.c_attn.kernel"].grad.abs().sum() > 0
+
+
+def test_golden_log_script_matches_the_pytorch_model():
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "scripts", "debug_golden_log.py")
+    spec = importlib.util.spec_from_file_location("debug_golden_log", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    rc = mod.main(["--random", "--n-layers", "2", "--n-head", "2", "--d-model", "64", "--ctx", "64", "--vocab", "300",
+                   "--new-tokens", "4", "--tolerance", "1e-3"])
+    assert rc == 0

@@ -104,6 +104,18 @@ def test_fused_ep_moe_fp8_two_gpus(tmp_path):
             assert v < 1e-1, res
 
 
+@pytest.mark.parametrize("nproc", [4, 8])
+def test_fused_ep_moe_forward_backward_fp8_more_gpus(tmp_path, nproc):
+    """The expert-parallel kernels with 4 and 8 ranks (16 experts: 4 and 2 per rank): forward against the dense
+    evaluation, backward against autograd of it, the FP8 forward against its quantised restatement."""
+    res = _run("ep", tmp_path, nproc=nproc, port=29631)
+    assert all(v < 2e-2 for k, v in res.items() if k.endswith("_vs_dense")), res
+    res = _run("ep_bwd", tmp_path, nproc=nproc, port=29632)
+    assert all(v < 3e-2 for v in res.values()), res
+    res = _run("ep_fp8", tmp_path, nproc=nproc, port=29633)
+    assert all(v < 2e-2 for k, v in res.items() if k.endswith("_vs_quantised_ref")), res
+
+
 def test_qwen35_expert_parallel_training_matches_single_process(tmp_path):
     res = _run("moe_train", tmp_path, port=29616)
     assert res["ep_loss"][0] > 5.5                      # ln(512) = 6.24 at random init
