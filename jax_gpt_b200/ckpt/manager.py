@@ -204,7 +204,7 @@ class CheckpointManager:
         return steps[-1] if steps else None
 
     def should_save(self, step: int) -> bool:
-        return step % self._config.save_interval == 0
+        return self._config.save_interval > 0 and step % self._config.save_interval == 0   # 0 = never save periodically
 
     def close(self):
         if self._writer is not None:

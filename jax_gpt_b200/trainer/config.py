@@ -28,6 +28,7 @@ class TrainConfig:
     dp: int = 1
     fsdp: int = 1
     tp: int = 1
+    pp: int = 1                      # pipeline stages (scripts/train.py --pp=N, GPT-2)
     sp: int = 1
     pp: int = 1
     ep: int = 1

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -69,10 +69,13 @@ class AdamW:
 
     @torch.no_grad()
     def update(self, grads: Dict[str, torch.Tensor], state: AdamWState, params: Dict[str, torch.Tensor], mesh=None,
-               model_config=None):
+               model_config=None, global_sq: Optional[torch.Tensor] = None):
         """Applies one step IN PLACE to ``params`` and the moments; returns (grad_norm, lr). With a tensor-parallel
         ``mesh`` the leaves are shards: the squared norms of the sharded leaves are summed over the group, those of
         the replicated leaves counted once, so every rank clips by the same global norm as a single process."""
+        if global_sq is not None:
+            # the caller already summed the squared gradient norm over its process group (pipeline stages)
+            return self._apply(grads, state, params, global_sq.float().reshape(()).cpu())
         sq = None
         sq_sharded = None
         tp = mesh is not None and getattr(mesh, "group", None) is not None and mesh.size("tp") > 1
@@ -86,6 +89,9 @@ class AdamW:
             import torch.distributed as dist
             dist.all_reduce(sq_sharded, group=mesh.group)
             sq = sq_sharded if sq is None else sq + sq_sharded
+        return self._apply(grads, state, params, sq)
+
+    def _apply(self, grads, state, params, sq):
         gnorm = float(sq.sqrt())
         lr = self.schedule(state.count)
         t = state.count + 1

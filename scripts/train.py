@@ -11,7 +11,8 @@ are sharded over the ranks (fused dispatch / grouped GEMM / combine kernels, for
 dense weights go through the fused sharded optimizer.
 
 ``--tp=N`` (GPT-2 presets, N = number of processes) trains tensor parallel on the shards of
-``trainer/sharding.py`` through the autograd model; with several ranks a watchdog over the rendezvous store turns a
+``trainer/sharding.py`` through the autograd model; ``--pp=N`` trains in N pipeline stages (1F1B over
+point-to-point sends, the ``--grad_accum_steps`` micro-batches fill the pipeline); with several ranks a watchdog over the rendezvous store turns a
 rank that stops beating into a ``PeerFailure`` on the others before their next step. The MoE families checkpoint
 periodically too (``--save_interval``, ``--resume_from=latest``): dense state gathered to rank 0, every rank writes
 its experts, and a checkpoint restores at another expert-parallel degree (ckpt/tree_ckpt.py).
@@ -191,6 +192,77 @@ def train_gpt2_tp(args, tc, cfg, rank, world, device):
     torch.distributed.destroy_process_group()
 
 
+def train_gpt2_pp(args, tc, cfg, rank, world, device):
+    """GPT-2 in ``--pp=N`` pipeline stages, one per process (parallel/pipeline.py): stage r runs its contiguous
+    range of blocks, activations and their gradients travel over point-to-point sends in the 1F1B order, the
+    ``grad_accum_steps`` micro-batches of a step are the pipeline's micro-batches. The first stage reads the
+    tokens and the last the targets of the same data windows; the tied embedding's gradient is summed between
+    them; the clipping norm is summed over the stages (the tied embedding counted once)."""
+    import os
+
+    import torch.distributed as dist
+
+    from jax_gpt_b200.data.pipeline import DataPipeline
+    from jax_gpt_b200.data.tokenize import write_synthetic
+    from jax_gpt_b200.models.gpt2 import GPT
+    from jax_gpt_b200.parallel.pipeline import gpt2_stage, sync_tied_embedding_grad
+    from jax_gpt_b200.trainer import MetricsLogger, create_optimizer
+    if tc.pp != world or world < 2:
+        raise SystemExit(f"--pp={tc.pp} needs exactly {tc.pp} processes (found {world})")
+    if cfg.n_layers < world:
+        raise SystemExit(f"{cfg.n_layers} layers cannot fill {world} pipeline stages")
+    if args.synthetic and rank == 0 and not os.path.exists(os.path.join(tc.local_data_path, "train.bin")):
+        write_synthetic(tc.local_data_path, args.synthetic_tokens, cfg.vocab_size, tc.seed)
+    dist.barrier()
+    model = GPT(cfg, seed=tc.seed, device=device, dtype=torch.float32)
+    model.requires_grad_(True)
+    tx = create_optimizer(model, tc)
+    opt_state = tx.init(model.params)
+    stage = gpt2_stage(model, rank, world, tc.micro_batch_size, tc.seq_len, device=device)
+    data = DataPipeline(tc, "train", _shard_index=0, _shard_count=1)       # every stage walks the same windows
+    logger = MetricsLogger(tc, cfg, jsonl_path=args.jsonl if rank == 0 else "")
+    wd = start_watchdog(rank, world)
+    n_micro = tc.grad_accum_steps
+    step, since, last_loss = 0, 0, float("nan")
+    while step < tc.max_steps:
+        if wd is not None:
+            wd.check()
+        micro = [data.get_batch() for _ in range(n_micro)]
+        if rank == 0:
+            inputs = [x.to(device) for x, _ in micro]
+        elif rank == world - 1:
+            inputs = [y.to(device) for _, y in micro]
+        else:
+            inputs = [None] * n_micro
+        loss = stage.run(inputs)
+        sync_tied_embedding_grad(model)
+        grads = {k: (p.grad if p.grad is not None else torch.zeros_like(p)) for k, p in model.params.items()}
+        sq = torch.zeros((), device=device)
+        for k, g in grads.items():
+            if k == "wte.embedding" and rank != 0:
+                continue                        # summed over the stages above: count it on the first stage only
+            sq = sq + (g.float() ** 2).sum()
+        dist.all_reduce(sq)
+        with torch.no_grad():
+            gnorm, lr = tx.update(grads, opt_state, model.params, global_sq=sq)
+        for p in model.params.values():
+            p.grad = None
+        lt = torch.tensor([float(loss) if loss is not None else 0.0], device=device)
+        dist.broadcast(lt, src=world - 1)
+        last_loss = float(lt)
+        step += 1
+        since += tc.micro_batch_size * tc.seq_len * n_micro
+        if step % tc.log_interval == 0:
+            logger.log(step, {"loss": last_loss, "grad_norm": gnorm, "lr": lr}, since)
+            since = 0
+    if rank == 0:
+        print(f"done: step {step} loss {last_loss:.4f} (pipeline parallel x{tc.pp})")
+    if wd is not None:
+        wd.stop()
+    data.close()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     from jax_gpt_b200.data.pipeline import DataPipeline
     from jax_gpt_b200.data.tokenize import write_synthetic
@@ -217,6 +289,8 @@ def main(argv=None):
     cfg = gpt_config(args.preset)
     if tc.tp > 1:
         return train_gpt2_tp(args, tc, cfg, rank, world, device)
+    if tc.pp > 1:
+        return train_gpt2_pp(args, tc, cfg, rank, world, device)
     tc = tc.replace(dp=world)
     if args.synthetic and rank == 0:
         import os
