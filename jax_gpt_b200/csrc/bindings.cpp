@@ -101,20 +101,22 @@ void gemm(const Tensor& a, bool a_mn_major, const Tensor& b, bool b_mn_major, Te
                                          b_mn_major ? 1 : 0, g, cur_stream()));
 }
 
-// All-gather -> GEMM over peer-mapped activation shards (pointers as int64), and GEMM ->
-// reduce-scatter into peer-mapped fp32 buffers. Shapes: each shard [rows_per_src, K] bf16.
-void gemm_gathered_a(std::vector<int64_t> a_ptrs, int64_t rows_per_src, int64_t first_src, int64_t K, int64_t lda,
-                     const Tensor& b, bool b_mn_major, Tensor out, const c10::optional<Tensor>& bias) {
+// All-gather -> GEMM, the gather pushed by copier CTAs of the same kernel. gather_ptrs[s] / ready_ptrs[s]: rank s's
+// gather buffer [n * rows_per_src, K] bf16 and ready array int32[n * rows_per_src / 128] as mapped here (entry `rank`
+// = this rank's own, whose block `rank` already holds the local rows).
+void gemm_gathered_a_staged(std::vector<int64_t> gather_ptrs, std::vector<int64_t> ready_ptrs, int64_t rows_per_src,
+                            int64_t K, int64_t rank, const Tensor& b, bool b_mn_major, Tensor out,
+                            const c10::optional<Tensor>& bias, int64_t epoch, double wait_seconds) {
   c10::cuda::CUDAGuard guard(b.device());
   check_bf16_2d(b, "b");
-  const int n_src = static_cast<int>(a_ptrs.size());
-  TORCH_CHECK(n_src >= 1 && n_src <= b200::kMaxPeers, "gemm_gathered_a: 1..8 sources");
-  const int N = static_cast<int>(b_mn_major ? b.size(1) : b.size(0));
+  const int n = static_cast<int>(gather_ptrs.size());
+  TORCH_CHECK(n >= 1 && n <= b200::kMaxPeers && ready_ptrs.size() == gather_ptrs.size() && rank >= 0 && rank < n,
+              "gemm_gathered_a_staged: 1..8 ranks");
   GemmArgs g{};
-  g.M = static_cast<int>(rows_per_src * n_src);
-  g.N = N;
+  g.M = static_cast<int>(rows_per_src * n);
   g.K = static_cast<int>(K);
-  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == g.M && out.size(1) == N, "gemm_gathered_a: bad out");
+  g.N = static_cast<int>(b_mn_major ? b.size(1) : b.size(0));
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == g.M && out.size(1) == g.N, "gemm_gathered_a_staged: bad out");
   g.out = out.data_ptr();
   g.ldo = out.stride(0);
   g.out_mode = b200::kOutBf16;
@@ -122,25 +124,33 @@ void gemm_gathered_a(std::vector<int64_t> a_ptrs, int64_t rows_per_src, int64_t 
   g.alpha = 1.f;
   g.split_k = 1;
   g.status = status_ptr(b);
-  const __nv_bfloat16* srcs[b200::kMaxPeers];
-  for (int i = 0; i < n_src; ++i) srcs[i] = reinterpret_cast<const __nv_bfloat16*>(a_ptrs[i]);
-  B200_CHECK_CUDA(b200::launch_gemm_bf16_gathered_a(srcs, n_src, static_cast<int>(rows_per_src),
-                                                    static_cast<int>(first_src), lda, bf16_ptr(b), b.stride(0),
-                                                    b_mn_major ? 1 : 0, g, cur_stream()));
+  __nv_bfloat16* peers[b200::kMaxPeers];
+  int* ready[b200::kMaxPeers];
+  for (int i = 0; i < n; ++i) {
+    peers[i] = reinterpret_cast<__nv_bfloat16*>(gather_ptrs[i]);
+    ready[i] = reinterpret_cast<int*>(ready_ptrs[i]);
+  }
+  B200_CHECK_CUDA(b200::launch_gemm_bf16_gathered_a_staged(peers, ready, n, static_cast<int>(rows_per_src),
+                                                           static_cast<int>(rank), bf16_ptr(b), b.stride(0),
+                                                           b_mn_major ? 1 : 0, g, static_cast<int>(epoch), wait_seconds,
+                                                           cur_stream()));
 }
 
-// x [M,K] @ W [K,N] where W is row-sharded over the ranks: shard_ptrs[s] -> [K / n, N] bf16.
-void gemm_sharded_b(const Tensor& a, std::vector<int64_t> shard_ptrs, int64_t first_src, int64_t N, Tensor out,
-                    const c10::optional<Tensor>& bias) {
+// x [M, K] @ W [K, N], W column-sharded over the ranks and pushed into every rank's gather buffer by copier CTAs of
+// the same kernel. w_ptrs[s] / ready_ptrs[s]: rank s's buffer (n matrices [K, N / n] bf16) and ready array
+// int32[n * K / 64] as mapped here.
+void gemm_sharded_b_staged(const Tensor& a, std::vector<int64_t> w_ptrs, std::vector<int64_t> ready_ptrs, int64_t N,
+                           int64_t rank, Tensor out, const c10::optional<Tensor>& bias, int64_t epoch, double wait_seconds) {
   c10::cuda::CUDAGuard guard(a.device());
   check_bf16_2d(a, "a");
-  const int n = static_cast<int>(shard_ptrs.size());
-  TORCH_CHECK(n >= 1 && n <= b200::kMaxPeers, "gemm_sharded_b: 1..8 shards");
+  const int n = static_cast<int>(w_ptrs.size());
+  TORCH_CHECK(n >= 1 && n <= b200::kMaxPeers && ready_ptrs.size() == w_ptrs.size() && rank >= 0 && rank < n,
+              "gemm_sharded_b_staged: 1..8 ranks");
   GemmArgs g{};
   g.M = static_cast<int>(a.size(0));
   g.K = static_cast<int>(a.size(1));
   g.N = static_cast<int>(N);
-  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == g.M && out.size(1) == N, "gemm_sharded_b: bad out");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == g.M && out.size(1) == g.N, "gemm_sharded_b_staged: bad out");
   g.out = out.data_ptr();
   g.ldo = out.stride(0);
   g.out_mode = b200::kOutBf16;
@@ -148,35 +158,53 @@ void gemm_sharded_b(const Tensor& a, std::vector<int64_t> shard_ptrs, int64_t fi
   g.alpha = 1.f;
   g.split_k = 1;
   g.status = status_ptr(a);
-  const __nv_bfloat16* srcs[b200::kMaxPeers];
-  for (int i = 0; i < n; ++i) srcs[i] = reinterpret_cast<const __nv_bfloat16*>(shard_ptrs[i]);
-  B200_CHECK_CUDA(b200::launch_gemm_bf16_sharded_b(bf16_ptr(a), a.stride(0), srcs, n, static_cast<int>(first_src), N, g,
-                                                   cur_stream()));
+  __nv_bfloat16* peers[b200::kMaxPeers];
+  int* ready[b200::kMaxPeers];
+  for (int i = 0; i < n; ++i) {
+    peers[i] = reinterpret_cast<__nv_bfloat16*>(w_ptrs[i]);
+    ready[i] = reinterpret_cast<int*>(ready_ptrs[i]);
+  }
+  B200_CHECK_CUDA(b200::launch_gemm_bf16_sharded_b_staged(bf16_ptr(a), a.stride(0), peers, ready, n, static_cast<int>(rank),
+                                                          g, static_cast<int>(epoch), wait_seconds, cur_stream()));
 }
 
-void gemm_reduce_scatter(const Tensor& a, const Tensor& b, bool b_mn_major, std::vector<int64_t> out_ptrs,
-                         int64_t rows_per_peer, int64_t ldo) {
+// GEMM -> reduce-scatter, partial tiles pushed to the row owners and summed there (one kernel).
+// recv_ptrs[r] / cnt_ptrs[r]: rank r's receive buffer [n, rows_per_peer, N] bf16 and arrival counters as mapped here.
+void gemm_reduce_scatter_push(const Tensor& a, const Tensor& b, bool b_mn_major, std::vector<int64_t> recv_ptrs,
+                              std::vector<int64_t> cnt_ptrs, int64_t rank, int64_t rows_per_peer, Tensor out,
+                              int64_t cnt_expected, double wait_seconds) {
   c10::cuda::CUDAGuard guard(a.device());
   check_bf16_2d(a, "a");
   check_bf16_2d(b, "b");
-  const int n = static_cast<int>(out_ptrs.size());
-  TORCH_CHECK(n >= 1 && n <= b200::kMaxPeers, "gemm_reduce_scatter: 1..8 peers");
+  const int n = static_cast<int>(recv_ptrs.size());
+  TORCH_CHECK(n >= 1 && n <= b200::kMaxPeers && cnt_ptrs.size() == recv_ptrs.size() && rank >= 0 && rank < n,
+              "gemm_reduce_scatter_push: 1..8 peers");
   GemmArgs g{};
   g.M = static_cast<int>(a.size(0));
   g.K = static_cast<int>(a.size(1));
   g.N = static_cast<int>(b_mn_major ? b.size(1) : b.size(0));
-  TORCH_CHECK(rows_per_peer * n == g.M, "gemm_reduce_scatter: rows_per_peer * peers must equal M");
+  TORCH_CHECK(rows_per_peer * n == g.M && rows_per_peer % 128 == 0 && g.N % 64 == 0,
+              "gemm_reduce_scatter_push: M = peers * rows_per_peer, rows_per_peer % 128 == 0, N % 64 == 0");
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.size(0) == rows_per_peer && out.size(1) == g.N,
+              "gemm_reduce_scatter_push: out [rows_per_peer, N] bf16");
   g.out = nullptr;
-  g.ldo = ldo;
-  g.out_mode = b200::kOutBf16PeerRed;
+  g.ldo = g.N;
+  g.out_mode = b200::kOutBf16PeerPush;
   g.n_peers = n;
+  g.self_rank = static_cast<int>(rank);
   g.rows_per_peer = static_cast<int>(rows_per_peer);
-  for (int i = 0; i < n; ++i) g.peer_out[i] = reinterpret_cast<float*>(out_ptrs[i]);
+  for (int i = 0; i < n; ++i) {
+    g.peer_out[i] = reinterpret_cast<float*>(recv_ptrs[i]);
+    g.peer_cnt[i] = reinterpret_cast<int*>(cnt_ptrs[i]);
+  }
+  g.cnt_expected = static_cast<int>(cnt_expected);
+  g.rs_out = bf16_mut(out);
+  g.rs_wait_ns = static_cast<unsigned long long>((wait_seconds > 0 ? wait_seconds : 20.0) * 1e9);
   g.alpha = 1.f;
   g.split_k = 1;
   g.status = status_ptr(a);
-  B200_CHECK_CUDA(b200::launch_gemm_bf16(bf16_ptr(a), a.stride(0), 0, bf16_ptr(b), b.stride(0), b_mn_major ? 1 : 0, g,
-                                         cur_stream()));
+  B200_CHECK_CUDA(b200::launch_gemm_bf16_reduce_scatter_push(bf16_ptr(a), a.stride(0), bf16_ptr(b), b.stride(0),
+                                                             b_mn_major ? 1 : 0, g, cur_stream()));
 }
 
 void norm_fwd(int64_t mode, const Tensor& x, const Tensor& gamma, const c10::optional<Tensor>& beta, Tensor y,
@@ -447,13 +475,17 @@ TORCH_LIBRARY(b200, m) {
       "Tensor? aux, int epilogue, int out_mode, float alpha, int split_k) -> ()",
       &gemm);
   m.def(
-      "gemm_gathered_a(int[] a_ptrs, int rows_per_src, int first_src, int K, int lda, Tensor b, bool b_mn_major, "
-      "Tensor(a!) out, Tensor? bias) -> ()",
-      &gemm_gathered_a);
-  m.def("gemm_sharded_b(Tensor a, int[] shard_ptrs, int first_src, int N, Tensor(a!) out, Tensor? bias) -> ()",
-        &gemm_sharded_b);
-  m.def("gemm_reduce_scatter(Tensor a, Tensor b, bool b_mn_major, int[] out_ptrs, int rows_per_peer, int ldo) -> ()",
-        &gemm_reduce_scatter);
+      "gemm_gathered_a_staged(int[] gather_ptrs, int[] ready_ptrs, int rows_per_src, int K, int rank, Tensor b, "
+      "bool b_mn_major, Tensor(a!) out, Tensor? bias, int epoch, float wait_seconds) -> ()",
+      &gemm_gathered_a_staged);
+  m.def(
+      "gemm_sharded_b_staged(Tensor a, int[] w_ptrs, int[] ready_ptrs, int N, int rank, Tensor(a!) out, Tensor? bias, "
+      "int epoch, float wait_seconds) -> ()",
+      &gemm_sharded_b_staged);
+  m.def(
+      "gemm_reduce_scatter_push(Tensor a, Tensor b, bool b_mn_major, int[] recv_ptrs, int[] cnt_ptrs, int rank, "
+      "int rows_per_peer, Tensor(a!) out, int cnt_expected, float wait_seconds) -> ()",
+      &gemm_reduce_scatter_push);
   m.def(
       "norm_fwd(int mode, Tensor x, Tensor gamma, Tensor? beta, Tensor(a!) y, Tensor(b!)? mean, Tensor(c!)? rstd, "
       "float eps) -> ()",

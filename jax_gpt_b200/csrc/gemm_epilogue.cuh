@@ -175,7 +175,8 @@ constexpr int kEpiStageBytesPerWarp = 4096;  // 32 rows x 128 bytes (64 bf16 col
 
 // True when a 64-column group can take the staged path below (warp-uniform).
 __device__ __forceinline__ bool gemm_epilogue_staged_ok(const GemmArgs& args, int col0, int ks) {
-  if (args.out_mode != kOutBf16 || col0 + 64 > args.N || (args.ldo & 7) != 0) return false;
+  if ((args.out_mode != kOutBf16 && args.out_mode != kOutBf16PeerPush) || col0 + 64 > args.N || (args.ldo & 7) != 0)
+    return false;
   const bool has_res = args.residual != nullptr && ks == 0;
   if (has_res && (args.epilogue == kEpiGeluGrad || (args.ldr & 7) != 0)) return false;
   if (args.epilogue != kEpiNone && (args.ldaux & 7) != 0) return false;
@@ -295,7 +296,15 @@ __device__ __forceinline__ void gemm_epilogue_group64(const GemmArgs& args, uint
                        pack_bf16x2(gelu_tanh(a2.x), gelu_tanh(a2.y)), pack_bf16x2(gelu_tanh(a3.x), gelu_tanh(a3.y)));
     }
   }
-  stage_store(static_cast<__nv_bfloat16*>(args.out), args.ldo);
+  if (args.out_mode == kOutBf16PeerPush) {
+    // the 32 rows belong to one owner: they go into this rank's slot of the owner's receive buffer
+    const int peer = row0 / args.rows_per_peer;
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(args.peer_out[peer]) +
+                          (static_cast<int64_t>(args.self_rank) - peer) * args.rows_per_peer * args.ldo;
+    stage_store(base, args.ldo);
+  } else {
+    stage_store(static_cast<__nv_bfloat16*>(args.out), args.ldo);
+  }
 }
 
 // fp32 outputs (plain store or reduction into a local buffer), 32 rows x 32 columns per call: the same staging

@@ -195,33 +195,46 @@ class NcclShardedAdamW(_ShardedBase):
 
 
 class ShardedWeight:
-    """A weight W (K, N) kept row-sharded across the ranks (FSDP), consumed WITHOUT materialising it:
-    ``matmul(x)`` runs the tcgen05 GEMM whose TMA producer reads each K-block of W from the shard
-    (local or peer-mapped over NVLink) that owns it, the local rows first, so the parameter
-    all-gather is fused into the first GEMM that needs the parameter."""
+    """A weight W (K, N) kept sharded across the ranks (FSDP: rank r owns the columns ``[r N / W, (r + 1) N / W)``
+    as a contiguous (K, N / W) matrix), gathered INSIDE the GEMM that consumes it: ``matmul(x)`` is one kernel whose
+    copier CTAs push this rank's shard into every peer's gather buffer (every byte over NVLink once, published 64
+    rows at a time) while its compute CTAs run the tcgen05 GEMM on their own gather buffer, the output columns of
+    the local shard first, then each peer's once its shard has landed. The gather buffers (two, alternating, so
+    that a peer one call ahead never overwrites a shard still being read) are shared by all weights of one shape:
+    resident memory stays one shard per weight plus two full-size buffers per distinct shape."""
+
+    _scratch = {}
 
     def __init__(self, comm: Communicator, w_full_or_shard: torch.Tensor, is_shard: bool = False):
         self.comm = comm
         W = comm.world
         if is_shard:
             shard = w_full_or_shard
-            self.K, self.N = shard.shape[0] * W, shard.shape[1]
+            self.K, self.N = shard.shape[0], shard.shape[1] * W
         else:
             self.K, self.N = w_full_or_shard.shape
-            assert self.K % (W * 64) == 0, "rows per rank must be a multiple of the 64-row K block"
-            kp = self.K // W
-            shard = w_full_or_shard[comm.rank * kp:(comm.rank + 1) * kp]
-        self.buf = comm.alloc(shard.numel(), torch.bfloat16)
-        self.shard = self.buf.tensor.view(shard.shape)
-        self.shard.copy_(shard)
-        comm.barrier()
+            npr = self.N // W
+            shard = w_full_or_shard[:, comm.rank * npr:(comm.rank + 1) * npr]
+        assert self.N % (W * 128) == 0 and self.K % 64 == 0, "columns per rank: a multiple of 128; K: a multiple of 64"
+        self.shard = shard.to(device=comm.device, dtype=torch.bfloat16).contiguous().clone()
+        key = (id(comm), self.K, self.N)
+        if key not in ShardedWeight._scratch:
+            bufs = [comm.alloc(self.K * self.N, torch.bfloat16, zero=False) for _ in range(2)]
+            ready = [comm.alloc(W * self.K // 64, torch.int32) for _ in range(2)]
+            torch.cuda.synchronize(comm.device)
+            dist.barrier(comm.group)          # zeroed ready arrays are in place everywhere
+            ShardedWeight._scratch[key] = [bufs, ready, 0]
+        self._key = key
 
     def matmul(self, x: torch.Tensor, bias=None) -> torch.Tensor:
+        st = ShardedWeight._scratch[self._key]
+        st[2] += 1
+        epoch = st[2]
+        buf, rdy = st[0][epoch & 1], st[1][epoch & 1]
+        W, r = self.comm.world, self.comm.rank
+        buf.tensor.view(W, self.K, self.N // W)[r].copy_(self.shard)
         x2 = x.reshape(-1, self.K)
         out = torch.empty(x2.shape[0], self.N, device=x.device, dtype=torch.bfloat16)
-        _ext.ops().gemm_sharded_b(x2, self.buf.peer_ptrs, self.comm.rank, self.N, out, bias)
+        _ext.ops().gemm_sharded_b_staged(x2, buf.peer_ptrs, rdy.peer_ptrs, self.N, r, out, bias, epoch,
+                                         self.comm.wait_seconds)
         return out.reshape(*x.shape[:-1], self.N)
-
-    def sync(self):
-        """Call after the shards were updated (optimizer step) and before the next matmul."""
-        self.comm.barrier()

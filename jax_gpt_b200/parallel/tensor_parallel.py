@@ -2,13 +2,15 @@
 
 Under sequence parallelism the tokens are sharded between the TP regions, so
 
-* a column-parallel projection is ``all-gather(x) @ W_col``  -> :meth:`TPContext.all_gather_matmul`
-  runs the tcgen05 GEMM with one TMA tensor map per rank: M-tiles of the local shard are
-  computed first while the peers' shards are read straight out of their memory by ordinary
-  (non-multicast) TMA tile loads over NVLink;
+* a column-parallel projection is ``all-gather(x) @ W_col``  -> :meth:`TPContext.all_gather_matmul`:
+  ONE kernel whose last CTAs push this rank's row block into every peer's gather buffer (bulk copies local ->
+  shared-memory ring -> peer, and plain 16-byte loads and stores, so every byte crosses NVLink once) and publish
+  it 128 rows at a time in the peer's ready array, while the other CTAs run the tcgen05 GEMM on their own gather
+  buffer, the tiles of the local rows first, waiting block by block for the flags the peers set. No barrier:
+  the gather buffers alternate between two copies;
 * a row-parallel projection is ``reduce-scatter(x @ W_row)`` -> :meth:`TPContext.matmul_reduce_scatter`
-  whose epilogue adds each output tile into the owning rank's fp32 buffer with vectorised
-  ``red.global.add`` over NVLink instead of writing a full partial result and calling NCCL.
+  whose epilogue stores each bf16 output tile into the owning rank's receive slot over NVLink and whose second
+  phase sums the slots of the rows this rank owns, instead of writing a full partial result and calling NCCL.
 
 Used for the MLA / gated-attention projections (q/k/v in, o out). The reference gets the same
 collectives implicitly from GSPMD annotations (jax_gpt/models/qwen35/sharding.py:41-90,
@@ -33,37 +35,57 @@ class TPContext:
 
     # ---- all-gather -> GEMM ------------------------------------------------------------------
     def all_gather_matmul(self, x_local: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
-        """``concat_ranks(x_local) @ w`` with ``w`` (in, out_local); x_local [rows, K] bf16, rows % 128 == 0."""
+        """``concat_ranks(x_local) @ w`` with ``w`` (in, out_local); x_local [rows, K] bf16, rows % 128 == 0.
+        The gather buffers and their ready arrays alternate between two copies per shape: a rank can only be one
+        call ahead of a peer (its next call needs that peer's rows of the call in between), so nobody overwrites
+        rows that are still being read."""
         rows, K = x_local.shape
         assert rows % 128 == 0 and x_local.dtype == torch.bfloat16
         key = (rows, K)
         if key not in self._ag:
-            self._ag[key] = self.comm.alloc(rows * K, torch.bfloat16)
-        buf = self._ag[key]
-        buf.tensor.view(rows, K).copy_(x_local)
-        self.comm.barrier()  # every rank's shard is in place
+            bufs = [self.comm.alloc(self.world * rows * K, torch.bfloat16, zero=False) for _ in range(2)]
+            ready = [self.comm.alloc(self.world * rows // 128, torch.int32) for _ in range(2)]
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.comm.group)                  # every ready array is zero before anyone publishes
+            self._ag[key] = [bufs, ready, 0]
+        bufs, ready, epoch = self._ag[key]
+        epoch += 1
+        self._ag[key][2] = epoch
+        buf, rdy = bufs[epoch & 1], ready[epoch & 1]
+        buf.tensor.view(self.world * rows, K)[self.rank * rows:(self.rank + 1) * rows].copy_(x_local)
         out = torch.empty(rows * self.world, w.shape[1], device=self.device, dtype=torch.bfloat16)
-        _ext.ops().gemm_gathered_a(buf.peer_ptrs, rows, self.rank, K, K, w, True, out, bias)
-        self.comm.barrier()  # nobody still reads this rank's staging buffer
+        _ext.ops().gemm_gathered_a_staged(buf.peer_ptrs, rdy.peer_ptrs, rows, K, self.rank, w, True, out, bias, epoch,
+                                          self.comm.wait_seconds)
         return out
 
     # ---- GEMM -> reduce-scatter ----------------------------------------------------------------
     def matmul_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """Rows ``[rank*R, (rank+1)*R)`` of ``sum_ranks(x @ w)``; x [R*world, K_local] bf16, w (K_local, N)."""
+        """Rows ``[rank*R, (rank+1)*R)`` of ``sum_ranks(x @ w)``; x [R*world, K_local] bf16, w (K_local, N).
+        One kernel: every 128 x BN tile is stored as bf16 into this rank's slot of the row owner's receive buffer
+        (plain 128-byte stores over NVLink, the owners after this rank first, its own rows last), every epilogue
+        warp bumps the owner's arrival counter of the row block, and when the tiles are done the CTAs sum the
+        ``world`` slots of the blocks this rank owns. No barrier and no zeroing: the receive buffers and counters
+        alternate between two copies (a rank cannot be two calls ahead of a peer whose partials it needs)."""
         M, K = x.shape
         N = w.shape[1]
-        assert M % self.world == 0
+        assert M % self.world == 0 and x.dtype == torch.bfloat16
         R = M // self.world
+        assert R % 128 == 0 and N % 64 == 0, "rows per rank must be a multiple of 128 and N of 64"
         key = (R, N)
         if key not in self._rs:
-            self._rs[key] = self.comm.alloc(R * N, torch.float32)
-        buf = self._rs[key]
-        buf.tensor.zero_()
-        self.comm.barrier()  # every destination is zeroed
-        _ext.ops().gemm_reduce_scatter(x, w, True, buf.peer_ptrs, R, N)
-        self.comm.barrier()  # every rank's contributions have landed
-        return buf.tensor.view(R, N).to(torch.bfloat16)
-
+            recv = [self.comm.alloc(self.world * R * N, torch.bfloat16, zero=False) for _ in range(2)]
+            cnt = [self.comm.alloc(R // 128, torch.int32) for _ in range(2)]
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.comm.group)                  # counters are zero everywhere before the first arrival
+            self._rs[key] = [recv, cnt, 0]
+        recv, cnt, calls = self._rs[key]
+        self._rs[key][2] = calls + 1
+        par = calls & 1
+        expected = (calls // 2 + 1) * self.world * 4 * (N // 64)     # four lane quarters x 64-column groups per source
+        out = torch.empty(R, N, device=self.device, dtype=torch.bfloat16)
+        _ext.ops().gemm_reduce_scatter_push(x, w, True, recv[par].peer_ptrs, cnt[par].peer_ptrs, self.rank, R, out, expected,
+                                            self.comm.wait_seconds)
+        return out
 
 def all_gather_matmul_nccl(x_local, w, group=None):
     """Library baseline: NCCL all-gather, then the local GEMM."""

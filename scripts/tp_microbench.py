@@ -9,7 +9,7 @@ collective followed (or preceded) by the plain GEMM:
 * all-gather -> GEMM   ``concat_ranks(x_local) @ W``   (column-parallel projection under sequence parallelism):
   ``x_local`` has ``--rows`` rows per rank, ``W`` is (K, N / world);
 * GEMM -> reduce-scatter   rows of ``sum_ranks(x @ W_r)``   (row-parallel projection): ``x`` is (rows * world, K / world);
-* sharded-weight GEMM   ``x @ W`` with W row-sharded over the ranks (FSDP parameter all-gather fused into the GEMM).
+* sharded-weight GEMM   ``x @ W`` with W column-sharded over the ranks (FSDP parameter all-gather fused into the GEMM).
 
 Roofline per path: the slower of (FLOPs of this rank / measured bf16 GEMM rate) and (bytes this rank must move
 over NVLink / link bandwidth per direction); the JSON line reports time, the two bounds and achieved / bound.
@@ -66,7 +66,7 @@ def main(argv=None):
     peak = peaks["bf16_tflops"] * 1e12
     link = args.link_gbs * 1e9
     rows, K, N = args.rows, args.K, args.N
-    assert K % (world * 64) == 0 and N % (world * 8) == 0 and rows % 128 == 0
+    assert K % (world * 64) == 0 and N % (world * 128) == 0 and rows % 128 == 0
     ctx = TPContext(device=device)
     g = torch.Generator(device=device).manual_seed(1 + rank)
     res = {"world": world, "rows_per_rank": rows, "K": K, "N": N, "denominators": peaks["source"], "link_gbs": args.link_gbs}
@@ -88,7 +88,7 @@ def main(argv=None):
     w_row = (torch.randn(K // world, N, device=device, generator=g) * 0.02).to(torch.bfloat16)
     ms = timed(lambda: ctx.matmul_reduce_scatter(x_full, w_row), args.warmup, args.iters, device, world)
     mb = timed(lambda: matmul_reduce_scatter_nccl(x_full, w_row), args.warmup, args.iters, device, world)
-    report("gemm_reduce_scatter", ms, mb, 2.0 * rows * world * (K // world) * N, 4.0 * rows * (world - 1) * N)
+    report("gemm_reduce_scatter", ms, mb, 2.0 * rows * world * (K // world) * N, 2.0 * rows * (world - 1) * N)   # bf16 partials
     # sharded-weight GEMM (FSDP)
     wg = torch.Generator(device=device).manual_seed(7)
     w_full = (torch.randn(K, N, device=device, generator=wg) * 0.02).to(torch.bfloat16)
@@ -96,9 +96,12 @@ def main(argv=None):
     from jax_gpt_b200.ops.gemm import gemm
 
     def base():
-        parts = torch.empty(K, N, device=device, dtype=torch.bfloat16)
-        dist.all_gather_into_tensor(parts, sw.shard.contiguous())
-        return gemm(x_local, parts, b_mn_major=True)
+        parts = torch.empty(world, K, N // world, device=device, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(parts, sw.shard)
+        out = torch.empty(rows, N, device=device, dtype=torch.bfloat16)
+        for s_ in range(world):
+            gemm(x_local, parts[s_], b_mn_major=True, out=out[:, s_ * (N // world):(s_ + 1) * (N // world)])
+        return out
     ms = timed(lambda: sw.matmul(x_local), args.warmup, args.iters, device, world)
     mb = timed(base, args.warmup, args.iters, device, world)
     report("sharded_weight_gemm", ms, mb, 2.0 * rows * K * N, 2.0 * K * N * (world - 1) / world)

@@ -172,25 +172,32 @@ def run_pp(rank, world, device):
 
 
 def run_tp(rank, world, device):
-    """all-gather -> GEMM and GEMM -> reduce-scatter against their unfused definitions."""
+    """all-gather -> GEMM and GEMM -> reduce-scatter (copier CTAs / pushed partials inside the GEMM kernel) against
+    their unfused definitions; several calls back to back with fresh data, so that the alternating staging buffers,
+    the epochs of the ready flags and the cumulative arrival counters are all exercised."""
     from jax_gpt_b200 import _ext
     from jax_gpt_b200.parallel.tensor_parallel import TPContext
     torch.manual_seed(7)
     ctx = TPContext(device=device, wait_seconds=5.0)
-    rows, K, N = 256, 512, 384
-    x_local = torch.randn(rows, K, device=device).to(torch.bfloat16) * (rank + 1)
-    w = (torch.randn(K, N, device=device, generator=torch.Generator(device=device).manual_seed(11)) * 0.05).to(torch.bfloat16)
-    y = ctx.all_gather_matmul(x_local, w)
-    parts = [torch.empty_like(x_local) for _ in range(world)]
-    dist.all_gather(parts, x_local)
-    ref = (torch.cat(parts).float() @ w.float())
-    res = {"ag_gemm": rel(y, ref)}
-    # row-parallel: each rank holds a K-slice; result rows are scattered
-    xr = torch.randn(rows * world, K, device=device, generator=torch.Generator(device=device).manual_seed(100 + rank)).to(torch.bfloat16)
-    z = ctx.matmul_reduce_scatter(xr, w)
-    full = xr.float() @ w.float()
-    dist.all_reduce(full)
-    res["gemm_rs"] = rel(z, full[rank * rows:(rank + 1) * rows])
+    res = {}
+    for (rows, K, N) in [(256, 512, 384), (1024, 1024, 2048)]:
+        w = (torch.randn(K, N, device=device, generator=torch.Generator(device=device).manual_seed(11)) * 0.05).to(torch.bfloat16)
+        worst_ag = worst_rs = 0.0
+        for call in range(4):
+            g = torch.Generator(device=device).manual_seed(1000 * call + rank)
+            x_local = (torch.randn(rows, K, device=device, generator=g) * (rank + 1)).to(torch.bfloat16)
+            y = ctx.all_gather_matmul(x_local, w)
+            parts = [torch.empty_like(x_local) for _ in range(world)]
+            dist.all_gather(parts, x_local)
+            worst_ag = max(worst_ag, rel(y, torch.cat(parts).float() @ w.float()))
+            # row-parallel: each rank holds a K-slice; result rows are scattered
+            xr = torch.randn(rows * world, K, device=device, generator=g).to(torch.bfloat16)
+            z = ctx.matmul_reduce_scatter(xr, w)
+            full = xr.float() @ w.float()
+            dist.all_reduce(full)
+            worst_rs = max(worst_rs, rel(z, full[rank * rows:(rank + 1) * rows]))
+        res[f"ag_gemm_{rows}x{K}x{N}"] = worst_ag
+        res[f"gemm_rs_{rows}x{K}x{N}"] = worst_rs
     torch.cuda.synchronize()
     _ext.check_status(device)
     dist.barrier()
@@ -198,21 +205,26 @@ def run_tp(rank, world, device):
 
 
 def run_fsdp_ag(rank, world, device):
-    """Row-sharded weight consumed through peer TMA loads vs all-gather + GEMM."""
+    """Column-sharded weight gathered inside the consuming GEMM (pushed by copier CTAs) vs the plain product."""
     from jax_gpt_b200 import _ext
     from jax_gpt_b200.comm.symm import Communicator
     from jax_gpt_b200.parallel.fsdp import ShardedWeight
     comm = Communicator(device=device, wait_seconds=5.0)
     res = {}
-    for (M, K, N) in [(512, 1024, 768), (300, 512, 264)]:
+    for (M, K, N) in [(512, 1024, 1024), (300, 512, 512)]:
         g = torch.Generator(device=device).manual_seed(21)
         w = (torch.randn(K, N, device=device, generator=g) * 0.05).to(torch.bfloat16)
         x = torch.randn(M, K, device=device, generator=torch.Generator(device=device).manual_seed(rank)).to(torch.bfloat16)
         sw = ShardedWeight(comm, w)
-        y = sw.matmul(x)
+        w2 = (w.float() * 0.5 + 0.01).to(torch.bfloat16)        # a second weight of the same shape shares the scratch buffer
+        sw2 = ShardedWeight(comm, w2)
+        worst = 0.0
+        for call in range(3):
+            y, y2 = sw.matmul(x), sw2.matmul(x)
+            worst = max(worst, rel(y, x.float() @ w.float()), rel(y2, x.float() @ w2.float()))
         torch.cuda.synchronize()
         _ext.check_status(device)
-        res[f"ag_gemm_{M}x{K}x{N}"] = rel(y, x.float() @ w.float())
+        res[f"ag_gemm_{M}x{K}x{N}"] = worst
         comm.barrier()
     dist.barrier()
     return res
