@@ -87,6 +87,67 @@ class TPContext:
                                             self.comm.wait_seconds)
         return out
 
+class _ColumnParallelFn(torch.autograd.Function):
+    """``concat_ranks(x_local) @ w`` (sequence-parallel input, column-parallel weight) with the fused kernels in
+    both directions: the backward's input gradient is the fused GEMM -> reduce-scatter of ``dy @ w^T``; the weight
+    gradient needs the gathered input again, which is re-gathered (NCCL) rather than kept alive."""
+
+    @staticmethod
+    def forward(ctx, x_local, w, tp):
+        ctx.tp = tp
+        ctx.save_for_backward(x_local, w)
+        return tp.all_gather_matmul(x_local, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import OUT_F32_ATOMIC, gemm
+        x_local, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        dx = tp.matmul_reduce_scatter(dy, w.t().contiguous()) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            full = torch.empty(x_local.shape[0] * tp.world, x_local.shape[1], device=x_local.device, dtype=x_local.dtype)
+            dist.all_gather_into_tensor(full, x_local.contiguous(), group=tp.comm.group)
+            dw = gemm(full, dy, a_mn_major=True, b_mn_major=True, out_mode=OUT_F32_ATOMIC).to(w.dtype)
+        return dx, dw, None
+
+
+class _RowParallelFn(torch.autograd.Function):
+    """Rows of ``sum_ranks(x @ w_r)`` owned by this rank (row-parallel weight, sequence-parallel output): forward is
+    the fused GEMM -> reduce-scatter, the input gradient the fused all-gather -> GEMM of ``dy_local`` with ``w^T``."""
+
+    @staticmethod
+    def forward(ctx, x, w, tp):
+        ctx.tp = tp
+        ctx.save_for_backward(x, w)
+        return tp.matmul_reduce_scatter(x, w)
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        from ..ops.gemm import OUT_F32_ATOMIC, gemm
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy_local = dy_local.contiguous()
+        dx = tp.all_gather_matmul(dy_local, w.t().contiguous()) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            full = torch.empty(dy_local.shape[0] * tp.world, dy_local.shape[1], device=x.device, dtype=dy_local.dtype)
+            dist.all_gather_into_tensor(full, dy_local, group=tp.comm.group)
+            dw = gemm(x, full, a_mn_major=True, b_mn_major=True, out_mode=OUT_F32_ATOMIC).to(w.dtype)
+        return dx, dw, None
+
+
+def column_parallel_linear(x_local, w, tp: "TPContext"):
+    """Differentiable ``all-gather(x_local) @ w``; x_local [rows, K] bf16 (rows % 128 == 0), w (K, N_local)."""
+    return _ColumnParallelFn.apply(x_local, w, tp)
+
+
+def row_parallel_linear(x, w, tp: "TPContext"):
+    """Differentiable ``reduce-scatter(x @ w)``; x [rows * world, K_local] bf16, w (K_local, N), N % 64 == 0."""
+    return _RowParallelFn.apply(x, w, tp)
+
+
 def all_gather_matmul_nccl(x_local, w, group=None):
     """Library baseline: NCCL all-gather, then the local GEMM."""
     world = dist.get_world_size(group)

@@ -198,6 +198,33 @@ def run_tp(rank, world, device):
             worst_rs = max(worst_rs, rel(z, full[rank * rows:(rank + 1) * rows]))
         res[f"ag_gemm_{rows}x{K}x{N}"] = worst_ag
         res[f"gemm_rs_{rows}x{K}x{N}"] = worst_rs
+    # a column-parallel + row-parallel pair (the shape of an MLP or attention block under sequence parallelism),
+    # differentiated through the fused kernels, against the same pair on gathered tensors with library collectives
+    from jax_gpt_b200.parallel.tensor_parallel import column_parallel_linear, row_parallel_linear
+    rows, K, H = 256, 512, 1024
+    gen = torch.Generator(device=device).manual_seed(50 + rank)
+    x_local = torch.randn(rows, K, device=device, generator=gen).to(torch.bfloat16).requires_grad_()
+    w1 = (torch.randn(K, H // world, device=device, generator=gen) * 0.05).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(H // world, K, device=device, generator=gen) * 0.05).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(rows, K, device=device, generator=gen).to(torch.bfloat16)
+    y = row_parallel_linear(torch.nn.functional.gelu(column_parallel_linear(x_local, w1, ctx).float()).to(torch.bfloat16), w2, ctx)
+    y.backward(dy)
+    xs = [torch.empty_like(x_local) for _ in range(world)]
+    dist.all_gather(xs, x_local.detach())
+    xf = torch.cat(xs).float().requires_grad_()
+    w1f, w2f = w1.detach().float().requires_grad_(), w2.detach().float().requires_grad_()
+    part = torch.nn.functional.gelu(xf @ w1f).to(torch.bfloat16).float() @ w2f
+    full = part.detach().clone()
+    dist.all_reduce(full)
+    dys = [torch.empty_like(dy) for _ in range(world)]
+    dist.all_gather(dys, dy)
+    part.backward(torch.cat(dys).float())
+    gx = xf.grad.clone()
+    dist.all_reduce(gx)
+    res["tp_pair_out"] = rel(y, full[rank * rows:(rank + 1) * rows])
+    res["tp_pair_dx"] = rel(x_local.grad, gx[rank * rows:(rank + 1) * rows])
+    res["tp_pair_dw1"] = rel(w1.grad, w1f.grad)
+    res["tp_pair_dw2"] = rel(w2.grad, w2f.grad)
     torch.cuda.synchronize()
     _ext.check_status(device)
     dist.barrier()

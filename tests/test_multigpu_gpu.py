@@ -63,12 +63,12 @@ def test_pipeline_1f1b_gpt2_over_nccl_two_gpus(tmp_path):
 
 def test_tp_fused_gemms_two_gpus(tmp_path):
     res = _run("tp", tmp_path, port=29612)
-    assert res and all(v < 1e-2 for v in res.values()), res
+    assert res and all(v < (3e-2 if k.startswith("tp_pair_d") else 1e-2) for k, v in res.items()), res
 
 
 def test_tp_fused_gemms_four_gpus(tmp_path):
     res = _run("tp", tmp_path, nproc=4, port=29622)
-    assert res and all(v < 1e-2 for v in res.values()), res
+    assert res and all(v < (3e-2 if k.startswith("tp_pair_d") else 1e-2) for k, v in res.items()), res
     res = _run("fsdp_ag", tmp_path, nproc=4, port=29623)
     assert all(v < 1e-2 for v in res.values()), res
 
