@@ -231,6 +231,35 @@ def run_tp(rank, world, device):
     return res
 
 
+def run_cp(rank, world, device):
+    """Context-parallel causal attention on the flash kernels (block by block, merged with log-sum-exps) against
+    dense attention in fp32; head widths 64 (GPT-2) and 256 with grouped kv heads (gated attention)."""
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.ops.attention import attention_ref
+    from jax_gpt_b200.parallel.context_parallel import context_parallel_attention, zigzag_split
+    res = {}
+    for (H, Hkv, D) in [(4, 4, 64), (4, 2, 256)]:
+        g = torch.Generator(device=device).manual_seed(17)
+        B, T = 2, 256 * 2 * world
+        q = torch.randn(B, T, H, D, device=device, generator=g).to(torch.bfloat16)
+        k = torch.randn(B, T, Hkv, D, device=device, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, T, Hkv, D, device=device, generator=g).to(torch.bfloat16)
+        w = torch.randn(B, T, H, D, device=device, generator=g).to(torch.bfloat16)
+        qr, kr, vr = [t.float().requires_grad_() for t in (q, k, v)]
+        ref = attention_ref(qr, kr, vr, causal=True)
+        (ref * w.float()).sum().backward()
+        ql, kl, vl = [zigzag_split(t, world, rank).contiguous().requires_grad_() for t in (q, k, v)]
+        out = context_parallel_attention(ql, kl, vl)
+        (out.float() * zigzag_split(w, world, rank).float()).sum().backward()
+        torch.cuda.synchronize()
+        _ext.check_status(device)
+        res[f"cp_out_d{D}"] = rel(out, zigzag_split(ref, world, rank))
+        res[f"cp_dq_d{D}"] = rel(ql.grad, zigzag_split(qr.grad, world, rank))
+        res[f"cp_dk_d{D}"] = rel(kl.grad, zigzag_split(kr.grad, world, rank))
+        res[f"cp_dv_d{D}"] = rel(vl.grad, zigzag_split(vr.grad, world, rank))
+    return res
+
+
 def run_fsdp_ag(rank, world, device):
     """Column-sharded weight gathered inside the consuming GEMM (pushed by copier CTAs) vs the plain product."""
     from jax_gpt_b200 import _ext
@@ -522,6 +551,8 @@ def main():
         res = run_pp(rank, world, device)
     elif what == "tp":
         res = run_tp(rank, world, device)
+    elif what == "cp":
+        res = run_cp(rank, world, device)
     elif what == "fsdp_ag":
         res = run_fsdp_ag(rank, world, device)
     elif what == "ep":

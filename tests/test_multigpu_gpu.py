@@ -73,6 +73,11 @@ def test_tp_fused_gemms_four_gpus(tmp_path):
     assert all(v < 1e-2 for v in res.values()), res
 
 
+def test_context_parallel_attention_two_gpus(tmp_path):
+    res = _run("cp", tmp_path, port=29624)
+    assert res and all(v < 3e-2 for v in res.values()), res
+
+
 def test_fsdp_all_gather_fused_into_gemm_two_gpus(tmp_path):
     res = _run("fsdp_ag", tmp_path, port=29614)
     assert all(v < 1e-2 for v in res.values()), res
