@@ -445,7 +445,7 @@ class GPT2TrainEngine:
         """fp32 master parameters as the reference tree. With a sharded optimizer this is a collective call
         (the shards are gathered first): every rank must make it."""
         if self.dist_optimizer is not None:
-            self.dist_optimizer.gather_master(self)
+            return self.flat.tree(self.dist_optimizer.gather_master(self))
         return self.flat.tree(self.flat.master)
 
     def opt_state(self) -> Dict[str, Dict[str, torch.Tensor]]:
@@ -458,19 +458,23 @@ class GPT2TrainEngine:
 
     def load(self, params: Dict[str, torch.Tensor], opt_state=None, step: Optional[int] = None):
         with torch.no_grad():
+            # with a sharded optimizer the replicated fp32 master was released: a temporary full vector takes
+            # the checkpoint's values, the bf16 copy and this rank's shard are cut from it
+            master = self.flat.master if self.flat.master is not None else torch.zeros(
+                self.flat.total, device=self.flat.compute.device, dtype=torch.float32)
             for n, t in params.items():
-                self.flat.view(self.flat.master, n).copy_(t)
-            self.flat.compute.copy_(self.flat.master)
+                self.flat.view(master, n).copy_(t)
+            self.flat.compute.copy_(master)
             if self.dist_optimizer is not None:
                 # sharded optimizer: assemble full-length moments, then keep this rank's slices
                 m = v = None
                 if opt_state is not None:
-                    m, v = torch.zeros_like(self.flat.master), torch.zeros_like(self.flat.master)
+                    m, v = torch.zeros_like(master), torch.zeros_like(master)
                     for n, t in opt_state["mu"].items():
                         self.flat.view(m, n).copy_(t)
                     for n, t in opt_state["nu"].items():
                         self.flat.view(v, n).copy_(t)
-                self.dist_optimizer.scatter_state(self, m, v)
+                self.dist_optimizer.scatter_state(self, master, m, v)
             elif opt_state is not None:
                 for n, t in opt_state["mu"].items():
                     self.flat.view(self.m, n).copy_(t)

@@ -73,23 +73,28 @@ class _ShardedBase:
         self.master = engine.flat.master[lo:hi].clone()
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
+        # from here on the fp32 master weights exist only as shards (ZeRO-style: 4 bytes per parameter and rank
+        # instead of 4 per parameter): the engine's replicated copy is released
+        engine.flat.master = None
 
-    def gather_master(self, engine):
-        """Refreshes the engine's full fp32 master copy from the shards (checkpointing path). Collective."""
-        dist.all_gather_into_tensor(engine.flat.master, self.master, group=self.group)
+    def gather_master(self, engine) -> torch.Tensor:
+        """The full fp32 master vector assembled from the shards (checkpointing path): a temporary. Collective."""
+        full = torch.empty(engine.flat.total, device=self.master.device, dtype=torch.float32)
+        dist.all_gather_into_tensor(full, self.master, group=self.group)
+        return full
 
     def gather_moments(self, engine):
         """Full-length Adam moments (m, v) assembled from every rank's shard. Collective; the result is
         independent of the number of ranks, so a checkpoint can be resumed at another sharding degree."""
-        m = torch.empty_like(engine.flat.master)
-        v = torch.empty_like(engine.flat.master)
+        m = torch.empty(engine.flat.total, device=self.master.device, dtype=torch.float32)
+        v = torch.empty_like(m)
         dist.all_gather_into_tensor(m, self.m, group=self.group)
         dist.all_gather_into_tensor(v, self.v, group=self.group)
         return m, v
 
-    def scatter_state(self, engine, m_full=None, v_full=None):
+    def scatter_state(self, engine, master_full, m_full=None, v_full=None):
         """Re-slices this rank's shards from full-length buffers (after a checkpoint was loaded into the engine)."""
-        self.master.copy_(engine.flat.master[self.lo:self.hi])
+        self.master.copy_(master_full[self.lo:self.hi])
         if m_full is not None:
             self.m.copy_(m_full[self.lo:self.hi])
         if v_full is not None:

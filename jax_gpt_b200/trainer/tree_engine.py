@@ -268,11 +268,10 @@ class TreeTrainEngine:
     # ------------------------------------------------------------------------------------------
     def master_tree(self) -> dict:
         """fp32 master parameters as a nested dict (checkpointing)."""
-        if self.dist_optimizer is not None:
-            self.dist_optimizer.gather_master(self)
+        master = self.dist_optimizer.gather_master(self) if self.dist_optimizer is not None else self.flat.master
         out: dict = {}
         for p, (o, n, shape) in self.offsets.items():
-            _set(out, p, self.flat.master[o:o + n].view(shape))
+            _set(out, p, master[o:o + n].view(shape))
         for p, (o, n, shape) in self.local_offsets.items():
             _set(out, p, self.local_master[o:o + n].view(shape))
         return out
@@ -283,13 +282,13 @@ class TreeTrainEngine:
         tree. With a sharded optimizer this gathers the shards: a COLLECTIVE call on every rank; the result does not
         depend on the number of ranks."""
         if self.dist_optimizer is not None:
-            self.dist_optimizer.gather_master(self)
+            master = self.dist_optimizer.gather_master(self)
             m, v = self.dist_optimizer.gather_moments(self)
         else:
-            m, v = self.m, self.v
+            master, m, v = self.flat.master, self.m, self.v
         out = ({}, {}, {})
         for p, (o, n, shape) in self.offsets.items():
-            for tree, buf in zip(out, (self.flat.master, m, v)):
+            for tree, buf in zip(out, (master, m, v)):
                 _set(tree, p, buf[o:o + n].view(shape))
         return out
 
@@ -310,16 +309,19 @@ class TreeTrainEngine:
             return tree
         if dense is not None:
             master, m, v = dense
-            full_m = torch.zeros_like(self.flat.master) if m is not None else None
-            full_v = torch.zeros_like(self.flat.master) if v is not None else None
+            # with a sharded optimizer the replicated fp32 master was released: load through a temporary
+            full = self.flat.master if self.flat.master is not None else torch.zeros(
+                self.flat.total, device=self.flat.compute.device, dtype=torch.float32)
+            full_m = torch.zeros_like(full) if m is not None else None
+            full_v = torch.zeros_like(full) if v is not None else None
             for p, (o, n, shape) in self.offsets.items():
-                self.flat.master[o:o + n].copy_(get(master, p).reshape(-1).to(self.flat.master))
+                full[o:o + n].copy_(get(master, p).reshape(-1).to(full))
                 if m is not None:
                     full_m[o:o + n].copy_(get(m, p).reshape(-1).to(full_m))
                     full_v[o:o + n].copy_(get(v, p).reshape(-1).to(full_v))
-            self.flat.compute.copy_(self.flat.master)
+            self.flat.compute.copy_(full)
             if self.dist_optimizer is not None:
-                self.dist_optimizer.scatter_state(self, full_m, full_v)
+                self.dist_optimizer.scatter_state(self, full, full_m, full_v)
             elif m is not None:
                 self.m.copy_(full_m)
                 self.v.copy_(full_v)
