@@ -106,15 +106,17 @@ class CheckpointManager:
         """Non-blocking: returns once the tensors are staged in host memory. With a sharded optimizer every rank
         must call it (the shards are gathered collectively) and only rank 0 writes."""
         eng = getattr(state, "engine", None)
+        gathered = None
         if eng is not None and getattr(eng, "dist_optimizer", None) is not None:
-            # the optimizer kernels update per-rank shards: refresh the full fp32 weights and moments first
-            eng.params()
+            # the optimizer kernels update per-rank shards and no rank holds the full fp32 weights: gather them
+            # (and the moments) now, into temporaries that only this save uses
+            gathered = eng.params()
             st = eng.opt_state()
             state.opt_state.mu, state.opt_state.nu = st["mu"], st["nu"]
             if getattr(eng.dist_optimizer, "rank", 0) != 0:
                 return
         self._prune()      # complete checkpoints only; the one about to be written does not count yet
-        params = _model_params(state.model)
+        params = gathered if gathered is not None else _model_params(state.model)
         flat_p = flatten(params) if any(isinstance(v, dict) for v in params.values()) else dict(params)
         opt = state.opt_state
         mu = getattr(opt, "mu", None) or (opt.get("mu") if isinstance(opt, dict) else {})

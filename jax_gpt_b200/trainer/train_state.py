@@ -35,7 +35,10 @@ def create_train_state(model, tx, *, train_config=None, device=None, dist_optimi
                               init={k: v.detach().cpu() for k, v in model.params.items()},
                               use_cuda_graph=c.cuda_graph, dist_optimizer=dist_optimizer,
                               overlap_grad_reduce=getattr(c, "overlap_grad_reduce", False))
-        model.params = eng.params()
+        # the model's tree aliases the engine's buffers: the fp32 master weights on one GPU; with a sharded optimizer
+        # no rank holds those in full, so the tree aliases the (always current) bf16 compute copy instead and the
+        # checkpoint manager gathers the fp32 values when it saves
+        model.params = eng.params() if dist_optimizer is None else eng.flat.tree(eng.flat.compute)
         from .optimizer import AdamWState
         st = eng.opt_state()
         return TrainState(0, model, tx, AdamWState(0, st["mu"], st["nu"]), eng)
