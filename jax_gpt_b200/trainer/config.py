@@ -29,6 +29,7 @@ class TrainConfig:
     fsdp: int = 1
     tp: int = 1
     pp: int = 1                      # pipeline stages (scripts/train.py --pp=N, GPT-2)
+    sequence_parallel: bool = False  # with --tp=N on GPUs: token rows sharded between the blocks, fused collective GEMMs
     sp: int = 1
     pp: int = 1
     ep: int = 1

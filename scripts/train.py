@@ -11,7 +11,9 @@ are sharded over the ranks (fused dispatch / grouped GEMM / combine kernels, for
 dense weights go through the fused sharded optimizer.
 
 ``--tp=N`` (GPT-2 presets, N = number of processes) trains tensor parallel on the shards of
-``trainer/sharding.py`` through the autograd model; ``--pp=N`` trains in N pipeline stages (1F1B over
+``trainer/sharding.py`` through the autograd model (add ``--sequence_parallel=true`` on GPUs to shard the token
+rows between the blocks and run the projections on the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels);
+``--pp=N`` trains in N pipeline stages (1F1B over
 point-to-point sends, the ``--grad_accum_steps`` micro-batches fill the pipeline); with several ranks a watchdog over the rendezvous store turns a
 rank that stops beating into a ``PeerFailure`` on the others before their next step. The MoE families checkpoint
 periodically too (``--save_interval``, ``--resume_from=latest``): dense state gathered to rank 0, every rank writes
@@ -192,6 +194,74 @@ def train_gpt2_tp(args, tc, cfg, rank, world, device):
     torch.distributed.destroy_process_group()
 
 
+def train_gpt2_sp(args, tc, cfg, rank, world, device):
+    """GPT-2 with ``--tp=N --sequence_parallel=true`` on GPUs: heads and MLP columns sharded, token rows sharded
+    between the blocks, the four projections of every block on the fused all-gather -> GEMM and GEMM ->
+    reduce-scatter kernels, forward and backward (parallel/sequence_parallel.py). bf16 compute copies, fp32 master
+    weights and AdamW per shard; every rank feeds the same batch and works on its own rows of it."""
+    import os
+
+    import torch.distributed as dist
+
+    from jax_gpt_b200.data.pipeline import DataPipeline
+    from jax_gpt_b200.data.tokenize import write_synthetic
+    from jax_gpt_b200.models.gpt2 import GPT
+    from jax_gpt_b200.parallel.sequence_parallel import (SHARDED, gpt2_sequence_parallel_loss,
+                                                         shard_gpt2_for_sequence_parallel, sync_replicated_grads)
+    from jax_gpt_b200.parallel.tensor_parallel import TPContext
+    from jax_gpt_b200.trainer import MetricsLogger, create_optimizer
+    if device.type != "cuda" or tc.tp != world:
+        raise SystemExit("--sequence_parallel needs GPUs and --tp equal to the number of processes")
+    if args.synthetic and rank == 0 and not os.path.exists(os.path.join(tc.local_data_path, "train.bin")):
+        write_synthetic(tc.local_data_path, args.synthetic_tokens, cfg.vocab_size, tc.seed)
+    dist.barrier()
+    full = GPT(cfg, seed=tc.seed, device=device, dtype=torch.float32)
+    master = shard_gpt2_for_sequence_parallel(full.params, cfg, world, rank)       # fp32, this rank's shard
+    del full
+    shard_model = type("Shard", (), {"params": master, "config": cfg})()
+    tx = create_optimizer(shard_model, tc)
+    opt_state = tx.init(master)
+    compute = {k: v.to(torch.bfloat16).requires_grad_(True) for k, v in master.items()}
+    tp = TPContext(device=device)
+    data = DataPipeline(tc, "train", _shard_index=0, _shard_count=1)            # the ranks read the same windows
+    logger = MetricsLogger(tc, cfg, jsonl_path=args.jsonl if rank == 0 else "")
+    wd = start_watchdog(rank, world)
+    n_micro = tc.grad_accum_steps
+    step, since, loss_v = 0, 0, float("nan")
+    while step < tc.max_steps:
+        if wd is not None:
+            wd.check()
+        tot = torch.zeros((), device=device)
+        for _ in range(n_micro):
+            x, y = [t.to(device) for t in data.get_batch()]
+            part = gpt2_sequence_parallel_loss(compute, cfg, x, y, tp) / n_micro
+            part.backward()
+            tot += part.detach()
+        sync_replicated_grads(compute)
+        grads = {k: (v.grad.float() if v.grad is not None else torch.zeros_like(master[k])) for k, v in compute.items()}
+        sq_sh = sum((g ** 2).sum() for k, g in grads.items() if k in SHARDED)
+        dist.all_reduce(sq_sh)
+        sq = sq_sh + sum((g ** 2).sum() for k, g in grads.items() if k not in SHARDED)
+        gnorm, lr = tx.update(grads, opt_state, master, global_sq=sq)
+        with torch.no_grad():
+            for k, v in compute.items():
+                v.copy_(master[k])
+                v.grad = None
+        dist.all_reduce(tot)
+        loss_v = float(tot)
+        step += 1
+        since += tc.micro_batch_size * tc.seq_len * n_micro
+        if step % tc.log_interval == 0:
+            logger.log(step, {"loss": loss_v, "grad_norm": gnorm, "lr": lr}, since)
+            since = 0
+    if rank == 0:
+        print(f"done: step {step} loss {loss_v:.4f} (tensor + sequence parallel x{tc.tp}, fused collective GEMMs)")
+    if wd is not None:
+        wd.stop()
+    data.close()
+    dist.destroy_process_group()
+
+
 def train_gpt2_pp(args, tc, cfg, rank, world, device):
     """GPT-2 in ``--pp=N`` pipeline stages, one per process (parallel/pipeline.py): stage r runs its contiguous
     range of blocks, activations and their gradients travel over point-to-point sends in the 1F1B order, the
@@ -287,6 +357,8 @@ def main(argv=None):
     if args.preset.startswith(("qwen35-", "deepseek-v3-")):
         return train_moe(args, tc.replace(dp=world), rank, world, device)
     cfg = gpt_config(args.preset)
+    if tc.tp > 1 and tc.sequence_parallel:
+        return train_gpt2_sp(args, tc, cfg, rank, world, device)
     if tc.tp > 1:
         return train_gpt2_tp(args, tc, cfg, rank, world, device)
     if tc.pp > 1:

@@ -260,6 +260,53 @@ def run_cp(rank, world, device):
     return res
 
 
+def run_sp(rank, world, device):
+    """GPT-2 with tensor + sequence parallelism on the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels:
+    loss and every gradient against the unsharded bf16 model run on the same batch."""
+    from types import SimpleNamespace
+    from jax_gpt_b200 import _ext
+    from jax_gpt_b200.models.gpt2 import GPT, GPTConfig
+    from jax_gpt_b200.parallel.sequence_parallel import (SHARDED, gpt2_sequence_parallel_loss,
+                                                         shard_gpt2_for_sequence_parallel, sync_replicated_grads)
+    from jax_gpt_b200.parallel.tensor_parallel import TPContext
+    from jax_gpt_b200.trainer.sharding import shard_gpt2_tensor
+    cfg = GPTConfig(d_model=256, d_head=64, d_ff=1024, d_context=256, n_head=4, n_kv_head=4, n_layers=2, vocab_size=512)
+    ref = GPT(cfg, seed=21, device=device, dtype=torch.bfloat16)
+    ref.requires_grad_(True)
+    g = torch.Generator().manual_seed(4)
+    tok = torch.randint(0, cfg.vocab_size, (2 * world, 257), generator=g).to(device)
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    logits, _ = ref(x)
+    loss_ref = torch.nn.functional.cross_entropy(logits.float().reshape(-1, cfg.vocab_size), y.reshape(-1))
+    loss_ref.backward()
+    tp = TPContext(device=device, wait_seconds=5.0)
+    params = shard_gpt2_for_sequence_parallel(ref.params, cfg, world, rank)
+    for v in params.values():
+        v.requires_grad_(True)
+    part = gpt2_sequence_parallel_loss(params, cfg, x, y, tp)
+    part.backward()
+    sync_replicated_grads(params)
+    torch.cuda.synchronize()
+    _ext.check_status(device)
+    tot = part.detach().clone()
+    dist.all_reduce(tot)
+    res = {"sp_loss_abs": abs(float(tot) - float(loss_ref))}
+    mesh = SimpleNamespace(size=lambda ax: world if ax == "tp" else 1, rank=lambda ax: rank if ax == "tp" else 0)
+    worst_sh = worst_rep = 0.0
+    for k, v in params.items():
+        rg = ref.params[k].grad
+        if rg is None or v.grad is None or k == "lm_head.kernel":
+            continue
+        if k in SHARDED:
+            worst_sh = max(worst_sh, rel(v.grad, shard_gpt2_tensor(k, rg, cfg, mesh)))
+        else:
+            worst_rep = max(worst_rep, rel(v.grad, rg))
+    res["sp_sharded_grad_rel"] = worst_sh
+    res["sp_replicated_grad_rel"] = worst_rep
+    dist.barrier()
+    return res
+
+
 def run_fsdp_ag(rank, world, device):
     """Column-sharded weight gathered inside the consuming GEMM (pushed by copier CTAs) vs the plain product."""
     from jax_gpt_b200 import _ext
@@ -551,6 +598,8 @@ def main():
         res = run_pp(rank, world, device)
     elif what == "tp":
         res = run_tp(rank, world, device)
+    elif what == "sp":
+        res = run_sp(rank, world, device)
     elif what == "cp":
         res = run_cp(rank, world, device)
     elif what == "fsdp_ag":

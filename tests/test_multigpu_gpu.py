@@ -73,6 +73,11 @@ def test_tp_fused_gemms_four_gpus(tmp_path):
     assert all(v < 1e-2 for v in res.values()), res
 
 
+def test_gpt2_sequence_parallel_on_fused_gemms_two_gpus(tmp_path):
+    res = _run("sp", tmp_path, port=29625)
+    assert res["sp_loss_abs"] < 2e-2 and res["sp_sharded_grad_rel"] < 6e-2 and res["sp_replicated_grad_rel"] < 6e-2, res
+
+
 def test_context_parallel_attention_two_gpus(tmp_path):
     res = _run("cp", tmp_path, port=29624)
     assert res and all(v < 3e-2 for v in res.values()), res
