@@ -472,7 +472,8 @@ __global__ void gdn_decode_kernel(const __nv_bfloat16* __restrict__ mixed, const
                                   float* __restrict__ conv_state, const __nv_bfloat16* __restrict__ conv_w,
                                   const __nv_bfloat16* __restrict__ A_log, const __nv_bfloat16* __restrict__ dt_bias,
                                   const __nv_bfloat16* __restrict__ norm_w, float* __restrict__ state,
-                                  __nv_bfloat16* __restrict__ out, int Hqk, int Hv, int dk, int dv, int Kc, float eps) {
+                                  __nv_bfloat16* __restrict__ out, int Hqk, int Hv, int dk, int dv, int Kc, float eps,
+                                  int ld_mixed, int ld_z, int ld_b, int ld_a) {
   extern __shared__ float sm[];
   float* qs = sm;            // [dk]
   float* ks = sm + dk;       // [dk]
@@ -481,7 +482,7 @@ __global__ void gdn_decode_kernel(const __nv_bfloat16* __restrict__ mixed, const
   const int rep = Hv / Hqk;
   const int Kd = Hqk * dk, Vd = Hv * dv, C = 2 * Kd + Vd;
   const int t = threadIdx.x;
-  const __nv_bfloat16* mx = mixed + static_cast<int64_t>(b) * C;
+  const __nv_bfloat16* mx = mixed + static_cast<int64_t>(b) * ld_mixed;   // the inputs may be column slices of one GEMM output
   float* cs = conv_state + static_cast<int64_t>(b) * C * Kc;
   float qv = 0.f, kv_ = 0.f;
   if (t < dk) {
@@ -503,8 +504,8 @@ __global__ void gdn_decode_kernel(const __nv_bfloat16* __restrict__ mixed, const
       const int cv = 2 * Kd + hv * dv + t;
       const float vv = conv_step(cs + static_cast<int64_t>(cv) * Kc, conv_w + static_cast<int64_t>(cv) * Kc, Kc,
                                  __bfloat162float(mx[cv]));
-      const float beta = 1.f / (1.f + __expf(-__bfloat162float(bproj[b * Hv + hv])));
-      const float xa = __bfloat162float(aproj[b * Hv + hv]) + __bfloat162float(dt_bias[hv]);
+      const float beta = 1.f / (1.f + __expf(-__bfloat162float(bproj[static_cast<int64_t>(b) * ld_b + hv])));
+      const float xa = __bfloat162float(aproj[static_cast<int64_t>(b) * ld_a + hv]) + __bfloat162float(dt_bias[hv]);
       const float sp = (xa > 20.f) ? xa : log1pf(__expf(xa));
       const float eg = __expf(-__expf(__bfloat162float(A_log[hv])) * sp);
       float* S = state + (static_cast<int64_t>(b) * Hv + hv) * dk * dv + t;  // column t, stride dv
@@ -516,7 +517,7 @@ __global__ void gdn_decode_kernel(const __nv_bfloat16* __restrict__ mixed, const
         S[static_cast<int64_t>(i) * dv] = s;
         o += s * qs[i];
       }
-      zv = __bfloat162float(z[static_cast<int64_t>(b) * Vd + hv * dv + t]);
+      zv = __bfloat162float(z[static_cast<int64_t>(b) * ld_z + hv * dv + t]);
     }
     const float ms = block_sum_256((t < dv) ? o * o : 0.f, scratch) / dv;
     if (t < dv)
@@ -599,12 +600,13 @@ cudaError_t launch_gdn_decode_step(const __nv_bfloat16* mixed, const __nv_bfloat
                                    const __nv_bfloat16* aproj, float* conv_state, const __nv_bfloat16* conv_w,
                                    const __nv_bfloat16* A_log, const __nv_bfloat16* dt_bias,
                                    const __nv_bfloat16* norm_w, float* state, __nv_bfloat16* out, int B, int Hqk, int Hv,
-                                   int dk, int dv, int Kc, float eps, cudaStream_t st) {
+                                   int dk, int dv, int Kc, float eps, int ld_mixed, int ld_z, int ld_b, int ld_a,
+                                   cudaStream_t st) {
   const int threads = ((dk > dv ? dk : dv) + 31) / 32 * 32;
   if (threads > 256 || Hv % Hqk != 0 || Kc < 1) return cudaErrorInvalidValue;
   gdn_decode_kernel<<<B * Hqk, threads, (2 * dk + 8) * sizeof(float), st>>>(mixed, z, bproj, aproj, conv_state, conv_w,
                                                                           A_log, dt_bias, norm_w, state, out, Hqk, Hv,
-                                                                          dk, dv, Kc, eps);
+                                                                          dk, dv, Kc, eps, ld_mixed, ld_z, ld_b, ld_a);
   return cudaGetLastError();
 }
 

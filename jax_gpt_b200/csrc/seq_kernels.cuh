@@ -39,14 +39,16 @@ cudaError_t launch_fp8_quant_mx(const __nv_bfloat16* x, uint8_t* q, float* scale
 
 // One decode step of a Gated-DeltaNet layer for B sequences, fused: conv-window update + depthwise
 // conv + SiLU, gates, L2-normalised q/k, state decay + delta-rule update, read-out, gated RMSNorm.
-//  mixed [B, 2*Kd + Vd] bf16 (projected q|k|v before the conv), z [B, Vd], bproj / aproj [B, Hv] bf16,
+//  mixed [B, 2*Kd + Vd] bf16 (projected q|k|v before the conv), z [B, Vd], bproj / aproj [B, Hv] bf16 (row strides
+//  ld_*: the four may be column slices of one merged projection output),
 //  conv_state [B, C, Kc] fp32 (updated in place), conv_w [C, Kc], A_log / dt_bias [Hv], norm_w [dv],
 //  state [B, Hv, dk, dv] fp32 (updated in place), out [B, Vd] bf16.
 cudaError_t launch_gdn_decode_step(const __nv_bfloat16* mixed, const __nv_bfloat16* z, const __nv_bfloat16* bproj,
                                    const __nv_bfloat16* aproj, float* conv_state, const __nv_bfloat16* conv_w,
                                    const __nv_bfloat16* A_log, const __nv_bfloat16* dt_bias,
                                    const __nv_bfloat16* norm_w, float* state, __nv_bfloat16* out, int B, int Hqk, int Hv,
-                                   int dk, int dv, int Kc, float eps, cudaStream_t st);
+                                   int dk, int dv, int Kc, float eps, int ld_mixed, int ld_z, int ld_b, int ld_a,
+                                   cudaStream_t st);
 
 // Backward of launch_rmsnorm_rope: dx [rows, H, dh] bf16; dw [dh] fp32 is ACCUMULATED into (may be nullptr).
 cudaError_t launch_rmsnorm_rope_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, const __nv_bfloat16* norm_w,

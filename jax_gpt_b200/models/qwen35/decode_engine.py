@@ -12,6 +12,9 @@ device memory:
   (csrc/attention_decode.cu), which reads the number of valid keys from that scalar, so every shape is static;
 * the routed experts go through the fused dispatch / grouped GEMM / combine kernel when an expert runtime is
   given (a launch per expert otherwise, which cannot be captured: the engine then runs eagerly);
+* projections that share their input run as one GEMM over weights concatenated once at construction (the four
+  DeltaNet input projections, attention q | k | v, the shared expert's gate | up); the fused decode kernel reads
+  the column slices of that GEMM's output in place;
 * embedding, all layers, the head, the arg-max and the position increment are captured in one CUDA graph the
   first time a step runs and replayed afterwards.
 
@@ -64,6 +67,38 @@ class Qwen35DecodeEngine:
         self.logits = None
         self.use_graph = bool(use_cuda_graph) and self.device.type == "cuda" and callable(ep)
         self._graph = None
+        self._layers = self._build_layers()
+
+    def _build_layers(self):
+        """Per-layer parameter dicts, sliced once, with the projections that share an input concatenated so that a
+        token step launches one GEMM where the function-style model launches four (DeltaNet q|k|v, z, b, a), three
+        (attention q, k, v) or two (shared expert gate, up). Only plain tensors are merged (FP8 dicts stay apart)."""
+        c, p = self.c, self.p
+        plain = lambda *ts: all(torch.is_tensor(t) for t in ts)
+        def merge_moe(moe):
+            moe = dict(moe)
+            if plain(moe["shared_gate_proj"], moe["shared_up_proj"]):
+                moe["shared_gate_up_proj"] = torch.cat([moe["shared_gate_proj"], moe["shared_up_proj"]], dim=1).contiguous()
+            return moe
+        layers = []
+        for gi in range(c.n_groups):
+            gp = _slice(p["groups"], gi)
+            delta = []
+            for i in range(c.n_delta_per_group):
+                lp = dict(_slice(gp["delta_layers"], i))
+                ap = dict(lp["attn"])
+                if plain(ap["in_proj_qkv"], ap["in_proj_z"], ap["in_proj_b"], ap["in_proj_a"]):
+                    ap["in_proj_all"] = torch.cat([ap["in_proj_qkv"], ap["in_proj_z"], ap["in_proj_b"], ap["in_proj_a"]],
+                                                  dim=1).contiguous()
+                lp["attn"], lp["moe"] = ap, merge_moe(lp["moe"])
+                delta.append(lp)
+            gl = dict(gp["gqa_layer"])
+            ap = dict(gl["attn"])
+            if plain(ap["q_proj"], ap["k_proj"], ap["v_proj"]):
+                ap["qkv_proj"] = torch.cat([ap["q_proj"], ap["k_proj"], ap["v_proj"]], dim=1).contiguous()
+            gl["attn"], gl["moe"] = ap, merge_moe(gl["moe"])
+            layers.append((delta, gl))
+        return layers
 
     # ---- layers (x is (B, D)) -------------------------------------------------------------------------
     def _moe(self, x, lp):
@@ -87,10 +122,17 @@ class Qwen35DecodeEngine:
         c, ap = self.c, lp["attn"]
         B, Hq, Hkv, dh = self.B, c.gqa_n_q_heads, c.gqa_n_kv_heads, c.gqa_head_dim
         h = rms_norm(x, lp["attn_norm"], c.rms_norm_eps)
-        qg = matmul_maybe_fp8(h, ap["q_proj"]).reshape(B, 1, Hq, 2 * dh)
+        if "qkv_proj" in ap:
+            qkv = matmul_maybe_fp8(h, ap["qkv_proj"])
+            nq, nk = 2 * Hq * dh, Hkv * dh
+            qg = qkv[:, :nq].reshape(B, 1, Hq, 2 * dh)
+            k = qkv[:, nq:nq + nk].reshape(B, 1, Hkv, dh)
+            v = qkv[:, nq + nk:].reshape(B, 1, Hkv, dh)
+        else:
+            qg = matmul_maybe_fp8(h, ap["q_proj"]).reshape(B, 1, Hq, 2 * dh)
+            k = matmul_maybe_fp8(h, ap["k_proj"]).reshape(B, 1, Hkv, dh)
+            v = matmul_maybe_fp8(h, ap["v_proj"]).reshape(B, 1, Hkv, dh)
         q, gate = qg[..., :dh], qg[..., dh:]
-        k = matmul_maybe_fp8(h, ap["k_proj"]).reshape(B, 1, Hkv, dh)
-        v = matmul_maybe_fp8(h, ap["v_proj"]).reshape(B, 1, Hkv, dh)
         fr = self.rope.index_select(0, self.pos_t)                                   # (1, rope_dim/2, 2)
         q = apply_rotary_emb(rms_norm(q.contiguous(), ap["q_norm"]), fr, c.gqa_rope_dim)
         k = apply_rotary_emb(rms_norm(k.contiguous(), ap["k_norm"]), fr, c.gqa_rope_dim)
@@ -104,11 +146,10 @@ class Qwen35DecodeEngine:
     def _token_step(self):
         c, p = self.c, self.p
         x = p["embed"][self.tokens]
-        for gi in range(c.n_groups):
-            gp = _slice(p["groups"], gi)
-            for i in range(c.n_delta_per_group):
-                x = self._delta_layer(x, _slice(gp["delta_layers"], i), gi, i)
-            x = self._gqa_layer(x, gp["gqa_layer"], gi)
+        for gi, (delta, gqa) in enumerate(self._layers):
+            for i, lp in enumerate(delta):
+                x = self._delta_layer(x, lp, gi, i)
+            x = self._gqa_layer(x, gqa, gi)
         logits = matmul_maybe_fp8(rms_norm(x, p["final_norm"], c.rms_norm_eps), p["lm_head"])
         self.next_tokens.copy_(logits.argmax(-1))
         self.pos_t.add_(1)

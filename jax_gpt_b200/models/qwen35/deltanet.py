@@ -81,6 +81,11 @@ def causal_conv1d_prefill(x: torch.Tensor, weight: torch.Tensor):
 
 
 def _project(x, params, n_qk, n_v, dk, dv):
+    if "in_proj_all" in params:
+        # the four projections as ONE GEMM over the concatenated weights (decode engine): column slices of its output
+        y = matmul_maybe_fp8(x, params["in_proj_all"])
+        c, vd = 2 * n_qk * dk + n_v * dv, n_v * dv
+        return y[..., :c], y[..., c:c + vd], y[..., c + vd:c + vd + n_v], y[..., c + vd + n_v:c + vd + 2 * n_v]
     mixed = matmul_maybe_fp8(x, params["in_proj_qkv"])
     z = matmul_maybe_fp8(x, params["in_proj_z"])
     b = matmul_maybe_fp8(x, params["in_proj_b"])
@@ -115,8 +120,8 @@ def deltanet_recurrent_step(x, params, state, conv_state, n_qk: int, n_v: int, d
         out = torch.empty(B, n_v * dv, device=x.device, dtype=torch.bfloat16)
         state_c, conv_c = state.contiguous(), conv_state.contiguous()
         bf = lambda t: t.to(torch.bfloat16).contiguous()
-        _ext.ops().gdn_decode_step(mixed[:, 0].contiguous(), z[:, 0].contiguous(), b[:, 0].contiguous(),
-                                   a[:, 0].contiguous(), conv_c, bf(params["conv_weight"]), bf(params["A_log"]),
+        # the kernel takes row strides: column slices of a merged projection output are read in place
+        _ext.ops().gdn_decode_step(mixed[:, 0], z[:, 0], b[:, 0], a[:, 0], conv_c, bf(params["conv_weight"]), bf(params["A_log"]),
                                    bf(params["dt_bias"]), bf(params["norm_weight"]), state_c, out, n_qk, n_v, dk, dv, 1e-6)
         y = matmul_maybe_fp8(out, params["out_proj"])
         return y[:, None, :], state_c, conv_c

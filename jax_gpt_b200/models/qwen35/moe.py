@@ -120,6 +120,10 @@ def expert_forward_tp(x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor,
 
 
 def shared_expert_forward(x: torch.Tensor, params) -> torch.Tensor:
+    if "shared_gate_up_proj" in params:       # gate | up as one GEMM over concatenated weights (decode engine)
+        gu = matmul_maybe_fp8(x, params["shared_gate_up_proj"])
+        half = gu.shape[-1] // 2
+        return matmul_maybe_fp8(F.silu(gu[..., :half]) * gu[..., half:], params["shared_down_proj"])
     g = matmul_maybe_fp8(x, params["shared_gate_proj"])
     u = matmul_maybe_fp8(x, params["shared_up_proj"])
     return matmul_maybe_fp8(F.silu(g) * u, params["shared_down_proj"])
