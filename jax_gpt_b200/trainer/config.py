@@ -28,10 +28,9 @@ class TrainConfig:
     dp: int = 1
     fsdp: int = 1
     tp: int = 1
-    pp: int = 1                      # pipeline stages (scripts/train.py --pp=N, GPT-2)
     sequence_parallel: bool = False  # with --tp=N on GPUs: token rows sharded between the blocks, fused collective GEMMs
     sp: int = 1
-    pp: int = 1
+    pp: int = 1                      # pipeline stages (scripts/train.py --pp=N, GPT-2)
     ep: int = 1
     # data
     data_source: str = "local"

@@ -363,7 +363,12 @@ def main(argv=None):
         return train_gpt2_tp(args, tc, cfg, rank, world, device)
     if tc.pp > 1:
         return train_gpt2_pp(args, tc, cfg, rank, world, device)
-    tc = tc.replace(dp=world)
+    if tc.fsdp > 1 and tc.fsdp != world:
+        raise SystemExit(f"--fsdp={tc.fsdp} must equal the number of processes ({world}): the data-parallel ranks ARE the "
+                         f"shards (gradients reduce-scattered, fp32 master weights and moments kept as shards)")
+    # several GPUs, no --tp / --pp: data parallel with sharded state (--fsdp=N spells it out): every rank keeps 1 / N of
+    # the fp32 master weights and Adam moments, one fused kernel does reduce-scatter + AdamW + all-gather
+    tc = tc.replace(dp=world if tc.fsdp == 1 else 1)
     if args.synthetic and rank == 0:
         import os
         if not os.path.exists(os.path.join(tc.local_data_path, "train.bin")):
