@@ -31,6 +31,13 @@ struct DecArgs {
   float scale_log2;
   float* part_o;            // [B, H, n_splits, D] un-normalised partial outputs
   float* part_ml;           // [B, H, n_splits, 2] (running max in log2 units, sum)
+  // paged cache (table != nullptr): k / v point at the K and V halves of a page pool [n_pages, page_size, width];
+  // key t of sequence seq_ids[b] sits in row table[seq, t / page_size] * page_size + t % page_size, kv_stride_t is the
+  // pool's row width, the number of valid keys is lens[seq] + len_add
+  const int* table;
+  const int* seq_ids;
+  const int* lens;
+  int page_size, max_pages;
 };
 
 template <int D, int G>
@@ -45,7 +52,14 @@ attn_decode_split_kernel(const DecArgs a) {
   const int n_splits = gridDim.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane % LPK, grp = lane / LPK;
-  const int len = a.pos_ptr != nullptr ? a.pos_ptr[0] + a.len_add : a.len;
+  const int seq = a.table != nullptr ? a.seq_ids[b] : b;
+  const int len = a.table != nullptr ? a.lens[seq] + a.len_add : (a.pos_ptr != nullptr ? a.pos_ptr[0] + a.len_add : a.len);
+  const int* pages = a.table != nullptr ? a.table + static_cast<int64_t>(seq) * a.max_pages : nullptr;
+  // cache row of key t: the key index itself for a dense cache, page * page_size + offset for a paged one
+  auto key_row = [&](int t) -> int64_t {
+    if (pages == nullptr) return t;
+    return static_cast<int64_t>(pages[t / a.page_size]) * a.page_size + t % a.page_size;
+  };
   const int per = ((len + n_splits - 1) / n_splits + KPS - 1) / KPS * KPS;
   const int k0 = split * per, k1 = min(len, k0 + per);
 
@@ -77,10 +91,11 @@ attn_decode_split_kernel(const DecArgs a) {
     const int ka = base + grp, kc = ka + KPS;
     const bool has_a = ka < k1, has_c = kc < k1;
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    const uint4 kua = has_a ? *reinterpret_cast<const uint4*>(kb + ka * a.kv_stride_t) : zero;
-    const uint4 vua = has_a ? *reinterpret_cast<const uint4*>(vb + ka * a.kv_stride_t) : zero;
-    const uint4 kuc = has_c ? *reinterpret_cast<const uint4*>(kb + kc * a.kv_stride_t) : zero;
-    const uint4 vuc = has_c ? *reinterpret_cast<const uint4*>(vb + kc * a.kv_stride_t) : zero;
+    const int64_t ra = has_a ? key_row(ka) * a.kv_stride_t : 0, rc = has_c ? key_row(kc) * a.kv_stride_t : 0;
+    const uint4 kua = has_a ? *reinterpret_cast<const uint4*>(kb + ra) : zero;
+    const uint4 vua = has_a ? *reinterpret_cast<const uint4*>(vb + ra) : zero;
+    const uint4 kuc = has_c ? *reinterpret_cast<const uint4*>(kb + rc) : zero;
+    const uint4 vuc = has_c ? *reinterpret_cast<const uint4*>(vb + rc) : zero;
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
       const uint4 ku = which == 0 ? kua : kuc;
@@ -217,7 +232,24 @@ cudaError_t launch_attn_decode(const __nv_bfloat16* q, int64_t ldq, const __nv_b
       ldq % 8 != 0)
     return cudaErrorInvalidValue;
   DecArgs a{q, ldq, k, v, kv_stride_b, kv_stride_h, kv_stride_t, pos_ptr, len, len_add, H, Hkv,
-            scale * 1.4426950408889634f, part_o, part_ml};
+            scale * 1.4426950408889634f, part_o, part_ml, nullptr, nullptr, nullptr, 0, 0};
+  switch (D) {
+    case 64: return decode_dispatch_g<64>(a, B, n_splits, out, ldo, stream);
+    case 128: return decode_dispatch_g<128>(a, B, n_splits, out, ldo, stream);
+    case 256: return decode_dispatch_g<256>(a, B, n_splits, out, ldo, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_attn_decode_paged(const __nv_bfloat16* q, int64_t ldq, const __nv_bfloat16* pool, int width,
+                                     const int* block_table, const int* seq_ids, const int* seq_lens, int len_add,
+                                     int page_size, int max_pages, int B, int H, int Hkv, int D, float scale, int n_splits,
+                                     float* part_o, float* part_ml, __nv_bfloat16* out, int64_t ldo, cudaStream_t stream) {
+  if (H % Hkv != 0 || n_splits < 1 || width != 2 * Hkv * D || width % 8 != 0 || ldq % 8 != 0 || page_size < 1)
+    return cudaErrorInvalidValue;
+  // a pool row holds K of every kv head, then V of every kv head
+  DecArgs a{q, ldq, pool, pool + Hkv * D, 0, D, width, nullptr, 0, len_add, H, Hkv,
+            scale * 1.4426950408889634f, part_o, part_ml, block_table, seq_ids, seq_lens, page_size, max_pages};
   switch (D) {
     case 64: return decode_dispatch_g<64>(a, B, n_splits, out, ldo, stream);
     case 128: return decode_dispatch_g<128>(a, B, n_splits, out, ldo, stream);

@@ -79,6 +79,15 @@ cudaError_t launch_attn_decode(const __nv_bfloat16* q, int64_t ldq, const __nv_b
                                int len, int len_add, int B, int H, int Hkv, int D, float scale, int n_splits,
                                float* part_o, float* part_ml, __nv_bfloat16* out, int64_t ldo, cudaStream_t stream);
 
+// The same decode attention over a PAGED cache: pool [n_pages, page_size, width] bf16 with width = 2 * Hkv * D (K of
+// every kv head, then V), block_table [max_seqs, max_pages] int32, seq_ids [B], seq_lens [max_seqs] (device); the
+// number of valid keys of a sequence is seq_lens[seq] + len_add (len_add = 1 when the new token's row has been written
+// but the length not yet advanced).
+cudaError_t launch_attn_decode_paged(const __nv_bfloat16* q, int64_t ldq, const __nv_bfloat16* pool, int width,
+                                     const int* block_table, const int* seq_ids, const int* seq_lens, int len_add,
+                                     int page_size, int max_pages, int B, int H, int Hkv, int D, float scale, int n_splits,
+                                     float* part_o, float* part_ml, __nv_bfloat16* out, int64_t ldo, cudaStream_t stream);
+
 // dst[r, c] (bf16, row stride ldd) = src[r, c] (fp32, row stride lds), for an M x N block.
 // In-place elementwise step of the recomputed attention backward: s [rows, kv] bf16 scores -> probabilities,
 // dp [rows, kv] bf16 (dO V^T) -> dS; lse (log2 units) and delta per row; row r is query position q0 + r % c.

@@ -438,6 +438,35 @@ void attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcache, co
                                            part_ml.data_ptr<float>(), bf16_mut(out), out.stride(0), cur_stream()));
 }
 
+// One query token per sequence against a paged cache: pool [n_pages, page_size, 2 * Hkv * D] bf16 (K of every kv head,
+// then V), block_table [max_seqs, max_pages] / seq_ids [B] / seq_lens [max_seqs] int32 on the device.
+void attn_decode_paged(const Tensor& q, const Tensor& pool, const Tensor& block_table, const Tensor& seq_ids,
+                       const Tensor& seq_lens, int64_t len_add, int64_t H, int64_t Hkv, double scale, Tensor part_o,
+                       Tensor part_ml, Tensor out) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_bf16_2d(q, "q");
+  check_bf16_2d(out, "out");
+  TORCH_CHECK(pool.dim() == 3 && pool.is_contiguous() && pool.scalar_type() == at::kBFloat16 && Hkv >= 1 &&
+                  pool.size(2) % (2 * Hkv) == 0,
+              "attn_decode_paged: pool [n_pages, page_size, 2 * Hkv * D] bf16");
+  const int64_t B = q.size(0), D = pool.size(2) / (2 * Hkv);
+  auto i32 = [](const Tensor& t) { return t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(); };
+  TORCH_CHECK(i32(block_table) && block_table.dim() == 2 && i32(seq_ids) && seq_ids.numel() >= B && i32(seq_lens) &&
+                  seq_lens.numel() == block_table.size(0),
+              "attn_decode_paged: block_table [max_seqs, max_pages], seq_ids [B], seq_lens [max_seqs] int32 on the device");
+  TORCH_CHECK(q.size(1) == H * D && out.size(0) == B && out.size(1) == H * D, "attn_decode_paged: q / out must be [B, H*D]");
+  TORCH_CHECK(part_o.scalar_type() == at::kFloat && part_ml.scalar_type() == at::kFloat && part_o.is_contiguous() &&
+                  part_ml.is_contiguous() && part_o.dim() == 4 && part_o.size(0) >= B && part_o.size(1) == H &&
+                  part_o.size(3) == D && part_ml.numel() * D == part_o.numel() * 2,
+              "attn_decode_paged: part_o [B, H, splits, D], part_ml [B, H, splits, 2] fp32");
+  B200_CHECK_CUDA(b200::launch_attn_decode_paged(
+      bf16_ptr(q), q.stride(0), bf16_ptr(pool), static_cast<int>(pool.size(2)), block_table.data_ptr<int>(),
+      seq_ids.data_ptr<int>(), seq_lens.data_ptr<int>(), static_cast<int>(len_add), static_cast<int>(pool.size(1)),
+      static_cast<int>(block_table.size(1)), static_cast<int>(B), static_cast<int>(H), static_cast<int>(Hkv),
+      static_cast<int>(D), static_cast<float>(scale), static_cast<int>(part_o.size(2)), part_o.data_ptr<float>(),
+      part_ml.data_ptr<float>(), bf16_mut(out), out.stride(0), cur_stream()));
+}
+
 void attn_bwd_probs(Tensor s, Tensor dp, const Tensor& lse, const Tensor& delta, int64_t c, int64_t q0, double scale,
                     bool causal) {
   c10::cuda::CUDAGuard guard(s.device());
@@ -530,6 +559,10 @@ TORCH_LIBRARY(b200, m) {
       "attn_decode(Tensor q, Tensor kcache, Tensor vcache, Tensor? pos, int len, int len_add, int H, float scale, "
       "Tensor(a!) part_o, Tensor(b!) part_ml, Tensor(c!) out) -> ()",
       &attn_decode);
+  m.def(
+      "attn_decode_paged(Tensor q, Tensor pool, Tensor block_table, Tensor seq_ids, Tensor seq_lens, int len_add, int H, "
+      "int Hkv, float scale, Tensor(a!) part_o, Tensor(b!) part_ml, Tensor(c!) out) -> ()",
+      &attn_decode_paged);
   m.def("attn_bwd_probs(Tensor(a!) s, Tensor(b!) dp, Tensor lse, Tensor delta, int c, int q0, float scale, bool causal) -> ()", &attn_bwd_probs);
   m.def("norm_bwd_scratch_floats(int D) -> int", [](int64_t D) { return b200::norm_bwd_scratch_floats(static_cast<int>(D)); });
   m.def("gemm_uses_pair(int M, int N, int split_k) -> bool", [](int64_t M, int64_t N, int64_t split_k) {

@@ -38,10 +38,14 @@ from .primitives import apply_rotary_emb, precompute_rope_freqs, rms_norm
 
 
 class Qwen35DecodeEngine:
-    def __init__(self, params: dict, config: Qwen35Config, cache: HybridCache, ep=None, use_cuda_graph: bool = True):
+    def __init__(self, params: dict, config: Qwen35Config, cache: HybridCache, ep=None, use_cuda_graph: bool = True,
+                 paged_kv: bool = False):
         """``cache`` holds the prompts (prefill done); its key / value buffers are used in place, the recurrent
         states are copied once into fp32 buffers. ``ep``: callable expert runtime
-        (parallel/expert_parallel.py:EPMoEInferenceRuntime) or None."""
+        (parallel/expert_parallel.py:EPMoEInferenceRuntime) or None. ``paged_kv``: the gated-attention layers keep
+        their keys and values in a paged cache (cache/paged.py: 64-token pages, block table, per-sequence lengths;
+        one pool row = K of both kv heads, then V) instead of the dense buffers: the prompt rows are copied into
+        pages here, a step scatters the new row with ``paged_kv_write`` and attends through the block table."""
         c = config
         self.p, self.c, self.ep = params, c, ep
         self.device = cache.gqa_k.device
@@ -68,6 +72,26 @@ class Qwen35DecodeEngine:
         self.use_graph = bool(use_cuda_graph) and self.device.type == "cuda" and callable(ep)
         self._graph = None
         self._layers = self._build_layers()
+        self.paged = None
+        if paged_kv:
+            from ...cache.paged import PagedCache
+            ps = 64
+            per_seq = (self.max_len + ps - 1) // ps
+            Hkv, dh = c.gqa_n_kv_heads, c.gqa_head_dim
+            self.paged = PagedCache(c.n_groups, 2 * Hkv * dh, n_pages=self.B * per_seq, page_size=ps, max_seqs=self.B,
+                                    max_pages_per_seq=per_seq, dtype=self.k.dtype, device=self.device)
+            self.seq_ids = list(range(self.B))
+            for sid in self.seq_ids:                      # every page a sequence can ever need: the table is static
+                self.paged.reserve(sid, self.max_len)
+            if self.pos > 0:
+                for gi in range(c.n_groups):              # (B, Hkv, pos, dh) x 2 -> rows (B, pos, 2 Hkv dh)
+                    kk = self.k[gi][:, :, :self.pos].permute(0, 2, 1, 3).reshape(self.B, self.pos, Hkv * dh)
+                    vv = self.v[gi][:, :, :self.pos].permute(0, 2, 1, 3).reshape(self.B, self.pos, Hkv * dh)
+                    self.paged.append(gi, self.seq_ids, torch.cat([kk, vv], dim=-1))
+                self.paged.commit(self.seq_ids, self.pos)
+            self.seq_id_t = self.paged.seq_id_tensor(self.seq_ids)
+            self.paged_lens = self.paged.seq_lens.clone()     # advanced on the device inside the captured step
+            self.k = self.v = None                            # the dense buffers are not used any more
 
     def _build_layers(self):
         """Per-layer parameter dicts, sliced once, with the projections that share an input concatenated so that a
@@ -136,10 +160,23 @@ class Qwen35DecodeEngine:
         fr = self.rope.index_select(0, self.pos_t)                                   # (1, rope_dim/2, 2)
         q = apply_rotary_emb(rms_norm(q.contiguous(), ap["q_norm"]), fr, c.gqa_rope_dim)
         k = apply_rotary_emb(rms_norm(k.contiguous(), ap["k_norm"]), fr, c.gqa_rope_dim)
-        ck, cv = self.k[gi], self.v[gi]                                              # (B, Hkv, max_len, dh)
-        ck.index_copy_(2, self.pos_t, k.permute(0, 2, 1, 3).to(ck.dtype))
-        cv.index_copy_(2, self.pos_t, v.permute(0, 2, 1, 3).to(cv.dtype))
-        o = attn_ops.attention_decode(q.reshape(B, Hq, dh), ck, cv, pos=self.pos_i32, scratch=self.dec_scratch)
+        if self.paged is not None:
+            pc = self.paged
+            row = torch.cat([k.reshape(B, 1, Hkv * dh), v.reshape(B, 1, Hkv * dh)], dim=-1).to(pc.pool.dtype)
+            if row.is_cuda:
+                pc._ops.paged_kv_write(row.contiguous(), pc.pool[gi], pc.block_table, self.seq_id_t, self.paged_lens)
+            else:
+                for b in range(B):
+                    pg, of = pc.slots(b, self.pos, 1)
+                    pc.pool[gi, pg, of] = row[b]
+            o = attn_ops.attention_decode_paged(q.reshape(B, Hq, dh), pc.pool[gi], pc.block_table, self.seq_id_t,
+                                                self.paged_lens, Hkv, len_add=1, scratch=self.dec_scratch,
+                                                max_len=self.max_len)
+        else:
+            ck, cv = self.k[gi], self.v[gi]                                          # (B, Hkv, max_len, dh)
+            ck.index_copy_(2, self.pos_t, k.permute(0, 2, 1, 3).to(ck.dtype))
+            cv.index_copy_(2, self.pos_t, v.permute(0, 2, 1, 3).to(cv.dtype))
+            o = attn_ops.attention_decode(q.reshape(B, Hq, dh), ck, cv, pos=self.pos_i32, scratch=self.dec_scratch)
         o = (o.float() * torch.sigmoid(gate[:, 0].float())).to(x.dtype)
         return self._moe(x + matmul_maybe_fp8(o.reshape(B, Hq * dh), ap["o_proj"]), lp)
 
@@ -154,6 +191,8 @@ class Qwen35DecodeEngine:
         self.next_tokens.copy_(logits.argmax(-1))
         self.pos_t.add_(1)
         self.pos_i32.add_(1)
+        if self.paged is not None:
+            self.paged_lens.add_(1)
         return logits
 
     # ---- public ---------------------------------------------------------------------------------------
@@ -179,6 +218,8 @@ class Qwen35DecodeEngine:
             self.conv.copy_(saved[1])
             self.pos_t.copy_(saved[2])
             self.pos_i32.copy_(saved[2])
+            if self.paged is not None:
+                self.paged_lens.sub_(1)
             self._graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self._graph):
                 self.logits = self._token_step()
@@ -190,6 +231,8 @@ class Qwen35DecodeEngine:
 
     def cache(self, dtype: Optional[torch.dtype] = None) -> HybridCache:
         """The state as a ``HybridCache`` (to continue with the function-style forward)."""
+        if self.paged is not None:
+            raise RuntimeError("a paged engine has no dense key / value buffers to hand back")
         dt = dtype or self.k.dtype
         return HybridCache(self.M.to(dt), self.conv.to(dt), self.k, self.v, self.pos)
 

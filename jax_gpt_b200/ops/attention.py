@@ -136,6 +136,44 @@ def attention_decode(q, cache_k, cache_v, kv_len=None, pos: Optional[torch.Tenso
     return out.view(B, H, D)
 
 
+def attention_decode_paged(q, pool, block_table, seq_ids, seq_lens, n_kv_heads: int, len_add: int = 1, scale=None,
+                           scratch=None, out=None, max_len: Optional[int] = None):
+    """One query token per sequence over a PAGED cache (cache/paged.py): ``pool`` (n_pages, page_size, 2 * Hkv * D)
+    holds K of every kv head then V per cached token, ``block_table`` (max_seqs, max_pages) the page ids,
+    ``seq_ids`` (B,) the sequence of every query row, ``seq_lens`` (max_seqs,) the committed lengths, all on the
+    device; ``len_add`` keys beyond the committed length are attended (1: the new token's row is written, the length
+    not yet advanced). q (B, H, D). Returns (B, H, D)."""
+    B, H, D = q.shape
+    Hkv = n_kv_heads
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    cuda_ok = (q.is_cuda and q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and D in (64, 128, 256)
+               and H % Hkv == 0 and (H // Hkv) in (1, 2, 4, 8) and pool.shape[-1] == 2 * Hkv * D)
+    if not cuda_ok:
+        outs = []
+        ps = pool.shape[1]
+        for b in range(B):
+            sid = int(seq_ids[b])
+            n = int(seq_lens[sid]) + len_add
+            pos = torch.arange(n, device=pool.device)
+            rows = pool[block_table[sid, (pos // ps).long()].long(), (pos % ps).long()]          # (n, 2 Hkv D)
+            kk = rows[:, :Hkv * D].reshape(1, n, Hkv, D).to(q.dtype)
+            vv = rows[:, Hkv * D:].reshape(1, n, Hkv, D).to(q.dtype)
+            outs.append(attention_ref(q[b:b + 1, None], kk, vv, causal=False, scale=scale)[:, 0])
+        return torch.cat(outs)
+    q2 = q.reshape(B, H * D)
+    if q2.stride(1) != 1 or q2.stride(0) % 8 != 0 or q2.data_ptr() % 16 != 0:
+        q2 = q2.contiguous()
+    if scratch is None:
+        S = decode_splits(B, Hkv, max_len or block_table.shape[1] * pool.shape[1])
+        scratch = (torch.empty(B, H, S, D, device=q.device, dtype=torch.float32),
+                   torch.empty(B, H, S, 2, device=q.device, dtype=torch.float32))
+    if out is None:
+        out = torch.empty(B, H * D, device=q.device, dtype=torch.bfloat16)
+    _ext.ops().attn_decode_paged(q2, pool, block_table, seq_ids, seq_lens, int(len_add), H, Hkv, scale, scratch[0],
+                                 scratch[1], out)
+    return out.view(B, H, D)
+
+
 class _AttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, scale):

@@ -112,7 +112,8 @@ def make_runner(args, device):
                 if eng is None:
                     engines.clear()
                     eng = engines[id(cache)] = Qwen35DecodeEngine(params, cfg, cache, ep=ep,
-                                                                  use_cuda_graph=not args.no_graph)
+                                                                  use_cuda_graph=not args.no_graph,
+                                                                  paged_kv=args.paged_kv)
                 return eng.step(nxt), cache
             logits, cache = forward(params, nxt[:, None], cfg, cache=cache, is_decode=True, ep_group=ep, tp_group=tp_group)
             return logits[:, -1].argmax(-1), cache
@@ -212,6 +213,8 @@ def main(argv=None):
     ap.add_argument("--experts", type=int, default=0, help="deepseek_v3: override the routed expert count")
     ap.add_argument("--engine", action="store_true", help="decode through the model family's CUDA-graph decode engine")
     ap.add_argument("--no-graph", action="store_true", help="with --engine: run the engine's step eagerly")
+    ap.add_argument("--paged-kv", action="store_true",
+                    help="qwen35 with --engine: gated-attention keys / values in a paged cache (64-token pages)")
     ap.add_argument("--prefill-reps", type=int, default=5)
     ap.add_argument("--decode-steps", type=int, default=256, help="timed decode steps (capped by the scenario)")
     ap.add_argument("--out", default="")

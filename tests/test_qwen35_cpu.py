@@ -242,6 +242,30 @@ def test_decode_engine_matches_function_style_decode(cfg, params):
         assert torch.allclose(back.gqa_k[:, :, :, :eng.pos], cache_a.gqa_k[:, :, :, :eng.pos], atol=1e-5)
 
 
+def test_decode_engine_with_paged_kv_matches_dense_engine(cfg, params):
+    """The engine with its gated-attention keys / values in a paged cache (pages, block table, per-sequence
+    lengths) produces the logits of the engine on the dense buffers, step after step."""
+    from jax_gpt_b200.models.qwen35.decode_engine import Qwen35DecodeEngine
+    torch.manual_seed(12)
+    B, T, steps = 2, 70, 5                      # 70 prompt tokens: the second 64-token page is in use
+    tok = torch.randint(0, cfg.vocab_size, (B, T))
+    with torch.no_grad():
+        ca = init_cache(cfg, B, T + steps + 2)
+        logits, ca = forward(params, tok, cfg, cache=ca)
+        cb = init_cache(cfg, B, T + steps + 2)
+        _, cb = forward(params, tok, cfg, cache=cb)
+        dense = Qwen35DecodeEngine(params, cfg, ca, use_cuda_graph=False)
+        paged = Qwen35DecodeEngine(params, cfg, cb, use_cuda_graph=False, paged_kv=True)
+        assert paged.k is None and paged.paged.length(0) == T
+        nxt = logits[:, -1].argmax(-1)
+        for _ in range(steps):
+            a = dense.step(nxt).clone()
+            b = paged.step(nxt).clone()
+            assert torch.allclose(paged.logits, dense.logits, atol=2e-4, rtol=1e-4)
+            assert torch.equal(a, b)
+            nxt = a
+
+
 def test_generate_with_engine_matches_generate(cfg, params):
     """Same continuation as ``generate`` for greedy decoding and for sampling with the same seed."""
     from jax_gpt_b200.models.qwen35.decode_engine import generate_with_engine

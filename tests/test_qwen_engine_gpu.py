@@ -68,6 +68,21 @@ with torch.no_grad():
         assert rows_close(graph_eng.M, ref_cache.delta_M, 2e-2) >= 0.9, (s, "recurrent state")
         nxt = graph_eng.next_tokens.clone()
     assert graph_eng.pos == eager_eng.pos == T + steps and int(graph_eng.pos_t) == T + steps
+    # the same engine with the gated-attention keys / values in a paged cache, captured in a graph as well: every
+    # step starts from the dense graph engine's recurrent state and is compared with it
+    _, cache_d = forward(params, tok, cfg, cache=fresh_cache(), ep_group=ep)
+    _, cache_e = forward(params, tok, cfg, cache=fresh_cache(), ep_group=ep)
+    dense_eng = Qwen35DecodeEngine(params, cfg, cache_d, ep=ep, use_cuda_graph=True)
+    paged_eng = Qwen35DecodeEngine(params, cfg, cache_e, ep=ep, use_cuda_graph=True, paged_kv=True)
+    nxt = logits[:, -1].argmax(-1)
+    for s in range(steps):
+        paged_eng.M.copy_(dense_eng.M)
+        paged_eng.conv.copy_(dense_eng.conv)
+        dense_eng.step(nxt)
+        paged_eng.step(nxt)
+        assert rows_close(paged_eng.logits, dense_eng.logits, 1e-2) >= 0.75, (s, "paged vs dense engine")
+        nxt = dense_eng.next_tokens.clone()
+    assert int(paged_eng.paged_lens[0]) == T + steps
 worst = 0.0
 torch.cuda.synchronize()
 _ext.check_status(dev)
