@@ -172,9 +172,12 @@ def main():
     ap.add_argument("--no-extra", action="store_true",
                     help="2+ GPUs: skip the expert-parallel extras (fused EP-MoE layer, Qwen3.5-style MoE training step)")
     ap.add_argument("--extra-budget-s", type=float, default=420.0, help="wall-clock limit of the extras; past it the line is printed without them")
+    ap.add_argument("--extras-child", default="", help=argparse.SUPPRESS)   # internal: run only the extras, write them to this file
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.extras_child:
+        return extras_child(args.extras_child)
 
     import torch
     import torch.distributed as dist
@@ -287,27 +290,62 @@ def main():
         }
     if world >= 2 and not args.no_extra:
         # The all-to-all paths on the same GPUs: the fused EP-MoE layer of the DeepSeek-V3 shape and a training step
-        # of the Qwen3.5-style hybrid MoE at the depth that fits N GPUs. They never endanger the headline line: a
-        # timer prints it without them if they overrun, an exception is recorded in their place.
-        done = threading.Event()
-
-        def overrun():
-            if not done.wait(args.extra_budget_s):
-                if rank == 0:
-                    out["extra"] = {"error": f"extras exceeded {args.extra_budget_s:.0f} s and were abandoned"}
-                    print(json.dumps(out), flush=True)
-                os._exit(0)
-        threading.Thread(target=overrun, daemon=True).start()
-        del state, eng, model, dev_x, dev_y
+        # of the Qwen3.5-style hybrid MoE at the depth that fits N GPUs. They run in CHILD processes (one per rank, a
+        # process group of their own), so that nothing that happens there (an error, a fault, an overrun) can cost
+        # the headline line: the parent only waits, with a time limit, and reads the child's result file.
+        import tempfile
+        del state, eng, model, dev_x, dev_y, dist_opt
+        import gc
+        gc.collect()
         torch.cuda.empty_cache()
-        extra = run_extras(device, rank, world, dist)
-        done.set()
+        dist.barrier()
+        dist.destroy_process_group()
+        path = os.path.join(tempfile.gettempdir(), f"b200_bench_extras_{os.environ.get('MASTER_PORT', '0')}.json")
+        if rank == 0 and os.path.exists(path):
+            os.remove(path)
+        # a rendezvous of the children's own: another port, and rank 0 hosts the store itself (under torchrun the
+        # workers are clients of the agent's store, which only exists on the original port)
+        env = dict(os.environ, MASTER_PORT=str(int(os.environ.get("MASTER_PORT", "29500")) + 17),
+                   TORCHELASTIC_USE_AGENT_STORE="False")
+        err = None
+        try:
+            r = subprocess.run([sys.executable, os.path.abspath(__file__), "--extras-child", path, "--gpus", str(world)],
+                               env=env, timeout=args.extra_budget_s, capture_output=True, text=True)
+            if r.returncode != 0:
+                err = f"extras exited with code {r.returncode}: {(r.stderr or '')[-300:]}"
+        except subprocess.TimeoutExpired:
+            err = f"extras exceeded {args.extra_budget_s:.0f} s and were stopped"
         if rank == 0:
-            out["extra"] = extra
+            try:
+                with open(path) as f:
+                    out["extra"] = json.load(f)
+            except Exception:
+                out["extra"] = {"error": err or "the extras left no result"}
+        print(json.dumps(out), flush=True) if rank == 0 else None
+        return 0
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    return 0
+
+
+def extras_child(path: str) -> int:
+    """Child process of one rank: own process group, the extras, rank 0 writes them to ``path``."""
+    import torch
+    import torch.distributed as dist
+    rank, local_rank, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=device)
+    extra = run_extras(device, rank, world, dist)
+    if rank == 0:
+        with open(path + ".tmp", "w") as f:
+            json.dump(extra, f)
+        os.replace(path + ".tmp", path)
+    dist.barrier()
+    dist.destroy_process_group()
     return 0
 
 
