@@ -352,7 +352,7 @@ def extras_child(path: str) -> int:
 def run_extras(device, rank, world, dist):
     """{"ep_moe_layer": ..., "qwen35_moe_train": ...}; a failed part carries {"error": ...} and the ranks agree on it."""
     import torch
-    from jax_gpt_b200.utils.bench_extras import ep_moe_layer_bench, moe_train_bench
+    from jax_gpt_b200.utils.bench_extras import ep_moe_layer_bench, moe_train_bench, tp_fused_gemm_bench
     extra = {}
 
     def guarded(name, fn):
@@ -378,6 +378,14 @@ def run_extras(device, rank, world, dist):
     guarded("qwen35_moe_train", lambda: moe_train_bench(device, rank, world, model="qwen35", layers=depth, experts=512,
                                                          seq=4096, batch=1, accum=max(1, 32 // world), lowmem=True,
                                                          steps=2, warmup=1))
+    # the fused collective + GEMM kernels (all-gather -> GEMM, GEMM -> reduce-scatter, FSDP weight gather -> GEMM)
+    # against NCCL + GEMM on the MLA output-projection shape, with their roofline fractions
+    guarded("tp_fused_gemms", lambda: tp_fused_gemm_bench(device, rank, world, rows=4096, K=7168, N=16384, warmup=2, iters=5))
+    # BASELINE config 3 at the depth that fits: DeepSeek-V3 widths, 256 experts, seq 4096, global batch 32, FP8 dense GEMMs
+    ds_depth = {2: 2, 4: 4}.get(world, 8 if world >= 8 else 2)
+    guarded("deepseek_v3_train", lambda: moe_train_bench(device, rank, world, model="deepseek_v3", layers=ds_depth,
+                                                          experts=256, seq=4096, batch=1, accum=max(1, 32 // world),
+                                                          fp8=True, lowmem=True, steps=2, warmup=1))
     return extra
 
 

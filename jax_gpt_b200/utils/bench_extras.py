@@ -186,3 +186,72 @@ def moe_train_bench(device, rank: int, world: int, model: str = "qwen35", layers
     del eng, ep, moe_layers
     torch.cuda.empty_cache()
     return res
+
+
+def tp_fused_gemm_bench(device, rank: int, world: int, rows: int = 4096, K: int = 7168, N: int = 16384, warmup: int = 3,
+                        iters: int = 10, link_gbs: float = 770.0) -> dict:
+    """The three fused collective + GEMM kernels (all-gather -> GEMM, GEMM -> reduce-scatter, FSDP weight gather ->
+    GEMM) against the same math done with a library collective around this package's plain GEMM: CUDA events, max
+    over ranks. Roofline per path: the slower of (FLOPs of this rank / measured bf16 GEMM rate) and (bytes this rank
+    must move over NVLink / ``link_gbs`` per direction); reported as bound / time."""
+    from .. import _ext
+    from ..ops.gemm import gemm
+    from ..parallel.fsdp import ShardedWeight
+    from ..parallel.tensor_parallel import TPContext, all_gather_matmul_nccl, matmul_reduce_scatter_nccl
+    from . import roofline as R
+    assert K % (world * 64) == 0 and N % (world * 128) == 0 and rows % 128 == 0
+    peaks = R.load_peaks()
+    peak, link = peaks["bf16_tflops"] * 1e12, link_gbs * 1e9
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    ctx = TPContext(device=device)
+    g = torch.Generator(device=device).manual_seed(1 + rank)
+    res = {"world": world, "rows_per_rank": rows, "K": K, "N": N, "denominators": peaks["source"], "link_gbs": link_gbs}
+
+    def report(name, ms, ms_base, flops, nvlink_bytes):
+        t_c, t_l = flops / peak * 1e3, nvlink_bytes / link * 1e3
+        res[name] = {"fused_ms": ms, "nccl_plus_gemm_ms": ms_base, "speedup": ms_base / ms, "compute_bound_ms": t_c,
+                     "nvlink_bound_ms": t_l, "roofline_fraction": max(t_c, t_l) / ms, "tflops": flops / ms / 1e9}
+
+    x_local = torch.randn(rows, K, device=device, generator=g).to(torch.bfloat16)
+    w_col = (torch.randn(K, N // world, device=device, generator=g) * 0.02).to(torch.bfloat16)
+    report("all_gather_gemm", timed(lambda: ctx.all_gather_matmul(x_local, w_col)),
+           timed(lambda: all_gather_matmul_nccl(x_local, w_col)), 2.0 * rows * world * K * (N // world),
+           2.0 * rows * (world - 1) * K)
+    x_full = torch.randn(rows * world, K // world, device=device, generator=g).to(torch.bfloat16)
+    w_row = (torch.randn(K // world, N, device=device, generator=g) * 0.02).to(torch.bfloat16)
+    report("gemm_reduce_scatter", timed(lambda: ctx.matmul_reduce_scatter(x_full, w_row)),
+           timed(lambda: matmul_reduce_scatter_nccl(x_full, w_row)), 2.0 * rows * world * (K // world) * N,
+           2.0 * rows * (world - 1) * N)        # bf16 partials
+    w_full = (torch.randn(K, N, device=device, generator=torch.Generator(device=device).manual_seed(7)) * 0.02).to(torch.bfloat16)
+    sw = ShardedWeight(ctx.comm, w_full)
+    del w_full
+
+    def base():
+        parts = torch.empty(world, K, N // world, device=device, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(parts, sw.shard)
+        out = torch.empty(rows, N, device=device, dtype=torch.bfloat16)
+        for s_ in range(world):
+            gemm(x_local, parts[s_], b_mn_major=True, out=out[:, s_ * (N // world):(s_ + 1) * (N // world)])
+        return out
+    report("sharded_weight_gemm", timed(lambda: sw.matmul(x_local)), timed(base), 2.0 * rows * K * N,
+           2.0 * K * N * (world - 1) / world)
+    torch.cuda.synchronize()
+    _ext.check_status(device)
+    return res

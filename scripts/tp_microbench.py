@@ -26,29 +26,8 @@ import torch
 import torch.distributed as dist
 
 
-def timed(fn, warmup, iters, device, world):
-    for _ in range(warmup):
-        fn()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    a.record()
-    for _ in range(iters):
-        fn()
-    b.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(b) / iters], device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t)
-
-
 def main(argv=None):
-    from jax_gpt_b200 import _ext
-    from jax_gpt_b200.parallel.fsdp import ShardedWeight
-    from jax_gpt_b200.parallel.tensor_parallel import (TPContext, all_gather_matmul_nccl, matmul_reduce_scatter_nccl)
-    from jax_gpt_b200.utils import roofline as R
+    from jax_gpt_b200.utils.bench_extras import tp_fused_gemm_bench
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--rows", type=int, default=4096, help="token rows per rank")
     ap.add_argument("--K", type=int, default=7168)
@@ -62,51 +41,8 @@ def main(argv=None):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29541")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
-    peaks = R.load_peaks()
-    peak = peaks["bf16_tflops"] * 1e12
-    link = args.link_gbs * 1e9
-    rows, K, N = args.rows, args.K, args.N
-    assert K % (world * 64) == 0 and N % (world * 128) == 0 and rows % 128 == 0
-    ctx = TPContext(device=device)
-    g = torch.Generator(device=device).manual_seed(1 + rank)
-    res = {"world": world, "rows_per_rank": rows, "K": K, "N": N, "denominators": peaks["source"], "link_gbs": args.link_gbs}
-
-    def report(name, ms, ms_base, flops, nvlink_bytes):
-        t_c, t_l = flops / peak * 1e3, nvlink_bytes / link * 1e3
-        bound = max(t_c, t_l)
-        res[name] = {"fused_ms": ms, "nccl_plus_gemm_ms": ms_base, "speedup": ms_base / ms, "compute_bound_ms": t_c,
-                     "nvlink_bound_ms": t_l, "roofline_fraction": bound / ms, "tflops": flops / ms / 1e9}
-
-    # all-gather -> GEMM
-    x_local = torch.randn(rows, K, device=device, generator=g).to(torch.bfloat16)
-    w_col = (torch.randn(K, N // world, device=device, generator=g) * 0.02).to(torch.bfloat16)
-    ms = timed(lambda: ctx.all_gather_matmul(x_local, w_col), args.warmup, args.iters, device, world)
-    mb = timed(lambda: all_gather_matmul_nccl(x_local, w_col), args.warmup, args.iters, device, world)
-    report("all_gather_gemm", ms, mb, 2.0 * rows * world * K * (N // world), 2.0 * rows * (world - 1) * K)
-    # GEMM -> reduce-scatter
-    x_full = torch.randn(rows * world, K // world, device=device, generator=g).to(torch.bfloat16)
-    w_row = (torch.randn(K // world, N, device=device, generator=g) * 0.02).to(torch.bfloat16)
-    ms = timed(lambda: ctx.matmul_reduce_scatter(x_full, w_row), args.warmup, args.iters, device, world)
-    mb = timed(lambda: matmul_reduce_scatter_nccl(x_full, w_row), args.warmup, args.iters, device, world)
-    report("gemm_reduce_scatter", ms, mb, 2.0 * rows * world * (K // world) * N, 2.0 * rows * (world - 1) * N)   # bf16 partials
-    # sharded-weight GEMM (FSDP)
-    wg = torch.Generator(device=device).manual_seed(7)
-    w_full = (torch.randn(K, N, device=device, generator=wg) * 0.02).to(torch.bfloat16)
-    sw = ShardedWeight(ctx.comm, w_full)
-    from jax_gpt_b200.ops.gemm import gemm
-
-    def base():
-        parts = torch.empty(world, K, N // world, device=device, dtype=torch.bfloat16)
-        dist.all_gather_into_tensor(parts, sw.shard)
-        out = torch.empty(rows, N, device=device, dtype=torch.bfloat16)
-        for s_ in range(world):
-            gemm(x_local, parts[s_], b_mn_major=True, out=out[:, s_ * (N // world):(s_ + 1) * (N // world)])
-        return out
-    ms = timed(lambda: sw.matmul(x_local), args.warmup, args.iters, device, world)
-    mb = timed(base, args.warmup, args.iters, device, world)
-    report("sharded_weight_gemm", ms, mb, 2.0 * rows * K * N, 2.0 * K * N * (world - 1) / world)
-    torch.cuda.synchronize()
-    _ext.check_status(device)
+    res = tp_fused_gemm_bench(device, rank, world, rows=args.rows, K=args.K, N=args.N, warmup=args.warmup, iters=args.iters,
+                              link_gbs=args.link_gbs)
     if rank == 0:
         print(json.dumps(res))
     dist.destroy_process_group()
