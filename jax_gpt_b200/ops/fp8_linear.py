@@ -25,7 +25,7 @@ from typing import Optional
 
 import torch
 
-from .rope import fp8_gemm_ref, fp8_quant_mx, mxfp8_gemm_packed
+from .fp8 import fp8_gemm_ref, fp8_quant_mx, mxfp8_gemm_packed
 
 _STATE = {"on": False}
 

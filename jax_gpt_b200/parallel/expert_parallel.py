@@ -117,7 +117,7 @@ def quantize_expert_weights_fp8(params: dict) -> dict:
     """Stacked bf16 expert weights (gate_proj / up_proj (E, D, I), down_proj (E, I, D)) -> what the FP8
     kernel reads: K-major e4m3 bytes with power-of-two 128 x 128 block scales, and the packed UE8M0
     scale chunks (csrc/moe_kernels.cuh: EpMoeFp8Args)."""
-    from ..ops.rope import fp8_quant_128x128
+    from ..ops.fp8 import fp8_quant_128x128
     gate, up, down = params["gate_proj"], params["up_proj"], params["down_proj"]
     E, D, I = gate.shape
     dev = gate.device
@@ -144,7 +144,7 @@ def quantize_expert_weights_fp8(params: dict) -> dict:
 def fp8_moe_reference(x, weights, idx, qw_full: dict) -> torch.Tensor:
     """fp32 restatement of the FP8 kernel's arithmetic with ALL experts local: 1 x 128 power-of-two
     activation quantisation, de-quantised block-scaled weights, SwiGLU, re-quantised activation."""
-    from ..ops.rope import fp8_quant_1x128_ref
+    from ..ops.fp8 import fp8_quant_1x128_ref
 
     def deq(qb, eb):  # (N, K) bytes + (N/128, K/128) exponents -> fp32 (N, K)
         sc = torch.exp2(eb.float() - 127).repeat_interleave(128, 0).repeat_interleave(128, 1)

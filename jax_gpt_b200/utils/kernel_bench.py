@@ -138,7 +138,7 @@ def main(argv=None):
         fn = lambda: misc.cross_entropy_fwd_bwd(logits, tg, V, 1.0 / M, loss=loss)
         bytes_ = 2.0 * 2 * M * V
     elif args.op == "gemm_mxfp8":
-        from ..ops import rope as Q
+        from ..ops import fp8 as Q
         M, N, K = args.M, args.N, args.K
         xq, xs = Q.fp8_quant_1x128(torch.randn(M, K, device=dev).to(torch.bfloat16), pow2=True)
         wq, ws = Q.fp8_quant_128x128(torch.randn(N, K, device=dev).to(torch.bfloat16), pow2=True)

@@ -78,7 +78,7 @@ def test_fp8_quant_mx_reference_layouts():
     """Reference side of the one-pass quantiser: the transposed form equals quantising the transposed matrix, the
     scales are powers of two, and the packed exponent bytes sit where the tensor-core GEMM reads them
     (byte (r % 32) * 16 + ((r % 128) // 32) * 4 + j of the chunk of row block r // 128 and 128-wide K block)."""
-    from jax_gpt_b200.ops.rope import fp8_gemm_ref, fp8_quant_mx
+    from jax_gpt_b200.ops.fp8 import fp8_gemm_ref, fp8_quant_mx
     torch.manual_seed(3)
     x = (torch.randn(256, 384) * torch.logspace(-1, 1, 384)[None, :]).to(torch.bfloat16)
     for block in (False, True):

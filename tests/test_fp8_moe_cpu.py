@@ -3,7 +3,7 @@ preparation, the fp32 restatement of the kernel's quantised arithmetic, the nati
 import pytest
 import torch
 
-from jax_gpt_b200.ops import rope as Q
+from jax_gpt_b200.ops import fp8 as Q
 
 
 def test_packed_scale_layout_per_row_and_per_block():

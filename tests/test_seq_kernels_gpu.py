@@ -65,7 +65,7 @@ def test_rmsnorm_rope(cuda_device, dh, rope, norm):
 
 @pytest.mark.parametrize("pow2", [False, True])
 def test_fp8_block_quant(cuda_device, pow2):
-    from jax_gpt_b200.ops import rope as RP
+    from jax_gpt_b200.ops import fp8 as RP
     torch.manual_seed(3)
     x = (torch.randn(300, 512, device=cuda_device) * torch.rand(300, 1, device=cuda_device) * 5).to(torch.bfloat16)
     q, sc = RP.fp8_quant_1x128(x, pow2)
@@ -116,7 +116,7 @@ def test_gdn_decode_step(cuda_device):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 256, 512), (1024, 2048, 7168), (4096, 4096, 2048)])
 def test_fp8_blockscaled_gemm(cuda_device, M, N, K):
-    from jax_gpt_b200.ops import rope as RP
+    from jax_gpt_b200.ops import fp8 as RP
     torch.manual_seed(5)
     x = (torch.randn(M, K, device=cuda_device) * (torch.rand(M, 1, device=cuda_device) * 3 + 0.1)).to(torch.bfloat16)
     w = (torch.randn(N, K, device=cuda_device) * 0.05).to(torch.bfloat16)
@@ -168,7 +168,7 @@ def test_mla_paged_decode_and_paged_write(cuda_device, heads, n_splits):
 def test_mxfp8_gemm_hardware_block_scales(cuda_device, M, N, K):
     """tcgen05 block-scaled MMA (UE8M0 scales in TMEM) vs the de-quantised fp32 product."""
     from jax_gpt_b200 import _ext
-    from jax_gpt_b200.ops import rope as Q
+    from jax_gpt_b200.ops import fp8 as Q
     torch.manual_seed(3)
     x = (torch.randn(M, K, device=cuda_device) * torch.rand(M, 1, device=cuda_device) * 4).to(torch.bfloat16)
     w = (torch.randn(N, K, device=cuda_device) * 0.05).to(torch.bfloat16)
@@ -463,7 +463,7 @@ def test_fp8_linear_training_path_on_gpu(cuda_device):
 def test_fp8_quant_mx_kernel_matches_reference(cuda_device, transpose, block):
     """One-pass quantise (+ transpose) + packed exponent bytes against the reference functions: same e4m3 bytes,
     same power-of-two scales, same packed layout."""
-    from jax_gpt_b200.ops import rope as R
+    from jax_gpt_b200.ops import fp8 as R
     torch.manual_seed(6)
     x = (torch.randn(384, 256) * torch.logspace(-2, 2, 256)[None, :]).to(torch.bfloat16)
     q, sf, sc = R.fp8_quant_mx(x.to(cuda_device), transpose, block)
