@@ -169,6 +169,9 @@ def main():
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--overlap", action="store_true", help="several GPUs: reduce-scatter each layer's gradients during backward")
+    ap.add_argument("--multimem", action="store_true",
+                    help="several GPUs: the optimizer kernel reduces and broadcasts through NVSwitch multicast (multimem.ld_reduce / "
+                         "multimem.st) instead of peer loads and stores")
     ap.add_argument("--no-extra", action="store_true",
                     help="2+ GPUs: skip the expert-parallel extras (fused EP-MoE layer, Qwen3.5-style MoE training step)")
     ap.add_argument("--extra-budget-s", type=float, default=420.0, help="wall-clock limit of the extras; past it the line is printed without them")
@@ -205,7 +208,7 @@ def main():
     dist_opt = None
     if world > 1:
         from jax_gpt_b200.parallel.fsdp import FusedShardedAdamW
-        dist_opt = FusedShardedAdamW(dist.group.WORLD, device)
+        dist_opt = FusedShardedAdamW(dist.group.WORLD, device, use_multimem=args.multimem)
     state = create_train_state(model, create_optimizer(model, tc), train_config=tc, device=device,
                                dist_optimizer=dist_opt)
     eng = state.engine
@@ -280,7 +283,7 @@ def main():
                        "l2": "per-step working set (~7 GB of activations and logits) exceeds the 126 MB L2; no flush",
                        "cuda_graph": not args.no_graph,
                        "grad_reduce": ("per-layer reduce-scatter kernels on a side stream during backward" if world > 1 and args.overlap
-                                       else ("inside the fused optimizer kernel after backward" if world > 1 else "none (1 GPU)"))},
+                                       else (("inside the fused optimizer kernel after backward" + (" (multimem)" if args.multimem else "")) if world > 1 else "none (1 GPU)"))},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": 2 * B * T * 4, "d2h_bytes_per_step": 4,
