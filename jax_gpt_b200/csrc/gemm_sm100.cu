@@ -113,7 +113,10 @@ __device__ void stage_copier(const StageCopy& sc, uint8_t* ring, int ring_bytes,
   };
   const int n_units = sc.n_remote * sc.units_per_src;
   for (int u = idx; u < n_units && ok; u += n_workers) {
-    const int i = u / sc.n_remote, j = u % sc.n_remote;      // unit-major: every peer gets its early units early
+    // peer-major: the whole shard goes to the peer that needs it first (the rank before this one, whose compute
+    // CTAs visit this rank's rows right after their own), then to the one before that, and so on: every consumer
+    // receives from one source at a time, in the order in which it consumes
+    const int j = u / sc.units_per_src, i = u % sc.units_per_src;
     const unsigned char* src = sc.src + static_cast<long long>(i) * sc.bytes_per_unit;
     unsigned char* dst = sc.dst[j] + static_cast<long long>(i) * sc.bytes_per_unit;
     for (long long off = 0; off < sc.bytes_per_unit && ok; off += slot_bytes) {
@@ -156,7 +159,7 @@ __device__ void stage_copier_ldst(const StageCopy& sc, int idx, int n_workers) {
   const int n_units = sc.n_remote * sc.units_per_src;
   const long long n16 = sc.bytes_per_unit / 16;
   for (int u = idx; u < n_units; u += n_workers) {
-    const int i = u / sc.n_remote, j = u % sc.n_remote;
+    const int j = u / sc.units_per_src, i = u % sc.units_per_src;
     const uint4* src = reinterpret_cast<const uint4*>(sc.src + static_cast<long long>(i) * sc.bytes_per_unit);
     uint4* dst = reinterpret_cast<uint4*>(sc.dst[j] + static_cast<long long>(i) * sc.bytes_per_unit);
     long long k = t;
@@ -624,7 +627,7 @@ void fill_stage_copy(StageCopy* sc, int n_src, int rank, int epoch, double wait_
   sc->epoch = epoch;
   sc->wait_ns = static_cast<unsigned long long>((wait_seconds > 0 ? wait_seconds : 20.0) * 1e9);
   sc->ready = peer_ready[rank];
-  for (int j = 0; j < n_src - 1; ++j) sc->peer_ready[j] = peer_ready[(rank + 1 + j) % n_src];
+  for (int j = 0; j < n_src - 1; ++j) sc->peer_ready[j] = peer_ready[(rank + n_src - 1 - j) % n_src];   // see stage_copier
 }
 
 }  // namespace
@@ -646,7 +649,7 @@ cudaError_t launch_gemm_bf16_gathered_a_staged(__nv_bfloat16* const* peer_gather
   sc.my_unit0 = rank * sc.units_per_src;
   sc.src = reinterpret_cast<const unsigned char*>(peer_gather[rank] + rank * slice);
   for (int j = 0; j < n_src - 1; ++j)
-    sc.dst[j] = reinterpret_cast<unsigned char*>(peer_gather[(rank + 1 + j) % n_src] + rank * slice);
+    sc.dst[j] = reinterpret_cast<unsigned char*>(peer_gather[(rank + n_src - 1 - j) % n_src] + rank * slice);
   return launch_common(srcs, n_src, rows_per_src, rank, K, 0, B, ldb, b_major, args, stream, nullptr, 1, 0, &sc);
 }
 
@@ -674,7 +677,7 @@ cudaError_t launch_gemm_bf16_sharded_b_staged(const __nv_bfloat16* A, int64_t ld
   sc.my_unit0 = rank * sc.units_per_src;
   sc.src = reinterpret_cast<const unsigned char*>(peer_w[rank] + rank * shard);
   for (int j = 0; j < n_src - 1; ++j)
-    sc.dst[j] = reinterpret_cast<unsigned char*>(peer_w[(rank + 1 + j) % n_src] + rank * shard);
+    sc.dst[j] = reinterpret_cast<unsigned char*>(peer_w[(rank + n_src - 1 - j) % n_src] + rank * shard);
   const __nv_bfloat16* srcs[1] = {A};
   return launch_common(srcs, 1, 0, 0, lda, 0, nullptr, n_per, 1, args, stream, b_srcs, n_src, rank, &sc);
 }

@@ -151,4 +151,13 @@ class Fp8Linear:
         return fp8_gemm(xq, xs, self.w_q, self.w_s).reshape(*shp[:-1], self.out_features)
 
 
-from .fp8_linear import fp8_eligible, fp8_enabled, fp8_linear, fp8_training  # noqa: E402,F401
+_TRAINING_NAMES = ("fp8_eligible", "fp8_enabled", "fp8_linear", "fp8_training")
+
+
+def __getattr__(name):
+    """The training path lives in ops/fp8_linear.py, which imports this module: its names are resolved on first use
+    instead of at import time, so that either module may be imported first."""
+    if name in _TRAINING_NAMES:
+        from . import fp8_linear
+        return getattr(fp8_linear, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
