@@ -294,3 +294,24 @@ def test_adamw_with_bf16_state_is_unbiased(cuda_device):
     p2, m2, v2, g2 = p0.clone(), m0.clone(), v0.clone(), g.clone()
     misc.adamw_bf16_state(p2, g2, m2, v2, hp, None, wd=0.1, seed=124)
     assert not torch.equal(p, p2)
+
+
+def test_grouped_matmul_without_host_sync_matches_the_loop(cuda_device):
+    """The single-device MoE fallback with device-side group sizes (one grouped GEMM, nothing read back to the host)
+    against the loop of per-group GEMMs, values and gradients, with an empty group."""
+    from jax_gpt_b200.ops.grouped_gemm import grouped_swiglu
+    torch.manual_seed(21)
+    E, D, I = 6, 128, 64
+    sizes = torch.tensor([40, 0, 17, 128, 3, 60], device=cuda_device)
+    R = int(sizes.sum())
+    mk = lambda *sh: (torch.randn(*sh, device=cuda_device) * 0.2).to(torch.bfloat16)
+    x0, g0, u0, d0 = mk(R, D), mk(E, D, I), mk(E, D, I), mk(E, I, D)
+    dy = mk(R, D)
+    outs = []
+    for sz in (sizes, sizes.tolist()):
+        leaves = [t.clone().requires_grad_() for t in (x0, g0, u0, d0)]
+        y = grouped_swiglu(leaves[0], sz, leaves[1], leaves[2], leaves[3])
+        y.backward(dy)
+        outs.append([y.detach()] + [t.grad for t in leaves])
+    for a, b in zip(*outs):
+        assert _rel_err(a, b) < 2e-2
