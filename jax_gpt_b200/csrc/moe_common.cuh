@@ -15,11 +15,11 @@ struct MoeTables {
   int send_off[kMoeMaxExperts];      // first row of MY pairs for global expert e in its destination buffer
   int rows[kMoeMaxLocalExperts];     // rows received per local expert
   int base[kMoeMaxLocalExperts];     // first row of the local expert in this rank's receive buffer
-  // Static tile order. Backward: tile0[el] is the first tile of local expert el. Forward: the order is cut into
-  // n_slots = EL + lag slots, slot s holding the GEMM1 (gate|up) tiles of expert s followed by the GEMM2 (down)
-  // tiles of expert s - lag; tile0[s] is the first tile of slot s. The lag keeps about two rounds of tiles
-  // between an expert's GEMM1 tiles and the GEMM2 tiles that wait for them, so that CTAs working side by side
-  // in the order do not stall on one another.
+  // Static tile order, cut into n_slots = EL + lag slots; tile0[s] is the first tile of slot s. Forward: slot s
+  // holds the GEMM1 (gate|up) tiles of expert s followed by the GEMM2 (down) tiles of expert s - lag. Backward:
+  // slot s holds the dAct and dW_down tiles of expert s followed by the dX and dW_gate|up tiles of expert s - lag
+  // (the ones that wait for that expert's dAct tiles). The lag keeps about two rounds of tiles between producer
+  // and consumer tiles, so that CTAs working side by side in the order do not stall on one another.
   int tile0[2 * kMoeMaxLocalExperts + 1];
   int lag, n_slots;
   int mt0[kMoeMaxLocalExperts + 1];    // first m-tile index of the local expert
@@ -41,6 +41,9 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
 }
 __device__ __forceinline__ void red_release_sys_add_u32(unsigned* p, unsigned v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_relaxed_sys_add_u32(unsigned* p, unsigned v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Bounded wait until *p (cumulative counter) has reached `target` (wrap-safe signed difference).
@@ -103,7 +106,6 @@ __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb
     int b = 0, t = 0, m = 0;
     for (int el = 0; el < EL; ++el) {
       tb->base[el] = b;
-      if (backward) tb->tile0[el] = t;
       tb->mt0[el] = m;
       const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
       b += (tb->rows[el] + pad - 1) / pad * pad;
@@ -116,25 +118,27 @@ __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb
       m += mt;
     }
     tb->mt0[EL] = m;
-    if (backward) {
-      tb->tile0[EL] = t;
-      tb->lag = 0;
-      tb->n_slots = EL;
-    } else {
-      // lag (in experts) worth about two rounds of the grid's CTAs at the average number of tiles per expert
-      int lag = (2 * static_cast<int>(gridDim.x) * EL + (t > 0 ? t : 1) - 1) / (t > 0 ? t : 1);
-      lag = lag < 1 ? 1 : (lag > EL ? EL : lag);
-      const int n_slots = EL + lag;
-      int u = 0;
-      for (int sl = 0; sl < n_slots; ++sl) {
-        tb->tile0[sl] = u;
-        if (sl < EL) u += ((tb->rows[sl] + kMoeBM - 1) / kMoeBM) * n1;
-        if (sl >= lag) u += ((tb->rows[sl - lag] + kMoeBM - 1) / kMoeBM) * n2;
+    // lag (in experts) worth about two rounds of the grid's CTAs at the average number of tiles per expert
+    int lag = (2 * static_cast<int>(gridDim.x) * EL + (t > 0 ? t : 1) - 1) / (t > 0 ? t : 1);
+    lag = lag < 1 ? 1 : (lag > EL ? EL : lag);
+    const int n_slots = EL + lag;
+    int u = 0;
+    for (int sl = 0; sl < n_slots; ++sl) {
+      tb->tile0[sl] = u;
+      if (sl < EL) {
+        const int mt = (tb->rows[sl] + kMoeBM - 1) / kMoeBM;
+        if (!backward) u += mt * n1;
+        else if (mt > 0) u += mt * (a.inter / kMoeBN) + (a.inter / kMoeBM) * n2;
       }
-      tb->tile0[n_slots] = u;
-      tb->lag = lag;
-      tb->n_slots = n_slots;
+      if (sl >= lag) {
+        const int mt = (tb->rows[sl - lag] + kMoeBM - 1) / kMoeBM;
+        if (!backward) u += mt * n2;
+        else if (mt > 0) u += mt * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
+      }
     }
+    tb->tile0[n_slots] = u;
+    tb->lag = lag;
+    tb->n_slots = n_slots;
   }
   __syncthreads();
 }

@@ -26,6 +26,8 @@
 
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "comm_device.cuh"
 #include "common.cuh"
 #include "moe_common.cuh"
@@ -41,6 +43,10 @@ constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 192;
+constexpr int kCopyBatch = 8;  // 16-byte loads a lane keeps in flight while it copies a token row
+
+// per-CTA phase timelines of the last profiled launch: [0] forward, [1] backward
+__device__ long long g_moe_prof[2][kMoeProfCtas * kMoeProfFields];
 
 struct MoeBars {
   uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
@@ -97,6 +103,12 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  long long* prof = (a.prof != nullptr && blockIdx.x < kMoeProfCtas) ? a.prof + blockIdx.x * kMoeProfFields : nullptr;
+  long long prof_clk0 = 0;
+  if (prof && threadIdx.x == 0) {
+    prof[0] = static_cast<long long>(globaltimer_ns());
+    prof_clk0 = clock64();
+  }
 
   // ---- 1. publish this rank's counts, wait for everybody's ----
   {
@@ -121,30 +133,48 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     alive = false;
   }
 
+  if (prof && threadIdx.x == 0) prof[1] = static_cast<long long>(globaltimer_ns());
+
   // ---- 2. dispatch: one warp per (token, expert) pair ----
   if (alive) {
-    const int n_pairs = a.tokens * a.top_k;
-    for (int p = blockIdx.x * (kThreads / 32) + warp; p < n_pairs; p += gridDim.x * (kThreads / 32)) {
+    const int n_pairs = a.tokens * a.top_k, nv = D / 8;
+    const int w0 = blockIdx.x * (kThreads / 32) + warp, wstep = gridDim.x * (kThreads / 32);
+    for (int p = w0; p < n_pairs; p += wstep) {
       const int e = a.idx[p];
-      const int dst = e / EL, el = e - dst * EL;
+      const int dst = e / EL;
       const int slot = tb->send_off[e] + a.pos[p];
       if (!bounds_ok(e, ET, a.status, 201) || !bounds_ok(slot, a.cap_rows, a.status, 202)) continue;
       const int tok = p / a.top_k;
       const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<int64_t>(tok) * D);
       uint4* out = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
-      for (int i = lane; i < D / 8; i += 32) out[i] = src[i];
+      for (int i0 = lane; i0 < nv; i0 += 32 * kCopyBatch) {  // all loads of a batch in flight before the first store
+        uint4 v[kCopyBatch];
+#pragma unroll
+        for (int u = 0; u < kCopyBatch; ++u)
+          if (i0 + 32 * u < nv) v[u] = __ldg(src + i0 + 32 * u);
+#pragma unroll
+        for (int u = 0; u < kCopyBatch; ++u)
+          if (i0 + 32 * u < nv) out[i0 + 32 * u] = v[u];
+      }
       if (lane == 0) {
         a.peer_recv_meta[dst][slot] = (a.rank << 24) | p;  // source rank and (token, choice) pair
         a.peer_recv_w[dst][slot] = a.w[p];
         a.slot_out[p] = slot;
       }
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_system();
-        red_release_sys_add_u32(a.peer_arrive[dst] + el, 1u);
-      }
+    }
+    // one fence for all rows this warp delivered, then their arrival counts (lane l signs for the warp's pairs
+    // l, l + 32, ...): barrier -> fence -> relaxed reduction is a release sequence over every lane's stores
+    __syncwarp();
+    __threadfence_system();
+    int j = 0;
+    for (int p = w0; p < n_pairs; p += wstep, ++j) {
+      if ((j & 31) != lane) continue;
+      const int e = a.idx[p];
+      if (e < 0 || e >= ET || tb->send_off[e] + a.pos[p] >= a.cap_rows) continue;  // skipped (and reported) above
+      red_relaxed_sys_add_u32(a.peer_arrive[e / EL] + (e % EL), 1u);
     }
   }
+  if (prof && threadIdx.x == 0) prof[2] = static_cast<long long>(globaltimer_ns());
 
   // ---- 3./4. grouped GEMMs over the local experts ----
   const int num_tiles = alive ? tb->tile0[tb->n_slots] : 0;
@@ -155,8 +185,10 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       uint32_t phase = 0;
       int ready_el = -1;
       bool ok = true;
+      long long dep_clk = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const TileInfo ti = decode_tile(a, tb, t);
+        const long long c_dep = prof ? clock64() : 0;
         if (ti.phase == 0) {
           if (ti.el != ready_el) {
             const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(tb->rows[ti.el]);
@@ -173,6 +205,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
             break;
           }
         }
+        if (prof) dep_clk += clock64() - c_dep;
         fence_proxy_async_global();
         const int row0 = tb->base[ti.el] + ti.m * BM;
         const int nkb = (ti.phase == 0 ? D : I) / BK;
@@ -205,6 +238,10 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
           }
         }
       }
+      if (prof) {
+        prof[3] = static_cast<long long>(globaltimer_ns());
+        prof[5] = dep_clk;
+      }
       if (!ok || *abort_flag) {
         for (int s = 0; s < kStages; ++s) {
           const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
@@ -220,21 +257,26 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     int stage = 0, iter = 0;
     uint32_t phase = 0;
     bool ok = true;
+    long long full_clk = 0, tmem_clk = 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
       const TileInfo ti = decode_tile(a, tb, t);
       const int acc = iter & 1;
+      const long long c_t = prof ? clock64() : 0;
       if (!mbar_wait(&bars->tmem_empty[acc], ((iter >> 1) & 1) ^ 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitTmemEmptyTimeout, 44, blockIdx.x, t);
         break;
       }
+      if (prof) tmem_clk += clock64() - c_t;
       tc_fence_after();
       const int nkb = (ti.phase == 0 ? D : I) / BK;
       for (int kb = 0; kb < nkb; ++kb) {
+        const long long c_f = prof ? clock64() : 0;
         if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
           if (lane == 0) report_status(a.status, kWaitFullTimeout, 45, blockIdx.x, t);
           ok = false;
           break;
         }
+        if (prof) full_clk += clock64() - c_f;
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb = sa + kABytes;
@@ -252,6 +294,10 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       }
       if (ok && lane == 0) tc_commit(&bars->tmem_full[acc]);
       __syncwarp();
+    }
+    if (prof && lane == 0) {
+      prof[6] = full_clk;
+      prof[7] = tmem_clk;
     }
   } else {
     const int q = warp & 3;
@@ -346,6 +392,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
         if (ti.phase == 0) atomicAdd(a.act_ready + tb->mt0[ti.el] + ti.m, 1);
       }
     }
+    if (prof && warp == 2 && lane == 0) prof[8] = static_cast<long long>(globaltimer_ns());
   }
 
   // ---- 5. every rank's contributions have landed before anybody returns ----
@@ -367,41 +414,61 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     }
     if (threadIdx.x == 0) my->epoch = epoch;
   }
+  if (prof && threadIdx.x == 0) {
+    prof[4] = static_cast<long long>(globaltimer_ns());
+    prof[9] = clock64() - prof_clk0;
+  }
 }
 
 
 // ------------------------------------------------------------------------------------------------
-// Backward. Tile order per local expert (rows > 0):
+// Backward. Tiles of a local expert (rows > 0):
 //   Q0  dAct = dYw W_down^T  (+ SwiGLU backward -> dGU, <dAct, act> per row)      mt x I/256 tiles
-//   Q1  dX   = dGU [W_gate | W_up]^T, pushed to the token owners                     mt x D/256
 //   Q2  dW_down += act^T dYw          (ragged K = the expert's rows, 64-row blocks)  I/128 x D/256
+//   Q1  dX   = dGU [W_gate | W_up]^T, pushed to the token owners                     mt x D/256
 //   Q3  dW_gate | dW_up += X^T dGU    (ragged K)                                     D/128 x 2I/256
-// Q1 waits for the Q0 tiles of its m-tile, Q3 for all Q0 tiles of its expert; both dependencies
-// point backwards in the static order.
+// Q1 waits for the Q0 tiles of its m-tile, Q3 for all Q0 tiles of its expert. Slot s of the static order holds
+// Q0 and Q2 of expert s, then Q1 and Q3 of expert s - lag: the dependencies point backwards by about two rounds
+// of the grid, so a CTA rarely reaches a dependent tile before the tiles it needs are done.
 struct BwdTile {
   int el, phase, m, n;
 };
 
 __device__ __forceinline__ BwdTile decode_bwd_tile(const EpMoeArgs& a, const MoeTables* tb, int t) {
-  int el = 0, hi = a.e_local - 1;  // first expert whose tile range ends after t
-  while (el < hi) {
-    const int mid = (el + hi) >> 1;
+  int sl = 0, hi = tb->n_slots - 1;  // first slot whose tile range ends after t
+  while (sl < hi) {
+    const int mid = (sl + hi) >> 1;
     if (tb->tile0[mid + 1] > t) hi = mid;
-    else el = mid + 1;
+    else sl = mid + 1;
   }
-  const int mt = (tb->rows[el] + BM - 1) / BM;
-  const int c0 = mt * (a.inter / BN), c1 = mt * (a.d_model / BN), c2 = (a.inter / BM) * (a.d_model / BN);
-  int r = t - tb->tile0[el];
+  int r = t - tb->tile0[sl];
+  const int n2 = a.d_model / BN;
   BwdTile ti;
-  ti.el = el;
-  if (r < c0) {
-    ti.phase = 0; ti.m = r % mt; ti.n = r / mt;
-  } else if (r < c0 + c1) {
-    r -= c0; ti.phase = 1; ti.m = r % mt; ti.n = r / mt;
-  } else if (r < c0 + c1 + c2) {
-    r -= c0 + c1; ti.phase = 2; ti.m = r % (a.inter / BM); ti.n = r / (a.inter / BM);
+  int front = 0;
+  if (sl < a.e_local) {
+    const int mt = (tb->rows[sl] + BM - 1) / BM;
+    if (mt > 0) {
+      const int c0 = mt * (a.inter / BN);
+      front = c0 + (a.inter / BM) * n2;
+      if (r < c0) {
+        ti.el = sl; ti.phase = 0; ti.m = r % mt; ti.n = r / mt;
+        return ti;
+      }
+      if (r < front) {
+        r -= c0;
+        ti.el = sl; ti.phase = 2; ti.m = r % (a.inter / BM); ti.n = r / (a.inter / BM);
+        return ti;
+      }
+    }
+  }
+  r -= front;
+  ti.el = sl - tb->lag;
+  const int mt = (tb->rows[ti.el] + BM - 1) / BM;
+  const int c1 = mt * n2;
+  if (r < c1) {
+    ti.phase = 1; ti.m = r % mt; ti.n = r / mt;
   } else {
-    r -= c0 + c1 + c2; ti.phase = 3; ti.m = r % (a.d_model / BM); ti.n = r / (a.d_model / BM);
+    r -= c1; ti.phase = 3; ti.m = r % (a.d_model / BM); ti.n = r / (a.d_model / BM);
   }
   return ti;
 }
@@ -446,6 +513,12 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gthreads = gridDim.x * blockDim.x;
+  long long* prof = (a.prof != nullptr && blockIdx.x < kMoeProfCtas) ? a.prof + blockIdx.x * kMoeProfFields : nullptr;
+  long long prof_clk0 = 0;
+  if (prof && threadIdx.x == 0) {
+    prof[0] = static_cast<long long>(globaltimer_ns());
+    prof_clk0 = clock64();
+  }
 
   // ---- 1. counts exchange (same protocol as forward), zero the per-launch counters ----
   {
@@ -471,6 +544,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
     if (alive && blockIdx.x == 0 && threadIdx.x == 0) report_status(a.status, kBadArgument, 50, a.cap_rows, 0);
     alive = false;
   }
+  if (prof && threadIdx.x == 0) prof[1] = static_cast<long long>(globaltimer_ns());
 
   // ---- 2. keep the padding rows of the receive buffers zero (nobody else writes them) ----
   if (alive) {
@@ -490,32 +564,47 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
   // ---- 3. dispatch the routing-weighted dout rows to the slots the forward pass used (the x rows, the
   //         routing metadata, act and the pre-activations are still in place from the forward launch) ----
   if (alive) {
-    const int n_pairs = a.tokens * a.top_k;
-    for (int p = blockIdx.x * (kThreads / 32) + warp; p < n_pairs; p += gridDim.x * (kThreads / 32)) {
+    const int n_pairs = a.tokens * a.top_k, nv = D / 8;
+    const int w0 = blockIdx.x * (kThreads / 32) + warp, wstep = gridDim.x * (kThreads / 32);
+    for (int p = w0; p < n_pairs; p += wstep) {
       const int e = a.idx[p];
-      const int dst = e / EL, el = e - dst * EL;
+      const int dst = e / EL;
       const int slot = tb->send_off[e] + a.pos[p];
       const int tok = p / a.top_k;
       const float wp = a.w[p];
       const uint4* sy = reinterpret_cast<const uint4*>(a.dout + static_cast<int64_t>(tok) * D);
       uint4* oy = reinterpret_cast<uint4*>(a.peer_recv_dy[dst] + static_cast<int64_t>(slot) * D);
-      for (int i = lane; i < D / 8; i += 32) {
-        const uint4 v = sy[i];
-        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
-        oy[i] = make_uint4(pack_bf16x2(f0.x * wp, f0.y * wp), pack_bf16x2(f1.x * wp, f1.y * wp),
-                           pack_bf16x2(f2.x * wp, f2.y * wp), pack_bf16x2(f3.x * wp, f3.y * wp));
-      }
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_system();
-        red_release_sys_add_u32(a.peer_arrive[dst] + el, 1u);
+      for (int i0 = lane; i0 < nv; i0 += 32 * kCopyBatch) {  // all loads of a batch in flight before the first store
+        uint4 v[kCopyBatch];
+#pragma unroll
+        for (int u = 0; u < kCopyBatch; ++u)
+          if (i0 + 32 * u < nv) v[u] = __ldg(sy + i0 + 32 * u);
+#pragma unroll
+        for (int u = 0; u < kCopyBatch; ++u) {
+          if (i0 + 32 * u < nv) {
+            const float2 f0 = unpack_bf16x2(v[u].x), f1 = unpack_bf16x2(v[u].y), f2 = unpack_bf16x2(v[u].z), f3 = unpack_bf16x2(v[u].w);
+            oy[i0 + 32 * u] = make_uint4(pack_bf16x2(f0.x * wp, f0.y * wp), pack_bf16x2(f1.x * wp, f1.y * wp),
+                                         pack_bf16x2(f2.x * wp, f2.y * wp), pack_bf16x2(f3.x * wp, f3.y * wp));
+          }
+        }
       }
     }
+    // one fence for all rows this warp delivered, then their arrival counts (lane l signs for the warp's pairs
+    // l, l + 32, ...): barrier -> fence -> relaxed reduction is a release sequence over every lane's stores
+    __syncwarp();
+    __threadfence_system();
+    int j = 0;
+    for (int p = w0; p < n_pairs; p += wstep, ++j) {
+      if ((j & 31) != lane) continue;
+      const int e = a.idx[p];
+      red_relaxed_sys_add_u32(a.peer_arrive[e / EL] + (e % EL), 1u);
+    }
   }
+  if (prof && threadIdx.x == 0) prof[2] = static_cast<long long>(globaltimer_ns());
   __threadfence();  // the zeroed padding rows are visible before any tile reads them
   grid.sync();
 
-  const int num_tiles = alive ? tb->tile0[EL] : 0;
+  const int num_tiles = alive ? tb->tile0[tb->n_slots] : 0;
   const unsigned q0_per_mtile = 4u * (I / BN);
   if (warp == 0) {
     if (lane == 0) {
@@ -523,11 +612,15 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       uint32_t phase = 0;
       int ready_el = -1;
       bool ok = true;
+      long long dep_clk = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const BwdTile ti = decode_bwd_tile(a, tb, t);
         const int rows = tb->rows[ti.el], base = tb->base[ti.el];
         const int mt = (rows + BM - 1) / BM;
-        if (ti.el != ready_el) {
+        const long long c_dep = prof ? clock64() : 0;
+        if ((ti.phase == 0 || ti.phase == 2) && ti.el != ready_el) {
+          // the dy rows of this expert have arrived (Q1 / Q3 read only what the Q0 tiles they wait for produced,
+          // and the x rows of the forward launch)
           const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(rows);
           if (!wait_counter_ge<true>(a.peer_arrive[a.rank] + ti.el, target, a.wait_budget_ns, abort_flag)) {
             report_status(a.status, kWaitFlagTimeout, 51, ti.el, t);
@@ -548,6 +641,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
             break;
           }
         }
+        if (prof) dep_clk += clock64() - c_dep;
         fence_proxy_async_global();
         const int nkb = ti.phase == 0 ? D / BK : (ti.phase == 1 ? 2 * I / BK : ((rows + 63) & ~63) / BK);
         for (int kb = 0; kb < nkb; ++kb) {
@@ -582,6 +676,10 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
           }
         }
       }
+      if (prof) {
+        prof[3] = static_cast<long long>(globaltimer_ns());
+        prof[5] = dep_clk;
+      }
       if (!ok || *abort_flag) {
         for (int s = 0; s < kStages; ++s) {
           const uint32_t armed = (s < stage) ? phase : (phase ^ 1);
@@ -598,23 +696,28 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
     int stage = 0, iter = 0;
     uint32_t phase = 0;
     bool ok = true;
+    long long full_clk = 0, tmem_clk = 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
       const BwdTile ti = decode_bwd_tile(a, tb, t);
       const int acc = iter & 1;
+      const long long c_t = prof ? clock64() : 0;
       if (!mbar_wait(&bars->tmem_empty[acc], ((iter >> 1) & 1) ^ 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitTmemEmptyTimeout, 55, blockIdx.x, t);
         break;
       }
+      if (prof) tmem_clk += clock64() - c_t;
       tc_fence_after();
       const int rows = tb->rows[ti.el];
       const int nkb = ti.phase == 0 ? D / BK : (ti.phase == 1 ? 2 * I / BK : ((rows + 63) & ~63) / BK);
       const bool mn = ti.phase >= 2;
       for (int kb = 0; kb < nkb; ++kb) {
+        const long long c_f = prof ? clock64() : 0;
         if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
           if (lane == 0) report_status(a.status, kWaitFullTimeout, 56, blockIdx.x, t);
           ok = false;
           break;
         }
+        if (prof) full_clk += clock64() - c_f;
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb = sa + kABytes;
@@ -634,6 +737,10 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       }
       if (ok && lane == 0) tc_commit(&bars->tmem_full[acc]);
       __syncwarp();
+    }
+    if (prof && lane == 0) {
+      prof[6] = full_clk;
+      prof[7] = tmem_clk;
     }
   } else {
     const int q = warp & 3;
@@ -727,14 +834,19 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
           __syncwarp();
         }
       } else {
-        // weight-gradient tiles: every row of the tile is a real weight row; accumulate in fp32
-        const int r = ti.m * BM + q * 32 + lane;
+        // weight-gradient tiles: every row of the tile is a real weight row; accumulate in fp32. Each lane holds
+        // one row of the accumulator; the chunk is transposed through shared memory so that eight lanes add
+        // 128 contiguous bytes of one weight row (whole sectors per reduction instead of 16-byte pieces).
         float* dst;
+        int64_t ld;
         if (ti.phase == 2) {
-          dst = a.d_down + (static_cast<int64_t>(ti.el) * I + r) * D + ti.n * BN;
+          ld = D;
+          dst = a.d_down + (static_cast<int64_t>(ti.el) * I + ti.m * BM + q * 32) * D + ti.n * BN;
         } else {
           const int col0 = ti.n * BN;
-          dst = (col0 < I ? a.d_gate : a.d_up) + (static_cast<int64_t>(ti.el) * D + r) * I + (col0 < I ? col0 : col0 - I);
+          ld = I;
+          dst = (col0 < I ? a.d_gate : a.d_up) + (static_cast<int64_t>(ti.el) * D + ti.m * BM + q * 32) * I +
+                (col0 < I ? col0 : col0 - I);
         }
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -742,11 +854,17 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
           tmem_ld_32x32(tacc + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 32 + j),
-                         "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])),
-                         "f"(__uint_as_float(v[j + 3]))
+          for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __uint_as_float(v[j]);
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 32; rr += 4) {
+            const int r2 = rr + (lane >> 3), c2 = (lane & 7) * 4;
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + r2 * ld + c * 32 + c2),
+                         "f"(stg[r2 * 33 + c2]), "f"(stg[r2 * 33 + c2 + 1]), "f"(stg[r2 * 33 + c2 + 2]),
+                         "f"(stg[r2 * 33 + c2 + 3])
                          : "memory");
+          }
+          __syncwarp();
         }
       }
       tc_fence_before();
@@ -763,6 +881,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
         }
       }
     }
+    if (prof && warp == 2 && lane == 0) prof[8] = static_cast<long long>(globaltimer_ns());
   }
 
   tc_fence_before();
@@ -799,9 +918,33 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
     }
     if (threadIdx.x == 0) my->epoch = epoch;
   }
+  if (prof && threadIdx.x == 0) {
+    prof[4] = static_cast<long long>(globaltimer_ns());
+    prof[9] = clock64() - prof_clk0;
+  }
 }
 
 }  // namespace
+
+namespace {
+// Address of the timeline buffer when B200_MOE_PROFILE=1 was set before the first launch, else nullptr.
+long long* moe_prof_buffer(int which) {
+  static int enabled = -1;
+  static long long* base = nullptr;
+  if (enabled < 0) {
+    const char* env = getenv("B200_MOE_PROFILE");
+    enabled = (env != nullptr && env[0] == '1') ? 1 : 0;
+    if (enabled && cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_moe_prof) != cudaSuccess) enabled = 0;
+  }
+  return enabled ? base + which * kMoeProfCtas * kMoeProfFields : nullptr;
+}
+}  // namespace
+
+cudaError_t moe_profile_read(int which, long long* host_out) {
+  if (which < 0 || which > 1) return cudaErrorInvalidValue;
+  return cudaMemcpyFromSymbol(host_out, g_moe_prof, sizeof(long long) * kMoeProfCtas * kMoeProfFields,
+                              sizeof(long long) * which * kMoeProfCtas * kMoeProfFields, cudaMemcpyDeviceToHost);
+}
 
 cudaError_t launch_moe_prepare(const int* idx, int n_pairs, int n_experts, int* counts, int* pos, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * n_experts, st);
@@ -836,6 +979,7 @@ cudaError_t launch_ep_moe_forward(const EpMoeArgs& args, const __nv_bfloat16* ga
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   EpMoeArgs args_copy = args;
+  args_copy.prof = moe_prof_buffer(0);
   void* params[] = {&t_recv, &t_act, &t_gate, &t_up, &t_down, &args_copy};
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ep_moe_forward_kernel), dim3(sms), dim3(kThreads), params,
                                      kSmemBytes, st);
@@ -870,6 +1014,7 @@ cudaError_t launch_ep_moe_backward(const EpMoeArgs& args, const __nv_bfloat16* g
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   EpMoeArgs args_copy = args;
+  args_copy.prof = moe_prof_buffer(1);
   void* params[] = {&tm, &args_copy};
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ep_moe_backward_kernel), dim3(sms), dim3(kThreads), params,
                                      kSmemBytes, st);

@@ -56,7 +56,16 @@ struct EpMoeArgs {
   float* d_down;                               // [e_local, inter, d_model]
   uint64_t wait_budget_ns;
   int* status;
+  long long* prof;  // set by the launchers: per-CTA phase timeline of this launch (kMoeProfFields per CTA), or nullptr
 };
+
+// Phase timeline of the bf16 forward (which = 0) / backward (which = 1) kernel, recorded when the environment
+// variable B200_MOE_PROFILE=1 is set before the first launch. Per CTA: [0] start, [1] tables built, [2] own
+// dispatch done, [3] last tile's loads issued, [4] end (all globaltimer ns), [5] SM cycles the load warp waited on
+// dependencies (arrivals, earlier tiles), [6] cycles the MMA warp waited for operands, [7] cycles it waited for a
+// free accumulator, [8] ns when the epilogue finished its last tile, [9] SM cycles from [0] to [4].
+constexpr int kMoeProfCtas = 160, kMoeProfFields = 10;
+cudaError_t moe_profile_read(int which, long long* host_out);  // host_out[kMoeProfCtas * kMoeProfFields]
 
 // counts[e] = number of pairs routed to global expert e; pos[p] = rank of pair p within its expert.
 cudaError_t launch_moe_prepare(const int* idx, int n_pairs, int n_experts, int* counts, int* pos, cudaStream_t st);

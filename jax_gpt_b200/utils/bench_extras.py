@@ -65,6 +65,8 @@ def ep_moe_layer_bench(device, rank: int, world: int, tokens: int = 4096, d_mode
     rows = fused.rows_out.sum().item()
     res = {"world": world, "tokens_per_rank": T, "router": router, "d_model": D, "inter": I, "experts": E, "top_k": k,
            "dtype": "bf16", "fused_fwd_ms": ms_fused, "rows_this_rank": rows}
+    if moe_phase_timeline(0) is not None:
+        res["fwd_timeline_us"] = moe_phase_timeline(0)
     if backward:
         dout = torch.randn(T, D, device=device, generator=gen).to(torch.bfloat16)
         grads = {n: torch.zeros_like(t, dtype=torch.float32) for n, t in local.items()}
@@ -73,6 +75,8 @@ def ep_moe_layer_bench(device, rank: int, world: int, tokens: int = 4096, d_mode
         _ext.check_status(device)
         res["fused_bwd_ms"] = ms_bwd
         res["bwd_tflops_this_rank"] = 2.0 * rows * 6 * D * I / ms_bwd / 1e9
+        if moe_phase_timeline(1) is not None:
+            res["bwd_timeline_us"] = moe_phase_timeline(1)
         del grads
     if fp8:
         from ..parallel.expert_parallel import FusedEPMoEFp8, quantize_expert_weights_fp8
@@ -111,6 +115,29 @@ def ep_moe_layer_bench(device, rank: int, world: int, tokens: int = 4096, d_mode
     del fused, local
     torch.cuda.empty_cache()
     return res
+
+
+def moe_phase_timeline(which: int) -> Optional[dict]:
+    """Summary (microseconds; median and max over the CTAs) of the phase timeline the fused MoE forward
+    (``which`` = 0) or backward (1) kernel recorded on its last launch; None unless ``B200_MOE_PROFILE=1`` was set
+    before the first launch. Wait columns are SM cycles converted with the launch's own cycles-per-nanosecond."""
+    import os
+    from .. import _ext
+    if os.environ.get("B200_MOE_PROFILE", "0") != "1":
+        return None
+    p = _ext.ops().moe_profile(which).double()
+    p = p[p[:, 0] > 0]
+    if p.numel() == 0:
+        return None
+    start = p[:, 0].min()
+    us = lambda col: {"median": round(((p[:, col] - start).median() / 1e3).item(), 1),
+                      "max": round(((p[:, col] - start).max() / 1e3).item(), 1)}
+    cyc_per_ns = (p[:, 9] / (p[:, 4] - p[:, 0]).clamp_min(1.0)).median().item()
+    wait = lambda col: {"median": round((p[:, col] / cyc_per_ns / 1e3).median().item(), 1),
+                        "max": round((p[:, col] / cyc_per_ns / 1e3).max().item(), 1)}
+    return {"ctas": int(p.shape[0]), "sm_mhz": round(cyc_per_ns * 1e3), "tables_built": us(1), "dispatch_done": us(2),
+            "loads_issued": us(3), "epilogue_done": us(8), "end": us(4), "load_warp_dependency_wait": wait(5),
+            "mma_operand_wait": wait(6), "mma_accumulator_wait": wait(7)}
 
 
 def moe_train_bench(device, rank: int, world: int, model: str = "qwen35", layers: int = 4, experts: int = 64,
