@@ -66,7 +66,8 @@ __device__ __forceinline__ bool wait_counter_ge(const unsigned* p, unsigned targ
 
 // Fills the shared-memory tables from the all-gathered count matrix counts[src][e].
 template <class Args>
-__device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb, bool backward = false, int pad = 64) {
+__device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb, bool backward = false, int pad = 64,
+                             int claim_ahead = 0) {
   const int W = a.world, EL = a.e_local, ET = W * EL;
   if (threadIdx.x == 0) tb->overflow = 0;
   __syncthreads();
@@ -103,23 +104,39 @@ __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb
   __syncthreads();
   if (threadIdx.x == 0) {
     const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
+    // Cost of a tile in 64-deep K blocks, plus a few blocks' worth of epilogue: the tiles other tiles wait for
+    // (GEMM1 / dAct, full-depth K) take longer than the average tile, and the lag has to cover their duration.
+    const float c_over = 6.f;
+    const float c_prod = a.d_model / 64 + c_over + (backward ? 4.f : 0.f);
+    float cost = 0.f;
     int b = 0, t = 0, m = 0;
     for (int el = 0; el < EL; ++el) {
       tb->base[el] = b;
       tb->mt0[el] = m;
       const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
-      b += (tb->rows[el] + pad - 1) / pad * pad;
+      const int padded = (tb->rows[el] + pad - 1) / pad * pad;
+      b += padded;
       if (!backward) {
         t += mt * (n1 + n2);
+        cost += mt * (n1 * c_prod + n2 * (a.inter / 64 + c_over));
       } else if (mt > 0) {
         // dAct tiles, dX tiles, dW_down tiles, dW_gate|up tiles
-        t += mt * (a.inter / kMoeBN) + mt * n2 + (a.inter / kMoeBM) * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
+        const int q0 = mt * (a.inter / kMoeBN), q1 = mt * n2;
+        const int q23 = (a.inter / kMoeBM) * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
+        t += q0 + q1 + q23;
+        cost += q0 * c_prod + q1 * (2 * a.inter / 64 + c_over) + q23 * (padded / 64 + c_over);
       }
       m += mt;
     }
     tb->mt0[EL] = m;
-    // lag (in experts) worth about two rounds of the grid's CTAs at the average number of tiles per expert
-    int lag = (2 * static_cast<int>(gridDim.x) * EL + (t > 0 ? t : 1) - 1) / (t > 0 ? t : 1);
+    // Lag in experts: while one producer tile runs, the grid claims about gridDim.x * (its cost / average cost)
+    // tiles; three times that, plus the tiles the CTAs claim ahead of their load warps, at the average number
+    // of tiles per expert.
+    int lag = 1;
+    if (t > 0) {
+      const float lag_tiles = static_cast<float>(gridDim.x) * (3.f * c_prod * t / cost + claim_ahead);
+      lag = static_cast<int>(lag_tiles * EL / t) + 1;
+    }
     lag = lag < 1 ? 1 : (lag > EL ? EL : lag);
     const int n_slots = EL + lag;
     int u = 0;

@@ -42,17 +42,35 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;  // warp 0 loads, 1 issues MMAs, 2-5 run the epilogue, 6 schedules tiles
 constexpr int kCopyBatch = 8;  // 16-byte loads a lane keeps in flight while it copies a token row
 
 // per-CTA phase timelines of the last profiled launch: [0] forward, [1] backward
 __device__ long long g_moe_prof[2][kMoeProfCtas * kMoeProfFields];
 
+constexpr int kTileQ = 16;      // ring of claimed tile ids read by the load, MMA and epilogue warps
+constexpr int kSchedAhead = 2;  // tiles the scheduler warp may hold ready ahead of the load warp
 struct MoeBars {
   uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+  uint64_t sched_full[kSchedAhead], sched_empty[kSchedAhead];
   uint32_t tmem_base;
   int abort_flag;
+  // Entry i % kTileQ holds the i-th tile this CTA claimed, or -1 after the last one. The scheduler warp writes it
+  // once the tile's dependencies are met and arrives on sched_full; the load warp reads it after that wait, the
+  // MMA warp after the tile's first operand wait and the epilogue after the accumulator wait. The scheduler runs
+  // at most kSchedAhead tiles ahead of the load warp, which runs at most kStages tiles ahead of the MMA warp,
+  // which runs at most two accumulators ahead of the epilogue: an entry is overwritten kTileQ claims later,
+  // after its last reader.
+  volatile int tile_q[kTileQ];
 };
+
+// Next unclaimed tile of the running forward [0] / backward [1] launch. The persistent CTAs take tiles in the
+// static order from this counter (a CTA that finishes a cheap tile takes the next one instead of idling beside a
+// CTA on an expensive tile). A scheduler warp per CTA claims the tile, waits for its dependencies (arrival
+// counters, earlier tiles) and only then hands it to the load warp: the claim's and the flags' round trips to L2
+// stay off the path that feeds the tensor cores. Each kernel needs every SM's shared memory, so two launches never overlap on a
+// device and one counter per kernel suffices; block 0 zeroes it before the grid barrier that precedes the tiles.
+__device__ int g_moe_tile_counter[2];
 
 constexpr int kStageBufBytes = 4 * 32 * 33 * 4;  // per-epilogue-warp transposition buffers
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(MoeTables) + sizeof(MoeBars) + 64 + kStageBufBytes;
@@ -92,6 +110,10 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       mbar_init(&bars->tmem_full[i], 1);
       mbar_init(&bars->tmem_empty[i], 4);
     }
+    for (int i = 0; i < kSchedAhead; ++i) {
+      mbar_init(&bars->sched_full[i], 1);
+      mbar_init(&bars->sched_empty[i], 1);
+    }
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -116,7 +138,10 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < max_mt; i += gridDim.x * blockDim.x) a.act_ready[i] = 0;
   }
   if (blockIdx.x == 0) {
-    if (threadIdx.x == 0) my->abort_flag = 0;
+    if (threadIdx.x == 0) {
+      my->abort_flag = 0;
+      g_moe_tile_counter[0] = 0;
+    }
     for (int i = threadIdx.x; i < ET; i += blockDim.x) {
       const int c = a.my_counts[i];
       for (int p = 0; p < W; ++p) a.peer_counts[p][a.rank * ET + i] = c;
@@ -127,7 +152,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   __threadfence();
   grid.sync();
   bool alive = (*reinterpret_cast<volatile int*>(&my->abort_flag) == 0);
-  build_tables(a, a.peer_counts[a.rank], tb);
+  build_tables(a, a.peer_counts[a.rank], tb, /*backward=*/false, /*pad=*/64, /*claim_ahead=*/kSchedAhead);
   if (tb->overflow) {
     if (alive && blockIdx.x == 0 && threadIdx.x == 0) report_status(a.status, kBadArgument, 40, a.cap_rows, 0);
     alive = false;
@@ -139,27 +164,61 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   if (alive) {
     const int n_pairs = a.tokens * a.top_k, nv = D / 8;
     const int w0 = blockIdx.x * (kThreads / 32) + warp, wstep = gridDim.x * (kThreads / 32);
-    for (int p = w0; p < n_pairs; p += wstep) {
-      const int e = a.idx[p];
-      const int dst = e / EL;
-      const int slot = tb->send_off[e] + a.pos[p];
-      if (!bounds_ok(e, ET, a.status, 201) || !bounds_ok(slot, a.cap_rows, a.status, 202)) continue;
-      const int tok = p / a.top_k;
-      const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<int64_t>(tok) * D);
-      uint4* out = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
-      for (int i0 = lane; i0 < nv; i0 += 32 * kCopyBatch) {  // all loads of a batch in flight before the first store
-        uint4 v[kCopyBatch];
+    // two rows per pass (twice the loads in flight); the routing entries of the next pass are fetched before
+    // this pass's rows so that their latency hides behind the copy
+    int e_nx[2], pos_nx[2];
+    float w_nx[2];
 #pragma unroll
-        for (int u = 0; u < kCopyBatch; ++u)
-          if (i0 + 32 * u < nv) v[u] = __ldg(src + i0 + 32 * u);
+    for (int h = 0; h < 2; ++h) {
+      const int pp = w0 + h * wstep;
+      e_nx[h] = pp < n_pairs ? a.idx[pp] : 0;
+      pos_nx[h] = pp < n_pairs ? a.pos[pp] : 0;
+      w_nx[h] = pp < n_pairs ? a.w[pp] : 0.f;
+    }
+    for (int p = w0; p < n_pairs; p += 2 * wstep) {
+      const uint4* src[2] = {nullptr, nullptr};
+      uint4* out[2] = {nullptr, nullptr};
+      int e_cur[2], pos_cur[2];
+      float w_cur[2];
 #pragma unroll
-        for (int u = 0; u < kCopyBatch; ++u)
-          if (i0 + 32 * u < nv) out[i0 + 32 * u] = v[u];
+      for (int h = 0; h < 2; ++h) {
+        e_cur[h] = e_nx[h];
+        pos_cur[h] = pos_nx[h];
+        w_cur[h] = w_nx[h];
+        const int pn = p + (2 + h) * wstep;
+        e_nx[h] = pn < n_pairs ? a.idx[pn] : 0;
+        pos_nx[h] = pn < n_pairs ? a.pos[pn] : 0;
+        w_nx[h] = pn < n_pairs ? a.w[pn] : 0.f;
       }
-      if (lane == 0) {
-        a.peer_recv_meta[dst][slot] = (a.rank << 24) | p;  // source rank and (token, choice) pair
-        a.peer_recv_w[dst][slot] = a.w[p];
-        a.slot_out[p] = slot;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int pp = p + h * wstep;
+        if (pp >= n_pairs) continue;
+        const int e = e_cur[h];
+        if (!bounds_ok(e, ET, a.status, 201)) continue;
+        const int dst = e / EL;
+        const int slot = tb->send_off[e] + pos_cur[h];
+        if (!bounds_ok(slot, a.cap_rows, a.status, 202)) continue;
+        src[h] = reinterpret_cast<const uint4*>(a.x + static_cast<int64_t>(pp / a.top_k) * D);
+        out[h] = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
+        if (lane == 0) {
+          a.peer_recv_meta[dst][slot] = (a.rank << 24) | pp;  // source rank and (token, choice) pair
+          a.peer_recv_w[dst][slot] = w_cur[h];
+          a.slot_out[pp] = slot;
+        }
+      }
+      for (int i0 = lane; i0 < nv; i0 += 32 * kCopyBatch) {  // all loads of a batch in flight before the first store
+        uint4 v[2][kCopyBatch];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int u = 0; u < kCopyBatch; ++u)
+            if (src[h] != nullptr && i0 + 32 * u < nv) v[h][u] = __ldg(src[h] + i0 + 32 * u);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int u = 0; u < kCopyBatch; ++u)
+            if (src[h] != nullptr && i0 + 32 * u < nv) out[h][i0 + 32 * u] = v[h][u];
       }
     }
     // one fence for all rows this warp delivered, then their arrival counts (lane l signs for the warp's pairs
@@ -183,29 +242,20 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      int ready_el = -1;
       bool ok = true;
       long long dep_clk = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const TileInfo ti = decode_tile(a, tb, t);
+      for (int iter = 0; ok; ++iter) {
+        const int sl = iter & (kSchedAhead - 1);
         const long long c_dep = prof ? clock64() : 0;
-        if (ti.phase == 0) {
-          if (ti.el != ready_el) {
-            const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(tb->rows[ti.el]);
-            if (!wait_counter_ge<true>(a.peer_arrive[a.rank] + ti.el, target, a.wait_budget_ns, abort_flag)) {
-              report_status(a.status, kWaitFlagTimeout, 41, ti.el, t);
-              break;
-            }
-            ready_el = ti.el;
-          }
-        } else {
-          const unsigned* ready = reinterpret_cast<const unsigned*>(a.act_ready) + tb->mt0[ti.el] + ti.m;
-          if (!wait_counter_ge<false>(ready, 4u * n1, a.wait_budget_ns, abort_flag)) {
-            report_status(a.status, kWaitFlagTimeout, 42, ti.el, t);
-            break;
-          }
-        }
+        if (!mbar_wait(&bars->sched_full[sl], (iter / kSchedAhead) & 1, abort_flag)) break;
         if (prof) dep_clk += clock64() - c_dep;
+        const int t = bars->tile_q[iter & (kTileQ - 1)];
+        mbar_arrive(&bars->sched_empty[sl]);
+        if (t < 0) {  // end mark through the same pipeline
+          if (mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag)) mbar_arrive(&bars->full[stage]);
+          break;
+        }
+        const TileInfo ti = decode_tile(a, tb, t);
         fence_proxy_async_global();
         const int row0 = tb->base[ti.el] + ti.m * BM;
         const int nkb = (ti.phase == 0 ? D : I) / BK;
@@ -258,25 +308,39 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     uint32_t phase = 0;
     bool ok = true;
     long long full_clk = 0, tmem_clk = 0;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
-      const TileInfo ti = decode_tile(a, tb, t);
+    for (; ok; ++iter) {
       const int acc = iter & 1;
+      // the first operands of the next tile (or the end mark) are in; its id was written before them
+      const long long c_f0 = prof ? clock64() : 0;
+      if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 45, blockIdx.x, iter);
+        break;
+      }
+      if (prof) full_clk += clock64() - c_f0;
+      const int t = bars->tile_q[iter & (kTileQ - 1)];
       const long long c_t = prof ? clock64() : 0;
       if (!mbar_wait(&bars->tmem_empty[acc], ((iter >> 1) & 1) ^ 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitTmemEmptyTimeout, 44, blockIdx.x, t);
         break;
       }
       if (prof) tmem_clk += clock64() - c_t;
+      if (t < 0) {  // hand the end mark on to the epilogue warps
+        if (lane == 0) mbar_arrive(&bars->tmem_full[acc]);
+        break;
+      }
+      const TileInfo ti = decode_tile(a, tb, t);
       tc_fence_after();
       const int nkb = (ti.phase == 0 ? D : I) / BK;
       for (int kb = 0; kb < nkb; ++kb) {
-        const long long c_f = prof ? clock64() : 0;
-        if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
-          if (lane == 0) report_status(a.status, kWaitFullTimeout, 45, blockIdx.x, t);
-          ok = false;
-          break;
+        if (kb > 0) {
+          const long long c_f = prof ? clock64() : 0;
+          if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+            if (lane == 0) report_status(a.status, kWaitFullTimeout, 45, blockIdx.x, t);
+            ok = false;
+            break;
+          }
+          if (prof) full_clk += clock64() - c_f;
         }
-        if (prof) full_clk += clock64() - c_f;
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb = sa + kABytes;
@@ -299,16 +363,51 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       prof[6] = full_clk;
       prof[7] = tmem_clk;
     }
+  } else if (warp == 6) {
+    if (lane == 0) {
+      int ready_el = -1;
+      for (int i = 0;; ++i) {
+        const int sl = i & (kSchedAhead - 1);
+        if (!mbar_wait(&bars->sched_empty[sl], ((i / kSchedAhead) & 1) ^ 1, abort_flag)) break;
+        const int t = atomicAdd(&g_moe_tile_counter[0], 1);
+        if (t >= num_tiles) {
+          bars->tile_q[i & (kTileQ - 1)] = -1;
+          mbar_arrive(&bars->sched_full[sl]);
+          break;
+        }
+        const TileInfo ti = decode_tile(a, tb, t);
+        if (ti.phase == 0) {
+          if (ti.el != ready_el) {
+            const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(tb->rows[ti.el]);
+            if (!wait_counter_ge<true>(a.peer_arrive[a.rank] + ti.el, target, a.wait_budget_ns, abort_flag)) {
+              report_status(a.status, kWaitFlagTimeout, 41, ti.el, t);
+              break;
+            }
+            ready_el = ti.el;
+          }
+        } else {
+          const unsigned* ready = reinterpret_cast<const unsigned*>(a.act_ready) + tb->mt0[ti.el] + ti.m;
+          if (!wait_counter_ge<false>(ready, 4u * n1, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 42, ti.el, t);
+            break;
+          }
+        }
+        bars->tile_q[i & (kTileQ - 1)] = t;
+        mbar_arrive(&bars->sched_full[sl]);
+      }
+    }
   } else {
     const int q = warp & 3;
     int iter = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++iter) {
-      const TileInfo ti = decode_tile(a, tb, t);
+    for (;; ++iter) {
       const int acc = iter & 1;
       if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 46, blockIdx.x, t);
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 46, blockIdx.x, iter);
         break;
       }
+      const int t = bars->tile_q[iter & (kTileQ - 1)];
+      if (t < 0) break;
+      const TileInfo ti = decode_tile(a, tb, t);
       tc_fence_after();
       const int r = ti.m * BM + q * 32 + lane;            // row within the expert
       const bool row_ok = r < tb->rows[ti.el];
@@ -501,6 +600,10 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       mbar_init(&bars->tmem_full[i], 1);
       mbar_init(&bars->tmem_empty[i], 4);
     }
+    for (int i = 0; i < kSchedAhead; ++i) {
+      mbar_init(&bars->sched_full[i], 1);
+      mbar_init(&bars->sched_empty[i], 1);
+    }
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -528,7 +631,10 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
     for (int i = gtid; i < a.cap_rows; i += gthreads) a.dw_rows[i] = 0.f;
   }
   if (blockIdx.x == 0) {
-    if (threadIdx.x == 0) my->abort_flag = 0;
+    if (threadIdx.x == 0) {
+      my->abort_flag = 0;
+      g_moe_tile_counter[1] = 0;
+    }
     for (int i = threadIdx.x; i < ET; i += blockDim.x) {
       const int c = a.my_counts[i];
       for (int p = 0; p < W; ++p) a.peer_counts[p][a.rank * ET + i] = c;
@@ -539,7 +645,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
   __threadfence();
   grid.sync();
   bool alive = (*reinterpret_cast<volatile int*>(&my->abort_flag) == 0);
-  build_tables(a, a.peer_counts[a.rank], tb, /*backward=*/true);
+  build_tables(a, a.peer_counts[a.rank], tb, /*backward=*/true, /*pad=*/64, /*claim_ahead=*/kSchedAhead);
   if (tb->overflow) {
     if (alive && blockIdx.x == 0 && threadIdx.x == 0) report_status(a.status, kBadArgument, 50, a.cap_rows, 0);
     alive = false;
@@ -566,25 +672,58 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
   if (alive) {
     const int n_pairs = a.tokens * a.top_k, nv = D / 8;
     const int w0 = blockIdx.x * (kThreads / 32) + warp, wstep = gridDim.x * (kThreads / 32);
-    for (int p = w0; p < n_pairs; p += wstep) {
-      const int e = a.idx[p];
-      const int dst = e / EL;
-      const int slot = tb->send_off[e] + a.pos[p];
-      const int tok = p / a.top_k;
-      const float wp = a.w[p];
-      const uint4* sy = reinterpret_cast<const uint4*>(a.dout + static_cast<int64_t>(tok) * D);
-      uint4* oy = reinterpret_cast<uint4*>(a.peer_recv_dy[dst] + static_cast<int64_t>(slot) * D);
+    // two rows per pass (twice the loads in flight); the routing entries of the next pass are fetched before
+    // this pass's rows so that their latency hides behind the copy
+    int e_nx[2], pos_nx[2];
+    float w_nx[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int pp = w0 + h * wstep;
+      e_nx[h] = pp < n_pairs ? a.idx[pp] : 0;
+      pos_nx[h] = pp < n_pairs ? a.pos[pp] : 0;
+      w_nx[h] = pp < n_pairs ? a.w[pp] : 0.f;
+    }
+    for (int p = w0; p < n_pairs; p += 2 * wstep) {
+      const uint4* sy[2] = {nullptr, nullptr};
+      uint4* oy[2] = {nullptr, nullptr};
+      float wp[2] = {0.f, 0.f};
+      int e_cur[2], pos_cur[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        e_cur[h] = e_nx[h];
+        pos_cur[h] = pos_nx[h];
+        wp[h] = w_nx[h];
+        const int pn = p + (2 + h) * wstep;
+        e_nx[h] = pn < n_pairs ? a.idx[pn] : 0;
+        pos_nx[h] = pn < n_pairs ? a.pos[pn] : 0;
+        w_nx[h] = pn < n_pairs ? a.w[pn] : 0.f;
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int pp = p + h * wstep;
+        if (pp >= n_pairs) continue;
+        const int e = e_cur[h];
+        const int slot = tb->send_off[e] + pos_cur[h];
+        sy[h] = reinterpret_cast<const uint4*>(a.dout + static_cast<int64_t>(pp / a.top_k) * D);
+        oy[h] = reinterpret_cast<uint4*>(a.peer_recv_dy[e / EL] + static_cast<int64_t>(slot) * D);
+      }
       for (int i0 = lane; i0 < nv; i0 += 32 * kCopyBatch) {  // all loads of a batch in flight before the first store
-        uint4 v[kCopyBatch];
+        uint4 v[2][kCopyBatch];
 #pragma unroll
-        for (int u = 0; u < kCopyBatch; ++u)
-          if (i0 + 32 * u < nv) v[u] = __ldg(sy + i0 + 32 * u);
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int u = 0; u < kCopyBatch; ++u) {
-          if (i0 + 32 * u < nv) {
-            const float2 f0 = unpack_bf16x2(v[u].x), f1 = unpack_bf16x2(v[u].y), f2 = unpack_bf16x2(v[u].z), f3 = unpack_bf16x2(v[u].w);
-            oy[i0 + 32 * u] = make_uint4(pack_bf16x2(f0.x * wp, f0.y * wp), pack_bf16x2(f1.x * wp, f1.y * wp),
-                                         pack_bf16x2(f2.x * wp, f2.y * wp), pack_bf16x2(f3.x * wp, f3.y * wp));
+          for (int u = 0; u < kCopyBatch; ++u)
+            if (sy[h] != nullptr && i0 + 32 * u < nv) v[h][u] = __ldg(sy[h] + i0 + 32 * u);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int u = 0; u < kCopyBatch; ++u) {
+            if (sy[h] != nullptr && i0 + 32 * u < nv) {
+              const uint4 x4 = v[h][u];
+              const float2 f0 = unpack_bf16x2(x4.x), f1 = unpack_bf16x2(x4.y), f2 = unpack_bf16x2(x4.z), f3 = unpack_bf16x2(x4.w);
+              oy[h][i0 + 32 * u] = make_uint4(pack_bf16x2(f0.x * wp[h], f0.y * wp[h]), pack_bf16x2(f1.x * wp[h], f1.y * wp[h]),
+                                              pack_bf16x2(f2.x * wp[h], f2.y * wp[h]), pack_bf16x2(f3.x * wp[h], f3.y * wp[h]));
+            }
           }
         }
       }
@@ -610,38 +749,21 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      int ready_el = -1;
       bool ok = true;
       long long dep_clk = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int iter = 0; ok; ++iter) {
+        const int sl = iter & (kSchedAhead - 1);
+        const long long c_dep = prof ? clock64() : 0;
+        if (!mbar_wait(&bars->sched_full[sl], (iter / kSchedAhead) & 1, abort_flag)) break;
+        if (prof) dep_clk += clock64() - c_dep;
+        const int t = bars->tile_q[iter & (kTileQ - 1)];
+        mbar_arrive(&bars->sched_empty[sl]);
+        if (t < 0) {  // end mark through the same pipeline
+          if (mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag)) mbar_arrive(&bars->full[stage]);
+          break;
+        }
         const BwdTile ti = decode_bwd_tile(a, tb, t);
         const int rows = tb->rows[ti.el], base = tb->base[ti.el];
-        const int mt = (rows + BM - 1) / BM;
-        const long long c_dep = prof ? clock64() : 0;
-        if ((ti.phase == 0 || ti.phase == 2) && ti.el != ready_el) {
-          // the dy rows of this expert have arrived (Q1 / Q3 read only what the Q0 tiles they wait for produced,
-          // and the x rows of the forward launch)
-          const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(rows);
-          if (!wait_counter_ge<true>(a.peer_arrive[a.rank] + ti.el, target, a.wait_budget_ns, abort_flag)) {
-            report_status(a.status, kWaitFlagTimeout, 51, ti.el, t);
-            break;
-          }
-          ready_el = ti.el;
-        }
-        if (ti.phase == 1) {
-          const unsigned* ready = reinterpret_cast<const unsigned*>(a.gu_ready) + tb->mt0[ti.el] + ti.m;
-          if (!wait_counter_ge<false>(ready, q0_per_mtile, a.wait_budget_ns, abort_flag)) {
-            report_status(a.status, kWaitFlagTimeout, 52, ti.el, t);
-            break;
-          }
-        } else if (ti.phase == 3) {
-          const unsigned* done = reinterpret_cast<const unsigned*>(a.expert_done) + ti.el;
-          if (!wait_counter_ge<false>(done, q0_per_mtile * mt, a.wait_budget_ns, abort_flag)) {
-            report_status(a.status, kWaitFlagTimeout, 53, ti.el, t);
-            break;
-          }
-        }
-        if (prof) dep_clk += clock64() - c_dep;
         fence_proxy_async_global();
         const int nkb = ti.phase == 0 ? D / BK : (ti.phase == 1 ? 2 * I / BK : ((rows + 63) & ~63) / BK);
         for (int kb = 0; kb < nkb; ++kb) {
@@ -697,27 +819,41 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
     uint32_t phase = 0;
     bool ok = true;
     long long full_clk = 0, tmem_clk = 0;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
-      const BwdTile ti = decode_bwd_tile(a, tb, t);
+    for (; ok; ++iter) {
       const int acc = iter & 1;
+      // the first operands of the next tile (or the end mark) are in; its id was written before them
+      const long long c_f0 = prof ? clock64() : 0;
+      if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+        if (lane == 0) report_status(a.status, kWaitFullTimeout, 56, blockIdx.x, iter);
+        break;
+      }
+      if (prof) full_clk += clock64() - c_f0;
+      const int t = bars->tile_q[iter & (kTileQ - 1)];
       const long long c_t = prof ? clock64() : 0;
       if (!mbar_wait(&bars->tmem_empty[acc], ((iter >> 1) & 1) ^ 1, abort_flag)) {
         if (lane == 0) report_status(a.status, kWaitTmemEmptyTimeout, 55, blockIdx.x, t);
         break;
       }
       if (prof) tmem_clk += clock64() - c_t;
+      if (t < 0) {  // hand the end mark on to the epilogue warps
+        if (lane == 0) mbar_arrive(&bars->tmem_full[acc]);
+        break;
+      }
+      const BwdTile ti = decode_bwd_tile(a, tb, t);
       tc_fence_after();
       const int rows = tb->rows[ti.el];
       const int nkb = ti.phase == 0 ? D / BK : (ti.phase == 1 ? 2 * I / BK : ((rows + 63) & ~63) / BK);
       const bool mn = ti.phase >= 2;
       for (int kb = 0; kb < nkb; ++kb) {
-        const long long c_f = prof ? clock64() : 0;
-        if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
-          if (lane == 0) report_status(a.status, kWaitFullTimeout, 56, blockIdx.x, t);
-          ok = false;
-          break;
+        if (kb > 0) {
+          const long long c_f = prof ? clock64() : 0;
+          if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+            if (lane == 0) report_status(a.status, kWaitFullTimeout, 56, blockIdx.x, t);
+            ok = false;
+            break;
+          }
+          if (prof) full_clk += clock64() - c_f;
         }
-        if (prof) full_clk += clock64() - c_f;
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sa = smem_u32(smem + stage * kStageBytes), sb = sa + kABytes;
@@ -742,18 +878,62 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       prof[6] = full_clk;
       prof[7] = tmem_clk;
     }
+  } else if (warp == 6) {
+    if (lane == 0) {
+      int ready_el = -1;
+      for (int i = 0;; ++i) {
+        const int sl = i & (kSchedAhead - 1);
+        if (!mbar_wait(&bars->sched_empty[sl], ((i / kSchedAhead) & 1) ^ 1, abort_flag)) break;
+        const int t = atomicAdd(&g_moe_tile_counter[1], 1);
+        if (t >= num_tiles) {
+          bars->tile_q[i & (kTileQ - 1)] = -1;
+          mbar_arrive(&bars->sched_full[sl]);
+          break;
+        }
+        const BwdTile ti = decode_bwd_tile(a, tb, t);
+        const int rows = tb->rows[ti.el];
+        const int mt = (rows + BM - 1) / BM;
+        if ((ti.phase == 0 || ti.phase == 2) && ti.el != ready_el) {
+          // the dy rows of this expert have arrived (Q1 / Q3 read only what the Q0 tiles they wait for produced,
+          // and the x rows of the forward launch)
+          const unsigned target = a.arrive_target[ti.el] + static_cast<unsigned>(rows);
+          if (!wait_counter_ge<true>(a.peer_arrive[a.rank] + ti.el, target, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 51, ti.el, t);
+            break;
+          }
+          ready_el = ti.el;
+        }
+        if (ti.phase == 1) {
+          const unsigned* ready = reinterpret_cast<const unsigned*>(a.gu_ready) + tb->mt0[ti.el] + ti.m;
+          if (!wait_counter_ge<false>(ready, q0_per_mtile, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 52, ti.el, t);
+            break;
+          }
+        } else if (ti.phase == 3) {
+          const unsigned* done = reinterpret_cast<const unsigned*>(a.expert_done) + ti.el;
+          if (!wait_counter_ge<false>(done, q0_per_mtile * mt, a.wait_budget_ns, abort_flag)) {
+            report_status(a.status, kWaitFlagTimeout, 53, ti.el, t);
+            break;
+          }
+        }
+        bars->tile_q[i & (kTileQ - 1)] = t;
+        mbar_arrive(&bars->sched_full[sl]);
+      }
+    }
   } else {
     const int q = warp & 3;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     float* stg = stage_buf + (warp - 2) * (32 * 33);
     int iter = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++iter) {
-      const BwdTile ti = decode_bwd_tile(a, tb, t);
+    for (;; ++iter) {
       const int acc = iter & 1;
       if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag)) {
-        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 57, blockIdx.x, t);
+        if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 57, blockIdx.x, iter);
         break;
       }
+      const int t = bars->tile_q[iter & (kTileQ - 1)];
+      if (t < 0) break;
+      const BwdTile ti = decode_bwd_tile(a, tb, t);
       tc_fence_after();
       const uint32_t tacc = tmem_base + acc * BN + lane_off;
       const int rows = tb->rows[ti.el], base = tb->base[ti.el];
