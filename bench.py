@@ -359,16 +359,21 @@ def run_extras(device, rank, world, dist):
     extra = {}
 
     def guarded(name, fn):
+        import gc
         err = None
         try:
             res = fn()
         except Exception as e:  # out of memory, a kernel status error ...
             res, err = None, f"{type(e).__name__}: {str(e)[:200]}"
+        # the parts are sized to fill a GPU: drop what the last one still holds (engines sit in reference cycles;
+        # symmetric buffers are freed with their owners) before the next one allocates
+        gc.collect()
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
         flag = torch.tensor([0 if err is None else 1], device=device)
         dist.all_reduce(flag)
         if int(flag) > 0:
             extra[name] = {"error": err or "failed on another rank"}
-            torch.cuda.empty_cache()
             return False
         extra[name] = res
         return True
