@@ -4,9 +4,10 @@
 //      stores + a flag barrier); from the full count table each CTA derives, in shared memory,
 //      where its rows go in every destination's receive buffer and how many rows each local
 //      expert receives - no host round trip, no separate exchange kernel;
-//   2. dispatch: one warp per (token, expert) pair copies the token row straight into the
-//      destination rank's expert-sorted receive buffer over NVLink, with its source id and
-//      routing weight, then bumps that expert's arrival counter on the destination;
+//   2. dispatch: four warps per CTA copy the token rows, in expert order (the pairs are sorted on the fly), straight
+//      into the destination rank's expert-sorted receive buffer over NVLink, with source id and routing weight,
+//      and bump that expert's arrival counter on the destination after a fence per few rows - WHILE the other
+//      warps of the CTA already run the tiles of the experts whose rows are complete;
 //   3. grouped GEMM 1 (tcgen05, TMA, TMEM): for each local expert, as soon as its rows have
 //      arrived, [gate | up] = X_e [W_gate_e | W_up_e] with SiLU(gate) * up in the epilogue;
 //   4. grouped GEMM 2: Y_e = act_e W_down_e; the epilogue multiplies each row by its routing
@@ -42,7 +43,10 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
-constexpr int kThreads = 224;  // warp 0 loads, 1 issues MMAs, 2-5 run the epilogue, 6 schedules tiles
+// warp 0 loads, 1 issues MMAs, 2-5 run the epilogue, 6 schedules tiles, 7-10 dispatch rows (in the forward they do
+// so WHILE the other warps already work on the experts whose rows are in; in the backward all warps dispatch first)
+constexpr int kThreads = 352;
+constexpr int kTileWarps = 7, kDispatchWarps = kThreads / 32 - kTileWarps;
 constexpr int kCopyBatch = 8;  // 16-byte loads a lane keeps in flight while it copies a token row
 
 // per-CTA phase timelines of the last profiled launch: [0] forward, [1] backward
@@ -132,6 +136,43 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     prof_clk0 = clock64();
   }
 
+  // ---- 0. this rank's pairs sorted by expert: order[first pair of e + pos[p]] = p (a.slot_out holds the order).
+  //         Rows are dispatched in this order, so the experts complete one after the other and the tiles of the
+  //         first experts run while the rows of the later ones are still on their way. ----
+  {
+    if (warp == 0) {  // exclusive scan of my_counts into tb->send_off (free until build_tables)
+      const int per = (ET + 31) / 32;
+      int sum = 0;
+      for (int i = 0; i < per; ++i) {
+        const int e = lane * per + i;
+        if (e < ET) sum += a.my_counts[e];
+      }
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      int run = incl - sum;
+      for (int i = 0; i < per; ++i) {
+        const int e = lane * per + i;
+        if (e < ET) {
+          tb->send_off[e] = run;
+          run += a.my_counts[e];
+        }
+      }
+    }
+    __syncthreads();
+    const int n_pairs = a.tokens * a.top_k;
+    for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += gridDim.x * blockDim.x) {
+      const int e = a.idx[p];
+      if (e >= 0 && e < ET) {
+        const int at = tb->send_off[e] + a.pos[p];
+        if (at >= 0 && at < n_pairs) a.slot_out[at] = p;
+      }
+    }
+  }
+
   // ---- 1. publish this rank's counts, wait for everybody's ----
   {
     const int max_mt = a.cap_rows / BM + EL;
@@ -159,81 +200,6 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   }
 
   if (prof && threadIdx.x == 0) prof[1] = static_cast<long long>(globaltimer_ns());
-
-  // ---- 2. dispatch: one warp per (token, expert) pair ----
-  if (alive) {
-    const int n_pairs = a.tokens * a.top_k, nv = D / 8;
-    const int w0 = blockIdx.x * (kThreads / 32) + warp, wstep = gridDim.x * (kThreads / 32);
-    // two rows per pass (twice the loads in flight); the routing entries of the next pass are fetched before
-    // this pass's rows so that their latency hides behind the copy
-    int e_nx[2], pos_nx[2];
-    float w_nx[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int pp = w0 + h * wstep;
-      e_nx[h] = pp < n_pairs ? a.idx[pp] : 0;
-      pos_nx[h] = pp < n_pairs ? a.pos[pp] : 0;
-      w_nx[h] = pp < n_pairs ? a.w[pp] : 0.f;
-    }
-    for (int p = w0; p < n_pairs; p += 2 * wstep) {
-      const uint4* src[2] = {nullptr, nullptr};
-      uint4* out[2] = {nullptr, nullptr};
-      int e_cur[2], pos_cur[2];
-      float w_cur[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        e_cur[h] = e_nx[h];
-        pos_cur[h] = pos_nx[h];
-        w_cur[h] = w_nx[h];
-        const int pn = p + (2 + h) * wstep;
-        e_nx[h] = pn < n_pairs ? a.idx[pn] : 0;
-        pos_nx[h] = pn < n_pairs ? a.pos[pn] : 0;
-        w_nx[h] = pn < n_pairs ? a.w[pn] : 0.f;
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int pp = p + h * wstep;
-        if (pp >= n_pairs) continue;
-        const int e = e_cur[h];
-        if (!bounds_ok(e, ET, a.status, 201)) continue;
-        const int dst = e / EL;
-        const int slot = tb->send_off[e] + pos_cur[h];
-        if (!bounds_ok(slot, a.cap_rows, a.status, 202)) continue;
-        src[h] = reinterpret_cast<const uint4*>(a.x + static_cast<int64_t>(pp / a.top_k) * D);
-        out[h] = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
-        if (lane == 0) {
-          a.peer_recv_meta[dst][slot] = (a.rank << 24) | pp;  // source rank and (token, choice) pair
-          a.peer_recv_w[dst][slot] = w_cur[h];
-          a.slot_out[pp] = slot;
-        }
-      }
-      for (int i0 = lane; i0 < nv; i0 += 32 * kCopyBatch) {  // all loads of a batch in flight before the first store
-        uint4 v[2][kCopyBatch];
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int u = 0; u < kCopyBatch; ++u)
-            if (src[h] != nullptr && i0 + 32 * u < nv) v[h][u] = __ldg(src[h] + i0 + 32 * u);
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int u = 0; u < kCopyBatch; ++u)
-            if (src[h] != nullptr && i0 + 32 * u < nv) out[h][i0 + 32 * u] = v[h][u];
-      }
-    }
-    // one fence for all rows this warp delivered, then their arrival counts (lane l signs for the warp's pairs
-    // l, l + 32, ...): barrier -> fence -> relaxed reduction is a release sequence over every lane's stores
-    __syncwarp();
-    __threadfence_system();
-    int j = 0;
-    for (int p = w0; p < n_pairs; p += wstep, ++j) {
-      if ((j & 31) != lane) continue;
-      const int e = a.idx[p];
-      if (e < 0 || e >= ET || tb->send_off[e] + a.pos[p] >= a.cap_rows) continue;  // skipped (and reported) above
-      red_relaxed_sys_add_u32(a.peer_arrive[e / EL] + (e % EL), 1u);
-    }
-  }
-  if (prof && threadIdx.x == 0) prof[2] = static_cast<long long>(globaltimer_ns());
 
   // ---- 3./4. grouped GEMMs over the local experts ----
   const int num_tiles = alive ? tb->tile0[tb->n_slots] : 0;
@@ -396,7 +362,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
         mbar_arrive(&bars->sched_full[sl]);
       }
     }
-  } else {
+  } else if (warp < kTileWarps) {
     const int q = warp & 3;
     int iter = 0;
     for (;; ++iter) {
@@ -492,6 +458,86 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       }
     }
     if (prof && warp == 2 && lane == 0) prof[8] = static_cast<long long>(globaltimer_ns());
+  } else if (alive) {
+    // ---- dispatch warps: rows in expert order, two per pass, 16-byte loads batched; the routing entries of the
+    //      next pass and the order entries of the one after are fetched ahead of the copy ----
+    const int n_pairs = a.tokens * a.top_k, nv = D / 8;
+    const int g0 = blockIdx.x * kDispatchWarps + (warp - kTileWarps), gs = gridDim.x * kDispatchWarps;
+    const int* order = a.slot_out;
+    int p_nx[2], e_nx[2], pos_nx[2], p_n2[2];
+    float w_nx[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int s0 = g0 + h * gs, s1 = g0 + (2 + h) * gs;
+      p_nx[h] = s0 < n_pairs ? order[s0] : -1;
+      p_n2[h] = s1 < n_pairs ? order[s1] : -1;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      e_nx[h] = p_nx[h] >= 0 ? a.idx[p_nx[h]] : 0;
+      pos_nx[h] = p_nx[h] >= 0 ? a.pos[p_nx[h]] : 0;
+      w_nx[h] = p_nx[h] >= 0 ? a.w[p_nx[h]] : 0.f;
+    }
+    int pend_e = -1;  // lane 2 * (pass % 4) + h remembers the expert of a delivered row until the next flush
+    for (int k = 0, s = g0; s < n_pairs; ++k, s += 2 * gs) {
+      const uint4* src[2] = {nullptr, nullptr};
+      uint4* out[2] = {nullptr, nullptr};
+      int p_cur[2], e_cur[2], pos_cur[2];
+      float w_cur[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        p_cur[h] = p_nx[h];
+        e_cur[h] = e_nx[h];
+        pos_cur[h] = pos_nx[h];
+        w_cur[h] = w_nx[h];
+        p_nx[h] = p_n2[h];
+        e_nx[h] = p_nx[h] >= 0 ? a.idx[p_nx[h]] : 0;
+        pos_nx[h] = p_nx[h] >= 0 ? a.pos[p_nx[h]] : 0;
+        w_nx[h] = p_nx[h] >= 0 ? a.w[p_nx[h]] : 0.f;
+        const int s2 = s + (4 + h) * gs;
+        p_n2[h] = s2 < n_pairs ? order[s2] : -1;
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int pp = p_cur[h];
+        if (pp < 0) continue;
+        const int e = e_cur[h];
+        if (!bounds_ok(pp, n_pairs, a.status, 200) || !bounds_ok(e, ET, a.status, 201)) continue;
+        const int dst = e / EL;
+        const int slot = tb->send_off[e] + pos_cur[h];
+        if (!bounds_ok(slot, a.cap_rows, a.status, 202)) continue;
+        src[h] = reinterpret_cast<const uint4*>(a.x + static_cast<int64_t>(pp / a.top_k) * D);
+        out[h] = reinterpret_cast<uint4*>(a.peer_recv_x[dst] + static_cast<int64_t>(slot) * D);
+        if (lane == 0) {
+          a.peer_recv_meta[dst][slot] = (a.rank << 24) | pp;  // source rank and (token, choice) pair
+          a.peer_recv_w[dst][slot] = w_cur[h];
+        }
+        if (lane == 2 * (k & 3) + h) pend_e = e;
+      }
+      for (int i0 = lane; i0 < nv; i0 += 32 * kCopyBatch) {  // all loads of a batch in flight before the first store
+        uint4 v[2][kCopyBatch];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int u = 0; u < kCopyBatch; ++u)
+            if (src[h] != nullptr && i0 + 32 * u < nv) v[h][u] = __ldg(src[h] + i0 + 32 * u);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int u = 0; u < kCopyBatch; ++u)
+            if (src[h] != nullptr && i0 + 32 * u < nv) out[h][i0 + 32 * u] = v[h][u];
+      }
+      // Arrivals of up to four passes with one fence (the first two passes signal at once so that the first
+      // experts start early): barrier -> fence -> relaxed reduction is a release sequence over every lane's stores.
+      if (k < 2 || (k & 3) == 3 || s + 2 * gs >= n_pairs) {
+        __syncwarp();
+        __threadfence_system();
+        if (pend_e >= 0) red_relaxed_sys_add_u32(a.peer_arrive[pend_e / EL] + (pend_e % EL), 1u);
+        pend_e = -1;
+        __syncwarp();
+      }
+    }
+    if (prof && warp == kTileWarps && lane == 0) prof[2] = static_cast<long long>(globaltimer_ns());
   }
 
   // ---- 5. every rank's contributions have landed before anybody returns ----
@@ -920,7 +966,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
         mbar_arrive(&bars->sched_full[sl]);
       }
     }
-  } else {
+  } else if (warp < kTileWarps) {
     const int q = warp & 3;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     float* stg = stage_buf + (warp - 2) * (32 * 33);

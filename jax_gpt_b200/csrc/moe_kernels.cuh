@@ -40,7 +40,8 @@ struct EpMoeArgs {
   __nv_bfloat16* gu;        // [cap_rows, 2 * inter] gate | up pre-activations saved for backward, or nullptr
   unsigned* arrive_target;  // [e_local] arrivals expected once this launch's rows are in (cumulative)
   int* act_ready;           // [cap_rows / 128 + e_local] per m-tile count of finished GEMM1 epilogue warps
-  int* slot_out;            // [tokens * top_k] row of each pair in its destination's receive buffer
+  int* slot_out;            // [tokens * top_k] bf16 forward: scratch, this rank's pair ids sorted by expert (the dispatch
+                            // order); FP8 forward: row of each pair in its destination's receive buffer
   int* rows_out;            // [e_local] rows received per local expert (for the caller / backward)
   // ---- backward only ----
   const __nv_bfloat16* dout;                   // [tokens, d_model] gradient of the routed output
