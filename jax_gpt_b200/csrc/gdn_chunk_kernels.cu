@@ -362,6 +362,8 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_chunk_prep_bwd_kernel(const P
 
 #pragma unroll 1
     for (int h = 0; h < 2; ++h) {              // h = 0: the value columns, h = 1: the key columns of the solve
+      // The two substitutions of a pass are independent (X needs the right-hand side, Y the incoming gradient):
+      // threads 0-127 solve the columns of X while threads 128-255 solve the columns of Y.
       if (tid < 128) {
         const int c = tid;
         float x[kC];
@@ -389,7 +391,9 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_chunk_prep_bwd_kernel(const P
         }
 #pragma unroll
         for (int i = 0; i < kC; ++i) sX[i * kLd + c] = x[i];
-        __syncwarp();      // keeps the two substitutions apart in the schedule (their merged live ranges spill)
+      } else {
+        const int c = tid - 128;
+        float x[kC];
         // Y = (I + A)^-T dX, right-looking: once y_j is final, y_i -= A_ji y_j for every i < j
         const __nv_bfloat16* dxp = h == 0 ? p.d_veff + chunk * kC * kD + c : p.d_kq + chunk * 2 * kC * kD + c;
 #pragma unroll
