@@ -107,6 +107,20 @@ def ep_moe_layer_bench(device, rank: int, world: int, tokens: int = 4096, d_mode
     nv_bytes = max(max_rows, T * k) * remote * (D * 2 + D * 4)   # bf16 row in, fp32 reduction out
     peaks = R.load_peaks()
     bound = max(flops / (peaks["bf16_tflops"] * 1e12), nv_bytes / (R.NVLINK_GBS_MEASURED * 1e9))
+    # HBM floors (bytes every launch has to move once): forward = the rank's expert weights, the received rows
+    # written and read, act written and read, the pre-activations written; backward = weights read, fp32 weight
+    # gradients read and written by the accumulation, dY rows written and read twice, x / act / pre-activations read,
+    # dGU written and read twice
+    w_elems = 3.0 * (E // world) * D * I
+    hbm = peaks["hbm_gbs"] * 1e9
+    fwd_bytes = w_elems * 2 + max_rows * (2 * D * 2 + 2 * I * 2 + 2 * I * 2)
+    bwd_bytes = w_elems * 2 + w_elems * 8 + max_rows * (3 * D * 2 + D * 2 + I * 2 + 2 * I * 2 + 3 * 2 * I * 2)
+    res.update(hbm_floor_fwd_ms=fwd_bytes / hbm * 1e3, hbm_floor_bwd_ms=bwd_bytes / hbm * 1e3)
+    if backward:
+        bwd_bound = max(2.0 * flops / (peaks["bf16_tflops"] * 1e12), bwd_bytes / hbm,
+                        nv_bytes / (R.NVLINK_GBS_MEASURED * 1e9))
+        res["roofline_fraction_bwd_with_hbm"] = bwd_bound * 1e3 / res["fused_bwd_ms"]
+    res["roofline_fraction_fwd_with_hbm"] = max(bound, fwd_bytes / hbm) * 1e3 / ms_fused
     res.update(max_rows_any_rank=max_rows, tflops_busiest_rank=flops / ms_fused / 1e9, roofline_ms=bound * 1e3,
                roofline_fraction=bound * 1e3 / ms_fused, denominators=peaks["source"],
                tokens_per_s=T * world / (ms_fused / 1e3))
