@@ -152,36 +152,64 @@ ep_moe_forward_fp8_kernel(const __grid_constant__ Fp8Maps tm, const __grid_const
     alive = false;
   }
 
-  // ---- 2. dispatch: one warp per (token, expert) pair: byte row + exponent words ----
+  // ---- 2. dispatch: one warp per (token, expert) pair: byte row + exponent words. Two rows per pass with eight
+  //         16-byte loads per lane and row in flight before the first store; one fence per warp after all its rows,
+  //         then their arrival counts (barrier -> fence -> relaxed reduction is a release sequence over every
+  //         lane's stores). ----
   if (alive) {
-    const int n_pairs = a.tokens * a.top_k;
-    for (int p = gwarp; p < n_pairs; p += gwarps) {
+    const int n_pairs = a.tokens * a.top_k, nv = D / 16;
+    constexpr int kBatch = 8;
+    for (int p = gwarp; p < n_pairs; p += 2 * gwarps) {
+      const uint4* src[2] = {nullptr, nullptr};
+      uint4* out[2] = {nullptr, nullptr};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int pp = p + h * gwarps;
+        if (pp >= n_pairs) continue;
+        const int e = a.idx[pp];
+        if (!bounds_ok(e, ET, a.status, 211)) continue;
+        const int dst = e / EL;
+        const int slot = tb->send_off[e] + a.pos[pp];
+        if (!bounds_ok(slot, a.cap_rows, a.status, 212)) continue;
+        const int tok = pp / a.top_k;
+        src[h] = reinterpret_cast<const uint4*>(a.xq + static_cast<int64_t>(tok) * D);
+        out[h] = reinterpret_cast<uint4*>(a.peer_recv_q[dst] + static_cast<int64_t>(slot) * D);
+        // scale exponents: chunk (slot / 128, g), word at (r % 32) * 16 + (r / 32) * 4 with r = slot % 128
+        const int r = slot & 127;
+        uint8_t* sfrow = a.peer_recv_sf[dst] + static_cast<int64_t>(slot >> 7) * dslabs * kSfBytes + (r & 31) * 16 + (r >> 5) * 4;
+        const uint8_t* xe = a.xe + static_cast<int64_t>(tok) * dslabs;
+        for (int g = lane; g < dslabs; g += 32) {
+          const uint32_t eb = __ldcg(xe + g);
+          *reinterpret_cast<uint32_t*>(sfrow + static_cast<int64_t>(g) * kSfBytes) = eb * 0x01010101u;
+        }
+        if (lane == 0) {
+          a.peer_recv_meta[dst][slot] = (a.rank << 24) | pp;
+          a.peer_recv_w[dst][slot] = a.w[pp];
+          a.slot_out[pp] = slot;
+        }
+      }
+      for (int i0 = lane; i0 < nv; i0 += 32 * kBatch) {
+        uint4 v[2][kBatch];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (src[h] != nullptr && i0 + 32 * u < nv) v[h][u] = __ldcg(src[h] + i0 + 32 * u);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u)
+            if (src[h] != nullptr && i0 + 32 * u < nv) out[h][i0 + 32 * u] = v[h][u];
+      }
+    }
+    __syncwarp();
+    __threadfence_system();
+    int j = 0;
+    for (int p = gwarp; p < n_pairs; p += gwarps, ++j) {
+      if ((j & 31) != lane) continue;
       const int e = a.idx[p];
-      const int dst = e / EL, el = e - dst * EL;
-      const int slot = tb->send_off[e] + a.pos[p];
-      if (!bounds_ok(e, ET, a.status, 211) || !bounds_ok(slot, a.cap_rows, a.status, 212)) continue;
-      const int tok = p / a.top_k;
-      const uint4* src = reinterpret_cast<const uint4*>(a.xq + static_cast<int64_t>(tok) * D);
-      uint4* out = reinterpret_cast<uint4*>(a.peer_recv_q[dst] + static_cast<int64_t>(slot) * D);
-      for (int i = lane; i < D / 16; i += 32) out[i] = __ldcg(src + i);
-      // scale exponents: chunk (slot / 128, g), word at (r % 32) * 16 + (r / 32) * 4 with r = slot % 128
-      const int r = slot & 127;
-      uint8_t* sfrow = a.peer_recv_sf[dst] + static_cast<int64_t>(slot >> 7) * dslabs * kSfBytes + (r & 31) * 16 + (r >> 5) * 4;
-      const uint8_t* xe = a.xe + static_cast<int64_t>(tok) * dslabs;
-      for (int g = lane; g < dslabs; g += 32) {
-        const uint32_t eb = __ldcg(xe + g);
-        *reinterpret_cast<uint32_t*>(sfrow + static_cast<int64_t>(g) * kSfBytes) = eb * 0x01010101u;
-      }
-      if (lane == 0) {
-        a.peer_recv_meta[dst][slot] = (a.rank << 24) | p;
-        a.peer_recv_w[dst][slot] = a.w[p];
-        a.slot_out[p] = slot;
-      }
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_system();
-        red_release_sys_add_u32(a.peer_arrive[dst] + el, 1u);
-      }
+      if (e < 0 || e >= ET || tb->send_off[e] + a.pos[p] >= a.cap_rows) continue;  // skipped (and reported) above
+      red_relaxed_sys_add_u32(a.peer_arrive[e / EL] + (e % EL), 1u);
     }
   }
 
