@@ -137,15 +137,18 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   }
 
   // ---- 0. this rank's pairs sorted by expert: order[first pair of e + pos[p]] = p (a.slot_out holds the order).
-  //         Rows are dispatched in this order, so the experts complete one after the other and the tiles of the
-  //         first experts run while the rows of the later ones are still on their way. ----
+  //         Rows are dispatched in this order, so the experts complete one after the other on every rank and the
+  //         tiles of the first experts run while the rows of the later ones are still on their way. ----
   {
-    if (warp == 0) {  // exclusive scan of my_counts into tb->send_off (free until build_tables)
+    // Sort key of global expert e = (dst, el): el * W + dst, so that the first local expert of EVERY destination
+    // comes first and all ranks can start their tiles together (in plain expert order the last rank would receive
+    // nothing until the others' experts had been served).
+    if (warp == 0) {  // exclusive scan of my_counts in key order into tb->send_off (free until build_tables)
       const int per = (ET + 31) / 32;
       int sum = 0;
       for (int i = 0; i < per; ++i) {
-        const int e = lane * per + i;
-        if (e < ET) sum += a.my_counts[e];
+        const int q = lane * per + i;
+        if (q < ET) sum += a.my_counts[(q % W) * EL + q / W];
       }
       int incl = sum;
 #pragma unroll
@@ -155,8 +158,9 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       }
       int run = incl - sum;
       for (int i = 0; i < per; ++i) {
-        const int e = lane * per + i;
-        if (e < ET) {
+        const int q = lane * per + i;
+        if (q < ET) {
+          const int e = (q % W) * EL + q / W;
           tb->send_off[e] = run;
           run += a.my_counts[e];
         }
