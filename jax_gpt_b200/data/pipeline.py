@@ -7,6 +7,12 @@
 prefetch thread fills pinned host tensors ahead of the training loop, so the host->device copy
 of step n+1 never waits for the page cache. ``skip_to_step`` seeks in O(1); the reference
 replays ``step * accum * micro_batch`` items (jax_gpt/data/pipeline.py:142-150).
+
+``data_source='gcs'`` names ``gs://<gcs_bucket>/<gcs_dataset_path>/<split>`` (jax_gpt/data/pipeline.py:29-30,
+93-98, where grain reads ArrayRecord shards from the bucket). Here the bucket is read through a file-system mount
+(gcsfuse or any other): ``<mount>/<gcs_bucket>/<gcs_dataset_path>/<split>.bin`` in the same flat uint16 format, with
+``<mount>`` taken from the environment variable ``B200_GCS_MOUNT`` (default ``/gcs``), so the memory-mapped native
+loader serves both sources. Without such a mount the constructor says what it looked for.
 """
 from __future__ import annotations
 
@@ -26,14 +32,30 @@ def _world():
     return 0, 1
 
 
+def gcs_mounted_path(config, split: str) -> str:
+    """File behind ``gs://<gcs_bucket>/<gcs_dataset_path>/<split>`` on the bucket's file-system mount."""
+    if not config.gcs_bucket:
+        raise ValueError("data_source='gcs' needs gcs_bucket (and gcs_dataset_path)")
+    root = os.environ.get("B200_GCS_MOUNT", "/gcs")
+    path = os.path.join(root, config.gcs_bucket, config.gcs_dataset_path.strip("/"), f"{split}.bin")
+    if not os.path.exists(path):
+        raise FileNotFoundError(
+            f"gs://{config.gcs_bucket}/{config.gcs_dataset_path}/{split}: expected the bucket mounted at {root} "
+            f"(set B200_GCS_MOUNT) with the flat uint16 token file {path}")
+    return path
+
+
 class DataPipeline:
     def __init__(self, config, split: str = "train", *, _shard_index=None, _shard_count=None, use_native: bool = True,
                  prefetch: int = 8):
-        if config.data_source != "local":
-            raise NotImplementedError("only data_source='local' is available (no object-store client in this image)")
-        self.path = os.path.join(config.local_data_path, f"{split}.bin")
-        if not os.path.exists(self.path):
-            raise FileNotFoundError(self.path)
+        if config.data_source == "local":
+            self.path = os.path.join(config.local_data_path, f"{split}.bin")
+            if not os.path.exists(self.path):
+                raise FileNotFoundError(self.path)
+        elif config.data_source == "gcs":
+            self.path = gcs_mounted_path(config, split)
+        else:
+            raise ValueError(f"Unknown data_source '{config.data_source}'. Expected 'local' or 'gcs'.")
         rank, world = _world()
         self.shard_index = rank if _shard_index is None else _shard_index
         self.shard_count = world if _shard_count is None else _shard_count
