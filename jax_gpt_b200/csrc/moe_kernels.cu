@@ -68,13 +68,12 @@ struct MoeBars {
   volatile int tile_q[kTileQ];
 };
 
-// Next unclaimed tile of the running forward [0] / backward [1] launch. The persistent CTAs take tiles in the
-// static order from this counter (a CTA that finishes a cheap tile takes the next one instead of idling beside a
-// CTA on an expensive tile). A scheduler warp per CTA claims the tile, waits for its dependencies (arrival
-// counters, earlier tiles) and only then hands it to the load warp: the claim's and the flags' round trips to L2
-// stay off the path that feeds the tensor cores. Each kernel needs every SM's shared memory, so two launches never overlap on a
-// device and one counter per kernel suffices; block 0 zeroes it before the grid barrier that precedes the tiles.
-__device__ int g_moe_tile_counter[2];
+// The persistent CTAs take tiles in the static order from a counter of the launch (a CTA that finishes a cheap tile
+// takes the next one instead of idling beside a CTA on an expensive tile). A scheduler warp per CTA claims the tile,
+// waits for its dependencies (arrival counters, earlier tiles) and only then hands it to the load warp: the claim's
+// and the flags' round trips to L2 stay off the path that feeds the tensor cores. The counter is the element after
+// the per-m-tile flags in the layer's own act_ready (forward) / gu_ready (backward) buffer, so launches of different
+// layers never share one; block 0 zeroes it before the grid barrier that precedes the tiles.
 
 constexpr int kStageBufBytes = 4 * 32 * 33 * 4;  // per-epilogue-warp transposition buffers
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(MoeTables) + sizeof(MoeBars) + 64 + kStageBufBytes;
@@ -180,12 +179,11 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   // ---- 1. publish this rank's counts, wait for everybody's ----
   {
     const int max_mt = a.cap_rows / BM + EL;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < max_mt; i += gridDim.x * blockDim.x) a.act_ready[i] = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i <= max_mt; i += gridDim.x * blockDim.x) a.act_ready[i] = 0;
   }
   if (blockIdx.x == 0) {
     if (threadIdx.x == 0) {
       my->abort_flag = 0;
-      g_moe_tile_counter[0] = 0;
     }
     for (int i = threadIdx.x; i < ET; i += blockDim.x) {
       const int c = a.my_counts[i];
@@ -339,7 +337,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       for (int i = 0;; ++i) {
         const int sl = i & (kSchedAhead - 1);
         if (!mbar_wait(&bars->sched_empty[sl], ((i / kSchedAhead) & 1) ^ 1, abort_flag)) break;
-        const int t = atomicAdd(&g_moe_tile_counter[0], 1);
+        const int t = atomicAdd(a.act_ready + a.cap_rows / BM + EL, 1);
         if (t >= num_tiles) {
           bars->tile_q[i & (kTileQ - 1)] = -1;
           mbar_arrive(&bars->sched_full[sl]);
@@ -676,14 +674,13 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
   // ---- 1. counts exchange (same protocol as forward), zero the per-launch counters ----
   {
     const int max_mt = a.cap_rows / BM + EL;
-    for (int i = gtid; i < max_mt; i += gthreads) a.gu_ready[i] = 0;
+    for (int i = gtid; i <= max_mt; i += gthreads) a.gu_ready[i] = 0;
     for (int i = gtid; i < EL; i += gthreads) a.expert_done[i] = 0;
     for (int i = gtid; i < a.cap_rows; i += gthreads) a.dw_rows[i] = 0.f;
   }
   if (blockIdx.x == 0) {
     if (threadIdx.x == 0) {
       my->abort_flag = 0;
-      g_moe_tile_counter[1] = 0;
     }
     for (int i = threadIdx.x; i < ET; i += blockDim.x) {
       const int c = a.my_counts[i];
@@ -934,7 +931,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       for (int i = 0;; ++i) {
         const int sl = i & (kSchedAhead - 1);
         if (!mbar_wait(&bars->sched_empty[sl], ((i / kSchedAhead) & 1) ^ 1, abort_flag)) break;
-        const int t = atomicAdd(&g_moe_tile_counter[1], 1);
+        const int t = atomicAdd(a.gu_ready + a.cap_rows / BM + EL, 1);
         if (t >= num_tiles) {
           bars->tile_q[i & (kTileQ - 1)] = -1;
           mbar_arrive(&bars->sched_full[sl]);

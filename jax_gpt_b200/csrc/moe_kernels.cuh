@@ -39,7 +39,8 @@ struct EpMoeArgs {
   __nv_bfloat16* act;       // [cap_rows, inter] SwiGLU output
   __nv_bfloat16* gu;        // [cap_rows, 2 * inter] gate | up pre-activations saved for backward, or nullptr
   unsigned* arrive_target;  // [e_local] arrivals expected once this launch's rows are in (cumulative)
-  int* act_ready;           // [cap_rows / 128 + e_local] per m-tile count of finished GEMM1 epilogue warps
+  int* act_ready;           // [cap_rows / 128 + e_local + 1] per m-tile count of finished GEMM1 epilogue warps, then the
+                            // forward launch's tile counter
   int* slot_out;            // [tokens * top_k] bf16 forward: scratch, this rank's pair ids sorted by expert (the dispatch
                             // order); FP8 forward: row of each pair in its destination's receive buffer
   int* rows_out;            // [e_local] rows received per local expert (for the caller / backward)
@@ -50,7 +51,8 @@ struct EpMoeArgs {
   float* peer_dw[kCommMaxRanks];               // [tokens * top_k of that rank] gradient of the routing weights
   __nv_bfloat16* dgu;                          // [cap_rows, 2 * inter] gradient of gate | up
   float* dw_rows;                              // [cap_rows] <dAct, act> per received row
-  int* gu_ready;                               // [cap_rows / 128 + e_local] per m-tile count of finished dAct epilogue warps
+  int* gu_ready;                               // [cap_rows / 128 + e_local + 1] per m-tile count of finished dAct epilogue
+                                               // warps, then the backward launch's tile counter
   int* expert_done;                            // [e_local] same, per expert
   float* d_gate;                               // [e_local, d_model, inter] fp32, accumulated
   float* d_up;                                 // [e_local, d_model, inter]

@@ -51,7 +51,7 @@ class FusedEPMoE:
         self.out_acc = comm.alloc(tokens * d_model, torch.float32)
         self.act = torch.zeros(self.cap_rows, inter, device=dev, dtype=torch.bfloat16)
         self.arrive_target = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
-        self.act_ready = torch.zeros(self.cap_rows // 128 + self.e_local, device=dev, dtype=torch.int32)
+        self.act_ready = torch.zeros(self.cap_rows // 128 + self.e_local + 1, device=dev, dtype=torch.int32)  # + tile counter
         self.slot_out = torch.zeros(tokens * top_k, device=dev, dtype=torch.int32)
         self.rows_out = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
         self.my_counts = torch.zeros(n_experts, device=dev, dtype=torch.int32)
@@ -63,7 +63,7 @@ class FusedEPMoE:
             self.dx_acc = comm.alloc(tokens * d_model, torch.float32)
             self.dw_out = comm.alloc(tokens * top_k, torch.float32)
             self.dw_rows = torch.zeros(self.cap_rows, device=dev, dtype=torch.float32)
-            self.gu_ready = torch.zeros(self.cap_rows // 128 + self.e_local, device=dev, dtype=torch.int32)
+            self.gu_ready = torch.zeros(self.cap_rows // 128 + self.e_local + 1, device=dev, dtype=torch.int32)  # + tile counter
             self.expert_done = torch.zeros(self.e_local, device=dev, dtype=torch.int32)
         else:
             self.gu = None
