@@ -128,6 +128,9 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // waits that sit behind a tile's dependencies (ready tile, its operands, its accumulator) may legitimately last as
+  // long as the arrival of a late peer's rows: the caller's budget on top of the pipeline's own
+  const uint64_t pipe_budget = a.wait_budget_ns + kWaitBudgetNs;
   long long* prof = (a.prof != nullptr && blockIdx.x < kMoeProfCtas) ? a.prof + blockIdx.x * kMoeProfFields : nullptr;
   long long prof_clk0 = 0;
   if (prof && threadIdx.x == 0) {
@@ -215,7 +218,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       for (int iter = 0; ok; ++iter) {
         const int sl = iter & (kSchedAhead - 1);
         const long long c_dep = prof ? clock64() : 0;
-        if (!mbar_wait(&bars->sched_full[sl], (iter / kSchedAhead) & 1, abort_flag)) break;
+        if (!mbar_wait(&bars->sched_full[sl], (iter / kSchedAhead) & 1, abort_flag, pipe_budget)) break;
         if (prof) dep_clk += clock64() - c_dep;
         const int t = bars->tile_q[iter & (kTileQ - 1)];
         mbar_arrive(&bars->sched_empty[sl]);
@@ -280,7 +283,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       const int acc = iter & 1;
       // the first operands of the next tile (or the end mark) are in; its id was written before them
       const long long c_f0 = prof ? clock64() : 0;
-      if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+      if (!mbar_wait(&bars->full[stage], phase, abort_flag, pipe_budget)) {
         if (lane == 0) report_status(a.status, kWaitFullTimeout, 45, blockIdx.x, iter);
         break;
       }
@@ -302,7 +305,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
       for (int kb = 0; kb < nkb; ++kb) {
         if (kb > 0) {
           const long long c_f = prof ? clock64() : 0;
-          if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+          if (!mbar_wait(&bars->full[stage], phase, abort_flag, pipe_budget)) {
             if (lane == 0) report_status(a.status, kWaitFullTimeout, 45, blockIdx.x, t);
             ok = false;
             break;
@@ -369,7 +372,7 @@ ep_moe_forward_kernel(const __grid_constant__ CUtensorMap t_recv, const __grid_c
     int iter = 0;
     for (;; ++iter) {
       const int acc = iter & 1;
-      if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag)) {
+      if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag, pipe_budget)) {
         if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 46, blockIdx.x, iter);
         break;
       }
@@ -663,6 +666,9 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // waits that sit behind a tile's dependencies (ready tile, its operands, its accumulator) may legitimately last as
+  // long as the arrival of a late peer's rows: the caller's budget on top of the pipeline's own
+  const uint64_t pipe_budget = a.wait_budget_ns + kWaitBudgetNs;
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gthreads = gridDim.x * blockDim.x;
   long long* prof = (a.prof != nullptr && blockIdx.x < kMoeProfCtas) ? a.prof + blockIdx.x * kMoeProfFields : nullptr;
   long long prof_clk0 = 0;
@@ -801,7 +807,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       for (int iter = 0; ok; ++iter) {
         const int sl = iter & (kSchedAhead - 1);
         const long long c_dep = prof ? clock64() : 0;
-        if (!mbar_wait(&bars->sched_full[sl], (iter / kSchedAhead) & 1, abort_flag)) break;
+        if (!mbar_wait(&bars->sched_full[sl], (iter / kSchedAhead) & 1, abort_flag, pipe_budget)) break;
         if (prof) dep_clk += clock64() - c_dep;
         const int t = bars->tile_q[iter & (kTileQ - 1)];
         mbar_arrive(&bars->sched_empty[sl]);
@@ -870,7 +876,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       const int acc = iter & 1;
       // the first operands of the next tile (or the end mark) are in; its id was written before them
       const long long c_f0 = prof ? clock64() : 0;
-      if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+      if (!mbar_wait(&bars->full[stage], phase, abort_flag, pipe_budget)) {
         if (lane == 0) report_status(a.status, kWaitFullTimeout, 56, blockIdx.x, iter);
         break;
       }
@@ -894,7 +900,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
       for (int kb = 0; kb < nkb; ++kb) {
         if (kb > 0) {
           const long long c_f = prof ? clock64() : 0;
-          if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+          if (!mbar_wait(&bars->full[stage], phase, abort_flag, pipe_budget)) {
             if (lane == 0) report_status(a.status, kWaitFullTimeout, 56, blockIdx.x, t);
             ok = false;
             break;
@@ -974,7 +980,7 @@ ep_moe_backward_kernel(const __grid_constant__ BwdMaps tm, const __grid_constant
     int iter = 0;
     for (;; ++iter) {
       const int acc = iter & 1;
-      if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag)) {
+      if (!mbar_wait(&bars->tmem_full[acc], (iter >> 1) & 1, abort_flag, pipe_budget)) {
         if (lane == 0) report_status(a.status, kWaitTmemFullTimeout, 57, blockIdx.x, iter);
         break;
       }
