@@ -5,6 +5,10 @@
 #include <torch/library.h>
 #include <torch/torch.h>
 
+#include <cstring>
+#include <tuple>
+#include <vector>
+
 #include "attention_sm100.cuh"
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"

@@ -64,6 +64,67 @@ __device__ __forceinline__ bool wait_counter_ge(const unsigned* p, unsigned targ
 }
 
 
+// From tb->rows: the regions of the local experts in the receive buffer (base), their m-tile numbering (mt0) and the
+// static tile order (lag, n_slots, tile0). One thread; also compiled for the host, where the tests walk the order.
+template <class Args>
+__host__ __device__ inline void build_tile_order(const Args& a, MoeTables* tb, bool backward, int pad, int claim_ahead,
+                                                 int grid_ctas) {
+  const int EL = a.e_local;
+  const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
+  // Cost of a tile in 64-deep K blocks, plus a few blocks' worth of epilogue: the tiles other tiles wait for
+  // (GEMM1 / dAct, full-depth K) take longer than the average tile, and the lag has to cover their duration.
+  const float c_over = 6.f;
+  const float c_prod = a.d_model / 64 + c_over + (backward ? 4.f : 0.f);
+  float cost = 0.f;
+  int b = 0, t = 0, m = 0;
+  for (int el = 0; el < EL; ++el) {
+    tb->base[el] = b;
+    tb->mt0[el] = m;
+    const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
+    const int padded = (tb->rows[el] + pad - 1) / pad * pad;
+    b += padded;
+    if (!backward) {
+      t += mt * (n1 + n2);
+      cost += mt * (n1 * c_prod + n2 * (a.inter / 64 + c_over));
+    } else if (mt > 0) {
+      // dAct tiles, dX tiles, dW_down tiles, dW_gate|up tiles
+      const int q0 = mt * (a.inter / kMoeBN), q1 = mt * n2;
+      const int q23 = (a.inter / kMoeBM) * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
+      t += q0 + q1 + q23;
+      cost += q0 * c_prod + q1 * (2 * a.inter / 64 + c_over) + q23 * (padded / 64 + c_over);
+    }
+    m += mt;
+  }
+  tb->mt0[EL] = m;
+  // Lag in experts: while one producer tile runs, the grid claims about gridDim.x * (its cost / average cost)
+  // tiles; three times that, plus the tiles the CTAs claim ahead of their load warps, at the average number
+  // of tiles per expert.
+  int lag = 1;
+  if (t > 0) {
+    const float lag_tiles = static_cast<float>(grid_ctas) * (3.f * c_prod * t / cost + claim_ahead);
+    lag = static_cast<int>(lag_tiles * EL / t) + 1;
+  }
+  lag = lag < 1 ? 1 : (lag > EL ? EL : lag);
+  const int n_slots = EL + lag;
+  int u = 0;
+  for (int sl = 0; sl < n_slots; ++sl) {
+    tb->tile0[sl] = u;
+    if (sl < EL) {
+      const int mt = (tb->rows[sl] + kMoeBM - 1) / kMoeBM;
+      if (!backward) u += mt * n1;
+      else if (mt > 0) u += mt * (a.inter / kMoeBN) + (a.inter / kMoeBM) * n2;
+    }
+    if (sl >= lag) {
+      const int mt = (tb->rows[sl - lag] + kMoeBM - 1) / kMoeBM;
+      if (!backward) u += mt * n2;
+      else if (mt > 0) u += mt * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
+    }
+  }
+  tb->tile0[n_slots] = u;
+  tb->lag = lag;
+  tb->n_slots = n_slots;
+}
+
 // Fills the shared-memory tables from the all-gathered count matrix counts[src][e].
 template <class Args>
 __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb, bool backward = false, int pad = 64,
@@ -102,61 +163,7 @@ __device__ void build_tables(const Args& a, const int* counts_all, MoeTables* tb
     tb->rows[el] = n;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
-    // Cost of a tile in 64-deep K blocks, plus a few blocks' worth of epilogue: the tiles other tiles wait for
-    // (GEMM1 / dAct, full-depth K) take longer than the average tile, and the lag has to cover their duration.
-    const float c_over = 6.f;
-    const float c_prod = a.d_model / 64 + c_over + (backward ? 4.f : 0.f);
-    float cost = 0.f;
-    int b = 0, t = 0, m = 0;
-    for (int el = 0; el < EL; ++el) {
-      tb->base[el] = b;
-      tb->mt0[el] = m;
-      const int mt = (tb->rows[el] + kMoeBM - 1) / kMoeBM;
-      const int padded = (tb->rows[el] + pad - 1) / pad * pad;
-      b += padded;
-      if (!backward) {
-        t += mt * (n1 + n2);
-        cost += mt * (n1 * c_prod + n2 * (a.inter / 64 + c_over));
-      } else if (mt > 0) {
-        // dAct tiles, dX tiles, dW_down tiles, dW_gate|up tiles
-        const int q0 = mt * (a.inter / kMoeBN), q1 = mt * n2;
-        const int q23 = (a.inter / kMoeBM) * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
-        t += q0 + q1 + q23;
-        cost += q0 * c_prod + q1 * (2 * a.inter / 64 + c_over) + q23 * (padded / 64 + c_over);
-      }
-      m += mt;
-    }
-    tb->mt0[EL] = m;
-    // Lag in experts: while one producer tile runs, the grid claims about gridDim.x * (its cost / average cost)
-    // tiles; three times that, plus the tiles the CTAs claim ahead of their load warps, at the average number
-    // of tiles per expert.
-    int lag = 1;
-    if (t > 0) {
-      const float lag_tiles = static_cast<float>(gridDim.x) * (3.f * c_prod * t / cost + claim_ahead);
-      lag = static_cast<int>(lag_tiles * EL / t) + 1;
-    }
-    lag = lag < 1 ? 1 : (lag > EL ? EL : lag);
-    const int n_slots = EL + lag;
-    int u = 0;
-    for (int sl = 0; sl < n_slots; ++sl) {
-      tb->tile0[sl] = u;
-      if (sl < EL) {
-        const int mt = (tb->rows[sl] + kMoeBM - 1) / kMoeBM;
-        if (!backward) u += mt * n1;
-        else if (mt > 0) u += mt * (a.inter / kMoeBN) + (a.inter / kMoeBM) * n2;
-      }
-      if (sl >= lag) {
-        const int mt = (tb->rows[sl - lag] + kMoeBM - 1) / kMoeBM;
-        if (!backward) u += mt * n2;
-        else if (mt > 0) u += mt * n2 + (a.d_model / kMoeBM) * (2 * a.inter / kMoeBN);
-      }
-    }
-    tb->tile0[n_slots] = u;
-    tb->lag = lag;
-    tb->n_slots = n_slots;
-  }
+  if (threadIdx.x == 0) build_tile_order(a, tb, backward, pad, claim_ahead, static_cast<int>(gridDim.x));
   __syncthreads();
 }
 
@@ -165,7 +172,7 @@ struct TileInfo {
 };
 
 template <class Args>
-__device__ __forceinline__ TileInfo decode_tile(const Args& a, const MoeTables* tb, int t) {
+__host__ __device__ __forceinline__ TileInfo decode_tile(const Args& a, const MoeTables* tb, int t) {
   const int n1 = a.inter / 128, n2 = a.d_model / kMoeBN;
   // first slot whose tile range ends after t (slots without tiles have empty ranges): binary search
   int sl = 0, hi = tb->n_slots - 1;

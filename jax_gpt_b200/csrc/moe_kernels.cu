@@ -584,7 +584,7 @@ struct BwdTile {
   int el, phase, m, n;
 };
 
-__device__ __forceinline__ BwdTile decode_bwd_tile(const EpMoeArgs& a, const MoeTables* tb, int t) {
+__host__ __device__ __forceinline__ BwdTile decode_bwd_tile(const EpMoeArgs& a, const MoeTables* tb, int t) {
   int sl = 0, hi = tb->n_slots - 1;  // first slot whose tile range ends after t
   while (sl < hi) {
     const int mid = (sl + hi) >> 1;
@@ -1172,6 +1172,37 @@ long long* moe_prof_buffer(int which) {
   return enabled ? base + which * kMoeProfCtas * kMoeProfFields : nullptr;
 }
 }  // namespace
+
+int moe_tile_order_host(const int* rows, int e_local, int d_model, int inter, int grid_ctas, bool backward,
+                        int* tiles_out, int max_tiles, int* lag_out) {
+  if (e_local < 1 || e_local > kMoeMaxLocalExperts || d_model % 256 != 0 || inter % 256 != 0 || grid_ctas < 1) return -1;
+  MoeTables* tb = new MoeTables();
+  EpMoeArgs a{};
+  a.world = 1;
+  a.e_local = e_local;
+  a.d_model = d_model;
+  a.inter = inter;
+  for (int el = 0; el < e_local; ++el) tb->rows[el] = rows[el];
+  build_tile_order(a, tb, backward, /*pad=*/64, /*claim_ahead=*/kSchedAhead, grid_ctas);
+  const int n = tb->tile0[tb->n_slots];
+  if (lag_out != nullptr) *lag_out = tb->lag;
+  for (int t = 0; t < n && t < max_tiles; ++t) {
+    int el, phase, m, nn;
+    if (backward) {
+      const BwdTile ti = decode_bwd_tile(a, tb, t);
+      el = ti.el; phase = ti.phase; m = ti.m; nn = ti.n;
+    } else {
+      const TileInfo ti = decode_tile(a, tb, t);
+      el = ti.el; phase = ti.phase; m = ti.m; nn = ti.n;
+    }
+    tiles_out[4 * t] = el;
+    tiles_out[4 * t + 1] = phase;
+    tiles_out[4 * t + 2] = m;
+    tiles_out[4 * t + 3] = nn;
+  }
+  delete tb;
+  return n;
+}
 
 cudaError_t moe_profile_read(int which, long long* host_out) {
   if (which < 0 || which > 1) return cudaErrorInvalidValue;

@@ -70,6 +70,13 @@ struct EpMoeArgs {
 constexpr int kMoeProfCtas = 160, kMoeProfFields = 10;
 cudaError_t moe_profile_read(int which, long long* host_out);  // host_out[kMoeProfCtas * kMoeProfFields]
 
+// Host walk of the static tile order the bf16 kernels build on the device (same code, compiled for the host), for
+// tests: given the rows every local expert receives, writes (expert, phase, m, n) of every tile in order and
+// returns their number (-1 for shapes the kernels reject). Forward phases: 0 gate|up GEMM, 1 down GEMM; backward:
+// 0 dAct, 1 dX, 2 dW_down, 3 dW_gate|up. tiles_out holds 4 * max_tiles ints.
+int moe_tile_order_host(const int* rows, int e_local, int d_model, int inter, int grid_ctas, bool backward,
+                        int* tiles_out, int max_tiles, int* lag_out);
+
 // counts[e] = number of pairs routed to global expert e; pos[p] = rank of pair p within its expert.
 cudaError_t launch_moe_prepare(const int* idx, int n_pairs, int n_experts, int* counts, int* pos, cudaStream_t st);
 
