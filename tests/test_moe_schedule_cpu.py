@@ -103,3 +103,32 @@ def test_consumers_follow_their_producers_by_more_than_the_tiles_in_flight(shape
 def test_rejected_shapes():
     with pytest.raises(RuntimeError):
         _ops().moe_tile_order(torch.tensor([128], dtype=torch.int32), 2048 + 64, 512, 148, False)
+
+
+def test_random_routings_keep_the_invariants():
+    """Property check over random expert counts, row counts (many empty experts, a few huge ones), widths and grid
+    sizes: every tile exactly once, every dependency earlier in the order, the lag within [1, experts]."""
+    hyp = pytest.importorskip("hypothesis")
+    st = pytest.importorskip("hypothesis.strategies")
+
+    rows_st = st.lists(st.one_of(st.just(0), st.integers(1, 200), st.integers(200, 3000)), min_size=1, max_size=40)
+
+    @hyp.settings(max_examples=60, deadline=None)
+    @hyp.given(rows=rows_st, d_mult=st.integers(1, 4), i_mult=st.integers(1, 4), grid=st.sampled_from([1, 8, 132, 148]),
+               backward=st.booleans())
+    def check(rows, d_mult, i_mult, grid, backward):
+        D, I = 256 * d_mult, 256 * i_mult
+        tiles, lag = _order(rows, D, I, grid, backward)
+        expected = (_expected_backward if backward else _expected_forward)(rows, D, I)
+        assert len(tiles) == len(expected) and set(tiles) == expected
+        assert 1 <= lag <= len(rows)
+        at = {t: i for i, t in enumerate(tiles)}
+        for (el, ph, m, n), i in at.items():
+            if ph == 1:
+                n_prod = (I // 256) if backward else (I // 128)
+                assert all(at[(el, 0, m, k)] < i for k in range(n_prod))
+            if backward and ph == 3:
+                mt = (rows[el] + 127) // 128
+                assert all(at[(el, 0, mm, k)] < i for mm in range(mt) for k in range(I // 256))
+
+    check()
