@@ -8,7 +8,10 @@ skewed over the experts; routing is the group-limited sigmoid top-k (8 groups, t
 Times the fused one-kernel path (dispatch + grouped SwiGLU GEMMs + weighted combine over NVLink)
 against the library baseline (NCCL all_to_all + per-expert GEMMs + all_to_all), with CUDA events,
 max over ranks, and prints one JSON line with the roofline fraction
-``max(FLOPs / measured GEMM rate, NVLink bytes / measured link rate) / time``.
+``max(FLOPs / measured GEMM rate, NVLink bytes / measured link rate) / time`` (``roofline_fraction``) and the same with
+the HBM floor of the launch added (``hbm_floor_*_ms``, ``roofline_fraction_*_with_hbm``). With ``B200_MOE_PROFILE=1``
+in the environment the line also carries the kernels' per-CTA phase timeline (``fwd_timeline_us``, ``bwd_timeline_us``:
+dispatch, tile phase, time the load warp waited for dependencies and the MMA warp for operands / accumulators).
 """
 from __future__ import annotations
 
