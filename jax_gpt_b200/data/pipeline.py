@@ -69,8 +69,11 @@ class DataPipeline:
             try:
                 from .. import _ext
                 self._ops = _ext.ops()
+                # num_workers (worker processes of the reference's grain loader, jax_gpt/data/pipeline.py:117-125) sizes
+                # the prefetch queue of the single native reader thread: batches kept ready ahead of the training loop
+                depth = max(prefetch, 2 * int(getattr(config, "num_workers", 0)))
                 self._handle = self._ops.loader_create(self.path, self.seq_len, self.mb, self.shard_index,
-                                                       self.shard_count, prefetch, torch.cuda.is_available())
+                                                       self.shard_count, depth, torch.cuda.is_available())
             except Exception:
                 self._handle = None
         if self._handle is None:
